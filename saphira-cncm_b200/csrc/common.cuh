@@ -1,0 +1,201 @@
+// Internal declarations shared by the translation units of libncm_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <math.h>
+
+#include "../../include/ncm_b200.h"
+
+namespace ncmb {
+
+[[noreturn]] void fatal(const char *fmt, ...);
+
+#define CUDA_CHECK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) \
+    ::ncmb::fatal("cuda: %s:%d %s", __FILE__, __LINE__, cudaGetErrorString(e_)); } while (0)
+
+// ---- process-wide context: one stream, launch counter, kernel-class timers ----
+struct Ctx {
+    cudaStream_t stream = 0;
+    long long launches = 0;
+    int gemm_mode = 2;
+    int rng_mode = 0;
+    long long row_offset = 0;
+    int sm_count = 148;
+    bool inited = false;
+};
+Ctx &ctx();
+void ensure_device();            // fails loudly when no CUDA device is present
+inline cudaStream_t stream() { return ctx().stream; }
+
+void prof_begin(int klass, double flops, double bytes);
+void prof_end();
+struct ProfScope {
+    ProfScope(int klass, double flops = 0, double bytes = 0) { prof_begin(klass, flops, bytes); }
+    ~ProfScope() { prof_end(); }
+};
+
+// every kernel launch goes through this: counts it and surfaces launch errors
+#define LAUNCH(kernel, grid, block, smem, ...) do { \
+    kernel<<<(grid), (block), (smem), ::ncmb::stream()>>>(__VA_ARGS__); \
+    ::ncmb::ctx().launches++; \
+    cudaError_t le_ = cudaGetLastError(); \
+    if (le_ != cudaSuccess) ::ncmb::fatal("launch %s failed: %s (%s:%d)", #kernel, \
+        cudaGetErrorString(le_), __FILE__, __LINE__); } while (0)
+
+static inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline unsigned grid1d(int64_t n, int block) {
+    int64_t g = cdiv(n, block);
+    if (g < 1) g = 1;
+    if (g > 0x7fffffff) fatal("grid too large");
+    return (unsigned)g;
+}
+
+// ---- device workspace: bump allocator over one cudaMalloc'ed slab, grown on demand ----
+struct Workspace {
+    char *base = nullptr;
+    size_t cap = 0, off = 0;
+    bool measuring = false;              // alloc() only advances `off` (sizing pass before reserve)
+    void reserve(size_t bytes);          // frees and reallocates when too small (contents lost)
+    void reset() { off = 0; }
+    void *alloc(size_t bytes);           // 256-byte aligned; fatal on overflow
+    template <class T> T *get(size_t n) { return (T *)alloc(n * sizeof(T)); }
+    void release();
+};
+
+// ---- activation codes for fused epilogues ----
+enum Act { ACT_NONE = 0, ACT_GELU = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU2 = 4 };
+
+// y[M,N] = act(x[M,K] W[N,K]^T + bias[N]) (+ res[M,N]); res may alias y. ldx/ldy: row strides.
+struct GemmArgs {
+    const float *x = nullptr; int64_t ldx = 0;
+    const float *W = nullptr;            // [N][K] row-major
+    const float *bias = nullptr;
+    const float *res = nullptr; int64_t ldres = 0;
+    float *y = nullptr; int64_t ldy = 0;
+    int64_t M = 0; int N = 0, K = 0;
+    int act = ACT_NONE;
+    // gated MLP: y[m, j] = act(acc[m, 2j]) * acc[m, 2j+1] with W holding interleaved
+    // gate/up rows (N = 2 * hidden); y has N/2 columns.
+    int glu = 0;
+    const void *wshadow = nullptr;       // engine-specific preprocessed copy of W (or null)
+};
+void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
+void gemm_simt(const GemmArgs &a);
+bool gemm_tc_supported(const GemmArgs &a);
+void gemm_tc(const GemmArgs &a);
+
+// ---- normalisation / elementwise (kernels_elem.cu) ----
+void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps);
+void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy);
+void add_inplace(float *y, const float *x, int64_t n);
+void add_rows_bcast(float *y, const float *rowvec, int64_t rows, int C);             // y[r,:] += v[:]
+void embed_rows(const float *W, const int *idx_dev, float *y, int64_t n, int D);
+void glu_combine(const float *gu, float *y, int64_t rows, int Hh, int act);          // [rows][2Hh] halves
+void act_inplace(float *x, int64_t n, int act);
+void fill_f32(float *p, float v, int64_t n);
+void argmax_rows(const float *x, int64_t rows, int V, int *out);                    // first max wins
+
+// ---- generic strided conv / norm / resampling (kernels_vq.cu); layouts via strides ----
+struct NCT { int64_t sn, sc, st; };     // element strides of (batch, channel, time)
+static inline NCT ncl(int C, int T) { return NCT{(int64_t)C * T, (int64_t)T, 1}; }
+static inline NCT nlc(int C, int T) { return NCT{(int64_t)C * T, 1, (int64_t)C}; }
+void conv1d(const float *x, NCT xs, const float *W, const float *b, float *y, NCT ys,
+            int N, int Cin, int Cout, int T, int K, int stride, int pad, const float *add, float add_scale);
+void convT1d(const float *x, NCT xs, const float *W, const float *b, float *y, NCT ys,
+             int N, int Cin, int Cout, int T, int K, int stride);
+void groupnorm(const float *x, NCT xs, float *y, NCT ys, int N, int G, int C, int T);
+void interp_area(const float *x, NCT xs, float *y, NCT ys, int N, int C, int Tin, int Tout);
+void interp_linear(const float *x, NCT xs, float *y, NCT ys, int N, int C, int Tin, int Tout);
+
+// ---- attention (attention.cu) ----
+// Token-major fused attention. Row r owns query tokens [q_start[r], q_start[r+1]) and
+// attends to key segment 1 tokens [k1_start[r], k1_start[r+1]) plus (optionally) key
+// segment 2 tokens [k2_start[r], k2_start[r+1]); all keys of a row are visible to all of
+// its queries (bidirectional). With causal != 0 segment-1 key j (0-based inside the row)
+// is visible to query i only when j <= i + causal_off.
+struct AttnArgs {
+    const float *q; int64_t ldq;                 // q[token][h*hd + d]
+    const float *k1, *v1; int64_t ldk1;          // [token][kvh*hd + d]
+    const float *k2 = nullptr, *v2 = nullptr; int64_t ldk2 = 0;
+    float *out; int64_t ldo;                     // out[token][h*hd + d]
+    const int *q_start, *k1_start, *k2_start = nullptr;   // device int[rows+1]
+    const int *k1_len = nullptr;                 // optional device int[rows]: segment-1 lengths (strided caches)
+    int rows, H, Hkv, hd;
+    int max_q;                                   // max queries of any row (grid sizing)
+    int causal = 0, causal_off = 0;
+    int window = 0;                              // > 0: key j visible to query i only if |i - j| <= window
+    int64_t total_q = 0; double avg_keys = 0;    // for the profiler only
+};
+void attention(const AttnArgs &a);
+// reference-layout SDPA with an additive [Tq][Tkv] mask (ncm.h API)
+void sdpa_masked(const float *q, const float *k, const float *v, const float *mask, float *out,
+                 int B, int Hq, int Hkv, int Tq, int Tkv, int hd);
+// in place on the q / k slices of a token-major fused projection: optional per-head
+// RMSNorm (eps 1e-6) then half-split rotary embedding with table row pos[token].
+void qk_post(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int hd, int64_t ntok,
+             const float *qnorm_w, const float *knorm_w, const float *cos_t, const float *sin_t,
+             const int *pos_dev);
+
+// ---- sampling (sampling.cu) ----
+struct SampleArgs {
+    const float *logits;       // [rows_model][Lc][V]; cond rows first, uncond rows at +uncond_off rows
+    int Bn, Lc, V;
+    int64_t uncond_off;        // in rows; 0 = no CFG
+    double cfg_w;              // blend weight tw: (1+tw)*cond - tw*uncond
+    float temp; int top_k; float top_p;
+    float freq, mu, adj_a; int adj_w; float adj_d;
+    const double *allow_dev;   // [V] or null
+    double *cnt;               // [Bn][cnt_stride] persistent counts (null when penalties are off)
+    int cnt_stride;
+    int *hist; int *hist_len; int hist_stride;   // [Bn][hist_stride], [Bn]
+    const double *uniforms;    // [Bn][Lc] pre-drawn uniforms in [0,1) (temp > 0); null = counter-based
+    unsigned long long rng_seed = 0; long long rng_row0 = 0; int rng_level = 0;   // counter-based stream key
+    int *out;                  // [Bn][out_stride] picks written at out_off + t
+    int out_stride, out_off;
+    float *blend_out;          // optional [Bn][Lc][V] copy of the logits actually sampled from
+    float *scratch;            // [Bn][V] when V does not fit shared memory, else null
+};
+void sample_rows(const SampleArgs &a);
+size_t sample_scratch_floats(int Bn, int V);
+
+// ---- transformer block shared by the NCP stack, the VQ-VAE blocks and the decoder LMs ----
+enum NormKind { NORM_LAYER = 0, NORM_RMS = 1 };
+struct BlockWeights {
+    int norm = NORM_LAYER; float eps = 1e-6f;
+    const float *ln1w = nullptr, *ln1b = nullptr, *ln2w = nullptr, *ln2b = nullptr;
+    const float *qkvw = nullptr, *qkvb = nullptr;      // [C + 2*nkv*hd][C]
+    const float *ow = nullptr, *ob = nullptr;          // [C][C]
+    const float *qnw = nullptr, *knw = nullptr;        // per-head RMSNorm gains or null
+    const float *fcw = nullptr, *fcb = nullptr;        // ungated [Hh][C]; gated [2*Hh][C] (gate rows, then up rows)
+    const float *pw = nullptr, *pb = nullptr;          // [C][Hh]
+    int Hh = 0, gated = 0, act = ACT_GELU;
+};
+struct BlockBufs { float *ln, *qkv, *ctx, *mlp, *h; };   // [n][C], [n][C+2kvd], [n][C], [n][Hh or 2Hh], [n][Hh]
+struct AttnPlan {
+    const int *q_start = nullptr, *k1_start = nullptr, *k1_len = nullptr, *k2_start = nullptr;
+    const float *k1 = nullptr, *v1 = nullptr; int64_t ldk1 = 0;   // null: segment 1 is this pass's own K/V
+    int self_is_k2 = 0;                  // segment 2 = this pass's own K/V (k2_start = q_start)
+    int rows = 0, max_q = 0, causal = 0, causal_off = 0, window = 0;
+    const int *pos = nullptr; const float *cos_t = nullptr, *sin_t = nullptr;
+    int64_t total_q = 0; double avg_keys = 0;
+    // after the K/V of this pass are final (norm + rope applied) they are stored here:
+    float *kv_store = nullptr; int64_t kv_pitch = 0;   // row pitch in floats; rows = tokens, width 2*kvd
+    int kv_rows_per_seq = 0; int64_t kv_seq_pitch = 0; // > 0: token t of sequence s goes to s*kv_seq_pitch + t*kv_pitch
+    int kv_only = 0;                     // stop after the K/V of this pass are stored (last layer of a cache fill)
+};
+void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights &w, const BlockBufs &b, const AttnPlan &p);
+void apply_norm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, int kind, float eps);
+
+// weight lookup helpers
+Tensor *wget(WeightStore *ws, const char *fmt, ...);      // null when missing
+Tensor *wneed(WeightStore *ws, const char *fmt, ...);     // fatal when missing
+float *dev_concat_rows(const float *a, int64_t na, const float *b, int64_t nb);   // new buffer [na+nb]; null parts -> zeros
+void upload(void *dev, const void *host, size_t bytes);
+void *dev_alloc(size_t bytes);
+void dev_free(void *p);
+
+} // namespace ncmb

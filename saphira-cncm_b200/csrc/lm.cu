@@ -1,0 +1,404 @@
+// GPT-2 and Qwen2 decoders with a KV cache, batched over independent prompts
+// (reference src/gpt2.c, src/qwen.c). The reference recomputes the whole context for
+// every new token at batch 1 (gpt2.c:187-198, qwen.c:217-227); causal attention makes
+// a cached, batched run produce the same logits, so each row here equals one
+// reference run. Layers reuse the transformer block of the NCP stack.
+#include "common.cuh"
+
+#include <vector>
+
+using namespace ncmb;
+
+typedef struct TokState TokState;
+extern "C" {
+// host tokenizer of the reference (src/ncm.h:294-303); optional at link time
+TokState *tok_load(const NCMConfig *c, const char *asset_dir) __attribute__((weak));
+void tok_free(TokState *t) __attribute__((weak));
+int tok_encode(TokState *t, const char *text, int *out, int cap) __attribute__((weak));
+int tok_decode(TokState *t, const int *ids, int n, char *out, int cap, int skip_special) __attribute__((weak));
+}
+
+struct NcmbLM {
+    NCMConfig cfg;
+    WeightStore ws{};
+    int is_qwen = 0;
+    int NL = 0, H = 0, nkv = 0, C = 0, hd = 0, I = 0, n_ctx = 0, V = 0, eos = -1;
+    const float *wte = nullptr, *wpe = nullptr, *lnfw = nullptr, *lnfb = nullptr;
+    float *cosb = nullptr, *sinb = nullptr;
+    std::vector<BlockWeights> blocks;
+    std::vector<void *> owned;
+    Workspace work;
+};
+
+static const float *need(WeightStore *ws, const char *who, const char *fmt, int li, const char *leaf) {
+    char key[192];
+    snprintf(key, sizeof key, fmt, li, leaf);
+    Tensor *t = weights_get(ws, key);
+    if (!t) { fprintf(stderr, "%s: missing tensor %s\n", who, key); exit(1); }
+    return t->data;
+}
+static const float *maybe(WeightStore *ws, const char *fmt, int li, const char *leaf) {
+    char key[192];
+    snprintf(key, sizeof key, fmt, li, leaf);
+    Tensor *t = weights_get(ws, key);
+    return t ? t->data : nullptr;
+}
+
+extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights) {
+    ensure_device();
+    (void)bf16_weights;      // weights are used as stored; files already rounded to bf16 load unchanged
+    NcmbLM *m = new NcmbLM();
+    m->cfg = *c; m->is_qwen = is_qwen;
+    if (weights_load(&m->ws, weights)) { delete m; return nullptr; }
+    WeightStore *ws = &m->ws;
+    m->NL = c->n_layer; m->H = c->n_head; m->C = c->n_embd; m->hd = m->C / m->H;
+    m->nkv = (is_qwen && c->n_kv_heads > 0) ? c->n_kv_heads : c->n_head;
+    m->eos = c->eos_token_id;
+    if (m->hd != 16 && m->hd != 32 && m->hd != 64 && m->hd != 128) fatal("head dim %d not supported", m->hd);
+    int C = m->C, kvd = m->nkv * m->hd;
+    if (!is_qwen) {
+        m->n_ctx = c->context_length > 0 ? c->context_length : 1024;
+        Tensor *wte = weights_get(ws, "wte.weight");
+        if (!wte) { fprintf(stderr, "gpt2: missing tensor wte.weight\n"); exit(1); }
+        m->V = (int)wte->shape[0]; m->wte = wte->data;
+        m->wpe = need(ws, "gpt2", "%.0dwpe.%s", 0, "weight");
+        m->lnfw = need(ws, "gpt2", "%.0dln_f.%s", 0, "weight");
+        m->lnfb = need(ws, "gpt2", "%.0dln_f.%s", 0, "bias");
+        m->I = 4 * C;
+        for (int li = 0; li < m->NL; li++) {
+            BlockWeights w;
+            w.norm = NORM_LAYER; w.eps = 1e-5f;
+            w.ln1w = need(ws, "gpt2", "h.%d.ln_1.%s", li, "weight"); w.ln1b = need(ws, "gpt2", "h.%d.ln_1.%s", li, "bias");
+            w.qkvw = need(ws, "gpt2", "h.%d.attn.c_attn.%s", li, "weight"); w.qkvb = maybe(ws, "h.%d.attn.c_attn.%s", li, "bias");
+            w.ow = need(ws, "gpt2", "h.%d.attn.c_proj.%s", li, "weight"); w.ob = maybe(ws, "h.%d.attn.c_proj.%s", li, "bias");
+            w.ln2w = need(ws, "gpt2", "h.%d.ln_2.%s", li, "weight"); w.ln2b = need(ws, "gpt2", "h.%d.ln_2.%s", li, "bias");
+            w.fcw = need(ws, "gpt2", "h.%d.mlp.c_fc.%s", li, "weight"); w.fcb = maybe(ws, "h.%d.mlp.c_fc.%s", li, "bias");
+            w.pw = need(ws, "gpt2", "h.%d.mlp.c_proj.%s", li, "weight"); w.pb = maybe(ws, "h.%d.mlp.c_proj.%s", li, "bias");
+            w.Hh = m->I; w.gated = 0; w.act = ACT_GELU_TANH;
+            m->blocks.push_back(w);
+        }
+    } else {
+        m->n_ctx = c->context_length > 0 ? c->context_length : 4096;
+        double theta = c->rope_theta > 0 ? c->rope_theta : 1000000.0;
+        Tensor *te = weights_get(ws, "model.embed_tokens.weight");
+        if (!te) { fprintf(stderr, "qwen: missing tensor model.embed_tokens.weight\n"); exit(1); }
+        m->V = (int)te->shape[0]; m->wte = te->data;
+        m->lnfw = need(ws, "qwen", "%.0dmodel.norm.%s", 0, "weight");
+        Tensor *tg = weights_get(ws, "model.layers.0.mlp.gate_proj.weight");
+        if (!tg) { fprintf(stderr, "qwen: missing tensor model.layers.0.mlp.gate_proj.weight\n"); exit(1); }
+        m->I = (int)tg->shape[0];
+        for (int li = 0; li < m->NL; li++) {
+            BlockWeights w;
+            w.norm = NORM_RMS; w.eps = 1e-6f;
+            w.ln1w = need(ws, "qwen", "model.layers.%d.input_layernorm.%s", li, "weight");
+            const float *qw = need(ws, "qwen", "model.layers.%d.self_attn.q_proj.%s", li, "weight");
+            const float *qb = need(ws, "qwen", "model.layers.%d.self_attn.q_proj.%s", li, "bias");
+            const float *kw = need(ws, "qwen", "model.layers.%d.self_attn.k_proj.%s", li, "weight");
+            const float *kb = need(ws, "qwen", "model.layers.%d.self_attn.k_proj.%s", li, "bias");
+            const float *vw = need(ws, "qwen", "model.layers.%d.self_attn.v_proj.%s", li, "weight");
+            const float *vb = need(ws, "qwen", "model.layers.%d.self_attn.v_proj.%s", li, "bias");
+            // fused [C + 2*kvd][C] projection: q rows, then k rows, then v rows
+            float *kvw = dev_concat_rows(kw, (int64_t)kvd * C, vw, (int64_t)kvd * C);
+            float *qkvw = dev_concat_rows(qw, (int64_t)C * C, kvw, (int64_t)2 * kvd * C);
+            float *kvb = dev_concat_rows(kb, kvd, vb, kvd);
+            float *qkvb = dev_concat_rows(qb, C, kvb, 2 * kvd);
+            CUDA_CHECK(cudaStreamSynchronize(stream()));
+            dev_free(kvw); dev_free(kvb);
+            m->owned.push_back(qkvw); m->owned.push_back(qkvb);
+            w.qkvw = qkvw; w.qkvb = qkvb;
+            w.ow = need(ws, "qwen", "model.layers.%d.self_attn.o_proj.%s", li, "weight");
+            w.ln2w = need(ws, "qwen", "model.layers.%d.post_attention_layernorm.%s", li, "weight");
+            const float *gw = need(ws, "qwen", "model.layers.%d.mlp.gate_proj.%s", li, "weight");
+            const float *uw = need(ws, "qwen", "model.layers.%d.mlp.up_proj.%s", li, "weight");
+            float *gu = dev_concat_rows(gw, (int64_t)m->I * C, uw, (int64_t)m->I * C);
+            m->owned.push_back(gu);
+            w.fcw = gu;
+            w.pw = need(ws, "qwen", "model.layers.%d.mlp.down_proj.%s", li, "weight");
+            w.Hh = m->I; w.gated = 1; w.act = ACT_SILU;
+            m->blocks.push_back(w);
+        }
+        // rotary tables [n_ctx][hd], angle t * theta^(-2d/hd), pair-duplicated (qwen.c:85-110)
+        int hd = m->hd, h = hd / 2, T = m->n_ctx;
+        std::vector<float> hc((size_t)T * hd), hs((size_t)T * hd);
+        for (int t = 0; t < T; t++) for (int d = 0; d < h; d++) {
+            double a = (double)t * pow(theta, -(double)(2 * d) / (double)hd);
+            float co = (float)cos(a), si = (float)sin(a);
+            hc[(size_t)t * hd + d] = co; hc[(size_t)t * hd + d + h] = co;
+            hs[(size_t)t * hd + d] = si; hs[(size_t)t * hd + d + h] = si;
+        }
+        m->cosb = (float *)dev_alloc(hc.size() * 4); m->sinb = (float *)dev_alloc(hs.size() * 4);
+        upload(m->cosb, hc.data(), hc.size() * 4); upload(m->sinb, hs.data(), hs.size() * 4);
+        m->owned.push_back(m->cosb); m->owned.push_back(m->sinb);
+    }
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    return m;
+}
+
+extern "C" void ncmb_lm_close(NcmbLM *m) {
+    if (!m) return;
+    for (void *p : m->owned) dev_free(p);
+    m->work.release();
+    weights_free(&m->ws);
+    delete m;
+}
+extern "C" int ncmb_lm_vocab(const NcmbLM *m) { return m->V; }
+
+namespace {
+
+struct LMRun {
+    NcmbLM *m;
+    int B, np, cap;
+    std::vector<float *> kv;      // per layer [B][cap][2*kvd]
+    BlockBufs bufs{};
+    float *x = nullptr, *last = nullptr, *logits = nullptr, *samp_scr = nullptr;
+    int *ids_d = nullptr, *pos_d = nullptr, *start_np = nullptr, *start_1 = nullptr, *kstart = nullptr;
+    int *posmat = nullptr, *lenmat = nullptr, *out_d = nullptr, *last_rows = nullptr;
+    double *uni_d = nullptr;
+};
+
+void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
+    NcmbLM *m = r.m;
+    int C = m->C, kvd = m->nkv * m->hd, Wq = C + 2 * kvd;
+    int64_t nmax = (int64_t)r.B * r.np;
+    r.kv.clear();
+    for (int li = 0; li < m->NL; li++) r.kv.push_back(w.get<float>((size_t)r.B * r.cap * 2 * kvd));
+    r.x = w.get<float>((size_t)nmax * C);
+    r.bufs.ln = w.get<float>((size_t)nmax * C);
+    r.bufs.qkv = w.get<float>((size_t)nmax * Wq);
+    r.bufs.ctx = w.get<float>((size_t)nmax * C);
+    r.bufs.mlp = m->is_qwen ? w.get<float>((size_t)nmax * 2 * m->I) : nullptr;
+    r.bufs.h = w.get<float>((size_t)nmax * m->I);
+    r.last = w.get<float>((size_t)r.B * C);
+    r.logits = w.get<float>((size_t)(all_logits ? nmax : r.B) * m->V);
+    size_t ss = sample_scratch_floats(r.B, m->V);
+    r.samp_scr = ss ? w.get<float>(ss) : nullptr;
+    r.ids_d = w.get<int>((size_t)nmax);
+    r.pos_d = w.get<int>((size_t)nmax);
+    r.start_np = w.get<int>(r.B + 1);
+    r.start_1 = w.get<int>(r.B + 1);
+    r.kstart = w.get<int>(r.B + 1);
+    r.posmat = w.get<int>((size_t)r.cap * r.B);
+    r.lenmat = w.get<int>((size_t)r.cap * r.B);
+    r.out_d = w.get<int>((size_t)r.B * (n_new > 0 ? n_new : 1));
+    r.last_rows = w.get<int>(r.B);
+    r.uni_d = w.get<double>((size_t)(n_new > 0 ? n_new : 1) * r.B);
+}
+
+void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
+    NcmbLM *m = r.m;
+    embed_rows(m->wte, ids_d, r.x, n, m->C);
+    if (!m->is_qwen) {
+        embed_rows(m->wpe, pos_d, r.bufs.ctx, n, m->C);
+        add_inplace(r.x, r.bufs.ctx, n * m->C);
+    }
+}
+
+void lm_head(LMRun &r, const float *h, int64_t rows, float *logits) {
+    NcmbLM *m = r.m;
+    apply_norm(h, m->lnfw, m->lnfb, r.bufs.ln, rows, m->C, m->is_qwen ? NORM_RMS : NORM_LAYER, m->is_qwen ? 1e-6f : 1e-5f);
+    GemmArgs g;
+    g.x = r.bufs.ln; g.ldx = m->C; g.W = m->wte; g.y = logits; g.ldy = m->V; g.M = rows; g.N = m->V; g.K = m->C;
+    gemm(g);
+}
+
+// prompt tokens of all rows through every layer, K/V into the cache
+void lm_prefill(LMRun &r) {
+    NcmbLM *m = r.m;
+    int kvd = m->nkv * m->hd;
+    int64_t n = (int64_t)r.B * r.np;
+    lm_embed(r, r.ids_d, r.pos_d, n);
+    AttnPlan p;
+    p.q_start = p.k1_start = r.start_np;
+    p.rows = r.B; p.max_q = r.np; p.causal = 1;
+    p.pos = r.pos_d;
+    if (m->is_qwen) { p.cos_t = m->cosb; p.sin_t = m->sinb; }
+    p.total_q = n; p.avg_keys = (r.np + 1) / 2.0;
+    p.kv_pitch = 2 * kvd; p.kv_rows_per_seq = r.np; p.kv_seq_pitch = (int64_t)r.cap * 2 * kvd;
+    for (int li = 0; li < m->NL; li++) {
+        p.kv_store = r.kv[li];
+        run_block(r.x, n, m->C, m->H, m->nkv, m->blocks[li], r.bufs, p);
+    }
+}
+
+// one new token per row at absolute position `pos`
+void lm_decode_step(LMRun &r, const int *ids_d, int pos) {
+    NcmbLM *m = r.m;
+    int kvd = m->nkv * m->hd;
+    lm_embed(r, ids_d, r.posmat + (size_t)pos * r.B, r.B);
+    AttnPlan p;
+    p.q_start = r.start_1; p.k1_start = r.kstart; p.k1_len = r.lenmat + (size_t)pos * r.B;
+    p.ldk1 = 2 * kvd;
+    p.rows = r.B; p.max_q = 1;
+    p.pos = r.posmat + (size_t)pos * r.B;
+    if (m->is_qwen) { p.cos_t = m->cosb; p.sin_t = m->sinb; }
+    p.total_q = r.B; p.avg_keys = pos + 1;
+    p.kv_pitch = 2 * kvd; p.kv_rows_per_seq = 1; p.kv_seq_pitch = (int64_t)r.cap * 2 * kvd;
+    for (int li = 0; li < m->NL; li++) {
+        p.k1 = r.kv[li]; p.v1 = r.kv[li] + kvd;
+        p.kv_store = r.kv[li] + (size_t)pos * 2 * kvd;
+        run_block(r.x, r.B, m->C, m->H, m->nkv, m->blocks[li], r.bufs, p);
+    }
+}
+
+void lm_setup(LMRun &r, const int *prompts, int n_new, bool all_logits) {
+    NcmbLM *m = r.m;
+    int B = r.B, np = r.np, cap = r.cap;
+    Workspace sizing;
+    sizing.measuring = true;
+    lm_layout(r, sizing, n_new, all_logits);
+    m->work.reserve(sizing.off + 4096);
+    m->work.reset();
+    lm_layout(r, m->work, n_new, all_logits);
+    std::vector<int> pos((size_t)B * np), st(B + 1), s1(B + 1), ks(B + 1), pm((size_t)cap * B), lm((size_t)cap * B), lr(B);
+    for (int b = 0; b < B; b++) for (int t = 0; t < np; t++) pos[(size_t)b * np + t] = t;
+    for (int b = 0; b <= B; b++) { st[b] = b * np; s1[b] = b; ks[b] = b * cap; }
+    for (int s = 0; s < cap; s++) for (int b = 0; b < B; b++) { pm[(size_t)s * B + b] = s; lm[(size_t)s * B + b] = s + 1; }
+    for (int b = 0; b < B; b++) lr[b] = b * np + np - 1;
+    upload(r.ids_d, prompts, (size_t)B * np * 4);
+    upload(r.pos_d, pos.data(), pos.size() * 4);
+    upload(r.start_np, st.data(), st.size() * 4);
+    upload(r.start_1, s1.data(), s1.size() * 4);
+    upload(r.kstart, ks.data(), ks.size() * 4);
+    upload(r.posmat, pm.data(), pm.size() * 4);
+    upload(r.lenmat, lm.data(), lm.size() * 4);
+    upload(r.last_rows, lr.data(), lr.size() * 4);
+}
+
+void lm_sample(LMRun &r, float temp, int top_k, float top_p, int step, int n_new) {
+    NcmbLM *m = r.m;
+    SampleArgs s{};
+    s.logits = r.logits; s.Bn = r.B; s.Lc = 1; s.V = m->V; s.uncond_off = 0; s.cfg_w = 0;
+    s.temp = temp; s.top_k = top_k; s.top_p = top_p;
+    s.freq = 0; s.mu = 0; s.adj_a = 0; s.adj_w = 0; s.adj_d = 1;
+    s.uniforms = temp > 0 ? r.uni_d + (size_t)step * r.B : nullptr;
+    s.out = r.out_d; s.out_stride = n_new; s.out_off = step;
+    s.scratch = r.samp_scr;
+    sample_rows(s);
+}
+
+__global__ void k_take_col(const int *__restrict__ src, int stride, int col, int n, int *__restrict__ dst) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[(size_t)i * stride + col];
+}
+
+} // namespace
+
+extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, int n_new,
+                                float temp, int top_k, float top_p, unsigned long long seed, int eos, int *out) {
+    ensure_device();
+    if (B <= 0 || np <= 0 || n_new <= 0) return 0;
+    if (np + n_new - 1 > m->n_ctx) fatal("%s: context overflow (%d + %d > %d)", m->is_qwen ? "qwen" : "gpt2", np, n_new, m->n_ctx);
+    LMRun r;
+    r.m = m; r.B = B; r.np = np; r.cap = np + n_new;
+    lm_setup(r, prompts, n_new, false);
+    if (temp > 0) {
+        // every row replays the reference's stream for this seed: one draw per generated token
+        std::vector<double> u((size_t)n_new * B);
+        unsigned long long st = seed ? seed : 0x12345678ULL;
+        for (int s = 0; s < n_new; s++) {
+            double v = (double)(rng_next(&st) >> 11) * (1.0 / 9007199254740992.0);
+            for (int b = 0; b < B; b++) u[(size_t)s * B + b] = v;
+        }
+        upload(r.uni_d, u.data(), u.size() * 8);
+    }
+    lm_prefill(r);
+    embed_rows(r.x, r.last_rows, r.last, B, m->C);           // hidden state of each row's last prompt token
+    lm_head(r, r.last, B, r.logits);
+    std::vector<int> col(B);
+    std::vector<char> done(B, 0);
+    int produced = 0;
+    for (int s = 0; s < n_new; s++) {
+        lm_sample(r, temp, top_k, top_p, s, n_new);
+        produced = s + 1;
+        LAUNCH(k_take_col, (unsigned)cdiv(B, 128), 128, 0, r.out_d, n_new, s, B, r.ids_d);
+        if (eos >= 0) {
+            mem_d2h(col.data(), r.ids_d, (size_t)B * 4);
+            bool all = true;
+            for (int b = 0; b < B; b++) { if (col[b] == eos) done[b] = 1; all = all && done[b]; }
+            if (all) break;
+        }
+        if (s + 1 == n_new) break;
+        lm_decode_step(r, r.ids_d, np + s);
+        lm_head(r, r.x, B, r.logits);
+    }
+    std::vector<int> tmp((size_t)B * n_new);
+    mem_d2h(tmp.data(), r.out_d, tmp.size() * 4);
+    for (int b = 0; b < B; b++) {
+        bool ended = false;
+        for (int s = 0; s < n_new; s++) {
+            int v = (s < produced && !ended) ? tmp[(size_t)b * n_new + s] : -1;
+            out[(size_t)b * n_new + s] = v;
+            if (eos >= 0 && v == eos) ended = true;
+        }
+    }
+    return produced;
+}
+
+extern "C" void ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, float *out_host) {
+    ensure_device();
+    if (T <= 0) return;
+    if (T > m->n_ctx) fatal("%s: context overflow", m->is_qwen ? "qwen" : "gpt2");
+    LMRun r;
+    r.m = m; r.B = 1; r.np = T; r.cap = T;
+    lm_setup(r, ids, 0, !last_only);
+    lm_prefill(r);
+    if (last_only) {
+        lm_head(r, r.x + (size_t)(T - 1) * m->C, 1, r.logits);
+        mem_d2h(out_host, r.logits, (size_t)m->V * 4);
+    } else {
+        // ln buffer holds T rows; head over all positions
+        lm_head(r, r.x, T, r.logits);
+        mem_d2h(out_host, r.logits, (size_t)T * m->V * 4);
+    }
+}
+
+static int lm_cmd_gen(const NCMConfig *c, const char *weights, const char *adir, const char *prompt, const char *ids_csv,
+                      int n_new, float temp, int top_k, float top_p, unsigned long long seed, int is_qwen) {
+    const char *who = is_qwen ? "qwen-gen" : "gpt2-gen";
+    NcmbLM *m = ncmb_lm_open(c, weights, is_qwen, 0);
+    if (!m) return 1;
+    TokState *tok = tok_load ? tok_load(c, adir) : nullptr;
+    const int cap = is_qwen ? 8192 : 4096;
+    std::vector<int> ids(cap);
+    int n = 0;
+    if (ids_csv) {
+        const char *p = ids_csv;
+        while (*p && n < cap) { ids[n++] = atoi(p); while (*p && *p != ',') p++; if (*p) p++; }
+    } else if (prompt) {
+        if (!tok || !tok_encode) { fprintf(stderr, "%s: text prompts need the host tokenizer linked in; pass --ids\n", who); return 2; }
+        n = tok_encode(tok, prompt, ids.data(), cap);
+    } else {
+        fprintf(stderr, is_qwen ? "qwen-gen needs --prompt TEXT | --ids CSV\n" : "gpt2-gen needs --prompt TEXT or --ids CSV\n");
+        return 2;
+    }
+    if (n == 0) { fprintf(stderr, "%s: empty prompt\n", who); return 2; }
+    int room = m->n_ctx - n + 1;
+    if (n_new > room) { fprintf(stderr, "%s: context overflow\n", is_qwen ? "qwen" : "gpt2"); n_new = room > 0 ? room : 0; }
+    std::vector<int> gen(n_new > 0 ? n_new : 1);
+    int ngen = 0;
+    if (n_new > 0) {
+        ncmb_lm_generate(m, ids.data(), 1, n, n_new, temp, top_k, top_p, seed, m->eos, gen.data());
+        while (ngen < n_new && gen[ngen] >= 0) ngen++;
+    }
+    printf("ids:");
+    for (int i = 0; i < ngen; i++) printf(" %d", gen[i]);
+    printf("\n");
+    if (tok && tok_decode) {
+        char *text = (char *)malloc(65536);
+        tok_decode(tok, gen.data(), ngen, text, 65536, 1);
+        printf("%s\n", text);
+        free(text);
+    }
+    if (tok && tok_free) tok_free(tok);
+    ncmb_lm_close(m);
+    return 0;
+}
+
+extern "C" int gpt2_cmd_gen(const NCMConfig *c, const char *weights, const char *adir, const char *prompt, const char *ids_csv,
+                            int n_new, float temp, int top_k, float top_p, unsigned long long seed) {
+    return lm_cmd_gen(c, weights, adir, prompt, ids_csv, n_new, temp, top_k, top_p, seed, 0);
+}
+extern "C" int qwen_cmd_gen(const NCMConfig *c, const char *weights, const char *adir, const char *prompt, const char *ids_csv,
+                            int n_new, float temp, int top_k, float top_p, unsigned long long seed) {
+    return lm_cmd_gen(c, weights, adir, prompt, ids_csv, n_new, temp, top_k, top_p, seed, 1);
+}

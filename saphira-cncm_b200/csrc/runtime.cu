@@ -1,0 +1,472 @@
+// Runtime of libncm_b200.so: device context, tensors, arenas, NCM1 weight files,
+// .conf parsing, kernel-class timers. Replaces the reference's src/tensor.c for a
+// B200 build: weights live in one HBM slab per file instead of one cudaMalloc per
+// tensor, and every copy goes through the library's stream.
+#include "common.cuh"
+
+#include <stdarg.h>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+namespace ncmb {
+
+void fatal(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    fprintf(stderr, "[ncm_b200] fatal: ");
+    vfprintf(stderr, fmt, ap);
+    fprintf(stderr, "\n");
+    va_end(ap);
+    exit(1);
+}
+
+Ctx &ctx() {
+    static Ctx c;
+    return c;
+}
+
+void ensure_device() {
+    Ctx &c = ctx();
+    if (c.inited) return;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0)
+        fatal("no CUDA device: this library has no CPU path (%s)",
+              e != cudaSuccess ? cudaGetErrorString(e) : "device count 0");
+    int dev = 0;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    cudaDeviceProp p;
+    CUDA_CHECK(cudaGetDeviceProperties(&p, dev));
+    if (p.major < 10)
+        fatal("device %s is sm_%d%d; this build targets sm_100a only", p.name, p.major, p.minor);
+    c.sm_count = p.multiProcessorCount;
+    const char *gm = getenv("NCM_B200_GEMM");
+    if (gm) c.gemm_mode = atoi(gm);
+    const char *rm = getenv("NCM_B200_RNG");
+    if (rm) c.rng_mode = atoi(rm);
+    c.inited = true;
+}
+
+// ------------------------------------------------------------------ profiler
+struct ProfRec { int klass; double flops, bytes; cudaEvent_t a, b; };
+struct Prof {
+    bool on = false;
+    std::vector<cudaEvent_t> pool;
+    std::vector<ProfRec> open;
+    ProfRec cur; bool in_scope = false; int depth = 0;
+    long long launches[NCMB_K_COUNT] = {0};
+    double ms[NCMB_K_COUNT] = {0}, flops[NCMB_K_COUNT] = {0}, bytes[NCMB_K_COUNT] = {0};
+    cudaEvent_t get() {
+        if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
+        cudaEvent_t e;
+        CUDA_CHECK(cudaEventCreate(&e));
+        return e;
+    }
+    void drain() {
+        if (open.empty()) return;
+        CUDA_CHECK(cudaEventSynchronize(open.back().b));
+        for (auto &r : open) {
+            float t = 0;
+            CUDA_CHECK(cudaEventElapsedTime(&t, r.a, r.b));
+            ms[r.klass] += t; flops[r.klass] += r.flops; bytes[r.klass] += r.bytes; launches[r.klass]++;
+            pool.push_back(r.a); pool.push_back(r.b);
+        }
+        open.clear();
+    }
+};
+static Prof &prof() { static Prof p; return p; }
+
+void prof_begin(int klass, double flops, double bytes) {
+    Prof &p = prof();
+    if (!p.on) return;
+    if (p.depth++ > 0) return;               // nested scopes fold into the outermost one
+    p.cur = ProfRec{klass, flops, bytes, p.get(), p.get()};
+    CUDA_CHECK(cudaEventRecord(p.cur.a, stream()));
+}
+void prof_end() {
+    Prof &p = prof();
+    if (!p.on) return;
+    if (--p.depth > 0) return;
+    CUDA_CHECK(cudaEventRecord(p.cur.b, stream()));
+    p.open.push_back(p.cur);
+    if (p.open.size() >= 8192) p.drain();
+}
+
+// ------------------------------------------------------------------ workspace
+void Workspace::reserve(size_t bytes) {
+    if (bytes <= cap) return;
+    ensure_device();
+    if (base) { CUDA_CHECK(cudaStreamSynchronize(stream())); CUDA_CHECK(cudaFree(base)); }
+    cudaError_t e = cudaMalloc((void **)&base, bytes);
+    if (e != cudaSuccess) fatal("workspace of %.1f MB: %s", bytes / 1048576.0, cudaGetErrorString(e));
+    cap = bytes; off = 0;
+}
+void *Workspace::alloc(size_t bytes) {
+    off = (off + 255) & ~(size_t)255;
+    if (measuring) { void *fake = (void *)(uintptr_t)(4096 + off); off += bytes; return fake; }
+    if (off + bytes > cap) fatal("workspace overflow: need %zu of %zu bytes", off + bytes, cap);
+    void *p = base + off;
+    off += bytes;
+    return p;
+}
+void Workspace::release() {
+    if (base) { cudaStreamSynchronize(stream()); cudaFree(base); }
+    base = nullptr; cap = off = 0;
+}
+
+} // namespace ncmb
+
+using namespace ncmb;
+
+// weight slabs: Tensor.data pointers that live inside a slab are not cudaFree'd one by one
+static std::unordered_set<const void *> &slab_members() { static std::unordered_set<const void *> s; return s; }
+static std::unordered_map<const void *, void *> &slab_of_store() { static std::unordered_map<const void *, void *> s; return s; }
+
+extern "C" {
+
+// ------------------------------------------------------------------ tensors
+int64_t tensor_numel(int ndim, const int64_t *shape) {
+    int64_t n = 1;
+    for (int i = 0; i < ndim; i++) n *= shape[i];
+    return n;
+}
+
+Tensor *tensor_alloc(int ndim, const int64_t *shape) {
+    ensure_device();
+    Tensor *t = (Tensor *)calloc(1, sizeof(Tensor));
+    if (!t) fatal("oom tensor");
+    t->ndim = ndim;
+    for (int i = 0; i < ndim; i++) t->shape[i] = shape[i];
+    t->n = tensor_numel(ndim, shape);
+    CUDA_CHECK(cudaMalloc((void **)&t->data, (size_t)(t->n > 0 ? t->n : 1) * sizeof(float)));
+    return t;
+}
+
+void tensor_free(Tensor *t) {
+    if (!t) return;
+    if (!slab_members().count(t->data)) {
+        cudaStreamSynchronize(stream());
+        cudaFree(t->data);
+    }
+    free(t);
+}
+
+void mem_d2h(void *h, const void *d, size_t n) {
+    ensure_device();
+    CUDA_CHECK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+}
+void mem_h2d(void *d, const void *h, size_t n) {
+    ensure_device();
+    CUDA_CHECK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));   // h may be freed by the caller right after
+}
+void mem_d2d(void *d, const void *s, size_t n) {
+    ensure_device();
+    CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, stream()));
+}
+void tensor_to_host(const Tensor *t, float *out) { mem_d2h(out, t->data, (size_t)t->n * sizeof(float)); }
+void tensor_to_backend(Tensor *t, const float *in) { mem_h2d(t->data, in, (size_t)t->n * sizeof(float)); }
+
+void *backend_to_host(const float *d, size_t nbytes) {
+    void *h = malloc(nbytes ? nbytes : 1);
+    if (!h) fatal("oom host copy");
+    mem_d2h(h, d, nbytes);
+    return h;
+}
+
+// ------------------------------------------------------------------ arenas
+static unsigned char *arena_base = nullptr, *parena_base = nullptr;
+static size_t arena_size = 0, arena_off = 0, parena_size = 0, parena_off = 0;
+
+void arena_free(void) {
+    if (!arena_base) return;
+    cudaStreamSynchronize(stream());
+    cudaFree(arena_base);
+    arena_base = nullptr; arena_size = arena_off = 0;
+}
+void arena_init(size_t bytes) {
+    ensure_device();
+    arena_free();
+    cudaError_t e = cudaMalloc((void **)&arena_base, bytes);
+    if (e != cudaSuccess) fatal("arena of %zu MB: %s", bytes >> 20, cudaGetErrorString(e));
+    arena_size = bytes; arena_off = 0;
+}
+void arena_init_default(void) {
+    const char *e = getenv("NCM_ARENA_MB");
+    size_t mb = e ? (size_t)atol(e) : 4096;
+    if (mb < 64) mb = 64;
+    arena_init(mb << 20);
+}
+float *arena_alloc(size_t n_floats) {
+    size_t need = n_floats * sizeof(float);
+    arena_off = (arena_off + 255) & ~(size_t)255;
+    if (!arena_base || arena_off + need > arena_size) {
+        fprintf(stderr, "arena overflow (%zu > %zu MB); raise NCM_ARENA_MB\n", arena_off + need, arena_size >> 20);
+        exit(1);
+    }
+    float *p = (float *)(arena_base + arena_off);
+    arena_off += need;
+    return p;
+}
+void arena_reset(void) { arena_off = 0; }
+
+void parena_init(size_t bytes) {
+    if (parena_base) return;
+    ensure_device();
+    CUDA_CHECK(cudaMalloc((void **)&parena_base, bytes));
+    parena_size = bytes; parena_off = 0;
+}
+float *parena_alloc(size_t n_floats) {
+    size_t need = n_floats * sizeof(float);
+    parena_off = (parena_off + 255) & ~(size_t)255;
+    if (!parena_base || parena_off + need > parena_size) {
+        fprintf(stderr, "parena overflow (%zu > %zu)\n", parena_off + need, parena_size);
+        exit(1);
+    }
+    float *p = (float *)(parena_base + parena_off);
+    parena_off += need;
+    return p;
+}
+
+// ------------------------------------------------------------------ NCM1 weight files
+// Layout (reference loader, src/tensor.c:70-128): "NCM1", u32 count, then per tensor
+// u8 name length, name, u8 ndim, u32 dims, u64 byte count, raw fp32. The whole file is
+// read once; all tensor payloads go into one 256-byte-aligned HBM slab with one copy.
+int weights_load(WeightStore *ws, const char *path) {
+    ensure_device();
+    ws->items = nullptr; ws->count = 0;
+    FILE *f = fopen(path, "rb");
+    if (!f) { fprintf(stderr, "cannot open %s\n", path); return -1; }
+    fseek(f, 0, SEEK_END);
+    long fsz = ftell(f);
+    fseek(f, 0, SEEK_SET);
+    if (fsz < 8) { fprintf(stderr, "%s: bad magic\n", path); fclose(f); return -1; }
+    unsigned char *buf = nullptr;
+    if (cudaMallocHost((void **)&buf, (size_t)fsz) != cudaSuccess) { fclose(f); fprintf(stderr, "%s: pinned staging alloc failed\n", path); return -1; }
+    size_t got = fread(buf, 1, (size_t)fsz, f);
+    fclose(f);
+    auto fail = [&](const char *why) { fprintf(stderr, "%s: %s\n", path, why); cudaFreeHost(buf); free(ws->items); ws->items = nullptr; ws->count = 0; return -1; };
+    if (got != (size_t)fsz) return fail("short read");
+    if (memcmp(buf, "NCM1", 4) != 0) {
+        if (memcmp(buf, "NCK1", 4) == 0) return fail("NCK1 training checkpoints are not read by this library; export NCM1 weights");
+        return fail("bad magic");
+    }
+    uint32_t count;
+    memcpy(&count, buf + 4, 4);
+    ws->items = (NamedTensor *)calloc(count ? count : 1, sizeof(NamedTensor));
+    struct Span { size_t file_off, nbytes, slab_off; };
+    std::vector<Span> spans(count);
+    size_t pos = 8, slab = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        if (pos + 1 > (size_t)fsz) return fail("truncated");
+        unsigned nl = buf[pos++];
+        if (pos + nl + 1 > (size_t)fsz) return fail("truncated");
+        memcpy(ws->items[i].name, buf + pos, nl);
+        ws->items[i].name[nl] = 0;
+        pos += nl;
+        unsigned nd = buf[pos++];
+        if (nd > NCM_MAX_DIMS || pos + 4 * nd + 8 > (size_t)fsz) return fail("truncated");
+        Tensor *t = (Tensor *)calloc(1, sizeof(Tensor));
+        t->ndim = (int)nd; t->n = 1;
+        for (unsigned d = 0; d < nd; d++) { uint32_t v; memcpy(&v, buf + pos, 4); pos += 4; t->shape[d] = v; t->n *= v; }
+        uint64_t nbytes;
+        memcpy(&nbytes, buf + pos, 8); pos += 8;
+        ws->items[i].t = t;
+        ws->count = (int)i + 1;
+        if ((uint64_t)t->n * 4 != nbytes) { fprintf(stderr, "%s: size mismatch\n", ws->items[i].name); for (int j = 0; j < ws->count; j++) free(ws->items[j].t); return fail("size mismatch"); }
+        if (pos + nbytes > (size_t)fsz) { for (int j = 0; j < ws->count; j++) free(ws->items[j].t); return fail("truncated payload"); }
+        spans[i] = Span{pos, (size_t)nbytes, slab};
+        slab += ((size_t)nbytes + 255) & ~(size_t)255;
+        pos += nbytes;
+    }
+    char *dslab = nullptr;
+    CUDA_CHECK(cudaMalloc((void **)&dslab, slab ? slab : 256));
+    for (uint32_t i = 0; i < count; i++) {
+        ws->items[i].t->data = (float *)(dslab + spans[i].slab_off);
+        slab_members().insert(ws->items[i].t->data);
+        if (spans[i].nbytes)
+            CUDA_CHECK(cudaMemcpyAsync(dslab + spans[i].slab_off, buf + spans[i].file_off, spans[i].nbytes,
+                                       cudaMemcpyHostToDevice, stream()));
+    }
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    cudaFreeHost(buf);
+    slab_of_store()[ws->items] = dslab;
+    return 0;
+}
+
+void weights_free(WeightStore *ws) {
+    if (!ws || !ws->items) return;
+    cudaStreamSynchronize(stream());
+    auto it = slab_of_store().find(ws->items);
+    for (int i = 0; i < ws->count; i++) {
+        Tensor *t = ws->items[i].t;
+        if (!t) continue;
+        if (slab_members().count(t->data)) slab_members().erase(t->data);
+        else cudaFree(t->data);
+        free(t);
+    }
+    if (it != slab_of_store().end()) { cudaFree(it->second); slab_of_store().erase(it); }
+    free(ws->items);
+    ws->items = nullptr; ws->count = 0;
+}
+
+Tensor *weights_get(WeightStore *ws, const char *name) {
+    for (int i = 0; i < ws->count; i++)
+        if (strcmp(ws->items[i].name, name) == 0) return ws->items[i].t;
+    return nullptr;
+}
+
+// ------------------------------------------------------------------ .conf
+// Flat key=value; unknown keys ignored; True/False accepted where the reference
+// accepts them (src/tensor.c:151-156); defaults as src/tensor.c:173-177.
+static int conf_boolish(const char *v) {
+    while (*v == ' ') v++;
+    if (*v == 'T' || *v == 't') return 1;
+    if (*v == 'F' || *v == 'f') return 0;
+    return atoi(v);
+}
+static int conf_int_list(const char *v, int *out, int cap) {
+    int k = 0;
+    const char *p = v;
+    while (*p && k < cap) {
+        while (*p == ' ' || *p == ',') p++;
+        if (!*p) break;
+        out[k++] = atoi(p);
+        while (*p && *p != ',') p++;
+    }
+    return k;
+}
+
+int config_load(NCMConfig *c, const char *path) {
+    memset(c, 0, sizeof(*c));
+    c->bias = 1; c->rope_base = 10000; c->rope_theta = 10000.0; c->n_kv_heads = -1;
+    c->prefix_pad_token_id = -1; c->eos_token_id = -1; c->pad_token_id = -1;
+    c->attn_pattern_block_diag = 1; c->gen_top_k = 1; c->gen_top_p = 1.0f;
+    FILE *f = fopen(path, "r");
+    if (!f) { fprintf(stderr, "cannot open %s\n", path); return -1; }
+    enum { BOOLISH, PLAIN };
+    struct IntKey { const char *key; int *dst; int kind; };
+    const IntKey ints[] = {
+        {"model.n_layer", &c->n_layer, BOOLISH}, {"model.n_head", &c->n_head, BOOLISH},
+        {"model.n_embd", &c->n_embd, BOOLISH}, {"model.context_length", &c->context_length, BOOLISH},
+        {"model.prefix_len", &c->prefix_len, BOOLISH}, {"model.raw_token_prefix", &c->raw_token_prefix, BOOLISH},
+        {"model.contextual_prefix", &c->contextual_prefix, BOOLISH},
+        {"model.prefix_pad_token_id", &c->prefix_pad_token_id, BOOLISH},
+        {"model.predict_level0", &c->predict_level0, BOOLISH}, {"model.query_level0", &c->query_level0, BOOLISH},
+        {"model.l0_autoregressive", &c->l0_autoregressive, BOOLISH},
+        {"model.use_positional_encoding", &c->use_positional_encoding, BOOLISH},
+        {"model.use_level_encoding", &c->use_level_encoding, BOOLISH},
+        {"model.use_rope", &c->use_rope, BOOLISH}, {"model.rope_base", &c->rope_base, BOOLISH},
+        {"model.use_qk_norm", &c->use_qk_norm, BOOLISH}, {"model.use_flex_attention", &c->use_flex_attention, BOOLISH},
+        {"model.n_kv_heads", &c->n_kv_heads, BOOLISH}, {"model.bias", &c->bias, PLAIN},
+        {"model.ctx_enabled", &c->ctx_enabled, BOOLISH}, {"model.ctx_n_layer", &c->ctx_n_layer, BOOLISH},
+        {"model.ctx_vocab", &c->ctx_vocab, BOOLISH}, {"model.puc_enabled", &c->puc_enabled, BOOLISH},
+        {"model.puc_kernel", &c->puc_kernel, BOOLISH}, {"model.shared_output_head", &c->shared_output_head, BOOLISH},
+        {"model.shared_head_per_level_bias", &c->shared_head_per_level_bias, BOOLISH},
+        {"model.untied_head_bias", &c->untied_head_bias, BOOLISH},
+        {"model.tie_heads_to_codebook", &c->tie_heads_to_codebook, BOOLISH},
+        {"model.tie_heads_learn_scale", &c->tie_heads_learn_scale, BOOLISH},
+        {"model.tie_heads_trainable", &c->tie_heads_trainable, BOOLISH},
+        {"model.tie_heads_bias", &c->tie_heads_bias, BOOLISH},
+        {"model.use_swiglu", &c->use_swiglu, BOOLISH}, {"model.use_geglu", &c->use_geglu, BOOLISH},
+        {"model.use_relu2", &c->use_relu2, BOOLISH}, {"model.parallel_block", &c->parallel_block, BOOLISH},
+        {"model.normformer", &c->normformer, BOOLISH}, {"model.use_layerscale", &c->use_layerscale, BOOLISH},
+        {"model.use_rezero", &c->use_rezero, BOOLISH}, {"model.sudoku_size", &c->sudoku_size, PLAIN},
+        {"vq.embed_dim", &c->vq_embed_dim, PLAIN}, {"vq.in_vocab", &c->vq_in_vocab, PLAIN},
+        {"vq.context_length", &c->vq_context_length, PLAIN}, {"vq.n_layers", &c->vq_n_layers, PLAIN},
+        {"vq.compression", &c->vq_compression, PLAIN}, {"vq.soft_levels", &c->vq_soft_levels, PLAIN},
+        {"vq.qr_enabled", &c->quant_resi_enabled, PLAIN}, {"vq.qr_share", &c->quant_resi_share_mode, PLAIN},
+        {"vq.l1_sampling", &c->learned_l1_sampling, PLAIN}, {"vq.l1_cascade", &c->learned_l1_cascade, PLAIN},
+        {"vq.l1_base", &c->learned_l1_cascade_base, PLAIN}, {"vq.l1_norm", &c->learned_l1_norm, BOOLISH},
+        {"vq.l1_norm_final", &c->learned_l1_norm_final, BOOLISH},
+        {"vq.all_sampling", &c->learned_all_sampling, PLAIN}, {"vq.pre_quant_gn", &c->pre_quant_groupnorm, PLAIN},
+        {"vq.qk_norm", &c->vq_qk_norm, BOOLISH}, {"vq.enc_layers", &c->enc_layers, PLAIN},
+        {"vq.enc_window", &c->enc_attn_window, PLAIN}, {"vq.enc_convs", &c->enc_conv_layers, PLAIN},
+        {"vq.enc_conv_kernel", &c->enc_conv_kernel, PLAIN}, {"vq.enc_positional", &c->enc_positional, PLAIN},
+        {"vq.dec_layers", &c->dec_layers, PLAIN}, {"vq.dec_positional", &c->dec_positional, PLAIN},
+        {"tok.eos_id", &c->eos_token_id, BOOLISH}, {"tok.pad_id", &c->pad_token_id, BOOLISH},
+        {"gen.top_k", &c->gen_top_k, PLAIN},
+    };
+    struct FltKey { const char *key; float *dst; };
+    const FltKey flts[] = {
+        {"model.dropout", &c->dropout}, {"model.layerscale_init", &c->layerscale_init},
+        {"vq.qr_ratio", &c->quant_resi_ratio}, {"gen.temperature", &c->gen_temperature},
+        {"gen.top_p", &c->gen_top_p}, {"gen.cfg_scale", &c->gen_cfg_scale},
+        {"gen.freq", &c->gen_freq}, {"gen.mu", &c->gen_mu},
+    };
+    char line[1024];
+    while (fgets(line, sizeof line, f)) {
+        char *eq = strchr(line, '=');
+        if (!eq) continue;
+        *eq = 0;
+        const char *k = line;
+        char *v = eq + 1;
+        v[strcspn(v, "\r\n")] = 0;
+        bool done = false;
+        for (const IntKey &ik : ints)
+            if (!strcmp(k, ik.key)) { *ik.dst = ik.kind == BOOLISH ? conf_boolish(v) : atoi(v); done = true; break; }
+        if (done) continue;
+        for (const FltKey &fk : flts)
+            if (!strcmp(k, fk.key)) { *fk.dst = (float)atof(v); done = true; break; }
+        if (done) continue;
+        if (!strcmp(k, "task")) { strncpy(c->task, v, sizeof(c->task) - 1); }
+        else if (!strcmp(k, "model.rope_theta")) c->rope_theta = atof(v);
+        else if (!strcmp(k, "model.attn_pattern")) c->attn_pattern_block_diag = (strcmp(v, "block_diagonal") == 0);
+        else if (!strcmp(k, "model.vocab_size")) c->n_levels_out = conf_int_list(v, c->vocab_size, NCM_MAX_VOCAB_LIST);
+        else if (!strcmp(k, "vq.soft_tau")) c->vq_soft_tau = atof(v);
+        else if (!strcmp(k, "vq.levels")) c->n_qlevels = conf_int_list(v, c->levels, NCM_MAX_LEVELS);
+        else if (!strcmp(k, "vq.vocab")) conf_int_list(v, c->vq_vocab, NCM_MAX_LEVELS);
+        else if (!strcmp(k, "tok.kind")) strncpy(c->pre_tok, v, sizeof(c->pre_tok) - 1);
+        else if (!strcmp(k, "tok.model_id")) strncpy(c->hf_model_id, v, sizeof(c->hf_model_id) - 1);
+        else if (!strcmp(k, "gen.adj")) {
+            if (v[0]) {
+                c->gen_adj_a = (float)atof(v);
+                char *q = strchr(v, ',');
+                c->gen_adj_w = q ? atoi(q + 1) : 1;
+                q = q ? strchr(q + 1, ',') : nullptr;
+                c->gen_adj_d = q ? (float)atof(q + 1) : 1.0f;
+            }
+        }
+    }
+    fclose(f);
+    if (c->n_kv_heads < 0) c->n_kv_heads = c->n_head;
+    return 0;
+}
+
+// ------------------------------------------------------------------ additions
+const char *ncmb_version(void) { return "ncm_b200 0.1 (sm_100a)"; }
+void ncmb_set_stream(void *s) { ensure_device(); ctx().stream = (cudaStream_t)s; }
+void *ncmb_get_stream(void) { return (void *)ctx().stream; }
+void ncmb_sync(void) { ensure_device(); CUDA_CHECK(cudaStreamSynchronize(stream())); }
+void ncmb_set_gemm_mode(int mode) { ensure_device(); ctx().gemm_mode = mode; }
+int ncmb_get_gemm_mode(void) { ensure_device(); return ctx().gemm_mode; }
+void ncmb_set_rng_mode(int mode) { ensure_device(); ctx().rng_mode = mode; }
+void ncmb_set_row_offset(long long off) { ctx().row_offset = off; }
+long long ncmb_launch_count(void) { return ctx().launches; }
+
+void ncmb_prof_enable(int on) {
+    ensure_device();
+    Prof &p = prof();
+    if (!on) p.drain();
+    p.on = on != 0; p.depth = 0;
+}
+void ncmb_prof_reset(void) {
+    Prof &p = prof();
+    p.drain();
+    for (int i = 0; i < NCMB_K_COUNT; i++) { p.launches[i] = 0; p.ms[i] = p.flops[i] = p.bytes[i] = 0; }
+}
+int ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes) {
+    if (klass < 0 || klass >= NCMB_K_COUNT) return -1;
+    Prof &p = prof();
+    p.drain();
+    if (launches) *launches = p.launches[klass];
+    if (ms) *ms = p.ms[klass];
+    if (flops) *flops = p.flops[klass];
+    if (bytes) *bytes = p.bytes[klass];
+    return 0;
+}
+
+} // extern "C"

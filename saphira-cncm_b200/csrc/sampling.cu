@@ -1,0 +1,284 @@
+// Device-side sampling of one level's positions for every row.
+//
+// One CTA per sequence row; positions are visited in order because the
+// frequency / deficit / adjacency penalties of position t depend on the picks at
+// positions < t (reference sample_level_rows, src/ncp.c:654-705). Per position:
+//   CFG blend (1+w) cond - w uncond in fp64 (src/ncp.c:1112-1116), penalties in fp64,
+//   then either first-index argmax (temp <= 0) or temperature / top-k / nucleus
+//   sampling (src/kernels.c:794-825): the top `keep` logits are found with a
+//   block-wide 4 x 8-bit radix select, sorted with a bitonic network, turned into
+//   fp64 probabilities and walked sequentially in rank order exactly as the
+//   reference does, using one pre-drawn uniform.
+// The uniforms come either from the reference's xorshift64* stream (drawn on the
+// host in the reference's (level, row, position) order) or from a counter-based
+// generator keyed by (seed, global row, level, position).
+#include "common.cuh"
+
+namespace ncmb {
+
+constexpr int SM_THREADS = 256;
+constexpr int SM_MAXKEEP = 2048;           // exact sorted path handles keep <= this
+constexpr int SM_SMEM_V = 16384;           // logits rows up to this many floats live in shared memory
+
+struct SampleDev {
+    SampleArgs a;
+    int vals_in_smem;
+};
+
+__device__ __forceinline__ unsigned okey(float f) {      // order-preserving float -> uint
+    unsigned u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float okey_inv(unsigned k) {
+    unsigned u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(u);
+}
+
+// splitmix64-style counter hash -> uniform double in [0, 1)
+__device__ __forceinline__ double counter_uniform(unsigned long long seed, long long row, int level, int t) {
+    unsigned long long z = seed ^ (0x9E3779B97F4A7C15ULL * (unsigned long long)(row + 1));
+    z += 0xBF58476D1CE4E5B9ULL * (unsigned long long)(level + 1) + 0x94D049BB133111EBULL * (unsigned long long)(t + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    z = z ^ (z >> 31);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = z ^ (z >> 29);
+    return (double)(z >> 11) * (1.0 / 9007199254740992.0);
+}
+
+__global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
+    const SampleArgs &a = sd.a;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    // layout: cand u64[SM_MAXKEEP] | probs f64[SM_MAXKEEP] | vals f32[V] (optional)
+    unsigned long long *cand = (unsigned long long *)smraw;
+    double *probs = (double *)(smraw + sizeof(unsigned long long) * SM_MAXKEEP);
+    float *vals = sd.vals_in_smem ? (float *)(smraw + 16 * SM_MAXKEEP) : a.scratch + (size_t)blockIdx.x * a.V;
+    __shared__ int hist[256];
+    __shared__ unsigned long long red[SM_THREADS];
+    __shared__ unsigned s_prefix, s_mask;
+    __shared__ int s_remaining, s_ncand, s_pick, s_eqbase[SM_THREADS + 1];
+
+    const int b = blockIdx.x, tid = threadIdx.x, V = a.V, Lc = a.Lc;
+    double *cnt = a.cnt ? a.cnt + (size_t)b * a.cnt_stride : nullptr;
+    int *hst = a.hist ? a.hist + (size_t)b * a.hist_stride : nullptr;
+    int hl = a.hist_len ? a.hist_len[b] : 0;
+    const bool penal = (a.freq > 0.f) || (a.adj_a != 0.f);
+
+    for (int t = 0; t < Lc; t++) {
+        const float *lc = a.logits + ((size_t)b * Lc + t) * V;
+        const float *lu = a.uncond_off ? a.logits + (((size_t)b + a.uncond_off) * Lc + t) * V : nullptr;
+        float *bo = a.blend_out ? a.blend_out + ((size_t)b * Lc + t) * V : nullptr;
+        for (int v = tid; v < V; v += SM_THREADS) {
+            float x = lc[v];
+            if (lu) x = (float)((1.0 + a.cfg_w) * (double)x - a.cfg_w * (double)lu[v]);
+            if (bo) bo[v] = x;
+            if (penal) {
+                double lg = x;
+                if (a.freq > 0.f) {
+                    double al = a.allow_dev ? a.allow_dev[v] * Lc : 0.0;
+                    double c = cnt[v];
+                    double excess = c - al;
+                    if (excess < 0) excess = 0;
+                    lg -= (double)a.freq * excess;
+                    if (a.mu > 0.f && a.allow_dev) {
+                        double def = al - c;
+                        if (def < 0) def = 0;
+                        lg += (double)a.mu * ((Lc - t) / (double)Lc) * def;
+                    }
+                }
+                x = (float)lg;
+            }
+            vals[v] = x;
+        }
+        __syncthreads();
+        if (a.adj_a != 0.f && tid == 0) {            // sequential: the same id may repeat in the window
+            int w = a.adj_w > 0 ? a.adj_w : 1;
+            int start = hl - w;
+            if (start < 0) start = 0;
+            for (int h = start; h < hl; h++) {
+                double pen = (double)a.adj_a * pow((double)a.adj_d, (double)(hl - 1 - h));
+                vals[hst[h]] -= (float)pen;
+            }
+        }
+        __syncthreads();
+
+        if (!(a.temp > 0.f)) {
+            // first-index argmax: max over (ordered key, inverted index)
+            unsigned long long best = 0;
+            for (int v = tid; v < V; v += SM_THREADS) {
+                unsigned long long c = ((unsigned long long)okey(vals[v]) << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+                if (c > best) best = c;
+            }
+            red[tid] = best;
+            __syncthreads();
+            for (int s = SM_THREADS / 2; s > 0; s >>= 1) {
+                if (tid < s && red[tid + s] > red[tid]) red[tid] = red[tid + s];
+                __syncthreads();
+            }
+            if (tid == 0) s_pick = (int)(0xffffffffu - (unsigned)(red[0] & 0xffffffffu));
+            __syncthreads();
+        } else {
+            for (int v = tid; v < V; v += SM_THREADS) vals[v] = vals[v] / a.temp;
+            int keep = (a.top_k > 0) ? (a.top_k < V ? a.top_k : V) : V;
+            // ---- radix select: key of the keep-th largest value ----
+            if (tid == 0) { s_prefix = 0; s_mask = 0; s_remaining = keep; }
+            __syncthreads();
+            for (int pass = 3; pass >= 0; pass--) {
+                hist[tid] = 0;
+                __syncthreads();
+                unsigned prefix = s_prefix, mask = s_mask;
+                for (int v = tid; v < V; v += SM_THREADS) {
+                    unsigned k = okey(vals[v]);
+                    if ((k & mask) == prefix) atomicAdd(&hist[(k >> (8 * pass)) & 0xff], 1);
+                }
+                __syncthreads();
+                if (tid == 0) {
+                    int rem = s_remaining, cum = 0, bin = 255;
+                    for (; bin > 0; bin--) { if (cum + hist[bin] >= rem) break; cum += hist[bin]; }
+                    s_remaining = rem - cum;
+                    s_prefix = prefix | ((unsigned)bin << (8 * pass));
+                    s_mask = mask | (0xffu << (8 * pass));
+                }
+                __syncthreads();
+            }
+            const unsigned thr = s_prefix;
+            const int need_eq = s_remaining;          // how many values equal to the threshold are kept
+            if (tid == 0) s_ncand = 0;
+            __syncthreads();
+            for (int v = tid; v < V; v += SM_THREADS) {
+                unsigned k = okey(vals[v]);
+                if (k > thr) {
+                    int p = atomicAdd(&s_ncand, 1);
+                    cand[p] = ((unsigned long long)k << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+                }
+            }
+            // threshold ties: lowest indices first (contiguous chunk per thread + exclusive scan)
+            const int chunk = (V + SM_THREADS - 1) / SM_THREADS;
+            const int v0 = tid * chunk, v1 = (v0 + chunk < V) ? v0 + chunk : V;
+            int eq = 0;
+            for (int v = v0; v < v1; v++) if (okey(vals[v]) == thr) eq++;
+            s_eqbase[tid + 1] = eq;
+            __syncthreads();
+            if (tid == 0) { s_eqbase[0] = 0; for (int i = 1; i <= SM_THREADS; i++) s_eqbase[i] += s_eqbase[i - 1]; }
+            __syncthreads();
+            {
+                int rank = s_eqbase[tid], gt = s_ncand;
+                for (int v = v0; v < v1 && rank < need_eq; v++)
+                    if (okey(vals[v]) == thr) {
+                        cand[gt + rank] = ((unsigned long long)thr << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+                        rank++;
+                    }
+            }
+            __syncthreads();
+            // ---- bitonic sort, descending: value desc, index asc ----
+            int n2 = 1;
+            while (n2 < keep) n2 <<= 1;
+            for (int i = keep + tid; i < n2; i += SM_THREADS) cand[i] = 0;
+            __syncthreads();
+            for (int k = 2; k <= n2; k <<= 1)
+                for (int j = k >> 1; j > 0; j >>= 1) {
+                    for (int i = tid; i < n2; i += SM_THREADS) {
+                        int ixj = i ^ j;
+                        if (ixj > i) {
+                            unsigned long long x = cand[i], y = cand[ixj];
+                            bool desc = ((i & k) == 0);
+                            if (desc ? (x < y) : (x > y)) { cand[i] = y; cand[ixj] = x; }
+                        }
+                    }
+                    __syncthreads();
+                }
+            // ---- probabilities in rank order (fp64), nucleus cut, renormalise, walk ----
+            const double mx = (double)okey_inv((unsigned)(cand[0] >> 32));
+            for (int r = tid; r < keep; r += SM_THREADS)
+                probs[r] = exp((double)okey_inv((unsigned)(cand[r] >> 32)) - mx);
+            __syncthreads();
+            if (tid == 0) {
+                double den = 0;
+                for (int r = 0; r < keep; r++) den += probs[r];
+                for (int r = 0; r < keep; r++) probs[r] /= den;
+                double cum = 0;
+                int nkeep = keep;
+                for (int r = 0; r < keep; r++) {
+                    if (cum - probs[r] > (double)a.top_p) { nkeep = r; break; }
+                    cum += probs[r];
+                }
+                den = 0;
+                for (int r = 0; r < nkeep; r++) den += probs[r];
+                double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
+                                        : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
+                double u = u01 * den, acc = 0;
+                int pr = nkeep - 1;
+                for (int r = 0; r < nkeep; r++) { acc += probs[r]; if (u <= acc) { pr = r; break; } }
+                s_pick = (int)(0xffffffffu - (unsigned)(cand[pr] & 0xffffffffu));
+            }
+            __syncthreads();
+        }
+        if (tid == 0) {
+            int pick = s_pick;
+            a.out[(size_t)b * a.out_stride + a.out_off + t] = pick;
+            if (cnt) cnt[pick] += 1.0;
+            if (hst) hst[hl] = pick;
+        }
+        hl++;
+        __syncthreads();
+    }
+    if (tid == 0 && a.hist_len) a.hist_len[b] = hl;
+}
+
+size_t sample_scratch_floats(int Bn, int V) { return V > SM_SMEM_V ? (size_t)Bn * V : 0; }
+
+void sample_rows(const SampleArgs &a) {
+    if (a.Bn <= 0 || a.Lc <= 0) return;
+    if (a.temp > 0.f) {
+        int keep = (a.top_k > 0) ? (a.top_k < a.V ? a.top_k : a.V) : a.V;
+        if (keep > SM_MAXKEEP)
+            fatal("sampling: top_k=%d over V=%d keeps %d candidates; this build sorts at most %d "
+                  "(set top_k)", a.top_k, a.V, keep, SM_MAXKEEP);
+    }
+    SampleDev sd;
+    sd.a = a;
+    sd.vals_in_smem = a.V <= SM_SMEM_V;
+    if (!sd.vals_in_smem && !a.scratch) fatal("sampling: V=%d needs a scratch buffer", a.V);
+    size_t smem = 16 * (size_t)SM_MAXKEEP + (sd.vals_in_smem ? sizeof(float) * (size_t)a.V : 0);
+    static size_t attr = 0;
+    if (smem > attr) {
+        CUDA_CHECK(cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(16 * SM_MAXKEEP + 4 * SM_SMEM_V)));
+        attr = 16 * SM_MAXKEEP + 4 * SM_SMEM_V;
+    }
+    ProfScope ps(NCMB_K_SAMPLE, 0, (double)a.Bn * a.Lc * a.V * (a.uncond_off ? 8 : 4));
+    LAUNCH(k_sample, (unsigned)a.Bn, SM_THREADS, smem, sd);
+}
+
+} // namespace ncmb
+
+// Host-side sampling helper of the reference kernel API (src/ncm.h:197): logits is a
+// host row; same algorithm and the same single uniform draw per call.
+static const float *g_sort_vals;
+static int cmp_desc_idx(const void *pa, const void *pb) {
+    float va = g_sort_vals[*(const int *)pa], vb = g_sort_vals[*(const int *)pb];
+    return (va < vb) - (va > vb);
+}
+extern "C" int sample_topkp(const float *logits, int V, float temp, int top_k, float top_p, unsigned long long *rng) {
+    if (!(temp > 0)) return argmax_row(logits, V);
+    float *work = (float *)malloc((size_t)V * sizeof(float));
+    int *ord = (int *)malloc((size_t)V * sizeof(int));
+    double *probs = (double *)malloc((size_t)V * sizeof(double));
+    if (!work || !ord || !probs) ncmb::fatal("oom in sample_topkp");
+    for (int i = 0; i < V; i++) { work[i] = logits[i] / temp; ord[i] = i; }
+    g_sort_vals = work;
+    qsort(ord, (size_t)V, sizeof(int), cmp_desc_idx);
+    int keep = (top_k > 0) ? (top_k < V ? top_k : V) : V;
+    double mx = work[ord[0]], den = 0;
+    for (int r = 0; r < keep; r++) { probs[r] = exp((double)work[ord[r]] - mx); den += probs[r]; }
+    for (int r = 0; r < keep; r++) probs[r] /= den;
+    double cum = 0;
+    int nkeep = keep;
+    for (int r = 0; r < keep; r++) { if (cum - probs[r] > top_p) { nkeep = r; break; } cum += probs[r]; }
+    den = 0;
+    for (int r = 0; r < nkeep; r++) den += probs[r];
+    double u = (double)(rng_next(rng) >> 11) * (1.0 / 9007199254740992.0) * den, acc = 0;
+    int pick = ord[nkeep - 1];
+    for (int r = 0; r < nkeep; r++) { acc += probs[r]; if (u <= acc) { pick = ord[r]; break; } }
+    free(work); free(ord); free(probs);
+    return pick;
+}
