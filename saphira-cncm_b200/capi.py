@@ -105,6 +105,31 @@ _SIGS = {
     "ncp_gen_step_size": (_I, [_P, _I]),
     "gpt2_cmd_gen": (_I, [_P, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, _I, _F, _I, _F, _U64]),
     "qwen_cmd_gen": (_I, [_P, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, _I, _F, _I, _F, _U64]),
+    # additions of libncm_b200.so (include/ncm_b200.h, "additions")
+    "ncmb_version": (C.c_char_p, []),
+    "ncmb_set_stream": (None, [_P]),
+    "ncmb_get_stream": (_P, []),
+    "ncmb_sync": (None, []),
+    "ncmb_set_gemm_mode": (None, [_I]),
+    "ncmb_get_gemm_mode": (_I, []),
+    "ncmb_set_rng_mode": (None, [_I]),
+    "ncmb_set_row_offset": (None, [C.c_longlong]),
+    "ncmb_prof_enable": (None, [_I]),
+    "ncmb_prof_reset": (None, []),
+    "ncmb_prof_read": (_I, [_I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                            C.POINTER(C.c_double)]),
+    "ncmb_launch_count": (C.c_longlong, []),
+    "ncmb_ncp_generate_ex": (_P, [_P, _P, _P, _I, _F, _I, _F, _F, _F, _F, _F, _I, _F, _P, _U64, _P]),
+    "ncmb_decode_tokens": (None, [_P, _P, _I, _P]),
+    "ncmb_gen_codes_dev": (_P, [_P]),
+    "ncmb_decode_tokens_dev": (None, [_P, _P, _I, _P]),
+    "ncmb_vq_encode_dev": (None, [_P, _P, _I, _P]),
+    "ncmb_vq_nearest_dev": (None, [_P, _I, _P, C.c_longlong, _P]),
+    "ncmb_lm_open": (_P, [_P, C.c_char_p, _I, _I]),
+    "ncmb_lm_close": (None, [_P]),
+    "ncmb_lm_vocab": (_I, [_P]),
+    "ncmb_lm_generate": (_I, [_P, _P, _I, _I, _I, _F, _I, _F, _U64, _I, _P]),
+    "ncmb_lm_logits": (None, [_P, _P, _I, _I, _P]),
 }
 
 _libc = C.CDLL(None)
@@ -206,3 +231,29 @@ class NcpModel:
         codes = np.ctypeslib.as_array(C.cast(out, C.POINTER(_I)), shape=(B, self.total)).copy()
         _libc.free(out)
         return codes
+
+    def generate_ex(self, prefix: np.ndarray, cap_floats: int, l0=None, temp=0.0, top_k=0, top_p=1.0,
+                    cfg=0.0, freq=0.0, mu=0.0, adj=(0.0, 0, 1.0), allow=None, seed=0):
+        """libncm_b200 only: codes plus the logits every sampled position was drawn from."""
+        prefix = np.ascontiguousarray(prefix, dtype=np.int32)
+        B = prefix.shape[0]
+        l0p = None
+        if l0 is not None:
+            l0 = np.ascontiguousarray(l0, dtype=np.int32)
+            l0p = l0.ctypes.data
+        ap = None
+        if allow is not None:
+            allow = np.ascontiguousarray(allow, dtype=np.float64)
+            ap = allow.ctypes.data
+        cap = np.zeros((B, cap_floats), np.float32)
+        out = self.lib.ncmb_ncp_generate_ex(self.ncp, l0p, prefix.ctypes.data, B, temp, top_k, top_p, cfg, freq,
+                                            mu, adj[0], adj[1], adj[2], ap, seed, cap.ctypes.data)
+        codes = np.ctypeslib.as_array(C.cast(out, C.POINTER(_I)), shape=(B, self.total)).copy()
+        _libc.free(out)
+        return codes, cap
+
+    def decode_tokens(self, codes: np.ndarray, L: int) -> np.ndarray:
+        codes = np.ascontiguousarray(codes, dtype=np.int32)
+        tok = np.zeros((codes.shape[0], L), np.int32)
+        self.lib.ncmb_decode_tokens(self.vqvae, codes.ctypes.data, codes.shape[0], tok.ctypes.data)
+        return tok

@@ -202,11 +202,12 @@ void attention(const AttnArgs &a) {
     dim3 grid((unsigned)cdiv(a.max_q, AT_QT), (unsigned)a.H, (unsigned)a.rows);
     ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
     switch (a.hd) {
+        case 8: launch_attention<8>(d, grid); break;
         case 16: launch_attention<16>(d, grid); break;
         case 32: launch_attention<32>(d, grid); break;
         case 64: launch_attention<64>(d, grid); break;
         case 128: launch_attention<128>(d, grid); break;
-        default: fatal("attention: head dim %d not supported (16, 32, 64, 128)", a.hd);
+        default: fatal("attention: head dim %d not supported (8, 16, 32, 64, 128)", a.hd);
     }
 }
 

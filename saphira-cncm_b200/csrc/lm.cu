@@ -54,7 +54,7 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
     m->NL = c->n_layer; m->H = c->n_head; m->C = c->n_embd; m->hd = m->C / m->H;
     m->nkv = (is_qwen && c->n_kv_heads > 0) ? c->n_kv_heads : c->n_head;
     m->eos = c->eos_token_id;
-    if (m->hd != 16 && m->hd != 32 && m->hd != 64 && m->hd != 128) fatal("head dim %d not supported", m->hd);
+    if (m->hd != 8 && m->hd != 16 && m->hd != 32 && m->hd != 64 && m->hd != 128) fatal("head dim %d not supported", m->hd);
     int C = m->C, kvd = m->nkv * m->hd;
     if (!is_qwen) {
         m->n_ctx = c->context_length > 0 ? c->context_length : 1024;

@@ -106,7 +106,7 @@ extern "C" NCPState *ncp_load(const NCMConfig *c, WeightStore *ws, VQVAEState *v
     m->n_tgt = c->n_qlevels - m->lvl_first;
     m->C = c->n_embd; m->H = c->n_head; m->nkv = c->n_kv_heads; m->hd = m->C / m->H;
     m->D = c->vq_embed_dim; m->NL = c->n_layer;
-    if (m->hd != 16 && m->hd != 32 && m->hd != 64 && m->hd != 128)
+    if (m->hd != 8 && m->hd != 16 && m->hd != 32 && m->hd != 64 && m->hd != 128)
         fatal("NCP head dim %d not supported (16, 32, 64, 128)", m->hd);
     int hd = m->hd, C = m->C, S = m->P + m->T;
     // rotary tables: the full-sequence one (API accessors) and one per target level
