@@ -35,13 +35,17 @@ def tmp(tmp_path_factory):
     return str(tmp_path_factory.mktemp("gpu"))
 
 
-def _cmp_float(name, got, want, atol):
+def _cmp_float(name, got, want, atol, rtol=1e-5):
+    """|got - want| <= atol + rtol * |want| element-wise; returns the max abs error."""
     assert got.shape == want.shape, name
     fin = np.isfinite(want)
     assert (np.isfinite(got) == fin).all(), f"{name}: non-finite pattern differs"
-    err = np.abs(got[fin] - want[fin]).max() if fin.any() else 0.0
-    assert err <= atol, f"{name}: max abs err {err:.3e} > {atol:.1e}"
-    return err
+    if not fin.any():
+        return 0.0
+    d = np.abs(got[fin].astype(np.float64) - want[fin])
+    over = d - (atol + rtol * np.abs(want[fin]))
+    assert over.max() <= 0, f"{name}: max abs err {d.max():.3e} exceeds {atol:.1e} + {rtol:.0e}*|x|"
+    return float(d.max())
 
 
 def test_layer_kernels_match_oracle(cuda):
