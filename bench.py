@@ -1,0 +1,384 @@
+"""Throughput of the token loop on B200s: NCP coarse-to-fine generate + decode.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference --steps 2 --warmup 1     # the reference's CPU build
+
+Workload (default "c2"): the mid NCP configuration -- 12 layers, d=512, 8 query /
+2 KV heads, SwiGLU, prefix 256, levels 1-4-16-32 over 4096-entry codebooks, CFG
+1.5, temperature 0.8, top-k 50, top-p 0.9, frequency penalty 0.2 -- on 256
+sequences per GPU with seeded N(0, 0.02) weights and Zipf(1.1) prefixes.  One
+step = one ncp_generate over the batch plus decoding the codes to token ids.
+Sequences are independent: each rank runs its own 256 (weak scaling), no
+collective on the data path.  "tokens" are nominal: 512 target tokens per
+sequence (32 concepts x 16 tokens), as the configuration states.
+
+One JSON line is printed by rank 0:
+  value      device-timed (CUDA events) whole-job tokens/s, ids already in HBM
+  e2e        the same through the host C API: host prefix ids in, host token ids out
+  roofline   the GEMM kernel class: FLOPs executed / event-timed duration vs measured peak
+  cpu_baseline  the reference CPU build (oracle/_ref) or the oracle port on a bounded sample
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "saphira-cncm_b200"))
+
+import capi  # noqa: E402
+import synth  # noqa: E402
+
+NOMINAL_TOKENS = {"c2": 512, "c5": 512, "c1": 81, "c1b": 81, "c2s": 512}
+
+
+def workload(name: str):
+    if name == "c2":
+        return synth.spec_c2(), 256
+    if name == "c2s":                      # C2 widths at 2 layers: quick functional runs
+        return synth.spec_c2(n_layer=2, name="c2s"), 32
+    if name == "c5":
+        return synth.spec_c5(), 1024
+    if name == "c1":
+        return synth.spec_c1(), 64
+    if name == "c1b":
+        return synth.spec_c1((1, 3, 9, 81)), 64
+    raise SystemExit(f"unknown workload {name}")
+
+
+def gen_kwargs(spec):
+    g = spec.gen
+    kw = dict(temp=float(g.get("temperature", 0.0)), top_k=int(g.get("top_k", 0)), top_p=float(g.get("top_p", 1.0)),
+              cfg=float(g.get("cfg_scale", 0.0)), freq=float(g.get("freq", 0.0)), mu=float(g.get("mu", 0.0)))
+    if spec.token_unigram:
+        kw["allow"] = np.full(max(spec.vocab), 1.0 / max(spec.vocab))
+    return kw
+
+
+def algorithmic_flops_per_row(spec) -> float:
+    """MACs * 2 per model row with the prefix processed once (attention included)."""
+    C_, H, nkv = spec.n_embd, spec.n_head, spec.n_kv_heads
+    hd = C_ // H
+    g = 3 if (spec.swiglu or spec.geglu) else 2
+    Hh = spec.mlp_hidden if spec.mlp_hidden else 4 * C_
+    lin = C_ * (C_ + 2 * nkv * hd) + C_ * C_ + g * C_ * Hh
+    P, Ls = spec.prefix_len, spec.levels
+    lv = Ls if spec.query_level0 else Ls[1:]
+    vs = spec.vocab if spec.query_level0 else spec.vocab[1:]
+    mac = spec.n_layer * lin * (P + sum(lv))
+    mac += spec.n_layer * (2 * P * P * C_ + sum(2 * l * (P + l) * C_ for l in lv))
+    mac += sum(l * v * C_ for l, v in zip(lv, vs)) + (P + sum(lv)) * C_ * spec.vq_dim
+    return 2.0 * mac
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.th.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []          # upper half: samples under load
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+
+def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int):
+    """Times the reference's CPU build (oracle/_ref) -- or, where that build is not
+    present, the CPU oracle port -- on `rows` sequences of the workload per step.
+    Returns (kind, cores, [seconds per step])."""
+    cores = os.cpu_count() or 1
+    kw = gen_kwargs(spec)
+    pre = synth.ncp_prefixes(spec, rows, seed)
+    ref_lib = os.path.join(ROOT, "oracle", "_ref", "libcncm_ref.so")
+    times = []
+    if os.path.exists(ref_lib):
+        os.environ["NCM_THREADS"] = str(cores)
+        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        ref = capi.NcmLib(ref_lib)
+        m = capi.NcpModel(ref, conf, w, arena_mb=2048)
+        L, D, Vp, nl = spec.L, spec.vq_dim, spec.in_vocab, len(spec.levels)
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            codes = m.generate(pre, seed=seed, **kw)
+            # decode as the reference CLI does (src/main.c:863-879): zhats -> decoder -> host argmax
+            ref.arena_reset()
+            zh = [ref.arena_alloc(rows * L * D) for _ in range(nl)]
+            lg = ref.arena_alloc(rows * L * Vp)
+            ref.vq_idx_to_zhats(m.vq, codes.ctypes.data, rows, (C.c_void_p * nl)(*zh))
+            ref.vqvae_decode(m.vqvae, zh[-1], lg, rows)
+            ref.to_host(lg, (rows, L, Vp)).argmax(axis=-1)
+            dt = time.perf_counter() - t0
+            if it >= warmup:
+                times.append(dt)
+        return "reference", cores, times
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import orc
+    m = orc.Model(conf, w)
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        codes = m.generate(pre, seed=seed, **kw)
+        m.decode_tokens(codes)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    return "port", min(cores, rows * (2 if kw["cfg"] > 0 else 1)), times
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    spec, B = workload(args.workload)
+    tok = NOMINAL_TOKENS[args.workload]
+    rows = args.cpu_rows
+    with tempfile.TemporaryDirectory() as tmp:
+        conf, w = synth.write_ncp(spec, tmp)
+        kind, cores, times = cpu_sample_run(spec, conf, w, rows, args.steps, args.warmup, 7)
+    total = sum(times)
+    value = rows * tok * len(times) / total
+    sample = f"{rows} of the {B} sequences per step (cost is linear in sequences: the reference loops rows)"
+    line = {
+        "impl": "reference", "metric": "generated tokens/sec", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000.0 * total / len(times), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 (fp64 accumulate)", "data": "synthetic",
+        "config": workload_config(args.workload, spec, B, args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, spec, B, n_gpus):
+    return {
+        "workload": f"{name}: NCP {spec.n_layer}x{spec.n_embd}, {spec.n_head}q/{spec.n_kv_heads}kv heads, "
+                    f"prefix {spec.prefix_len}, levels {'-'.join(map(str, spec.levels))}, codebooks {spec.vocab[0]}x{spec.vq_dim}, "
+                    f"{'CFG %.1f, ' % spec.gen.get('cfg_scale', 0) if spec.gen.get('cfg_scale', 0) else ''}"
+                    f"temp {spec.gen.get('temperature', 0)}, top-k {spec.gen.get('top_k', 0)}, top-p {spec.gen.get('top_p', 1.0)}; "
+                    f"generate + decode to token ids",
+        "sequences_per_gpu": B, "global_sequences": B * n_gpus,
+        "nominal_tokens_per_sequence": NOMINAL_TOKENS[name], "codes_per_sequence": sum(spec.levels),
+        "parallelism": f"independent sequences sharded over {n_gpus} GPU(s), no collective",
+        "l2_policy": "working set (K/V cache + activations, > 1 GB) exceeds the 126 MB L2 between iterations",
+    }
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the library has no CPU path)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib_path = os.path.join(ROOT, "saphira-cncm_b200", "libncm_b200.so")
+    if not os.path.exists(lib_path):
+        raise SystemExit("bench.py: libncm_b200.so is not built (python saphira-cncm_b200/build.py)")
+    lib = capi.NcmLib(lib_path)
+    if args.gemm is not None:
+        lib.ncmb_set_gemm_mode(args.gemm)
+    stream = torch.cuda.current_stream()
+    lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
+
+    spec, B = workload(args.workload)
+    if args.batch:
+        B = args.batch
+    tok = NOMINAL_TOKENS[args.workload]
+    kw = gen_kwargs(spec)
+    tmp = tempfile.TemporaryDirectory()
+    conf, w = synth.write_ncp(spec, tmp.name)
+    model = capi.NcpModel(lib, conf, w, arena_mb=64)
+    # each rank owns a distinct block of sequences; pinned host buffers for the end-to-end path
+    prefix = torch.from_numpy(synth.ncp_prefixes(spec, B, 1000 + rank)).pin_memory()
+    tokens_host = torch.empty((B, spec.L), dtype=torch.int32).pin_memory()
+    tokens_dev = torch.empty((B, spec.L), dtype=torch.int32, device="cuda")
+    allow = kw.get("allow")
+    allow_p = allow.ctypes.data if allow is not None else None
+    lib.ncmb_set_row_offset(rank * B)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step_device(seed):
+        """ids already resident: plan + upload outside the timed events, all device work inside."""
+        g = lib.ncp_gen_begin(model.ncp, None, prefix.data_ptr(), B, kw["temp"], kw["top_k"], kw["top_p"], kw["cfg"],
+                              kw["freq"], kw["mu"], 0.0, 0, 1.0, allow_p, seed)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        while lib.ncp_gen_step(g, None, None) == 0:
+            pass
+        lib.ncmb_decode_tokens_dev(model.vqvae, lib.ncmb_gen_codes_dev(g), B, tokens_dev.data_ptr())
+        e1.record(stream)
+        return g, e0, e1
+
+    def step_e2e(seed):
+        """host prefix ids in, host token ids out, through the public C API."""
+        out = lib.ncp_generate(model.ncp, None, prefix.data_ptr(), B, kw["temp"], kw["top_k"], kw["top_p"], kw["cfg"],
+                               kw["freq"], kw["mu"], 0.0, 0, 1.0, allow_p, seed)
+        lib.ncmb_decode_tokens(model.vqvae, out, B, tokens_host.data_ptr())
+        capi._libc.free(out)
+
+    for i in range(args.warmup):
+        g, _, _ = step_device(100 + i)
+        torch.cuda.synchronize()
+        lib.ncp_gen_abort(g)
+        step_e2e(100 + i)
+
+    # ---- device-timed steps (value) with kernel-class timers and clock sampling ----
+    lib.ncmb_prof_reset()
+    lib.ncmb_prof_enable(1)
+    n0 = lib.ncmb_launch_count()
+    barrier()
+    dev_ms = 0.0
+    with ClockSampler(local) as clk:
+        t_wall0 = time.perf_counter()
+        for i in range(args.steps):
+            g, e0, e1 = step_device(200 + i)
+            e1.synchronize()
+            dev_ms += e0.elapsed_time(e1)
+            lib.ncp_gen_abort(g)
+        barrier()
+        t_wall = time.perf_counter() - t_wall0
+    launches = lib.ncmb_launch_count() - n0
+    lib.ncmb_prof_enable(0)
+    prof = {}
+    for name, k in (("gemm", 0), ("attention", 1), ("norm", 2), ("sampling", 3), ("elementwise", 4), ("quantizer", 5)):
+        n, ms, fl, by = C.c_longlong(), C.c_double(), C.c_double(), C.c_double()
+        lib.ncmb_prof_read(k, C.byref(n), C.byref(ms), C.byref(fl), C.byref(by))
+        prof[name] = {"launches": n.value, "ms": ms.value, "flops": fl.value, "bytes": by.value}
+
+    # ---- end-to-end steps through the host API ----
+    h0, d0 = C.c_ulonglong(), C.c_ulonglong()
+    lib.ncmb_copy_bytes(C.byref(h0), C.byref(d0))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step_e2e(300 + i)
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    h1, d1 = C.c_ulonglong(), C.c_ulonglong()
+    lib.ncmb_copy_bytes(C.byref(h1), C.byref(d1))
+
+    t = torch.tensor([dev_ms / 1000.0, e2e_s, t_wall], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_s, e2e_max, _ = t.tolist()
+    if rank == 0:
+        peaks = {}
+        pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(pk):
+            peaks = json.load(open(pk))
+        peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+        gm = prof["gemm"]
+        ach = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
+        total_tok = world * B * tok * args.steps
+        mode = lib.ncmb_get_gemm_mode()
+        line = {
+            "metric": "generated tokens/sec", "value": total_tok / dev_s, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * dev_s / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": {0: "f32", 1: "tf32 (fp32 accumulate)", 2: "3xtf32 (fp32 accumulate)"}.get(mode, "f32"),
+            "data": "synthetic",
+            "config": workload_config(args.workload, spec, B, world),
+            "codes_per_sec": world * B * sum(spec.levels) * args.steps / dev_s,
+            "e2e": {"value": total_tok / e2e_max, "unit": "tokens/s",
+                    "h2d_bytes_per_step": (h1.value - h0.value) // args.steps,
+                    "d2h_bytes_per_step": (d1.value - d0.value) // args.steps},
+            "gpu_launches": launches,
+            "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "kernel": "gemm (QKV/O/MLP/head linears)", "achieved": ach, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": ach / peak_tf if peak_tf else None, "traffic": None,
+                         "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained" if peaks else "fallback",
+                         "launches": gm["launches"], "avg_launch_ms": gm["ms"] / max(gm["launches"], 1)},
+            "algorithmic_tflop_per_step": algorithmic_flops_per_row(spec) * B * (2 if kw["cfg"] > 0 else 1) / 1e12,
+            "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            kind, cores, times = cpu_sample_run(spec, conf, w, args.cpu_rows, 1, 0, 7)
+            line["cpu_baseline"] = {
+                "value": args.cpu_rows * tok / times[0], "unit": "tokens/s", "cores": cores, "kind": kind,
+                "sample": f"{args.cpu_rows} of the {B} sequences, one pass (reference cost is linear in sequences)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    tmp.cleanup()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2")
+    ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the workload's)")
+    ap.add_argument("--gemm", type=int, default=None, help="GEMM engine override (0 fp32, 1 tf32, 2 3xtf32)")
+    ap.add_argument("--cpu-rows", type=int, default=1, help="sequences in the CPU sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours" and args.workload == "c2":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -261,6 +261,8 @@ void  ncmb_prof_enable(int on);
 void  ncmb_prof_reset(void);
 int   ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes);
 long long ncmb_launch_count(void);            /* kernels launched since load */
+/* bytes this library has copied host->device and device->host since load */
+void  ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h);
 
 /* NCP generate, extended: same as ncp_generate, and when logits_host is not NULL
  * it receives the logits each sampled position was drawn from (after the CFG

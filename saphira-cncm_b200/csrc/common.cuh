@@ -25,6 +25,7 @@ struct Ctx {
     int rng_mode = 0;
     long long row_offset = 0;
     int sm_count = 148;
+    unsigned long long h2d_bytes = 0, d2h_bytes = 0;   // bytes moved across PCIe by this library
     bool inited = false;
 };
 Ctx &ctx();

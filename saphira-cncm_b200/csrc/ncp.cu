@@ -481,6 +481,7 @@ static void capture_level(NCPGen *g, int Lc, int V) {
     CUDA_CHECK(cudaMemcpy2D(g->cap_host + g->cap_off, g->cap_row * 4, g->blend, (size_t)Lc * V * 4, (size_t)Lc * V * 4,
                             g->B, cudaMemcpyDeviceToHost));
     g->cap_off += (size_t)Lc * V;
+    ctx().d2h_bytes += (unsigned long long)g->B * Lc * V * 4;
 }
 
 static void gen_l0(NCPGen *g) {

@@ -157,11 +157,13 @@ void mem_d2h(void *h, const void *d, size_t n) {
     ensure_device();
     CUDA_CHECK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, stream()));
     CUDA_CHECK(cudaStreamSynchronize(stream()));
+    ctx().d2h_bytes += n;
 }
 void mem_h2d(void *d, const void *h, size_t n) {
     ensure_device();
     CUDA_CHECK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, stream()));
     CUDA_CHECK(cudaStreamSynchronize(stream()));   // h may be freed by the caller right after
+    ctx().h2d_bytes += n;
 }
 void mem_d2d(void *d, const void *s, size_t n) {
     ensure_device();
@@ -446,6 +448,10 @@ int ncmb_get_gemm_mode(void) { ensure_device(); return ctx().gemm_mode; }
 void ncmb_set_rng_mode(int mode) { ensure_device(); ctx().rng_mode = mode; }
 void ncmb_set_row_offset(long long off) { ctx().row_offset = off; }
 long long ncmb_launch_count(void) { return ctx().launches; }
+void ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h) {
+    if (h2d) *h2d = ctx().h2d_bytes;
+    if (d2h) *d2h = ctx().d2h_bytes;
+}
 
 void ncmb_prof_enable(int on) {
     ensure_device();

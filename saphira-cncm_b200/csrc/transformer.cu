@@ -102,6 +102,7 @@ void upload(void *dev, const void *host, size_t bytes) {
     if (!bytes) return;
     CUDA_CHECK(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, stream()));
     CUDA_CHECK(cudaStreamSynchronize(stream()));
+    ctx().h2d_bytes += bytes;
 }
 float *dev_concat_rows(const float *a, int64_t na, const float *b, int64_t nb) {
     float *d = (float *)dev_alloc((size_t)(na + nb) * sizeof(float));
