@@ -244,6 +244,9 @@ void  ncmb_sync(void);
  * 2 = tcgen05 3xTF32 (fp32-grade). Default from NCM_B200_GEMM, else 2. */
 void  ncmb_set_gemm_mode(int mode);
 int   ncmb_get_gemm_mode(void);
+/* The tensor-core kernels bound every barrier wait; when one runs out they record a
+ * code and drain. Returns and clears that code (0 = never happened); synchronises. */
+int   ncmb_gemm_tc_check(void);
 /* Sampling stream: 0 = the reference's single xorshift64* stream consumed in
  * (level, row, position) order (src/ncp.c:660-705) -- sampled codes equal the
  * reference's; 1 = counter-based, keyed by (seed, row_offset + row, level,

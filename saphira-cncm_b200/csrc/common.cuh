@@ -25,6 +25,7 @@ struct Ctx {
     int rng_mode = 0;
     long long row_offset = 0;
     int sm_count = 148;
+    int w_static = 0;                 // > 0: GEMM weights are model weights that do not change (split copies may be cached)
     unsigned long long h2d_bytes = 0, d2h_bytes = 0;   // bytes moved across PCIe by this library
     bool inited = false;
 };
@@ -88,6 +89,9 @@ void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and sh
 void gemm_simt(const GemmArgs &a);
 bool gemm_tc_supported(const GemmArgs &a);
 void gemm_tc(const GemmArgs &a);
+void gemm_tc_forget_weights();
+struct StaticWeights { StaticWeights() { ctx().w_static++; } ~StaticWeights() { ctx().w_static--; } };
+int gemm_tc_check();                    // reads + clears the tensor-core engine's timeout word
 
 // ---- normalisation / elementwise (kernels_elem.cu) ----
 void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps);

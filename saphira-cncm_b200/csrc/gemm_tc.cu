@@ -1,7 +1,447 @@
-// tcgen05 tensor-core GEMM engine (placeholder until the TMA/TMEM kernel lands).
+// tcgen05 tensor-core GEMM for sm_100a: y = act(x W^T + bias) (+ res), fp32 operands
+// consumed as TF32, fp32 accumulation in tensor memory.
+//
+// One CTA per 128 x BN output tile, six warps:
+//   warp 0   TMA producer: cp.async.bulk.tensor tiles of x and W (128-byte swizzle)
+//            into a ring of shared-memory stages, completion counted on mbarriers;
+//   warp 1   allocates BN columns of tensor memory and (one lane) issues
+//            tcgen05.mma.kind::tf32 over each stage, tcgen05.commit frees the stage;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = output row), fuse bias /
+//            activation / gated product / residual, store fp32 rows.
+// Two CTAs fit one SM (shared memory and tensor-memory columns), so one tile's
+// epilogue overlaps the other's main loop. Every mbarrier wait is bounded: on a
+// timeout the kernel records an error code and drains instead of spinning.
 #include "common.cuh"
 
+#include <cuda.h>
+#include <unordered_map>
+
 namespace ncmb {
-bool gemm_tc_supported(const GemmArgs &) { return false; }
-void gemm_tc(const GemmArgs &a) { gemm_simt(a); }
+
+constexpr int TC_BM = 128, TC_BK = 32;           // BK floats = 128 bytes = one swizzle row
+constexpr int TC_THREADS = 192;
+constexpr unsigned long long TC_WAIT_NS = 2000000000ull;   // 2 s per barrier wait, then give up
+
+struct TcEpi {
+    const float *bias; const float *res; int64_t ldres;
+    float *y; int64_t ldy;
+    int64_t M; int N; int act; int glu;
+    int *err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// bounded wait on a phase parity; false (and an error code) when the limit runs out
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0;; it++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 255u) {
+            unsigned long long now = gtime_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > TC_WAIT_NS) { atomicExch(err, code); return false; }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// shared-memory matrix descriptor, K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);           // start address
+    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+    d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                            // layout: SWIZZLE_128B
+    return d;
+}
+// instruction descriptor: D fp32, A/B tf32, both K-major, M x N tile
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float tc_act(float v, int act) {
+    switch (act) {
+        case ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.7071067811865475f));
+        case ACT_GELU_TANH: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        case ACT_SILU: return v / (1.0f + expf(-v));
+        case ACT_RELU2: { float r = v > 0.f ? v : 0.f; return r * r; }
+        default: return v;
+    }
+}
+
+// X3 = false: one TF32 pass over (A, B).  X3 = true: operands arrive split as
+// a = a_hi + a_lo (both exactly representable in TF32) and the tile accumulates
+// a_lo b_hi + a_hi b_lo + a_hi b_hi: fp32-grade products from three TF32 MMAs.
+template <int BN, int STAGES, bool X3>
+__global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ CUtensorMap tmA,
+                                                       const __grid_constant__ CUtensorMap tmB,
+                                                       const __grid_constant__ CUtensorMap tmAlo,
+                                                       const __grid_constant__ CUtensorMap tmBlo,
+                                                       TcEpi ep, int num_kb) {
+    extern __shared__ unsigned char smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int A_TILE = TC_BM * TC_BK * 4, B_TILE = BN * TC_BK * 4;
+    constexpr int A_BYTES = A_TILE * (X3 ? 2 : 1), B_BYTES = B_TILE * (X3 ? 2 : 1);   // [hi | lo] per stage
+    unsigned char *sA = smem, *sB = smem + STAGES * A_BYTES;
+    uint64_t *bars = (uint64_t *)(sB + STAGES * B_BYTES);       // full[STAGES], empty[STAGES], tmem_full
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 1);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull = smem_u32(bars + 2 * STAGES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;
+    const int64_t m0 = (int64_t)blockIdx.y * TC_BM;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(tfull, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+        if (X3) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmAlo) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tmBlo) : "memory");
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int armed = 0;
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; kb++) {
+                int s = kb % STAGES; uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 1);
+                if (!ok) break;
+                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, kb * TC_BK, (int)m0, full0 + 8 * s);
+                tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, kb * TC_BK, n0, full0 + 8 * s);
+                if (X3) {
+                    tma_load_2d(smem_u32(sA + s * A_BYTES + A_TILE), &tmAlo, kb * TC_BK, (int)m0, full0 + 8 * s);
+                    tma_load_2d(smem_u32(sB + s * B_BYTES + B_TILE), &tmBlo, kb * TC_BK, n0, full0 + 8 * s);
+                }
+                armed = kb + 1;
+            }
+            if (!ok) {   // drain: wait (bounded) for the copies already in flight before leaving
+                int first = armed - STAGES < 0 ? 0 : armed - STAGES;
+                for (int kb = first; kb < armed; kb++) mbar_wait(full0 + 8 * (kb % STAGES), (uint32_t)(kb / STAGES) & 1u, ep.err, 4);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_tf32(TC_BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; kb++) {
+                int s = kb % STAGES; uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                ok = mbar_wait(full0 + 8 * s, ph, ep.err, 2);
+                if (!ok) break;
+                tc_fence_after();
+                uint64_t ad = umma_desc_sw128(smem_u32(sA + s * A_BYTES));
+                uint64_t bd = umma_desc_sw128(smem_u32(sB + s * B_BYTES));
+                if (X3) {
+                    uint64_t al = umma_desc_sw128(smem_u32(sA + s * A_BYTES + A_TILE));
+                    uint64_t bl = umma_desc_sw128(smem_u32(sB + s * B_BYTES + B_TILE));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 8; k++) {
+                        umma_tf32(tmem_base, al + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                        umma_tf32(tmem_base, ad + (uint64_t)(k * 2), bl + (uint64_t)(k * 2), idesc, 1u);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < TC_BK / 8; k++)      // 8 tf32 (32 bytes) per MMA: advance the start address
+                    umma_tf32(tmem_base, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (X3 || (kb | k)) ? 1u : 0u);
+                umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
+            }
+            umma_commit(tfull);                          // accumulator complete (also reached on the error path)
+        }
+    } else {
+        const int q = warp & 3;                          // TMEM lane quadrant this warp may read
+        const int64_t m = m0 + q * 32 + lane;
+        bool ok = mbar_wait(tfull, 0, ep.err, 3);
+        tc_fence_after();
+        if (ok) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                if (m < ep.M && n0 + c0 < ep.N) {
+                    if (ep.glu) {
+                        // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
+                        float *yr = ep.y + m * ep.ldy + ((n0 + c0) >> 1);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            int n = n0 + c0 + 2 * j;
+                            if (n + 1 < ep.N) {
+                                float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
+                                if (ep.bias) { g += ep.bias[n]; u += ep.bias[n + 1]; }
+                                yr[j] = __fmul_rn(tc_act(g, ep.act), u);
+                            }
+                        }
+                    } else {
+                        float *yr = ep.y + m * ep.ldy + n0 + c0;
+                        const float *rr = ep.res ? ep.res + m * ep.ldres + n0 + c0 : nullptr;
+                        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0) && (!rr || (ep.ldres & 3) == 0);
+                        if (full) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                                if (ep.bias) {
+                                    float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
+                                    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                                }
+                                v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
+                                if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
+                                *(float4 *)(yr + j) = v;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                int n = n0 + c0 + j;
+                                if (n < ep.N) {
+                                    float v = __uint_as_float(r[j]);
+                                    if (ep.bias) v += ep.bias[n];
+                                    v = tc_act(v, ep.act);
+                                    if (rr) v += rr[j];
+                                    yr[j] = v;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) fatal("cuTensorMapEncodeTiled is not available in this driver");
+        fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+struct MapKey {
+    const void *p; int64_t rows, ld; int K, box_rows, dtype;
+    bool operator==(const MapKey &o) const { return p == o.p && rows == o.rows && ld == o.ld && K == o.K && box_rows == o.box_rows && dtype == o.dtype; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey &k) const {
+        size_t h = (size_t)(uintptr_t)k.p;
+        h = h * 1000003u ^ (size_t)k.rows; h = h * 1000003u ^ (size_t)k.ld; h = h * 1000003u ^ (size_t)k.K;
+        return h * 1000003u ^ (size_t)(k.box_rows * 4 + k.dtype);
+    }
+};
+
+static int tma_dtype_mode() {          // 1 (default): TMA rounds fp32 to tf32 while loading; 0: raw fp32 bits
+    static int m = -1;
+    if (m < 0) { const char *e = getenv("NCM_B200_TMA_TF32"); m = e ? atoi(e) : 1; }
+    return m;
+}
+
+// 2-D map over a row-major [rows][K] fp32 matrix with row stride ld: box = 32 floats x box_rows.
+// round_tf32: let the TMA unit round each element to TF32 on the way into shared memory.
+static const CUtensorMap *get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    int dt = (round_tf32 && tma_dtype_mode()) ? 1 : 0;
+    MapKey key{p, rows, ld, K, box_rows, dt};
+    auto it = cache.find(key);
+    if (it != cache.end()) return &it->second;
+    if (cache.size() > 4096) cache.clear();
+    CUtensorMap tm;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(&tm, dt ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                             (void *)p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) fatal("cuTensorMapEncodeTiled failed (%d) for [%lld][%d] ld %lld", (int)r, (long long)rows, K, (long long)ld);
+    return &cache.emplace(key, tm).first->second;
+}
+
+static int *tc_err_flag() {
+    static int *d = nullptr;
+    if (!d) { d = (int *)dev_alloc(sizeof(int)); CUDA_CHECK(cudaMemsetAsync(d, 0, sizeof(int), stream())); }
+    return d;
+}
+
+// reads and clears the device-side error word of the tensor-core engine (0 = no timeout seen)
+int gemm_tc_check() {
+    int v = 0;
+    int *d = tc_err_flag();
+    CUDA_CHECK(cudaMemcpyAsync(&v, d, sizeof(int), cudaMemcpyDeviceToHost, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    if (v) CUDA_CHECK(cudaMemsetAsync(d, 0, sizeof(int), stream()));
+    return v;
+}
+
+// ---- hi / lo split for the three-pass mode: hi = rn_tf32(x), lo = x - hi (exact in fp32) ----
+__global__ void k_split_tf32(const float *__restrict__ x, int64_t ldx, float *__restrict__ hi, float *__restrict__ lo,
+                             int64_t rows, int K4) {
+    int64_t total = rows * K4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / K4; int c = (int)(i % K4);
+        float4 v = *(const float4 *)(x + r * ldx + c * 4);
+        float4 h, l;
+        uint32_t u;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.x)); h.x = __uint_as_float(u); l.x = v.x - h.x;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.y)); h.y = __uint_as_float(u); l.y = v.y - h.y;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.z)); h.z = __uint_as_float(u); l.z = v.z - h.z;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v.w)); h.w = __uint_as_float(u); l.w = v.w - h.w;
+        *(float4 *)(hi + i * 4) = h;
+        *(float4 *)(lo + i * 4) = l;
+    }
+}
+static void split_tf32(const float *x, int64_t ldx, float *hi, float *lo, int64_t rows, int K) {
+    int64_t n = rows * (K / 4);
+    int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+    ProfScope ps(NCMB_K_ELEM, 0, (double)rows * K * 12);
+    LAUNCH(k_split_tf32, (unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 256, 0, x, ldx, hi, lo, rows, K / 4);
+}
+
+struct Shadow { float *hi, *lo; int64_t n; };
+static std::unordered_map<const float *, Shadow> &shadow_cache() { static std::unordered_map<const float *, Shadow> c; return c; }
+static Workspace &split_ws() { static Workspace w; return w; }
+
+// Drops the cached hi/lo copies of weights (call when weight memory is freed or rewritten).
+void gemm_tc_forget_weights() {
+    for (auto &kv : shadow_cache()) { dev_free(kv.second.hi); }
+    shadow_cache().clear();
+}
+
+static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+bool gemm_tc_supported(const GemmArgs &a) {
+    int64_t ldx = a.ldx ? a.ldx : a.K, ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    if (a.M < 64 || a.N < 32 || a.K < 32) return false;            // skinny shapes stay on CUDA cores
+    if ((a.K & 3) || (ldx & 3)) return false;                       // TMA strides: multiples of 16 bytes
+    if (!al16(a.x) || !al16(a.W) || !al16(a.y) || (a.bias && !al16(a.bias)) || (a.res && !al16(a.res))) return false;
+    if (a.glu && ((a.N & 1) || (ldy & 1))) return false;
+    return true;
+}
+
+template <int BN, int STAGES, bool X3>
+static void launch_tc(const GemmArgs &a, const TcEpi &ep, const CUtensorMap *ma, const CUtensorMap *mb,
+                      const CUtensorMap *mal, const CUtensorMap *mbl) {
+    constexpr size_t smem = 1024 + (size_t)STAGES * (TC_BM + BN) * TC_BK * 4 * (X3 ? 2 : 1) + (2 * STAGES + 1) * 8 + 16;
+    static bool set = false;
+    if (!set) {
+        CUDA_CHECK(cudaFuncSetAttribute((k_gemm_tc<BN, STAGES, X3>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set = true;
+    }
+    dim3 grid((unsigned)cdiv(a.N, BN), (unsigned)cdiv(a.M, TC_BM));
+    int num_kb = (int)cdiv(a.K, TC_BK);
+    LAUNCH((k_gemm_tc<BN, STAGES, X3>), grid, TC_THREADS, smem, *ma, *mb, *mal, *mbl, ep, num_kb);
+}
+
+void gemm_tc(const GemmArgs &a) {
+    if (a.M <= 0 || a.N <= 0) return;
+    TcEpi ep;
+    ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
+    ep.y = a.y; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
+    int64_t ldx = a.ldx ? a.ldx : a.K;
+    const bool x3 = ctx().gemm_mode >= 2;
+    if (!x3) {
+        const CUtensorMap *ma = get_map(a.x, a.M, a.K, ldx, TC_BM, true);
+        const CUtensorMap *mb = get_map(a.W, a.N, a.K, a.K, 128, true);
+        ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
+                     4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
+        launch_tc<128, 3, false>(a, ep, ma, mb, ma, mb);
+        return;
+    }
+    // three-pass mode: split both operands; static weights are split once and cached
+    const int64_t nx = a.M * a.K, nw = (int64_t)a.N * a.K;
+    float *whi, *wlo;
+    Workspace &ws = split_ws();
+    bool cache_w = ctx().w_static != 0;
+    size_t need = (size_t)(2 * nx + (cache_w ? 0 : 2 * nw)) * 4 + 4096;
+    if (need > ws.cap) ws.reserve(need + need / 4);
+    ws.reset();
+    float *xhi = ws.get<float>(nx), *xlo = ws.get<float>(nx);
+    if (cache_w) {
+        auto &sc = shadow_cache();
+        auto it = sc.find(a.W);
+        if (it == sc.end() || it->second.n != nw) {
+            if (it != sc.end()) dev_free(it->second.hi);
+            float *buf = (float *)dev_alloc((size_t)2 * nw * 4);
+            split_tf32(a.W, a.K, buf, buf + nw, a.N, a.K);
+            it = sc.insert_or_assign(a.W, Shadow{buf, buf + nw, nw}).first;
+        }
+        whi = it->second.hi; wlo = it->second.lo;
+    } else {
+        whi = ws.get<float>(nw); wlo = ws.get<float>(nw);
+        split_tf32(a.W, a.K, whi, wlo, a.N, a.K);
+    }
+    split_tf32(a.x, ldx, xhi, xlo, a.M, a.K);
+    const CUtensorMap *ma = get_map(xhi, a.M, a.K, a.K, TC_BM, false), *mal = get_map(xlo, a.M, a.K, a.K, TC_BM, true);
+    const CUtensorMap *mb = get_map(whi, a.N, a.K, a.K, 128, false), *mbl = get_map(wlo, a.N, a.K, a.K, 128, true);
+    ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
+                 4.0 * (2.0 * (double)a.M * a.K + 2.0 * (double)a.N * a.K + (double)a.M * a.N));
+    launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);
+}
+
 } // namespace ncmb

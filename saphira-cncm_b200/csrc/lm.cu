@@ -287,6 +287,7 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
                                 float temp, int top_k, float top_p, unsigned long long seed, int eos, int *out) {
     ensure_device();
     if (B <= 0 || np <= 0 || n_new <= 0) return 0;
+    StaticWeights sw;
     if (np + n_new - 1 > m->n_ctx) fatal("%s: context overflow (%d + %d > %d)", m->is_qwen ? "qwen" : "gpt2", np, n_new, m->n_ctx);
     LMRun r;
     r.m = m; r.B = B; r.np = np; r.cap = np + n_new;
@@ -337,6 +338,7 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
 extern "C" void ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, float *out_host) {
     ensure_device();
     if (T <= 0) return;
+    StaticWeights sw;
     if (T > m->n_ctx) fatal("%s: context overflow", m->is_qwen ? "qwen" : "gpt2");
     LMRun r;
     r.m = m; r.B = 1; r.np = T; r.cap = T;

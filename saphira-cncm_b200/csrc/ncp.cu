@@ -592,6 +592,7 @@ int ncp_gen_step_size(NCPGen *g, int s) {
 
 int ncp_gen_step(NCPGen *g, int *codes_out, int *n_out) {
     if (g->phase == 2) return 1;
+    StaticWeights sw;
     if (g->phase == 0) {
         gen_l0(g);
         if (g->m->cfg.n_qlevels <= 1) g->phase = 2;
@@ -664,6 +665,7 @@ __global__ void k_scatter_logits(const float *__restrict__ lg, float *__restrict
 
 void ncp_forward(NCPState *m, const float *x, const int *prefix_ids, float *logits, int B) {
     ensure_device();
+    StaticWeights sw;
     const NCMConfig *c = &m->cfg;
     if (!c->attn_pattern_block_diag)
         fatal("ncp_forward: block_causal attention pattern is not implemented in this build (block_diagonal only)");

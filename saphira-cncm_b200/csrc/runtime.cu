@@ -301,6 +301,7 @@ int weights_load(WeightStore *ws, const char *path) {
 
 void weights_free(WeightStore *ws) {
     if (!ws || !ws->items) return;
+    gemm_tc_forget_weights();        // cached hi/lo splits point at memory that is about to go away
     cudaStreamSynchronize(stream());
     auto it = slab_of_store().find(ws->items);
     for (int i = 0; i < ws->count; i++) {
@@ -445,6 +446,7 @@ void *ncmb_get_stream(void) { return (void *)ctx().stream; }
 void ncmb_sync(void) { ensure_device(); CUDA_CHECK(cudaStreamSynchronize(stream())); }
 void ncmb_set_gemm_mode(int mode) { ensure_device(); ctx().gemm_mode = mode; }
 int ncmb_get_gemm_mode(void) { ensure_device(); return ctx().gemm_mode; }
+int ncmb_gemm_tc_check(void) { ensure_device(); return gemm_tc_check(); }
 void ncmb_set_rng_mode(int mode) { ensure_device(); ctx().rng_mode = mode; }
 void ncmb_set_row_offset(long long off) { ctx().row_offset = off; }
 long long ncmb_launch_count(void) { return ctx().launches; }

@@ -68,6 +68,7 @@ static void vae_run_block(VQVAEState *v, const BlockWeights &w, float *x, int B,
 
 // zhat [B][T][D] (device) -> logits [B][T][V] (device). reference src/vqvae.c:422-470
 void vqvae_decode_dev(VQVAEState *v, const float *zhat, float *logits, int B) {
+    StaticWeights sw;
     const NCMConfig *c = &v->cfg;
     int T = c->vq_context_length, D = c->vq_embed_dim, V = c->vq_in_vocab;
     if (c->vq_compression > 1) { fprintf(stderr, "decoder upsampling (compression>1) not wired\n"); exit(1); }
@@ -159,6 +160,7 @@ void vqvae_encode_z(VQVAEState *v, const int *ids, float *z, int B) {
     const NCMConfig *c = &v->cfg;
     WeightStore *ws = v->ws;
     if (!v->enc_ready) { fprintf(stderr, "missing weight tok.encoder.*\n"); exit(1); }
+    StaticWeights sw;
     int T = c->vq_context_length, D = c->vq_embed_dim;
     int64_t n = (int64_t)B * T;
     int Hh = v->enc.empty() ? 4 * D : v->enc[0].Hh;
