@@ -210,6 +210,26 @@ def workload_config(name, spec, B, n_gpus):
     }
 
 
+# --------------------------------------------------------------------------- sharding helpers
+
+def shard_plan(rank: int, world: int, per_gpu: int) -> dict:
+    """Weak scaling over independent sequences: rank r owns global rows [r*per_gpu, (r+1)*per_gpu),
+    draws its own prefixes (seed 1000 + r) and keys the counter-based sampler by global row."""
+    assert 0 <= rank < world
+    return {"rows": per_gpu, "row_offset": rank * per_gpu, "prefix_seed": 1000 + rank,
+            "global_rows": world * per_gpu}
+
+
+def max_over_ranks(values, device="cpu"):
+    """Element-wise maximum of a list of floats over all ranks (identity without a process group)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.tolist()
+
+
 # --------------------------------------------------------------------------- GPU arm
 
 def run_gpu_arm(args):
@@ -242,12 +262,13 @@ def run_gpu_arm(args):
     conf, w = synth.write_ncp(spec, tmp.name)
     model = capi.NcpModel(lib, conf, w, arena_mb=64)
     # each rank owns a distinct block of sequences; pinned host buffers for the end-to-end path
-    prefix = torch.from_numpy(synth.ncp_prefixes(spec, B, 1000 + rank)).pin_memory()
+    plan = shard_plan(rank, world, B)
+    prefix = torch.from_numpy(synth.ncp_prefixes(spec, B, plan["prefix_seed"])).pin_memory()
     tokens_host = torch.empty((B, spec.L), dtype=torch.int32).pin_memory()
     tokens_dev = torch.empty((B, spec.L), dtype=torch.int32, device="cuda")
     allow = kw.get("allow")
     allow_p = allow.ctypes.data if allow is not None else None
-    lib.ncmb_set_row_offset(rank * B)
+    lib.ncmb_set_row_offset(plan["row_offset"])
 
     def barrier():
         if world > 1:
@@ -314,10 +335,7 @@ def run_gpu_arm(args):
     h1, d1 = C.c_ulonglong(), C.c_ulonglong()
     lib.ncmb_copy_bytes(C.byref(h1), C.byref(d1))
 
-    t = torch.tensor([dev_ms / 1000.0, e2e_s, t_wall], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_s, e2e_max, _ = t.tolist()
+    dev_s, e2e_max, _ = max_over_ranks([dev_ms / 1000.0, e2e_s, t_wall], device="cuda")
     if rank == 0:
         peaks = {}
         pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
