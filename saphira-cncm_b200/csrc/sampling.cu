@@ -14,6 +14,9 @@
 // generator keyed by (seed, global row, level, position).
 #include "common.cuh"
 
+#include <cub/device/device_segmented_radix_sort.cuh>
+#include <vector>
+
 namespace ncmb {
 
 constexpr int SM_THREADS = 256;
@@ -227,13 +230,125 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
 
 size_t sample_scratch_floats(int Bn, int V) { return V > SM_SMEM_V ? (size_t)Bn * V : 0; }
 
+// ---- large candidate sets (top_k = 0 or > 2048 over a big vocabulary, one position per row) ----
+// The row is sorted once (value descending, index ascending on ties: a stable segmented
+// radix sort) and one CTA per row then walks it with block-wide fp64 prefix sums: the
+// nucleus cut "cum_before - p > top_p" and the draw "u <= cum" are monotone in the sorted
+// rank, so each is the minimum rank that satisfies a predicate. Sums are formed in a
+// different order than the reference's sequential loop (relative differences ~1e-16).
+constexpr int SL_THREADS = 1024;
+
+__global__ void k_sort_prep(const float *__restrict__ logits, float temp, int64_t n, int V, float *__restrict__ keys, int *__restrict__ idx) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        keys[i] = logits[i] / temp;
+        idx[i] = (int)(i % V);
+    }
+}
+
+__device__ __forceinline__ double block_excl_scan(double v, double *sm, double *total) {
+    // exclusive scan of one value per thread over SL_THREADS threads
+    int tid = threadIdx.x;
+    sm[tid] = v;
+    __syncthreads();
+    for (int off = 1; off < SL_THREADS; off <<= 1) {
+        double t = tid >= off ? sm[tid - off] : 0.0;
+        __syncthreads();
+        sm[tid] += t;
+        __syncthreads();
+    }
+    double incl = sm[tid];
+    *total = sm[SL_THREADS - 1];
+    __syncthreads();
+    return incl - v;
+}
+
+__global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const float *__restrict__ keys, const int *__restrict__ idx, int V, int keep,
+                                                           float top_p, const double *__restrict__ uniforms,
+                                                           unsigned long long seed, long long row0, int level,
+                                                           int *__restrict__ out, int out_stride, int out_off) {
+    __shared__ double sm[SL_THREADS];
+    __shared__ int s_min;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const float *kr = keys + (size_t)b * V;
+    const int *ir = idx + (size_t)b * V;
+    const double mx = (double)kr[0];
+    const int chunk = (keep + SL_THREADS - 1) / SL_THREADS;
+    const int r0 = tid * chunk, r1 = min(r0 + chunk, keep);
+    double local = 0;
+    for (int r = r0; r < r1; r++) local += exp((double)kr[r] - mx);
+    double den;
+    const double base = block_excl_scan(local, sm, &den);
+    // nucleus cut: first rank with (cum_before - p) / den > top_p
+    if (tid == 0) s_min = keep;
+    __syncthreads();
+    {
+        double cum = base;
+        for (int r = r0; r < r1; r++) {
+            double p = exp((double)kr[r] - mx);
+            if ((cum - p) / den > (double)top_p) { atomicMin(&s_min, r); break; }
+            cum += p;
+        }
+    }
+    __syncthreads();
+    const int nkeep = s_min;
+    __syncthreads();
+    // mass of the kept prefix
+    double lk = 0;
+    for (int r = r0; r < r1 && r < nkeep; r++) lk += exp((double)kr[r] - mx);
+    double den2;
+    const double base2 = block_excl_scan(lk, sm, &den2);
+    const double u01 = uniforms ? uniforms[b] : counter_uniform(seed, row0 + b, level, 0);
+    const double u = u01 * den2;
+    if (tid == 0) s_min = nkeep - 1;
+    __syncthreads();
+    {
+        double acc = base2;
+        for (int r = r0; r < r1 && r < nkeep; r++) {
+            acc += exp((double)kr[r] - mx);
+            if (u <= acc) { atomicMin(&s_min, r); break; }
+        }
+    }
+    __syncthreads();
+    if (tid == 0) out[(size_t)b * out_stride + out_off] = ir[s_min < 0 ? 0 : s_min];
+}
+
+static void sample_rows_large(const SampleArgs &a, int keep) {
+    if (a.Lc != 1 || a.uncond_off || a.freq > 0.f || a.adj_a != 0.f)
+        fatal("sampling: more than %d candidates (top_k=%d, V=%d) is supported for single-position rows "
+              "without CFG or penalties only; set top_k <= %d", SM_MAXKEEP, a.top_k, a.V, SM_MAXKEEP);
+    static Workspace ws;
+    const int64_t n = (int64_t)a.Bn * a.V;
+    size_t temp_bytes = 0;
+    cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
+                                                       (const int *)nullptr, (int *)nullptr, n, a.Bn, (const int *)nullptr,
+                                                       (const int *)nullptr, 0, 32, stream());
+    size_t need = (size_t)n * 16 + (size_t)(a.Bn + 1) * 4 + temp_bytes + 4096;
+    if (need > ws.cap) ws.reserve(need);
+    ws.reset();
+    float *k_in = ws.get<float>(n), *k_out = ws.get<float>(n);
+    int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
+    int *offs = ws.get<int>(a.Bn + 1);
+    void *temp = ws.alloc(temp_bytes);
+    static std::vector<int> hoffs;
+    hoffs.resize(a.Bn + 1);
+    for (int b = 0; b <= a.Bn; b++) hoffs[b] = b * a.V;
+    upload(offs, hoffs.data(), hoffs.size() * 4);
+    ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
+    int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+    LAUNCH(k_sort_prep, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
+    cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, n, a.Bn,
+                                                                        offs, offs + 1, 0, 32, stream());
+    if (e != cudaSuccess) fatal("segmented sort failed: %s", cudaGetErrorString(e));
+    ctx().launches += 4;
+    LAUNCH(k_pick_sorted, (unsigned)a.Bn, SL_THREADS, 0, k_out, i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed, a.rng_row0,
+           a.rng_level, a.out, a.out_stride, a.out_off);
+}
+
 void sample_rows(const SampleArgs &a) {
     if (a.Bn <= 0 || a.Lc <= 0) return;
     if (a.temp > 0.f) {
         int keep = (a.top_k > 0) ? (a.top_k < a.V ? a.top_k : a.V) : a.V;
-        if (keep > SM_MAXKEEP)
-            fatal("sampling: top_k=%d over V=%d keeps %d candidates; this build sorts at most %d "
-                  "(set top_k)", a.top_k, a.V, keep, SM_MAXKEEP);
+        if (keep > SM_MAXKEEP) { sample_rows_large(a, keep); return; }
     }
     SampleDev sd;
     sd.a = a;
