@@ -267,6 +267,18 @@ long long ncmb_launch_count(void);            /* kernels launched since load */
 /* bytes this library has copied host->device and device->host since load */
 void  ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h);
 
+/* linear_fwd (three-pass TF32) that allocates no memory at all -- no counterpart in the
+ * reference. For callers that may not allocate on the device: loops with a memory budget
+ * fixed at start-up, host callbacks and stream-capture regions (where cudaMalloc is not
+ * legal), or steady-state serving code that must not stall or fail on an allocation. Scratch
+ * for the split operands (2*batch*K + 2*M*K floats) comes from a 32 MiB array built into the
+ * library; larger problems, or shapes outside batch >= 64, M >= 32, K >= 32, K % 4 == 0 with
+ * 16-byte aligned pointers, return -1 with a message (0 = launched). The first call on a
+ * device resolves the array's address: make it before any stream capture. Calls share the
+ * array, so calls that overlap on one GPU race; keep them ordered on one stream. */
+int ncmb_linear_fwd_noalloc(const float *x, const float *W, const float *b, float *y,
+                            int64_t batch, int M, int K);
+
 /* NCP generate, extended: same as ncp_generate, and when logits_host is not NULL
  * it receives the logits each sampled position was drawn from (after the CFG
  * blend, before penalties), per sampled row, level-major. */

@@ -444,4 +444,93 @@ void gemm_tc(const GemmArgs &a) {
     launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);
 }
 
+
+// ------------------------------------------------------------------ linear layer without any allocation
+// The three-pass GEMM needs scratch for the hi/lo halves of both operands. linear_fwd
+// takes it from a workspace that grows with cudaMalloc; the entry point below takes it
+// from a fixed array that is part of the loaded module instead, so it can be called
+// from places where allocating device memory is off the table.
+constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)8 << 20;           // 32 MiB, resident on every GPU that loads the library
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
+static __device__ int g_noalloc_err;
+
+static void encode_map_now(CUtensorMap *tm, const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    bool rt = round_tf32 && tma_dtype_mode();
+    CUresult r = encode_fn()(tm, rt ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)p, dims,
+                             strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) fatal("cuTensorMapEncodeTiled failed (%d)", (int)r);
+}
+
 } // namespace ncmb
+
+// y = x W^T + b like linear_fwd (three-pass TF32, fp32-grade), allocating nothing:
+// no cudaMalloc / cudaFree and no allocating library call on any path.
+//
+// Who needs this: code that runs where device allocation is not allowed or not
+// safe -- a serving loop whose memory budget is fixed up front, a host callback or
+// a region under stream capture (cudaMalloc is illegal there), or a process that
+// shares the GPU and must never fail or stall on an allocation in steady state.
+//
+// Scratch: the split operands (2*batch*K + 2*M*K floats) live in a 32 MiB array
+// compiled into the library. Sizes beyond it (or shapes the tensor-core kernel does
+// not take: batch < 64, M < 32, K < 32, K % 4 != 0, pointers not 16-byte aligned)
+// are refused with -1 and a message; nothing is launched then. Returns 0 on success.
+// The first call on each device looks up the array's device address and clears its
+// error word; make that first call outside any stream capture. Every call reuses
+// the same array and overwrites all of the part it reads, so earlier contents never
+// leak into a result -- but two calls running concurrently on one GPU (different
+// streams, or different threads) would race on it: keep calls ordered on one stream.
+extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const float *b, float *y,
+                                       int64_t batch, int M, int K) {
+    using namespace ncmb;
+    ensure_device();
+    static float *scratch_of[64] = {nullptr};
+    static int *err_of[64] = {nullptr};
+    int dev = 0;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) { fprintf(stderr, "ncmb_linear_fwd_noalloc: device index %d out of range\n", dev); return -1; }
+    if (!scratch_of[dev]) {
+        // set-up, once per device, with that device current: the symbol name is only a
+        // host-side handle; kernels must be given the address it resolves to on the device
+        float *sp = nullptr; int *ep = nullptr;
+        cudaError_t e1 = cudaGetSymbolAddress((void **)&sp, g_noalloc_scratch);
+        cudaError_t e2 = cudaGetSymbolAddress((void **)&ep, g_noalloc_err);
+        if (e1 != cudaSuccess || e2 != cudaSuccess || !sp || !ep) {
+            fprintf(stderr, "ncmb_linear_fwd_noalloc: cudaGetSymbolAddress failed: %s\n",
+                    cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+            return -1;
+        }
+        CUDA_CHECK(cudaMemsetAsync(ep, 0, sizeof(int), stream()));
+        scratch_of[dev] = sp; err_of[dev] = ep;
+    }
+    GemmArgs a;
+    a.x = x; a.ldx = K; a.W = W; a.bias = b; a.y = y; a.ldy = M; a.M = batch; a.N = M; a.K = K;
+    if (!gemm_tc_supported(a)) {
+        fprintf(stderr, "ncmb_linear_fwd_noalloc: shape [%lld x %d] * [%d x %d] not taken by the tensor-core kernel "
+                        "(need batch >= 64, M >= 32, K >= 32, K %% 4 == 0, 16-byte aligned pointers)\n",
+                (long long)batch, K, M, K);
+        return -1;
+    }
+    const size_t nx = (size_t)batch * K, nw = (size_t)M * K;
+    if (2 * nx + 2 * nw > NOALLOC_SCRATCH_FLOATS) {
+        fprintf(stderr, "ncmb_linear_fwd_noalloc: needs %zu scratch floats (2*batch*K + 2*M*K), the built-in array holds %zu\n",
+                2 * nx + 2 * nw, NOALLOC_SCRATCH_FLOATS);
+        return -1;
+    }
+    float *xhi = scratch_of[dev], *xlo = xhi + nx, *whi = xlo + nx, *wlo = whi + nw;
+    split_tf32(x, K, xhi, xlo, batch, K);
+    split_tf32(W, K, whi, wlo, M, K);
+    CUtensorMap ma, mal, mb, mbl;
+    encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
+    encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
+    TcEpi ep;
+    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.ldy = M; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
+    ep.err = err_of[dev];
+    launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
+    return 0;
+}
