@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 #include <math.h>
+#include <vector>
 
 #include "../../include/ncm_b200.h"
 
@@ -84,6 +85,10 @@ struct GemmArgs {
     // gate/up rows (N = 2 * hidden); y has N/2 columns.
     int glu = 0;
     const void *wshadow = nullptr;       // engine-specific preprocessed copy of W (or null)
+    // three-pass mode: x may arrive already split (x = hi part, x_lo = lo part, both [M][K] with stride ldx),
+    // and the result may be written split (y = hi, y_lo = lo, same stride) for the next GEMM to consume.
+    const float *x_lo = nullptr;
+    float *y_lo = nullptr;
 };
 void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
 void gemm_simt(const GemmArgs &a);
@@ -95,6 +100,10 @@ int gemm_tc_check();                    // reads + clears the tensor-core engine
 
 // ---- normalisation / elementwise (kernels_elem.cu) ----
 void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps);
+// y_lo != null: the result is written as a TF32 hi / lo pair (y = hi, y_lo = value - hi)
+void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps);
+void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C);
+float *dev_interleave_rows(const float *a, const float *b, int64_t rows, int64_t cols);   // new [2*rows][cols]: a0,b0,a1,b1,...
 void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy);
 void add_inplace(float *y, const float *x, int64_t n);
 void add_rows_bcast(float *y, const float *rowvec, int64_t rows, int C);             // y[r,:] += v[:]
@@ -127,6 +136,7 @@ struct AttnArgs {
     const float *k1, *v1; int64_t ldk1;          // [token][kvh*hd + d]
     const float *k2 = nullptr, *v2 = nullptr; int64_t ldk2 = 0;
     float *out; int64_t ldo;                     // out[token][h*hd + d]
+    float *out_lo = nullptr;                     // optional: write the context as a TF32 hi / lo pair
     const int *q_start, *k1_start, *k2_start = nullptr;   // device int[rows+1]
     const int *k1_len = nullptr;                 // optional device int[rows]: segment-1 lengths (strided caches)
     int rows, H, Hkv, hd;
@@ -176,6 +186,7 @@ struct BlockWeights {
     const float *ow = nullptr, *ob = nullptr;          // [C][C]
     const float *qnw = nullptr, *knw = nullptr;        // per-head RMSNorm gains or null
     const float *fcw = nullptr, *fcb = nullptr;        // ungated [Hh][C]; gated [2*Hh][C] (gate rows, then up rows)
+    const float *fcw_il = nullptr, *fcb_il = nullptr;  // gated only: gate/up rows interleaved (fused gated epilogue)
     const float *pw = nullptr, *pb = nullptr;          // [C][Hh]
     int Hh = 0, gated = 0, act = ACT_GELU;
 };
@@ -194,6 +205,8 @@ struct AttnPlan {
 };
 void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights &w, const BlockBufs &b, const AttnPlan &p);
 void apply_norm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, int kind, float eps);
+void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps);
+void make_gated_interleaved(BlockWeights &w, int C, std::vector<void *> &owned);   // fills fcw_il / fcb_il from fcw / fcb
 
 // weight lookup helpers
 Tensor *wget(WeightStore *ws, const char *fmt, ...);      // null when missing

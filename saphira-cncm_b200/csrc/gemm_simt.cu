@@ -236,8 +236,9 @@ void gemm_simt(const GemmArgs &g) {
 }
 
 void gemm(const GemmArgs &a) {
-    if (ctx().gemm_mode >= 1 && gemm_tc_supported(a)) gemm_tc(a);
-    else gemm_simt(a);
+    if (ctx().gemm_mode >= 1 && gemm_tc_supported(a)) { gemm_tc(a); return; }
+    if (a.x_lo || a.y_lo) fatal("gemm: split operands reached the CUDA-core engine (M=%lld N=%d K=%d)", (long long)a.M, a.N, a.K);
+    gemm_simt(a);
 }
 
 } // namespace ncmb

@@ -24,10 +24,16 @@ constexpr unsigned long long TC_WAIT_NS = 2000000000ull;   // 2 s per barrier wa
 
 struct TcEpi {
     const float *bias; const float *res; int64_t ldres;
-    float *y; int64_t ldy;
+    float *y; float *y_lo; int64_t ldy;
     int64_t M; int N; int act; int glu;
     int *err;
 };
+
+__device__ __forceinline__ float tc_tf32_hi(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return __uint_as_float(u);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -213,13 +219,36 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                     if (ep.glu) {
                         // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
                         float *yr = ep.y + m * ep.ldy + ((n0 + c0) >> 1);
+                        float *lr = ep.y_lo ? ep.y_lo + m * ep.ldy + ((n0 + c0) >> 1) : nullptr;
+                        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0);
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            int n = n0 + c0 + 2 * j;
-                            if (n + 1 < ep.N) {
-                                float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-                                if (ep.bias) { g += ep.bias[n]; u += ep.bias[n + 1]; }
-                                yr[j] = __fmul_rn(tc_act(g, ep.act), u);
+                        for (int j = 0; j < 16; j += 4) {
+                            float o[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                int n = n0 + c0 + 2 * (j + e);
+                                float g = __uint_as_float(r[2 * (j + e)]), u = __uint_as_float(r[2 * (j + e) + 1]);
+                                if (ep.bias && n + 1 < ep.N) { g += ep.bias[n]; u += ep.bias[n + 1]; }
+                                o[e] = __fmul_rn(tc_act(g, ep.act), u);
+                            }
+                            if (full) {
+                                float4 v = make_float4(o[0], o[1], o[2], o[3]);
+                                if (lr) {
+                                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
+                                    *(float4 *)(lr + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
+                                    v = h4;
+                                }
+                                *(float4 *)(yr + j) = v;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; e++) {
+                                    int n = n0 + c0 + 2 * (j + e);
+                                    if (n + 1 < ep.N) {
+                                        float v = o[e];
+                                        if (lr) { float hi = tc_tf32_hi(v); lr[j + e] = v - hi; v = hi; }
+                                        yr[j + e] = v;
+                                    }
+                                }
                             }
                         }
                     } else {
@@ -237,6 +266,11 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                                 }
                                 v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
                                 if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
+                                if (ep.y_lo) {
+                                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
+                                    *(float4 *)(ep.y_lo + m * ep.ldy + n0 + c0 + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
+                                    v = h4;
+                                }
                                 *(float4 *)(yr + j) = v;
                             }
                         } else {
@@ -248,6 +282,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                                     if (ep.bias) v += ep.bias[n];
                                     v = tc_act(v, ep.act);
                                     if (rr) v += rr[j];
+                                    if (ep.y_lo) { float hi = tc_tf32_hi(v); ep.y_lo[m * ep.ldy + n] = v - hi; v = hi; }
                                     yr[j] = v;
                                 }
                             }
@@ -401,7 +436,7 @@ void gemm_tc(const GemmArgs &a) {
     if (a.M <= 0 || a.N <= 0) return;
     TcEpi ep;
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
-    ep.y = a.y; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    ep.y = a.y; ep.y_lo = a.y_lo; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
     int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool x3 = ctx().gemm_mode >= 2;
@@ -414,14 +449,20 @@ void gemm_tc(const GemmArgs &a) {
         return;
     }
     // three-pass mode: split both operands; static weights are split once and cached
-    const int64_t nx = a.M * a.K, nw = (int64_t)a.N * a.K;
+    const bool pre_split = a.x_lo != nullptr;
+    const int64_t nx = pre_split ? 0 : a.M * a.K, nw = (int64_t)a.N * a.K;
     float *whi, *wlo;
     Workspace &ws = split_ws();
     bool cache_w = ctx().w_static != 0;
     size_t need = (size_t)(2 * nx + (cache_w ? 0 : 2 * nw)) * 4 + 4096;
     if (need > ws.cap) ws.reserve(need + need / 4);
     ws.reset();
-    float *xhi = ws.get<float>(nx), *xlo = ws.get<float>(nx);
+    const float *xhi = a.x, *xlo = a.x_lo;
+    int64_t ldsplit = ldx;
+    if (!pre_split) {
+        float *h = ws.get<float>(nx), *l = ws.get<float>(nx);
+        xhi = h; xlo = l; ldsplit = a.K;
+    }
     if (cache_w) {
         auto &sc = shadow_cache();
         auto it = sc.find(a.W);
@@ -436,8 +477,8 @@ void gemm_tc(const GemmArgs &a) {
         whi = ws.get<float>(nw); wlo = ws.get<float>(nw);
         split_tf32(a.W, a.K, whi, wlo, a.N, a.K);
     }
-    split_tf32(a.x, ldx, xhi, xlo, a.M, a.K);
-    const CUtensorMap *ma = get_map(xhi, a.M, a.K, a.K, TC_BM, false), *mal = get_map(xlo, a.M, a.K, a.K, TC_BM, true);
+    if (!pre_split) split_tf32(a.x, ldx, (float *)xhi, (float *)xlo, a.M, a.K);
+    const CUtensorMap *ma = get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), *mal = get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
     const CUtensorMap *mb = get_map(whi, a.N, a.K, a.K, 128, false), *mbl = get_map(wlo, a.N, a.K, a.K, 128, true);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * (2.0 * (double)a.M * a.K + 2.0 * (double)a.N * a.K + (double)a.M * a.N));
@@ -529,7 +570,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
     encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
     TcEpi ep;
-    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.ldy = M; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
+    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.ldy = M; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
     return 0;

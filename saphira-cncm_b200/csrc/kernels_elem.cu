@@ -22,18 +22,25 @@ __device__ __forceinline__ float act_apply(float v, int act) {
     }
 }
 
+__device__ __forceinline__ float tf32_hi(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return __uint_as_float(u);
+}
+
 // ---- LayerNorm: y = (x - mean) * rstd * w + b, statistics over C in two passes ----
 // One warp per row; the row (<= a few KB) is re-read from L1 for the second and third
 // pass. The affine step is evaluated unfused (mul then add) like the CPU definition.
 template <bool VEC4>
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ w,
                                                   const float *__restrict__ b, float *__restrict__ y,
-                                                  int64_t rows, int C, float eps) {
+                                                  float *__restrict__ ylo, int64_t rows, int C, float eps) {
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float *xr = x + row * C;
     float *yr = y + row * C;
+    float *lr = ylo ? ylo + row * C : nullptr;
     float s = 0.f;
     if (VEC4) {
         for (int c = lane * 4; c < C; c += 128) { float4 v = *(const float4 *)(xr + c); s += (v.x + v.y) + (v.z + v.w); }
@@ -63,28 +70,39 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
             o.y = __fadd_rn(__fmul_rn(__fmul_rn(v.y - mean, inv), ww.y), bb.y);
             o.z = __fadd_rn(__fmul_rn(__fmul_rn(v.z - mean, inv), ww.z), bb.z);
             o.w = __fadd_rn(__fmul_rn(__fmul_rn(v.w - mean, inv), ww.w), bb.w);
+            if (lr) {
+                float4 h = make_float4(tf32_hi(o.x), tf32_hi(o.y), tf32_hi(o.z), tf32_hi(o.w));
+                *(float4 *)(lr + c) = make_float4(o.x - h.x, o.y - h.y, o.z - h.z, o.w - h.w);
+                o = h;
+            }
             *(float4 *)(yr + c) = o;
         }
     } else {
-        for (int c = lane; c < C; c += 32)
-            yr[c] = __fadd_rn(__fmul_rn(__fmul_rn(xr[c] - mean, inv), w ? w[c] : 1.f), b ? b[c] : 0.f);
+        for (int c = lane; c < C; c += 32) {
+            float o = __fadd_rn(__fmul_rn(__fmul_rn(xr[c] - mean, inv), w ? w[c] : 1.f), b ? b[c] : 0.f);
+            if (lr) { float h = tf32_hi(o); lr[c] = o - h; o = h; }
+            yr[c] = o;
+        }
     }
 }
 
 static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
-void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps) {
+void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps) {
     if (rows <= 0) return;
-    ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 8);
-    bool v4 = (C % 4 == 0) && aligned16(x) && aligned16(y) && (!w || aligned16(w)) && (!b || aligned16(b));
+    ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * (y_lo ? 12 : 8));
+    bool v4 = (C % 4 == 0) && aligned16(x) && aligned16(y) && (!y_lo || aligned16(y_lo)) && (!w || aligned16(w)) && (!b || aligned16(b));
     unsigned g = grid1d(rows, 8);
-    if (v4) LAUNCH(k_layernorm<true>, g, 256, 0, x, w, b, y, rows, C, eps);
-    else LAUNCH(k_layernorm<false>, g, 256, 0, x, w, b, y, rows, C, eps);
+    if (v4) LAUNCH(k_layernorm<true>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps);
+    else LAUNCH(k_layernorm<false>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps);
+}
+void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps) {
+    layernorm_split(x, w, b, y, nullptr, rows, C, eps);
 }
 
 // ---- RMSNorm: y = x * rsqrt(mean(x^2) + 1e-6) * w ----
 __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ w,
-                                                float *__restrict__ y, int64_t rows, int C,
+                                                float *__restrict__ y, float *__restrict__ ylo, int64_t rows, int C,
                                                 int64_t ldx, int64_t ldy) {
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
@@ -95,13 +113,23 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, co
     for (int c = lane; c < C; c += 32) { float v = xr[c]; s += v * v; }
     float ms = warp_sum(s) / (float)C;
     float r = 1.0f / sqrtf(ms + 1e-6f);
-    for (int c = lane; c < C; c += 32) yr[c] = __fmul_rn(__fmul_rn(xr[c], r), w ? w[c] : 1.f);
+    float *lr = ylo ? ylo + row * ldy : nullptr;
+    for (int c = lane; c < C; c += 32) {
+        float o = __fmul_rn(__fmul_rn(xr[c], r), w ? w[c] : 1.f);
+        if (lr) { float h = tf32_hi(o); lr[c] = o - h; o = h; }
+        yr[c] = o;
+    }
 }
 
 void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 8);
-    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, rows, C, ldx, ldy);
+    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, (float *)nullptr, rows, C, ldx, ldy);
+}
+void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C) {
+    if (rows <= 0) return;
+    ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 12);
+    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, y_lo, rows, C, (int64_t)C, (int64_t)C);
 }
 
 // ---- element-wise ----
@@ -142,11 +170,26 @@ __global__ void k_glu(const float *__restrict__ gu, float *__restrict__ y, int64
     }
 }
 
+__global__ void k_interleave_rows(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ y, int64_t rows, int64_t cols) {
+    int64_t n = 2 * rows * cols;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / cols, c = i % cols;
+        const float *src = (r & 1) ? b : a;
+        y[i] = src ? src[(r >> 1) * cols + c] : 0.f;
+    }
+}
+
 static unsigned ew_grid(int64_t n) {
     int64_t g = cdiv(n, 256);
     int64_t cap = (int64_t)ctx().sm_count * 16;
     if (g > cap) g = cap;
     return (unsigned)(g < 1 ? 1 : g);
+}
+
+float *dev_interleave_rows(const float *a, const float *b, int64_t rows, int64_t cols) {
+    float *d = (float *)dev_alloc((size_t)(2 * rows * cols) * sizeof(float));
+    LAUNCH(k_interleave_rows, ew_grid(2 * rows * cols), 256, 0, a, b, d, rows, cols);
+    return d;
 }
 
 void add_inplace(float *y, const float *x, int64_t n) {

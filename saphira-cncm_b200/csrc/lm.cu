@@ -115,6 +115,7 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
             w.fcw = gu;
             w.pw = need(ws, "qwen", "model.layers.%d.mlp.down_proj.%s", li, "weight");
             w.Hh = m->I; w.gated = 1; w.act = ACT_SILU;
+            make_gated_interleaved(w, C, m->owned);
             m->blocks.push_back(w);
         }
         // rotary tables [n_ctx][hd], angle t * theta^(-2d/hd), pair-duplicated (qwen.c:85-110)

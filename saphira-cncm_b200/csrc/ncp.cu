@@ -193,6 +193,7 @@ extern "C" NCPState *ncp_load(const NCMConfig *c, WeightStore *ws, VQVAEState *v
         }
         w.pw = wneed(ws, "%smlp.c_proj.weight", pre)->data; w.pb = opt_data(wget(ws, "%smlp.c_proj.bias", pre));
         if (w.Hh > m->Hh) m->Hh = w.Hh;
+        make_gated_interleaved(w, C, m->owned);
         m->blocks.push_back(w);
     }
     // output heads (src/ncp.c:406-477)

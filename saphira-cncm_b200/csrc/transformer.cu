@@ -10,6 +10,24 @@
 
 namespace ncmb {
 
+void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps) {
+    if (kind == NORM_RMS) { if (y_lo) rmsnorm_split(x, w, y, y_lo, rows, C); else rmsnorm(x, w, y, rows, C, C, C); }
+    else layernorm_split(x, w, b, y, y_lo, rows, C, eps);
+}
+
+void make_gated_interleaved(BlockWeights &w, int C, std::vector<void *> &owned) {
+    if (!w.gated) return;
+    const float *gate = w.fcw, *up = w.fcw + (size_t)w.Hh * C;
+    float *il = dev_interleave_rows(gate, up, w.Hh, C);
+    owned.push_back(il);
+    w.fcw_il = il;
+    if (w.fcb) {
+        float *bil = dev_interleave_rows(w.fcb, w.fcb + w.Hh, w.Hh, 1);
+        owned.push_back(bil);
+        w.fcb_il = bil;
+    }
+}
+
 void apply_norm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, int kind, float eps) {
     if (kind == NORM_RMS) rmsnorm(x, w, y, rows, C, C, C);
     else layernorm(x, w, b, y, rows, C, eps);
@@ -27,12 +45,29 @@ __global__ void k_kv_store(const float *__restrict__ src, int64_t ldsrc, float *
     }
 }
 
+// Scratch for the lo halves of the block's GEMM inputs in three-pass mode (ln, ctx, hidden).
+static Workspace &block_lo_ws() { static Workspace w; return w; }
+
 void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights &w, const BlockBufs &b, const AttnPlan &p) {
     if (ntok <= 0) return;
     const int hd = C / H, kvd = nkv * hd, Wq = C + 2 * kvd;
-    apply_norm(x, w.ln1w, w.ln1b, b.ln, ntok, C, w.norm, w.eps);
+    // In three-pass mode the producers of GEMM inputs (norms, attention, MLP activation) write
+    // TF32 hi / lo pairs directly, so no separate split pass runs between kernels.
+    GemmArgs probe;
+    probe.x = b.ln; probe.ldx = C; probe.W = w.qkvw; probe.y = b.qkv; probe.ldy = Wq; probe.M = ntok; probe.N = Wq; probe.K = C;
+    static const bool fuse_split = !getenv("NCM_B200_NO_SPLIT_FUSE");
+    bool split = fuse_split && ctx().gemm_mode >= 2 && gemm_tc_supported(probe) && (C % 4 == 0) && (w.Hh % 4 == 0) && C >= 32 && w.Hh >= 32;
+    float *ln_lo = nullptr, *ctx_lo = nullptr, *h_lo = nullptr;
+    if (split) {
+        Workspace &lw = block_lo_ws();
+        size_t need = (size_t)ntok * (2 * (size_t)C + w.Hh) * 4 + 4096;
+        if (need > lw.cap) lw.reserve(need + need / 4);
+        lw.reset();
+        ln_lo = lw.get<float>((size_t)ntok * C); ctx_lo = lw.get<float>((size_t)ntok * C); h_lo = lw.get<float>((size_t)ntok * w.Hh);
+    }
+    apply_norm_split(x, w.ln1w, w.ln1b, b.ln, ln_lo, ntok, C, w.norm, w.eps);
     GemmArgs g;
-    g.x = b.ln; g.ldx = C; g.W = w.qkvw; g.bias = w.qkvb; g.y = b.qkv; g.ldy = Wq; g.M = ntok; g.N = Wq; g.K = C;
+    g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.W = w.qkvw; g.bias = w.qkvb; g.y = b.qkv; g.ldy = Wq; g.M = ntok; g.N = Wq; g.K = C;
     gemm(g);
     float *qp = b.qkv, *kp = b.qkv + C, *vp = b.qkv + C + kvd;
     qk_post(qp, Wq, H, kp, Wq, nkv, hd, ntok, w.qnw, w.knw, p.cos_t, p.sin_t, p.pos);
@@ -51,7 +86,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     else { a.k1 = kp; a.v1 = vp; a.ldk1 = Wq; }
     a.k1_start = p.k1_start; a.k1_len = p.k1_len;
     if (p.self_is_k2) { a.k2 = kp; a.v2 = vp; a.ldk2 = Wq; a.k2_start = p.k2_start ? p.k2_start : p.q_start; }
-    a.out = b.ctx; a.ldo = C;
+    a.out = b.ctx; a.out_lo = ctx_lo; a.ldo = C;
     a.q_start = p.q_start;
     a.rows = p.rows; a.H = H; a.Hkv = nkv; a.hd = hd; a.max_q = p.max_q;
     a.causal = p.causal; a.causal_off = p.causal_off; a.window = p.window;
@@ -59,21 +94,32 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     attention(a);
     // x += ctx Wo^T + bo
     g = GemmArgs();
-    g.x = b.ctx; g.ldx = C; g.W = w.ow; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
+    g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
     gemm(g);
-    apply_norm(x, w.ln2w, w.ln2b, b.ln, ntok, C, w.norm, w.eps);
+    apply_norm_split(x, w.ln2w, w.ln2b, b.ln, ln_lo, ntok, C, w.norm, w.eps);
     g = GemmArgs();
-    g.x = b.ln; g.ldx = C; g.W = w.fcw; g.bias = w.fcb; g.M = ntok; g.K = C;
+    g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.M = ntok; g.K = C;
     if (w.gated) {
-        g.y = b.mlp; g.N = 2 * w.Hh; g.ldy = 2 * w.Hh;
-        gemm(g);
-        glu_combine(b.mlp, b.h, ntok, w.Hh, w.act);
+        GemmArgs t = g;
+        t.W = w.fcw_il; t.bias = w.fcb_il; t.N = 2 * w.Hh; t.glu = 1; t.act = w.act; t.y = b.h; t.ldy = w.Hh;
+        static const bool fuse_glu = !getenv("NCM_B200_NO_GLU_FUSE");
+        if (fuse_glu && w.fcw_il && ctx().gemm_mode >= 1 && gemm_tc_supported(t)) {
+            t.y_lo = h_lo;                       // gated product fused into the epilogue (interleaved gate/up rows)
+            gemm(t);
+        } else {
+            g.x_lo = ln_lo;
+            g.W = w.fcw; g.bias = w.fcb; g.y = b.mlp; g.N = 2 * w.Hh; g.ldy = 2 * w.Hh;
+            gemm(g);
+            glu_combine(b.mlp, b.h, ntok, w.Hh, w.act);
+            h_lo = nullptr;
+        }
     } else {
-        g.y = b.h; g.N = w.Hh; g.ldy = w.Hh; g.act = w.act;
+        g.W = w.fcw; g.bias = w.fcb; g.y = b.h; g.y_lo = h_lo; g.N = w.Hh; g.ldy = w.Hh; g.act = w.act;
+        if (!(ctx().gemm_mode >= 1 && gemm_tc_supported(g))) { g.y_lo = nullptr; h_lo = nullptr; }
         gemm(g);
     }
     g = GemmArgs();
-    g.x = b.h; g.ldx = w.Hh; g.W = w.pw; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
+    g.x = b.h; g.x_lo = h_lo; g.ldx = w.Hh; g.W = w.pw; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
     gemm(g);
 }
 
