@@ -2,6 +2,7 @@
 // consumed as TF32, fp32 accumulation in tensor memory.
 //
 // One CTA per 128 x BN output tile, six warps:
+//   (persistent CTAs, one per SM, each walking a strided list of output tiles)
 //   warp 0   TMA producer: cp.async.bulk.tensor tiles of x and W (128-byte swizzle)
 //            into a ring of shared-memory stages, completion counted on mbarriers;
 //   warp 1   allocates BN columns of tensor memory and (one lane) issues
@@ -114,6 +115,91 @@ __device__ __forceinline__ float tc_act(float v, int act) {
     }
 }
 
+// Fused epilogue for one 32-column chunk of an accumulator row held in registers.
+__device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_t *r, int64_t m, int n0, int c0) {
+    if (m >= ep.M || n0 + c0 >= ep.N) return;
+    if (ep.glu) {
+        // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
+        float *yr = ep.y + m * ep.ldy + ((n0 + c0) >> 1);
+        float *lr = ep.y_lo ? ep.y_lo + m * ep.ldy + ((n0 + c0) >> 1) : nullptr;
+        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0);
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int n = n0 + c0 + 2 * (j + e);
+                float g = __uint_as_float(r[2 * (j + e)]), u = __uint_as_float(r[2 * (j + e) + 1]);
+                if (ep.bias && n + 1 < ep.N) { g += ep.bias[n]; u += ep.bias[n + 1]; }
+                o[e] = __fmul_rn(tc_act(g, ep.act), u);
+            }
+            if (full) {
+                float4 v = make_float4(o[0], o[1], o[2], o[3]);
+                if (lr) {
+                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
+                    *(float4 *)(lr + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
+                    v = h4;
+                }
+                *(float4 *)(yr + j) = v;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    int n = n0 + c0 + 2 * (j + e);
+                    if (n + 1 < ep.N) {
+                        float v = o[e];
+                        if (lr) { float hi = tc_tf32_hi(v); lr[j + e] = v - hi; v = hi; }
+                        yr[j + e] = v;
+                    }
+                }
+            }
+        }
+        return;
+    }
+    float *yr = ep.y + m * ep.ldy + n0 + c0;
+    const float *rr = ep.res ? ep.res + m * ep.ldres + n0 + c0 : nullptr;
+    const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0) && (!rr || (ep.ldres & 3) == 0);
+    if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            if (ep.bias) {
+                float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
+            if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
+            if (ep.y_lo) {
+                float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
+                *(float4 *)(ep.y_lo + m * ep.ldy + n0 + c0 + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
+                v = h4;
+            }
+            *(float4 *)(yr + j) = v;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            int n = n0 + c0 + j;
+            if (n < ep.N) {
+                float v = __uint_as_float(r[j]);
+                if (ep.bias) v += ep.bias[n];
+                v = tc_act(v, ep.act);
+                if (rr) v += rr[j];
+                if (ep.y_lo) { float hi = tc_tf32_hi(v); ep.y_lo[m * ep.ldy + n] = v - hi; v = hi; }
+                yr[j] = v;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Persistent kernel: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
+// (n-tile fastest, so CTAs running side by side share the same rows of x in L2). The
+// shared-memory ring runs continuously across tiles, and two TMEM accumulators alternate:
+// while the epilogue warps drain tile i, the MMA warp already accumulates tile i + 1.
+//
 // X3 = false: one TF32 pass over (A, B).  X3 = true: operands arrive split as
 // a = a_hi + a_lo (both exactly representable in TF32) and the tile accumulates
 // a_lo b_hi + a_hi b_lo + a_hi b_hi: fp32-grade products from three TF32 MMAs.
@@ -122,23 +208,23 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
                                                        const __grid_constant__ CUtensorMap tmB,
                                                        const __grid_constant__ CUtensorMap tmAlo,
                                                        const __grid_constant__ CUtensorMap tmBlo,
-                                                       TcEpi ep, int num_kb) {
+                                                       TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
     extern __shared__ unsigned char smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int A_TILE = TC_BM * TC_BK * 4, B_TILE = BN * TC_BK * 4;
     constexpr int A_BYTES = A_TILE * (X3 ? 2 : 1), B_BYTES = B_TILE * (X3 ? 2 : 1);   // [hi | lo] per stage
     unsigned char *sA = smem, *sB = smem + STAGES * A_BYTES;
-    uint64_t *bars = (uint64_t *)(sB + STAGES * B_BYTES);       // full[STAGES], empty[STAGES], tmem_full
-    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 1);
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull = smem_u32(bars + 2 * STAGES);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint64_t *bars = (uint64_t *)(sB + STAGES * B_BYTES);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * STAGES + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t afull0 = smem_u32(bars + 2 * STAGES), aempty0 = smem_u32(bars + 2 * STAGES + 2);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN;
-    const int64_t m0 = (int64_t)blockIdx.y * TC_BM;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        mbar_init(tfull, 1);
+        for (int a = 0; a < 2; a++) { mbar_init(afull0 + 8 * a, 1); mbar_init(aempty0 + 8 * a, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
@@ -148,7 +234,7 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
         }
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -158,145 +244,91 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            int armed = 0;
+            int kbg = 0, armed = 0;                       // k-block counter over all of this CTA's tiles
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; kb++) {
-                int s = kb % STAGES; uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-                ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 1);
-                if (!ok) break;
-                mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
-                tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, kb * TC_BK, (int)m0, full0 + 8 * s);
-                tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, kb * TC_BK, n0, full0 + 8 * s);
-                if (X3) {
-                    tma_load_2d(smem_u32(sA + s * A_BYTES + A_TILE), &tmAlo, kb * TC_BK, (int)m0, full0 + 8 * s);
-                    tma_load_2d(smem_u32(sB + s * B_BYTES + B_TILE), &tmBlo, kb * TC_BK, n0, full0 + 8 * s);
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int n0 = (t % tiles_n) * BN, m0 = (t / tiles_n) * TC_BM;
+                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                    int s = kbg % STAGES; uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+                    ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 1);
+                    if (!ok) break;
+                    mbar_expect_tx(full0 + 8 * s, A_BYTES + B_BYTES);
+                    tma_load_2d(smem_u32(sA + s * A_BYTES), &tmA, kb * TC_BK, m0, full0 + 8 * s);
+                    tma_load_2d(smem_u32(sB + s * B_BYTES), &tmB, kb * TC_BK, n0, full0 + 8 * s);
+                    if (X3) {
+                        tma_load_2d(smem_u32(sA + s * A_BYTES + A_TILE), &tmAlo, kb * TC_BK, m0, full0 + 8 * s);
+                        tma_load_2d(smem_u32(sB + s * B_BYTES + B_TILE), &tmBlo, kb * TC_BK, n0, full0 + 8 * s);
+                    }
+                    armed = kbg + 1;
                 }
-                armed = kb + 1;
             }
             if (!ok) {   // drain: wait (bounded) for the copies already in flight before leaving
                 int first = armed - STAGES < 0 ? 0 : armed - STAGES;
-                for (int kb = first; kb < armed; kb++) mbar_wait(full0 + 8 * (kb % STAGES), (uint32_t)(kb / STAGES) & 1u, ep.err, 4);
+                for (int k = first; k < armed; k++) mbar_wait(full0 + 8 * (k % STAGES), (uint32_t)(k / STAGES) & 1u, ep.err, 4);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_tf32(TC_BM, BN);
+            int kbg = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; kb++) {
-                int s = kb % STAGES; uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
-                ok = mbar_wait(full0 + 8 * s, ph, ep.err, 2);
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+                const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
+                ok = mbar_wait(aempty0 + 8 * acc, (use & 1u) ^ 1u, ep.err, 5);     // epilogue has drained this accumulator
                 if (!ok) break;
                 tc_fence_after();
-                uint64_t ad = umma_desc_sw128(smem_u32(sA + s * A_BYTES));
-                uint64_t bd = umma_desc_sw128(smem_u32(sB + s * B_BYTES));
-                if (X3) {
-                    uint64_t al = umma_desc_sw128(smem_u32(sA + s * A_BYTES + A_TILE));
-                    uint64_t bl = umma_desc_sw128(smem_u32(sB + s * B_BYTES + B_TILE));
+                const uint32_t tacc = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                    int s = kbg % STAGES; uint32_t ph = (uint32_t)(kbg / STAGES) & 1u;
+                    ok = mbar_wait(full0 + 8 * s, ph, ep.err, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint64_t ad = umma_desc_sw128(smem_u32(sA + s * A_BYTES));
+                    uint64_t bd = umma_desc_sw128(smem_u32(sB + s * B_BYTES));
+                    if (X3) {
+                        uint64_t al = umma_desc_sw128(smem_u32(sA + s * A_BYTES + A_TILE));
+                        uint64_t bl = umma_desc_sw128(smem_u32(sB + s * B_BYTES + B_TILE));
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 8; k++) {
-                        umma_tf32(tmem_base, al + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-                        umma_tf32(tmem_base, ad + (uint64_t)(k * 2), bl + (uint64_t)(k * 2), idesc, 1u);
+                        for (int k = 0; k < TC_BK / 8; k++) {
+                            umma_tf32(tacc, al + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                            umma_tf32(tacc, ad + (uint64_t)(k * 2), bl + (uint64_t)(k * 2), idesc, 1u);
+                        }
                     }
-                }
 #pragma unroll
-                for (int k = 0; k < TC_BK / 8; k++)      // 8 tf32 (32 bytes) per MMA: advance the start address
-                    umma_tf32(tmem_base, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (X3 || (kb | k)) ? 1u : 0u);
-                umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
+                    for (int k = 0; k < TC_BK / 8; k++)      // 8 tf32 (32 bytes) per MMA: advance the start address
+                        umma_tf32(tacc, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (X3 || (kb | k)) ? 1u : 0u);
+                    umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
+                }
+                umma_commit(afull0 + 8 * acc);               // accumulator complete (also reached on the error path)
             }
-            umma_commit(tfull);                          // accumulator complete (also reached on the error path)
         }
     } else {
-        const int q = warp & 3;                          // TMEM lane quadrant this warp may read
-        const int64_t m = m0 + q * 32 + lane;
-        bool ok = mbar_wait(tfull, 0, ep.err, 3);
-        tc_fence_after();
-        if (ok) {
+        const int q = warp & 3;                              // TMEM lane quadrant this warp may read
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+            const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
+            const int n0 = (t % tiles_n) * BN;
+            const int64_t m = (int64_t)(t / tiles_n) * TC_BM + q * 32 + lane;
+            ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 3);
+            tc_fence_after();
+            if (!ok) break;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
-                if (m < ep.M && n0 + c0 < ep.N) {
-                    if (ep.glu) {
-                        // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
-                        float *yr = ep.y + m * ep.ldy + ((n0 + c0) >> 1);
-                        float *lr = ep.y_lo ? ep.y_lo + m * ep.ldy + ((n0 + c0) >> 1) : nullptr;
-                        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0);
-#pragma unroll
-                        for (int j = 0; j < 16; j += 4) {
-                            float o[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                int n = n0 + c0 + 2 * (j + e);
-                                float g = __uint_as_float(r[2 * (j + e)]), u = __uint_as_float(r[2 * (j + e) + 1]);
-                                if (ep.bias && n + 1 < ep.N) { g += ep.bias[n]; u += ep.bias[n + 1]; }
-                                o[e] = __fmul_rn(tc_act(g, ep.act), u);
-                            }
-                            if (full) {
-                                float4 v = make_float4(o[0], o[1], o[2], o[3]);
-                                if (lr) {
-                                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
-                                    *(float4 *)(lr + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
-                                    v = h4;
-                                }
-                                *(float4 *)(yr + j) = v;
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 4; e++) {
-                                    int n = n0 + c0 + 2 * (j + e);
-                                    if (n + 1 < ep.N) {
-                                        float v = o[e];
-                                        if (lr) { float hi = tc_tf32_hi(v); lr[j + e] = v - hi; v = hi; }
-                                        yr[j + e] = v;
-                                    }
-                                }
-                            }
-                        }
-                    } else {
-                        float *yr = ep.y + m * ep.ldy + n0 + c0;
-                        const float *rr = ep.res ? ep.res + m * ep.ldres + n0 + c0 : nullptr;
-                        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0) && (!rr || (ep.ldres & 3) == 0);
-                        if (full) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 4) {
-                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                if (ep.bias) {
-                                    float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
-                                    v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-                                }
-                                v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
-                                if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
-                                if (ep.y_lo) {
-                                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
-                                    *(float4 *)(ep.y_lo + m * ep.ldy + n0 + c0 + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
-                                    v = h4;
-                                }
-                                *(float4 *)(yr + j) = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 32; j++) {
-                                int n = n0 + c0 + j;
-                                if (n < ep.N) {
-                                    float v = __uint_as_float(r[j]);
-                                    if (ep.bias) v += ep.bias[n];
-                                    v = tc_act(v, ep.act);
-                                    if (rr) v += rr[j];
-                                    if (ep.y_lo) { float hi = tc_tf32_hi(v); ep.y_lo[m * ep.ldy + n] = v - hi; v = hi; }
-                                    yr[j] = v;
-                                }
-                            }
-                        }
-                    }
-                }
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
+                tc_epilogue_chunk(ep, r, m, n0, c0);
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(aempty0 + 8 * acc);   // 4 arrivals (one per epilogue warp) free the accumulator
         }
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }
 }
 
@@ -421,15 +453,19 @@ bool gemm_tc_supported(const GemmArgs &a) {
 template <int BN, int STAGES, bool X3>
 static void launch_tc(const GemmArgs &a, const TcEpi &ep, const CUtensorMap *ma, const CUtensorMap *mb,
                       const CUtensorMap *mal, const CUtensorMap *mbl) {
-    constexpr size_t smem = 1024 + (size_t)STAGES * (TC_BM + BN) * TC_BK * 4 * (X3 ? 2 : 1) + (2 * STAGES + 1) * 8 + 16;
+    constexpr size_t smem = 1024 + (size_t)STAGES * (TC_BM + BN) * TC_BK * 4 * (X3 ? 2 : 1) + (2 * STAGES + 4) * 8 + 16;
+    static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
     static bool set = false;
     if (!set) {
         CUDA_CHECK(cudaFuncSetAttribute((k_gemm_tc<BN, STAGES, X3>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         set = true;
     }
-    dim3 grid((unsigned)cdiv(a.N, BN), (unsigned)cdiv(a.M, TC_BM));
+    int tiles_n = (int)cdiv(a.N, BN);
+    int64_t tiles = (int64_t)tiles_n * cdiv(a.M, TC_BM);
+    if (tiles > 0x7fffffff) fatal("gemm_tc: too many tiles");
+    int grid = (int)(tiles < ctx().sm_count ? tiles : ctx().sm_count);     // persistent: one CTA per SM
     int num_kb = (int)cdiv(a.K, TC_BK);
-    LAUNCH((k_gemm_tc<BN, STAGES, X3>), grid, TC_THREADS, smem, *ma, *mb, *mal, *mbl, ep, num_kb);
+    LAUNCH((k_gemm_tc<BN, STAGES, X3>), grid, TC_THREADS, smem, *ma, *mb, *mal, *mbl, ep, num_kb, tiles_n, (int)tiles);
 }
 
 void gemm_tc(const GemmArgs &a) {
@@ -445,7 +481,7 @@ void gemm_tc(const GemmArgs &a) {
         const CUtensorMap *mb = get_map(a.W, a.N, a.K, a.K, 128, true);
         ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                      4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
-        launch_tc<128, 3, false>(a, ep, ma, mb, ma, mb);
+        launch_tc<128, 6, false>(a, ep, ma, mb, ma, mb);
         return;
     }
     // three-pass mode: split both operands; static weights are split once and cached
