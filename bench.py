@@ -378,6 +378,121 @@ def run_gpu_arm(args):
     tmp.cleanup()
 
 
+# --------------------------------------------------------------------------- decoder LMs / quantizer sweep
+
+def lm_workload(name):
+    if name == "c3":
+        return synth.spec_gpt2_124m(), dict(prompt=128, n_new=256, temp=0.0, top_k=0, top_p=1.0, batch=1)
+    if name == "c4":
+        return synth.spec_qwen_05b(), dict(prompt=512, n_new=512, temp=0.7, top_k=0, top_p=0.95, batch=1)
+    if name == "c3t":
+        return synth.spec_gpt2_tiny(), dict(prompt=9, n_new=12, temp=0.0, top_k=0, top_p=1.0, batch=2)
+    raise SystemExit(f"unknown workload {name}")
+
+
+def run_lm_arm(args):
+    """GPT-2 / Qwen2 shaped decoding with a KV cache: tokens/s and achieved HBM GB/s per decode step."""
+    import torch
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    lib = capi.NcmLib(os.path.join(ROOT, "saphira-cncm_b200", "libncm_b200.so"))
+    if args.gemm is not None:
+        lib.ncmb_set_gemm_mode(args.gemm)
+    stream = torch.cuda.current_stream()
+    lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
+    spec, w = lm_workload(args.workload)
+    B = args.batch or w["batch"]
+    tmp = tempfile.TemporaryDirectory()
+    conf, wt = synth.write_lm(spec, tmp.name)
+    cfg = lib.load_config(conf)
+    m = lib.ncmb_lm_open(cfg, wt.encode(), int(spec.kind == "qwen"), 0)
+    prompts = np.ascontiguousarray(synth.lm_prompts(spec, B, w["prompt"], 5))
+    out = np.zeros((B, w["n_new"]), np.int32)
+
+    def step(seed):
+        lib.ncmb_lm_generate(m, prompts.ctypes.data, B, w["prompt"], w["n_new"], w["temp"], w["top_k"], w["top_p"],
+                             seed, -1, out.ctypes.data)
+
+    for i in range(args.warmup):
+        step(1 + i)
+    n0 = lib.ncmb_launch_count()
+    torch.cuda.synchronize()
+    with ClockSampler(local) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for i in range(args.steps):
+            step(100 + i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+    dev_s = e0.elapsed_time(e1) / 1000.0
+    launches = lib.ncmb_launch_count() - n0
+    C_, hd = spec.n_embd, spec.n_embd // spec.n_head
+    kvd = spec.n_kv_heads * hd
+    per_layer = C_ * (C_ + 2 * kvd) + C_ * C_ + (3 if spec.kind == "qwen" else 2) * C_ * spec.n_inner
+    params = spec.n_layer * per_layer + spec.vocab * C_
+    mean_ctx = w["prompt"] + w["n_new"] / 2.0
+    bytes_step = 4.0 * params + B * spec.n_layer * 2 * kvd * 4.0 * mean_ctx
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = peaks.get("hbm_gbs", 6650.0)
+    steps_total = args.steps * w["n_new"]
+    ach = bytes_step * steps_total / dev_s / 1e9
+    line = {
+        "metric": "generated tokens/sec", "value": B * steps_total / dev_s, "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * dev_s / args.steps,
+        "p50_token_latency_ms": 1000.0 * dev_s / steps_total, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: {spec.kind} {spec.n_layer}x{spec.n_embd}, vocab {spec.vocab}, prompt {w['prompt']}, "
+                               f"+{w['n_new']} tokens, batch {B}, temp {w['temp']}, top-p {w['top_p']}; KV-cached decode incl. prefill"},
+        "e2e": {"value": B * steps_total / wall, "unit": "tokens/s", "h2d_bytes_per_step": int(prompts.nbytes),
+                "d2h_bytes_per_step": int(out.nbytes)},
+        "gpu_launches": launches, "clocks": clk.summary(),
+        "roofline": {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)", "achieved": ach,
+                     "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                     "algorithmic_bytes_per_step": bytes_step},
+    }
+    print(json.dumps(line), flush=True)
+    lib.ncmb_lm_close(m)
+    tmp.cleanup()
+
+
+def run_quantizer_arm(args):
+    """Flat nearest-code search: N(0,1) 64-d vectors against a 16384 x 64 codebook (config-5 sweep)."""
+    import torch
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    lib = capi.NcmLib(os.path.join(ROOT, "saphira-cncm_b200", "libncm_b200.so"))
+    stream = torch.cuda.current_stream()
+    lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
+    spec = synth.spec_c2(n_layer=1, vocab=16384, name="c5q")
+    tmp = tempfile.TemporaryDirectory()
+    conf, wt = synth.write_ncp(spec, tmp.name)
+    model = capi.NcpModel(lib, conf, wt, arena_mb=64)
+    n = args.batch or (1 << 20)
+    x = torch.randn((n, 64), device="cuda", dtype=torch.float32, generator=torch.Generator(device="cuda").manual_seed(3))
+    idx = torch.empty((n,), device="cuda", dtype=torch.int32)
+    for _ in range(args.warmup):
+        lib.ncmb_vq_nearest_dev(model.vq, 3, x.data_ptr(), n, idx.data_ptr())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(args.steps):
+        lib.ncmb_vq_nearest_dev(model.vq, 3, x.data_ptr(), n, idx.data_ptr())
+    e1.record(stream)
+    torch.cuda.synchronize()
+    dev_s = e0.elapsed_time(e1) / 1000.0 / args.steps
+    flops = 2.0 * n * 16384 * 64
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = peaks.get("bf16_tflops", 1590.0)
+    print(json.dumps({"metric": "quantized vectors/sec", "value": n / dev_s, "unit": "vectors/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * dev_s, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"c5q: {n} fp32 N(0,1) 64-d vectors vs 16384 x 64 codebook, nearest code"},
+                      "roofline": {"bound": "tensor", "achieved": flops / dev_s / 1e12, "peak": peak, "unit": "TFLOP/s",
+                                   "frac": flops / dev_s / 1e12 / peak, "traffic": None}}), flush=True)
+    tmp.cleanup()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -392,7 +507,11 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and args.workload == "c2":
         args.warmup = 3
-    if args.impl == "reference":
+    if args.workload in ("c3", "c4", "c3t"):
+        run_lm_arm(args)
+    elif args.workload == "c5q":
+        run_quantizer_arm(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

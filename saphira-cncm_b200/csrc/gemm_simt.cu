@@ -218,6 +218,8 @@ void gemm_simt(const GemmArgs &g) {
     d.vec = (g.K % 4 == 0) && (d.ldx % 4 == 0) && (((uintptr_t)g.x & 15) == 0) && (((uintptr_t)g.W & 15) == 0);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)g.M * g.N * g.K,
                  4.0 * ((double)g.M * g.K + (double)g.N * g.K + (double)g.M * g.N));
+    // Few rows: the weights dominate the traffic and a 64x64 / 128x128 tiling would leave most
+    // SMs idle, so stream each weight row once through one warp (decode-time GEMV / skinny GEMM).
     if (g.M <= 16) {
         unsigned grid = grid1d((int64_t)g.N * 32, 256);
         if (g.M <= 1) LAUNCH(k_gemm_skinny<1>, grid, 256, 0, d);
