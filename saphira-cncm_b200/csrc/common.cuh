@@ -89,6 +89,10 @@ struct GemmArgs {
     // and the result may be written split (y = hi, y_lo = lo, same stride) for the next GEMM to consume.
     const float *x_lo = nullptr;
     float *y_lo = nullptr;
+    // nearest-row search instead of a stored product (tensor-core engine only): for every x row, the
+    // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
+    const float *argmin_colnorm = nullptr;
+    unsigned long long *argmin_best = nullptr;
 };
 void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
 void gemm_simt(const GemmArgs &a);

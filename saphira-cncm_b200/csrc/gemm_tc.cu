@@ -27,6 +27,7 @@ struct TcEpi {
     const float *bias; const float *res; int64_t ldres;
     float *y; float *y_lo; int64_t ldy;
     int64_t M; int N; int act; int glu;
+    const float *colnorm; unsigned long long *best;     // nearest-row mode
     int *err;
 };
 
@@ -313,11 +314,28 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
             ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 3);
             tc_fence_after();
             if (!ok) break;
+            float bestd = INFINITY; int bestn = 0x7fffffff;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                tc_epilogue_chunk(ep, r, m, n0, c0);
+                if (ep.best) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        int n = n0 + c0 + j;
+                        if (n < ep.N) {
+                            float d = fmaf(-2.0f, __uint_as_float(r[j]), ep.colnorm[n]);
+                            if (d < bestd) { bestd = d; bestn = n; }      // ascending n: strict < keeps the first minimum
+                        }
+                    }
+                } else {
+                    tc_epilogue_chunk(ep, r, m, n0, c0);
+                }
+            }
+            if (ep.best && m < ep.M && bestn != 0x7fffffff) {
+                unsigned u = __float_as_uint(bestd);
+                u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);           // order-preserving float -> uint
+                atomicMin(ep.best + m, ((unsigned long long)u << 32) | (unsigned)bestn);
             }
             tc_fence_before();
             __syncwarp();
@@ -445,7 +463,7 @@ bool gemm_tc_supported(const GemmArgs &a) {
     int64_t ldx = a.ldx ? a.ldx : a.K, ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     if (a.M < 64 || a.N < 32 || a.K < 32) return false;            // skinny shapes stay on CUDA cores (weight streaming)
     if ((a.K & 3) || (ldx & 3)) return false;                       // TMA strides: multiples of 16 bytes
-    if (!al16(a.x) || !al16(a.W) || !al16(a.y) || (a.bias && !al16(a.bias)) || (a.res && !al16(a.res))) return false;
+    if (!al16(a.x) || !al16(a.W) || (!a.argmin_best && !al16(a.y)) || (a.bias && !al16(a.bias)) || (a.res && !al16(a.res))) return false;
     if (a.glu && ((a.N & 1) || (ldy & 1))) return false;
     return true;
 }
@@ -474,6 +492,7 @@ void gemm_tc(const GemmArgs &a) {
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
     ep.y = a.y; ep.y_lo = a.y_lo; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
+    ep.colnorm = a.argmin_colnorm; ep.best = a.argmin_best;
     int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool x3 = ctx().gemm_mode >= 2;
     if (!x3) {
@@ -606,7 +625,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
     encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
     TcEpi ep;
-    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.ldy = M; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
+    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
     return 0;

@@ -87,8 +87,48 @@ __global__ void __launch_bounds__(NR_TILE) k_nearest(const float *__restrict__ x
     }
 }
 
+// ---- tensor-core route: |x - e|^2 = |x|^2 - 2 x.e + |e|^2, and |x|^2 does not change the argmin, so
+// the search is a [rows x V x D] GEMM whose epilogue keeps min_n(|e_n|^2 - 2 x.e_n) per row and never
+// writes the products. Three-pass TF32 keeps the dot products fp32-grade. ----
+__global__ void k_row_sqnorm(const float *__restrict__ E, int V, int D, float *__restrict__ out) {
+    int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= V) return;
+    float s = 0.f;
+    for (int c = 0; c < D; c++) { float e = E[(int64_t)v * D + c]; s = fmaf(e, e, s); }
+    out[v] = s;
+}
+__global__ void k_unpack_best(const unsigned long long *__restrict__ best, int64_t rows, int *__restrict__ idx_out,
+                              int out_tlen, int out_stride, int out_off) {
+    int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= rows) return;
+    int64_t b = r / out_tlen; int t = (int)(r % out_tlen);
+    idx_out[b * out_stride + out_off + t] = (int)(best[r] & 0xffffffffull);
+}
+
+static bool vq_nearest_tc(const float *x, const float *E, int64_t rows, int V, int D, int *idx_out, int out_tlen, int out_stride, int out_off) {
+    static Workspace ws;
+    GemmArgs g;
+    g.x = x; g.ldx = D; g.W = E; g.M = rows; g.N = V; g.K = D;
+    size_t need = (size_t)rows * 8 + (size_t)V * 4 + 1024;
+    if (need > ws.cap) ws.reserve(need + need / 4);
+    ws.reset();
+    unsigned long long *best = ws.get<unsigned long long>(rows);
+    float *cn = ws.get<float>(V);
+    g.argmin_best = best; g.argmin_colnorm = cn;
+    if (ctx().gemm_mode < 1 || !gemm_tc_supported(g)) return false;
+    CUDA_CHECK(cudaMemsetAsync(best, 0xff, (size_t)rows * 8, stream()));
+    LAUNCH(k_row_sqnorm, (unsigned)cdiv(V, 128), 128, 0, E, V, D, cn);
+    {
+        StaticWeights sw;                       // codebooks are model weights: cache their hi / lo split
+        gemm_tc(g);
+    }
+    LAUNCH(k_unpack_best, (unsigned)cdiv(rows, 256), 256, 0, best, rows, idx_out, out_tlen, out_stride, out_off);
+    return true;
+}
+
 void vq_nearest(const float *x, const float *E, int64_t rows, int V, int D, int *idx_out, int out_tlen, int out_stride, int out_off) {
     if (rows <= 0) return;
+    if (rows >= 1024 && vq_nearest_tc(x, E, rows, V, D, idx_out, out_tlen, out_stride, out_off)) return;
     size_t es_fl = (size_t)NR_TILE * (D + 1);
     if (es_fl < 2 * (size_t)NR_ROWS * NR_TILE) es_fl = 2 * (size_t)NR_ROWS * NR_TILE;
     size_t smem = sizeof(float) * ((size_t)NR_ROWS * D + es_fl);

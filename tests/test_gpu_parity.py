@@ -234,6 +234,36 @@ def test_quantizer_nearest_code_sweep(cuda, tmp):
     print(f"nearest-code: {len(diff)} near-ties of {n}")
 
 
+def test_quantizer_sweep_box_scale_codebook(cuda, tmp):
+    """N(0,1) vectors against a 16384 x 64 codebook (the box-scale sweep's shapes) on the tensor-core
+    route; 512 sampled rows are checked against the oracle's distances."""
+    import capi
+    import orc
+    import synth
+    spec = synth.spec_c2(n_layer=1, vocab=16384, name="c5_q")
+    conf, w = synth.write_ncp(spec, tmp)
+    m = capi.NcpModel(cuda, conf, w, arena_mb=64)
+    rng = np.random.default_rng(8)
+    n = 1 << 16
+    x = rng.standard_normal((n, 64)).astype(np.float32)
+    xd, idx_d = cuda.to_backend(x), cuda.alloc(n)
+    cuda.ncmb_vq_nearest_dev(m.vq, 2, xd, n, idx_d)
+    got = cuda.to_host(idx_d, (n,), np.int32)
+    assert cuda.ncmb_gemm_tc_check() == 0
+    assert got.min() >= 0 and got.max() < 16384
+    E = synth.ncp_tensors(spec, 1234)["tok.vq.embeddings.2.weight"]
+    pick = rng.choice(n, 512, replace=False)
+    d = orc.l2sq(x[pick], E)
+    want = d.argmin(axis=1)
+    ties = 0
+    for r, i in enumerate(pick):
+        if got[i] != want[r]:
+            a, b = d[r, got[i]], d[r, want[r]]
+            assert abs(a - b) <= 1e-5 * abs(b), (i, a, b)
+            ties += 1
+    print(f"box-scale nearest-code: {ties} near-ties in 512 sampled rows")
+
+
 @pytest.mark.parametrize("kind", ["gpt2", "qwen"])
 def test_decoder_lm_logits_and_generation(cuda, tmp, kind):
     import orc
