@@ -247,6 +247,14 @@ int   ncmb_get_gemm_mode(void);
 /* The tensor-core kernels bound every barrier wait; when one runs out they record a
  * code and drain. Returns and clears that code (0 = never happened); synchronises. */
 int   ncmb_gemm_tc_check(void);
+/* Diagnostic: the transformer blocks' token-major attention (head dim 64) on caller-supplied DEVICE
+ * buffers, with engine 0 (CUDA-core kernel) or 1 (tcgen05 kernel), so both can be compared on the same
+ * inputs. q [q_total][H*64]; kv1 / kv2 [tokens][2*Hkv*64] (keys, then values); *_start are HOST
+ * int[rows+1] prefix offsets, k2_start NULL for one key segment. Returns 0, -1 when the tensor-core
+ * engine does not take the shape, else the timeout code. No counterpart in the reference. */
+int   ncmb_attention_check(const float *q, const float *kv1, const float *kv2, float *out,
+                           const int *q_start, const int *k1_start, const int *k2_start,
+                           int rows, int H, int Hkv, int causal, int window, int engine);
 /* Sampling stream: 0 = the reference's single xorshift64* stream consumed in
  * (level, row, position) order (src/ncp.c:660-705) -- sampled codes equal the
  * reference's; 1 = counter-based, keyed by (seed, row_offset + row, level,

@@ -202,6 +202,7 @@ static void launch_attention(const AttnDev &d, dim3 grid) {
 
 void attention(const AttnArgs &a) {
     if (a.rows <= 0 || a.max_q <= 0) return;
+    if (ctx().gemm_mode >= 1 && attention_tc_supported(a)) { attention_tc(a); return; }
     AttnDev d;
     d.q = a.q; d.ldq = a.ldq; d.k1 = a.k1; d.v1 = a.v1; d.ldk1 = a.ldk1;
     d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo;

@@ -1,0 +1,424 @@
+// Tensor-core attention for head dim 64 on sm_100a (tcgen05 + TMEM + TMA).
+//
+// One CTA (256 threads) per (sequence row, head, 128-query tile):
+//   S = Q K^T   tcgen05.mma.kind::tf32 into tensor memory, keys in blocks of <= 128 columns; the
+//               first two key blocks and the query tile are fetched together by TMA
+//   softmax     two threads per query row (each takes half of the columns) read the scores with
+//               tcgen05.ld; all keys of a row are resident, so the row maximum is known before
+//               any exponential is taken and no rescaling is needed
+//   O += P V    per 32-key chunk: P is written to shared memory by the softmax threads, V (fetched
+//               for up to eight chunks ahead) is transposed on chip, tcgen05.mma accumulates the
+//               128 x 64 output in TMEM; P / V^T are double-buffered so the MMAs of one chunk run
+//               under the softmax of the next
+// Every product is three TF32 MMAs over hi/lo splits (a = a_hi + a_lo), formed on chip from the
+// fp32 tiles TMA brings in, so scores and outputs are fp32-grade like the CUDA-core kernel.
+// Key rows come from up to two segments (cached prefix, tokens of the current pass); each
+// segment is padded to a multiple of 32 score columns and the padding is masked in the softmax.
+//
+// Shared memory, three 64 KB regions reused between the two phases:
+//   R0  Q hi | Q lo                      then  V^T hi/lo, two buffers
+//   R1  even key blocks, K hi | K lo     then  ring of eight raw V chunks
+//   R2  odd key blocks,  K hi | K lo     then  P hi/lo, two buffers
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace ncmb {
+
+constexpr int ATC_THREADS = 256;
+constexpr int ATC_OCOL = 448;            // TMEM column of the output accumulator; scores use columns [0, 448)
+constexpr int ATC_VSLOTS = 8;
+constexpr int ATC_SMEM = 1024 + 3 * 65536 + 256 * 4 + 32 * 8 + 64;
+
+struct AttnTcDev {
+    float *out; float *out_lo; int64_t ldo;
+    const int *q_start, *k1_start, *k2_start, *k1_len;
+    int H, Hkv, causal, causal_off, window;
+    int pack;        // 1: the tile holds the (<= 32) queries of all H/Hkv (<= 4) heads that share one kv head, 32 rows per head
+    float scale;
+    int *err;
+};
+
+// byte offset of element (row, col) in a K-major tile of 32 floats per row with 128-byte swizzle
+__device__ __forceinline__ uint32_t sw128_off(int row, int col) {
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) & 7) << 4) + ((col & 3) << 2));
+}
+__device__ __forceinline__ float atc_hi(float v) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// in place: tile -> hi, and lo into the twin buffer; n4 float4 elements, layout-agnostic
+__device__ __forceinline__ void split_tile(unsigned char *hi, unsigned char *lo, int n4, int tid) {
+    for (int i = tid; i < n4; i += ATC_THREADS) {
+        float4 x = ((float4 *)hi)[i];
+        float4 h = make_float4(atc_hi(x.x), atc_hi(x.y), atc_hi(x.z), atc_hi(x.w));
+        ((float4 *)hi)[i] = h;
+        ((float4 *)lo)[i] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+    }
+}
+
+// A barrier wait that ran out marks the thread: its later waits return at once, so a CTA leaves within a
+// few wait limits. Control flow never depends on the outcome (all threads keep meeting at the same
+// __syncthreads); the host sees the code and discards the results.
+struct BoundedWaiter {
+    int *err; bool dead;
+    __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, int code) {
+        if (dead) return;
+        if (!mbar_wait(bar, parity, err, code)) dead = true;
+    }
+};
+
+__global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_constant__ CUtensorMap mq,
+                                                             const __grid_constant__ CUtensorMap mk1,
+                                                             const __grid_constant__ CUtensorMap mk2,
+                                                             AttnTcDev a) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char *R0 = smem, *R1 = smem + 65536, *R2 = smem + 131072;
+    float *xch = (float *)(smem + 196608);                       // 256 floats: row max / row sum exchange
+    uint64_t *bars = (uint64_t *)(xch + 256);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 32);
+    // barriers: 0 Q | 1,2 K region full | 3,4 S MMAs of a region done | 5,6 PV MMAs of a buffer done | 8..15 V slots
+    const uint32_t bar_q = smem_u32(bars), bar_k0 = smem_u32(bars + 1), bar_s0 = smem_u32(bars + 3);
+    const uint32_t bar_pv0 = smem_u32(bars + 5), bar_v0 = smem_u32(bars + 8);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int row = blockIdx.z, qt = blockIdx.x;
+    const int G = a.H / a.Hkv;
+    const int kvh = a.pack ? (int)blockIdx.y : (int)blockIdx.y / G;
+    const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
+    if (qt * 128 >= nq) return;
+    // a barrier wait that ran out anywhere earlier (this launch or a previous one) stops the rest of the grid
+    __shared__ int s_abort;
+    if (tid == 0) s_abort = *(volatile int *)a.err;
+    __syncthreads();
+    if (s_abort) return;
+    const int k10 = a.k1_start[row], n1 = a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - k10;
+    const int k20 = a.k2_start ? a.k2_start[row] : 0, n2 = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
+    const int n1p = (n1 + 31) & ~31, n2p = (n2 + 31) & ~31, nkp = n1p + n2p;
+    const int nblk = (nkp + 127) >> 7, nchunks = nkp >> 5;
+    const int vofs = a.Hkv * 64;
+    BoundedWaiter w{a.err, false};
+
+    if (tid == 0) {
+        for (int i = 0; i < 7; i++) mbar_init(bar_q + 8 * i, 1);
+        for (int i = 0; i < ATC_VSLOTS; i++) mbar_init(bar_v0 + 8 * i, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    // K block kb (128 padded keys, or what is left) -> region R1 / R2 as raw fp32, 32-row boxes
+    auto load_kblock = [&](int kb) {
+        unsigned char *dst = (kb & 1) ? R2 : R1;
+        const int kb0 = kb * 128, nrows = (nkp - kb0) < 128 ? (nkp - kb0) : 128;
+        const uint32_t bar = bar_k0 + 8 * (kb & 1);
+        mbar_expect_tx(bar, (uint32_t)nrows * 256);
+        for (int g = 0; g < nrows / 32; g++) {
+            int j0 = kb0 + g * 32;
+            const CUtensorMap *mk = j0 < n1p ? &mk1 : &mk2;
+            int tok = j0 < n1p ? k10 + j0 : k20 + (j0 - n1p);
+            tma_load_2d(smem_u32(dst + g * 4096), mk, kvh * 64, tok, bar);
+            tma_load_2d(smem_u32(dst + 16384 + g * 4096), mk, kvh * 64 + 32, tok, bar);
+        }
+    };
+    auto load_vchunk = [&](int c) {
+        const int c0 = c * 32, slot = c % ATC_VSLOTS;
+        const CUtensorMap *mk = c0 < n1p ? &mk1 : &mk2;
+        int tok = c0 < n1p ? k10 + c0 : k20 + (c0 - n1p);
+        const uint32_t bar = bar_v0 + 8 * slot;
+        mbar_expect_tx(bar, 8192);
+        tma_load_2d(smem_u32(R1 + slot * 8192), mk, vofs + kvh * 64, tok, bar);
+        tma_load_2d(smem_u32(R1 + slot * 8192 + 4096), mk, vofs + kvh * 64 + 32, tok, bar);
+    };
+
+    // ================= phase 1: S = Q K^T =================
+    if (tid == 0) {
+        if (a.pack) {                                             // mq has 32-row boxes here: one per head of the group
+            mbar_expect_tx(bar_q, (uint32_t)G * 8192);
+            for (int g = 0; g < G; g++) {
+                tma_load_2d(smem_u32(R0 + g * 4096), &mq, (kvh * G + g) * 64, q0, bar_q);
+                tma_load_2d(smem_u32(R0 + 16384 + g * 4096), &mq, (kvh * G + g) * 64 + 32, q0, bar_q);
+            }
+        } else {
+            mbar_expect_tx(bar_q, 32768);
+            tma_load_2d(smem_u32(R0), &mq, (int)blockIdx.y * 64, q0 + qt * 128, bar_q);
+            tma_load_2d(smem_u32(R0 + 16384), &mq, (int)blockIdx.y * 64 + 32, q0 + qt * 128, bar_q);
+        }
+        if (nblk > 0) load_kblock(0);
+        if (nblk > 1) load_kblock(1);
+    }
+    w.wait(bar_q, 0, 11);
+    split_tile(R0, R0 + 32768, 2048, tid);
+    uint32_t s_uses[2] = {0, 0}, s_waited[2] = {0, 0};            // commits issued / waited per region (uniform)
+    for (int kb = 0; kb < nblk; kb++) {
+        const int rg = kb & 1;
+        unsigned char *Kr = rg ? R2 : R1;
+        const int nrows = (nkp - kb * 128) < 128 ? (nkp - kb * 128) : 128;
+        w.wait(bar_k0 + 8 * rg, (uint32_t)(kb >> 1) & 1u, 12);
+        // rows >= nrows of a short block are never read by the MMA (N = nrows)
+        for (int at = 0; at < 2; at++) split_tile(Kr + at * 16384, Kr + 32768 + at * 16384, nrows * 8, tid);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t idesc = umma_idesc_tf32(128, nrows);
+            const uint32_t d = tmem + (uint32_t)(kb * 128);
+            for (int at = 0; at < 2; at++) {
+                uint64_t qh = umma_desc_sw128(smem_u32(R0 + at * 16384)), ql = umma_desc_sw128(smem_u32(R0 + 32768 + at * 16384));
+                uint64_t kh = umma_desc_sw128(smem_u32(Kr + at * 16384)), kl = umma_desc_sw128(smem_u32(Kr + 32768 + at * 16384));
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    umma_tf32(d, ql + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, (at | k) ? 1u : 0u);
+                    umma_tf32(d, qh + (uint64_t)(k * 2), kl + (uint64_t)(k * 2), idesc, 1u);
+                    umma_tf32(d, qh + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, 1u);
+                }
+            }
+            umma_commit(bar_s0 + 8 * rg);
+        }
+        s_uses[rg]++;
+        if (kb + 2 < nblk) {                                      // the region is needed again: drain it, refill
+            w.wait(bar_s0 + 8 * rg, s_waited[rg] & 1u, 13);
+            s_waited[rg]++;
+            if (tid == 0) load_kblock(kb + 2);
+        }
+    }
+    for (int rg = 0; rg < 2; rg++)
+        if (s_waited[rg] < s_uses[rg]) { w.wait(bar_s0 + 8 * rg, s_waited[rg] & 1u, 13); s_waited[rg]++; }
+    tc_fence_after();
+    __syncthreads();                                              // every thread is past phase 1: regions may be reused
+
+    // ================= phase 2: softmax and O = P V =================
+    if (tid == 0)
+        for (int c = 0; c < nchunks && c < ATC_VSLOTS; c++) load_vchunk(c);
+    const int r = tid & 127, half = tid >> 7;                     // query row of the tile, column half
+    const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
+    const int h = a.pack ? kvh * G + (r >> 5) : (int)blockIdx.y;
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    // visible columns of chunk c for this thread's query, as [jlo, jhi) relative to the chunk start
+    auto chunk_range = [&](int c, int &jlo, int &jhi) {
+        const int c0 = c * 32;
+        int lo, hi, base;                                         // key index = base + j
+        if (c0 < n1p) {
+            base = c0; lo = 0; hi = n1;
+            if (a.causal) hi = min(hi, qi + a.causal_off + 1);
+        } else {
+            base = n1 + (c0 - n1p); lo = n1; hi = n1 + n2;
+        }
+        if (a.window > 0) { lo = max(lo, qi - a.window); hi = min(hi, qi + a.window + 1); }
+        jlo = lo - base; jhi = hi - base;
+    };
+    float mx = -INFINITY;
+    for (int c = half; c < nchunks; c += 2) {
+        uint32_t v[32];
+        tmem_ld32(lane_addr + (uint32_t)(c * 32), v);
+        int jlo, jhi;
+        chunk_range(c, jlo, jhi);
+#pragma unroll
+        for (int j = 0; j < 32; j++)
+            if (j >= jlo && j < jhi) mx = fmaxf(mx, __uint_as_float(v[j]));
+    }
+    xch[tid] = mx;
+    __syncthreads();
+    mx = fmaxf(mx, xch[tid ^ 128]);
+    __syncthreads();                                              // xch is reused for the row sums
+    const bool any = mx != -INFINITY;
+    const float sl2 = a.scale * 1.4426950408889634f;
+
+    float l = 0.f;
+    for (int c = 0; c < nchunks; c++) {
+        const int b = c & 1;
+        unsigned char *Phi = R2 + b * 32768, *Plo = Phi + 16384;
+        unsigned char *Vthi = R0 + b * 16384, *Vtlo = Vthi + 8192;
+        if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
+        {
+            uint32_t v[16];
+            tmem_ld16(lane_addr + (uint32_t)(c * 32 + half * 16), v);
+            int jlo, jhi;
+            chunk_range(c, jlo, jhi);
+            jlo -= half * 16; jhi -= half * 16;
+            const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                float p[4], ph[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int j = g * 4 + e;
+                    float x = 0.f;
+                    if (any && j >= jlo && j < jhi) x = exp2f((__uint_as_float(v[j]) - mx) * sl2);
+                    l += x; p[e] = x; ph[e] = atc_hi(x);
+                }
+                const uint32_t o = rowoff + ((uint32_t)(((half * 4 + g) ^ (r & 7)) & 7) << 4);
+                *(float4 *)(Phi + o) = make_float4(ph[0], ph[1], ph[2], ph[3]);
+                *(float4 *)(Plo + o) = make_float4(p[0] - ph[0], p[1] - ph[1], p[2] - ph[2], p[3] - ph[3]);
+            }
+        }
+        w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
+        {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
+            const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
+            const int c0 = c * 32;
+            const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
+            const int kk = tid & 31;
+#pragma unroll
+            for (int n = 0; n < 8; n++) {
+                const int d = (tid >> 5) + 8 * n;
+                float x = *(const float *)(Vraw + (d >> 5) * 4096 + sw128_off(kk, d & 31));
+                if (kk >= nvalid) x = 0.f;
+                float hi = atc_hi(x);
+                uint32_t o = sw128_off(d, kk);
+                *(float *)(Vthi + o) = hi; *(float *)(Vtlo + o) = x - hi;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();
+        if (tid == 0) {
+            tc_fence_after();
+            const uint32_t idesc = umma_idesc_tf32(128, 64);
+            const uint32_t d = tmem + (uint32_t)ATC_OCOL;
+            uint64_t ph = umma_desc_sw128(smem_u32(Phi)), pl = umma_desc_sw128(smem_u32(Plo));
+            uint64_t vh = umma_desc_sw128(smem_u32(Vthi)), vl = umma_desc_sw128(smem_u32(Vtlo));
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                umma_tf32(d, pl + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
+                umma_tf32(d, ph + (uint64_t)(k * 2), vl + (uint64_t)(k * 2), idesc, 1u);
+                umma_tf32(d, ph + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, 1u);
+            }
+            umma_commit(bar_pv0 + 8 * b);
+            if (c + ATC_VSLOTS < nchunks) load_vchunk(c + ATC_VSLOTS);   // this chunk's raw V slot is free again
+        }
+    }
+    // the commits complete in order: the last one covers every earlier MMA
+    if (nchunks > 0) { const int c = nchunks - 1; w.wait(bar_pv0 + 8 * (c & 1), (uint32_t)(c >> 1) & 1u, 16); }
+    tc_fence_after();
+    xch[tid] = l;
+    __syncthreads();
+    l += xch[tid ^ 128];
+    // ---- output row: O / l; the two threads of a row take 32 columns each ----
+    {
+        const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + half * 32;
+        uint32_t v[32];
+        if (nchunks > 0) tmem_ld32(lane_addr + (uint32_t)(ATC_OCOL + half * 32), v);
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
+                                        __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (a.out_lo) {
+                    float4 h4 = make_float4(atc_hi(o4.x), atc_hi(o4.y), atc_hi(o4.z), atc_hi(o4.w));
+                    *(float4 *)(a.out_lo + ofs + j) = make_float4(o4.x - h4.x, o4.y - h4.y, o4.z - h4.z, o4.w - h4.w);
+                    o4 = h4;
+                }
+                *(float4 *)(a.out + ofs + j) = o4;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+bool attention_tc_supported(const AttnArgs &a) {
+    static const bool off = getenv("NCM_B200_ATTN_SIMT") != nullptr;
+    if (off || a.hd != 64 || a.Hkv <= 0 || a.H % a.Hkv) return false;
+    const int G = a.H / a.Hkv;
+    const bool pack = a.max_q <= 32 && G >= 2 && G <= 4;         // grouped-query passes with few queries per row
+    if (!pack && a.max_q < 64) return false;
+    if (a.max_k1 <= 0 && a.max_k2 <= 0) return false;
+    int n1p = (a.max_k1 + 31) & ~31, n2p = (a.max_k2 + 31) & ~31;
+    if (n1p + n2p > ATC_OCOL || n1p + n2p == 0) return false;
+    if (a.q_total <= 0 || a.k1_total <= 0 || (a.k2 && a.k2_total <= 0)) return false;
+    if ((a.ldq | a.ldk1 | a.ldk2 | a.ldo) & 3) return false;
+    if (a.v1 != a.k1 + a.Hkv * 64 || (a.k2 && a.v2 != a.k2 + a.Hkv * 64)) return false;
+    auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (!al(a.q) || !al(a.k1) || (a.k2 && !al(a.k2)) || !al(a.out) || (a.out_lo && !al(a.out_lo))) return false;
+    return true;
+}
+
+void attention_tc(const AttnArgs &a) {
+    AttnTcDev d;
+    d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo;
+    d.q_start = a.q_start; d.k1_start = a.k1_start; d.k2_start = a.k2 ? a.k2_start : nullptr; d.k1_len = a.k1_len;
+    d.H = a.H; d.Hkv = a.Hkv; d.causal = a.causal; d.causal_off = a.causal_off; d.window = a.window;
+    d.scale = 1.0f / sqrtf(64.0f);
+    d.err = tc_err_flag();
+    const int G = a.H / a.Hkv;
+    d.pack = (a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
+    const CUtensorMap *mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);
+    const CUtensorMap *mk1 = tc_get_map(a.k1, a.k1_total, 2 * a.Hkv * 64, a.ldk1, 32, false);
+    const CUtensorMap *mk2 = a.k2 ? tc_get_map(a.k2, a.k2_total, 2 * a.Hkv * 64, a.ldk2, 32, false) : mk1;
+    static bool set = false;
+    if (!set) {
+        CUDA_CHECK(cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+        set = true;
+    }
+    dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
+    ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+    LAUNCH(k_attention_tc, grid, ATC_THREADS, ATC_SMEM, *mq, *mk1, *mk2, d);
+}
+
+} // namespace ncmb
+
+// Diagnostic entry point: runs the token-major attention of the transformer blocks on caller-supplied
+// device buffers with either engine (0: CUDA-core kernel, 1: tcgen05 kernel), so the two can be compared
+// on the same inputs. q [q_total][H*64]; kv1 / kv2 [tokens][2*Hkv*64] (keys then values); the *_start
+// arrays are host int[rows+1] prefix offsets (k2_start null: one key segment). Returns 0, -1 when the
+// tensor-core engine does not take the shape, or the engine's timeout code.
+extern "C" int ncmb_attention_check(const float *q, const float *kv1, const float *kv2, float *out,
+                                    const int *q_start, const int *k1_start, const int *k2_start,
+                                    int rows, int H, int Hkv, int causal, int window, int engine) {
+    using namespace ncmb;
+    ensure_device();
+    int *d_q = (int *)dev_alloc((size_t)(rows + 1) * 4), *d_k1 = (int *)dev_alloc((size_t)(rows + 1) * 4), *d_k2 = nullptr;
+    upload(d_q, q_start, (size_t)(rows + 1) * 4);
+    upload(d_k1, k1_start, (size_t)(rows + 1) * 4);
+    if (k2_start) { d_k2 = (int *)dev_alloc((size_t)(rows + 1) * 4); upload(d_k2, k2_start, (size_t)(rows + 1) * 4); }
+    AttnArgs a;
+    int kvd = Hkv * 64;
+    a.q = q; a.ldq = H * 64; a.k1 = kv1; a.v1 = kv1 + kvd; a.ldk1 = 2 * kvd;
+    if (k2_start) { a.k2 = kv2; a.v2 = kv2 + kvd; a.ldk2 = 2 * kvd; a.k2_start = d_k2; }
+    a.out = out; a.ldo = H * 64; a.q_start = d_q; a.k1_start = d_k1;
+    a.rows = rows; a.H = H; a.Hkv = Hkv; a.hd = 64; a.causal = causal; a.window = window;
+    for (int r = 0; r < rows; r++) {
+        a.max_q = std::max(a.max_q, q_start[r + 1] - q_start[r]);
+        a.max_k1 = std::max(a.max_k1, k1_start[r + 1] - k1_start[r]);
+        if (k2_start) a.max_k2 = std::max(a.max_k2, k2_start[r + 1] - k2_start[r]);
+    }
+    a.q_total = q_start[rows]; a.k1_total = k1_start[rows]; a.k2_total = k2_start ? k2_start[rows] : 0;
+    a.total_q = a.q_total; a.avg_keys = rows ? (double)(a.k1_total + a.k2_total) / rows : 0;
+    int rc = 0;
+    if (engine == 1) {
+        int saved_max_q = a.max_q;
+        a.max_q = std::max(a.max_q, 64);               // the size threshold is a dispatch heuristic, not a limit
+        if (!attention_tc_supported(a)) rc = -1;
+        else { a.max_q = saved_max_q; attention_tc(a); rc = gemm_tc_check(); }
+    } else {
+        int saved = ctx().gemm_mode;
+        ctx().gemm_mode = 0;
+        attention(a);
+        ctx().gemm_mode = saved;
+    }
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    dev_free(d_q); dev_free(d_k1); if (d_k2) dev_free(d_k2);
+    return rc;
+}

@@ -144,12 +144,17 @@ struct AttnArgs {
     const int *q_start, *k1_start, *k2_start = nullptr;   // device int[rows+1]
     const int *k1_len = nullptr;                 // optional device int[rows]: segment-1 lengths (strided caches)
     int rows, H, Hkv, hd;
-    int max_q;                                   // max queries of any row (grid sizing)
+    int max_q = 0;                                 // max queries of any row (grid sizing)
     int causal = 0, causal_off = 0;
     int window = 0;                              // > 0: key j visible to query i only if |i - j| <= window
     int64_t total_q = 0; double avg_keys = 0;    // for the profiler only
+    // tensor-core path only (0 = unknown, which keeps the call on the CUDA-core kernel):
+    int max_k1 = 0, max_k2 = 0;                  // longest key segment of any row
+    int64_t q_total = 0, k1_total = 0, k2_total = 0;   // token rows the q / k1 / k2 buffers hold (TMA bounds)
 };
 void attention(const AttnArgs &a);
+bool attention_tc_supported(const AttnArgs &a);  // attention_tc.cu: head dim 64, >= 64 queries, <= 448 padded keys
+void attention_tc(const AttnArgs &a);
 // reference-layout SDPA with an additive [Tq][Tkv] mask (ncm.h API)
 void sdpa_masked(const float *q, const float *k, const float *v, const float *mask, float *out,
                  int B, int Hq, int Hkv, int Tq, int Tkv, int hd);
@@ -202,6 +207,7 @@ struct AttnPlan {
     int rows = 0, max_q = 0, causal = 0, causal_off = 0, window = 0;
     const int *pos = nullptr; const float *cos_t = nullptr, *sin_t = nullptr;
     int64_t total_q = 0; double avg_keys = 0;
+    int max_k1 = 0; int64_t k1_total = 0;  // longest segment-1 key run; token rows behind k1 (0 = not stated)
     // after the K/V of this pass are final (norm + rope applied) they are stored here:
     float *kv_store = nullptr; int64_t kv_pitch = 0;   // row pitch in floats; rows = tokens, width 2*kvd
     int kv_rows_per_seq = 0; int64_t kv_seq_pitch = 0; // > 0: token t of sequence s goes to s*kv_seq_pitch + t*kv_pitch

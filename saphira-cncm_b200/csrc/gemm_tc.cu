@@ -13,15 +13,14 @@
 // epilogue overlaps the other's main loop. Every mbarrier wait is bounded: on a
 // timeout the kernel records an error code and drains instead of spinning.
 #include "common.cuh"
+#include "tc_common.cuh"
 
-#include <cuda.h>
 #include <unordered_map>
 
 namespace ncmb {
 
-constexpr int TC_BM = 128, TC_BK = 32;           // BK floats = 128 bytes = one swizzle row
+constexpr int TC_BM = 128;
 constexpr int TC_THREADS = 192;
-constexpr unsigned long long TC_WAIT_NS = 2000000000ull;   // 2 s per barrier wait, then give up
 
 struct TcEpi {
     const float *bias; const float *res; int64_t ldres;
@@ -31,80 +30,6 @@ struct TcEpi {
     int *err;
 };
 
-__device__ __forceinline__ float tc_tf32_hi(float v) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
-    return __uint_as_float(u);
-}
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ unsigned long long gtime_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-// bounded wait on a phase parity; false (and an error code) when the limit runs out
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *err, int code) {
-    unsigned long long t0 = 0;
-    for (uint32_t it = 0;; it++) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((it & 255u) == 255u) {
-            unsigned long long now = gtime_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > TC_WAIT_NS) { atomicExch(err, code); return false; }
-        }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tm, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// shared-memory matrix descriptor, K-major, 128-byte swizzle: 8-row groups are 1024 bytes apart
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);           // start address
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
-    d |= (uint64_t)1 << 46;                            // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                            // layout: SWIZZLE_128B
-    return d;
-}
-// instruction descriptor: D fp32, A/B tf32, both K-major, M x N tile
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 __device__ __forceinline__ float tc_act(float v, int act) {
     switch (act) {
@@ -192,9 +117,6 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_
     }
 }
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // Persistent kernel: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
 // (n-tile fastest, so CTAs running side by side share the same rows of x in L2). The
@@ -388,7 +310,7 @@ static int tma_dtype_mode() {          // 1 (default): TMA rounds fp32 to tf32 w
 
 // 2-D map over a row-major [rows][K] fp32 matrix with row stride ld: box = 32 floats x box_rows.
 // round_tf32: let the TMA unit round each element to TF32 on the way into shared memory.
-static const CUtensorMap *get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
+const CUtensorMap *tc_get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     int dt = (round_tf32 && tma_dtype_mode()) ? 1 : 0;
     MapKey key{p, rows, ld, K, box_rows, dt};
@@ -407,7 +329,7 @@ static const CUtensorMap *get_map(const float *p, int64_t rows, int K, int64_t l
     return &cache.emplace(key, tm).first->second;
 }
 
-static int *tc_err_flag() {
+int *tc_err_flag() {
     static int *d = nullptr;
     if (!d) { d = (int *)dev_alloc(sizeof(int)); CUDA_CHECK(cudaMemsetAsync(d, 0, sizeof(int), stream())); }
     return d;
@@ -496,8 +418,8 @@ void gemm_tc(const GemmArgs &a) {
     int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool x3 = ctx().gemm_mode >= 2;
     if (!x3) {
-        const CUtensorMap *ma = get_map(a.x, a.M, a.K, ldx, TC_BM, true);
-        const CUtensorMap *mb = get_map(a.W, a.N, a.K, a.K, 128, true);
+        const CUtensorMap *ma = tc_get_map(a.x, a.M, a.K, ldx, TC_BM, true);
+        const CUtensorMap *mb = tc_get_map(a.W, a.N, a.K, a.K, 128, true);
         ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                      4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
         launch_tc<128, 6, false>(a, ep, ma, mb, ma, mb);
@@ -533,8 +455,8 @@ void gemm_tc(const GemmArgs &a) {
         split_tf32(a.W, a.K, whi, wlo, a.N, a.K);
     }
     if (!pre_split) split_tf32(a.x, ldx, (float *)xhi, (float *)xlo, a.M, a.K);
-    const CUtensorMap *ma = get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), *mal = get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
-    const CUtensorMap *mb = get_map(whi, a.N, a.K, a.K, 128, false), *mbl = get_map(wlo, a.N, a.K, a.K, 128, true);
+    const CUtensorMap *ma = tc_get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), *mal = tc_get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
+    const CUtensorMap *mb = tc_get_map(whi, a.N, a.K, a.K, 128, false), *mbl = tc_get_map(wlo, a.N, a.K, a.K, 128, true);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * (2.0 * (double)a.M * a.K + 2.0 * (double)a.N * a.K + (double)a.M * a.N));
     launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);

@@ -210,7 +210,7 @@ void lm_prefill(LMRun &r) {
     lm_embed(r, r.ids_d, r.pos_d, n);
     AttnPlan p;
     p.q_start = p.k1_start = r.start_np;
-    p.rows = r.B; p.max_q = r.np; p.causal = 1;
+    p.rows = r.B; p.max_q = r.np; p.max_k1 = r.np; p.causal = 1;
     p.pos = r.pos_d;
     if (m->is_qwen) { p.cos_t = m->cosb; p.sin_t = m->sinb; }
     p.total_q = n; p.avg_keys = (r.np + 1) / 2.0;

@@ -285,7 +285,7 @@ static void prefix_pass(NCPGen *g) {
     NCPState *m = g->m;
     AttnPlan p;
     p.q_start = p.k1_start = g->row_start_d;
-    p.rows = g->Bm; p.max_q = g->max_row;
+    p.rows = g->Bm; p.max_q = g->max_row; p.max_k1 = g->max_row;
     p.pos = g->tok_pos_d;
     if (m->cfg.use_rope) { p.cos_t = m->gcos[0]; p.sin_t = m->gsin[0]; }
     p.total_q = g->ntok; p.avg_keys = g->Bm ? (double)g->ntok / g->Bm : 0;
@@ -309,7 +309,7 @@ static void level_pass(NCPGen *g, float *x, int Lc, int hi, int lev_slot) {
     p.k1_start = g->row_start_d;
     p.ldk1 = 2 * kvd;
     p.self_is_k2 = 1;
-    p.rows = g->Bm; p.max_q = Lc;
+    p.rows = g->Bm; p.max_q = Lc; p.max_k1 = g->max_row; p.k1_total = g->ntok;
     p.pos = g->lev_pos_d[lev_slot];
     if (m->cfg.use_rope) { p.cos_t = m->gcos[hi]; p.sin_t = m->gsin[hi]; }
     p.total_q = n; p.avg_keys = (g->Bm ? (double)g->ntok / g->Bm : 0) + Lc;

@@ -91,6 +91,8 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     a.rows = p.rows; a.H = H; a.Hkv = nkv; a.hd = hd; a.max_q = p.max_q;
     a.causal = p.causal; a.causal_off = p.causal_off; a.window = p.window;
     a.total_q = p.total_q; a.avg_keys = p.avg_keys;
+    a.max_k1 = p.max_k1; a.max_k2 = p.self_is_k2 ? p.max_q : 0;
+    a.q_total = ntok; a.k1_total = p.k1 ? p.k1_total : ntok; a.k2_total = p.self_is_k2 ? ntok : 0;
     attention(a);
     // x += ctx Wo^T + bo
     g = GemmArgs();

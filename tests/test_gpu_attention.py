@@ -1,0 +1,98 @@
+"""Token-major attention of the transformer blocks: the tcgen05 kernel against the CUDA-core kernel
+and against a float64 softmax(QK^T/sqrt(d))V, through ncmb_attention_check.
+
+Shapes follow the callers: ragged prefix rows attending to themselves (the NCP prefix pass,
+reference src/ncp.c forward over the prefix), causal rows (decoder-LM prefill), rows whose few
+queries see a cached segment plus their own tokens (NCP level passes; grouped-query heads are
+packed into one tile), and the windowed form of the VQ-VAE attention layers.
+"""
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    import capi
+    return capi.NcmLib(helpers.CUDA_LIB)
+
+
+def _want(q, kv1, kv2, qs, k1s, k2s, H, Hkv, causal, window):
+    out = np.zeros(q.shape, dtype=np.float64)
+    kvd = Hkv * 64
+    for r in range(len(qs) - 1):
+        for h in range(H):
+            kvh = h // (H // Hkv)
+            Q = q[qs[r]:qs[r + 1], h * 64:(h + 1) * 64].astype(np.float64)
+            K = kv1[k1s[r]:k1s[r + 1], kvh * 64:(kvh + 1) * 64]
+            V = kv1[k1s[r]:k1s[r + 1], kvd + kvh * 64:kvd + (kvh + 1) * 64]
+            n1 = K.shape[0]
+            if k2s is not None:
+                K = np.concatenate([K, kv2[k2s[r]:k2s[r + 1], kvh * 64:(kvh + 1) * 64]])
+                V = np.concatenate([V, kv2[k2s[r]:k2s[r + 1], kvd + kvh * 64:kvd + (kvh + 1) * 64]])
+            S = Q @ K.astype(np.float64).T * 0.125
+            qi = np.arange(Q.shape[0])[:, None]
+            kj = np.arange(K.shape[0])[None, :]
+            vis = np.ones(S.shape, bool)
+            if causal:
+                vis &= ~((kj < n1) & (kj > qi))
+            if window > 0:
+                vis &= np.abs(kj - qi) <= window
+            S = np.where(vis, S, -np.inf)
+            P = np.exp(S - S.max(1, keepdims=True))
+            out[qs[r]:qs[r + 1], h * 64:(h + 1) * 64] = (P / P.sum(1, keepdims=True)) @ V.astype(np.float64)
+    return out
+
+
+CASES = {
+    # name: (query rows, segment-1 keys, segment-2 keys or None, H, Hkv, causal, window)
+    "one_full_tile": ([128], [128], None, 1, 1, 0, 0),
+    "ragged_prefix_rows": ([256, 70, 131, 1], [256, 70, 131, 1], None, 8, 8, 0, 0),
+    "grouped_heads_prefix": ([200, 33], [200, 33], None, 8, 2, 0, 0),
+    "causal_prefill": ([200, 64, 448], [200, 64, 448], None, 4, 2, 1, 0),
+    "cache_plus_own_tokens": ([64, 17, 100], [250, 3, 77], [64, 17, 100], 4, 4, 0, 0),
+    "level_pass_packed_g4": ([32, 17, 1, 4], [250, 3, 77, 256], [32, 17, 1, 4], 8, 2, 0, 0),
+    "level_pass_packed_g2": ([16, 5], [40, 100], [16, 5], 4, 2, 0, 0),
+    "packed_one_segment_three_key_blocks": ([8, 32], [300, 129], None, 4, 1, 0, 0),
+    "windowed": ([150], [150], None, 2, 2, 0, 16),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_tensor_core_attention_matches_cuda_core_and_float64(cuda, name):
+    qlens, k1lens, k2lens, H, Hkv, causal, window = CASES[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    off = lambda lens: np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    qs, k1s = off(qlens), off(k1lens)
+    k2s = None if k2lens is None else off(k2lens)
+    q = rng.standard_normal((qs[-1], H * 64)).astype(np.float32)
+    kv1 = rng.standard_normal((k1s[-1], 2 * Hkv * 64)).astype(np.float32)
+    kv2 = None if k2s is None else rng.standard_normal((k2s[-1], 2 * Hkv * 64)).astype(np.float32)
+    qd, k1d = cuda.to_backend(q), cuda.to_backend(kv1)
+    k2d = None if kv2 is None else cuda.to_backend(kv2)
+    want = _want(q, kv1, kv2, qs, k1s, k2s, H, Hkv, causal, window)
+    got = {}
+    for engine in (0, 1):
+        od = cuda.alloc(q.size)
+        rc = cuda.ncmb_attention_check(qd, k1d, k2d, od, qs.ctypes.data, k1s.ctypes.data,
+                                       None if k2s is None else k2s.ctypes.data,
+                                       len(qlens), H, Hkv, causal, window, engine)
+        assert rc == 0, (name, engine, rc)
+        got[engine] = cuda.to_host(od, q.shape)
+    # fp32 CUDA-core kernel: ~1e-6; three-pass TF32 drops only the lo*lo term: a few 1e-6
+    assert np.abs(got[0] - want).max() < 4e-6
+    assert np.abs(got[1] - want).max() < 8e-6
+    assert not np.isnan(got[1]).any()
+
+
+def test_shapes_outside_the_tensor_core_kernel_are_reported_not_rerouted(cuda):
+    # 480 padded keys + 64 output columns do not fit the 512 tensor-memory columns
+    qs = np.array([0, 64], np.int32)
+    ks = np.array([0, 480], np.int32)
+    q = cuda.alloc(64 * 64)
+    kv = cuda.alloc(480 * 128)
+    out = cuda.alloc(64 * 64)
+    assert cuda.ncmb_attention_check(q, kv, None, out, qs.ctypes.data, ks.ctypes.data, None, 1, 1, 1, 0, 0, 1) == -1
