@@ -351,7 +351,8 @@ def run_gpu_arm(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": 1000.0 * dev_s / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None,
-            "dtype": {0: "f32", 1: "tf32 (fp32 accumulate)", 2: "3xtf32 (fp32 accumulate)"}.get(mode, "f32"),
+            "dtype": {0: "f32", 1: "tf32 (fp32 accumulate)", 2: "3xtf32 (fp32 accumulate)",
+                      3: "f16 pairs x3 (fp32-grade operands, fp32 accumulate)"}.get(mode, "f32"),
             "data": "synthetic",
             "config": workload_config(args.workload, spec, B, world),
             "codes_per_sec": world * B * sum(spec.levels) * args.steps / dev_s,
@@ -501,7 +502,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2")
     ap.add_argument("--batch", type=int, default=0, help="sequences per GPU (default: the workload's)")
-    ap.add_argument("--gemm", type=int, default=None, help="GEMM engine override (0 fp32, 1 tf32, 2 3xtf32)")
+    ap.add_argument("--gemm", type=int, default=None, help="GEMM engine override (0 fp32, 1 tf32, 2 3xtf32, 3 fp16 pairs)")
     ap.add_argument("--cpu-rows", type=int, default=1, help="sequences in the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

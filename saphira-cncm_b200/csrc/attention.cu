@@ -12,6 +12,7 @@
 //  * sdpa_masked(): the reference kernel API (head-major tensors, additive mask).
 //  * qk_post(): per-head RMSNorm (optional) + rotary embedding, in place.
 #include "common.cuh"
+#include "split.cuh"
 
 namespace ncmb {
 
@@ -24,7 +25,7 @@ struct AttnDev {
     const float *q; int64_t ldq;
     const float *k1, *v1; int64_t ldk1;
     const float *k2, *v2; int64_t ldk2;
-    float *out; float *out_lo; int64_t ldo;
+    float *out; float *out_lo; int64_t ldo; int out_fmt;
     const int *q_start, *k1_start, *k2_start, *k1_len;
     int H, Hkv, hd;
     int causal, causal_off, window;
@@ -175,14 +176,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) k_attention(AttnDev a) {
             if (d < HD) {
                 float v = o[t][i] * inv;
                 int64_t at = (int64_t)(q0 + qi) * a.ldo + h * HD + d;
-                if (a.out_lo) {
-                    uint32_t u;
-                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
-                    float hi = __uint_as_float(u);
-                    a.out_lo[at] = v - hi;
-                    v = hi;
-                }
-                a.out[at] = v;
+                if (a.out_lo) store_split1(a.out, a.out_lo, at, v, a.out_fmt);
+                else a.out[at] = v;
             }
         }
     }
@@ -205,7 +200,7 @@ void attention(const AttnArgs &a) {
     if (ctx().gemm_mode >= 1 && attention_tc_supported(a)) { attention_tc(a); return; }
     AttnDev d;
     d.q = a.q; d.ldq = a.ldq; d.k1 = a.k1; d.v1 = a.v1; d.ldk1 = a.ldk1;
-    d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo;
+    d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo; d.out_fmt = a.out_fmt;
     d.q_start = a.q_start; d.k1_start = a.k1_start; d.k2_start = a.k2_start; d.k1_len = a.k1_len;
     d.H = a.H; d.Hkv = a.Hkv; d.hd = a.hd;
     d.causal = a.causal; d.causal_off = a.causal_off; d.window = a.window;

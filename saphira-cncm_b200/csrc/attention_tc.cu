@@ -21,6 +21,7 @@
 //   R2  odd key blocks,  K hi | K lo     then  P hi/lo, two buffers
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "split.cuh"
 
 namespace ncmb {
 
@@ -30,7 +31,7 @@ constexpr int ATC_VSLOTS = 8;
 constexpr int ATC_SMEM = 1024 + 3 * 65536 + 256 * 4 + 32 * 8 + 64;
 
 struct AttnTcDev {
-    float *out; float *out_lo; int64_t ldo;
+    float *out; float *out_lo; int64_t ldo; int out_fmt;
     const int *q_start, *k1_start, *k2_start, *k1_len;
     int H, Hkv, causal, causal_off, window;
     int pack;        // 1: the tile holds the (<= 32) queries of all H/Hkv (<= 4) heads that share one kv head, 32 rows per head
@@ -321,12 +322,8 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
                 float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
                                         __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
                 if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.out_lo) {
-                    float4 h4 = make_float4(atc_hi(o4.x), atc_hi(o4.y), atc_hi(o4.z), atc_hi(o4.w));
-                    *(float4 *)(a.out_lo + ofs + j) = make_float4(o4.x - h4.x, o4.y - h4.y, o4.z - h4.z, o4.w - h4.w);
-                    o4 = h4;
-                }
-                *(float4 *)(a.out + ofs + j) = o4;
+                if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
+                else *(float4 *)(a.out + ofs + j) = o4;
             }
         }
     }
@@ -357,7 +354,7 @@ bool attention_tc_supported(const AttnArgs &a) {
 
 void attention_tc(const AttnArgs &a) {
     AttnTcDev d;
-    d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo;
+    d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo; d.out_fmt = a.out_fmt;
     d.q_start = a.q_start; d.k1_start = a.k1_start; d.k2_start = a.k2 ? a.k2_start : nullptr; d.k1_len = a.k1_len;
     d.H = a.H; d.Hkv = a.Hkv; d.causal = a.causal; d.causal_off = a.causal_off; d.window = a.window;
     d.scale = 1.0f / sqrtf(64.0f);

@@ -22,7 +22,7 @@ namespace ncmb {
 struct Ctx {
     cudaStream_t stream = 0;
     long long launches = 0;
-    int gemm_mode = 2;
+    int gemm_mode = 3;                  // 0 fp32 CUDA cores | 1 TF32 | 2 3xTF32 | 3 fp16 pairs, three fp16 MMAs (default)
     int rng_mode = 0;
     long long row_offset = 0;
     int sm_count = 148;
@@ -72,6 +72,12 @@ struct Workspace {
 // ---- activation codes for fused epilogues ----
 enum Act { ACT_NONE = 0, ACT_GELU = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU2 = 4 };
 
+// Format of a GEMM input that its producer already wrote as a split pair (x, x_lo):
+//   SPLIT_TF32: float arrays, x = rn_tf32(v), x_lo = v - x
+//   SPLIT_H16:  both buffers read as __half arrays with the same element stride,
+//               x = rn_f16(v), x_lo = rn_f16((v - x) * 2^11)
+enum SplitFmt { SPLIT_NONE = 0, SPLIT_TF32 = 1, SPLIT_H16 = 2 };
+
 // y[M,N] = act(x[M,K] W[N,K]^T + bias[N]) (+ res[M,N]); res may alias y. ldx/ldy: row strides.
 struct GemmArgs {
     const float *x = nullptr; int64_t ldx = 0;
@@ -89,6 +95,7 @@ struct GemmArgs {
     // and the result may be written split (y = hi, y_lo = lo, same stride) for the next GEMM to consume.
     const float *x_lo = nullptr;
     float *y_lo = nullptr;
+    int x_fmt = SPLIT_TF32, y_fmt = SPLIT_TF32;   // formats of (x, x_lo) and (y, y_lo) when the lo pointer is set
     // nearest-row search instead of a stored product (tensor-core engine only): for every x row, the
     // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
     const float *argmin_colnorm = nullptr;
@@ -98,15 +105,19 @@ void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and sh
 void gemm_simt(const GemmArgs &a);
 bool gemm_tc_supported(const GemmArgs &a);
 void gemm_tc(const GemmArgs &a);
+// gemm mode 3: fp16 split pairs, three kind::f16 MMAs per k-step into two accumulators (gemm_h3.cu)
+bool gemm_h3_supported(const GemmArgs &a);
+void gemm_h3(const GemmArgs &a);
+void gemm_h3_forget_weights();
 void gemm_tc_forget_weights();
 struct StaticWeights { StaticWeights() { ctx().w_static++; } ~StaticWeights() { ctx().w_static--; } };
 int gemm_tc_check();                    // reads + clears the tensor-core engine's timeout word
 
 // ---- normalisation / elementwise (kernels_elem.cu) ----
 void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps);
-// y_lo != null: the result is written as a TF32 hi / lo pair (y = hi, y_lo = value - hi)
-void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps);
-void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C);
+// y_lo != null: the result is written as a split pair in format fmt (SplitFmt)
+void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps, int fmt);
+void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C, int fmt);
 float *dev_interleave_rows(const float *a, const float *b, int64_t rows, int64_t cols);   // new [2*rows][cols]: a0,b0,a1,b1,...
 void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy);
 void add_inplace(float *y, const float *x, int64_t n);
@@ -140,7 +151,8 @@ struct AttnArgs {
     const float *k1, *v1; int64_t ldk1;          // [token][kvh*hd + d]
     const float *k2 = nullptr, *v2 = nullptr; int64_t ldk2 = 0;
     float *out; int64_t ldo;                     // out[token][h*hd + d]
-    float *out_lo = nullptr;                     // optional: write the context as a TF32 hi / lo pair
+    float *out_lo = nullptr;                     // optional: write the context as a split pair ...
+    int out_fmt = SPLIT_TF32;                    // ... in this format
     const int *q_start, *k1_start, *k2_start = nullptr;   // device int[rows+1]
     const int *k1_len = nullptr;                 // optional device int[rows]: segment-1 lengths (strided caches)
     int rows, H, Hkv, hd;
@@ -215,7 +227,7 @@ struct AttnPlan {
 };
 void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights &w, const BlockBufs &b, const AttnPlan &p);
 void apply_norm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, int kind, float eps);
-void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps);
+void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps, int fmt);
 void make_gated_interleaved(BlockWeights &w, int C, std::vector<void *> &owned);   // fills fcw_il / fcb_il from fcw / fcb
 
 // weight lookup helpers

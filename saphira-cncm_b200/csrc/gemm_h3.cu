@@ -1,0 +1,263 @@
+// fp32-grade GEMM on the fp16 tensor path of sm_100a: y = act(x W^T + bias) (+ res).
+//
+// Both operands are carried as pairs of fp16 arrays,
+//     v = v1 + v2 * 2^-11,   v1 = rn_f16(v),   v2 = rn_f16((v - v1) * 2^11)
+// (22 significant bits; scaling the remainder keeps it in the normal fp16 range). The product is
+//     x W^T = x1 W1^T  +  2^-11 (x2 W1^T + x1 W2^T)        (the 2^-22 term is dropped)
+// so every k-step issues three tcgen05.mma.kind::f16 into TWO fp32 accumulators in tensor memory
+// (main, cross terms); the epilogue combines them as main + cross * 2^-11. Against three TF32
+// passes this moves half the operand bytes and runs on the twice-as-fast fp16 pipe.
+//
+// Structure: persistent CTAs (one per SM) walking output tiles of 128 x 128; warp 0 feeds a ring
+// of shared-memory stages by TMA (four 128 x 64 fp16 tiles per stage, 128-byte swizzle), one lane of
+// warp 1 issues the MMAs, warps 2-5 run the fused epilogue out of tensor memory. Accumulator
+// pairs alternate between two halves of tensor memory so a tile's epilogue overlaps the next
+// tile's MMAs. Every mbarrier wait is bounded; a timeout records a code and drains.
+#include "common.cuh"
+#include "tc_common.cuh"
+#include "tc_epilogue.cuh"
+
+#include <unordered_map>
+
+namespace ncmb {
+
+constexpr int H3_BM = 128, H3_BN = 128, H3_BK = 64;      // BK halfs = 128 bytes = one swizzle row
+constexpr int H3_STAGES = 3;
+constexpr int H3_THREADS = 192;
+constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand tile: 16 KB
+constexpr int H3_STAGE = 4 * H3_TILE;                    // x1 | x2 | W1 | W2
+
+// instruction descriptor: D fp32, A/B fp16, both K-major, M x N tile
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+__global__ void __launch_bounds__(H3_THREADS) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
+                                                       const __grid_constant__ CUtensorMap tmX2,
+                                                       const __grid_constant__ CUtensorMap tmW1,
+                                                       const __grid_constant__ CUtensorMap tmW2,
+                                                       TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+    uint64_t *bars = (uint64_t *)(smem + H3_STAGES * H3_STAGE);
+    uint32_t *tmem_slot = (uint32_t *)(bars + 2 * H3_STAGES + 4);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + H3_STAGES);
+    const uint32_t afull0 = smem_u32(bars + 2 * H3_STAGES), aempty0 = smem_u32(bars + 2 * H3_STAGES + 2);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < H3_STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(afull0 + 8 * a, 1); mbar_init(aempty0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX2) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW2) : "memory");
+    }
+    if (warp == 1) {   // 2 accumulator pairs x (main, cross) x 128 columns = all 512 columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int kbg = 0, armed = 0;                       // k-block counter over all of this CTA's tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int n0 = (t % tiles_n) * H3_BN, m0 = (t / tiles_n) * H3_BM;
+                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                    int s = kbg % H3_STAGES; uint32_t ph = (uint32_t)(kbg / H3_STAGES) & 1u;
+                    ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 21);
+                    if (!ok) break;
+                    const uint32_t dst = smem_u32(smem + s * H3_STAGE), bar = full0 + 8 * s;
+                    mbar_expect_tx(bar, H3_STAGE);
+                    tma_load_2d(dst, &tmX1, kb * H3_BK, m0, bar);
+                    tma_load_2d(dst + H3_TILE, &tmX2, kb * H3_BK, m0, bar);
+                    tma_load_2d(dst + 2 * H3_TILE, &tmW1, kb * H3_BK, n0, bar);
+                    tma_load_2d(dst + 3 * H3_TILE, &tmW2, kb * H3_BK, n0, bar);
+                    armed = kbg + 1;
+                }
+            }
+            if (!ok) {   // drain: wait (bounded) for the copies already in flight before leaving
+                int first = armed - H3_STAGES < 0 ? 0 : armed - H3_STAGES;
+                for (int k = first; k < armed; k++) mbar_wait(full0 + 8 * (k % H3_STAGES), (uint32_t)(k / H3_STAGES) & 1u, ep.err, 24);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(H3_BM, H3_BN);
+            int kbg = 0, it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+                const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
+                ok = mbar_wait(aempty0 + 8 * acc, (use & 1u) ^ 1u, ep.err, 25);    // epilogue has drained this accumulator pair
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmain = tmem_base + (uint32_t)(acc * 2 * H3_BN), tcross = tmain + (uint32_t)H3_BN;
+                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                    int s = kbg % H3_STAGES; uint32_t ph = (uint32_t)(kbg / H3_STAGES) & 1u;
+                    ok = mbar_wait(full0 + 8 * s, ph, ep.err, 22);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t base = smem_u32(smem + s * H3_STAGE);
+                    const uint64_t x1 = umma_desc_sw128(base), x2 = umma_desc_sw128(base + H3_TILE);
+                    const uint64_t w1 = umma_desc_sw128(base + 2 * H3_TILE), w2 = umma_desc_sw128(base + 3 * H3_TILE);
+#pragma unroll
+                    for (int k = 0; k < H3_BK / 16; k++) {    // 16 halfs (32 bytes) per MMA: advance the start address
+                        const uint64_t o = (uint64_t)(k * 2);
+                        umma_f16(tmain, x1 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
+                        umma_f16(tcross, x2 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
+                        umma_f16(tcross, x1 + o, w2 + o, idesc, 1u);
+                    }
+                    umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
+                }
+                umma_commit(afull0 + 8 * acc);               // accumulators complete (also reached on the error path)
+            }
+        }
+    } else {
+        const int q = warp & 3;                              // TMEM lane quadrant this warp may read
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+            const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
+            const int n0 = (t % tiles_n) * H3_BN;
+            const int64_t m = (int64_t)(t / tiles_n) * H3_BM + q * 32 + lane;
+            ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 23);
+            tc_fence_after();
+            if (!ok) break;
+            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < H3_BN; c0 += 32) {
+                uint32_t r[32], c[32];
+                tmem_ld32(trow + (uint32_t)c0, r);
+                tmem_ld32(trow + (uint32_t)(H3_BN + c0), c);
+#pragma unroll
+                for (int j = 0; j < 32; j++)
+                    r[j] = __float_as_uint(fmaf(__uint_as_float(c[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
+                tc_epilogue_chunk(ep, r, m, n0, c0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(aempty0 + 8 * acc);   // 4 arrivals (one per epilogue warp) free the pair
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+// fp32 [rows][K] (row stride ldx) -> the fp16 pair, dense [rows][K] each
+__global__ void k_split_h16(const float *__restrict__ x, int64_t ldx, unsigned short *__restrict__ v1,
+                            unsigned short *__restrict__ v2, int64_t rows, int K4) {
+    int64_t total = rows * K4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i / K4; int c = (int)(i % K4);
+        float4 v = *(const float4 *)(x + r * ldx + c * 4);
+        store_split4((float *)v1, (float *)v2, i * 4, v, SPLIT_H16);
+    }
+}
+static void split_h16(const float *x, int64_t ldx, void *v1, void *v2, int64_t rows, int K) {
+    int64_t n = rows * (K / 4);
+    int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+    ProfScope ps(NCMB_K_ELEM, 0, (double)rows * K * 8);
+    LAUNCH(k_split_h16, (unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 256, 0, x, ldx, (unsigned short *)v1,
+           (unsigned short *)v2, rows, K / 4);
+}
+
+struct ShadowH { unsigned short *v1, *v2; int64_t n; };
+static std::unordered_map<const float *, ShadowH> &shadow_h() { static std::unordered_map<const float *, ShadowH> c; return c; }
+static Workspace &split_ws_h() { static Workspace w; return w; }
+
+// Drops the cached fp16 pairs of weights (call when weight memory is freed or rewritten).
+void gemm_h3_forget_weights() {
+    for (auto &kv : shadow_h()) dev_free(kv.second.v1);
+    shadow_h().clear();
+}
+
+static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
+
+bool gemm_h3_supported(const GemmArgs &a) {
+    int64_t ldx = a.ldx ? a.ldx : a.K, ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    if (a.argmin_best) return false;                                // nearest-row search stays on the TF32 kernel
+    if (a.M < 64 || a.N < 32 || a.K < 32) return false;            // skinny shapes stay on CUDA cores (weight streaming)
+    if ((a.K & 7) || (ldx & 7)) return false;                       // fp16 rows: TMA strides are multiples of 16 bytes
+    if (a.x_lo && a.x_fmt != SPLIT_H16) return false;
+    if (!al16(a.x) || (a.x_lo && !al16(a.x_lo)) || !al16(a.W) || !al16(a.y) || (a.y_lo && !al16(a.y_lo)) ||
+        (a.bias && !al16(a.bias)) || (a.res && !al16(a.res))) return false;
+    if (a.glu && ((a.N & 1) || (ldy & 1))) return false;
+    if (a.y_lo && a.y_fmt == SPLIT_H16 && (ldy & 7)) return false;
+    return true;
+}
+
+void gemm_h3(const GemmArgs &a) {
+    if (a.M <= 0 || a.N <= 0) return;
+    TcEpi ep;
+    ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
+    ep.y = a.y; ep.y_lo = a.y_lo; ep.y_fmt = a.y_fmt; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
+    ep.colnorm = nullptr; ep.best = nullptr;
+    const int64_t ldx = a.ldx ? a.ldx : a.K;
+    const bool pre_split = a.x_lo != nullptr;
+    const int64_t nx = pre_split ? 0 : a.M * a.K, nw = (int64_t)a.N * a.K;
+    Workspace &ws = split_ws_h();
+    const bool cache_w = ctx().w_static != 0;
+    size_t need = (size_t)(2 * nx + (cache_w ? 0 : 2 * nw)) * 2 + 4096;
+    if (need > ws.cap) ws.reserve(need + need / 4);
+    ws.reset();
+    const void *x1 = a.x, *x2 = a.x_lo;
+    int64_t ldh = ldx;
+    if (!pre_split) {
+        unsigned short *p1 = ws.get<unsigned short>(nx), *p2 = ws.get<unsigned short>(nx);
+        split_h16(a.x, ldx, p1, p2, a.M, a.K);
+        x1 = p1; x2 = p2; ldh = a.K;
+    }
+    const unsigned short *w1, *w2;
+    if (cache_w) {
+        auto &sc = shadow_h();
+        auto it = sc.find(a.W);
+        if (it == sc.end() || it->second.n != nw) {
+            if (it != sc.end()) dev_free(it->second.v1);
+            unsigned short *buf = (unsigned short *)dev_alloc((size_t)2 * nw * 2);
+            split_h16(a.W, a.K, buf, buf + nw, a.N, a.K);
+            it = sc.insert_or_assign(a.W, ShadowH{buf, buf + nw, nw}).first;
+        }
+        w1 = it->second.v1; w2 = it->second.v2;
+    } else {
+        unsigned short *p1 = ws.get<unsigned short>(nw), *p2 = ws.get<unsigned short>(nw);
+        split_h16(a.W, a.K, p1, p2, a.N, a.K);
+        w1 = p1; w2 = p2;
+    }
+    const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
+    const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, H3_BN), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, H3_BN);
+    constexpr size_t smem = 1024 + (size_t)H3_STAGES * H3_STAGE + (2 * H3_STAGES + 4) * 8 + 16;
+    static bool set = false;
+    if (!set) {
+        CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        set = true;
+    }
+    int tiles_n = (int)cdiv(a.N, H3_BN);
+    int64_t tiles = (int64_t)tiles_n * cdiv(a.M, H3_BM);
+    if (tiles > 0x7fffffff) fatal("gemm_h3: too many tiles");
+    int grid = (int)(tiles < ctx().sm_count ? tiles : ctx().sm_count);     // persistent: one CTA per SM
+    int num_kb = (int)cdiv(a.K, H3_BK);
+    ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
+                 4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
+    LAUNCH(k_gemm_h3, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, ep, num_kb, tiles_n, (int)tiles);
+}
+
+} // namespace ncmb

@@ -238,7 +238,14 @@ void gemm_simt(const GemmArgs &g) {
 }
 
 void gemm(const GemmArgs &a) {
-    if (ctx().gemm_mode >= 1 && gemm_tc_supported(a)) { gemm_tc(a); return; }
+    const int mode = ctx().gemm_mode;
+    // a pre-split input names its engine; otherwise mode 3 prefers the fp16-pair kernel
+    if (a.x_lo && a.x_fmt == SPLIT_H16) {
+        if (!gemm_h3_supported(a)) fatal("gemm: fp16-pair operands for a shape the fp16-pair kernel does not take (M=%lld N=%d K=%d)", (long long)a.M, a.N, a.K);
+        gemm_h3(a); return;
+    }
+    if (mode >= 3 && !a.x_lo && gemm_h3_supported(a)) { gemm_h3(a); return; }
+    if (mode >= 1 && gemm_tc_supported(a)) { gemm_tc(a); return; }
     if (a.x_lo || a.y_lo) fatal("gemm: split operands reached the CUDA-core engine (M=%lld N=%d K=%d)", (long long)a.M, a.N, a.K);
     gemm_simt(a);
 }

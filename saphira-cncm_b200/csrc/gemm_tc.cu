@@ -14,6 +14,7 @@
 // timeout the kernel records an error code and drains instead of spinning.
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "tc_epilogue.cuh"
 
 #include <unordered_map>
 
@@ -21,102 +22,6 @@ namespace ncmb {
 
 constexpr int TC_BM = 128;
 constexpr int TC_THREADS = 192;
-
-struct TcEpi {
-    const float *bias; const float *res; int64_t ldres;
-    float *y; float *y_lo; int64_t ldy;
-    int64_t M; int N; int act; int glu;
-    const float *colnorm; unsigned long long *best;     // nearest-row mode
-    int *err;
-};
-
-
-__device__ __forceinline__ float tc_act(float v, int act) {
-    switch (act) {
-        case ACT_GELU: return 0.5f * v * (1.0f + erff(v * 0.7071067811865475f));
-        case ACT_GELU_TANH: return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-        case ACT_SILU: return v / (1.0f + expf(-v));
-        case ACT_RELU2: { float r = v > 0.f ? v : 0.f; return r * r; }
-        default: return v;
-    }
-}
-
-// Fused epilogue for one 32-column chunk of an accumulator row held in registers.
-__device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_t *r, int64_t m, int n0, int c0) {
-    if (m >= ep.M || n0 + c0 >= ep.N) return;
-    if (ep.glu) {
-        // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
-        float *yr = ep.y + m * ep.ldy + ((n0 + c0) >> 1);
-        float *lr = ep.y_lo ? ep.y_lo + m * ep.ldy + ((n0 + c0) >> 1) : nullptr;
-        const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0);
-#pragma unroll
-        for (int j = 0; j < 16; j += 4) {
-            float o[4];
-#pragma unroll
-            for (int e = 0; e < 4; e++) {
-                int n = n0 + c0 + 2 * (j + e);
-                float g = __uint_as_float(r[2 * (j + e)]), u = __uint_as_float(r[2 * (j + e) + 1]);
-                if (ep.bias && n + 1 < ep.N) { g += ep.bias[n]; u += ep.bias[n + 1]; }
-                o[e] = __fmul_rn(tc_act(g, ep.act), u);
-            }
-            if (full) {
-                float4 v = make_float4(o[0], o[1], o[2], o[3]);
-                if (lr) {
-                    float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
-                    *(float4 *)(lr + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
-                    v = h4;
-                }
-                *(float4 *)(yr + j) = v;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    int n = n0 + c0 + 2 * (j + e);
-                    if (n + 1 < ep.N) {
-                        float v = o[e];
-                        if (lr) { float hi = tc_tf32_hi(v); lr[j + e] = v - hi; v = hi; }
-                        yr[j + e] = v;
-                    }
-                }
-            }
-        }
-        return;
-    }
-    float *yr = ep.y + m * ep.ldy + n0 + c0;
-    const float *rr = ep.res ? ep.res + m * ep.ldres + n0 + c0 : nullptr;
-    const bool full = (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0) && (!rr || (ep.ldres & 3) == 0);
-    if (full) {
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            if (ep.bias) {
-                float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-            }
-            v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
-            if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
-            if (ep.y_lo) {
-                float4 h4 = make_float4(tc_tf32_hi(v.x), tc_tf32_hi(v.y), tc_tf32_hi(v.z), tc_tf32_hi(v.w));
-                *(float4 *)(ep.y_lo + m * ep.ldy + n0 + c0 + j) = make_float4(v.x - h4.x, v.y - h4.y, v.z - h4.z, v.w - h4.w);
-                v = h4;
-            }
-            *(float4 *)(yr + j) = v;
-        }
-    } else {
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-            int n = n0 + c0 + j;
-            if (n < ep.N) {
-                float v = __uint_as_float(r[j]);
-                if (ep.bias) v += ep.bias[n];
-                v = tc_act(v, ep.act);
-                if (rr) v += rr[j];
-                if (ep.y_lo) { float hi = tc_tf32_hi(v); ep.y_lo[m * ep.ldy + n] = v - hi; v = hi; }
-                yr[j] = v;
-            }
-        }
-    }
-}
-
 
 // Persistent kernel: each CTA walks output tiles t = blockIdx.x, blockIdx.x + gridDim.x, ...
 // (n-tile fastest, so CTAs running side by side share the same rows of x in L2). The
@@ -329,6 +234,25 @@ const CUtensorMap *tc_get_map(const float *p, int64_t rows, int K, int64_t ld, i
     return &cache.emplace(key, tm).first->second;
 }
 
+// 2-D map over a row-major [rows][K] fp16 matrix with row stride ld (elements): box = 64 halfs x box_rows
+const CUtensorMap *tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld, int box_rows) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{p, rows, ld, K, box_rows, 2};
+    auto it = cache.find(key);
+    if (it != cache.end()) return &it->second;
+    if (cache.size() > 4096) cache.clear();
+    CUtensorMap tm;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)p, dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) fatal("cuTensorMapEncodeTiled (fp16) failed (%d) for [%lld][%d] ld %lld", (int)r, (long long)rows, K, (long long)ld);
+    return &cache.emplace(key, tm).first->second;
+}
+
 int *tc_err_flag() {
     static int *d = nullptr;
     if (!d) { d = (int *)dev_alloc(sizeof(int)); CUDA_CHECK(cudaMemsetAsync(d, 0, sizeof(int), stream())); }
@@ -412,7 +336,7 @@ void gemm_tc(const GemmArgs &a) {
     if (a.M <= 0 || a.N <= 0) return;
     TcEpi ep;
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
-    ep.y = a.y; ep.y_lo = a.y_lo; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
+    ep.y = a.y; ep.y_lo = a.y_lo; ep.y_fmt = a.y_fmt; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
     ep.colnorm = a.argmin_colnorm; ep.best = a.argmin_best;
     int64_t ldx = a.ldx ? a.ldx : a.K;
@@ -456,10 +380,16 @@ void gemm_tc(const GemmArgs &a) {
     }
     if (!pre_split) split_tf32(a.x, ldx, (float *)xhi, (float *)xlo, a.M, a.K);
     const CUtensorMap *ma = tc_get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), *mal = tc_get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
-    const CUtensorMap *mb = tc_get_map(whi, a.N, a.K, a.K, 128, false), *mbl = tc_get_map(wlo, a.N, a.K, a.K, 128, true);
+    // 256-wide N tiles read a third less of the operands per MMA flop (from L2 and from shared memory);
+    // they are used once the launch still fills every SM a few times over
+    static const bool wide_ok = !getenv("NCM_B200_NO_BN256");
+    const bool wide = wide_ok && a.N >= 256 && cdiv(a.N, 256) * cdiv(a.M, TC_BM) >= 2 * (int64_t)ctx().sm_count;
+    const int bn = wide ? 256 : 128;
+    const CUtensorMap *mb = tc_get_map(whi, a.N, a.K, a.K, bn, false), *mbl = tc_get_map(wlo, a.N, a.K, a.K, bn, true);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * (2.0 * (double)a.M * a.K + 2.0 * (double)a.N * a.K + (double)a.M * a.N));
-    launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);
+    if (wide) launch_tc<256, 2, true>(a, ep, ma, mb, mal, mbl);
+    else launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);
 }
 
 
@@ -547,7 +477,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
     encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
     TcEpi ep;
-    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
+    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.y_fmt = SPLIT_TF32; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
     return 0;

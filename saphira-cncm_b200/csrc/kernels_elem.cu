@@ -3,6 +3,7 @@
 // C entry points of the reference's kernel API that map onto them
 // (src/ncm.h:148-158, 163-165, 184-190).
 #include "common.cuh"
+#include "split.cuh"
 
 namespace ncmb {
 
@@ -34,7 +35,7 @@ __device__ __forceinline__ float tf32_hi(float v) {
 template <bool VEC4>
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ w,
                                                   const float *__restrict__ b, float *__restrict__ y,
-                                                  float *__restrict__ ylo, int64_t rows, int C, float eps) {
+                                                  float *__restrict__ ylo, int64_t rows, int C, float eps, int fmt) {
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -70,40 +71,36 @@ __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, 
             o.y = __fadd_rn(__fmul_rn(__fmul_rn(v.y - mean, inv), ww.y), bb.y);
             o.z = __fadd_rn(__fmul_rn(__fmul_rn(v.z - mean, inv), ww.z), bb.z);
             o.w = __fadd_rn(__fmul_rn(__fmul_rn(v.w - mean, inv), ww.w), bb.w);
-            if (lr) {
-                float4 h = make_float4(tf32_hi(o.x), tf32_hi(o.y), tf32_hi(o.z), tf32_hi(o.w));
-                *(float4 *)(lr + c) = make_float4(o.x - h.x, o.y - h.y, o.z - h.z, o.w - h.w);
-                o = h;
-            }
-            *(float4 *)(yr + c) = o;
+            if (lr) store_split4(y, ylo, row * C + c, o, fmt);
+            else *(float4 *)(yr + c) = o;
         }
     } else {
         for (int c = lane; c < C; c += 32) {
             float o = __fadd_rn(__fmul_rn(__fmul_rn(xr[c] - mean, inv), w ? w[c] : 1.f), b ? b[c] : 0.f);
-            if (lr) { float h = tf32_hi(o); lr[c] = o - h; o = h; }
-            yr[c] = o;
+            if (lr) store_split1(y, ylo, row * C + c, o, fmt);
+            else yr[c] = o;
         }
     }
 }
 
 static inline bool aligned16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
-void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps) {
+void layernorm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, float eps, int fmt) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * (y_lo ? 12 : 8));
     bool v4 = (C % 4 == 0) && aligned16(x) && aligned16(y) && (!y_lo || aligned16(y_lo)) && (!w || aligned16(w)) && (!b || aligned16(b));
     unsigned g = grid1d(rows, 8);
-    if (v4) LAUNCH(k_layernorm<true>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps);
-    else LAUNCH(k_layernorm<false>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps);
+    if (v4) LAUNCH(k_layernorm<true>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
+    else LAUNCH(k_layernorm<false>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
 }
 void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps) {
-    layernorm_split(x, w, b, y, nullptr, rows, C, eps);
+    layernorm_split(x, w, b, y, nullptr, rows, C, eps, SPLIT_NONE);
 }
 
 // ---- RMSNorm: y = x * rsqrt(mean(x^2) + 1e-6) * w ----
 __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ w,
                                                 float *__restrict__ y, float *__restrict__ ylo, int64_t rows, int C,
-                                                int64_t ldx, int64_t ldy) {
+                                                int64_t ldx, int64_t ldy, int fmt) {
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -116,20 +113,20 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, co
     float *lr = ylo ? ylo + row * ldy : nullptr;
     for (int c = lane; c < C; c += 32) {
         float o = __fmul_rn(__fmul_rn(xr[c], r), w ? w[c] : 1.f);
-        if (lr) { float h = tf32_hi(o); lr[c] = o - h; o = h; }
-        yr[c] = o;
+        if (lr) store_split1(y, ylo, row * ldy + c, o, fmt);
+        else yr[c] = o;
     }
 }
 
 void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 8);
-    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, (float *)nullptr, rows, C, ldx, ldy);
+    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, (float *)nullptr, rows, C, ldx, ldy, (int)SPLIT_NONE);
 }
-void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C) {
+void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C, int fmt) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 12);
-    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, y_lo, rows, C, (int64_t)C, (int64_t)C);
+    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, y_lo, rows, C, (int64_t)C, (int64_t)C, fmt);
 }
 
 // ---- element-wise ----

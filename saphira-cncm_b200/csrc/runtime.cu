@@ -301,7 +301,8 @@ int weights_load(WeightStore *ws, const char *path) {
 
 void weights_free(WeightStore *ws) {
     if (!ws || !ws->items) return;
-    gemm_tc_forget_weights();        // cached hi/lo splits point at memory that is about to go away
+    gemm_tc_forget_weights();
+    gemm_h3_forget_weights();        // cached hi/lo splits point at memory that is about to go away
     cudaStreamSynchronize(stream());
     auto it = slab_of_store().find(ws->items);
     for (int i = 0; i < ws->count; i++) {

@@ -10,9 +10,9 @@
 
 namespace ncmb {
 
-void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps) {
-    if (kind == NORM_RMS) { if (y_lo) rmsnorm_split(x, w, y, y_lo, rows, C); else rmsnorm(x, w, y, rows, C, C, C); }
-    else layernorm_split(x, w, b, y, y_lo, rows, C, eps);
+void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps, int fmt) {
+    if (kind == NORM_RMS) { if (y_lo) rmsnorm_split(x, w, y, y_lo, rows, C, fmt); else rmsnorm(x, w, y, rows, C, C, C); }
+    else layernorm_split(x, w, b, y, y_lo, rows, C, eps, fmt);
 }
 
 void make_gated_interleaved(BlockWeights &w, int C, std::vector<void *> &owned) {
@@ -57,6 +57,10 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     probe.x = b.ln; probe.ldx = C; probe.W = w.qkvw; probe.y = b.qkv; probe.ldy = Wq; probe.M = ntok; probe.N = Wq; probe.K = C;
     static const bool fuse_split = !getenv("NCM_B200_NO_SPLIT_FUSE");
     bool split = fuse_split && ctx().gemm_mode >= 2 && gemm_tc_supported(probe) && (C % 4 == 0) && (w.Hh % 4 == 0) && C >= 32 && w.Hh >= 32;
+    // mode 3: fp16 pairs for the fp16-pair kernel (rows of C and Hh halfs must keep 16-byte strides)
+    int fmt = split ? SPLIT_TF32 : SPLIT_NONE;
+    if (split && ctx().gemm_mode >= 3 && gemm_h3_supported(probe) && (C % 8 == 0) && (w.Hh % 8 == 0)) fmt = SPLIT_H16;
+    auto tc_ok = [&](const GemmArgs &q) { return fmt == SPLIT_H16 ? gemm_h3_supported(q) : (ctx().gemm_mode >= 1 && gemm_tc_supported(q)); };
     float *ln_lo = nullptr, *ctx_lo = nullptr, *h_lo = nullptr;
     if (split) {
         Workspace &lw = block_lo_ws();
@@ -65,8 +69,9 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         lw.reset();
         ln_lo = lw.get<float>((size_t)ntok * C); ctx_lo = lw.get<float>((size_t)ntok * C); h_lo = lw.get<float>((size_t)ntok * w.Hh);
     }
-    apply_norm_split(x, w.ln1w, w.ln1b, b.ln, ln_lo, ntok, C, w.norm, w.eps);
+    apply_norm_split(x, w.ln1w, w.ln1b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
     GemmArgs g;
+    g.x_fmt = fmt;
     g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.W = w.qkvw; g.bias = w.qkvb; g.y = b.qkv; g.ldy = Wq; g.M = ntok; g.N = Wq; g.K = C;
     gemm(g);
     float *qp = b.qkv, *kp = b.qkv + C, *vp = b.qkv + C + kvd;
@@ -86,7 +91,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     else { a.k1 = kp; a.v1 = vp; a.ldk1 = Wq; }
     a.k1_start = p.k1_start; a.k1_len = p.k1_len;
     if (p.self_is_k2) { a.k2 = kp; a.v2 = vp; a.ldk2 = Wq; a.k2_start = p.k2_start ? p.k2_start : p.q_start; }
-    a.out = b.ctx; a.out_lo = ctx_lo; a.ldo = C;
+    a.out = b.ctx; a.out_lo = ctx_lo; a.out_fmt = fmt; a.ldo = C;
     a.q_start = p.q_start;
     a.rows = p.rows; a.H = H; a.Hkv = nkv; a.hd = hd; a.max_q = p.max_q;
     a.causal = p.causal; a.causal_off = p.causal_off; a.window = p.window;
@@ -96,16 +101,18 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     attention(a);
     // x += ctx Wo^T + bo
     g = GemmArgs();
+    g.x_fmt = fmt;
     g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
     gemm(g);
-    apply_norm_split(x, w.ln2w, w.ln2b, b.ln, ln_lo, ntok, C, w.norm, w.eps);
+    apply_norm_split(x, w.ln2w, w.ln2b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
     g = GemmArgs();
+    g.x_fmt = fmt; g.y_fmt = fmt;
     g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.M = ntok; g.K = C;
     if (w.gated) {
         GemmArgs t = g;
         t.W = w.fcw_il; t.bias = w.fcb_il; t.N = 2 * w.Hh; t.glu = 1; t.act = w.act; t.y = b.h; t.ldy = w.Hh;
         static const bool fuse_glu = !getenv("NCM_B200_NO_GLU_FUSE");
-        if (fuse_glu && w.fcw_il && ctx().gemm_mode >= 1 && gemm_tc_supported(t)) {
+        if (fuse_glu && w.fcw_il && tc_ok(t)) {
             t.y_lo = h_lo;                       // gated product fused into the epilogue (interleaved gate/up rows)
             gemm(t);
         } else {
@@ -117,10 +124,11 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         }
     } else {
         g.W = w.fcw; g.bias = w.fcb; g.y = b.h; g.y_lo = h_lo; g.N = w.Hh; g.ldy = w.Hh; g.act = w.act;
-        if (!(ctx().gemm_mode >= 1 && gemm_tc_supported(g))) { g.y_lo = nullptr; h_lo = nullptr; }
+        if (!tc_ok(g)) { g.y_lo = nullptr; h_lo = nullptr; }
         gemm(g);
     }
     g = GemmArgs();
+    g.x_fmt = fmt;
     g.x = b.h; g.x_lo = h_lo; g.ldx = w.Hh; g.W = w.pw; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
     gemm(g);
 }

@@ -1,0 +1,48 @@
+"""linear_fwd (reference src/ncm.h:146, y = x W^T + b) on every GEMM engine of the library.
+
+Engines 0 (fp32 CUDA cores), 2 (three TF32 MMAs over hi/lo pairs) and 3 (three fp16 MMAs over
+scaled fp16 pairs into two accumulators) must all be fp32-grade against a float64 product;
+engine 1 (one TF32 pass) is the fast, coarse option and only has to be TF32-grade.
+"""
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+# (rows, out features, in features): full tiles, ragged tiles, K tails inside a TMA box,
+# K not a multiple of 8 (fp16 rows would break the 16-byte stride rule: engine 3 hands over to 2),
+# few rows (CUDA-core weight streaming)
+SHAPES = [(128, 128, 64), (256, 256, 512), (1000, 768, 520), (333, 200, 100), (2048, 1024, 2048), (8, 512, 512)]
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    import capi
+    lib = capi.NcmLib(helpers.CUDA_LIB)
+    yield lib
+    lib.ncmb_set_gemm_mode(3)
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_linear_fwd_on_every_engine(cuda, shape):
+    M, N, K = shape
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    # activations with a wide dynamic range: most entries O(1), some tiny, some in the hundreds
+    x = (rng.standard_normal((M, K)) * np.exp(rng.uniform(-9, 5, size=(M, 1)))).astype(np.float32)
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    want = x.astype(np.float64) @ W.astype(np.float64).T + b
+    # scale of one row's products: what an fp32 dot product of that row can resolve
+    row_scale = (np.abs(x).astype(np.float64) @ np.abs(W).astype(np.float64).T) + np.abs(b)
+    xd, Wd, bd = cuda.to_backend(x), cuda.to_backend(W), cuda.to_backend(b)
+    yd = cuda.alloc(M * N)
+    for mode, rel in ((0, 2e-6), (2, 4e-6), (3, 2e-6), (1, 2e-3)):
+        cuda.ncmb_set_gemm_mode(mode)
+        cuda.linear_fwd(xd, Wd, bd, yd, M, N, K)
+        cuda.ncmb_sync()
+        assert cuda.ncmb_gemm_tc_check() == 0
+        y = cuda.to_host(yd, (M, N))
+        err = np.abs(y - want) / row_scale
+        assert err.max() <= rel, f"engine {mode}: {err.max():.3e} of the row scale"

@@ -26,7 +26,7 @@ def cuda():
     if not os.path.exists(helpers.CUDA_LIB):
         pytest.fail("libncm_b200.so is not built: run python saphira-cncm_b200/build.py")
     lib = capi.NcmLib(helpers.CUDA_LIB)
-    lib.ncmb_set_gemm_mode(int(os.environ.get("NCM_TEST_GEMM", "2")))
+    lib.ncmb_set_gemm_mode(int(os.environ.get("NCM_TEST_GEMM", "3")))
     return lib
 
 
