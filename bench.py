@@ -317,6 +317,8 @@ def run_gpu_arm(args):
         t_wall = time.perf_counter() - t_wall0
     launches = lib.ncmb_launch_count() - n0
     lib.ncmb_prof_enable(0)
+    if os.environ.get("NCM_B200_PROF_SHAPES") and rank == 0:
+        lib.ncmb_prof_dump_shapes()          # per-call-shape table on stderr (diagnostic)
     prof = {}
     for name, k in (("gemm", 0), ("attention", 1), ("norm", 2), ("sampling", 3), ("elementwise", 4), ("quantizer", 5)):
         n, ms, fl, by = C.c_longlong(), C.c_double(), C.c_double(), C.c_double()

@@ -10,7 +10,7 @@
 //
 // Structure: persistent CTAs (one per SM) walking output tiles of 128 x 128; warp 0 feeds a ring
 // of shared-memory stages by TMA (four 128 x 64 fp16 tiles per stage, 128-byte swizzle), one lane of
-// warp 1 issues the MMAs, warps 2-5 run the fused epilogue out of tensor memory. Accumulator
+// warp 1 issues the MMAs, warps 2-9 run the fused epilogue out of tensor memory (64 columns each). Accumulator
 // pairs alternate between two halves of tensor memory so a tile's epilogue overlaps the next
 // tile's MMAs. Every mbarrier wait is bounded; a timeout records a code and drains.
 #include "common.cuh"
@@ -23,7 +23,8 @@ namespace ncmb {
 
 constexpr int H3_BM = 128, H3_BN = 128, H3_BK = 64;      // BK halfs = 128 bytes = one swizzle row
 constexpr int H3_STAGES = 3;
-constexpr int H3_THREADS = 192;
+constexpr int H3_EPI_WARPS = 8;                         // two per TMEM lane quadrant, 64 columns each
+constexpr int H3_THREADS = 64 + 32 * H3_EPI_WARPS;
 constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand tile: 16 KB
 constexpr int H3_STAGE = 4 * H3_TILE;                    // x1 | x2 | W1 | W2
 
@@ -37,7 +38,7 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
-__global__ void __launch_bounds__(H3_THREADS) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
+__global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
                                                        const __grid_constant__ CUtensorMap tmX2,
                                                        const __grid_constant__ CUtensorMap tmW1,
                                                        const __grid_constant__ CUtensorMap tmW2,
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(H3_THREADS) k_gemm_h3(const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < H3_STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(afull0 + 8 * a, 1); mbar_init(aempty0 + 8 * a, 4); }
+        for (int a = 0; a < 2; a++) { mbar_init(afull0 + 8 * a, 1); mbar_init(aempty0 + 8 * a, H3_EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX1) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmX2) : "memory");
@@ -126,29 +127,46 @@ __global__ void __launch_bounds__(H3_THREADS) k_gemm_h3(const __grid_constant__ 
         }
     } else {
         const int q = warp & 3;                              // TMEM lane quadrant this warp may read
+        const int ch = (warp - 2) >> 2;                      // which 64-column half of the tile this warp drains
         int it = 0;
         bool ok = true;
+        const bool glu_fast = tc_glu_silu_h16(ep);
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
             const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
-            const int n0 = (t % tiles_n) * H3_BN;
+            const int n0 = (t % tiles_n) * H3_BN + ch * 64;
             const int64_t m = (int64_t)(t / tiles_n) * H3_BM + q * 32 + lane;
+            // the residual of this thread's 64 outputs is requested before the accumulators are waited for,
+            // so its latency runs under the tile's MMAs
+            float4 resv[16];
+            bool pre[2];
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                pre[c] = tc_residual_prefetchable(ep, m, n0, c * 32);
+                if (pre[c]) {
+                    const float4 *rr = (const float4 *)(ep.res + m * ep.ldres + n0 + c * 32);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) resv[c * 8 + j] = rr[j];
+                }
+            }
             ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 23);
             tc_fence_after();
             if (!ok) break;
-            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN);
-#pragma unroll 1
-            for (int c0 = 0; c0 < H3_BN; c0 += 32) {
-                uint32_t r[32], c[32];
-                tmem_ld32(trow + (uint32_t)c0, r);
-                tmem_ld32(trow + (uint32_t)(H3_BN + c0), c);
+            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN + ch * 64);
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
+                uint32_t r[32], x[32];
+                tmem_ld32_issue(trow + (uint32_t)(c * 32), r);
+                tmem_ld32_issue(trow + (uint32_t)(H3_BN + c * 32), x);
+                tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; j++)
-                    r[j] = __float_as_uint(fmaf(__uint_as_float(c[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
-                tc_epilogue_chunk(ep, r, m, n0, c0);
+                    r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
+                if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
+                else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr);
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(aempty0 + 8 * acc);   // 4 arrivals (one per epilogue warp) free the pair
+            if (lane == 0) mbar_arrive(aempty0 + 8 * acc);   // one arrival per epilogue warp frees the pair
         }
     }
     tc_fence_before();

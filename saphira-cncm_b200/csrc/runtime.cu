@@ -4,6 +4,11 @@
 // tensor, and every copy goes through the library's stream.
 #include "common.cuh"
 
+#include <algorithm>
+#include <map>
+#include <string>
+#include <tuple>
+
 #include <stdarg.h>
 #include <string>
 #include <unordered_map>
@@ -58,6 +63,9 @@ struct Prof {
     ProfRec cur; bool in_scope = false; int depth = 0;
     long long launches[NCMB_K_COUNT] = {0};
     double ms[NCMB_K_COUNT] = {0}, flops[NCMB_K_COUNT] = {0}, bytes[NCMB_K_COUNT] = {0};
+    // NCM_B200_PROF_SHAPES=1: also keep one line per distinct (class, flops, bytes) scope, i.e. per call shape
+    std::map<std::tuple<int, double, double>, std::pair<long long, double>> shapes;
+    bool by_shape = getenv("NCM_B200_PROF_SHAPES") != nullptr;
     cudaEvent_t get() {
         if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
         cudaEvent_t e;
@@ -71,6 +79,7 @@ struct Prof {
             float t = 0;
             CUDA_CHECK(cudaEventElapsedTime(&t, r.a, r.b));
             ms[r.klass] += t; flops[r.klass] += r.flops; bytes[r.klass] += r.bytes; launches[r.klass]++;
+            if (by_shape) { auto &e = shapes[std::make_tuple(r.klass, r.flops, r.bytes)]; e.first++; e.second += t; }
             pool.push_back(r.a); pool.push_back(r.b);
         }
         open.clear();
@@ -467,6 +476,23 @@ void ncmb_prof_reset(void) {
     p.drain();
     for (int i = 0; i < NCMB_K_COUNT; i++) { p.launches[i] = 0; p.ms[i] = p.flops[i] = p.bytes[i] = 0; }
 }
+// prints the per-shape table (NCM_B200_PROF_SHAPES=1) to stderr, largest total first, and clears it
+void ncmb_prof_dump_shapes(void) {
+    Prof &p = prof();
+    p.drain();
+    std::vector<std::pair<double, std::string>> rows;
+    for (auto &kv : p.shapes) {
+        char buf[256];
+        double fl = std::get<1>(kv.first), by = std::get<2>(kv.first), ms = kv.second.second;
+        snprintf(buf, sizeof buf, "class %d  %6lld x %9.1f us = %9.2f ms  flops %.4g (%.1f TF/s)  bytes %.4g (%.0f GB/s)", std::get<0>(kv.first),
+                 kv.second.first, 1e3 * ms / kv.second.first, ms, fl, fl * kv.second.first / ms / 1e9, by, by * kv.second.first / ms / 1e6);
+        rows.emplace_back(-ms, buf);
+    }
+    std::sort(rows.begin(), rows.end());
+    for (auto &r : rows) fprintf(stderr, "%s\n", r.second.c_str());
+    p.shapes.clear();
+}
+
 int ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes) {
     if (klass < 0 || klass >= NCMB_K_COUNT) return -1;
     Prof &p = prof();

@@ -28,7 +28,13 @@ __device__ __forceinline__ float tc_act(float v, int act) {
 }
 
 // Fused epilogue for one 32-column chunk of an accumulator row held in registers.
-__device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_t *r, int64_t m, int n0, int c0) {
+// rp: the chunk's eight residual float4 already in registers (only honoured on the vector path, whose
+// conditions tc_residual_prefetchable() restates), or null to load them here.
+__device__ __forceinline__ bool tc_residual_prefetchable(const TcEpi &ep, int64_t m, int n0, int c0) {
+    return ep.res && !ep.glu && m < ep.M && (n0 + c0 + 32 <= ep.N) && ((ep.ldy & 3) == 0) && ((ep.ldres & 3) == 0);
+}
+__device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_t *r, int64_t m, int n0, int c0,
+                                                  const float4 *rp = nullptr) {
     if (m >= ep.M || n0 + c0 >= ep.N) return;
     if (ep.glu) {
         // interleaved gate/up columns: out[j] = act(acc[2j] + b[2j]) * (acc[2j+1] + b[2j+1])
@@ -73,8 +79,8 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_
                 float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
                 v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
             }
-            v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act);
-            if (rr) { float4 q4 = *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
+            if (ep.act != ACT_NONE) { v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act); }
+            if (rr) { float4 q4 = rp ? rp[j >> 2] : *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
             if (ep.y_lo) store_split4(ep.y, ep.y_lo, m * ep.ldy + n0 + c0 + j, v, ep.y_fmt);
             else *(float4 *)(yr + j) = v;
         }
@@ -95,5 +101,37 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcEpi &ep, const uint32_
 }
 
 
+
+// The gated MLP's up-projection in fp16-pair mode, specialised: 32 accumulator columns (interleaved
+// gate / up) become 16 outputs silu(gate) * up, each stored as an fp16 pair. SiLU goes through
+// ex2.approx / rcp.approx: its few-ulp error is below the 22 significant bits the pair keeps.
+// Ragged edges fall back to the generic chunk.
+__device__ __forceinline__ bool tc_glu_silu_h16(const TcEpi &ep) {
+    return ep.glu && ep.act == ACT_SILU && ep.y_lo && ep.y_fmt == SPLIT_H16 && (ep.ldy & 7) == 0;
+}
+__device__ __forceinline__ void tc_epilogue_glu_silu_h16(const TcEpi &ep, const uint32_t *r, int64_t m, int n0, int c0) {
+    if (m >= ep.M) return;
+    if (n0 + c0 + 32 > ep.N) { tc_epilogue_chunk(ep, r, m, n0, c0); return; }
+    uint32_t p1[8], p2[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {                       // two outputs (four accumulator columns) per step
+        float g0 = __uint_as_float(r[4 * j]), u0 = __uint_as_float(r[4 * j + 1]);
+        float g1 = __uint_as_float(r[4 * j + 2]), u1 = __uint_as_float(r[4 * j + 3]);
+        if (ep.bias) {
+            const float4 b = *(const float4 *)(ep.bias + n0 + c0 + 4 * j);
+            g0 += b.x; u0 += b.y; g1 += b.z; u1 += b.w;
+        }
+        const float o0 = __fmul_rn(__fdividef(g0, 1.0f + __expf(-g0)), u0);
+        const float o1 = __fmul_rn(__fdividef(g1, 1.0f + __expf(-g1)), u1);
+        unsigned short h0, l0, h1, l1;
+        h16_pair(o0, h0, l0); h16_pair(o1, h1, l1);
+        p1[j] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+        p2[j] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+    }
+    const int64_t e0 = m * ep.ldy + ((n0 + c0) >> 1);   // first output element; a multiple of 8 halfs (16 bytes)
+    uint4 *d1 = (uint4 *)((unsigned short *)ep.y + e0), *d2 = (uint4 *)((unsigned short *)ep.y_lo + e0);
+    d1[0] = make_uint4(p1[0], p1[1], p1[2], p1[3]); d1[1] = make_uint4(p1[4], p1[5], p1[6], p1[7]);
+    d2[0] = make_uint4(p2[0], p2[1], p2[2], p2[3]); d2[1] = make_uint4(p2[4], p2[5], p2[6], p2[7]);
+}
 
 } // namespace ncmb
