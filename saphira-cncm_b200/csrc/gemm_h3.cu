@@ -42,11 +42,13 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                                                        const __grid_constant__ CUtensorMap tmX2,
                                                        const __grid_constant__ CUtensorMap tmW1,
                                                        const __grid_constant__ CUtensorMap tmW2,
+                                                       const __grid_constant__ CUtensorMap tmY,
                                                        TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
-    uint64_t *bars = (uint64_t *)(smem + H3_STAGES * H3_STAGE);
+    unsigned char *stage0 = smem + H3_STAGES * H3_STAGE;         // one 4 KB store staging buffer per epilogue warp
+    uint64_t *bars = (uint64_t *)(stage0 + H3_EPI_WARPS * 4096);
     uint32_t *tmem_slot = (uint32_t *)(bars + 2 * H3_STAGES + 4);
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + H3_STAGES);
     const uint32_t afull0 = smem_u32(bars + 2 * H3_STAGES), aempty0 = smem_u32(bars + 2 * H3_STAGES + 2);
@@ -131,6 +133,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         int it = 0;
         bool ok = true;
         const bool glu_fast = tc_glu_silu_h16(ep);
+        unsigned char *stage = stage0 + (warp - 2) * 4096;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
             const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
             const int n0 = (t % tiles_n) * H3_BN + ch * 64;
@@ -162,12 +165,16 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 for (int j = 0; j < 32; j++)
                     r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
                 if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
+                else if (ep.tma_store && n0 + c * 32 + 32 <= ep.N)
+                    tc_epilogue_chunk_tma(ep, r, m, m - lane, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr, stage, &tmY, lane);
                 else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(aempty0 + 8 * acc);   // one arrival per epilogue warp frees the pair
         }
+        // result tiles still on their way out of the staging buffer must be written before the CTA retires
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -262,7 +269,11 @@ void gemm_h3(const GemmArgs &a) {
     }
     const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
     const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, H3_BN), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, H3_BN);
-    constexpr size_t smem = 1024 + (size_t)H3_STAGES * H3_STAGE + (2 * H3_STAGES + 4) * 8 + 16;
+    // fp32 results leave through TMA stores when the rows keep 16-byte strides
+    ep.tma_store = (!a.glu && !a.y_lo && (ep.ldy & 3) == 0 && !getenv("NCM_B200_NO_TMA_STORE")) ? 1 : 0;
+    const CUtensorMap *my = ep.tma_store ? tc_get_map(a.y, a.M, a.N, ep.ldy, 32, false) : mx1;
+    constexpr size_t smem = 1024 + (size_t)H3_STAGES * H3_STAGE + H3_EPI_WARPS * 4096 + (2 * H3_STAGES + 4) * 8 + 16;
+    static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");
     static bool set = false;
     if (!set) {
         CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -275,7 +286,7 @@ void gemm_h3(const GemmArgs &a) {
     int num_kb = (int)cdiv(a.K, H3_BK);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
-    LAUNCH(k_gemm_h3, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, ep, num_kb, tiles_n, (int)tiles);
+    LAUNCH(k_gemm_h3, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
 }
 
 } // namespace ncmb

@@ -338,7 +338,7 @@ void gemm_tc(const GemmArgs &a) {
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
     ep.y = a.y; ep.y_lo = a.y_lo; ep.y_fmt = a.y_fmt; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
-    ep.colnorm = a.argmin_colnorm; ep.best = a.argmin_best;
+    ep.colnorm = a.argmin_colnorm; ep.best = a.argmin_best; ep.tma_store = 0;
     int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool x3 = ctx().gemm_mode >= 2;
     if (!x3) {
@@ -477,7 +477,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
     encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
     TcEpi ep;
-    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.y_fmt = SPLIT_TF32; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
+    ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.y_fmt = SPLIT_TF32; ep.tma_store = 0; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
     return 0;

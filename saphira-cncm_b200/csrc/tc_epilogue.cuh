@@ -5,6 +5,8 @@
 #include "common.cuh"
 #include "split.cuh"
 
+#include <cuda.h>
+
 namespace ncmb {
 
 struct TcEpi {
@@ -14,6 +16,7 @@ struct TcEpi {
     int64_t M; int N; int act; int glu;
     const float *colnorm; unsigned long long *best;     // nearest-row mode
     int *err;
+    int tma_store;                                      // fp32 result tiles leave through shared memory and TMA stores
 };
 
 
@@ -132,6 +135,37 @@ __device__ __forceinline__ void tc_epilogue_glu_silu_h16(const TcEpi &ep, const 
     uint4 *d1 = (uint4 *)((unsigned short *)ep.y + e0), *d2 = (uint4 *)((unsigned short *)ep.y_lo + e0);
     d1[0] = make_uint4(p1[0], p1[1], p1[2], p1[3]); d1[1] = make_uint4(p1[4], p1[5], p1[6], p1[7]);
     d2[0] = make_uint4(p2[0], p2[1], p2[2], p2[3]); d2[1] = make_uint4(p2[4], p2[5], p2[6], p2[7]);
+}
+
+// fp32 result chunk (32 rows of one warp x 32 columns) through shared memory and one TMA store: each
+// thread writes its row's eight float4 into a 4 KB staging buffer in the 128-byte-swizzle layout, the
+// TMA unit then writes 32 full 128-byte rows (and clips rows >= M itself). A thread-per-row store
+// straight to global memory would issue 32 separate 16-byte pieces per instruction.
+// Only for chunks that lie fully inside N; `stage` must be 1024-byte aligned.
+__device__ __forceinline__ void tc_epilogue_chunk_tma(const TcEpi &ep, const uint32_t *r, int64_t m, int64_t m_warp0, int n0, int c0,
+                                                      const float4 *rp, unsigned char *stage, const CUtensorMap *tmY, int lane) {
+    // the previous store out of this buffer must have finished reading it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+    const float *rr = (ep.res && m < ep.M) ? ep.res + m * ep.ldres + n0 + c0 : nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        if (ep.bias) {
+            float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        if (ep.act != ACT_NONE) { v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act); }
+        if (rr) { float4 q4 = rp ? rp[j >> 2] : *(const float4 *)(rr + j); v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w; }
+        *(float4 *)(stage + lane * 128 + ((((j >> 2) ^ (lane & 7)) & 7) << 4)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                     ::"l"(tmY), "r"(n0 + c0), "r"((int)m_warp0), "r"((uint32_t)__cvta_generic_to_shared(stage)) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
 }
 
 } // namespace ncmb
