@@ -317,6 +317,10 @@ def run_gpu_arm(args):
         t_wall = time.perf_counter() - t_wall0
     launches = lib.ncmb_launch_count() - n0
     lib.ncmb_prof_enable(0)
+    top = None
+    tn, tms, tfl, tby = C.c_longlong(), C.c_double(), C.c_double(), C.c_double()
+    if lib.ncmb_prof_top_shape(0, C.byref(tn), C.byref(tms), C.byref(tfl), C.byref(tby)) == 0 and tn.value > 0:
+        top = {"launches": tn.value, "ms": tms.value, "flops": tfl.value, "bytes": tby.value}
     if os.environ.get("NCM_B200_PROF_SHAPES") and rank == 0:
         lib.ncmb_prof_dump_shapes()          # per-call-shape table on stderr (diagnostic)
     prof = {}
@@ -345,7 +349,13 @@ def run_gpu_arm(args):
             peaks = json.load(open(pk))
         peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
         gm = prof["gemm"]
-        ach = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
+        ach_class = gm["flops"] / (gm["ms"] * 1e-3) / 1e12 if gm["ms"] > 0 else 0.0
+        # roofline of the dominant kernel: the GEMM call shape with the largest total time in the timed steps
+        roof_kernel, ach, traffic, roof_ms, roof_n = "gemm (all linear layers)", ach_class, None, gm["ms"] / max(gm["launches"], 1), gm["launches"]
+        if top:
+            roof_ms, roof_n = top["ms"] / top["launches"], top["launches"]
+            ach = top["flops"] / (roof_ms * 1e-3) / 1e12
+            roof_kernel, traffic = describe_gemm_shape(spec, top["flops"])
         total_tok = world * B * tok * args.steps
         mode = lib.ncmb_get_gemm_mode()
         line = {
@@ -363,10 +373,15 @@ def run_gpu_arm(args):
                     "d2h_bytes_per_step": (d1.value - d0.value) // args.steps},
             "gpu_launches": launches,
             "clocks": clk.summary(),
-            "roofline": {"bound": "tensor", "kernel": "gemm (QKV/O/MLP/head linears)", "achieved": ach, "peak": peak_tf,
-                         "unit": "TFLOP/s", "frac": ach / peak_tf if peak_tf else None, "traffic": None,
+            "roofline": {"bound": "tensor", "kernel": roof_kernel, "achieved": ach, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": ach / peak_tf if peak_tf else None, "traffic": traffic,
                          "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained" if peaks else "fallback",
-                         "launches": gm["launches"], "avg_launch_ms": gm["ms"] / max(gm["launches"], 1)},
+                         "launches": roof_n, "avg_launch_ms": roof_ms,
+                         "mma_passes": 3 if mode >= 2 else 1,
+                         "note": "achieved counts algorithmic flops (2MNK); fp32-grade operands cost 3 tensor-core "
+                                 "MMAs per algorithmic MMA, so the tensor pipe runs at mma_passes x achieved",
+                         "all_gemm_launches": {"achieved": ach_class, "launches": gm["launches"],
+                                               "ms_per_step": gm["ms"] / args.steps}},
             "algorithmic_tflop_per_step": algorithmic_flops_per_row(spec) * B * (2 if kw["cfg"] > 0 else 1) / 1e12,
             "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
         }
@@ -379,6 +394,27 @@ def run_gpu_arm(args):
     if world > 1:
         dist.destroy_process_group()
     tmp.cleanup()
+
+
+def describe_gemm_shape(spec, flops):
+    """Names the transformer GEMM whose 2*M*N*K equals `flops` and, for the gated up-projection, scales the
+    DRAM traffic measured under ncu (profiles/k_gemm_h3__c2s_b128.md: 293.3 MB read+write at M=32896,
+    N=4096, K=512, i.e. 8916 bytes per token row; traffic is proportional to M at fixed N, K)."""
+    C_ = spec.n_embd
+    Hh = spec.mlp_hidden if spec.mlp_hidden else 4 * C_
+    kvd = (spec.n_kv_heads or spec.n_head) * (C_ // spec.n_head)
+    gated = bool(spec.mlp_hidden)
+    shapes = [("MLP up-projection" + (" with fused gated SiLU, fp16-pair output" if gated else ""), (2 * Hh if gated else Hh), C_),
+              ("MLP down-projection + residual", C_, Hh), ("QKV projection", C_ + 2 * kvd, C_),
+              ("attention output projection + residual", C_, C_)]
+    for name, N, K in shapes:
+        M = flops / (2.0 * N * K)
+        if abs(M - round(M)) < 1e-6 and M >= 1:
+            traffic = None
+            if gated and name.startswith("MLP up") and (N, K) == (4096, 512):
+                traffic = 8916.0 * round(M)
+            return f"k_gemm_h3: {name}, M={int(round(M))} N={N} K={K}", traffic
+    return "k_gemm_h3 (largest GEMM call shape)", None
 
 
 # --------------------------------------------------------------------------- decoder LMs / quantizer sweep

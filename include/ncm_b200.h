@@ -272,8 +272,11 @@ enum { NCMB_K_GEMM = 0, NCMB_K_ATTN = 1, NCMB_K_NORM = 2, NCMB_K_SAMPLE = 3,
        NCMB_K_ELEM = 4, NCMB_K_VQ = 5, NCMB_K_COUNT = 6 };
 void  ncmb_prof_enable(int on);
 void  ncmb_prof_reset(void);
-/* With NCM_B200_PROF_SHAPES=1 in the environment the profiler also keeps one line per distinct call
- * shape (class, flops, bytes); this prints that table to stderr, largest total first, and clears it. */
+/* The profiler also keeps one entry per distinct call shape (class, flops, bytes of one call).
+ * ncmb_prof_top_shape: the shape of class `klass` with the largest total time since the last reset
+ * (launch count, total ms, flops and bytes of ONE call); -1 when the class recorded nothing.
+ * ncmb_prof_dump_shapes: prints the whole table to stderr, largest total first, and clears it. */
+int   ncmb_prof_top_shape(int klass, long long *launches, double *ms, double *flops, double *bytes);
 void  ncmb_prof_dump_shapes(void);
 int   ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes);
 long long ncmb_launch_count(void);            /* kernels launched since load */

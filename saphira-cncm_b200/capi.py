@@ -119,6 +119,8 @@ _SIGS = {
     "ncmb_prof_enable": (None, [_I]),
     "ncmb_prof_reset": (None, []),
     "ncmb_prof_dump_shapes": (None, []),
+    "ncmb_prof_top_shape": (_I, [_I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                 C.POINTER(C.c_double)]),
     "ncmb_prof_read": (_I, [_I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double),
                             C.POINTER(C.c_double)]),
     "ncmb_linear_fwd_noalloc": (_I, [_P, _P, _P, _P, _I64, _I, _I]),

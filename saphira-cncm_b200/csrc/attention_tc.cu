@@ -1,9 +1,9 @@
 // Tensor-core attention for head dim 64 on sm_100a (tcgen05 + TMEM + TMA).
 //
-// One CTA (256 threads) per (sequence row, head, 128-query tile):
+// One CTA (512 threads) per (sequence row, head, 128-query tile):
 //   S = Q K^T   tcgen05.mma.kind::tf32 into tensor memory, keys in blocks of <= 128 columns; the
 //               first two key blocks and the query tile are fetched together by TMA
-//   softmax     two threads per query row (each takes half of the columns) read the scores with
+//   softmax     four threads per query row (each takes a quarter of the columns) read the scores with
 //               tcgen05.ld; all keys of a row are resident, so the row maximum is known before
 //               any exponential is taken and no rescaling is needed
 //   O += P V    per 32-key chunk: P is written to shared memory by the softmax threads, V (fetched
@@ -25,10 +25,10 @@
 
 namespace ncmb {
 
-constexpr int ATC_THREADS = 256;
+constexpr int ATC_THREADS = 512;          // four threads per query row, eight score columns of a chunk each
 constexpr int ATC_OCOL = 448;            // TMEM column of the output accumulator; scores use columns [0, 448)
 constexpr int ATC_VSLOTS = 8;
-constexpr int ATC_SMEM = 1024 + 3 * 65536 + 256 * 4 + 32 * 8 + 64;
+constexpr int ATC_SMEM = 1024 + 3 * 65536 + ATC_THREADS * 4 + 32 * 8 + 64;
 
 struct AttnTcDev {
     float *out; float *out_lo; int64_t ldo; int out_fmt;
@@ -53,6 +53,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                    "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -84,8 +90,8 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *R0 = smem, *R1 = smem + 65536, *R2 = smem + 131072;
-    float *xch = (float *)(smem + 196608);                       // 256 floats: row max / row sum exchange
-    uint64_t *bars = (uint64_t *)(xch + 256);
+    float *xch = (float *)(smem + 196608);                       // one float per thread: row max / row sum exchange
+    uint64_t *bars = (uint64_t *)(xch + ATC_THREADS);
     uint32_t *tmem_slot = (uint32_t *)(bars + 32);
     // barriers: 0 Q | 1,2 K region full | 3,4 S MMAs of a region done | 5,6 PV MMAs of a buffer done | 8..15 V slots
     const uint32_t bar_q = smem_u32(bars), bar_k0 = smem_u32(bars + 1), bar_s0 = smem_u32(bars + 3);
@@ -206,7 +212,7 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     // ================= phase 2: softmax and O = P V =================
     if (tid == 0)
         for (int c = 0; c < nchunks && c < ATC_VSLOTS; c++) load_vchunk(c);
-    const int r = tid & 127, half = tid >> 7;                     // query row of the tile, column half
+    const int r = tid & 127, part = tid >> 7;                     // query row of the tile, which quarter of each chunk's columns
     const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
     const int h = a.pack ? kvh * G + (r >> 5) : (int)blockIdx.y;
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -224,7 +230,7 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
         jlo = lo - base; jhi = hi - base;
     };
     float mx = -INFINITY;
-    for (int c = half; c < nchunks; c += 2) {
+    for (int c = part; c < nchunks; c += 4) {
         uint32_t v[32];
         tmem_ld32(lane_addr + (uint32_t)(c * 32), v);
         int jlo, jhi;
@@ -235,7 +241,7 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     }
     xch[tid] = mx;
     __syncthreads();
-    mx = fmaxf(mx, xch[tid ^ 128]);
+    mx = fmaxf(fmaxf(xch[r], xch[r + 128]), fmaxf(xch[r + 256], xch[r + 384]));
     __syncthreads();                                              // xch is reused for the row sums
     const bool any = mx != -INFINITY;
     const float sl2 = a.scale * 1.4426950408889634f;
@@ -247,14 +253,14 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
         unsigned char *Vthi = R0 + b * 16384, *Vtlo = Vthi + 8192;
         if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
         {
-            uint32_t v[16];
-            tmem_ld16(lane_addr + (uint32_t)(c * 32 + half * 16), v);
+            uint32_t v[8];
+            tmem_ld8(lane_addr + (uint32_t)(c * 32 + part * 8), v);
             int jlo, jhi;
             chunk_range(c, jlo, jhi);
-            jlo -= half * 16; jhi -= half * 16;
+            jlo -= part * 8; jhi -= part * 8;
             const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
 #pragma unroll
-            for (int g = 0; g < 4; g++) {
+            for (int g = 0; g < 2; g++) {
                 float p[4], ph[4];
 #pragma unroll
                 for (int e = 0; e < 4; e++) {
@@ -263,7 +269,7 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
                     if (any && j >= jlo && j < jhi) x = exp2f((__uint_as_float(v[j]) - mx) * sl2);
                     l += x; p[e] = x; ph[e] = atc_hi(x);
                 }
-                const uint32_t o = rowoff + ((uint32_t)(((half * 4 + g) ^ (r & 7)) & 7) << 4);
+                const uint32_t o = rowoff + ((uint32_t)(((part * 2 + g) ^ (r & 7)) & 7) << 4);
                 *(float4 *)(Phi + o) = make_float4(ph[0], ph[1], ph[2], ph[3]);
                 *(float4 *)(Plo + o) = make_float4(p[0] - ph[0], p[1] - ph[1], p[2] - ph[2], p[3] - ph[3]);
             }
@@ -275,8 +281,8 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
             const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
             const int kk = tid & 31;
 #pragma unroll
-            for (int n = 0; n < 8; n++) {
-                const int d = (tid >> 5) + 8 * n;
+            for (int n = 0; n < 4; n++) {
+                const int d = (tid >> 5) + 16 * n;
                 float x = *(const float *)(Vraw + (d >> 5) * 4096 + sw128_off(kk, d & 31));
                 if (kk >= nvalid) x = 0.f;
                 float hi = atc_hi(x);
@@ -308,17 +314,17 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     tc_fence_after();
     xch[tid] = l;
     __syncthreads();
-    l += xch[tid ^ 128];
-    // ---- output row: O / l; the two threads of a row take 32 columns each ----
+    l = (xch[r] + xch[r + 128]) + (xch[r + 256] + xch[r + 384]);
+    // ---- output row: O / l; the four threads of a row take 16 columns each ----
     {
         const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
         const float inv = l > 0.f ? 1.0f / l : 0.f;
-        const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + half * 32;
-        uint32_t v[32];
-        if (nchunks > 0) tmem_ld32(lane_addr + (uint32_t)(ATC_OCOL + half * 32), v);
+        const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
+        uint32_t v[16];
+        if (nchunks > 0) tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
         if (live) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int j = 0; j < 16; j += 4) {
                 float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
                                         __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
                 if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);

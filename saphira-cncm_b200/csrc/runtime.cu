@@ -63,9 +63,9 @@ struct Prof {
     ProfRec cur; bool in_scope = false; int depth = 0;
     long long launches[NCMB_K_COUNT] = {0};
     double ms[NCMB_K_COUNT] = {0}, flops[NCMB_K_COUNT] = {0}, bytes[NCMB_K_COUNT] = {0};
-    // NCM_B200_PROF_SHAPES=1: also keep one line per distinct (class, flops, bytes) scope, i.e. per call shape
+    // one entry per distinct (class, flops, bytes) scope, i.e. per call shape
     std::map<std::tuple<int, double, double>, std::pair<long long, double>> shapes;
-    bool by_shape = getenv("NCM_B200_PROF_SHAPES") != nullptr;
+    bool by_shape = true;
     cudaEvent_t get() {
         if (!pool.empty()) { cudaEvent_t e = pool.back(); pool.pop_back(); return e; }
         cudaEvent_t e;
@@ -475,8 +475,25 @@ void ncmb_prof_reset(void) {
     Prof &p = prof();
     p.drain();
     for (int i = 0; i < NCMB_K_COUNT; i++) { p.launches[i] = 0; p.ms[i] = p.flops[i] = p.bytes[i] = 0; }
+    p.shapes.clear();
 }
-// prints the per-shape table (NCM_B200_PROF_SHAPES=1) to stderr, largest total first, and clears it
+// the call shape of class `klass` with the largest total time since the last reset: its launch count,
+// total ms, and the flops / bytes ONE call declared. Returns -1 when the class recorded nothing.
+int ncmb_prof_top_shape(int klass, long long *launches, double *ms, double *flops, double *bytes) {
+    Prof &p = prof();
+    p.drain();
+    const std::pair<const std::tuple<int, double, double>, std::pair<long long, double>> *best = nullptr;
+    for (auto &kv : p.shapes)
+        if (std::get<0>(kv.first) == klass && (!best || kv.second.second > best->second.second)) best = &kv;
+    if (!best) return -1;
+    if (launches) *launches = best->second.first;
+    if (ms) *ms = best->second.second;
+    if (flops) *flops = std::get<1>(best->first);
+    if (bytes) *bytes = std::get<2>(best->first);
+    return 0;
+}
+
+// prints the per-shape table to stderr, largest total first, and clears it
 void ncmb_prof_dump_shapes(void) {
     Prof &p = prof();
     p.drain();
