@@ -140,7 +140,7 @@ def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int)
     times = []
     if os.path.exists(ref_lib):
         os.environ["NCM_THREADS"] = str(cores)
-        os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+        os.environ["OMP_NUM_THREADS"] = str(cores)      # torchrun presets 1; the reference build reads it when it loads
         ref = capi.NcmLib(ref_lib)
         m = capi.NcpModel(ref, conf, w, arena_mb=2048)
         L, D, Vp, nl = spec.L, spec.vq_dim, spec.in_vocab, len(spec.levels)
