@@ -250,7 +250,8 @@ int   ncmb_get_gemm_mode(void);
  * code and drain. Returns and clears that code (0 = never happened); synchronises. */
 int   ncmb_gemm_tc_check(void);
 /* Diagnostic: the transformer blocks' token-major attention (head dim 64) on caller-supplied DEVICE
- * buffers, with engine 0 (CUDA-core kernel) or 1 (tcgen05 kernel), so both can be compared on the same
+ * buffers, with engine 0 (CUDA-core kernel), 1 (tcgen05 kernel) or 2 (split-key decode kernel, one query
+ * per row, one key segment), so they can be compared on the same
  * inputs. q [q_total][H*64]; kv1 / kv2 [tokens][2*Hkv*64] (keys, then values); *_start are HOST
  * int[rows+1] prefix offsets, k2_start NULL for one key segment. Returns 0, -1 when the tensor-core
  * engine does not take the shape, else the timeout code. No counterpart in the reference. */

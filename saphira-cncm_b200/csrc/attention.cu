@@ -197,7 +197,9 @@ static void launch_attention(const AttnDev &d, dim3 grid) {
 
 void attention(const AttnArgs &a) {
     if (a.rows <= 0 || a.max_q <= 0) return;
+    if (attention_decode_supported(a)) { attention_decode(a); return; }
     if (ctx().gemm_mode >= 1 && attention_tc_supported(a)) { attention_tc(a); return; }
+    if (a.step_d) fatal("attention: a step-indexed plan reached a kernel that does not read the step counter");
     AttnDev d;
     d.q = a.q; d.ldq = a.ldq; d.k1 = a.k1; d.v1 = a.v1; d.ldk1 = a.ldk1;
     d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo; d.out_fmt = a.out_fmt;
@@ -294,7 +296,8 @@ void sdpa_masked(const float *q, const float *k, const float *v, const float *ma
 __global__ void __launch_bounds__(256) k_qk_post(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int hd,
                                                 int64_t ntok, const float *__restrict__ qw, const float *__restrict__ kw,
                                                 const float *__restrict__ cs, const float *__restrict__ sn,
-                                                const int *__restrict__ pos) {
+                                                const int *__restrict__ pos, const int *__restrict__ step_d, int64_t pos_step) {
+    if (step_d) pos += (int64_t)(*step_d) * pos_step;          // decode steps replayed from one graph
     int64_t w = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     int lane = threadIdx.x & 31;
     int HT = H + Hkv;
@@ -326,12 +329,68 @@ __global__ void __launch_bounds__(256) k_qk_post(float *q, int64_t ldq, int H, f
     }
 }
 
+// Same operation, one warp per TOKEN (head dim <= 64): the lane owns the pair (d, d + hd/2) of every head, so the
+// position and the four table values are fetched once per token instead of once per head, and the loads of
+// eight heads are in flight together.
+constexpr int QKP_HG = 8;
+__global__ void __launch_bounds__(256) k_qk_post_tok(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int hd,
+                                                    int64_t ntok, const float *__restrict__ qw, const float *__restrict__ kw,
+                                                    const float *__restrict__ cs, const float *__restrict__ sn,
+                                                    const int *__restrict__ pos, const int *__restrict__ step_d, int64_t pos_step) {
+    if (step_d) pos += (int64_t)(*step_d) * pos_step;
+    const int64_t tok = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31, half = hd / 2, HT = H + Hkv;
+    if (tok >= ntok) return;
+    const bool on = lane < half;
+    float c0 = 1.f, c1 = 1.f, s0 = 0.f, s1 = 0.f;
+    if (cs && on) {
+        const int64_t p = (int64_t)pos[tok] * hd;
+        c0 = cs[p + lane]; c1 = cs[p + lane + half]; s0 = sn[p + lane]; s1 = sn[p + lane + half];
+    }
+    for (int h0 = 0; h0 < HT; h0 += QKP_HG) {
+        float a[QKP_HG], b[QKP_HG];
+        float *xp[QKP_HG];
+#pragma unroll
+        for (int i = 0; i < QKP_HG; i++) {
+            const int hh = h0 + i;
+            xp[i] = hh < H ? q + tok * ldq + hh * hd : k + tok * ldk + (hh - H) * hd;
+            a[i] = (hh < HT && on) ? xp[i][lane] : 0.f;
+            b[i] = (hh < HT && on) ? xp[i][lane + half] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < QKP_HG; i++) {
+            const int hh = h0 + i;
+            if (hh >= HT) break;
+            const float *nw = hh < H ? qw : kw;
+            float x0 = a[i], x1 = b[i];
+            if (nw) {
+                float ss = x0 * x0 + x1 * x1;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                const float r = 1.0f / sqrtf(ss / (float)hd + 1e-6f);
+                if (on) { x0 = __fmul_rn(__fmul_rn(x0, r), nw[lane]); x1 = __fmul_rn(__fmul_rn(x1, r), nw[lane + half]); }
+            }
+            if (cs) {
+                const float y0 = __fadd_rn(__fmul_rn(x0, c0), __fmul_rn(-x1, s0));
+                const float y1 = __fadd_rn(__fmul_rn(x1, c1), __fmul_rn(x0, s1));
+                x0 = y0; x1 = y1;
+            }
+            if (on) { xp[i][lane] = x0; xp[i][lane + half] = x1; }
+        }
+    }
+}
+
 void qk_post(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int hd, int64_t ntok,
-             const float *qnorm_w, const float *knorm_w, const float *cos_t, const float *sin_t, const int *pos_dev) {
+             const float *qnorm_w, const float *knorm_w, const float *cos_t, const float *sin_t, const int *pos_dev, const int *step_d, int64_t pos_step) {
     if (ntok <= 0 || (!qnorm_w && !cos_t)) return;
     ProfScope ps(NCMB_K_ELEM, 0, (double)ntok * (H + Hkv) * hd * 8);
+    if (hd <= 64 && (hd & 1) == 0) {
+        LAUNCH(k_qk_post_tok, grid1d(ntok * 32, 256), 256, 0, q, ldq, H, k, ldk, Hkv, hd, ntok,
+               qnorm_w, knorm_w, cos_t, sin_t, pos_dev, step_d, pos_step);
+        return;
+    }
     LAUNCH(k_qk_post, grid1d(ntok * (H + Hkv) * 32, 256), 256, 0, q, ldq, H, k, ldk, Hkv, hd, ntok,
-           qnorm_w, knorm_w, cos_t, sin_t, pos_dev);
+           qnorm_w, knorm_w, cos_t, sin_t, pos_dev, step_d, pos_step);
 }
 
 // table row = index within each group of T rows (reference rope_apply semantics)

@@ -1,0 +1,214 @@
+// Decode-step attention: ONE query per sequence row against that row's K/V cache (the decoder-LM
+// token loop, reference src/gpt2.c:92 / src/qwen.c:121 run with a KV cache instead of recomputing).
+//
+// With one query there is nothing to tile over queries, so the keys are split instead: one CTA per
+// (32-key chunk, kv head, row) computes the chunk's scores for every query head that shares the kv
+// head (K and V are read once per group), a local softmax and the partial context, and writes
+// (max, sum, context[hd]) per head to scratch. The last CTA of a (row, kv head) to finish -- an
+// atomic counter tells it -- merges the partials with the usual log-sum-exp rescaling and writes the
+// context row. A batch-1, 12-head step with 300 cached keys thus runs on ~120 CTAs instead of 12.
+//
+// step_d: optional device counter. When set, row lengths are read from k1_len + (*step_d) * len_step,
+// so one captured CUDA graph serves every decode step.
+#include "common.cuh"
+#include "split.cuh"
+
+namespace ncmb {
+
+constexpr int AD_KEYS = 32, AD_THREADS = 128, AD_MAXG = 8, AD_MAXSPLIT = 64;   // up to 2048 cached keys per row
+
+struct AttnDecDev {
+    const float *q; int64_t ldq;
+    const float *k, *v; int64_t ldk;
+    float *out; float *out_lo; int out_fmt; int64_t ldo;
+    const int *q_start, *k_start, *k_len;
+    const int *step_d; int64_t len_step;
+    int H, Hkv, max_split;
+    float scale;
+    float *part; unsigned *count;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
+    constexpr int DP = HD / 4;                         // dims per thread in the score step (4 threads per key)
+    constexpr int GROUPS = AD_THREADS / HD > 0 ? AD_THREADS / HD : 1;   // key groups in the PV step
+    constexpr int KPG = AD_KEYS / GROUPS;
+    __shared__ __align__(16) float qs[AD_MAXG][HD];
+    __shared__ float sc[AD_MAXG][AD_KEYS];
+    __shared__ float red[GROUPS][AD_MAXG][HD];
+    __shared__ float mg[AD_MAXG], lg[AD_MAXG];
+    __shared__ int s_last;
+    const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
+    const int G = a.H / a.Hkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_launch_dependents();          // programmatic dependent launch: the successor may start launching now,
+    pdl_wait();                       // and nothing the predecessor wrote is read before this point
+    const int *lens = a.k_len ? a.k_len + (a.step_d ? (int64_t)(*a.step_d) * a.len_step : 0) : nullptr;
+    const int k00 = a.k_start[row], n1 = lens ? lens[row] : a.k_start[row + 1] - k00;
+    const int nsplit = (n1 + AD_KEYS - 1) / AD_KEYS;
+    if (sp >= nsplit) return;
+    const int k0 = sp * AD_KEYS;
+    const int q0 = a.q_start[row];
+
+    for (int i = tid; i < G * HD; i += AD_THREADS) {
+        int g = i / HD, d = i % HD;
+        qs[g][d] = a.q[(int64_t)q0 * a.ldq + (kvh * G + g) * HD + d];
+    }
+    __syncthreads();
+    {   // scores: four threads per key, each a quarter of the head dim
+        const int j = tid >> 2, part = tid & 3;
+        const bool valid = k0 + j < n1;
+        float kr[DP];
+        if (valid) {
+            const float4 *kp = (const float4 *)(a.k + (int64_t)(k00 + k0 + j) * a.ldk + kvh * HD + part * DP);
+#pragma unroll
+            for (int i = 0; i < DP / 4; i++) { float4 t = kp[i]; kr[4 * i] = t.x; kr[4 * i + 1] = t.y; kr[4 * i + 2] = t.z; kr[4 * i + 3] = t.w; }
+        } else {
+#pragma unroll
+            for (int i = 0; i < DP; i++) kr[i] = 0.f;
+        }
+        for (int g = 0; g < G; g++) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < DP; i++) dot = fmaf(kr[i], qs[g][part * DP + i], dot);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            if (part == 0) sc[g][j] = valid ? dot * a.scale : -INFINITY;
+        }
+    }
+    __syncthreads();
+    for (int g = warp; g < G; g += AD_THREADS / 32) {   // chunk softmax, one warp per head
+        float s = sc[g][lane];
+        float m = s;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float p = (s == -INFINITY) ? 0.f : expf(s - m);
+        float l = p;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+        sc[g][lane] = p;
+        if (lane == 0) { mg[g] = m; lg[g] = l; }
+    }
+    __syncthreads();
+    {   // partial context: thread = (key group, dim); V rows are read once for all heads of the group
+        const int grp = tid / HD, d = tid % HD;
+        float acc[AD_MAXG];
+#pragma unroll
+        for (int g = 0; g < AD_MAXG; g++) acc[g] = 0.f;
+        if (grp < GROUPS) {
+            float vr[KPG];                                   // all V loads of this thread in flight together
+#pragma unroll
+            for (int jj = 0; jj < KPG; jj++) {
+                const int j = grp * KPG + jj;
+                vr[jj] = (k0 + j < n1) ? a.v[(int64_t)(k00 + k0 + j) * a.ldk + kvh * HD + d] : 0.f;
+            }
+#pragma unroll
+            for (int jj = 0; jj < KPG; jj++) {
+                const int j = grp * KPG + jj;
+#pragma unroll
+                for (int g = 0; g < AD_MAXG; g++) if (g < G) acc[g] = fmaf(sc[g][j], vr[jj], acc[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < AD_MAXG; g++) if (g < G) red[grp][g][d] = acc[g];
+        }
+    }
+    __syncthreads();
+    float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * G * (HD + 2);
+    for (int i = tid; i < G * HD; i += AD_THREADS) {
+        int g = i / HD, d = i % HD;
+        float o = 0.f;
+#pragma unroll
+        for (int r = 0; r < GROUPS; r++) o += red[r][g][d];
+        mine[g * (HD + 2) + 2 + d] = o;
+        if (d == 0) { mine[g * (HD + 2)] = mg[g]; mine[g * (HD + 2) + 1] = lg[g]; }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned old = atomicAdd(a.count + row * a.Hkv + kvh, 1u);
+        s_last = (old == (unsigned)(nsplit - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // merge: the chunk partials of this (row, kv head), read through L2. Maxima and sums first (one load per
+    // thread, all in flight together), then the rescaling weights once per head, then the context columns
+    // with independent loads -- a chain of dependent L2 round trips per split would dominate the kernel.
+    __shared__ float wsm[AD_MAXSPLIT][AD_MAXG], lsm[AD_MAXSPLIT][AD_MAXG], Lg[AD_MAXG];
+    const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * G * (HD + 2);
+    for (int i = tid; i < nsplit * G; i += AD_THREADS) {
+        int s = i / G, g = i % G;
+        const float *ps = base + ((int64_t)s * G + g) * (HD + 2);
+        wsm[s][g] = __ldcg(ps); lsm[s][g] = __ldcg(ps + 1);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY, L = 0.f;
+        for (int s = 0; s < nsplit; s++) M = fmaxf(M, wsm[s][tid]);
+        for (int s = 0; s < nsplit; s++) { float w = expf(wsm[s][tid] - M); wsm[s][tid] = w; L = fmaf(lsm[s][tid], w, L); }
+        Lg[tid] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += AD_THREADS) {
+        int g = i / HD, d = i % HD;
+        float O = 0.f;
+        int s = 0;
+        for (; s + 4 <= nsplit; s += 4) {
+            float o0 = __ldcg(base + ((int64_t)(s + 0) * G + g) * (HD + 2) + 2 + d);
+            float o1 = __ldcg(base + ((int64_t)(s + 1) * G + g) * (HD + 2) + 2 + d);
+            float o2 = __ldcg(base + ((int64_t)(s + 2) * G + g) * (HD + 2) + 2 + d);
+            float o3 = __ldcg(base + ((int64_t)(s + 3) * G + g) * (HD + 2) + 2 + d);
+            O = fmaf(o0, wsm[s][g], O); O = fmaf(o1, wsm[s + 1][g], O); O = fmaf(o2, wsm[s + 2][g], O); O = fmaf(o3, wsm[s + 3][g], O);
+        }
+        for (; s < nsplit; s++) O = fmaf(__ldcg(base + ((int64_t)s * G + g) * (HD + 2) + 2 + d), wsm[s][g], O);
+        const float L = Lg[g];
+        const float r = L > 0.f ? O / L : 0.f;
+        const int64_t at = (int64_t)q0 * a.ldo + (kvh * G + g) * HD + d;
+        if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+        else a.out[at] = r;
+    }
+    if (tid == 0) a.count[row * a.Hkv + kvh] = 0;          // ready for the next launch
+}
+
+bool attention_decode_supported(const AttnArgs &a) {
+    if (a.max_q != 1 || a.k2 || a.causal || a.window > 0) return false;
+    if (a.hd != 16 && a.hd != 32 && a.hd != 64 && a.hd != 128) return false;
+    if (a.Hkv <= 0 || a.H % a.Hkv || a.H / a.Hkv > AD_MAXG) return false;
+    if (a.max_k1 <= 0 || a.max_k1 > AD_KEYS * AD_MAXSPLIT) return false;
+    if ((a.ldk1 & 3) || ((uintptr_t)a.k1 & 15)) return false;
+    return true;
+}
+
+void attention_decode(const AttnArgs &a) {
+    static float *part = nullptr; static size_t part_cap = 0;
+    static unsigned *count = nullptr; static size_t count_cap = 0;
+    const int max_split = (int)cdiv(a.max_k1, AD_KEYS);
+    size_t need = (size_t)a.rows * a.H * max_split * (a.hd + 2);
+    if (need > part_cap) {
+        if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
+        part = (float *)dev_alloc(need * 4); part_cap = need;
+    }
+    size_t nc = (size_t)a.rows * a.Hkv;
+    if (nc > count_cap) {
+        if (count) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(count); }
+        count = (unsigned *)dev_alloc(nc * 4); count_cap = nc;
+        CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
+    }
+    AttnDecDev d;
+    d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
+    d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
+    d.step_d = a.step_d; d.len_step = a.k1_len_step;
+    d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split;
+    d.scale = 1.0f / sqrtf((float)a.hd);
+    d.part = part; d.count = count;
+    dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
+    ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+    switch (a.hd) {
+        case 16: LAUNCH_PDL(k_attention_decode<16>, grid, AD_THREADS, 0, d); break;
+        case 32: LAUNCH_PDL(k_attention_decode<32>, grid, AD_THREADS, 0, d); break;
+        case 64: LAUNCH_PDL(k_attention_decode<64>, grid, AD_THREADS, 0, d); break;
+        default: LAUNCH_PDL(k_attention_decode<128>, grid, AD_THREADS, 0, d); break;
+    }
+}
+
+} // namespace ncmb

@@ -384,7 +384,7 @@ void attention_tc(const AttnArgs &a) {
 
 // Diagnostic entry point: runs the token-major attention of the transformer blocks on caller-supplied
 // device buffers with either engine (0: CUDA-core kernel, 1: tcgen05 kernel), so the two can be compared
-// on the same inputs. q [q_total][H*64]; kv1 / kv2 [tokens][2*Hkv*64] (keys then values); the *_start
+// on the same inputs (engine 2: the split-key decode kernel, one query per row). q [q_total][H*64]; kv1 / kv2 [tokens][2*Hkv*64] (keys then values); the *_start
 // arrays are host int[rows+1] prefix offsets (k2_start null: one key segment). Returns 0, -1 when the
 // tensor-core engine does not take the shape, or the engine's timeout code.
 extern "C" int ncmb_attention_check(const float *q, const float *kv1, const float *kv2, float *out,
@@ -415,10 +415,16 @@ extern "C" int ncmb_attention_check(const float *q, const float *kv1, const floa
         a.max_q = std::max(a.max_q, 64);               // the size threshold is a dispatch heuristic, not a limit
         if (!attention_tc_supported(a)) rc = -1;
         else { a.max_q = saved_max_q; attention_tc(a); rc = gemm_tc_check(); }
+    } else if (engine == 2) {
+        if (!attention_decode_supported(a)) rc = -1;
+        else attention_decode(a);
     } else {
-        int saved = ctx().gemm_mode;
+        // the CUDA-core kernel, called directly: the dispatcher would pick the other engines where they apply
+        int saved = ctx().gemm_mode, saved_q = a.max_q;
         ctx().gemm_mode = 0;
+        if (attention_decode_supported(a)) a.max_q = 2;     // grid sizing only; rows still hold one query
         attention(a);
+        a.max_q = saved_q;
         ctx().gemm_mode = saved;
     }
     CUDA_CHECK(cudaStreamSynchronize(stream()));

@@ -36,6 +36,7 @@ inline cudaStream_t stream() { return ctx().stream; }
 
 void prof_begin(int klass, double flops, double bytes);
 void prof_end();
+bool prof_enabled();
 struct ProfScope {
     ProfScope(int klass, double flops = 0, double bytes = 0) { prof_begin(klass, flops, bytes); }
     ~ProfScope() { prof_end(); }
@@ -48,6 +49,32 @@ struct ProfScope {
     cudaError_t le_ = cudaGetLastError(); \
     if (le_ != cudaSuccess) ::ncmb::fatal("launch %s failed: %s (%s:%d)", #kernel, \
         cudaGetErrorString(le_), __FILE__, __LINE__); } while (0)
+
+// Programmatic dependent launch (decode-step kernels): the kernel may begin while its predecessor on the
+// stream is still running; it must not read anything the predecessor writes before pdl_wait(). A kernel
+// calls pdl_launch_dependents() early so that its own successor may begin the same way.
+template <typename... KArgs, typename... Args>
+static inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    static const bool off = getenv("NCM_B200_NO_PDL") != nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ::ncmb::stream();
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = off ? 0 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) ::ncmb::fatal("launch failed: %s", cudaGetErrorString(e));
+}
+#define LAUNCH_PDL(kernel, grid, block, smem, ...) do { \
+    ::ncmb::launch_pdl(kernel, dim3(grid), dim3(block), (size_t)(smem), __VA_ARGS__); \
+    ::ncmb::ctx().launches++; \
+    cudaError_t le_ = cudaGetLastError(); \
+    if (le_ != cudaSuccess) ::ncmb::fatal("launch %s failed: %s (%s:%d)", #kernel, \
+        cudaGetErrorString(le_), __FILE__, __LINE__); } while (0)
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 static inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline unsigned grid1d(int64_t n, int block) {
@@ -96,6 +123,12 @@ struct GemmArgs {
     const float *x_lo = nullptr;
     float *y_lo = nullptr;
     int x_fmt = SPLIT_TF32, y_fmt = SPLIT_TF32;   // formats of (x, x_lo) and (y, y_lo) when the lo pointer is set
+    // few-row (decode) calls only, honoured by the GEMV kernel (see gemv_fusable()):
+    //  * the input rows are normalised on the fly: x <- norm(x) * ln_w (+ ln_b), ln_kind 1 LayerNorm, 2 RMSNorm
+    //  * output columns >= y2_col0 are also written to y2[m*ldy2 + (*y2_step_d)*y2_step + (n - y2_col0)]
+    //    (the K|V part of a fused QKV projection going straight into the cache)
+    int ln_kind = 0; const float *ln_w = nullptr, *ln_b = nullptr; float ln_eps = 0.f;
+    float *y2 = nullptr; int y2_col0 = 0; int64_t ldy2 = 0; const int *y2_step_d = nullptr; int64_t y2_step = 0;
     // nearest-row search instead of a stored product (tensor-core engine only): for every x row, the
     // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
     const float *argmin_colnorm = nullptr;
@@ -103,6 +136,7 @@ struct GemmArgs {
 };
 void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
 void gemm_simt(const GemmArgs &a);
+bool gemv_fusable(const GemmArgs &a);    // true when the call will run on the GEMV kernel (M <= 16, 16-byte rows)
 bool gemm_tc_supported(const GemmArgs &a);
 void gemm_tc(const GemmArgs &a);
 // gemm mode 3: fp16 split pairs, three kind::f16 MMAs per k-step into two accumulators (gemm_h3.cu)
@@ -163,8 +197,12 @@ struct AttnArgs {
     // tensor-core path only (0 = unknown, which keeps the call on the CUDA-core kernel):
     int max_k1 = 0, max_k2 = 0;                  // longest key segment of any row
     int64_t q_total = 0, k1_total = 0, k2_total = 0;   // token rows the q / k1 / k2 buffers hold (TMA bounds)
+    // decode steps replayed from one CUDA graph: lengths are read from k1_len + (*step_d) * k1_len_step
+    const int *step_d = nullptr; int64_t k1_len_step = 0;
 };
 void attention(const AttnArgs &a);
+bool attention_decode_supported(const AttnArgs &a);   // attention_decode.cu: one query per row, keys split over CTAs
+void attention_decode(const AttnArgs &a);
 bool attention_tc_supported(const AttnArgs &a);  // attention_tc.cu: head dim 64, >= 64 queries, <= 448 padded keys
 void attention_tc(const AttnArgs &a);
 // reference-layout SDPA with an additive [Tq][Tkv] mask (ncm.h API)
@@ -174,7 +212,7 @@ void sdpa_masked(const float *q, const float *k, const float *v, const float *ma
 // RMSNorm (eps 1e-6) then half-split rotary embedding with table row pos[token].
 void qk_post(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int hd, int64_t ntok,
              const float *qnorm_w, const float *knorm_w, const float *cos_t, const float *sin_t,
-             const int *pos_dev);
+             const int *pos_dev, const int *step_d = nullptr, int64_t pos_step = 0);
 
 // ---- sampling (sampling.cu) ----
 struct SampleArgs {
@@ -220,6 +258,9 @@ struct AttnPlan {
     const int *pos = nullptr; const float *cos_t = nullptr, *sin_t = nullptr;
     int64_t total_q = 0; double avg_keys = 0;
     int max_k1 = 0; int64_t k1_total = 0;  // longest segment-1 key run; token rows behind k1 (0 = not stated)
+    // one captured graph for every decode step: per-step arrays are indexed by the device counter *step_d
+    const int *step_d = nullptr;
+    int64_t k1_len_step = 0, pos_step = 0, kv_store_step = 0;   // strides (elements) of k1_len / pos / kv_store per step
     // after the K/V of this pass are final (norm + rope applied) they are stored here:
     float *kv_store = nullptr; int64_t kv_pitch = 0;   // row pitch in floats; rows = tokens, width 2*kvd
     int kv_rows_per_seq = 0; int64_t kv_seq_pitch = 0; // > 0: token t of sequence s goes to s*kv_seq_pitch + t*kv_pitch

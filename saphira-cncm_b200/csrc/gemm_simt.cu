@@ -25,6 +25,8 @@ struct GemmDev {
     int64_t M; int N, K;
     int act;
     int vec;        // 1: K % 4 == 0 and x / W rows are 16-byte aligned
+    int ln_kind; const float *ln_w, *ln_b; float ln_eps;
+    float *y2; int y2_col0; int64_t ldy2; const int *y2_step_d; int64_t y2_step;
 };
 
 // ---- tiled kernel: BM x BN output tile per CTA, BK-deep stages, TMxTN per thread ----
@@ -206,6 +208,153 @@ __global__ void __launch_bounds__(256) k_gemm_skinny(GemmDev a) {
     }
 }
 
+// ---- GEMV-like kernel (M <= 8 rows per pass, vector path): one CTA per GV_NC output columns, all 256 threads
+// stride over K together, so every thread has its 128-bit weight loads of all columns in flight at once
+// (the weights are read exactly once, coalesced 512 bytes per warp and column); partial dot products are
+// reduced by warp shuffles and one shared-memory pass. Decode steps (one token per sequence) live here: they
+// are bound by streaming the weights, not by arithmetic.
+// The kernel is launched with programmatic stream serialization: it lets its successor start at once
+// (griddepcontrol.launch_dependents), requests the weights of its first GV_PF k-steps -- which no kernel of a
+// decode step writes -- and only then waits for its predecessor (griddepcontrol.wait) before touching x. So
+// the launch latency and the DRAM latency of the weight stream run under the previous kernel. ----
+template <int MT, int GV_NC, int GV_PF>
+__global__ void __launch_bounds__(256) k_gemv(GemmDev a) {
+    __shared__ float red[8][MT][GV_NC];
+    __shared__ float stat[8][MT], s_mean[MT], s_rstd[MT];
+    const int n0 = blockIdx.x * GV_NC;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    const float *wr[GV_NC];
+#pragma unroll
+    for (int c = 0; c < GV_NC; c++) wr[c] = a.W + (int64_t)min(n0 + c, a.N - 1) * a.K;
+    float4 wpre[GV_PF][GV_NC];
+#pragma unroll
+    for (int p = 0; p < GV_PF; p++) {
+        const int k = tid * 4 + p * 1024;
+        if (k < a.K) {
+#pragma unroll
+            for (int c = 0; c < GV_NC; c++) wpre[p][c] = __ldg((const float4 *)(wr[c] + k));
+        }
+    }
+    pdl_wait();
+    for (int64_t mb = 0; mb < a.M; mb += MT) {
+        float acc[MT][GV_NC];
+#pragma unroll
+        for (int i = 0; i < MT; i++)
+#pragma unroll
+            for (int c = 0; c < GV_NC; c++) acc[i][c] = 0.f;
+        if (a.ln_kind) {
+            // row statistics of the MT input rows (every CTA repeats them: a row is a few KB out of L2)
+            float mean[MT];
+            for (int pass = 0; pass < 2; pass++) {
+                if (pass == 0 && a.ln_kind == 2) {
+#pragma unroll
+                    for (int i = 0; i < MT; i++) mean[i] = 0.f;
+                    continue;                                   // RMSNorm: no mean
+                }
+                float part[MT];
+#pragma unroll
+                for (int i = 0; i < MT; i++) part[i] = 0.f;
+                for (int k = tid * 4; k < a.K; k += 1024) {
+#pragma unroll
+                    for (int i = 0; i < MT; i++) {
+                        if (mb + i < a.M) {
+                            const float4 v = *(const float4 *)(a.x + (mb + i) * a.ldx + k);
+                            if (pass == 0) part[i] += (v.x + v.y) + (v.z + v.w);
+                            else {
+                                float d0 = v.x - mean[i], d1 = v.y - mean[i], d2 = v.z - mean[i], d3 = v.w - mean[i];
+                                part[i] += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < MT; i++) {
+                    float v = part[i];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0) stat[warp][i] = v;
+                }
+                __syncthreads();
+                if (tid < MT) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int w8 = 0; w8 < 8; w8++) v += stat[w8][tid];
+                    v /= (float)a.K;
+                    if (pass == 0) s_mean[tid] = v; else s_rstd[tid] = 1.0f / sqrtf(v + a.ln_eps);
+                }
+                __syncthreads();
+                if (pass == 0) {
+#pragma unroll
+                    for (int i = 0; i < MT; i++) mean[i] = s_mean[i];
+                }
+            }
+        }
+        auto kstep = [&](int k, const float4 *w) {
+            float4 lw = make_float4(1.f, 1.f, 1.f, 1.f), lb = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.ln_kind) {
+                if (a.ln_w) lw = __ldg((const float4 *)(a.ln_w + k));
+                if (a.ln_b) lb = __ldg((const float4 *)(a.ln_b + k));
+            }
+#pragma unroll
+            for (int i = 0; i < MT; i++) {
+                if (mb + i < a.M) {
+                    float4 xv = *(const float4 *)(a.x + (mb + i) * a.ldx + k);
+                    if (a.ln_kind) {   // unfused mul / mul / add like the stand-alone norm kernels
+                        const float mu = a.ln_kind == 1 ? s_mean[i] : 0.f, rs = s_rstd[i];
+                        xv.x = __fadd_rn(__fmul_rn(__fmul_rn(xv.x - mu, rs), lw.x), lb.x);
+                        xv.y = __fadd_rn(__fmul_rn(__fmul_rn(xv.y - mu, rs), lw.y), lb.y);
+                        xv.z = __fadd_rn(__fmul_rn(__fmul_rn(xv.z - mu, rs), lw.z), lb.z);
+                        xv.w = __fadd_rn(__fmul_rn(__fmul_rn(xv.w - mu, rs), lw.w), lb.w);
+                    }
+#pragma unroll
+                    for (int c = 0; c < GV_NC; c++) {
+                        acc[i][c] = fmaf(xv.x, w[c].x, acc[i][c]); acc[i][c] = fmaf(xv.y, w[c].y, acc[i][c]);
+                        acc[i][c] = fmaf(xv.z, w[c].z, acc[i][c]); acc[i][c] = fmaf(xv.w, w[c].w, acc[i][c]);
+                    }
+                }
+            }
+        };
+#pragma unroll
+        for (int p = 0; p < GV_PF; p++) {
+            const int k = tid * 4 + p * 1024;
+            if (k < a.K) kstep(k, wpre[p]);
+        }
+        for (int k = tid * 4 + GV_PF * 1024; k < a.K; k += 1024) {
+            float4 w[GV_NC];
+#pragma unroll
+            for (int c = 0; c < GV_NC; c++) w[c] = __ldg((const float4 *)(wr[c] + k));
+            kstep(k, w);
+        }
+#pragma unroll
+        for (int i = 0; i < MT; i++)
+#pragma unroll
+            for (int c = 0; c < GV_NC; c++) {
+                float v = acc[i][c];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) red[warp][i][c] = v;
+            }
+        __syncthreads();
+        if (tid < MT * GV_NC) {
+            const int i = tid / GV_NC, c = tid % GV_NC;
+            const int64_t m = mb + i; const int n = n0 + c;
+            if (m < a.M && n < a.N) {
+                float v = 0.f;
+#pragma unroll
+                for (int w8 = 0; w8 < 8; w8++) v += red[w8][i][c];
+                if (a.bias) v += a.bias[n];
+                v = act_fn(v, a.act);
+                if (a.res) v += a.res[m * a.ldres + n];
+                a.y[m * a.ldy + n] = v;
+                if (a.y2 && n >= a.y2_col0)
+                    a.y2[m * a.ldy2 + (a.y2_step_d ? (int64_t)(*a.y2_step_d) * a.y2_step : 0) + (n - a.y2_col0)] = v;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 void gemm_simt(const GemmArgs &g) {
     if (g.M <= 0 || g.N <= 0) return;
     if (g.glu) fatal("gemm_simt: fused gated epilogue is a tensor-core engine feature");
@@ -216,10 +365,33 @@ void gemm_simt(const GemmArgs &g) {
     d.y = g.y; d.ldy = g.ldy ? g.ldy : g.N;
     d.M = g.M; d.N = g.N; d.K = g.K; d.act = g.act;
     d.vec = (g.K % 4 == 0) && (d.ldx % 4 == 0) && (((uintptr_t)g.x & 15) == 0) && (((uintptr_t)g.W & 15) == 0);
+    d.ln_kind = g.ln_kind; d.ln_w = g.ln_w; d.ln_b = g.ln_b; d.ln_eps = g.ln_eps;
+    d.y2 = g.y2; d.y2_col0 = g.y2_col0; d.ldy2 = g.ldy2; d.y2_step_d = g.y2_step_d; d.y2_step = g.y2_step;
+    if ((g.ln_kind || g.y2) && !(g.M <= 16 && d.vec)) fatal("gemm_simt: fused norm / second output on a call the GEMV kernel does not take");
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)g.M * g.N * g.K,
                  4.0 * ((double)g.M * g.K + (double)g.N * g.K + (double)g.M * g.N));
     // Few rows: the weights dominate the traffic and a 64x64 / 128x128 tiling would leave most
     // SMs idle, so stream each weight row once through one warp (decode-time GEMV / skinny GEMM).
+    if (g.M <= 16 && d.vec) {
+        // columns per CTA: more of them when there are many, so a CTA moves tens of KB per launch-and-reduce
+        // cycle and a few waves cover the matrix (N = vocabulary: 16 columns; MLP widths: 8)
+        const int nc = (g.M <= 2 && g.N >= 32768) ? 16 : (g.M <= 4 && g.N >= 2048) ? 8 : 4;
+        unsigned grid = (unsigned)cdiv(g.N, nc);
+        if (nc == 16) {
+            if (g.M <= 1) LAUNCH_PDL((k_gemv<1, 16, 1>), grid, 256, 0, d);
+            else LAUNCH_PDL((k_gemv<2, 16, 1>), grid, 256, 0, d);
+        } else if (nc == 8) {
+            if (g.M <= 1) LAUNCH_PDL((k_gemv<1, 8, 2>), grid, 256, 0, d);
+            else if (g.M <= 2) LAUNCH_PDL((k_gemv<2, 8, 1>), grid, 256, 0, d);
+            else LAUNCH_PDL((k_gemv<4, 8, 1>), grid, 256, 0, d);
+        } else {
+            if (g.M <= 1) LAUNCH_PDL((k_gemv<1, 4, 3>), grid, 256, 0, d);
+            else if (g.M <= 2) LAUNCH_PDL((k_gemv<2, 4, 3>), grid, 256, 0, d);
+            else if (g.M <= 4) LAUNCH_PDL((k_gemv<4, 4, 3>), grid, 256, 0, d);
+            else LAUNCH_PDL((k_gemv<8, 4, 2>), grid, 256, 0, d);
+        }
+        return;
+    }
     if (g.M <= 16) {
         unsigned grid = grid1d((int64_t)g.N * 32, 256);
         if (g.M <= 1) LAUNCH(k_gemm_skinny<1>, grid, 256, 0, d);
@@ -235,6 +407,13 @@ void gemm_simt(const GemmArgs &g) {
         dim3 grid((unsigned)cdiv(g.N, 64), (unsigned)cdiv(g.M, 64));
         LAUNCH((k_gemm_tiled<64, 64, 16>), grid, 64, 0, d);
     }
+}
+
+bool gemv_fusable(const GemmArgs &g) {
+    int64_t ldx = g.ldx ? g.ldx : g.K;
+    return g.M <= 16 && g.M > 0 && !g.glu && !g.x_lo && !g.y_lo && (g.K % 4 == 0) && (ldx % 4 == 0) &&
+           (((uintptr_t)g.x & 15) == 0) && (((uintptr_t)g.W & 15) == 0) &&
+           (!g.ln_w || ((uintptr_t)g.ln_w & 15) == 0) && (!g.ln_b || ((uintptr_t)g.ln_b & 15) == 0);
 }
 
 void gemm(const GemmArgs &a) {

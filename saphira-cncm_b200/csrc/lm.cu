@@ -155,6 +155,11 @@ struct LMRun {
     int *ids_d = nullptr, *pos_d = nullptr, *start_np = nullptr, *start_1 = nullptr, *kstart = nullptr;
     int *posmat = nullptr, *lenmat = nullptr, *out_d = nullptr, *last_rows = nullptr;
     double *uni_d = nullptr;
+    // decode loop state on the device: absolute position of the step, this step's picks / packed argmax / uniforms
+    int *step_d = nullptr, *pick_d = nullptr;
+    long long graph_launches = 0;                      // kernel launches one replay of the captured step stands for
+    unsigned long long *amax_d = nullptr;
+    double *uni_cur = nullptr;
 };
 
 void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
@@ -183,6 +188,10 @@ void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
     r.out_d = w.get<int>((size_t)r.B * (n_new > 0 ? n_new : 1));
     r.last_rows = w.get<int>(r.B);
     r.uni_d = w.get<double>((size_t)(n_new > 0 ? n_new : 1) * r.B);
+    r.uni_cur = w.get<double>(r.B);
+    r.amax_d = w.get<unsigned long long>(r.B);
+    r.pick_d = w.get<int>(r.B);
+    r.step_d = w.get<int>(4);
 }
 
 void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
@@ -196,9 +205,13 @@ void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
 
 void lm_head(LMRun &r, const float *h, int64_t rows, float *logits) {
     NcmbLM *m = r.m;
-    apply_norm(h, m->lnfw, m->lnfb, r.bufs.ln, rows, m->C, m->is_qwen ? NORM_RMS : NORM_LAYER, m->is_qwen ? 1e-6f : 1e-5f);
     GemmArgs g;
-    g.x = r.bufs.ln; g.ldx = m->C; g.W = m->wte; g.y = logits; g.ldy = m->V; g.M = rows; g.N = m->V; g.K = m->C;
+    g.x = h; g.ldx = m->C; g.W = m->wte; g.y = logits; g.ldy = m->V; g.M = rows; g.N = m->V; g.K = m->C;
+    g.ln_kind = m->is_qwen ? 2 : 1; g.ln_w = m->lnfw; g.ln_b = m->lnfb; g.ln_eps = m->is_qwen ? 1e-6f : 1e-5f;
+    if (!gemv_fusable(g)) {        // many rows: stand-alone norm, tensor-core GEMM
+        apply_norm(h, m->lnfw, m->lnfb, r.bufs.ln, rows, m->C, m->is_qwen ? NORM_RMS : NORM_LAYER, m->is_qwen ? 1e-6f : 1e-5f);
+        g.x = r.bufs.ln; g.ln_kind = 0;
+    }
     gemm(g);
 }
 
@@ -221,22 +234,50 @@ void lm_prefill(LMRun &r) {
     }
 }
 
-// one new token per row at absolute position `pos`
-void lm_decode_step(LMRun &r, const int *ids_d, int pos) {
+// token + position embedding of the decode step whose absolute position sits in *step_d
+__global__ void k_lm_embed_dec(const float *__restrict__ wte, const float *__restrict__ wpe, const int *__restrict__ ids,
+                               const int *__restrict__ posmat, const int *__restrict__ step_d, int pos_base, int B, int C,
+                               float *__restrict__ x) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int *pos = posmat + (int64_t)(*step_d + pos_base) * B;
+    int64_t n = (int64_t)B * C;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int b = (int)(i / C), c = (int)(i % C);
+        float v = wte[(int64_t)ids[b] * C + c];
+        if (wpe) v = __fadd_rn(v, wpe[(int64_t)pos[b] * C + c]);
+        x[i] = v;
+    }
+}
+
+// One new token per row. *r.step_d = v counts the tokens finalised so far (k_lm_finish_step advances it); this
+// step's token sits at absolute position np + v - 1, and every per-step array is indexed through the
+// counter (bases shifted by np - 1 steps), so the same launches -- eagerly or replayed from one captured
+// CUDA graph -- serve every step.
+void lm_decode_step(LMRun &r, const int *ids_d) {
     NcmbLM *m = r.m;
     int kvd = m->nkv * m->hd;
-    lm_embed(r, ids_d, r.posmat + (size_t)pos * r.B, r.B);
+    {
+        int64_t n = (int64_t)r.B * m->C, g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 8;
+        ProfScope ps(NCMB_K_ELEM, 0, (double)n * 8);
+        LAUNCH_PDL(k_lm_embed_dec, (unsigned)(g > cap ? cap : g), 256, 0, m->wte, m->is_qwen ? (const float *)nullptr : m->wpe, ids_d,
+               r.posmat, r.step_d, r.np - 1, r.B, m->C, r.x);
+    }
     AttnPlan p;
-    p.q_start = r.start_1; p.k1_start = r.kstart; p.k1_len = r.lenmat + (size_t)pos * r.B;
+    p.step_d = r.step_d;
+    p.q_start = r.start_1; p.k1_start = r.kstart;
+    const int64_t sh = r.np - 1;                               // counter value v <-> absolute position np - 1 + v
+    p.k1_len = r.lenmat + sh * r.B; p.k1_len_step = r.B;
     p.ldk1 = 2 * kvd;
-    p.rows = r.B; p.max_q = 1;
-    p.pos = r.posmat + (size_t)pos * r.B;
+    p.rows = r.B; p.max_q = 1; p.max_k1 = r.cap; p.k1_total = (int64_t)r.B * r.cap;
+    p.pos = r.posmat + sh * r.B; p.pos_step = r.B;
     if (m->is_qwen) { p.cos_t = m->cosb; p.sin_t = m->sinb; }
-    p.total_q = r.B; p.avg_keys = pos + 1;
+    p.total_q = r.B; p.avg_keys = (r.np + r.cap) / 2.0;
     p.kv_pitch = 2 * kvd; p.kv_rows_per_seq = 1; p.kv_seq_pitch = (int64_t)r.cap * 2 * kvd;
+    p.kv_store_step = 2 * kvd;
     for (int li = 0; li < m->NL; li++) {
         p.k1 = r.kv[li]; p.v1 = r.kv[li] + kvd;
-        p.kv_store = r.kv[li] + (size_t)pos * 2 * kvd;
+        p.kv_store = r.kv[li] + sh * 2 * kvd;
         run_block(r.x, r.B, m->C, m->H, m->nkv, m->blocks[li], r.bufs, p);
     }
 }
@@ -265,21 +306,70 @@ void lm_setup(LMRun &r, const int *prompts, int n_new, bool all_logits) {
     upload(r.last_rows, lr.data(), lr.size() * 4);
 }
 
-void lm_sample(LMRun &r, float temp, int top_k, float top_p, int step, int n_new) {
-    NcmbLM *m = r.m;
-    SampleArgs s{};
-    s.logits = r.logits; s.Bn = r.B; s.Lc = 1; s.V = m->V; s.uncond_off = 0; s.cfg_w = 0;
-    s.temp = temp; s.top_k = top_k; s.top_p = top_p;
-    s.freq = 0; s.mu = 0; s.adj_a = 0; s.adj_w = 0; s.adj_d = 1;
-    s.uniforms = temp > 0 ? r.uni_d + (size_t)step * r.B : nullptr;
-    s.out = r.out_d; s.out_stride = n_new; s.out_off = step;
-    s.scratch = r.samp_scr;
-    sample_rows(s);
+// greedy pick over a long vocabulary row on many CTAs: block-local first-index argmax, then one atomicMax per
+// block on (order-preserving value bits << 32 | ~index), so equal values resolve to the smallest index
+__global__ void __launch_bounds__(256) k_argmax_packed(const float *__restrict__ logits, int V, int chunk,
+                                                      unsigned long long *__restrict__ amax) {
+    __shared__ unsigned long long red[256];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y, v0 = blockIdx.x * chunk, v1 = min(V, v0 + chunk);
+    const float *row = logits + (size_t)b * V;
+    unsigned long long best = 0;
+    for (int v = v0 + threadIdx.x; v < v1; v += 256) {
+        unsigned u = __float_as_uint(row[v]);
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        unsigned long long p = ((unsigned long long)u << 32) | (0xffffffffu - (unsigned)v);
+        if (p > best) best = p;
+    }
+    red[threadIdx.x] = best;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s && red[threadIdx.x + s] > red[threadIdx.x]) red[threadIdx.x] = red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && red[0]) atomicMax(amax + b, red[0]);
 }
 
-__global__ void k_take_col(const int *__restrict__ src, int stride, int col, int n, int *__restrict__ dst) {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = src[(size_t)i * stride + col];
+// closes a step: token s = *step_d of every row goes to out[b][s] and to ids[b] (the next step's input), the
+// next step's uniforms are staged, the packed argmax is cleared, and the counter advances
+__global__ void k_lm_finish_step(const int *__restrict__ pick, unsigned long long *__restrict__ amax, int greedy, int B, int n_new,
+                                 int *__restrict__ out, int *__restrict__ ids, const double *__restrict__ uni, double *__restrict__ uni_cur,
+                                 int *__restrict__ step_d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = *step_d;
+    for (int b = threadIdx.x; b < B; b += blockDim.x) {
+        int t = greedy ? (int)(0xffffffffu - (unsigned)(amax[b] & 0xffffffffull)) : pick[b];
+        out[(size_t)b * n_new + s] = t;
+        ids[b] = t;
+        if (greedy) amax[b] = 0;
+        else if (s + 1 < n_new) uni_cur[b] = uni[(size_t)(s + 1) * B + b];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *step_d = s + 1;
+}
+
+void lm_sample(LMRun &r, float temp, int top_k, float top_p, int n_new) {
+    NcmbLM *m = r.m;
+    const int greedy = !(temp > 0.f);
+    if (greedy) {
+        const int chunk = 2048;
+        dim3 grid((unsigned)cdiv(m->V, chunk), (unsigned)r.B);
+        ProfScope ps(NCMB_K_SAMPLE, 0, (double)r.B * m->V * 4);
+        LAUNCH_PDL(k_argmax_packed, grid, 256, 0, r.logits, m->V, chunk, r.amax_d);
+    } else {
+        SampleArgs s{};
+        s.logits = r.logits; s.Bn = r.B; s.Lc = 1; s.V = m->V; s.uncond_off = 0; s.cfg_w = 0;
+        s.temp = temp; s.top_k = top_k; s.top_p = top_p;
+        s.freq = 0; s.mu = 0; s.adj_a = 0; s.adj_w = 0; s.adj_d = 1;
+        s.uniforms = r.uni_cur;
+        s.out = r.pick_d; s.out_stride = 1; s.out_off = 0;
+        s.scratch = r.samp_scr;
+        sample_rows(s);
+    }
+    ProfScope ps(NCMB_K_SAMPLE, 0, 0);
+    LAUNCH_PDL(k_lm_finish_step, 1, 256, 0, r.pick_d, r.amax_d, greedy, r.B, n_new, r.out_d, r.ids_d, r.uni_d, r.uni_cur, r.step_d);
 }
 
 } // namespace
@@ -303,16 +393,34 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
         }
         upload(r.uni_d, u.data(), u.size() * 8);
     }
+    CUDA_CHECK(cudaMemsetAsync(r.step_d, 0, 4 * sizeof(int), stream()));
+    CUDA_CHECK(cudaMemsetAsync(r.amax_d, 0, (size_t)B * 8, stream()));
+    if (temp > 0) CUDA_CHECK(cudaMemcpyAsync(r.uni_cur, r.uni_d, (size_t)B * 8, cudaMemcpyDeviceToDevice, stream()));
     lm_prefill(r);
     embed_rows(r.x, r.last_rows, r.last, B, m->C);           // hidden state of each row's last prompt token
     lm_head(r, r.last, B, r.logits);
     std::vector<int> col(B);
     std::vector<char> done(B, 0);
     int produced = 0;
+    // Steps without a host decision (no EOS to watch) are replayed from one CUDA graph: the first decode step
+    // runs eagerly (it sizes every workspace), the second is captured, the rest are graph launches. The work
+    // moves to a stream of its own for that, because the caller's stream may be the legacy default stream,
+    // which cannot be captured.
+    static const bool graphs_ok = !getenv("NCM_B200_NO_GRAPH");
+    const bool use_graph = graphs_ok && eos < 0 && n_new >= 4 && !prof_enabled();
+    cudaStream_t user = stream(), gs = nullptr;
+    cudaEvent_t ev = nullptr;
+    cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr;
+    if (use_graph) {
+        CUDA_CHECK(cudaStreamCreateWithFlags(&gs, cudaStreamNonBlocking));
+        CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        CUDA_CHECK(cudaEventRecord(ev, user));
+        CUDA_CHECK(cudaStreamWaitEvent(gs, ev, 0));
+        ctx().stream = gs;
+    }
     for (int s = 0; s < n_new; s++) {
-        lm_sample(r, temp, top_k, top_p, s, n_new);
+        if (s == 0 || !gexec) lm_sample(r, temp, top_k, top_p, n_new);       // (inside the graph for replayed steps)
         produced = s + 1;
-        LAUNCH(k_take_col, (unsigned)cdiv(B, 128), 128, 0, r.out_d, n_new, s, B, r.ids_d);
         if (eos >= 0) {
             mem_d2h(col.data(), r.ids_d, (size_t)B * 4);
             bool all = true;
@@ -320,8 +428,29 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
             if (all) break;
         }
         if (s + 1 == n_new) break;
-        lm_decode_step(r, r.ids_d, np + s);
+        if (gexec) { CUDA_CHECK(cudaGraphLaunch(gexec, gs)); ctx().launches += r.graph_launches; continue; }
+        const bool capture = use_graph && s == 1;
+        long long l0 = ctx().launches;
+        if (capture) CUDA_CHECK(cudaStreamBeginCapture(gs, cudaStreamCaptureModeThreadLocal));
+        lm_decode_step(r, r.ids_d);
         lm_head(r, r.x, B, r.logits);
+        if (capture) {
+            lm_sample(r, temp, top_k, top_p, n_new);
+            CUDA_CHECK(cudaStreamEndCapture(gs, &graph));
+            CUDA_CHECK(cudaGraphInstantiate(&gexec, graph, 0));
+            r.graph_launches = ctx().launches - l0;
+            CUDA_CHECK(cudaGraphLaunch(gexec, gs));                      // capturing did not run the step: run it now
+        }
+    }
+    if (use_graph) {
+        CUDA_CHECK(cudaEventRecord(ev, gs));
+        CUDA_CHECK(cudaStreamWaitEvent(user, ev, 0));
+        ctx().stream = user;
+        CUDA_CHECK(cudaStreamSynchronize(user));
+        if (gexec) CUDA_CHECK(cudaGraphExecDestroy(gexec));
+        if (graph) CUDA_CHECK(cudaGraphDestroy(graph));
+        CUDA_CHECK(cudaEventDestroy(ev));
+        CUDA_CHECK(cudaStreamDestroy(gs));
     }
     std::vector<int> tmp((size_t)B * n_new);
     mem_d2h(tmp.data(), r.out_d, tmp.size() * 4);

@@ -94,6 +94,7 @@ void prof_begin(int klass, double flops, double bytes) {
     p.cur = ProfRec{klass, flops, bytes, p.get(), p.get()};
     CUDA_CHECK(cudaEventRecord(p.cur.a, stream()));
 }
+bool prof_enabled() { return prof().on; }
 void prof_end() {
     Prof &p = prof();
     if (!p.on) return;

@@ -14,6 +14,7 @@
 // generator keyed by (seed, global row, level, position).
 #include "common.cuh"
 
+#include <cub/device/device_radix_sort.cuh>
 #include <cub/device/device_segmented_radix_sort.cuh>
 #include <vector>
 
@@ -318,10 +319,17 @@ static void sample_rows_large(const SampleArgs &a, int keep) {
               "without CFG or penalties only; set top_k <= %d", SM_MAXKEEP, a.top_k, a.V, SM_MAXKEEP);
     static Workspace ws;
     const int64_t n = (int64_t)a.Bn * a.V;
+    // Few rows: one device-wide radix sort per row (the segmented sort gives each row a single CTA, which
+    // takes ~1 ms for a 150 K vocabulary); many rows: one segmented sort over all of them.
+    const bool per_row = a.Bn <= 8;
     size_t temp_bytes = 0;
-    cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
-                                                       (const int *)nullptr, (int *)nullptr, n, a.Bn, (const int *)nullptr,
-                                                       (const int *)nullptr, 0, 32, stream());
+    if (per_row)
+        cub::DeviceRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
+                                                  (const int *)nullptr, (int *)nullptr, a.V, 0, 32, stream());
+    else
+        cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
+                                                           (const int *)nullptr, (int *)nullptr, n, a.Bn, (const int *)nullptr,
+                                                           (const int *)nullptr, 0, 32, stream());
     size_t need = (size_t)n * 16 + (size_t)(a.Bn + 1) * 4 + temp_bytes + 4096;
     if (need > ws.cap) ws.reserve(need);
     ws.reset();
@@ -329,17 +337,32 @@ static void sample_rows_large(const SampleArgs &a, int keep) {
     int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
     int *offs = ws.get<int>(a.Bn + 1);
     void *temp = ws.alloc(temp_bytes);
+    // segment offsets b * V: uploaded only when the shape or the buffer changes, so a decode step that
+    // repeats the call (possibly inside a stream capture) issues no host copy
     static std::vector<int> hoffs;
-    hoffs.resize(a.Bn + 1);
-    for (int b = 0; b <= a.Bn; b++) hoffs[b] = b * a.V;
-    upload(offs, hoffs.data(), hoffs.size() * 4);
+    static int last_Bn = -1, last_V = -1; static const int *last_offs = nullptr;
+    if (!per_row && (last_Bn != a.Bn || last_V != a.V || last_offs != offs)) {
+        hoffs.resize(a.Bn + 1);
+        for (int b = 0; b <= a.Bn; b++) hoffs[b] = b * a.V;
+        upload(offs, hoffs.data(), hoffs.size() * 4);
+        CUDA_CHECK(cudaStreamSynchronize(stream()));
+        last_Bn = a.Bn; last_V = a.V; last_offs = offs;
+    }
     ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
     int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
     LAUNCH(k_sort_prep, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
-    cudaError_t e = cub::DeviceSegmentedRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, n, a.Bn,
-                                                                        offs, offs + 1, 0, 32, stream());
-    if (e != cudaSuccess) fatal("segmented sort failed: %s", cudaGetErrorString(e));
-    ctx().launches += 4;
+    cudaError_t e = cudaSuccess;
+    if (per_row) {
+        for (int b = 0; b < a.Bn && e == cudaSuccess; b++)
+            e = cub::DeviceRadixSort::SortPairsDescending(temp, temp_bytes, k_in + (size_t)b * a.V, k_out + (size_t)b * a.V,
+                                                          i_in + (size_t)b * a.V, i_out + (size_t)b * a.V, a.V, 0, 32, stream());
+        ctx().launches += 7 * a.Bn;
+    } else {
+        e = cub::DeviceSegmentedRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, n, a.Bn,
+                                                               offs, offs + 1, 0, 32, stream());
+        ctx().launches += 4;
+    }
+    if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
     LAUNCH(k_pick_sorted, (unsigned)a.Bn, SL_THREADS, 0, k_out, i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed, a.rng_row0,
            a.rng_level, a.out, a.out_stride, a.out_off);
 }

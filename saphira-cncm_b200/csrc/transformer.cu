@@ -34,7 +34,9 @@ void apply_norm(const float *x, const float *w, const float *b, float *y, int64_
 }
 
 __global__ void k_kv_store(const float *__restrict__ src, int64_t ldsrc, float *__restrict__ dst, int64_t pitch,
-                           int rows_per_seq, int64_t seq_pitch, int64_t ntok, int width4) {
+                           int rows_per_seq, int64_t seq_pitch, int64_t ntok, int width4,
+                           const int *__restrict__ step_d, int64_t step_stride) {
+    if (step_d) dst += (int64_t)(*step_d) * step_stride;       // decode steps replayed from one graph
     int64_t total = ntok * width4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t tok = i / width4; int c = (int)(i % width4);
@@ -69,20 +71,35 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         lw.reset();
         ln_lo = lw.get<float>((size_t)ntok * C); ctx_lo = lw.get<float>((size_t)ntok * C); h_lo = lw.get<float>((size_t)ntok * w.Hh);
     }
-    apply_norm_split(x, w.ln1w, w.ln1b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
+    // Few rows (decode steps): the projections run on the GEMV kernel, which normalises its input rows on the
+    // fly and can write the K|V columns straight into the cache -- three launches fewer per block.
     GemmArgs g;
-    g.x_fmt = fmt;
-    g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.W = w.qkvw; g.bias = w.qkvb; g.y = b.qkv; g.ldy = Wq; g.M = ntok; g.N = Wq; g.K = C;
+    g.x = x; g.ldx = C; g.W = w.qkvw; g.bias = w.qkvb; g.y = b.qkv; g.ldy = Wq; g.M = ntok; g.N = Wq; g.K = C;
+    g.ln_kind = w.norm == NORM_RMS ? 2 : 1; g.ln_w = w.ln1w; g.ln_b = w.ln1b; g.ln_eps = w.norm == NORM_RMS ? 1e-6f : w.eps;
+    static const bool fuse_small = !getenv("NCM_B200_NO_GEMV_FUSE");
+    const bool small = fuse_small && !split && gemv_fusable(g);
+    bool kv_written = false;
+    if (small) {
+        if (p.kv_store && !w.qnw && !p.cos_t && p.kv_rows_per_seq == 1) {
+            g.y2 = p.kv_store; g.y2_col0 = C; g.ldy2 = p.kv_seq_pitch; g.y2_step_d = p.step_d; g.y2_step = p.kv_store_step;
+            kv_written = true;
+        }
+    } else {
+        apply_norm_split(x, w.ln1w, w.ln1b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
+        g.ln_kind = 0;
+        g.x_fmt = fmt;
+        g.x = b.ln; g.x_lo = ln_lo;
+    }
     gemm(g);
     float *qp = b.qkv, *kp = b.qkv + C, *vp = b.qkv + C + kvd;
-    qk_post(qp, Wq, H, kp, Wq, nkv, hd, ntok, w.qnw, w.knw, p.cos_t, p.sin_t, p.pos);
-    if (p.kv_store) {
+    qk_post(qp, Wq, H, kp, Wq, nkv, hd, ntok, w.qnw, w.knw, p.cos_t, p.sin_t, p.pos, p.step_d, p.pos_step);
+    if (p.kv_store && !kv_written) {
         int width4 = 2 * kvd / 4;
         int64_t n = ntok * width4;
         int64_t gsz = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
         ProfScope ps(NCMB_K_ELEM, 0, (double)ntok * 2 * kvd * 8);
         LAUNCH(k_kv_store, (unsigned)(gsz > cap ? cap : gsz), 256, 0, kp, (int64_t)Wq, p.kv_store, p.kv_pitch,
-               p.kv_rows_per_seq, p.kv_seq_pitch, ntok, width4);
+               p.kv_rows_per_seq, p.kv_seq_pitch, ntok, width4, p.step_d, p.kv_store_step);
     }
     if (p.kv_only) return;
     AttnArgs a;
@@ -97,6 +114,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     a.causal = p.causal; a.causal_off = p.causal_off; a.window = p.window;
     a.total_q = p.total_q; a.avg_keys = p.avg_keys;
     a.max_k1 = p.max_k1; a.max_k2 = p.self_is_k2 ? p.max_q : 0;
+    a.step_d = p.step_d; a.k1_len_step = p.k1_len_step;
     a.q_total = ntok; a.k1_total = p.k1 ? p.k1_total : ntok; a.k2_total = p.self_is_k2 ? ntok : 0;
     attention(a);
     // x += ctx Wo^T + bo
@@ -104,10 +122,16 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     g.x_fmt = fmt;
     g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
     gemm(g);
-    apply_norm_split(x, w.ln2w, w.ln2b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
     g = GemmArgs();
-    g.x_fmt = fmt; g.y_fmt = fmt;
-    g.x = b.ln; g.x_lo = ln_lo; g.ldx = C; g.M = ntok; g.K = C;
+    g.ldx = C; g.M = ntok; g.K = C;
+    if (small) {
+        g.x = x;
+        g.ln_kind = w.norm == NORM_RMS ? 2 : 1; g.ln_w = w.ln2w; g.ln_b = w.ln2b; g.ln_eps = w.norm == NORM_RMS ? 1e-6f : w.eps;
+    } else {
+        apply_norm_split(x, w.ln2w, w.ln2b, b.ln, ln_lo, ntok, C, w.norm, w.eps, fmt);
+        g.x_fmt = fmt; g.y_fmt = fmt;
+        g.x = b.ln; g.x_lo = ln_lo;
+    }
     if (w.gated) {
         GemmArgs t = g;
         t.W = w.fcw_il; t.bias = w.fcb_il; t.N = 2 * w.Hh; t.glu = 1; t.act = w.act; t.y = b.h; t.ldy = w.Hh;

@@ -88,6 +88,39 @@ def test_tensor_core_attention_matches_cuda_core_and_float64(cuda, name):
     assert not np.isnan(got[1]).any()
 
 
+DECODE_CASES = {
+    # one query per row against a cache of ragged lengths: (cache lengths, H, Hkv)
+    "gpt2_like_12_heads": ([1, 31, 32, 33, 300, 1000], 12, 12),
+    "qwen_like_7_heads_per_kv": ([5, 64, 513, 2048], 14, 2),
+    "single_head_group_of_4": ([129, 7], 4, 1),
+}
+
+
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name):
+    lens, H, Hkv = DECODE_CASES[name]
+    rng = np.random.default_rng(sum(map(ord, name)))
+    rows = len(lens)
+    qs = np.arange(rows + 1, dtype=np.int32)
+    ks = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    q = rng.standard_normal((rows, H * 64)).astype(np.float32)
+    kv = rng.standard_normal((ks[-1], 2 * Hkv * 64)).astype(np.float32)
+    want = _want(q, kv, None, qs, ks, None, H, Hkv, 0, 0)
+    qd, kd = cuda.to_backend(q), cuda.to_backend(kv)
+    got = {}
+    for engine in (0, 2):
+        od = cuda.alloc(q.size)
+        rc = cuda.ncmb_attention_check(qd, kd, None, od, qs.ctypes.data, ks.ctypes.data, None, rows, H, Hkv, 0, 0, engine)
+        assert rc == 0, (name, engine, rc)
+        got[engine] = cuda.to_host(od, q.shape)
+    assert np.abs(got[0] - want).max() < 4e-6
+    assert np.abs(got[2] - want).max() < 4e-6
+    # twice in a row: the kernel's completion counters must be back at zero after each launch
+    od = cuda.alloc(q.size)
+    assert cuda.ncmb_attention_check(qd, kd, None, od, qs.ctypes.data, ks.ctypes.data, None, rows, H, Hkv, 0, 0, 2) == 0
+    assert np.array_equal(cuda.to_host(od, q.shape), got[2])
+
+
 def test_shapes_outside_the_tensor_core_kernel_are_reported_not_rerouted(cuda):
     # 480 padded keys + 64 output columns do not fit the 512 tensor-memory columns
     qs = np.array([0, 64], np.int32)
