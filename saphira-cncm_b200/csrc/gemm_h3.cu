@@ -21,12 +21,15 @@
 
 namespace ncmb {
 
-constexpr int H3_BM = 128, H3_BN = 128, H3_BK = 64;      // BK halfs = 128 bytes = one swizzle row
-constexpr int H3_STAGES = 3;
+constexpr int H3_BM = 128, H3_BK = 64;                   // BK halfs = 128 bytes = one swizzle row
+// Tile widths: 128 columns for large problems; 32 columns when there are few rows (batched decode steps,
+// M <= 128), so that N / 32 CTAs stream the weights instead of N / 128.
+constexpr int h3_stages(int BN) { return BN >= 128 ? 3 : 4; }
 constexpr int H3_EPI_WARPS = 8;                         // two per TMEM lane quadrant, 64 columns each
 constexpr int H3_THREADS = 64 + 32 * H3_EPI_WARPS;
 constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand tile: 16 KB
-constexpr int H3_STAGE = 4 * H3_TILE;                    // x1 | x2 | W1 | W2
+constexpr int h3_wtile(int BN) { return BN * H3_BK * 2; }  // one BN-row weight tile
+constexpr int h3_stage(int BN) { return 2 * H3_TILE + 2 * h3_wtile(BN); }   // x1 | x2 | W1 | W2
 
 // instruction descriptor: D fp32, A/B fp16, both K-major, M x N tile
 __host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N) {
@@ -38,12 +41,14 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+template <int H3_BN>
 __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
                                                        const __grid_constant__ CUtensorMap tmX2,
                                                        const __grid_constant__ CUtensorMap tmW1,
                                                        const __grid_constant__ CUtensorMap tmW2,
                                                        const __grid_constant__ CUtensorMap tmY,
                                                        TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
+    constexpr int H3_STAGES = h3_stages(H3_BN), H3_STAGE = h3_stage(H3_BN), H3_WTILE = h3_wtile(H3_BN);
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
@@ -63,8 +68,8 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW1) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW2) : "memory");
     }
-    if (warp == 1) {   // 2 accumulator pairs x (main, cross) x 128 columns = all 512 columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    if (warp == 1) {   // 2 accumulator pairs x (main, cross) x BN columns (BN = 128: all 512 columns)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(4 * H3_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -87,7 +92,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                     tma_load_2d(dst, &tmX1, kb * H3_BK, m0, bar);
                     tma_load_2d(dst + H3_TILE, &tmX2, kb * H3_BK, m0, bar);
                     tma_load_2d(dst + 2 * H3_TILE, &tmW1, kb * H3_BK, n0, bar);
-                    tma_load_2d(dst + 3 * H3_TILE, &tmW2, kb * H3_BK, n0, bar);
+                    tma_load_2d(dst + 2 * H3_TILE + H3_WTILE, &tmW2, kb * H3_BK, n0, bar);
                     armed = kbg + 1;
                 }
             }
@@ -114,7 +119,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                     tc_fence_after();
                     const uint32_t base = smem_u32(smem + s * H3_STAGE);
                     const uint64_t x1 = umma_desc_sw128(base), x2 = umma_desc_sw128(base + H3_TILE);
-                    const uint64_t w1 = umma_desc_sw128(base + 2 * H3_TILE), w2 = umma_desc_sw128(base + 3 * H3_TILE);
+                    const uint64_t w1 = umma_desc_sw128(base + 2 * H3_TILE), w2 = umma_desc_sw128(base + 2 * H3_TILE + H3_WTILE);
 #pragma unroll
                     for (int k = 0; k < H3_BK / 16; k++) {    // 16 halfs (32 bytes) per MMA: advance the start address
                         const uint64_t o = (uint64_t)(k * 2);
@@ -129,22 +134,25 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         }
     } else {
         const int q = warp & 3;                              // TMEM lane quadrant this warp may read
-        const int ch = (warp - 2) >> 2;                      // which 64-column half of the tile this warp drains
+        const int ch = (warp - 2) >> 2;                      // which half of the tile's 32-column chunks this warp drains
+        constexpr int NCH = H3_BN / 64;                      // chunks per warp (BN = 32: the first four warps take the one chunk)
+        constexpr int NCH1 = NCH > 0 ? NCH : 1;
+        const bool has_cols = NCH > 0 || ch == 0;
         int it = 0;
         bool ok = true;
         const bool glu_fast = tc_glu_silu_h16(ep);
         unsigned char *stage = stage0 + (warp - 2) * 4096;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
             const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
-            const int n0 = (t % tiles_n) * H3_BN + ch * 64;
+            const int n0 = (t % tiles_n) * H3_BN + ch * (H3_BN / 2);
             const int64_t m = (int64_t)(t / tiles_n) * H3_BM + q * 32 + lane;
             // the residual of this thread's 64 outputs is requested before the accumulators are waited for,
             // so its latency runs under the tile's MMAs
-            float4 resv[16];
-            bool pre[2];
+            float4 resv[8 * NCH1];
+            bool pre[NCH1];
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                pre[c] = tc_residual_prefetchable(ep, m, n0, c * 32);
+            for (int c = 0; c < NCH1; c++) {
+                pre[c] = has_cols && tc_residual_prefetchable(ep, m, n0, c * 32);
                 if (pre[c]) {
                     const float4 *rr = (const float4 *)(ep.res + m * ep.ldres + n0 + c * 32);
 #pragma unroll
@@ -154,9 +162,10 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
             ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 23);
             tc_fence_after();
             if (!ok) break;
-            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN + ch * 64);
+            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN + ch * (H3_BN / 2));
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
+            for (int c = 0; c < NCH1; c++) {
+                if (!has_cols) break;
                 uint32_t r[32], x[32];
                 tmem_ld32_issue(trow + (uint32_t)(c * 32), r);
                 tmem_ld32_issue(trow + (uint32_t)(H3_BN + c * 32), x);
@@ -180,7 +189,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4 * H3_BN) : "memory");
     }
 }
 
@@ -267,26 +276,35 @@ void gemm_h3(const GemmArgs &a) {
         split_h16(a.W, a.K, p1, p2, a.N, a.K);
         w1 = p1; w2 = p2;
     }
+    // small problems (decode steps, the first NCP levels): 128-wide tiles would leave most SMs idle, and the
+    // call is bound by streaming W once -- narrow tiles put four times as many CTAs on it
+    static const bool narrow_ok = !getenv("NCM_B200_NO_BN32");
+    const bool narrow = narrow_ok && cdiv(a.N, 128) * cdiv(a.M, H3_BM) * 2 <= ctx().sm_count;
+    const int bn = narrow ? 32 : 128;
     const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
-    const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, H3_BN), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, H3_BN);
+    const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
     // fp32 results leave through TMA stores when the rows keep 16-byte strides
     ep.tma_store = (!a.glu && !a.y_lo && (ep.ldy & 3) == 0 && !getenv("NCM_B200_NO_TMA_STORE")) ? 1 : 0;
     const CUtensorMap *my = ep.tma_store ? tc_get_map(a.y, a.M, a.N, ep.ldy, 32, false) : mx1;
-    constexpr size_t smem = 1024 + (size_t)H3_STAGES * H3_STAGE + H3_EPI_WARPS * 4096 + (2 * H3_STAGES + 4) * 8 + 16;
-    static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");
-    static bool set = false;
-    if (!set) {
-        CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        set = true;
-    }
-    int tiles_n = (int)cdiv(a.N, H3_BN);
+    int tiles_n = (int)cdiv(a.N, bn);
     int64_t tiles = (int64_t)tiles_n * cdiv(a.M, H3_BM);
     if (tiles > 0x7fffffff) fatal("gemm_h3: too many tiles");
     int grid = (int)(tiles < ctx().sm_count ? tiles : ctx().sm_count);     // persistent: one CTA per SM
     int num_kb = (int)cdiv(a.K, H3_BK);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
-    LAUNCH(k_gemm_h3, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
+    if (narrow) {
+        constexpr size_t smem = 1024 + (size_t)h3_stages(32) * h3_stage(32) + H3_EPI_WARPS * 4096 + (2 * h3_stages(32) + 4) * 8 + 16;
+        static bool set = false;
+        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+        LAUNCH(k_gemm_h3<32>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
+    } else {
+        constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
+        static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");
+        static bool set = false;
+        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+        LAUNCH(k_gemm_h3<128>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
+    }
 }
 
 } // namespace ncmb
