@@ -1,8 +1,9 @@
 // Tensor-core attention for head dim 64 on sm_100a (tcgen05 + TMEM + TMA).
 //
 // One CTA (512 threads) per (sequence row, head, 128-query tile):
-//   S = Q K^T   tcgen05.mma.kind::tf32 into tensor memory, keys in blocks of <= 128 columns; the
-//               first two key blocks and the query tile are fetched together by TMA
+//   S = Q K^T   tcgen05.mma.kind::tf32 into tensor memory; the query tile and ALL keys of the row (up to 288
+//               padded keys: a 256-token prefix plus a 32-token level) are fetched together by TMA and stay
+//               resident, so the score phase is one load, one split pass and one batch of MMAs
 //   softmax     four threads per query row (each takes a quarter of the columns) read the scores with
 //               tcgen05.ld; all keys of a row are resident, so the row maximum is known before
 //               any exponential is taken and no rescaling is needed
@@ -15,20 +16,24 @@
 // Key rows come from up to two segments (cached prefix, tokens of the current pass); each
 // segment is padded to a multiple of 32 score columns and the padding is masked in the softmax.
 //
-// Shared memory, three 64 KB regions reused between the two phases:
-//   R0  Q hi | Q lo                      then  V^T hi/lo, two buffers
-//   R1  even key blocks, K hi | K lo     then  ring of eight raw V chunks
-//   R2  odd key blocks,  K hi | K lo     then  P hi/lo, two buffers
+// Shared memory, reused between the two phases:
+//   QA  (64 KB)   Q hi | Q lo                                 then  V^T hi/lo, two buffers (32 KB)
+//   KA  (144 KB)  K hi atoms | K lo atoms, 288 rows each      then  raw V, one 8 KB slot per 32-key chunk (72 KB)
+//                                                                   and P hi/lo, two buffers (64 KB)
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "split.cuh"
 
 namespace ncmb {
 
-constexpr int ATC_THREADS = 512;          // four threads per query row, eight score columns of a chunk each
-constexpr int ATC_OCOL = 448;            // TMEM column of the output accumulator; scores use columns [0, 448)
-constexpr int ATC_VSLOTS = 8;
-constexpr int ATC_SMEM = 1024 + 3 * 65536 + ATC_THREADS * 4 + 32 * 8 + 64;
+constexpr int ATC_THREADS = 512;          // softmax team: four threads per query row, eight score columns of a chunk each
+constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the PV MMAs while the team works on the next chunk
+constexpr int ATC_MAXK = 288;            // padded keys per row the kernel keeps resident
+constexpr int ATC_OCOL = 288;            // TMEM column of the output accumulator; scores use columns [0, 288)
+constexpr int ATC_VSLOTS = ATC_MAXK / 32;
+constexpr int ATC_KATOM = ATC_MAXK * 128;                    // one 32-column atom of all key rows: 36 KB
+constexpr int ATC_QA = 65536, ATC_KA = 4 * ATC_KATOM;        // 64 KB + 144 KB
+constexpr int ATC_SMEM = 1024 + ATC_QA + ATC_KA + ATC_THREADS * 4 + 32 * 8 + 64;
 
 struct AttnTcDev {
     float *out; float *out_lo; int64_t ldo; int out_fmt;
@@ -56,11 +61,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r) {
+// without the wait: issue all loads of a row, then tmem_ld_wait() once
+__device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t *r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 // in place: tile -> hi, and lo into the twin buffer; n4 float4 elements, layout-agnostic
 __device__ __forceinline__ void split_tile(unsigned char *hi, unsigned char *lo, int n4, int tid) {
@@ -83,20 +88,23 @@ struct BoundedWaiter {
     }
 };
 
-__global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_constant__ CUtensorMap mq,
+__global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constant__ CUtensorMap mq,
                                                              const __grid_constant__ CUtensorMap mk1,
                                                              const __grid_constant__ CUtensorMap mk2,
                                                              AttnTcDev a) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *R0 = smem, *R1 = smem + 65536, *R2 = smem + 131072;
-    float *xch = (float *)(smem + 196608);                       // one float per thread: row max / row sum exchange
+    unsigned char *R0 = smem;                                    // QA
+    unsigned char *KA = smem + ATC_QA;                           // K hi atom 0 | hi atom 1 | lo atom 0 | lo atom 1
+    unsigned char *R1 = KA;                                      // phase 2: raw V slots
+    unsigned char *R2 = KA + ATC_VSLOTS * 8192;                  // phase 2: P buffers
+    float *xch = (float *)(smem + ATC_QA + ATC_KA);                       // one float per thread: row max / row sum exchange
     uint64_t *bars = (uint64_t *)(xch + ATC_THREADS);
     uint32_t *tmem_slot = (uint32_t *)(bars + 32);
-    // barriers: 0 Q | 1,2 K region full | 3,4 S MMAs of a region done | 5,6 PV MMAs of a buffer done | 8..15 V slots
+    // barriers: 0 Q | 1 K full | 3 S MMAs done | 5,6 PV MMAs of a buffer done | 8..16 V slots | 20,21 P / V^T buffer ready
     const uint32_t bar_q = smem_u32(bars), bar_k0 = smem_u32(bars + 1), bar_s0 = smem_u32(bars + 3);
-    const uint32_t bar_pv0 = smem_u32(bars + 5), bar_v0 = smem_u32(bars + 8);
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t bar_pv0 = smem_u32(bars + 5), bar_v0 = smem_u32(bars + 8), bar_rdy0 = smem_u32(bars + 20);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = blockIdx.z, qt = blockIdx.x;
     const int G = a.H / a.Hkv;
     const int kvh = a.pack ? (int)blockIdx.y : (int)blockIdx.y / G;
@@ -110,13 +118,14 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     const int k10 = a.k1_start[row], n1 = a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - k10;
     const int k20 = a.k2_start ? a.k2_start[row] : 0, n2 = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
     const int n1p = (n1 + 31) & ~31, n2p = (n2 + 31) & ~31, nkp = n1p + n2p;
-    const int nblk = (nkp + 127) >> 7, nchunks = nkp >> 5;
+    const int nchunks = nkp >> 5;
     const int vofs = a.Hkv * 64;
     BoundedWaiter w{a.err, false};
 
     if (tid == 0) {
         for (int i = 0; i < 7; i++) mbar_init(bar_q + 8 * i, 1);
         for (int i = 0; i < ATC_VSLOTS; i++) mbar_init(bar_v0 + 8 * i, 1);
+        mbar_init(bar_rdy0, ATC_THREADS / 32); mbar_init(bar_rdy0 + 8, ATC_THREADS / 32);   // one arrival per team warp
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -129,18 +138,15 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // K block kb (128 padded keys, or what is left) -> region R1 / R2 as raw fp32, 32-row boxes
-    auto load_kblock = [&](int kb) {
-        unsigned char *dst = (kb & 1) ? R2 : R1;
-        const int kb0 = kb * 128, nrows = (nkp - kb0) < 128 ? (nkp - kb0) : 128;
-        const uint32_t bar = bar_k0 + 8 * (kb & 1);
-        mbar_expect_tx(bar, (uint32_t)nrows * 256);
-        for (int g = 0; g < nrows / 32; g++) {
-            int j0 = kb0 + g * 32;
+    // all (padded) key rows of the row -> KA as raw fp32, 32-row boxes, two 32-column atoms
+    auto load_keys = [&]() {
+        mbar_expect_tx(bar_k0, (uint32_t)nkp * 256);
+        for (int g = 0; g < nkp / 32; g++) {
+            int j0 = g * 32;
             const CUtensorMap *mk = j0 < n1p ? &mk1 : &mk2;
             int tok = j0 < n1p ? k10 + j0 : k20 + (j0 - n1p);
-            tma_load_2d(smem_u32(dst + g * 4096), mk, kvh * 64, tok, bar);
-            tma_load_2d(smem_u32(dst + 16384 + g * 4096), mk, kvh * 64 + 32, tok, bar);
+            tma_load_2d(smem_u32(KA + g * 4096), mk, kvh * 64, tok, bar_k0);
+            tma_load_2d(smem_u32(KA + ATC_KATOM + g * 4096), mk, kvh * 64 + 32, tok, bar_k0);
         }
     };
     auto load_vchunk = [&](int c) {
@@ -166,170 +172,183 @@ __global__ void __launch_bounds__(ATC_THREADS) k_attention_tc(const __grid_const
             tma_load_2d(smem_u32(R0), &mq, (int)blockIdx.y * 64, q0 + qt * 128, bar_q);
             tma_load_2d(smem_u32(R0 + 16384), &mq, (int)blockIdx.y * 64 + 32, q0 + qt * 128, bar_q);
         }
-        if (nblk > 0) load_kblock(0);
-        if (nblk > 1) load_kblock(1);
+        if (nkp > 0) load_keys();
     }
     w.wait(bar_q, 0, 11);
-    split_tile(R0, R0 + 32768, 2048, tid);
-    uint32_t s_uses[2] = {0, 0}, s_waited[2] = {0, 0};            // commits issued / waited per region (uniform)
-    for (int kb = 0; kb < nblk; kb++) {
-        const int rg = kb & 1;
-        unsigned char *Kr = rg ? R2 : R1;
-        const int nrows = (nkp - kb * 128) < 128 ? (nkp - kb * 128) : 128;
-        w.wait(bar_k0 + 8 * rg, (uint32_t)(kb >> 1) & 1u, 12);
-        // rows >= nrows of a short block are never read by the MMA (N = nrows)
-        for (int at = 0; at < 2; at++) split_tile(Kr + at * 16384, Kr + 32768 + at * 16384, nrows * 8, tid);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
+    if (tid < ATC_THREADS) split_tile(R0, R0 + 32768, 2048, tid);
+    if (nkp > 0) {
+        w.wait(bar_k0, 0, 12);
+        if (tid < ATC_THREADS)
+            for (int at = 0; at < 2; at++) split_tile(KA + at * ATC_KATOM, KA + (2 + at) * ATC_KATOM, nkp * 8, tid);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    if (nkp > 0) {
         if (tid == 0) {
             tc_fence_after();
-            const uint32_t idesc = umma_idesc_tf32(128, nrows);
-            const uint32_t d = tmem + (uint32_t)(kb * 128);
-            for (int at = 0; at < 2; at++) {
-                uint64_t qh = umma_desc_sw128(smem_u32(R0 + at * 16384)), ql = umma_desc_sw128(smem_u32(R0 + 32768 + at * 16384));
-                uint64_t kh = umma_desc_sw128(smem_u32(Kr + at * 16384)), kl = umma_desc_sw128(smem_u32(Kr + 32768 + at * 16384));
+            for (int r0 = 0; r0 < nkp; r0 += 256) {                   // N <= 256 per MMA: 256 + 32 for a full row
+                const int nrows = (nkp - r0) < 256 ? (nkp - r0) : 256;
+                const uint32_t idesc = umma_idesc_tf32(128, nrows);
+                const uint32_t d = tmem + (uint32_t)r0;
+                for (int at = 0; at < 2; at++) {
+                    uint64_t qh = umma_desc_sw128(smem_u32(R0 + at * 16384)), ql = umma_desc_sw128(smem_u32(R0 + 32768 + at * 16384));
+                    uint64_t kh = umma_desc_sw128(smem_u32(KA + at * ATC_KATOM + r0 * 128));
+                    uint64_t kl = umma_desc_sw128(smem_u32(KA + (2 + at) * ATC_KATOM + r0 * 128));
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    umma_tf32(d, ql + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, (at | k) ? 1u : 0u);
-                    umma_tf32(d, qh + (uint64_t)(k * 2), kl + (uint64_t)(k * 2), idesc, 1u);
-                    umma_tf32(d, qh + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, 1u);
+                    for (int k = 0; k < 4; k++) {
+                        umma_tf32(d, ql + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, (at | k) ? 1u : 0u);
+                        umma_tf32(d, qh + (uint64_t)(k * 2), kl + (uint64_t)(k * 2), idesc, 1u);
+                        umma_tf32(d, qh + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, 1u);
+                    }
                 }
             }
-            umma_commit(bar_s0 + 8 * rg);
+            umma_commit(bar_s0);
         }
-        s_uses[rg]++;
-        if (kb + 2 < nblk) {                                      // the region is needed again: drain it, refill
-            w.wait(bar_s0 + 8 * rg, s_waited[rg] & 1u, 13);
-            s_waited[rg]++;
-            if (tid == 0) load_kblock(kb + 2);
-        }
+        w.wait(bar_s0, 0, 13);
     }
-    for (int rg = 0; rg < 2; rg++)
-        if (s_waited[rg] < s_uses[rg]) { w.wait(bar_s0 + 8 * rg, s_waited[rg] & 1u, 13); s_waited[rg]++; }
     tc_fence_after();
     __syncthreads();                                              // every thread is past phase 1: regions may be reused
 
     // ================= phase 2: softmax and O = P V =================
     if (tid == 0)
-        for (int c = 0; c < nchunks && c < ATC_VSLOTS; c++) load_vchunk(c);
-    const int r = tid & 127, part = tid >> 7;                     // query row of the tile, which quarter of each chunk's columns
-    const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
-    const int h = a.pack ? kvh * G + (r >> 5) : (int)blockIdx.y;
-    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    // visible columns of chunk c for this thread's query, as [jlo, jhi) relative to the chunk start
-    auto chunk_range = [&](int c, int &jlo, int &jhi) {
-        const int c0 = c * 32;
-        int lo, hi, base;                                         // key index = base + j
-        if (c0 < n1p) {
-            base = c0; lo = 0; hi = n1;
-            if (a.causal) hi = min(hi, qi + a.causal_off + 1);
-        } else {
-            base = n1 + (c0 - n1p); lo = n1; hi = n1 + n2;
-        }
-        if (a.window > 0) { lo = max(lo, qi - a.window); hi = min(hi, qi + a.window + 1); }
-        jlo = lo - base; jhi = hi - base;
-    };
-    float mx = -INFINITY;
-    for (int c = part; c < nchunks; c += 4) {
-        uint32_t v[32];
-        tmem_ld32(lane_addr + (uint32_t)(c * 32), v);
-        int jlo, jhi;
-        chunk_range(c, jlo, jhi);
-#pragma unroll
-        for (int j = 0; j < 32; j++)
-            if (j >= jlo && j < jhi) mx = fmaxf(mx, __uint_as_float(v[j]));
-    }
-    xch[tid] = mx;
-    __syncthreads();
-    mx = fmaxf(fmaxf(xch[r], xch[r + 128]), fmaxf(xch[r + 256], xch[r + 384]));
-    __syncthreads();                                              // xch is reused for the row sums
-    const bool any = mx != -INFINITY;
-    const float sl2 = a.scale * 1.4426950408889634f;
-
-    float l = 0.f;
-    for (int c = 0; c < nchunks; c++) {
-        const int b = c & 1;
-        unsigned char *Phi = R2 + b * 32768, *Plo = Phi + 16384;
-        unsigned char *Vthi = R0 + b * 16384, *Vtlo = Vthi + 8192;
-        if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
-        {
-            uint32_t v[8];
-            tmem_ld8(lane_addr + (uint32_t)(c * 32 + part * 8), v);
-            int jlo, jhi;
-            chunk_range(c, jlo, jhi);
-            jlo -= part * 8; jhi -= part * 8;
-            const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-#pragma unroll
-            for (int g = 0; g < 2; g++) {
-                float p[4], ph[4];
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int j = g * 4 + e;
-                    float x = 0.f;
-                    if (any && j >= jlo && j < jhi) x = exp2f((__uint_as_float(v[j]) - mx) * sl2);
-                    l += x; p[e] = x; ph[e] = atc_hi(x);
-                }
-                const uint32_t o = rowoff + ((uint32_t)(((part * 2 + g) ^ (r & 7)) & 7) << 4);
-                *(float4 *)(Phi + o) = make_float4(ph[0], ph[1], ph[2], ph[3]);
-                *(float4 *)(Plo + o) = make_float4(p[0] - ph[0], p[1] - ph[1], p[2] - ph[2], p[3] - ph[3]);
-            }
-        }
-        w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
-        {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
-            const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
-            const int c0 = c * 32;
-            const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
-            const int kk = tid & 31;
-#pragma unroll
-            for (int n = 0; n < 4; n++) {
-                const int d = (tid >> 5) + 16 * n;
-                float x = *(const float *)(Vraw + (d >> 5) * 4096 + sw128_off(kk, d & 31));
-                if (kk >= nvalid) x = 0.f;
-                float hi = atc_hi(x);
-                uint32_t o = sw128_off(d, kk);
-                *(float *)(Vthi + o) = hi; *(float *)(Vtlo + o) = x - hi;
-            }
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
+        for (int c = 0; c < nchunks; c++) load_vchunk(c);      // one slot per chunk: every V load is in flight now
+    auto team_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(ATC_THREADS) : "memory"); };
+    if (warp == ATC_THREADS / 32) {
+        // ---- MMA warp: O += P V for every chunk as soon as the team has filled a P / V^T buffer ----
+        if (lane == 0) {
             const uint32_t idesc = umma_idesc_tf32(128, 64);
             const uint32_t d = tmem + (uint32_t)ATC_OCOL;
-            uint64_t ph = umma_desc_sw128(smem_u32(Phi)), pl = umma_desc_sw128(smem_u32(Plo));
-            uint64_t vh = umma_desc_sw128(smem_u32(Vthi)), vl = umma_desc_sw128(smem_u32(Vtlo));
+            for (int c = 0; c < nchunks; c++) {
+                const int b = c & 1;
+                w.wait(bar_rdy0 + 8 * b, (uint32_t)(c >> 1) & 1u, 17);
+                tc_fence_after();
+                uint64_t ph = umma_desc_sw128(smem_u32(R2 + b * 32768)), pl = umma_desc_sw128(smem_u32(R2 + b * 32768 + 16384));
+                uint64_t vh = umma_desc_sw128(smem_u32(R0 + b * 16384)), vl = umma_desc_sw128(smem_u32(R0 + b * 16384 + 8192));
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                umma_tf32(d, pl + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
-                umma_tf32(d, ph + (uint64_t)(k * 2), vl + (uint64_t)(k * 2), idesc, 1u);
-                umma_tf32(d, ph + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, 1u);
+                for (int k = 0; k < 4; k++) {
+                    umma_tf32(d, pl + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
+                    umma_tf32(d, ph + (uint64_t)(k * 2), vl + (uint64_t)(k * 2), idesc, 1u);
+                    umma_tf32(d, ph + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, 1u);
+                }
+                umma_commit(bar_pv0 + 8 * b);
             }
-            umma_commit(bar_pv0 + 8 * b);
-            if (c + ATC_VSLOTS < nchunks) load_vchunk(c + ATC_VSLOTS);   // this chunk's raw V slot is free again
         }
-    }
-    // the commits complete in order: the last one covers every earlier MMA
-    if (nchunks > 0) { const int c = nchunks - 1; w.wait(bar_pv0 + 8 * (c & 1), (uint32_t)(c >> 1) & 1u, 16); }
-    tc_fence_after();
-    xch[tid] = l;
-    __syncthreads();
-    l = (xch[r] + xch[r + 128]) + (xch[r + 256] + xch[r + 384]);
-    // ---- output row: O / l; the four threads of a row take 16 columns each ----
-    {
-        const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
-        uint32_t v[16];
-        if (nchunks > 0) tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
-        if (live) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-                float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
-                                        __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
-                if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
-                else *(float4 *)(a.out + ofs + j) = o4;
+    } else {
+        const int r = tid & 127, part = tid >> 7;                     // query row of the tile, which quarter of each chunk's columns
+        const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
+        const int h = a.pack ? kvh * G + (r >> 5) : (int)blockIdx.y;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        // visible columns of chunk c for this thread's query, as [jlo, jhi) relative to the chunk start
+        auto chunk_range = [&](int c, int &jlo, int &jhi) {
+            const int c0 = c * 32;
+            int lo, hi, base;                                         // key index = base + j
+            if (c0 < n1p) {
+                base = c0; lo = 0; hi = n1;
+                if (a.causal) hi = min(hi, qi + a.causal_off + 1);
+            } else {
+                base = n1 + (c0 - n1p); lo = n1; hi = n1 + n2;
+            }
+            if (a.window > 0) { lo = max(lo, qi - a.window); hi = min(hi, qi + a.window + 1); }
+            jlo = lo - base; jhi = hi - base;
+        };
+        // The thread's scores -- eight columns of every chunk -- are read from tensor memory ONCE, all loads in
+        // flight together, and stay in registers for the maximum and for the exponentials: a tcgen05.ld round
+        // trip costs about a microsecond, and one per chunk was most of the chunk loop.
+        uint32_t sv[ATC_VSLOTS][8];
+    #pragma unroll
+        for (int c = 0; c < ATC_VSLOTS; c++) tmem_ld8_issue(lane_addr + (uint32_t)(c * 32 + part * 8), sv[c]);
+        tmem_ld_wait();
+        float mx = -INFINITY;
+    #pragma unroll
+        for (int c = 0; c < ATC_VSLOTS; c++) {
+            if (c < nchunks) {
+                int jlo, jhi;
+                chunk_range(c, jlo, jhi);
+                jlo -= part * 8; jhi -= part * 8;
+    #pragma unroll
+                for (int j = 0; j < 8; j++)
+                    if (j >= jlo && j < jhi) mx = fmaxf(mx, __uint_as_float(sv[c][j]));
+            }
+        }
+        xch[tid] = mx;
+        team_sync();
+        mx = fmaxf(fmaxf(xch[r], xch[r + 128]), fmaxf(xch[r + 256], xch[r + 384]));
+        team_sync();                                                  // xch is reused for the row sums
+        const bool any = mx != -INFINITY;
+        const float sl2 = a.scale * 1.4426950408889634f;
+
+        float l = 0.f;
+    #pragma unroll
+        for (int c = 0; c < ATC_VSLOTS; c++) {
+            if (c >= nchunks) break;
+            const int b = c & 1;
+            unsigned char *Phi = R2 + b * 32768, *Plo = Phi + 16384;
+            unsigned char *Vthi = R0 + b * 16384, *Vtlo = Vthi + 8192;
+            if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
+            {
+                const uint32_t *v = sv[c];
+                int jlo, jhi;
+                chunk_range(c, jlo, jhi);
+                jlo -= part * 8; jhi -= part * 8;
+                const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+    #pragma unroll
+                for (int g = 0; g < 2; g++) {
+                    float p[4], ph[4];
+    #pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int j = g * 4 + e;
+                        float x = 0.f;
+                        if (any && j >= jlo && j < jhi) x = exp2f((__uint_as_float(v[j]) - mx) * sl2);
+                        l += x; p[e] = x; ph[e] = atc_hi(x);
+                    }
+                    const uint32_t o = rowoff + ((uint32_t)(((part * 2 + g) ^ (r & 7)) & 7) << 4);
+                    *(float4 *)(Phi + o) = make_float4(ph[0], ph[1], ph[2], ph[3]);
+                    *(float4 *)(Plo + o) = make_float4(p[0] - ph[0], p[1] - ph[1], p[2] - ph[2], p[3] - ph[3]);
+                }
+            }
+            w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
+            {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
+                const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
+                const int c0 = c * 32;
+                const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
+                const int kk = tid & 31;
+    #pragma unroll
+                for (int n = 0; n < 4; n++) {
+                    const int d = (tid >> 5) + 16 * n;
+                    float x = *(const float *)(Vraw + (d >> 5) * 4096 + sw128_off(kk, d & 31));
+                    if (kk >= nvalid) x = 0.f;
+                    float hi = atc_hi(x);
+                    uint32_t o = sw128_off(d, kk);
+                    *(float *)(Vthi + o) = hi; *(float *)(Vtlo + o) = x - hi;
+                }
+            }
+            // hand the buffers to the MMA warp: this warp's writes are visible to the async proxy, one arrival per warp
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_rdy0 + 8 * b);
+        }
+        // the commits complete in order: the last one covers every earlier MMA
+        if (nchunks > 0) { const int c = nchunks - 1; w.wait(bar_pv0 + 8 * (c & 1), (uint32_t)(c >> 1) & 1u, 16); }
+        tc_fence_after();
+        xch[tid] = l;
+        team_sync();
+        l = (xch[r] + xch[r + 128]) + (xch[r + 256] + xch[r + 384]);
+        // ---- output row: O / l; the four threads of a row take 16 columns each ----
+        {
+            const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
+            uint32_t v[16];
+            if (nchunks > 0) tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
+            if (live) {
+    #pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
+                                            __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                    if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
+                    else *(float4 *)(a.out + ofs + j) = o4;
+                }
             }
         }
     }
@@ -349,7 +368,7 @@ bool attention_tc_supported(const AttnArgs &a) {
     if (!pack && a.max_q < 64) return false;
     if (a.max_k1 <= 0 && a.max_k2 <= 0) return false;
     int n1p = (a.max_k1 + 31) & ~31, n2p = (a.max_k2 + 31) & ~31;
-    if (n1p + n2p > ATC_OCOL || n1p + n2p == 0) return false;
+    if (n1p + n2p > ATC_MAXK || n1p + n2p == 0) return false;
     if (a.q_total <= 0 || a.k1_total <= 0 || (a.k2 && a.k2_total <= 0)) return false;
     if ((a.ldq | a.ldk1 | a.ldk2 | a.ldo) & 3) return false;
     if (a.v1 != a.k1 + a.Hkv * 64 || (a.k2 && a.v2 != a.k2 + a.Hkv * 64)) return false;
@@ -377,7 +396,7 @@ void attention_tc(const AttnArgs &a) {
     }
     dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
     ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
-    LAUNCH(k_attention_tc, grid, ATC_THREADS, ATC_SMEM, *mq, *mk1, *mk2, d);
+    LAUNCH(k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, *mq, *mk1, *mk2, d);
 }
 
 } // namespace ncmb

