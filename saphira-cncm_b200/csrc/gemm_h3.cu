@@ -228,7 +228,7 @@ static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 bool gemm_h3_supported(const GemmArgs &a) {
     int64_t ldx = a.ldx ? a.ldx : a.K, ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     if (a.argmin_best) return false;                                // nearest-row search stays on the TF32 kernel
-    if (a.M < 64 || a.N < 32 || a.K < 32) return false;            // skinny shapes stay on CUDA cores (weight streaming)
+    if (a.M <= 16 || a.N < 32 || a.K < 32) return false;           // up to 16 rows: the weight-streaming GEMV kernel
     if ((a.K & 7) || (ldx & 7)) return false;                       // fp16 rows: TMA strides are multiples of 16 bytes
     if (a.x_lo && a.x_fmt != SPLIT_H16) return false;
     if (!al16(a.x) || (a.x_lo && !al16(a.x_lo)) || !al16(a.W) || !al16(a.y) || (a.y_lo && !al16(a.y_lo)) ||

@@ -307,7 +307,7 @@ static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool gemm_tc_supported(const GemmArgs &a) {
     int64_t ldx = a.ldx ? a.ldx : a.K, ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
-    if (a.M < 64 || a.N < 32 || a.K < 32) return false;            // skinny shapes stay on CUDA cores (weight streaming)
+    if (a.M <= 16 || a.N < 32 || a.K < 32) return false;           // up to 16 rows: the weight-streaming GEMV kernel
     if ((a.K & 3) || (ldx & 3)) return false;                       // TMA strides: multiples of 16 bytes
     if (!al16(a.x) || !al16(a.W) || (!a.argmin_best && !al16(a.y)) || (a.bias && !al16(a.bias)) || (a.res && !al16(a.res))) return false;
     if (a.glu && ((a.N & 1) || (ldy & 1))) return false;
