@@ -53,6 +53,12 @@ __device__ __forceinline__ float atc_hi(float v) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
     return __uint_as_float(u);
 }
+// 2^x through the special-function unit (about 2 ulp): the probabilities are split into 22-bit pairs right after
+__device__ __forceinline__ float atc_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
                  "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -255,17 +261,17 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         // flight together, and stay in registers for the maximum and for the exponentials: a tcgen05.ld round
         // trip costs about a microsecond, and one per chunk was most of the chunk loop.
         uint32_t sv[ATC_VSLOTS][8];
-    #pragma unroll
+#pragma unroll
         for (int c = 0; c < ATC_VSLOTS; c++) tmem_ld8_issue(lane_addr + (uint32_t)(c * 32 + part * 8), sv[c]);
         tmem_ld_wait();
         float mx = -INFINITY;
-    #pragma unroll
+#pragma unroll
         for (int c = 0; c < ATC_VSLOTS; c++) {
             if (c < nchunks) {
                 int jlo, jhi;
                 chunk_range(c, jlo, jhi);
                 jlo -= part * 8; jhi -= part * 8;
-    #pragma unroll
+#pragma unroll
                 for (int j = 0; j < 8; j++)
                     if (j >= jlo && j < jhi) mx = fmaxf(mx, __uint_as_float(sv[c][j]));
             }
@@ -277,8 +283,17 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         const bool any = mx != -INFINITY;
         const float sl2 = a.scale * 1.4426950408889634f;
 
+        // shared-memory offsets of the thread's four V elements (source: raw [key][d] atoms, destination: V^T)
+        const int kk = tid & 31;
+        uint32_t vsrc[4], vdst[4];
+#pragma unroll
+        for (int n = 0; n < 4; n++) {
+            const int d = (tid >> 5) + 16 * n;
+            vsrc[n] = (uint32_t)((d >> 5) * 4096) + sw128_off(kk, d & 31);
+            vdst[n] = sw128_off(d, kk);
+        }
         float l = 0.f;
-    #pragma unroll
+#pragma unroll
         for (int c = 0; c < ATC_VSLOTS; c++) {
             if (c >= nchunks) break;
             const int b = c & 1;
@@ -290,15 +305,16 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 int jlo, jhi;
                 chunk_range(c, jlo, jhi);
                 jlo -= part * 8; jhi -= part * 8;
+                const bool inner = any && jlo <= 0 && jhi >= 8;
                 const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-    #pragma unroll
+#pragma unroll
                 for (int g = 0; g < 2; g++) {
                     float p[4], ph[4];
-    #pragma unroll
+#pragma unroll
                     for (int e = 0; e < 4; e++) {
                         const int j = g * 4 + e;
-                        float x = 0.f;
-                        if (any && j >= jlo && j < jhi) x = exp2f((__uint_as_float(v[j]) - mx) * sl2);
+                        float x = atc_ex2((__uint_as_float(v[j]) - mx) * sl2);
+                        if (!inner && !(any && j >= jlo && j < jhi)) x = 0.f;     // interior chunks skip the range tests
                         l += x; p[e] = x; ph[e] = atc_hi(x);
                     }
                     const uint32_t o = rowoff + ((uint32_t)(((part * 2 + g) ^ (r & 7)) & 7) << 4);
@@ -311,15 +327,12 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
                 const int c0 = c * 32;
                 const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
-                const int kk = tid & 31;
-    #pragma unroll
+#pragma unroll
                 for (int n = 0; n < 4; n++) {
-                    const int d = (tid >> 5) + 16 * n;
-                    float x = *(const float *)(Vraw + (d >> 5) * 4096 + sw128_off(kk, d & 31));
+                    float x = *(const float *)(Vraw + vsrc[n]);
                     if (kk >= nvalid) x = 0.f;
                     float hi = atc_hi(x);
-                    uint32_t o = sw128_off(d, kk);
-                    *(float *)(Vthi + o) = hi; *(float *)(Vtlo + o) = x - hi;
+                    *(float *)(Vthi + vdst[n]) = hi; *(float *)(Vtlo + vdst[n]) = x - hi;
                 }
             }
             // hand the buffers to the MMA warp: this warp's writes are visible to the async proxy, one arrival per warp
@@ -341,7 +354,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             uint32_t v[16];
             if (nchunks > 0) tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
             if (live) {
-    #pragma unroll
+#pragma unroll
                 for (int j = 0; j < 16; j += 4) {
                     float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
                                             __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
