@@ -136,12 +136,35 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
                     if ((k & mask) == prefix) atomicAdd(&hist[(k >> (8 * pass)) & 0xff], 1);
                 }
                 __syncthreads();
-                if (tid == 0) {
-                    int rem = s_remaining, cum = 0, bin = 255;
-                    for (; bin > 0; bin--) { if (cum + hist[bin] >= rem) break; cum += hist[bin]; }
-                    s_remaining = rem - cum;
-                    s_prefix = prefix | ((unsigned)bin << (8 * pass));
-                    s_mask = mask | (0xffu << (8 * pass));
+                if (tid < 32) {
+                    // the bin, scanning from 255 down, where the running count first reaches `rem`: lane l owns bins
+                    // 255-8l .. 248-8l; lane totals are scanned with shuffles instead of one thread walking 256 bins
+                    const int rem = s_remaining, top = 255 - 8 * tid;
+                    int h8[8], tot = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) { h8[i] = hist[top - i]; tot += h8[i]; }
+                    int incl = tot;
+#pragma unroll
+                    for (int o = 1; o < 32; o <<= 1) { int t2 = __shfl_up_sync(0xffffffffu, incl, o); if (tid >= o) incl += t2; }
+                    int cum = incl - tot;                               // count in all bins above this lane's
+                    const bool here = cum < rem && incl >= rem;          // the crossing lies in this lane's bins
+                    const unsigned who = __ballot_sync(0xffffffffu, here);
+                    if (who == 0) {                                      // fewer than rem values in total: bin 0, as the serial walk ends
+                        if (tid == 31) {
+                            s_remaining = rem - (incl - h8[7]);
+                            s_prefix = prefix; s_mask = mask | (0xffu << (8 * pass));
+                        }
+                    } else if (tid == __ffs(who) - 1) {
+                        int bin = top;
+                        for (int i = 0; i < 8; i++) {
+                            bin = top - i;
+                            if (bin == 0 || cum + h8[i] >= rem) break;
+                            cum += h8[i];
+                        }
+                        s_remaining = rem - cum;
+                        s_prefix = prefix | ((unsigned)bin << (8 * pass));
+                        s_mask = mask | (0xffu << (8 * pass));
+                    }
                 }
                 __syncthreads();
             }
@@ -163,7 +186,18 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
             for (int v = v0; v < v1; v++) if (okey(vals[v]) == thr) eq++;
             s_eqbase[tid + 1] = eq;
             __syncthreads();
-            if (tid == 0) { s_eqbase[0] = 0; for (int i = 1; i <= SM_THREADS; i++) s_eqbase[i] += s_eqbase[i - 1]; }
+            {   // inclusive scan of the per-thread tie counts: warp shuffles, then the eight warp totals
+                const int lane = tid & 31, wp = tid >> 5;
+                int v = eq;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) { int t2 = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += t2; }
+                if (lane == 31) hist[wp] = v;
+                __syncthreads();
+                int base = 0;
+                for (int i = 0; i < wp; i++) base += hist[i];
+                s_eqbase[tid + 1] = base + v;
+                if (tid == 0) s_eqbase[0] = 0;
+            }
             __syncthreads();
             {
                 int rank = s_eqbase[tid], gt = s_ncand;
