@@ -325,6 +325,10 @@ typedef struct NcmbLM NcmbLM;
 NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights);
 void   ncmb_lm_close(NcmbLM *m);
 int    ncmb_lm_vocab(const NcmbLM *m);
+/* Decode steps of up to four sequences (head dim 64) can run as ONE persistent cooperative kernel with grid
+ * barriers between the phases of a layer instead of a replayed chain of kernels. Off by default (it is the
+ * slower of the two today); results are the same either way. No counterpart in the reference. */
+void  ncmb_set_lm_persistent(int on);
 /* prompts: host int[B][np]; out: host int[B][n_new]; eos < 0 disables stopping.
  * Returns the number of ids generated per row (n_new unless every row hit eos). */
 int    ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, int n_new,

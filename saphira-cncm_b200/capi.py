@@ -113,6 +113,7 @@ _SIGS = {
     "ncmb_set_gemm_mode": (None, [_I]),
     "ncmb_get_gemm_mode": (_I, []),
     "ncmb_gemm_tc_check": (_I, []),
+    "ncmb_set_lm_persistent": (None, [_I]),
     "ncmb_attention_check": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I]),
     "ncmb_set_rng_mode": (None, [_I]),
     "ncmb_set_row_offset": (None, [C.c_longlong]),

@@ -4,6 +4,8 @@
 // a cached, batched run produce the same logits, so each row here equals one
 // reference run. Layers reuse the transformer block of the NCP stack.
 #include "common.cuh"
+#include "lm_mega.cuh"
+#include "tc_common.cuh"
 
 #include <vector>
 
@@ -143,6 +145,7 @@ extern "C" void ncmb_lm_close(NcmbLM *m) {
     delete m;
 }
 extern "C" int ncmb_lm_vocab(const NcmbLM *m) { return m->V; }
+extern "C" void ncmb_set_lm_persistent(int on) { lm_mega_enable(on); }
 
 namespace {
 
@@ -157,7 +160,9 @@ struct LMRun {
     double *uni_d = nullptr;
     // decode loop state on the device: absolute position of the step, this step's picks / packed argmax / uniforms
     int *step_d = nullptr, *pick_d = nullptr;
-    long long graph_launches = 0;                      // kernel launches one replay of the captured step stands for
+    long long graph_launches = 0;
+    // persistent decode kernel (up to four rows, head dim 64)
+    float *mg_part = nullptr; unsigned *mg_count = nullptr, *mg_bar = nullptr; MegaLayer *mg_layers = nullptr;                      // kernel launches one replay of the captured step stands for
     unsigned long long *amax_d = nullptr;
     double *uni_cur = nullptr;
 };
@@ -192,6 +197,11 @@ void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
     r.amax_d = w.get<unsigned long long>(r.B);
     r.pick_d = w.get<int>(r.B);
     r.step_d = w.get<int>(4);
+    const int max_split = (r.cap + 31) / 32;
+    r.mg_part = w.get<float>((size_t)r.B * m->H * max_split * 66);
+    r.mg_count = w.get<unsigned>((size_t)r.B * m->nkv + 4);
+    r.mg_bar = w.get<unsigned>(4);
+    r.mg_layers = (MegaLayer *)w.get<unsigned char>(sizeof(MegaLayer) * (size_t)m->NL);
 }
 
 void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
@@ -406,8 +416,37 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
     // runs eagerly (it sizes every workspace), the second is captured, the rest are graph launches. The work
     // moves to a stream of its own for that, because the caller's stream may be the legacy default stream,
     // which cannot be captured.
+    // Up to four rows (head dim 64): the whole decode step is one persistent cooperative kernel; nothing to replay.
+    bool qk_norm = false;
+    for (auto &bw : m->blocks) qk_norm = qk_norm || bw.qnw || bw.knw;
+    const bool mega = lm_mega_eligible(B, m->hd, m->C, m->I, qk_norm) && r.cap <= 2048 && n_new >= 2;
+    MegaArgs mg{};
+    if (mega) {
+        std::vector<MegaLayer> hl(m->NL);
+        for (int li = 0; li < m->NL; li++) {
+            const BlockWeights &bw = m->blocks[li];
+            hl[li] = MegaLayer{bw.ln1w, bw.ln1b, bw.qkvw, bw.qkvb, bw.ow, bw.ob, bw.ln2w, bw.ln2b, bw.fcw, bw.fcb, bw.pw, bw.pb, r.kv[li]};
+        }
+        upload(r.mg_layers, hl.data(), sizeof(MegaLayer) * hl.size());
+        CUDA_CHECK(cudaMemsetAsync(r.mg_count, 0, ((size_t)B * m->nkv + 4) * 4, stream()));
+        CUDA_CHECK(cudaMemsetAsync(r.mg_bar, 0, 16, stream()));
+        CUDA_CHECK(cudaStreamSynchronize(stream()));             // hl goes out of scope
+        const BlockWeights &b0 = m->blocks[0];
+        mg.B = B; mg.C = m->C; mg.H = m->H; mg.nkv = m->nkv; mg.I = m->I; mg.NL = m->NL; mg.V = m->V;
+        mg.norm = b0.norm == NORM_RMS ? 2 : 1; mg.gated = b0.gated; mg.act = b0.act; mg.rope = m->is_qwen ? 1 : 0;
+        mg.eps = b0.norm == NORM_RMS ? 1e-6f : b0.eps; mg.eps_f = m->is_qwen ? 1e-6f : 1e-5f;
+        mg.layers = r.mg_layers; mg.wte = m->wte; mg.wpe = m->is_qwen ? nullptr : m->wpe; mg.lnfw = m->lnfw; mg.lnfb = m->lnfb;
+        mg.cosb = m->cosb; mg.sinb = m->sinb;
+        mg.x = r.x; mg.qkv = r.bufs.qkv; mg.ctx = r.bufs.ctx; mg.h = r.bufs.h; mg.logits = r.logits;
+        mg.part = r.mg_part; mg.count = r.mg_count;
+        mg.ids = r.ids_d; mg.posmat = r.posmat; mg.lenmat = r.lenmat; mg.step_d = r.step_d;
+        mg.np = np; mg.cap = r.cap; mg.n_new = n_new; mg.max_split = (r.cap + 31) / 32;
+        mg.kv_seq_pitch = (int64_t)r.cap * 2 * m->nkv * m->hd;
+        mg.bar = r.mg_bar; mg.bar_base = r.mg_bar + 1; mg.err = tc_err_flag();
+        mg.greedy = !(temp > 0.f); mg.amax = r.amax_d; mg.out = r.out_d; mg.ids_out = r.ids_d;
+    }
     static const bool graphs_ok = !getenv("NCM_B200_NO_GRAPH");
-    const bool use_graph = graphs_ok && eos < 0 && n_new >= 4 && !prof_enabled();
+    const bool use_graph = !mega && graphs_ok && eos < 0 && n_new >= 4 && !prof_enabled();
     cudaStream_t user = stream(), gs = nullptr;
     cudaEvent_t ev = nullptr;
     cudaGraph_t graph = nullptr; cudaGraphExec_t gexec = nullptr;
@@ -419,7 +458,8 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
         ctx().stream = gs;
     }
     for (int s = 0; s < n_new; s++) {
-        if (s == 0 || !gexec) lm_sample(r, temp, top_k, top_p, n_new);       // (inside the graph for replayed steps)
+        // (the sample + finish of a step is inside the graph for replayed steps, inside the kernel for greedy persistent steps)
+        if (s == 0 || (!gexec && !(mega && mg.greedy))) lm_sample(r, temp, top_k, top_p, n_new);
         produced = s + 1;
         if (eos >= 0) {
             mem_d2h(col.data(), r.ids_d, (size_t)B * 4);
@@ -428,6 +468,7 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
             if (all) break;
         }
         if (s + 1 == n_new) break;
+        if (mega) { lm_mega_launch(mg); continue; }
         if (gexec) { CUDA_CHECK(cudaGraphLaunch(gexec, gs)); ctx().launches += r.graph_launches; continue; }
         const bool capture = use_graph && s == 1;
         long long l0 = ctx().launches;

@@ -264,16 +264,31 @@ def test_quantizer_sweep_box_scale_codebook(cuda, tmp):
     print(f"box-scale nearest-code: {ties} near-ties in 512 sampled rows")
 
 
-@pytest.mark.parametrize("kind", ["gpt2", "qwen"])
+LM_SPECS = {
+    # head dim 16: every kernel of the generic path (GEMV, split-key attention, CUDA graph replay)
+    "gpt2": lambda synth: synth.spec_gpt2_tiny(),
+    "qwen": lambda synth: synth.spec_qwen_tiny(),
+    # head dim 64 (the decode-attention and GEMV kernels at the models' real head size)
+    "gpt2_hd64": lambda synth: synth.LMSpec("gpt2_hd64", "gpt2", 2, 128, 2, 2, 512, 300, 64, rand_affine=1),
+    "qwen_hd64": lambda synth: synth.LMSpec("qwen_hd64", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, rand_affine=1),
+    # the same two through the persistent cooperative decode kernel (rotary pairs, grouped heads, gated MLP)
+    "gpt2_hd64_persistent": lambda synth: synth.LMSpec("gpt2_hd64", "gpt2", 2, 128, 2, 2, 512, 300, 64, rand_affine=1),
+    "qwen_hd64_persistent": lambda synth: synth.LMSpec("qwen_hd64", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, rand_affine=1),
+}
+
+
+@pytest.mark.parametrize("kind", sorted(LM_SPECS))
 def test_decoder_lm_logits_and_generation(cuda, tmp, kind):
     import orc
     import synth
-    spec = synth.spec_gpt2_tiny() if kind == "gpt2" else synth.spec_qwen_tiny()
+    spec = LM_SPECS[kind](synth)
+    cuda.ncmb_set_lm_persistent(int(kind.endswith("_persistent")))
+    is_qwen = spec.kind == "qwen"
     conf, w = synth.write_lm(spec, tmp)
     cfg = cuda.load_config(conf)
-    m = cuda.ncmb_lm_open(cfg, w.encode(), int(kind == "qwen"), 0)
+    m = cuda.ncmb_lm_open(cfg, w.encode(), int(is_qwen), 0)
     assert m
-    om = orc.LM(conf, w, kind == "qwen")
+    om = orc.LM(conf, w, is_qwen)
     prompts = synth.lm_prompts(spec, 3, 9, 3)
     for pr in prompts:
         pr = np.ascontiguousarray(pr)
@@ -292,4 +307,6 @@ def test_decoder_lm_logits_and_generation(cuda, tmp, kind):
         for b in range(P.shape[0]):
             want = om.generate(P[b], n_new, temp=t, top_k=tk, top_p=tp, seed=sd)
             assert (out[b] == want).all(), (kind, t, tk, tp, b, out[b], want)
+        assert cuda.ncmb_gemm_tc_check() == 0           # no bounded wait (mbarrier, grid barrier) ran out
+    cuda.ncmb_set_lm_persistent(0)
     cuda.ncmb_lm_close(m)
