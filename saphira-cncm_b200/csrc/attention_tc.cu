@@ -39,6 +39,7 @@ struct AttnTcDev {
     float *out; float *out_lo; int64_t ldo; int out_fmt;
     const int *q_start, *k1_start, *k2_start, *k1_len;
     int H, Hkv, causal, causal_off, window;
+    const float *v1; int64_t ldv1;   // segment-1 values as plain pointers (single-key shortcut)
     int pack;        // 1: the tile holds the (<= 32) queries of all H/Hkv (<= 4) heads that share one kv head, 32 rows per head
     float scale;
     int *err;
@@ -116,6 +117,18 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     const int kvh = a.pack ? (int)blockIdx.y : (int)blockIdx.y / G;
     const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
     if (qt * 128 >= nq) return;
+    // one query, one key (the unconditional rows of a classifier-free-guidance batch: a one-token prefix):
+    // the softmax weight is exactly 1, the context is the value row
+    if (!a.pack && nq == 1 && !a.k2_start && (a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - a.k1_start[row]) == 1) {
+        if (tid < 64) {
+            const int kvh1 = (int)blockIdx.y / G;
+            const float x = a.v1[(int64_t)a.k1_start[row] * a.ldv1 + kvh1 * 64 + tid];
+            const int64_t at = (int64_t)q0 * a.ldo + (int)blockIdx.y * 64 + tid;
+            if (a.out_lo) store_split1(a.out, a.out_lo, at, x, a.out_fmt);
+            else a.out[at] = x;
+        }
+        return;
+    }
     // a barrier wait that ran out anywhere earlier (this launch or a previous one) stops the rest of the grid
     __shared__ int s_abort;
     if (tid == 0) s_abort = *(volatile int *)a.err;
@@ -394,6 +407,7 @@ void attention_tc(const AttnArgs &a) {
     AttnTcDev d;
     d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo; d.out_fmt = a.out_fmt;
     d.q_start = a.q_start; d.k1_start = a.k1_start; d.k2_start = a.k2 ? a.k2_start : nullptr; d.k1_len = a.k1_len;
+    d.v1 = a.v1; d.ldv1 = a.ldk1;
     d.H = a.H; d.Hkv = a.Hkv; d.causal = a.causal; d.causal_off = a.causal_off; d.window = a.window;
     d.scale = 1.0f / sqrtf(64.0f);
     d.err = tc_err_flag();

@@ -40,6 +40,16 @@ __global__ void k_convT1d(const float *__restrict__ x, NCT xs, const float *__re
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int co = (int)(i % Cout); int t = (int)((i / Cout) % Tout); int n = (int)(i / ((int64_t)Cout * Tout));
         float acc = b ? b[co] : 0.f;
+        if (K == stride) {                    // non-overlapping taps (the up-cascade): exactly one (input step, tap) per output step
+            const int ti = t / stride, kk = t - ti * stride;
+            if (ti < T) {
+                const float *xc = x + n * xs.sn + ti * xs.st;
+                const float *wc = W + (int64_t)co * K + kk;
+                for (int ci = 0; ci < Cin; ci++) acc = fmaf(xc[ci * xs.sc], wc[(int64_t)ci * Cout * K], acc);
+            }
+            y[n * ys.sn + co * ys.sc + t * ys.st] = acc;
+            continue;
+        }
         for (int ci = 0; ci < Cin; ci++) {
             const float *xc = x + n * xs.sn + ci * xs.sc;
             for (int kk = 0; kk < K; kk++) {
