@@ -1,5 +1,7 @@
-// Decode-step attention: ONE query per sequence row against that row's K/V cache (the decoder-LM
-// token loop, reference src/gpt2.c:92 / src/qwen.c:121 run with a KV cache instead of recomputing).
+// Few-query attention: ONE query per sequence row against that row's K/V cache (the decoder-LM token loop,
+// reference src/gpt2.c:92 / src/qwen.c:121 run with a KV cache instead of recomputing), or up to four queries
+// per row against the cached prefix plus the row's own new tokens (the first levels of the NCP generate,
+// reference src/ncp.c:990: level sizes 1 and 4).
 //
 // With one query there is nothing to tile over queries, so the keys are split instead: one CTA per
 // (32-key chunk, kv head, row) computes the chunk's scores for every query head that shares the kv
@@ -15,11 +17,13 @@
 
 namespace ncmb {
 
-constexpr int AD_KEYS = 32, AD_THREADS = 128, AD_MAXG = 8, AD_MAXSPLIT = 64;   // up to 2048 cached keys per row
+constexpr int AD_KEYS = 32, AD_THREADS = 128, AD_MAXSPLIT = 64;   // up to 2048 keys per row
+constexpr int AD_MAXG = 16;        // (query, head) pairs of one kv group handled together: G * queries per row <= 16
 
 struct AttnDecDev {
     const float *q; int64_t ldq;
     const float *k, *v; int64_t ldk;
+    const float *k2, *v2; int64_t ldk2; const int *k2_start;      // optional second key segment (this pass's own tokens)
     float *out; float *out_lo; int out_fmt; int64_t ldo;
     const int *q_start, *k_start, *k_len;
     const int *step_d; int64_t len_step;
@@ -39,20 +43,30 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     __shared__ float mg[AD_MAXG], lg[AD_MAXG];
     __shared__ int s_last;
     const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
-    const int G = a.H / a.Hkv;
+    const int Gh = a.H / a.Hkv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_launch_dependents();          // programmatic dependent launch: the successor may start launching now,
     pdl_wait();                       // and nothing the predecessor wrote is read before this point
     const int *lens = a.k_len ? a.k_len + (a.step_d ? (int64_t)(*a.step_d) * a.len_step : 0) : nullptr;
-    const int k00 = a.k_start[row], n1 = lens ? lens[row] : a.k_start[row + 1] - k00;
+    const int k00 = a.k_start[row], n1s = lens ? lens[row] : a.k_start[row + 1] - k00;
+    const int k20 = a.k2_start ? a.k2_start[row] : 0, n2s = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
+    const int n1 = n1s + n2s;                          // keys of both segments, segment 1 first
     const int nsplit = (n1 + AD_KEYS - 1) / AD_KEYS;
     if (sp >= nsplit) return;
     const int k0 = sp * AD_KEYS;
-    const int q0 = a.q_start[row];
+    const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
+    const int G = Gh * nq;                             // virtual heads: vh = g * nq + qi
+    // row pointer of key j of the row (either segment)
+    auto krow = [&](int j) -> const float * {
+        return j < n1s ? a.k + (int64_t)(k00 + j) * a.ldk : a.k2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
+    auto vrow = [&](int j) -> const float * {
+        return j < n1s ? a.v + (int64_t)(k00 + j) * a.ldk : a.v2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
 
     for (int i = tid; i < G * HD; i += AD_THREADS) {
-        int g = i / HD, d = i % HD;
-        qs[g][d] = a.q[(int64_t)q0 * a.ldq + (kvh * G + g) * HD + d];
+        int vh = i / HD, d = i % HD;
+        qs[vh][d] = a.q[(int64_t)(q0 + vh % nq) * a.ldq + (kvh * Gh + vh / nq) * HD + d];
     }
     __syncthreads();
     {   // scores: four threads per key, each a quarter of the head dim
@@ -60,7 +74,7 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
         const bool valid = k0 + j < n1;
         float kr[DP];
         if (valid) {
-            const float4 *kp = (const float4 *)(a.k + (int64_t)(k00 + k0 + j) * a.ldk + kvh * HD + part * DP);
+            const float4 *kp = (const float4 *)(krow(k0 + j) + kvh * HD + part * DP);
 #pragma unroll
             for (int i = 0; i < DP / 4; i++) { float4 t = kp[i]; kr[4 * i] = t.x; kr[4 * i + 1] = t.y; kr[4 * i + 2] = t.z; kr[4 * i + 3] = t.w; }
         } else {
@@ -100,7 +114,7 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
 #pragma unroll
             for (int jj = 0; jj < KPG; jj++) {
                 const int j = grp * KPG + jj;
-                vr[jj] = (k0 + j < n1) ? a.v[(int64_t)(k00 + k0 + j) * a.ldk + kvh * HD + d] : 0.f;
+                vr[jj] = (k0 + j < n1) ? vrow(k0 + j)[kvh * HD + d] : 0.f;
             }
 #pragma unroll
             for (int jj = 0; jj < KPG; jj++) {
@@ -113,7 +127,7 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
         }
     }
     __syncthreads();
-    float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * G * (HD + 2);
+    float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * AD_MAXG * (HD + 2);
     for (int i = tid; i < G * HD; i += AD_THREADS) {
         int g = i / HD, d = i % HD;
         float o = 0.f;
@@ -135,10 +149,10 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     // thread, all in flight together), then the rescaling weights once per head, then the context columns
     // with independent loads -- a chain of dependent L2 round trips per split would dominate the kernel.
     __shared__ float wsm[AD_MAXSPLIT][AD_MAXG], lsm[AD_MAXSPLIT][AD_MAXG], Lg[AD_MAXG];
-    const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * G * (HD + 2);
+    const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * AD_MAXG * (HD + 2);
     for (int i = tid; i < nsplit * G; i += AD_THREADS) {
         int s = i / G, g = i % G;
-        const float *ps = base + ((int64_t)s * G + g) * (HD + 2);
+        const float *ps = base + ((int64_t)s * AD_MAXG + g) * (HD + 2);
         wsm[s][g] = __ldcg(ps); lsm[s][g] = __ldcg(ps + 1);
     }
     __syncthreads();
@@ -154,16 +168,16 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
         float O = 0.f;
         int s = 0;
         for (; s + 4 <= nsplit; s += 4) {
-            float o0 = __ldcg(base + ((int64_t)(s + 0) * G + g) * (HD + 2) + 2 + d);
-            float o1 = __ldcg(base + ((int64_t)(s + 1) * G + g) * (HD + 2) + 2 + d);
-            float o2 = __ldcg(base + ((int64_t)(s + 2) * G + g) * (HD + 2) + 2 + d);
-            float o3 = __ldcg(base + ((int64_t)(s + 3) * G + g) * (HD + 2) + 2 + d);
+            float o0 = __ldcg(base + ((int64_t)(s + 0) * AD_MAXG + g) * (HD + 2) + 2 + d);
+            float o1 = __ldcg(base + ((int64_t)(s + 1) * AD_MAXG + g) * (HD + 2) + 2 + d);
+            float o2 = __ldcg(base + ((int64_t)(s + 2) * AD_MAXG + g) * (HD + 2) + 2 + d);
+            float o3 = __ldcg(base + ((int64_t)(s + 3) * AD_MAXG + g) * (HD + 2) + 2 + d);
             O = fmaf(o0, wsm[s][g], O); O = fmaf(o1, wsm[s + 1][g], O); O = fmaf(o2, wsm[s + 2][g], O); O = fmaf(o3, wsm[s + 3][g], O);
         }
-        for (; s < nsplit; s++) O = fmaf(__ldcg(base + ((int64_t)s * G + g) * (HD + 2) + 2 + d), wsm[s][g], O);
+        for (; s < nsplit; s++) O = fmaf(__ldcg(base + ((int64_t)s * AD_MAXG + g) * (HD + 2) + 2 + d), wsm[s][g], O);
         const float L = Lg[g];
         const float r = L > 0.f ? O / L : 0.f;
-        const int64_t at = (int64_t)q0 * a.ldo + (kvh * G + g) * HD + d;
+        const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
         if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
         else a.out[at] = r;
     }
@@ -171,19 +185,20 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
 }
 
 bool attention_decode_supported(const AttnArgs &a) {
-    if (a.max_q != 1 || a.k2 || a.causal || a.window > 0) return false;
+    if (a.max_q < 1 || a.max_q > 4 || a.causal || a.window > 0) return false;      // a few queries per row, no mask
     if (a.hd != 16 && a.hd != 32 && a.hd != 64 && a.hd != 128) return false;
-    if (a.Hkv <= 0 || a.H % a.Hkv || a.H / a.Hkv > AD_MAXG) return false;
-    if (a.max_k1 <= 0 || a.max_k1 > AD_KEYS * AD_MAXSPLIT) return false;
+    if (a.Hkv <= 0 || a.H % a.Hkv || (a.H / a.Hkv) * a.max_q > AD_MAXG) return false;
+    if (a.max_k1 <= 0 || a.max_k1 + a.max_k2 > AD_KEYS * AD_MAXSPLIT) return false;
     if ((a.ldk1 & 3) || ((uintptr_t)a.k1 & 15)) return false;
+    if (a.k2 && ((a.ldk2 & 3) || ((uintptr_t)a.k2 & 15) || a.step_d)) return false;
     return true;
 }
 
 void attention_decode(const AttnArgs &a) {
     static float *part = nullptr; static size_t part_cap = 0;
     static unsigned *count = nullptr; static size_t count_cap = 0;
-    const int max_split = (int)cdiv(a.max_k1, AD_KEYS);
-    size_t need = (size_t)a.rows * a.H * max_split * (a.hd + 2);
+    const int max_split = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
+    size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
     if (need > part_cap) {
         if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
         part = (float *)dev_alloc(need * 4); part_cap = need;
@@ -195,7 +210,8 @@ void attention_decode(const AttnArgs &a) {
         CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
     }
     AttnDecDev d;
-    d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
+    d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1;
+    d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
     d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
     d.step_d = a.step_d; d.len_step = a.k1_len_step;
     d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split;

@@ -121,6 +121,23 @@ def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name):
     assert np.array_equal(cuda.to_host(od, q.shape), got[2])
 
 
+def test_split_key_attention_with_a_few_queries_and_two_key_segments(cuda):
+    # the first NCP levels: 1 or 4 new tokens per row attend to the cached prefix and to themselves
+    rng = np.random.default_rng(77)
+    qlens, k1lens, H, Hkv = [1, 4, 3, 4], [250, 3, 77, 1], 8, 2
+    off = lambda lens: np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    qs, k1s, k2s = off(qlens), off(k1lens), off(qlens)
+    q = rng.standard_normal((qs[-1], H * 64)).astype(np.float32)
+    kv1 = rng.standard_normal((k1s[-1], 2 * Hkv * 64)).astype(np.float32)
+    kv2 = rng.standard_normal((k2s[-1], 2 * Hkv * 64)).astype(np.float32)
+    want = _want(q, kv1, kv2, qs, k1s, k2s, H, Hkv, 0, 0)
+    qd, k1d, k2d = cuda.to_backend(q), cuda.to_backend(kv1), cuda.to_backend(kv2)
+    od = cuda.alloc(q.size)
+    rc = cuda.ncmb_attention_check(qd, k1d, k2d, od, qs.ctypes.data, k1s.ctypes.data, k2s.ctypes.data, len(qlens), H, Hkv, 0, 0, 2)
+    assert rc == 0
+    assert np.abs(cuda.to_host(od, q.shape) - want).max() < 4e-6
+
+
 def test_shapes_outside_the_tensor_core_kernel_are_reported_not_rerouted(cuda):
     # the kernel keeps at most 288 padded keys of a row resident
     qs = np.array([0, 64], np.int32)
