@@ -454,7 +454,7 @@ def run_lm_arm(args):
     tmp = tempfile.TemporaryDirectory()
     conf, wt = synth.write_lm(spec, tmp.name)
     cfg = lib.load_config(conf)
-    m = lib.ncmb_lm_open(cfg, wt.encode(), int(spec.kind == "qwen"), 0)
+    m = lib.ncmb_lm_open(cfg, wt.encode(), int(spec.kind == "qwen"), int(spec.bf16_round))
     prompts = np.ascontiguousarray(synth.lm_prompts(spec, B, w["prompt"], 5))
     out = np.zeros((B, w["n_new"]), np.int32)
 

@@ -320,7 +320,10 @@ void ncmb_vq_nearest_dev(VQState *vq, int level, const float *x_dev, long long n
 
 /* Batched GPT-2 / Qwen2 decoding with a KV cache. The reference decodes one
  * prompt per process and recomputes the whole context per token
- * (gpt2.c:179-202, qwen.c:209-231); results here equal B independent runs of it. */
+ * (gpt2.c:179-202, qwen.c:209-231); results here equal B independent runs of it.
+ * bf16_weights != 0: the file holds values already rounded to bf16 (stored as fp32, which is how the
+ * fp32-only reference consumes them); every projection matrix whose elements all are bf16 values gets an
+ * exact 2-byte copy that decode steps stream instead of the fp32 one -- same results, half the bytes. */
 typedef struct NcmbLM NcmbLM;
 NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights);
 void   ncmb_lm_close(NcmbLM *m);

@@ -129,6 +129,8 @@ struct GemmArgs {
     //    (the K|V part of a fused QKV projection going straight into the cache)
     int ln_kind = 0; const float *ln_w = nullptr, *ln_b = nullptr; float ln_eps = 0.f;
     float *y2 = nullptr; int y2_col0 = 0; int64_t ldy2 = 0; const int *y2_step_d = nullptr; int64_t y2_step = 0;
+    //  * W16: an exact bf16 copy of W ([N][K]); the GEMV kernel streams it instead of W (other engines ignore it)
+    const unsigned short *W16 = nullptr;
     // nearest-row search instead of a stored product (tensor-core engine only): for every x row, the
     // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
     const float *argmin_colnorm = nullptr;
@@ -247,6 +249,8 @@ struct BlockWeights {
     const float *fcw = nullptr, *fcb = nullptr;        // ungated [Hh][C]; gated [2*Hh][C] (gate rows, then up rows)
     const float *fcw_il = nullptr, *fcb_il = nullptr;  // gated only: gate/up rows interleaved (fused gated epilogue)
     const float *pw = nullptr, *pb = nullptr;          // [C][Hh]
+    // exact bf16 copies of the four matrices (decode steps stream these), or null
+    const unsigned short *qkvw16 = nullptr, *ow16 = nullptr, *fcw16 = nullptr, *pw16 = nullptr;
     int Hh = 0, gated = 0, act = ACT_GELU;
 };
 struct BlockBufs { float *ln, *qkv, *ctx, *mlp, *h; };   // [n][C], [n][C+2kvd], [n][C], [n][Hh or 2Hh], [n][Hh]
@@ -269,6 +273,8 @@ struct AttnPlan {
 void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights &w, const BlockBufs &b, const AttnPlan &p);
 void apply_norm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, int kind, float eps);
 void apply_norm_split(const float *x, const float *w, const float *b, float *y, float *y_lo, int64_t rows, int C, int kind, float eps, int fmt);
+// [rows][cols] fp32 -> bf16 copy when every element is exactly representable in bf16, else null (new device buffer)
+unsigned short *dev_bf16_exact(const float *w, int64_t n);
 void make_gated_interleaved(BlockWeights &w, int C, std::vector<void *> &owned);   // fills fcw_il / fcb_il from fcw / fcb
 
 // weight lookup helpers

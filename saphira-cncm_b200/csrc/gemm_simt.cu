@@ -27,6 +27,7 @@ struct GemmDev {
     int vec;        // 1: K % 4 == 0 and x / W rows are 16-byte aligned
     int ln_kind; const float *ln_w, *ln_b; float ln_eps;
     float *y2; int y2_col0; int64_t ldy2; const int *y2_step_d; int64_t y2_step;
+    const unsigned short *W16;      // optional exact bf16 copy of W (GEMV kernel only): half the bytes to stream
 };
 
 // ---- tiled kernel: BM x BN output tile per CTA, BK-deep stages, TMxTN per thread ----
@@ -217,6 +218,16 @@ __global__ void __launch_bounds__(256) k_gemm_skinny(GemmDev a) {
 // (griddepcontrol.launch_dependents), requests the weights of its first GV_PF k-steps -- which no kernel of a
 // decode step writes -- and only then waits for its predecessor (griddepcontrol.wait) before touching x. So
 // the launch latency and the DRAM latency of the weight stream run under the previous kernel. ----
+// four consecutive weights of row `row` at column k: fp32, or bf16 widened exactly (bits << 16)
+__device__ __forceinline__ float4 gv_w4(const GemmDev &a, int64_t row, int k) {
+    if (a.W16) {
+        const uint2 u = __ldg((const uint2 *)(a.W16 + row * a.K + k));
+        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                           __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+    }
+    return __ldg((const float4 *)(a.W + row * a.K + k));
+}
+
 template <int MT, int GV_NC, int GV_PF>
 __global__ void __launch_bounds__(256) k_gemv(GemmDev a) {
     __shared__ float red[8][MT][GV_NC];
@@ -224,16 +235,16 @@ __global__ void __launch_bounds__(256) k_gemv(GemmDev a) {
     const int n0 = blockIdx.x * GV_NC;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_launch_dependents();
-    const float *wr[GV_NC];
+    int64_t wr[GV_NC];                                   // weight rows of this CTA's columns
 #pragma unroll
-    for (int c = 0; c < GV_NC; c++) wr[c] = a.W + (int64_t)min(n0 + c, a.N - 1) * a.K;
+    for (int c = 0; c < GV_NC; c++) wr[c] = min(n0 + c, a.N - 1);
     float4 wpre[GV_PF][GV_NC];
 #pragma unroll
     for (int p = 0; p < GV_PF; p++) {
         const int k = tid * 4 + p * 1024;
         if (k < a.K) {
 #pragma unroll
-            for (int c = 0; c < GV_NC; c++) wpre[p][c] = __ldg((const float4 *)(wr[c] + k));
+            for (int c = 0; c < GV_NC; c++) wpre[p][c] = gv_w4(a, wr[c], k);
         }
     }
     pdl_wait();
@@ -323,7 +334,7 @@ __global__ void __launch_bounds__(256) k_gemv(GemmDev a) {
         for (int k = tid * 4 + GV_PF * 1024; k < a.K; k += 1024) {
             float4 w[GV_NC];
 #pragma unroll
-            for (int c = 0; c < GV_NC; c++) w[c] = __ldg((const float4 *)(wr[c] + k));
+            for (int c = 0; c < GV_NC; c++) w[c] = gv_w4(a, wr[c], k);
             kstep(k, w);
         }
 #pragma unroll
@@ -365,6 +376,7 @@ void gemm_simt(const GemmArgs &g) {
     d.y = g.y; d.ldy = g.ldy ? g.ldy : g.N;
     d.M = g.M; d.N = g.N; d.K = g.K; d.act = g.act;
     d.vec = (g.K % 4 == 0) && (d.ldx % 4 == 0) && (((uintptr_t)g.x & 15) == 0) && (((uintptr_t)g.W & 15) == 0);
+    d.W16 = (g.M <= 16 && d.vec) ? g.W16 : nullptr;
     d.ln_kind = g.ln_kind; d.ln_w = g.ln_w; d.ln_b = g.ln_b; d.ln_eps = g.ln_eps;
     d.y2 = g.y2; d.y2_col0 = g.y2_col0; d.ldy2 = g.ldy2; d.y2_step_d = g.y2_step_d; d.y2_step = g.y2_step;
     if ((g.ln_kind || g.y2) && !(g.M <= 16 && d.vec)) fatal("gemm_simt: fused norm / second output on a call the GEMV kernel does not take");

@@ -26,6 +26,7 @@ struct NcmbLM {
     int is_qwen = 0;
     int NL = 0, H = 0, nkv = 0, C = 0, hd = 0, I = 0, n_ctx = 0, V = 0, eos = -1;
     const float *wte = nullptr, *wpe = nullptr, *lnfw = nullptr, *lnfb = nullptr;
+    const unsigned short *wte16 = nullptr;      // exact bf16 copy of the embedding / head matrix (bf16 weight files)
     float *cosb = nullptr, *sinb = nullptr;
     std::vector<BlockWeights> blocks;
     std::vector<void *> owned;
@@ -48,7 +49,6 @@ static const float *maybe(WeightStore *ws, const char *fmt, int li, const char *
 
 extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights) {
     ensure_device();
-    (void)bf16_weights;      // weights are used as stored; files already rounded to bf16 load unchanged
     NcmbLM *m = new NcmbLM();
     m->cfg = *c; m->is_qwen = is_qwen;
     if (weights_load(&m->ws, weights)) { delete m; return nullptr; }
@@ -133,6 +133,24 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
         upload(m->cosb, hc.data(), hc.size() * 4); upload(m->sinb, hs.data(), hs.size() * 4);
         m->owned.push_back(m->cosb); m->owned.push_back(m->sinb);
     }
+    // bf16 weight files (values already rounded to bf16, stored as fp32): decode steps are bound by streaming the
+    // weights, so the matrices get an exact 2-byte copy that the GEMV kernel reads instead -- same values, half
+    // the bytes. A matrix with any element that is not a bf16 value keeps its fp32 path.
+    if (bf16_weights) {
+        const int kvd2 = m->nkv * m->hd;
+        auto shadow = [&](const float *w, int64_t n) -> const unsigned short * {
+            unsigned short *p = dev_bf16_exact(w, n);
+            if (p) m->owned.push_back(p);
+            return p;
+        };
+        for (auto &bw : m->blocks) {
+            bw.qkvw16 = shadow(bw.qkvw, (int64_t)(m->C + 2 * kvd2) * m->C);
+            bw.ow16 = shadow(bw.ow, (int64_t)m->C * m->C);
+            bw.fcw16 = shadow(bw.fcw, (int64_t)(bw.gated ? 2 : 1) * bw.Hh * m->C);
+            bw.pw16 = shadow(bw.pw, (int64_t)m->C * bw.Hh);
+        }
+        m->wte16 = shadow(m->wte, (int64_t)m->V * m->C);
+    }
     CUDA_CHECK(cudaStreamSynchronize(stream()));
     return m;
 }
@@ -216,7 +234,7 @@ void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
 void lm_head(LMRun &r, const float *h, int64_t rows, float *logits) {
     NcmbLM *m = r.m;
     GemmArgs g;
-    g.x = h; g.ldx = m->C; g.W = m->wte; g.y = logits; g.ldy = m->V; g.M = rows; g.N = m->V; g.K = m->C;
+    g.x = h; g.ldx = m->C; g.W = m->wte; g.W16 = m->wte16; g.y = logits; g.ldy = m->V; g.M = rows; g.N = m->V; g.K = m->C;
     g.ln_kind = m->is_qwen ? 2 : 1; g.ln_w = m->lnfw; g.ln_b = m->lnfb; g.ln_eps = m->is_qwen ? 1e-6f : 1e-5f;
     if (!gemv_fusable(g)) {        // many rows: stand-alone norm, tensor-core GEMM
         apply_norm(h, m->lnfw, m->lnfb, r.bufs.ln, rows, m->C, m->is_qwen ? NORM_RMS : NORM_LAYER, m->is_qwen ? 1e-6f : 1e-5f);

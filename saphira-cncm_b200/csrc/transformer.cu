@@ -47,6 +47,28 @@ __global__ void k_kv_store(const float *__restrict__ src, int64_t ldsrc, float *
     }
 }
 
+__global__ void k_to_bf16_exact(const float *__restrict__ w, unsigned short *__restrict__ o, int64_t n, int *bad) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        unsigned u = __float_as_uint(w[i]);
+        if (u & 0xffffu) *bad = 1;                     // low mantissa bits set: not a bf16 value
+        o[i] = (unsigned short)(u >> 16);
+    }
+}
+unsigned short *dev_bf16_exact(const float *w, int64_t n) {
+    if (!w || n <= 0) return nullptr;
+    unsigned short *o = (unsigned short *)dev_alloc((size_t)n * 2);
+    int *bad = (int *)dev_alloc(4);
+    CUDA_CHECK(cudaMemsetAsync(bad, 0, 4, stream()));
+    int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+    LAUNCH(k_to_bf16_exact, (unsigned)(g > cap ? cap : g), 256, 0, w, o, n, bad);
+    int h = 0;
+    CUDA_CHECK(cudaMemcpyAsync(&h, bad, 4, cudaMemcpyDeviceToHost, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    dev_free(bad);
+    if (h) { dev_free(o); return nullptr; }
+    return o;
+}
+
 // Scratch for the lo halves of the block's GEMM inputs in three-pass mode (ln, ctx, hidden).
 static Workspace &block_lo_ws() { static Workspace w; return w; }
 
@@ -79,6 +101,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     static const bool fuse_small = !getenv("NCM_B200_NO_GEMV_FUSE");
     const bool small = fuse_small && !split && gemv_fusable(g);
     bool kv_written = false;
+    g.W16 = w.qkvw16;
     if (small) {
         if (p.kv_store && !w.qnw && !p.cos_t && p.kv_rows_per_seq == 1) {
             g.y2 = p.kv_store; g.y2_col0 = C; g.ldy2 = p.kv_seq_pitch; g.y2_step_d = p.step_d; g.y2_step = p.kv_store_step;
@@ -120,7 +143,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     // x += ctx Wo^T + bo
     g = GemmArgs();
     g.x_fmt = fmt;
-    g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
+    g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.W16 = w.ow16; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
     gemm(g);
     g = GemmArgs();
     g.ldx = C; g.M = ntok; g.K = C;
@@ -141,19 +164,19 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
             gemm(t);
         } else {
             g.x_lo = ln_lo;
-            g.W = w.fcw; g.bias = w.fcb; g.y = b.mlp; g.N = 2 * w.Hh; g.ldy = 2 * w.Hh;
+            g.W = w.fcw; g.W16 = w.fcw16; g.bias = w.fcb; g.y = b.mlp; g.N = 2 * w.Hh; g.ldy = 2 * w.Hh;
             gemm(g);
             glu_combine(b.mlp, b.h, ntok, w.Hh, w.act);
             h_lo = nullptr;
         }
     } else {
-        g.W = w.fcw; g.bias = w.fcb; g.y = b.h; g.y_lo = h_lo; g.N = w.Hh; g.ldy = w.Hh; g.act = w.act;
+        g.W = w.fcw; g.W16 = w.fcw16; g.bias = w.fcb; g.y = b.h; g.y_lo = h_lo; g.N = w.Hh; g.ldy = w.Hh; g.act = w.act;
         if (!tc_ok(g)) { g.y_lo = nullptr; h_lo = nullptr; }
         gemm(g);
     }
     g = GemmArgs();
     g.x_fmt = fmt;
-    g.x = b.h; g.x_lo = h_lo; g.ldx = w.Hh; g.W = w.pw; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
+    g.x = b.h; g.x_lo = h_lo; g.ldx = w.Hh; g.W = w.pw; g.W16 = w.pw16; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
     gemm(g);
 }
 

@@ -271,6 +271,8 @@ LM_SPECS = {
     # head dim 64 (the decode-attention and GEMV kernels at the models' real head size)
     "gpt2_hd64": lambda synth: synth.LMSpec("gpt2_hd64", "gpt2", 2, 128, 2, 2, 512, 300, 64, rand_affine=1),
     "qwen_hd64": lambda synth: synth.LMSpec("qwen_hd64", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, rand_affine=1),
+    # weights rounded to bf16 in the file, opened with bf16_weights = 1: decode steps stream the exact 2-byte copies
+    "qwen_hd64_bf16": lambda synth: synth.LMSpec("qwen_hd64_bf16", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, bf16_round=1),
     # the same two through the persistent cooperative decode kernel (rotary pairs, grouped heads, gated MLP)
     "gpt2_hd64_persistent": lambda synth: synth.LMSpec("gpt2_hd64", "gpt2", 2, 128, 2, 2, 512, 300, 64, rand_affine=1),
     "qwen_hd64_persistent": lambda synth: synth.LMSpec("qwen_hd64", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, rand_affine=1),
@@ -286,7 +288,7 @@ def test_decoder_lm_logits_and_generation(cuda, tmp, kind):
     is_qwen = spec.kind == "qwen"
     conf, w = synth.write_lm(spec, tmp)
     cfg = cuda.load_config(conf)
-    m = cuda.ncmb_lm_open(cfg, w.encode(), int(is_qwen), 0)
+    m = cuda.ncmb_lm_open(cfg, w.encode(), int(is_qwen), int(spec.bf16_round))
     assert m
     om = orc.LM(conf, w, is_qwen)
     prompts = synth.lm_prompts(spec, 3, 9, 3)
