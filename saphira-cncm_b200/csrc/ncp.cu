@@ -72,6 +72,7 @@ struct NCPGen {
     double *cnt_d = nullptr, *cnt0_d = nullptr, *uni_d = nullptr, *allow_d = nullptr;
     size_t uni_off = 0;
     unsigned long long seed = 0;
+    const std::vector<double> *uni_given = nullptr;    // wave of a larger batch: this wave's slice of the batch's RNG stream
     int prefix_done = 0;
     int phase = 0, li = 0, level_accum = 0, out_off = 0, last_n = 0;
     float *cap_host = nullptr; size_t cap_row = 0, cap_off = 0;
@@ -373,9 +374,14 @@ static void gen_plan(NCPGen *g, const int *l0, const int *prefix_ids, const doub
     }
     std::vector<double> uni;
     if (ndraw && ctx().rng_mode == 0) {
-        uni.resize(ndraw);
-        unsigned long long st = g->seed ? g->seed : 0x9E3779B97F4A7C15ULL;
-        for (size_t i = 0; i < ndraw; i++) uni[i] = (double)(rng_next(&st) >> 11) * (1.0 / 9007199254740992.0);
+        if (g->uni_given) {
+            if (g->uni_given->size() != ndraw) fatal("ncp_generate: wave RNG slice has %zu draws, expected %zu", g->uni_given->size(), ndraw);
+            uni = *g->uni_given;
+        } else {
+            uni.resize(ndraw);
+            unsigned long long st = g->seed ? g->seed : 0x9E3779B97F4A7C15ULL;
+            for (size_t i = 0; i < ndraw; i++) uni[i] = (double)(rng_next(&st) >> 11) * (1.0 / 9007199254740992.0);
+        }
     }
     // ---- workspace: one sizing pass over the layout, then the real one ----
     int64_t nmax = g->ntok > (int64_t)Bm * g->Lmax ? g->ntok : (int64_t)Bm * g->Lmax;
@@ -623,12 +629,30 @@ void ncp_gen_abort(NCPGen *g) {
     delete g;
 }
 
-int *ncmb_ncp_generate_ex(NCPState *m, const int *l0, const int *prefix_ids, int B,
-                          float temp, int top_k, float top_p, float cfg_scale,
-                          float freq, float mu, float adj_a, int adj_w, float adj_d,
-                          const double *allow, unsigned long long seed, float *logits_host) {
-    ensure_device();
-    if (B <= 0) fatal("ncp_generate: batch %d", B);
+// Device bytes one generate over B sequences needs (upper bound: every prefix position kept), following the
+// workspace layout of gen_plan plus the split-pair scratch of the blocks.
+static double gen_bytes_bound(NCPState *m, int B, bool use_cfg, bool capture) {
+    const NCMConfig *c = &m->cfg;
+    const int nlev = c->n_qlevels, C = m->C, D = m->D, kvd = m->nkv * m->hd, Wq = C + 2 * kvd, Hh = m->Hh;
+    int Lmax = 0, Vmax = 0, total = 0;
+    for (int k = 0; k < nlev; k++) { Lmax = std::max(Lmax, c->levels[k]); total += c->levels[k]; }
+    for (int k = 0; k < m->n_tgt; k++) Vmax = std::max(Vmax, c->vocab_size[k]);
+    const double Bm = use_cfg ? 2.0 * B : B;
+    const double ntok = (double)B * m->P + (use_cfg ? B : 0), nmax = std::max(ntok, Bm * Lmax);
+    bool gated = false;
+    for (auto &bw : m->blocks) gated |= (bw.gated != 0);
+    double fl = ntok * C + nmax * (2.0 * C + Wq + (gated ? 2.0 * Hh : 0.0) + Hh) + m->NL * ntok * 2.0 * kvd
+              + Bm * Lmax * (C + 2.0 * D + (capture ? 2.0 : 1.0) * Vmax) + 6.0 * Bm * m->vq->L * D
+              + nmax * (2.0 * C + Hh)                                   /* split-pair scratch of the blocks */
+              + 2.0 * ntok + Bm * (total + 70.0) + B * (double)total;   /* index arrays */
+    double db = 2.0 * Bm * Vmax + Bm * total;
+    return 4.0 * fl + 8.0 * db + (64 << 20);
+}
+
+static int *gen_one(NCPState *m, const int *l0, const int *prefix_ids, int B,
+                    float temp, int top_k, float top_p, float cfg_scale,
+                    float freq, float mu, float adj_a, int adj_w, float adj_d,
+                    const double *allow, unsigned long long seed, float *logits_host, const std::vector<double> *uni) {
     NCPGen *g = new NCPGen();
     g->m = m; g->B = B;
     g->temp = temp; g->top_k = top_k; g->top_p = top_p; g->cfg_scale = cfg_scale;
@@ -636,12 +660,83 @@ int *ncmb_ncp_generate_ex(NCPState *m, const int *l0, const int *prefix_ids, int
     g->seed = seed;
     g->use_cfg = cfg_scale > 0;
     g->Bm = g->use_cfg ? 2 * B : B;
-    if (g->use_cfg && m->cfg.prefix_pad_token_id < 0)
-        fatal("classifier-free guidance needs model.prefix_pad_token_id >= 0 (the null prefix is built from it)");
     g->cap_host = logits_host;
+    g->uni_given = uni;
     gen_plan(g, l0, prefix_ids, allow);
     while (!ncp_gen_step(g, nullptr, nullptr)) { }
     return ncp_gen_finish(g);
+}
+
+// A batch that does not fit the GPU's free memory runs as waves of rows. Rows are independent, so the result is
+// the same as one pass; in the reference-stream RNG mode every wave gets exactly the draws its rows would have
+// consumed in the full batch (the stream is laid out level by level, row by row), in the counter mode the
+// row offset does it. NCM_B200_WAVE_MB overrides the memory budget, NCM_B200_WAVE_ROWS caps the wave size (testing).
+int *ncmb_ncp_generate_ex(NCPState *m, const int *l0, const int *prefix_ids, int B,
+                          float temp, int top_k, float top_p, float cfg_scale,
+                          float freq, float mu, float adj_a, int adj_w, float adj_d,
+                          const double *allow, unsigned long long seed, float *logits_host) {
+    ensure_device();
+    if (B <= 0) fatal("ncp_generate: batch %d", B);
+    const NCMConfig *c = &m->cfg;
+    const bool use_cfg = cfg_scale > 0;
+    if (use_cfg && c->prefix_pad_token_id < 0)
+        fatal("classifier-free guidance needs model.prefix_pad_token_id >= 0 (the null prefix is built from it)");
+    size_t free_b = 0, total_b = 0;
+    CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
+    double budget = 0.85 * ((double)free_b + (double)m->work.cap);
+    if (const char *e = getenv("NCM_B200_WAVE_MB")) budget = atof(e) * 1048576.0;
+    int Bw = B;
+    if (gen_bytes_bound(m, B, use_cfg, logits_host != nullptr) > budget) {
+        int lo = 1, hi = B;                                  // largest wave that fits
+        while (lo < hi) { int mid = (lo + hi + 1) / 2; if (gen_bytes_bound(m, mid, use_cfg, logits_host != nullptr) <= budget) lo = mid; else hi = mid - 1; }
+        Bw = lo;
+    }
+    if (const char *e = getenv("NCM_B200_WAVE_ROWS")) { int v = atoi(e); if (v >= 1 && v < Bw) Bw = v; }   // testing: force waves
+    if (Bw >= B) return gen_one(m, l0, prefix_ids, B, temp, top_k, top_p, cfg_scale, freq, mu, adj_a, adj_w, adj_d, allow, seed, logits_host, nullptr);
+    if (logits_host) fatal("ncp_generate_ex: logits capture needs the batch in one wave (%d rows fit, %d asked)", Bw, B);
+
+    const int nlev = c->n_qlevels, P = m->P, l0len = c->levels[0];
+    int total = 0;
+    for (int k = 0; k < nlev; k++) total += c->levels[k];
+    const int Bm = use_cfg ? 2 * B : B;
+    const bool sample_l0 = !l0 && c->query_level0;
+    // the whole batch's stream, then one slice per wave
+    std::vector<double> all;
+    if (temp > 0 && ctx().rng_mode == 0) {
+        size_t nd = (sample_l0 ? (size_t)Bm * l0len : 0);
+        for (int k = 1; k < nlev; k++) nd += (size_t)B * c->levels[k];
+        all.resize(nd);
+        unsigned long long st = seed ? seed : 0x9E3779B97F4A7C15ULL;
+        for (size_t i = 0; i < nd; i++) all[i] = (double)(rng_next(&st) >> 11) * (1.0 / 9007199254740992.0);
+    }
+    int *out = (int *)malloc((size_t)B * total * sizeof(int));
+    if (!out) fatal("oom codes");
+    const long long row_off0 = ctx().row_offset;
+    for (int r0 = 0; r0 < B; r0 += Bw) {
+        const int nb = std::min(Bw, B - r0);
+        std::vector<double> uni;
+        if (!all.empty()) {
+            size_t base = 0;
+            if (sample_l0) {                                  // level 0: rows 0..Bm-1 of the batch (conditional rows, then unconditional)
+                for (int b = 0; b < nb; b++) uni.insert(uni.end(), all.begin() + (size_t)(r0 + b) * l0len, all.begin() + (size_t)(r0 + b + 1) * l0len);
+                if (use_cfg)
+                    for (int b = 0; b < nb; b++) uni.insert(uni.end(), all.begin() + (size_t)(B + r0 + b) * l0len, all.begin() + (size_t)(B + r0 + b + 1) * l0len);
+                base = (size_t)Bm * l0len;
+            }
+            for (int k = 1; k < nlev; k++) {
+                const size_t Lk = c->levels[k];
+                uni.insert(uni.end(), all.begin() + base + (size_t)r0 * Lk, all.begin() + base + (size_t)(r0 + nb) * Lk);
+                base += (size_t)B * Lk;
+            }
+        }
+        ctx().row_offset = row_off0 + r0;
+        int *part = gen_one(m, l0 ? l0 + (size_t)r0 * l0len : nullptr, prefix_ids ? prefix_ids + (size_t)r0 * P : nullptr, nb,
+                            temp, top_k, top_p, cfg_scale, freq, mu, adj_a, adj_w, adj_d, allow, seed, nullptr, all.empty() ? nullptr : &uni);
+        memcpy(out + (size_t)r0 * total, part, (size_t)nb * total * sizeof(int));
+        free(part);
+    }
+    ctx().row_offset = row_off0;
+    return out;
 }
 
 int *ncp_generate(NCPState *m, const int *l0, const int *prefix_ids, int B,

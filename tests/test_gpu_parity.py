@@ -264,6 +264,26 @@ def test_quantizer_sweep_box_scale_codebook(cuda, tmp):
     print(f"box-scale nearest-code: {ties} near-ties in 512 sampled rows")
 
 
+def test_generate_in_waves_equals_one_pass(cuda, tmp):
+    """A batch that does not fit the GPU runs as waves of rows; sampled codes must not change (reference RNG stream
+    sliced per wave, CFG rows kept with their sequences)."""
+    import synth
+    spec = synth.spec_tiny()
+    conf, w = synth.write_ncp(spec, tmp)
+    pre = synth.ncp_prefixes(spec, 7, 21)
+    kw = dict(temp=0.9, top_k=6, top_p=0.95, cfg=1.3, freq=0.2, seed=77)
+    import capi
+    model = capi.NcpModel(cuda, conf, w)
+    try:
+        os.environ.pop("NCM_B200_WAVE_ROWS", None)
+        one = model.generate(pre, **kw)
+        for rows in (1, 3):
+            os.environ["NCM_B200_WAVE_ROWS"] = str(rows)
+            assert np.array_equal(model.generate(pre, **kw), one), rows
+    finally:
+        os.environ.pop("NCM_B200_WAVE_ROWS", None)
+
+
 LM_SPECS = {
     # head dim 16: every kernel of the generic path (GEMV, split-key attention, CUDA graph replay)
     "gpt2": lambda synth: synth.spec_gpt2_tiny(),
