@@ -683,7 +683,7 @@ int *ncmb_ncp_generate_ex(NCPState *m, const int *l0, const int *prefix_ids, int
         fatal("classifier-free guidance needs model.prefix_pad_token_id >= 0 (the null prefix is built from it)");
     size_t free_b = 0, total_b = 0;
     CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
-    double budget = 0.85 * ((double)free_b + (double)m->work.cap);
+    double budget = 0.6 * ((double)free_b + (double)m->work.cap);      // head room for the engines' own scratch and the caller
     if (const char *e = getenv("NCM_B200_WAVE_MB")) budget = atof(e) * 1048576.0;
     int Bw = B;
     if (gen_bytes_bound(m, B, use_cfg, logits_host != nullptr) > budget) {
