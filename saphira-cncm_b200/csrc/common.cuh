@@ -258,6 +258,8 @@ struct AttnPlan {
     const int *q_start = nullptr, *k1_start = nullptr, *k1_len = nullptr, *k2_start = nullptr;
     const float *k1 = nullptr, *v1 = nullptr; int64_t ldk1 = 0;   // null: segment 1 is this pass's own K/V
     int self_is_k2 = 0;                  // segment 2 = this pass's own K/V (k2_start = q_start)
+    const float *k2 = nullptr, *v2 = nullptr; int64_t ldk2 = 0;   // or an explicit second segment (k2_start required)
+    int max_k2 = 0; int64_t k2_total = 0;
     int rows = 0, max_q = 0, causal = 0, causal_off = 0, window = 0;
     const int *pos = nullptr; const float *cos_t = nullptr, *sin_t = nullptr;
     int64_t total_q = 0; double avg_keys = 0;

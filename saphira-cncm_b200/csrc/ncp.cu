@@ -322,6 +322,35 @@ static void level_pass(NCPGen *g, float *x, int Lc, int hi, int lev_slot) {
     head_logits(m, hi, g->bufs.ln, n, g->logits, g->bufs.ctx);
 }
 
+// The same for the teacher-forced forward with the block-causal pattern (reference src/ncp.c:361-404: a target
+// token sees the prefix and every target token of its own and of earlier levels). Levels are passed in order;
+// each layer keeps the levels' final K|V in a cache of its own (`lvlkv[li]`, [B][T][2*kvd]), so a level's keys are
+// that cache up to and including itself (segment 1, per-row length `len_d`) plus the cached prefix (segment 2).
+static void level_pass_causal(NCPGen *g, float *x, int Lc, int hi, int lev_slot, int off, std::vector<float *> &lvlkv,
+                              const int *seq_start_d, const int *len_d) {
+    NCPState *m = g->m;
+    int kvd = m->nkv * m->hd;
+    int64_t n = (int64_t)g->Bm * Lc;
+    AttnPlan p;
+    p.q_start = g->lev_start_d[lev_slot];
+    p.k1_start = seq_start_d; p.k1_len = len_d; p.ldk1 = 2 * kvd;
+    p.max_k1 = off + Lc; p.k1_total = (int64_t)g->Bm * m->T;
+    p.k2_start = g->row_start_d; p.ldk2 = 2 * kvd; p.max_k2 = g->max_row; p.k2_total = g->ntok;
+    p.rows = g->Bm; p.max_q = Lc;
+    p.pos = g->lev_pos_d[lev_slot];
+    if (m->cfg.use_rope) { p.cos_t = m->gcos[hi]; p.sin_t = m->gsin[hi]; }
+    p.total_q = n; p.avg_keys = (g->Bm ? (double)g->ntok / g->Bm : 0) + off + Lc;
+    p.kv_pitch = 2 * kvd; p.kv_rows_per_seq = Lc; p.kv_seq_pitch = (int64_t)m->T * 2 * kvd;
+    for (int li = 0; li < m->NL; li++) {
+        p.k1 = lvlkv[li]; p.v1 = lvlkv[li] + kvd;
+        p.k2 = g->kv[li]; p.v2 = g->kv[li] + kvd;
+        p.kv_store = lvlkv[li] + (size_t)off * 2 * kvd;
+        run_block(x, n, m->C, m->H, m->nkv, m->blocks[li], g->bufs, p);
+    }
+    layernorm(x, m->lnfw, m->lnfb, g->bufs.ln, n, m->C, 1e-6f);
+    head_logits(m, hi, g->bufs.ln, n, g->logits, g->bufs.ctx);
+}
+
 // x += conv(x) as the reference's GENERATE path computes it: the conv output stays in
 // [B][D][L] order and is added element i to element i onto the [B][L][D] tensor
 // (src/ncp.c:863-869, 1040-1045). Kept bit-compatible on purpose.
@@ -749,8 +778,9 @@ int *ncp_generate(NCPState *m, const int *l0, const int *prefix_ids, int B,
 
 // ------------------------------------------------------------------ teacher-forced forward
 // x: [B][P+T][D] (device), logits: [B][T][maxV] (device), unused vocabulary slots -inf
-// (reference src/ncp.c:480-647). Each target level attends to the prefix and to itself
-// (block-diagonal pattern), which is one level pass per level over the shared cache.
+// (reference src/ncp.c:480-647). Block-diagonal pattern: each target level attends to the prefix and to itself,
+// one level pass per level over the shared prefix cache. Block-causal pattern: also to every earlier level,
+// whose keys and values each layer keeps as the levels are passed in order.
 __global__ void k_scatter_logits(const float *__restrict__ lg, float *__restrict__ out, int B, int lk, int V, int T, int off, int maxV) {
     int64_t n = (int64_t)B * lk * V;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
@@ -763,8 +793,6 @@ void ncp_forward(NCPState *m, const float *x, const int *prefix_ids, float *logi
     ensure_device();
     StaticWeights sw;
     const NCMConfig *c = &m->cfg;
-    if (!c->attn_pattern_block_diag)
-        fatal("ncp_forward: block_causal attention pattern is not implemented in this build (block_diagonal only)");
     int P = m->P, T = m->T, S = P + T, C = m->C, D = m->D;
     NCPGen *g = new NCPGen();
     g->m = m; g->B = B; g->Bm = B;
@@ -790,6 +818,24 @@ void ncp_forward(NCPState *m, const float *x, const int *prefix_ids, float *logi
         }
     }
     prefix_pass(g);
+    // block-causal pattern: per-layer K|V of the target tokens, per-row starts and (per level) visible lengths
+    const bool causal = !c->attn_pattern_block_diag;
+    std::vector<float *> lvlkv;
+    int *seq_start_d = nullptr, *len_d = nullptr;
+    if (causal) {
+        const int kvd = m->nkv * m->hd;
+        for (int li = 0; li < m->NL; li++) lvlkv.push_back((float *)dev_alloc((size_t)B * T * 2 * kvd * 4 + 64));
+        std::vector<int> st(B + 1);
+        for (int b = 0; b <= B; b++) st[b] = b * T;
+        seq_start_d = (int *)dev_alloc((size_t)(B + 1) * 4);
+        len_d = (int *)dev_alloc((size_t)B * 4 * (m->n_tgt > 0 ? m->n_tgt : 1));
+        upload(seq_start_d, st.data(), st.size() * 4);
+        std::vector<int> ln((size_t)B * m->n_tgt);
+        int o = 0;
+        for (int k = 0; k < m->n_tgt; k++) { o += c->levels[k + m->lvl_first]; for (int b = 0; b < B; b++) ln[(size_t)k * B + b] = o; }
+        upload(len_d, ln.data(), ln.size() * 4);
+        CUDA_CHECK(cudaStreamSynchronize(stream()));
+    }
     int maxV = 0;
     for (int k = 0; k < m->n_tgt; k++) if (c->vocab_size[k] > maxV) maxV = c->vocab_size[k];
     fill_f32(logits, -INFINITY, (int64_t)B * T * maxV);
@@ -813,13 +859,17 @@ void ncp_forward(NCPState *m, const float *x, const int *prefix_ids, float *logi
         a.x = g->xout; a.ldx = D; a.W = m->wteW; a.bias = m->wteB; a.y = g->xlev; a.ldy = C; a.M = (int64_t)B * lk; a.N = C; a.K = D;
         gemm(a);
         add_rows_bcast(g->xlev, m->lvl_pos + (size_t)off * C, B, lk * C);
-        level_pass(g, g->xlev, lk, k, k + m->lvl_first);
+        if (causal) level_pass_causal(g, g->xlev, lk, k, k + m->lvl_first, off, lvlkv, seq_start_d, len_d + (size_t)k * B);
+        else level_pass(g, g->xlev, lk, k, k + m->lvl_first);
         int64_t n = (int64_t)B * lk * V;
         int64_t gsz = cdiv(n, 256);
         LAUNCH(k_scatter_logits, (unsigned)(gsz > 4096 ? 4096 : gsz), 256, 0, g->logits, logits, B, lk, V, T, off, maxV);
         off += lk;
     }
     CUDA_CHECK(cudaStreamSynchronize(stream()));
+    for (float *p : lvlkv) dev_free(p);
+    if (seq_start_d) dev_free(seq_start_d);
+    if (len_d) dev_free(len_d);
     delete g;
 }
 

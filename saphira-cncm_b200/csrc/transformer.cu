@@ -131,14 +131,15 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     else { a.k1 = kp; a.v1 = vp; a.ldk1 = Wq; }
     a.k1_start = p.k1_start; a.k1_len = p.k1_len;
     if (p.self_is_k2) { a.k2 = kp; a.v2 = vp; a.ldk2 = Wq; a.k2_start = p.k2_start ? p.k2_start : p.q_start; }
+    else if (p.k2) { a.k2 = p.k2; a.v2 = p.v2; a.ldk2 = p.ldk2; a.k2_start = p.k2_start; }
     a.out = b.ctx; a.out_lo = ctx_lo; a.out_fmt = fmt; a.ldo = C;
     a.q_start = p.q_start;
     a.rows = p.rows; a.H = H; a.Hkv = nkv; a.hd = hd; a.max_q = p.max_q;
     a.causal = p.causal; a.causal_off = p.causal_off; a.window = p.window;
     a.total_q = p.total_q; a.avg_keys = p.avg_keys;
-    a.max_k1 = p.max_k1; a.max_k2 = p.self_is_k2 ? p.max_q : 0;
+    a.max_k1 = p.max_k1; a.max_k2 = p.self_is_k2 ? p.max_q : (p.k2 ? p.max_k2 : 0);
     a.step_d = p.step_d; a.k1_len_step = p.k1_len_step;
-    a.q_total = ntok; a.k1_total = p.k1 ? p.k1_total : ntok; a.k2_total = p.self_is_k2 ? ntok : 0;
+    a.q_total = ntok; a.k1_total = p.k1 ? p.k1_total : ntok; a.k2_total = p.self_is_k2 ? ntok : (p.k2 ? p.k2_total : 0);
     attention(a);
     // x += ctx Wo^T + bo
     g = GemmArgs();

@@ -28,6 +28,7 @@ NCP_VARIANTS = {
                   qr_enabled=0, all_sampling=0, puc=0, pad_id=-1, eos_id=-1, swiglu=0,
                   mlp_hidden=0, n_kv_heads=4, enc_convs=1, enc_window=2, pre_quant_gn=4),
     "given_l0": dict(query_level0=0),
+    "causal": dict(attn_block_diag=0),           # block-causal level pattern in the teacher-forced forward
 }
 
 

@@ -59,7 +59,7 @@ def test_layer_kernels_match_oracle(cuda):
             _cmp_float(k, got[k], want[k], ATOL_KERNEL)
 
 
-@pytest.mark.parametrize("variant", ["plain", "full", "tied", "shared", "norope_relu2", "given_l0"])
+@pytest.mark.parametrize("variant", ["plain", "full", "tied", "shared", "norope_relu2", "given_l0", "causal"])
 def test_ncp_variant_matches_oracle(cuda, tmp, variant):
     got, want = {}, {}
     helpers.capi_ncp(cuda, got, tmp, variants=[variant], with_c1=False)
