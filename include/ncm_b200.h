@@ -230,6 +230,17 @@ int gpt2_cmd_gen(const NCMConfig *c, const char *weights, const char *adir,
 int qwen_cmd_gen(const NCMConfig *c, const char *weights, const char *adir,
                  const char *prompt, const char *ids_csv, int n_new,
                  float temp, int top_k, float top_p, unsigned long long seed);
+/* src/ncm.h:318-321, 329-332. *_cmd_ppl (gpt2.c:237-270, qwen.c:266-297): one document per line of texts_path,
+ * non-overlapping windows (n_ctx ids for GPT-2, 512 for Qwen2), prints
+ * "docs=%d tokens=%ld nll=%.6f ppl=%.6f". *_cmd_verify (gpt2.c:417-485, qwen.c:386-478): checks
+ * <stem>_tok.txt / <stem>_logits_<name>.f32 / <stem>_gen.txt / <stem>_ppl.txt of fixtures_dir with the
+ * reference's bounds and prints its "ok" / "FAIL" lines and "<STEM>-VERIFY PASS|FAIL (n checked)"; returns 1 on a
+ * failure. Without the host tokenizer linked in, a texts line is read as white-space separated token ids and
+ * the fixture checks that need text print "skip ..." (the logits check uses the fixture's ids and always runs). */
+int gpt2_cmd_ppl(const NCMConfig *c, const char *weights, const char *adir, const char *texts_path);
+int gpt2_cmd_verify(const NCMConfig *c, const char *weights, const char *adir, const char *fixtures_dir);
+int qwen_cmd_ppl(const NCMConfig *c, const char *weights, const char *adir, const char *texts_path);
+int qwen_cmd_verify(const NCMConfig *c, const char *weights, const char *adir, const char *fixtures_dir);
 
 /* ================================================================ additions
  * Entry points with no counterpart in the reference. */
@@ -339,6 +350,11 @@ int    ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, int n_new,
                         int eos, int *out);
 /* logits of one sequence: all positions ([T][V]) or the last one ([V]) to host */
 void   ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, float *out_host);
+/* Mean next-token negative log-likelihood of B windows (gpt2_nll gpt2.c:160-176, qwen_nll qwen.c:192-208, which
+ * take one window and read the [T][V] logits on the host). ids: host int[B][T]; lens: host int[B] ids used per
+ * window (NULL = T); nll_out: host double[B], the mean over lens[b] - 1 positions of
+ * -log(exp(l[next] - max) / sum exp(l - max) + 1e-30) in fp64. Logits never leave the device. */
+void   ncmb_lm_nll(NcmbLM *m, const int *ids, int B, int T, const int *lens, double *nll_out);
 
 #ifdef __cplusplus
 }

@@ -1650,6 +1650,24 @@ void orc_lm_logits(OrcLM *m, const int *ids, int T, int last_only, float *out) {
     else gpt2_logits(m, ids, T, last_only, out);
 }
 
+/* reference gpt2_nll src/gpt2.c:160-176 = qwen_nll src/qwen.c:192-208: mean over the T-1 shifted positions of
+ * -log(exp(l[next] - max) / sum_v exp(l[v] - max) + 1e-30), all in fp64, v in index order */
+double orc_lm_nll(OrcLM *m, const int *ids, int T) {
+    float *lg = falloc((size_t)T * m->V);
+    orc_lm_logits(m, ids, T, 0, lg);
+    double tot = 0;
+    for (int t = 0; t + 1 < T; t++) {
+        const float *row = lg + (size_t)t * m->V;
+        double mx = row[0];
+        for (int v = 1; v < m->V; v++) if (row[v] > mx) mx = row[v];
+        double den = 0;
+        for (int v = 0; v < m->V; v++) den += exp(row[v] - mx);
+        tot += -log(exp(row[ids[t + 1]] - mx) / den + 1e-30);
+    }
+    free(lg);
+    return tot / (T - 1);
+}
+
 /* reference src/gpt2.c:179-202, src/qwen.c:209-231 */
 int orc_lm_generate(OrcLM *m, const int *prompt, int np, int n_new, float temp,
                     int top_k, float top_p, uint64_t seed, int eos, int *out) {

@@ -83,6 +83,7 @@ def lib():
             "orc_lm_free": (None, [_P]),
             "orc_lm_vocab": (_I, [_P]),
             "orc_lm_logits": (None, [_P, _P, _I, _I, _P]),
+            "orc_lm_nll": (C.c_double, [_P, _P, _I]),
             "orc_lm_generate": (_I, [_P, _P, _I, _I, _F, _I, _F, _U64, _I, _P]),
         }
         for k, (r, a) in sig.items():
@@ -348,6 +349,11 @@ class LM:
         out = np.zeros((self.V,) if last_only else (T, self.V), np.float32)
         lib().orc_lm_logits(self.h, _p(ids), T, int(last_only), _p(out))
         return out
+
+    def nll(self, ids):
+        """mean next-token negative log-likelihood of one window (gpt2_nll / qwen_nll)"""
+        ids = _i(ids)
+        return float(lib().orc_lm_nll(self.h, _p(ids), ids.size))
 
     def generate(self, prompt, n_new, temp=0.0, top_k=0, top_p=1.0, seed=0, eos=-1):
         prompt = _i(prompt)

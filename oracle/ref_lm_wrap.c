@@ -19,6 +19,7 @@ void ref_gpt2_logits(void *h, const int *ids, int T, float *out) {
     float *lg = gpt2_forward(g, ids, T);
     mem_d2h(out, lg, (size_t)T * g->vocab_size * sizeof(float));
 }
+double ref_gpt2_nll(void *h, const int *ids, int T) { return gpt2_nll((GPT2 *)h, ids, T); }
 int ref_gpt2_generate(void *h, const int *prompt, int np, int n_new, float temp,
                       int top_k, float top_p, unsigned long long seed, int *out) {
     unsigned long long rng = seed ? seed : 0x12345678ULL;
@@ -41,6 +42,7 @@ void ref_qwen_logits(void *h, const int *ids, int T, int last_only, float *out) 
     float *lg = qwen_forward(m, ids, T, last_only);
     mem_d2h(out, lg, (size_t)(last_only ? 1 : T) * m->vocab_size * sizeof(float));
 }
+double ref_qwen_nll(void *h, const int *ids, int T) { return qwen_nll((QWEN *)h, ids, T); }
 int ref_qwen_generate(void *h, const int *prompt, int np, int n_new, float temp,
                       int top_k, float top_p, unsigned long long seed, int *out) {
     unsigned long long rng = seed ? seed : 0x12345678ULL;

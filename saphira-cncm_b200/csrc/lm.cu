@@ -7,6 +7,8 @@
 #include "lm_mega.cuh"
 #include "tc_common.cuh"
 
+#include <algorithm>
+#include <string>
 #include <vector>
 
 using namespace ncmb;
@@ -183,9 +185,11 @@ struct LMRun {
     float *mg_part = nullptr; unsigned *mg_count = nullptr, *mg_bar = nullptr; MegaLayer *mg_layers = nullptr;                      // kernel launches one replay of the captured step stands for
     unsigned long long *amax_d = nullptr;
     double *uni_cur = nullptr;
+    // likelihood runs: next-token target and result per token row
+    int64_t nll_rows = 0; int *tgt_d = nullptr; double *nll_d = nullptr;
 };
 
-void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
+void lm_layout(LMRun &r, Workspace &w, int n_new, int64_t logit_rows) {
     NcmbLM *m = r.m;
     int C = m->C, kvd = m->nkv * m->hd, Wq = C + 2 * kvd;
     int64_t nmax = (int64_t)r.B * r.np;
@@ -198,7 +202,7 @@ void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
     r.bufs.mlp = m->is_qwen ? w.get<float>((size_t)nmax * 2 * m->I) : nullptr;
     r.bufs.h = w.get<float>((size_t)nmax * m->I);
     r.last = w.get<float>((size_t)r.B * C);
-    r.logits = w.get<float>((size_t)(all_logits ? nmax : r.B) * m->V);
+    r.logits = w.get<float>((size_t)(logit_rows > r.B ? logit_rows : r.B) * m->V);
     size_t ss = sample_scratch_floats(r.B, m->V);
     r.samp_scr = ss ? w.get<float>(ss) : nullptr;
     r.ids_d = w.get<int>((size_t)nmax);
@@ -220,6 +224,7 @@ void lm_layout(LMRun &r, Workspace &w, int n_new, bool all_logits) {
     r.mg_count = w.get<unsigned>((size_t)r.B * m->nkv + 4);
     r.mg_bar = w.get<unsigned>(4);
     r.mg_layers = (MegaLayer *)w.get<unsigned char>(sizeof(MegaLayer) * (size_t)m->NL);
+    if (r.nll_rows > 0) { r.tgt_d = w.get<int>((size_t)r.nll_rows); r.nll_d = w.get<double>((size_t)r.nll_rows); }
 }
 
 void lm_embed(LMRun &r, const int *ids_d, const int *pos_d, int64_t n) {
@@ -310,15 +315,15 @@ void lm_decode_step(LMRun &r, const int *ids_d) {
     }
 }
 
-void lm_setup(LMRun &r, const int *prompts, int n_new, bool all_logits) {
+void lm_setup(LMRun &r, const int *prompts, int n_new, int64_t logit_rows) {
     NcmbLM *m = r.m;
     int B = r.B, np = r.np, cap = r.cap;
     Workspace sizing;
     sizing.measuring = true;
-    lm_layout(r, sizing, n_new, all_logits);
+    lm_layout(r, sizing, n_new, logit_rows);
     m->work.reserve(sizing.off + 4096);
     m->work.reset();
-    lm_layout(r, m->work, n_new, all_logits);
+    lm_layout(r, m->work, n_new, logit_rows);
     std::vector<int> pos((size_t)B * np), st(B + 1), s1(B + 1), ks(B + 1), pm((size_t)cap * B), lm((size_t)cap * B), lr(B);
     for (int b = 0; b < B; b++) for (int t = 0; t < np; t++) pos[(size_t)b * np + t] = t;
     for (int b = 0; b <= B; b++) { st[b] = b * np; s1[b] = b; ks[b] = b * cap; }
@@ -410,7 +415,7 @@ extern "C" int ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, in
     if (np + n_new - 1 > m->n_ctx) fatal("%s: context overflow (%d + %d > %d)", m->is_qwen ? "qwen" : "gpt2", np, n_new, m->n_ctx);
     LMRun r;
     r.m = m; r.B = B; r.np = np; r.cap = np + n_new;
-    lm_setup(r, prompts, n_new, false);
+    lm_setup(r, prompts, n_new, 0);
     if (temp > 0) {
         // every row replays the reference's stream for this seed: one draw per generated token
         std::vector<double> u((size_t)n_new * B);
@@ -531,7 +536,7 @@ extern "C" void ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, 
     if (T > m->n_ctx) fatal("%s: context overflow", m->is_qwen ? "qwen" : "gpt2");
     LMRun r;
     r.m = m; r.B = 1; r.np = T; r.cap = T;
-    lm_setup(r, ids, 0, !last_only);
+    lm_setup(r, ids, 0, last_only ? 1 : T);
     lm_prefill(r);
     if (last_only) {
         lm_head(r, r.x + (size_t)(T - 1) * m->C, 1, r.logits);
@@ -540,6 +545,86 @@ extern "C" void ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, 
         // ln buffer holds T rows; head over all positions
         lm_head(r, r.x, T, r.logits);
         mem_d2h(out_host, r.logits, (size_t)T * m->V * 4);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Next-token negative log-likelihood (reference gpt2_nll src/gpt2.c:160-176, qwen_nll src/qwen.c:192-208): the
+// reference brings the [T][V] logits to the host and takes, per position, -log(exp(l[target] - max) / sum + 1e-30)
+// in fp64. Here the logits stay on the device: one CTA per token row takes the row maximum and the fp64 sum of
+// exponentials, and one double per position goes back to the host, which adds them in position order as the
+// reference does.
+__global__ void __launch_bounds__(256) k_nll_rows(const float *__restrict__ logits, const int *__restrict__ target, int V,
+                                                  double *__restrict__ out) {
+    __shared__ double red[256];
+    const int64_t r = blockIdx.x;
+    const int tg = target[r];
+    if (tg < 0) { if (threadIdx.x == 0) out[r] = 0.0; return; }      // block-uniform: position without a successor
+    const float *row = logits + r * V;
+    float mxf = -INFINITY;
+    for (int v = threadIdx.x; v < V; v += 256) mxf = fmaxf(mxf, row[v]);
+    red[threadIdx.x] = (double)mxf;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) red[threadIdx.x] = fmax(red[threadIdx.x], red[threadIdx.x + s]);
+        __syncthreads();
+    }
+    const double mx = red[0];
+    __syncthreads();
+    double den = 0.0;
+    for (int v = threadIdx.x; v < V; v += 256) den += exp((double)row[v] - mx);
+    red[threadIdx.x] = den;
+    __syncthreads();
+    for (int s = 128; s > 0; s >>= 1) {
+        if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[r] = -log(exp((double)row[tg] - mx) / red[0] + 1e-30);
+}
+
+// B windows of up to T ids each (row pitch T, lens[b] ids used; lens == NULL means T everywhere); nll_out[b] = mean
+// over the lens[b] - 1 shifted positions. Padding sits behind the used ids, where causal attention cannot see it.
+extern "C" void ncmb_lm_nll(NcmbLM *m, const int *ids, int B, int T, const int *lens, double *nll_out) {
+    ensure_device();
+    if (B <= 0 || T <= 0) return;
+    StaticWeights sw;
+    if (T > m->n_ctx) fatal("%s: context overflow", m->is_qwen ? "qwen" : "gpt2");
+    const int64_t n = (int64_t)B * T;
+    int64_t chunk = ((int64_t)512 << 20) / ((int64_t)m->V * 4);          // head rows per pass: at most 512 MB of logits
+    if (chunk < 1) chunk = 1;
+    if (chunk > n) chunk = n;
+    std::vector<int> clean((size_t)n), tgt((size_t)n);
+    for (int b = 0; b < B; b++) {
+        const int len = lens ? lens[b] : T;
+        if (len < 0 || len > T) fatal("ncmb_lm_nll: window %d has length %d outside 0..%d", b, len, T);
+        for (int t = 0; t < T; t++) {
+            const int id = t < len ? ids[(size_t)b * T + t] : 0;
+            if (id < 0 || id >= m->V) fatal("ncmb_lm_nll: id %d out of range", id);
+            clean[(size_t)b * T + t] = id;
+            tgt[(size_t)b * T + t] = t + 1 < len ? ids[(size_t)b * T + t + 1] : -1;
+        }
+    }
+    LMRun r;
+    r.m = m; r.B = B; r.np = T; r.cap = T; r.nll_rows = n;
+    lm_setup(r, clean.data(), 0, chunk);
+    int *tgt_d = r.tgt_d;
+    double *nll_d = r.nll_d;
+    upload(tgt_d, tgt.data(), (size_t)n * 4);
+    lm_prefill(r);
+    for (int64_t r0 = 0; r0 < n; r0 += chunk) {
+        const int64_t rows = n - r0 < chunk ? n - r0 : chunk;
+        lm_head(r, r.x + r0 * m->C, rows, r.logits);
+        ProfScope ps(NCMB_K_SAMPLE, 0, (double)rows * m->V * 4);
+        k_nll_rows<<<(unsigned)rows, 256, 0, stream()>>>(r.logits, tgt_d + r0, m->V, nll_d + r0);
+        CUDA_CHECK(cudaGetLastError());
+    }
+    std::vector<double> h((size_t)n);
+    mem_d2h(h.data(), nll_d, (size_t)n * 8);
+    for (int b = 0; b < B; b++) {
+        const int len = lens ? lens[b] : T;
+        double tot = 0;
+        for (int t = 0; t + 1 < len; t++) tot += h[(size_t)b * T + t];
+        nll_out[b] = len > 1 ? tot / (len - 1) : 0.0;
     }
 }
 
@@ -592,4 +677,268 @@ extern "C" int gpt2_cmd_gen(const NCMConfig *c, const char *weights, const char 
 extern "C" int qwen_cmd_gen(const NCMConfig *c, const char *weights, const char *adir, const char *prompt, const char *ids_csv,
                             int n_new, float temp, int top_k, float top_p, unsigned long long seed) {
     return lm_cmd_gen(c, weights, adir, prompt, ids_csv, n_new, temp, top_k, top_p, seed, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// gpt2-ppl / qwen-ppl / gpt2-verify / qwen-verify (reference src/gpt2.c:237-270, 330-485; src/qwen.c:266-297,
+// 323-478): same files in, same lines out. Windows of a document are batched onto the device instead of being run
+// one by one. Text needs the reference's host tokenizer linked in (the weak tok_* symbols); without it a line of
+// the texts file is read as white-space separated token ids, and the fixture checks that need text are skipped.
+
+static int lm_line_ids(TokState *tok, const char *line, int *out, int cap) {
+    if (tok && tok_encode) return tok_encode(tok, line, out, cap);
+    int n = 0;
+    const char *p = line;
+    while (*p && n < cap) {
+        while (*p == ' ' || *p == '\t' || *p == ',') p++;
+        if (!*p) break;
+        char *end = nullptr;
+        long v = strtol(p, &end, 10);
+        if (end == p) return -1;                      // not a list of ids
+        out[n++] = (int)v;
+        p = end;
+    }
+    return n;
+}
+
+namespace {
+struct NllWindow { std::vector<int> ids; };
+
+// mean NLL per window, windows batched by a token budget; results in the order given
+std::vector<double> lm_nll_windows(NcmbLM *m, const std::vector<NllWindow> &ws) {
+    std::vector<double> out(ws.size());
+    const size_t budget = 16384;
+    size_t i = 0;
+    while (i < ws.size()) {
+        size_t j = i, T = 0;
+        while (j < ws.size()) {
+            size_t t2 = std::max(T, ws[j].ids.size());
+            if (j > i && t2 * (j - i + 1) > budget) break;
+            T = t2; j++;
+        }
+        const int B = (int)(j - i);
+        std::vector<int> ids((size_t)B * T, 0), lens(B);
+        for (int b = 0; b < B; b++) {
+            lens[b] = (int)ws[i + b].ids.size();
+            std::copy(ws[i + b].ids.begin(), ws[i + b].ids.end(), ids.begin() + (size_t)b * T);
+        }
+        ncmb_lm_nll(m, ids.data(), B, (int)T, lens.data(), out.data() + i);
+        i = j;
+    }
+    return out;
+}
+} // namespace
+
+static int lm_cmd_ppl(const NCMConfig *c, const char *weights, const char *adir, const char *texts_path, int is_qwen) {
+    NcmbLM *m = ncmb_lm_open(c, weights, is_qwen, 0);
+    if (!m) return 1;
+    TokState *tok = tok_load ? tok_load(c, adir) : nullptr;
+    FILE *f = fopen(texts_path, "r");
+    if (!f) { fprintf(stderr, "cannot open %s\n", texts_path); return 1; }
+    const int window = is_qwen ? 512 : m->n_ctx;        // qwen.c:284, gpt2.c:255
+    char *line = nullptr;
+    size_t cap = 0;
+    ssize_t len;
+    int ndoc = 0;
+    std::vector<int> ids(8192);
+    std::vector<NllWindow> ws;
+    while ((len = getline(&line, &cap, f)) >= 0) {
+        while (len > 0 && (line[len - 1] == '\n' || line[len - 1] == '\r')) line[--len] = 0;
+        if (!len) continue;
+        int n = lm_line_ids(tok, line, ids.data(), 8192);
+        if (n < 0) { fprintf(stderr, "%s: text lines need the host tokenizer linked in; give token ids\n", is_qwen ? "qwen-ppl" : "gpt2-ppl"); return 2; }
+        if (n < 2) continue;
+        for (int o = 0; o + 1 < n; o += window) {
+            int T = n - o > window ? window : n - o;
+            if (T < 2) break;
+            NllWindow w;
+            w.ids.assign(ids.begin() + o, ids.begin() + o + T);
+            ws.push_back(std::move(w));
+        }
+        ndoc++;
+    }
+    free(line);
+    fclose(f);
+    std::vector<double> nw = lm_nll_windows(m, ws);
+    double tot = 0;
+    long ntok = 0;
+    for (size_t i = 0; i < ws.size(); i++) {
+        const int T = (int)ws[i].ids.size();
+        tot += nw[i] * (T - 1);
+        ntok += T - 1;
+    }
+    double nll = tot / ntok;
+    printf("docs=%d tokens=%ld nll=%.6f ppl=%.6f\n", ndoc, ntok, nll, exp(nll));
+    if (tok && tok_free) tok_free(tok);
+    ncmb_lm_close(m);
+    return 0;
+}
+
+extern "C" int gpt2_cmd_ppl(const NCMConfig *c, const char *weights, const char *adir, const char *texts_path) {
+    return lm_cmd_ppl(c, weights, adir, texts_path, 0);
+}
+extern "C" int qwen_cmd_ppl(const NCMConfig *c, const char *weights, const char *adir, const char *texts_path) {
+    return lm_cmd_ppl(c, weights, adir, texts_path, 1);
+}
+
+namespace {
+int hex_nibble(char ch) {
+    if (ch >= '0' && ch <= '9') return ch - '0';
+    if (ch >= 'a' && ch <= 'f') return ch - 'a' + 10;
+    if (ch >= 'A' && ch <= 'F') return ch - 'A' + 10;
+    return -1;
+}
+bool hex_to_text(const char *h, std::string &out) {
+    size_t n = strlen(h);
+    if (n % 2) return false;
+    out.clear();
+    for (size_t i = 0; i < n; i += 2) {
+        int a = hex_nibble(h[i]), b = hex_nibble(h[i + 1]);
+        if (a < 0 || b < 0) return false;
+        out.push_back((char)((a << 4) | b));
+    }
+    return true;
+}
+std::vector<int> ids_of(const char *s, size_t cap) {
+    std::vector<int> v;
+    while (*s && v.size() < cap) {
+        while (*s == ' ') s++;
+        if (!*s || *s == '\n' || *s == '\r') break;
+        v.push_back(atoi(s));
+        while (*s && *s != ' ' && *s != '\n' && *s != '\r') s++;
+    }
+    return v;
+}
+// splits "a\tb\tc" in place; false when a tab is missing
+bool three_fields(char *line, char **b, char **c) {
+    char *t1 = strchr(line, '\t');
+    if (!t1) return false;
+    *t1 = 0;
+    char *t2 = strchr(t1 + 1, '\t');
+    if (!t2) return false;
+    *t2 = 0;
+    *b = t1 + 1; *c = t2 + 1;
+    return true;
+}
+} // namespace
+
+static int lm_cmd_verify(const NCMConfig *c, const char *weights, const char *adir, const char *dir, int is_qwen) {
+    const char *stem = is_qwen ? "qwen" : "gpt2";
+    NcmbLM *m = ncmb_lm_open(c, weights, is_qwen, 0);
+    if (!m) return 1;
+    TokState *tok = tok_load ? tok_load(c, adir) : nullptr;
+    const bool have_tok = tok && tok_encode;
+    int fails = 0, checked = 0;
+    char path[1024];
+    std::vector<char> line(65536);
+    const int V = m->V;
+    // 1 + 2: tokenisation and all-position logits
+    snprintf(path, sizeof(path), "%s/%s_tok.txt", dir, stem);
+    FILE *f = fopen(path, "r");
+    if (!f) { fprintf(stderr, "missing %s\n", path); return 1; }
+    while (fgets(line.data(), (int)line.size(), f)) {
+        char *hex, *idtxt;
+        if (!three_fields(line.data(), &hex, &idtxt)) continue;
+        const char *name = line.data();
+        std::string text;
+        if (!hex_to_text(hex, text)) { printf("FAIL tok %s: bad hex\n", name); fails++; checked++; continue; }
+        std::vector<int> want = ids_of(idtxt, 8192);
+        if (have_tok) {
+            std::vector<int> got(8192);
+            int n = tok_encode(tok, text.c_str(), got.data(), 8192);
+            int bad = -1;
+            if (n != (int)want.size()) { printf("FAIL tok %s: len %d vs %d\n", name, n, (int)want.size()); fails++; }
+            else {
+                for (int i = 0; i < n && bad < 0; i++) if (got[i] != want[i]) bad = i;
+                if (bad >= 0) { printf("FAIL tok %s: pos %d got %d want %d\n", name, bad, got[bad], want[bad]); fails++; }
+                else printf("ok   tok %s (%d ids exact)\n", name, n);
+            }
+        } else {
+            printf("skip tok %s (host tokenizer not linked)\n", name);
+        }
+        checked++;
+        const int T = (int)want.size();
+        snprintf(path, sizeof(path), "%s/%s_logits_%s.f32", dir, stem, name);
+        FILE *lf = fopen(path, "rb");
+        checked++;
+        if (!lf) { printf("FAIL logits %s: missing %s\n", name, path); fails++; continue; }
+        std::vector<float> ref((size_t)T * V), got((size_t)T * V);
+        size_t rd = fread(ref.data(), sizeof(float), ref.size(), lf);
+        fclose(lf);
+        if (rd != ref.size()) { printf("FAIL logits %s: short read\n", name); fails++; continue; }
+        ncmb_lm_logits(m, want.data(), T, 0, got.data());
+        double maxabs = 0, maxrel = 0;
+        for (size_t i = 0; i < ref.size(); i++) {
+            double a = got[i], b = ref[i], d = fabs(a - b);
+            if (d > maxabs) maxabs = d;
+            double r = d / (fabs(b) + 1.0);
+            if (r > maxrel) maxrel = r;
+        }
+        const bool ok = is_qwen ? (maxrel < 5e-4 && maxabs < 1e-3) : (maxrel < 1e-4 && maxabs < 1e-2);   // qwen.c:379, gpt2.c:385
+        printf("%s logits %s: maxabs=%.3g maxrel=%.3g\n", ok ? "ok  " : "FAIL", name, maxabs, maxrel);
+        if (!ok) fails++;
+    }
+    fclose(f);
+    // 3: greedy continuations
+    snprintf(path, sizeof(path), "%s/%s_gen.txt", dir, stem);
+    f = fopen(path, "r");
+    if (!f) { fprintf(stderr, "missing %s\n", path); return 1; }
+    while (fgets(line.data(), (int)line.size(), f)) {
+        char *hex, *idtxt;
+        if (!three_fields(line.data(), &hex, &idtxt)) continue;
+        const char *name = line.data();
+        std::string text;
+        if (!hex_to_text(hex, text)) continue;
+        std::vector<int> want = ids_of(idtxt, 256);
+        const int ne = (int)want.size();
+        if (!have_tok) { printf("skip gen %s (host tokenizer not linked)\n", name); checked++; continue; }
+        std::vector<int> prompt(8192);
+        int np = tok_encode(tok, text.c_str(), prompt.data(), 8192);
+        std::vector<int> gen(ne > 0 ? ne : 1, -1);
+        int ng = 0;
+        if (ne > 0 && np > 0) {
+            ncmb_lm_generate(m, prompt.data(), 1, np, ne, 0.0f, 0, 1.0f, 0, m->eos, gen.data());
+            while (ng < ne && gen[ng] >= 0) ng++;
+        }
+        bool ok = ng == ne;
+        for (int i = 0; ok && i < ne; i++) if (gen[i] != want[i]) ok = false;
+        if (ok) printf("ok   gen %s (%d tokens exact)\n", name, ne);
+        else { printf("FAIL gen %s: got %d tokens, want %d\n", name, ng, ne); fails++; }
+        checked++;
+    }
+    fclose(f);
+    // 4: likelihood of one text
+    snprintf(path, sizeof(path), "%s/%s_ppl.txt", dir, stem);
+    f = fopen(path, "r");
+    if (f && fgets(line.data(), (int)line.size(), f)) {
+        char *a, *b;
+        if (three_fields(line.data(), &a, &b)) {
+            std::string text;
+            const double want_nll = atof(a), want_ppl = atof(b);
+            if (hex_to_text(line.data(), text)) {
+                if (!have_tok) { printf("skip ppl (host tokenizer not linked)\n"); }
+                else {
+                    std::vector<int> ids(8192);
+                    int n = tok_encode(tok, text.c_str(), ids.data(), 8192);
+                    double nll = 0;
+                    ncmb_lm_nll(m, ids.data(), 1, n, nullptr, &nll);
+                    if (fabs(nll - want_nll) < 1e-4) printf("ok   ppl nll=%.6f (want %.6f) ppl=%.4f (want %.4f)\n", nll, want_nll, exp(nll), want_ppl);
+                    else { printf("FAIL ppl nll=%.6f want %.6f\n", nll, want_nll); fails++; }
+                }
+                checked++;
+            }
+        }
+    }
+    if (f) fclose(f);
+    printf("%s-VERIFY %s (%d checked)\n", is_qwen ? "QWEN" : "GPT2", fails ? "FAIL" : "PASS", checked);
+    if (tok && tok_free) tok_free(tok);
+    ncmb_lm_close(m);
+    return fails != 0;
+}
+
+extern "C" int gpt2_cmd_verify(const NCMConfig *c, const char *weights, const char *adir, const char *dir) {
+    return lm_cmd_verify(c, weights, adir, dir, 0);
+}
+extern "C" int qwen_cmd_verify(const NCMConfig *c, const char *weights, const char *adir, const char *dir) {
+    return lm_cmd_verify(c, weights, adir, dir, 1);
 }

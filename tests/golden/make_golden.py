@@ -50,6 +50,8 @@ def lms(ref, out, tmp):
             else:
                 fn.argtypes = [P, P, I, I, P]; fn(h, pr.ctypes.data, pr.size, 0, lg.ctypes.data)
             out[f"lm_{kind}_logits{i}"] = lg
+            nl = getattr(ref.lib, f"ref_{kind}_nll"); nl.restype = C.c_double; nl.argtypes = [P, P, I]
+            out[f"lm_{kind}_nll{i}"] = np.array([nl(h, pr.ctypes.data, pr.size)], np.float64)
             gen = getattr(ref.lib, f"ref_{kind}_generate"); gen.restype = I
             gen.argtypes = [P, P, I, I, F, I, F, U, P]
             for tag, (t, tk, tp, sd) in (("greedy", (0.0, 0, 1.0, 0)), ("sampled", (0.7, 0, 0.95, 9)), ("topk", (0.9, 8, 1.0, 5))):

@@ -253,6 +253,7 @@ def orc_lms(out, tmp):
         prompts = synth.lm_prompts(spec, 2, 9, 3)
         for i, pr in enumerate(prompts):
             out[f"lm_{kind}_logits{i}"] = m.logits(pr)
+            out[f"lm_{kind}_nll{i}"] = np.array([m.nll(pr)], np.float64)
             for tag, (t, tk, tp, sd) in (("greedy", (0.0, 0, 1.0, 0)), ("sampled", (0.7, 0, 0.95, 9)), ("topk", (0.9, 8, 1.0, 5))):
                 out[f"lm_{kind}_gen{i}_{tag}"] = m.generate(pr, 12, temp=t, top_k=tk, top_p=tp, seed=sd)
 

@@ -44,6 +44,7 @@ def test_reference_entry_points_are_all_present(lib):
     for n in ("weights_load", "config_load", "arena_init_default", "vqvae_load", "ncp_load", "ncp_generate",
               "ncp_gen_begin", "ncp_gen_step", "ncp_gen_finish", "ncp_gen_abort", "vq_idx_to_zhats",
               "vqvae_decode", "vq_z_to_idx", "vqvae_encode_z", "ncp_forward", "gpt2_cmd_gen", "qwen_cmd_gen",
+              "gpt2_cmd_ppl", "gpt2_cmd_verify", "qwen_cmd_ppl", "qwen_cmd_verify",
               "linear_fwd", "sdpa_fwd_gqa", "rowwise_l2sq", "sample_topkp", "argmax_row"):
         assert hasattr(lib, n), n
 

@@ -332,3 +332,105 @@ def test_decoder_lm_logits_and_generation(cuda, tmp, kind):
         assert cuda.ncmb_gemm_tc_check() == 0           # no bounded wait (mbarrier, grid barrier) ran out
     cuda.ncmb_set_lm_persistent(0)
     cuda.ncmb_lm_close(m)
+
+
+def _flush_c_stdout():
+    import ctypes
+    ctypes.CDLL(None).fflush(None)
+
+
+PPL_SPECS = {
+    # GPT-2 windows are n_ctx ids long (64 here); Qwen2 windows are 512 ids whatever the context length
+    "gpt2": lambda synth: synth.LMSpec("gpt2_ppl", "gpt2", 2, 128, 2, 2, 512, 300, 64, rand_affine=1),
+    "qwen": lambda synth: synth.LMSpec("qwen_ppl", "qwen", 2, 128, 2, 1, 256, 411, 600, rope_theta=1e6, rand_affine=1),
+}
+
+
+@pytest.mark.parametrize("kind", sorted(PPL_SPECS))
+def test_decoder_lm_likelihood_and_fixture_commands(cuda, tmp, kind, capfd):
+    """ncmb_lm_nll, *_cmd_ppl and *_cmd_verify against the oracle's window likelihood (reference gpt2_nll / qwen_nll)."""
+    import orc
+    import synth
+    spec = PPL_SPECS[kind](synth)
+    is_qwen = kind == "qwen"
+    conf, w = synth.write_lm(spec, tmp)
+    cfg = cuda.load_config(conf)
+    om = orc.LM(conf, w, is_qwen)
+    window = 512 if is_qwen else spec.n_ctx
+    docs = [synth.lm_prompts(spec, 1, n, 11 + i)[0] for i, n in enumerate((9, 2 * window + 22, 33, window + 1, 1))]
+    # the windows the reference cuts (gpt2.c:253-260, qwen.c:283-288) and their likelihoods from the oracle
+    wins = []
+    for d in docs:
+        if d.size < 2:
+            continue
+        o = 0
+        while o + 1 < d.size:
+            T = min(window, d.size - o)
+            if T < 2:
+                break
+            wins.append(d[o:o + T])
+            o += window
+    want = np.array([om.nll(x) for x in wins])
+    tol = 5e-5                                # logits agree to about 1e-5; the likelihood is a smooth function of them
+    m = cuda.ncmb_lm_open(cfg, w.encode(), int(is_qwen), 0)
+    # one window at a time, then all of them ragged in one batch
+    one = np.zeros(len(wins))
+    for i, x in enumerate(wins):
+        x = np.ascontiguousarray(x, np.int32)
+        got = np.zeros(1)
+        cuda.ncmb_lm_nll(m, x.ctypes.data, 1, x.size, None, got.ctypes.data)
+        one[i] = got[0]
+    assert np.abs(one - want).max() < tol, (one, want)
+    T = max(x.size for x in wins)
+    ids = np.full((len(wins), T), 7, np.int32)            # tail padding must not matter
+    lens = np.array([x.size for x in wins], np.int32)
+    for i, x in enumerate(wins):
+        ids[i, :x.size] = x
+    got = np.zeros(len(wins))
+    cuda.ncmb_lm_nll(m, ids.ctypes.data, len(wins), T, lens.ctypes.data, got.ctypes.data)
+    assert np.abs(got - want).max() < tol, (got, want)
+    cuda.ncmb_lm_close(m)
+
+    # *_cmd_ppl: ids per line (no host tokenizer is linked into the test process)
+    texts = os.path.join(tmp, f"{kind}_texts.txt")
+    with open(texts, "w") as f:
+        for d in docs:
+            f.write(" ".join(str(int(v)) for v in d) + "\n\n")
+    capfd.readouterr()
+    rc = getattr(cuda, f"{kind if is_qwen else 'gpt2'}_cmd_ppl")(cfg, w.encode(), tmp.encode(), texts.encode())
+    _flush_c_stdout()
+    line = [ln for ln in capfd.readouterr().out.splitlines() if ln.startswith("docs=")][-1]
+    assert rc == 0
+    ntok = sum(x.size - 1 for x in wins)
+    tot = 0.0
+    for x, v in zip(wins, want):
+        tot += v * (x.size - 1)
+    f = dict(kv.split("=") for kv in line.split())
+    assert int(f["docs"]) == sum(1 for d in docs if d.size >= 2) and int(f["tokens"]) == ntok, line
+    assert abs(float(f["nll"]) - tot / ntok) < 1e-4 and abs(float(f["ppl"]) - np.exp(tot / ntok)) < 1e-4 * np.exp(tot / ntok) + 1e-5, line
+
+    # *_cmd_verify on fixtures written from the oracle: logits pass, a disturbed file fails
+    fx = os.path.join(tmp, f"{kind}_fx")
+    os.makedirs(fx, exist_ok=True)
+    names = {"s1": docs[0], "s2": docs[2]}
+    with open(os.path.join(fx, f"{kind}_tok.txt"), "w") as f:
+        for nm, d in names.items():
+            f.write(f"{nm}\t{'text'.encode().hex()}\t{' '.join(str(int(v)) for v in d)}\n")
+            om.logits(d).tofile(os.path.join(fx, f"{kind}_logits_{nm}.f32"))
+    with open(os.path.join(fx, f"{kind}_gen.txt"), "w") as f:
+        f.write(f"g1\t{'text'.encode().hex()}\t1 2 3\n")
+    with open(os.path.join(fx, f"{kind}_ppl.txt"), "w") as f:
+        f.write(f"{'text'.encode().hex()}\t{want[0]:.6f}\t{np.exp(want[0]):.4f}\n")
+    verify = getattr(cuda, f"{kind}_cmd_verify")
+    rc = verify(cfg, w.encode(), tmp.encode(), fx.encode())
+    _flush_c_stdout()
+    out = capfd.readouterr().out
+    assert rc == 0, out
+    assert out.count("ok   logits") == 2 and f"{kind.upper()}-VERIFY PASS (6 checked)" in out, out
+    bad = om.logits(names["s2"])
+    bad[3, 5] += 0.5
+    bad.tofile(os.path.join(fx, f"{kind}_logits_s2.f32"))
+    rc = verify(cfg, w.encode(), tmp.encode(), fx.encode())
+    _flush_c_stdout()
+    out = capfd.readouterr().out
+    assert rc == 1 and "FAIL logits s2" in out and f"{kind.upper()}-VERIFY FAIL" in out, out
