@@ -119,7 +119,13 @@ void  arena_free(void);
 void  parena_init(size_t bytes);
 float *parena_alloc(size_t n_floats);
 /* src/ncm.h:68-70, 139, 261 (tensor.c:70-143, 170-266, 369-373) */
-int  weights_load(WeightStore *ws, const char *path);     /* NCM1 files; 0 / -1 */
+int  weights_load(WeightStore *ws, const char *path);     /* NCM1 weights or NCK1 checkpoints; 0 / -1 */
+/* src/ncm.h:441, 465 (ckpt.c:67-77, 549-625): which of the two a file is (1 = NCK1 training checkpoint,
+ * 0 = NCM1, -1 = neither), and the checkpoint's tensor records alone -- checksum verified first, run state and
+ * optimizer section ignored -- so that every inference command accepts a training checkpoint. 0 / -1 with the
+ * reason in err. Saving and resuming checkpoints belong to training and are not part of this library. */
+int  ckpt_probe(const char *path);
+int  ckpt_load_weights_only(const char *path, WeightStore *ws, char *err, size_t errcap);
 void weights_free(WeightStore *ws);
 Tensor *weights_get(WeightStore *ws, const char *name);   /* NULL if missing */
 int  config_load(NCMConfig *c, const char *path);         /* 0 / -1 */

@@ -32,6 +32,11 @@ class WeightStore(C.Structure):
     _fields_ = [("items", _P), ("count", _I)]
 
 
+class Tensor(C.Structure):
+    """src/ncm.h:27-34"""
+    _fields_ = [("data", _P), ("shape", _I64 * 4), ("ndim", _I), ("n", _I64)]
+
+
 # name -> (restype, argtypes); only the inference surface
 _SIGS = {
     # runtime (src/ncm.h:37-70,139,261)
@@ -49,6 +54,8 @@ _SIGS = {
     "parena_alloc": (_P, [_SZ]),
     "weights_load": (_I, [C.POINTER(WeightStore), C.c_char_p]),
     "weights_free": (None, [C.POINTER(WeightStore)]),
+    "ckpt_probe": (_I, [C.c_char_p]),
+    "ckpt_load_weights_only": (_I, [C.c_char_p, C.POINTER(WeightStore), C.c_char_p, _SZ]),
     "weights_get": (_P, [C.POINTER(WeightStore), C.c_char_p]),
     "config_load": (_I, [_P, C.c_char_p]),
     # layer kernels (src/ncm.h:146-199)
@@ -202,6 +209,18 @@ class NcmLib:
         if self.config_load(buf, conf_path.encode()) != 0:
             raise RuntimeError(f"config_load failed: {conf_path}")
         return buf
+
+    def tensor_host(self, ws: WeightStore, name: str):
+        """float32 copy of one named tensor (None if the store has no such name)"""
+        p = self.weights_get(C.byref(ws), name.encode())
+        if not p:
+            return None
+        t = C.cast(p, C.POINTER(Tensor)).contents
+        out = np.zeros([t.shape[d] for d in range(t.ndim)], np.float32)
+        assert out.size == t.n
+        if out.size:
+            self.mem_d2h(out.ctypes.data, t.data, out.nbytes)
+        return out
 
     def load_weights(self, path: str) -> WeightStore:
         ws = WeightStore()

@@ -247,40 +247,62 @@ float *parena_alloc(size_t n_floats) {
 // Layout (reference loader, src/tensor.c:70-128): "NCM1", u32 count, then per tensor
 // u8 name length, name, u8 ndim, u32 dims, u64 byte count, raw fp32. The whole file is
 // read once; all tensor payloads go into one 256-byte-aligned HBM slab with one copy.
-int weights_load(WeightStore *ws, const char *path) {
-    ensure_device();
-    ws->items = nullptr; ws->count = 0;
+// ---- weight files -----------------------------------------------------------------------------
+// NCM1 (reference weights_load src/tensor.c:70-130): "NCM1", u32 count, then per tensor u8 name length, name,
+// u8 ndim, u32 dims, u64 payload bytes, fp32 payload. NCK1 training checkpoints (reference src/ckpt.c:200-262)
+// hold the same per-tensor records after a run-state header and before the optimizer section, with an FNV-1a 64
+// checksum of everything in the last eight bytes; like the reference (ckpt_load_weights_only src/ckpt.c:549-625,
+// reached from weights_load src/tensor.c:73-80) only the tensor records are read. The file is staged once in
+// pinned memory and every payload goes to one device slab.
+
+namespace {
+struct FileImage {
+    unsigned char *buf = nullptr;
+    size_t len = 0;
+    ~FileImage() { if (buf) { memset(buf, 0, len); cudaFreeHost(buf); } }      // weights do not linger in host memory
+};
+
+int read_image(const char *path, FileImage &im, char *err, size_t errcap) {
     FILE *f = fopen(path, "rb");
-    if (!f) { fprintf(stderr, "cannot open %s\n", path); return -1; }
+    if (!f) { snprintf(err, errcap, "cannot open %s", path); return -1; }
     fseek(f, 0, SEEK_END);
     long fsz = ftell(f);
     fseek(f, 0, SEEK_SET);
-    if (fsz < 8) { fprintf(stderr, "%s: bad magic\n", path); fclose(f); return -1; }
-    unsigned char *buf = nullptr;
-    if (cudaMallocHost((void **)&buf, (size_t)fsz) != cudaSuccess) { fclose(f); fprintf(stderr, "%s: pinned staging alloc failed\n", path); return -1; }
-    size_t got = fread(buf, 1, (size_t)fsz, f);
+    if (fsz < 8) { snprintf(err, errcap, "%s: bad magic", path); fclose(f); return -1; }
+    if (cudaMallocHost((void **)&im.buf, (size_t)fsz) != cudaSuccess) { fclose(f); im.buf = nullptr; snprintf(err, errcap, "%s: pinned staging alloc failed", path); return -1; }
+    im.len = (size_t)fsz;
+    size_t got = fread(im.buf, 1, im.len, f);
     fclose(f);
-    auto fail = [&](const char *why) { fprintf(stderr, "%s: %s\n", path, why); cudaFreeHost(buf); free(ws->items); ws->items = nullptr; ws->count = 0; return -1; };
-    if (got != (size_t)fsz) return fail("short read");
-    if (memcmp(buf, "NCM1", 4) != 0) {
-        if (memcmp(buf, "NCK1", 4) == 0) return fail("NCK1 training checkpoints are not read by this library; export NCM1 weights");
-        return fail("bad magic");
-    }
-    uint32_t count;
-    memcpy(&count, buf + 4, 4);
+    if (got != im.len) { snprintf(err, errcap, "%s: short read", path); return -1; }
+    return 0;
+}
+
+// tensor records [pos, end) of a staged file -> ws (one device slab). strict: NCK1 rules (no empty names).
+int load_tensor_records(WeightStore *ws, const char *path, const FileImage &im, size_t pos, size_t end, uint32_t count, bool strict,
+                        char *err, size_t errcap) {
+    const unsigned char *buf = im.buf;
     ws->items = (NamedTensor *)calloc(count ? count : 1, sizeof(NamedTensor));
+    ws->count = 0;
+    if (!ws->items) { snprintf(err, errcap, "out of memory"); return -1; }
+    auto fail = [&](const char *why) {
+        if (!err[0]) snprintf(err, errcap, "%s: %s", path, why);
+        for (int j = 0; j < ws->count; j++) free(ws->items[j].t);
+        free(ws->items); ws->items = nullptr; ws->count = 0;
+        return -1;
+    };
     struct Span { size_t file_off, nbytes, slab_off; };
     std::vector<Span> spans(count);
-    size_t pos = 8, slab = 0;
+    size_t slab = 0;
+    const char *trunc = strict ? "truncated tensor section" : "truncated";
     for (uint32_t i = 0; i < count; i++) {
-        if (pos + 1 > (size_t)fsz) return fail("truncated");
+        if (pos + 1 > end) return fail(trunc);
         unsigned nl = buf[pos++];
-        if (pos + nl + 1 > (size_t)fsz) return fail("truncated");
+        if ((strict && nl == 0) || nl >= sizeof(ws->items[0].name) || pos + nl + 1 > end) return fail(trunc);
         memcpy(ws->items[i].name, buf + pos, nl);
         ws->items[i].name[nl] = 0;
         pos += nl;
         unsigned nd = buf[pos++];
-        if (nd > NCM_MAX_DIMS || pos + 4 * nd + 8 > (size_t)fsz) return fail("truncated");
+        if (nd > NCM_MAX_DIMS || pos + 4 * nd + 8 > end) return fail(trunc);
         Tensor *t = (Tensor *)calloc(1, sizeof(Tensor));
         t->ndim = (int)nd; t->n = 1;
         for (unsigned d = 0; d < nd; d++) { uint32_t v; memcpy(&v, buf + pos, 4); pos += 4; t->shape[d] = v; t->n *= v; }
@@ -288,8 +310,11 @@ int weights_load(WeightStore *ws, const char *path) {
         memcpy(&nbytes, buf + pos, 8); pos += 8;
         ws->items[i].t = t;
         ws->count = (int)i + 1;
-        if ((uint64_t)t->n * 4 != nbytes) { fprintf(stderr, "%s: size mismatch\n", ws->items[i].name); for (int j = 0; j < ws->count; j++) free(ws->items[j].t); return fail("size mismatch"); }
-        if (pos + nbytes > (size_t)fsz) { for (int j = 0; j < ws->count; j++) free(ws->items[j].t); return fail("truncated payload"); }
+        if (nbytes > end - pos) return fail(strict ? trunc : "truncated payload");
+        if ((uint64_t)t->n * 4 != nbytes) {
+            snprintf(err, errcap, "%s: tensor '%s' size mismatch", path, ws->items[i].name);
+            return fail("size mismatch");
+        }
         spans[i] = Span{pos, (size_t)nbytes, slab};
         slab += ((size_t)nbytes + 255) & ~(size_t)255;
         pos += nbytes;
@@ -304,9 +329,90 @@ int weights_load(WeightStore *ws, const char *path) {
                                        cudaMemcpyHostToDevice, stream()));
     }
     CUDA_CHECK(cudaStreamSynchronize(stream()));
-    cudaFreeHost(buf);
     slab_of_store()[ws->items] = dslab;
     return 0;
+}
+
+uint64_t fnv1a64(const unsigned char *b, size_t n) {
+    uint64_t h = 14695981039346656037ULL;
+    for (size_t i = 0; i < n; i++) { h ^= b[i]; h *= 1099511628211ULL; }
+    return h;
+}
+
+// bounds-checked little-endian cursor over the checkpoint header
+struct Cursor {
+    const unsigned char *p, *end;
+    bool bad = false;
+    uint64_t le(int n) {
+        if (bad || (size_t)(end - p) < (size_t)n) { bad = true; return 0; }
+        uint64_t v = 0;
+        for (int i = n - 1; i >= 0; i--) v = (v << 8) | p[i];
+        p += n;
+        return v;
+    }
+    void skip_str() {
+        uint64_t n = le(2);
+        if (bad || (size_t)(end - p) < n) { bad = true; return; }
+        p += n;
+    }
+};
+} // namespace
+
+// 1 = NCK1 checkpoint, 0 = NCM1 weights, -1 = neither / unreadable (reference ckpt_probe src/ckpt.c:67-77)
+int ckpt_probe(const char *path) {
+    FILE *f = fopen(path, "rb");
+    if (!f) return -1;
+    char magic[4];
+    size_t r = fread(magic, 1, 4, f);
+    fclose(f);
+    if (r != 4) return -1;
+    if (memcmp(magic, "NCK1", 4) == 0) return 1;
+    if (memcmp(magic, "NCM1", 4) == 0) return 0;
+    return -1;
+}
+
+int ckpt_load_weights_only(const char *path, WeightStore *ws, char *err, size_t errcap) {
+    ensure_device();
+    char local[256];
+    if (!err || !errcap) { err = local; errcap = sizeof(local); }
+    err[0] = 0;
+    ws->items = nullptr; ws->count = 0;
+    FileImage im;
+    if (read_image(path, im, err, errcap)) return -1;
+    uint64_t file_sum;
+    memcpy(&file_sum, im.buf + im.len - 8, 8);
+    if (fnv1a64(im.buf, im.len - 8) != file_sum) { snprintf(err, errcap, "%s: checksum mismatch", path); return -1; }
+    Cursor c{im.buf, im.buf + im.len - 8};
+    const bool magic_ok = im.len - 8 >= 4 && memcmp(im.buf, "NCK1", 4) == 0;
+    c.le(4);
+    if (!magic_ok || c.le(4) != 1u || c.bad) { snprintf(err, errcap, "%s: not an NCK1 checkpoint", path); return -1; }
+    // run state: step i64, batch rng u64, three f64 of the schedule, batch i32, pending i32, rows i64, row length i32,
+    // data hash u64, data path, conf hash u64, tokenizer id, training config
+    c.le(8); c.le(8); c.le(8); c.le(8); c.le(8); c.le(4); c.le(4); c.le(8); c.le(4); c.le(8);
+    c.skip_str(); c.le(8); c.skip_str(); c.skip_str();
+    uint32_t n = (uint32_t)c.le(4);
+    if (c.bad || n > (1u << 24)) { snprintf(err, errcap, "%s: bad tensor count", path); return -1; }
+    return load_tensor_records(ws, path, im, (size_t)(c.p - im.buf), im.len - 8, n, true, err, errcap);
+}
+
+int weights_load(WeightStore *ws, const char *path) {
+    ensure_device();
+    ws->items = nullptr; ws->count = 0;
+    char err[256] = {0};
+    if (ckpt_probe(path) == 1) {
+        if (ckpt_load_weights_only(path, ws, err, sizeof(err))) { fprintf(stderr, "%s\n", err); return -1; }
+        return 0;
+    }
+    FileImage im;
+    int rc = read_image(path, im, err, sizeof(err));
+    if (!rc && memcmp(im.buf, "NCM1", 4) != 0) { snprintf(err, sizeof(err), "%s: bad magic", path); rc = -1; }
+    if (!rc) {
+        uint32_t count;
+        memcpy(&count, im.buf + 4, 4);
+        rc = load_tensor_records(ws, path, im, 8, im.len, count, false, err, sizeof(err));
+    }
+    if (rc) fprintf(stderr, "%s\n", err);
+    return rc;
 }
 
 void weights_free(WeightStore *ws) {

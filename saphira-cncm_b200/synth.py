@@ -47,6 +47,50 @@ def write_ncm(path: str, tensors: "dict[str, np.ndarray]") -> None:
             f.write(raw)
 
 
+def _fnv1a64(data: bytes) -> int:
+    """FNV-1a 64 (a serial chain; fine for the small files tests write)."""
+    h = 14695981039346656037
+    mask = (1 << 64) - 1
+    for b in data:
+        h = ((h ^ b) * 1099511628211) & mask
+    return h
+
+
+def write_nck1(path: str, tensors: "dict[str, np.ndarray]", step: int = 7, optimizer_slots: int = 1) -> None:
+    """A training checkpoint in the reference's NCK1 v1 layout (writer: src/ckpt.c:200-262): run-state header, the
+    tensor records (same record layout as NCM1), an AdamW section, FNV-1a 64 of everything before it in the last
+    eight bytes. Inference reads the tensor records only; the run state and the moments written here are filler of
+    the right shape (moments for the first `optimizer_slots` tensors)."""
+    out = bytearray()
+    out += b"NCK1" + struct.pack("<I", 1)
+    out += struct.pack("<qQdddiiqiQ", step, 0x9E3779B97F4A7C15, 3e-4, 100.0, 1000.0, 8, 0, 1234, 81, 0xABCDEF)
+    for sfield in (b"data/train.bin",):
+        out += struct.pack("<H", len(sfield)) + sfield
+    out += struct.pack("<Q", 0x1234)
+    for sfield in (b"sudoku", b'{"lr": 0.0003}'):
+        out += struct.pack("<H", len(sfield)) + sfield
+    out += struct.pack("<I", len(tensors))
+    arrs = []
+    for name, arr in tensors.items():
+        t = np.ascontiguousarray(arr, dtype=np.float32)
+        nb = name.encode()
+        assert 0 < len(nb) < 256 and 1 <= t.ndim <= 4, name
+        out += struct.pack("<B", len(nb)) + nb + struct.pack("<B", t.ndim)
+        for d in t.shape:
+            out += struct.pack("<I", d)
+        raw = t.tobytes()
+        out += struct.pack("<Q", len(raw)) + raw
+        arrs.append(t)
+    n_opt = min(optimizer_slots, len(arrs))
+    out += b"ADAM" + struct.pack("<ddddIq", 0.9, 0.95, 1e-8, 0.1, n_opt, step)
+    for i in range(n_opt):
+        nbytes = arrs[i].size * 4
+        out += struct.pack("<IdQ", i, 3e-4, nbytes) + bytes(nbytes) + struct.pack("<Q", nbytes) + bytes(nbytes)
+    out += struct.pack("<Q", _fnv1a64(bytes(out)))
+    with open(path, "wb") as f:
+        f.write(out)
+
+
 def write_conf(path: str, kv: "dict[str, object]") -> None:
     with open(path, "w") as f:
         for k, v in kv.items():

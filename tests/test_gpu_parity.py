@@ -434,3 +434,79 @@ def test_decoder_lm_likelihood_and_fixture_commands(cuda, tmp, kind, capfd):
     _flush_c_stdout()
     out = capfd.readouterr().out
     assert rc == 1 and "FAIL logits s2" in out and f"{kind.upper()}-VERIFY FAIL" in out, out
+
+
+def test_training_checkpoints_load_as_weights(cuda, tmp, capfd):
+    """weights_load on an NCK1 training checkpoint (reference src/tensor.c:73-80 -> ckpt_load_weights_only
+    src/ckpt.c:549-625): same tensors as the NCM1 file, checksum and truncation are refused, and a model opened
+    from the checkpoint computes what it computes from the weights file."""
+    import ctypes as C
+    import synth
+    spec = synth.spec_gpt2_tiny()
+    conf, w = synth.write_lm(spec, tmp)
+    tensors = synth.lm_tensors(spec, 1)
+    ncm = os.path.join(tmp, "ck_same.ncm")
+    ck = os.path.join(tmp, "ck_same.nckpt")
+    synth.write_ncm(ncm, tensors)
+    synth.write_nck1(ck, tensors, optimizer_slots=2)
+    assert cuda.ckpt_probe(ck.encode()) == 1 and cuda.ckpt_probe(ncm.encode()) == 0
+    assert cuda.ckpt_probe(conf.encode()) == -1 and cuda.ckpt_probe(b"/nonexistent/file") == -1
+    a, b = cuda.load_weights(ncm), cuda.load_weights(ck)
+    assert a.count == b.count == len(tensors)
+    for name, want in tensors.items():
+        got = cuda.tensor_host(b, name)
+        assert helpers.same_bits(got, np.ascontiguousarray(want, np.float32)), name
+        assert helpers.same_bits(got, cuda.tensor_host(a, name)), name
+    cuda.weights_free(C.byref(a))
+    cuda.weights_free(C.byref(b))
+    # refusals: a flipped byte (checksum), a cut file, a wrong version
+    raw = open(ck, "rb").read()
+    import struct
+    variants = {"flip": raw[:len(raw) // 2] + bytes([raw[len(raw) // 2] ^ 1]) + raw[len(raw) // 2 + 1:],
+                "cut": raw[:len(raw) // 3]}
+    v2 = bytearray(raw[:-8])
+    v2[4:8] = struct.pack("<I", 2)
+    variants["version"] = bytes(v2) + struct.pack("<Q", synth._fnv1a64(bytes(v2)))
+    for tag, data in variants.items():
+        path = os.path.join(tmp, f"ck_{tag}.nckpt")
+        open(path, "wb").write(data)
+        import capi
+        ws = capi.WeightStore()
+        err = C.create_string_buffer(256)
+        assert cuda.ckpt_load_weights_only(path.encode(), C.byref(ws), err, 256) == -1, tag
+        assert ws.count == 0 and not ws.items
+        msg = err.value.decode()
+        assert ("checksum mismatch" in msg) if tag != "version" else ("not an NCK1 checkpoint" in msg), (tag, msg)
+        assert cuda.weights_load(C.byref(ws), path.encode()) == -1
+    capfd.readouterr()
+    # a decoder LM opened straight from a checkpoint of its weights
+    ck2 = os.path.join(tmp, "lm_from_ckpt.nckpt")
+    synth.write_nck1(ck2, _read_ncm(w))
+    cfg = cuda.load_config(conf)
+    pr = np.ascontiguousarray(synth.lm_prompts(spec, 1, 9, 3)[0])
+    outs = []
+    for path in (w, ck2):
+        m = cuda.ncmb_lm_open(cfg, path.encode(), 0, 0)
+        assert m
+        lg = np.zeros((pr.size, spec.vocab), np.float32)
+        cuda.ncmb_lm_logits(m, pr.ctypes.data, pr.size, 0, lg.ctypes.data)
+        outs.append(lg)
+        cuda.ncmb_lm_close(m)
+    assert helpers.same_bits(outs[0], outs[1])
+
+
+def _read_ncm(path):
+    """tensors of an NCM1 file, in file order"""
+    import struct
+    out = {}
+    with open(path, "rb") as f:
+        assert f.read(4) == b"NCM1"
+        (count,) = struct.unpack("<I", f.read(4))
+        for _ in range(count):
+            (nl,) = struct.unpack("<B", f.read(1))
+            name = f.read(nl).decode()
+            (nd,) = struct.unpack("<B", f.read(1))
+            shape = struct.unpack(f"<{nd}I", f.read(4 * nd))
+            (nb,) = struct.unpack("<Q", f.read(8))
+            out[name] = np.frombuffer(f.read(nb), np.float32).reshape(shape).copy()
+    return out

@@ -64,3 +64,34 @@ def test_oracle_matches_live_reference_on_a_fresh_case(tmp_path):
     got = orc.Model(conf, w).generate(pre, **kw)
     want = capi.NcpModel(ref, conf, w, arena_mb=256).generate(pre, **kw)
     assert (got == want).all()
+
+
+def _ckpt_tensors():
+    rng = np.random.default_rng(5)
+    return {"wte.weight": rng.standard_normal((7, 5)).astype(np.float32),
+            "h.0.ln_1.bias": rng.standard_normal(5).astype(np.float32),
+            "conv.weight": rng.standard_normal((3, 4, 2)).astype(np.float32)}
+
+
+@pytest.mark.skipif(not os.path.exists(helpers.REF_LIB), reason="reference build not present")
+def test_checkpoint_writer_is_read_by_the_reference(tmp_path):
+    """The NCK1 files the GPU tests feed to the library are files the reference's own reader accepts
+    (weights_load -> ckpt_load_weights_only, src/tensor.c:73-80, src/ckpt.c:549-625) and reads the same tensors from."""
+    import capi
+    import synth
+    ref = capi.NcmLib(helpers.REF_LIB)
+    tensors = _ckpt_tensors()
+    ck = str(tmp_path / "w.nckpt")
+    synth.write_nck1(ck, tensors)
+    assert ref.ckpt_probe(ck.encode()) == 1
+    ws = ref.load_weights(ck)
+    assert ws.count == len(tensors)
+    for name, want in tensors.items():
+        assert helpers.same_bits(ref.tensor_host(ws, name), want), name
+    # a flipped payload byte is caught by the checksum
+    raw = bytearray(open(ck, "rb").read())
+    raw[len(raw) // 2] ^= 0x40
+    bad = str(tmp_path / "bad.nckpt")
+    open(bad, "wb").write(raw)
+    with pytest.raises(RuntimeError):
+        ref.load_weights(bad)
