@@ -8,12 +8,16 @@
 // head (K and V are read once per group), a local softmax and the partial context, and writes
 // (max, sum, context[hd]) per head to scratch. The last CTA of a (row, kv head) to finish -- an
 // atomic counter tells it -- merges the partials with the usual log-sum-exp rescaling and writes the
-// context row. A batch-1, 12-head step with 300 cached keys thus runs on ~120 CTAs instead of 12.
+// context row. A batch-1, 12-head step with 300 cached keys thus runs on ~120 CTAs instead of 12. With many
+// rows a CTA takes several consecutive chunks (running maximum and sum), and a CTA that sees all keys of its
+// row writes the context directly.
 //
 // step_d: optional device counter. When set, row lengths are read from k1_len + (*step_d) * len_step,
 // so one captured CUDA graph serves every decode step.
 #include "common.cuh"
 #include "split.cuh"
+
+#include <algorithm>
 
 namespace ncmb {
 
@@ -27,20 +31,23 @@ struct AttnDecDev {
     float *out; float *out_lo; int out_fmt; int64_t ldo;
     const int *q_start, *k_start, *k_len;
     const int *step_d; int64_t len_step;
-    int H, Hkv, max_split;
+    int H, Hkv, max_split, cps;
     float scale;
     float *part; unsigned *count;
 };
 
-template <int HD>
+// GM: compile-time bound on the (query, head) pairs of a kv group (1, 4, 8 or 16). Every loop over them is unrolled
+// to GM, so a one-head-per-kv-head model (GPT-2) does not issue the 16-wide context step of a grouped one.
+template <int HD, int GM>
 __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     constexpr int DP = HD / 4;                         // dims per thread in the score step (4 threads per key)
+    constexpr int QP = DP + 4;                         // pitch of a quarter in qs: the four quarters land in distinct banks
     constexpr int GROUPS = AD_THREADS / HD > 0 ? AD_THREADS / HD : 1;   // key groups in the PV step
     constexpr int KPG = AD_KEYS / GROUPS;
-    __shared__ __align__(16) float qs[AD_MAXG][HD];
-    __shared__ float sc[AD_MAXG][AD_KEYS];
-    __shared__ float red[GROUPS][AD_MAXG][HD];
-    __shared__ float mg[AD_MAXG], lg[AD_MAXG];
+    __shared__ __align__(16) float qs[GM][4 * QP];
+    __shared__ __align__(16) float sc[AD_KEYS][GM];    // scores, then probabilities, of the chunk: [key][head]
+    __shared__ float red[GROUPS][GM][HD];
+    __shared__ float mg[GM], lg[GM], alpha[GM];
     __shared__ int s_last;
     const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
     const int Gh = a.H / a.Hkv;
@@ -51,9 +58,11 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     const int k00 = a.k_start[row], n1s = lens ? lens[row] : a.k_start[row + 1] - k00;
     const int k20 = a.k2_start ? a.k2_start[row] : 0, n2s = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
     const int n1 = n1s + n2s;                          // keys of both segments, segment 1 first
-    const int nsplit = (n1 + AD_KEYS - 1) / AD_KEYS;
+    const int nchunks = (n1 + AD_KEYS - 1) / AD_KEYS;
+    const int nsplit = (nchunks + a.cps - 1) / a.cps;   // CTAs that share the row's keys, cps 32-key chunks each
     if (sp >= nsplit) return;
-    const int k0 = sp * AD_KEYS;
+    const int k0 = sp * a.cps * AD_KEYS;
+    const int nch = min(a.cps, nchunks - sp * a.cps);
     const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
     const int G = Gh * nq;                             // virtual heads: vh = g * nq + qi
     // row pointer of key j of the row (either segment)
@@ -66,67 +75,127 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
 
     for (int i = tid; i < G * HD; i += AD_THREADS) {
         int vh = i / HD, d = i % HD;
-        qs[vh][d] = a.q[(int64_t)(q0 + vh % nq) * a.ldq + (kvh * Gh + vh / nq) * HD + d];
+        qs[vh][(d / DP) * QP + d % DP] = a.q[(int64_t)(q0 + vh % nq) * a.ldq + (kvh * Gh + vh / nq) * HD + d];
     }
-    __syncthreads();
-    {   // scores: four threads per key, each a quarter of the head dim
-        const int j = tid >> 2, part = tid & 3;
-        const bool valid = k0 + j < n1;
-        float kr[DP];
-        if (valid) {
-            const float4 *kp = (const float4 *)(krow(k0 + j) + kvh * HD + part * DP);
+    if (tid < GM) { mg[tid] = -INFINITY; lg[tid] = 0.f; alpha[tid] = 0.f; }
+    for (int i = tid; i < AD_KEYS * GM; i += AD_THREADS) (&sc[0][0])[i] = 0.f;     // heads past G stay 0 in the context step
+    // The CTA walks its cps chunks with a running maximum / sum per head (the usual rescaling when the maximum
+    // grows). Loads run ahead of the arithmetic: the V elements of a chunk are requested before its scores are
+    // formed, the K rows of the next chunk before the softmax of this one.
+    const int sj = tid >> 2, spart = tid & 3;             // score step: four threads per key, a quarter of the head dim each
+    const int grp = tid / HD, d = tid % HD;               // context step: thread = (key group, dim)
+    float kr[DP];
+    auto load_k = [&](int kbase) {
+        if (kbase + sj < n1) {
+            const float4 *kp = (const float4 *)(krow(kbase + sj) + kvh * HD + spart * DP);
 #pragma unroll
             for (int i = 0; i < DP / 4; i++) { float4 t = kp[i]; kr[4 * i] = t.x; kr[4 * i + 1] = t.y; kr[4 * i + 2] = t.z; kr[4 * i + 3] = t.w; }
         } else {
 #pragma unroll
             for (int i = 0; i < DP; i++) kr[i] = 0.f;
         }
-        for (int g = 0; g < G; g++) {
-            float dot = 0.f;
+    };
+    float acc[GM];
 #pragma unroll
-            for (int i = 0; i < DP; i++) dot = fmaf(kr[i], qs[g][part * DP + i], dot);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            if (part == 0) sc[g][j] = valid ? dot * a.scale : -INFINITY;
-        }
-    }
+    for (int g = 0; g < GM; g++) acc[g] = 0.f;
+    load_k(k0);
     __syncthreads();
-    for (int g = warp; g < G; g += AD_THREADS / 32) {   // chunk softmax, one warp per head
-        float s = sc[g][lane];
-        float m = s;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        float p = (s == -INFINITY) ? 0.f : expf(s - m);
-        float l = p;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-        sc[g][lane] = p;
-        if (lane == 0) { mg[g] = m; lg[g] = l; }
-    }
-    __syncthreads();
-    {   // partial context: thread = (key group, dim); V rows are read once for all heads of the group
-        const int grp = tid / HD, d = tid % HD;
-        float acc[AD_MAXG];
-#pragma unroll
-        for (int g = 0; g < AD_MAXG; g++) acc[g] = 0.f;
+    for (int c = 0; c < nch; c++) {
+        const int kb = k0 + c * AD_KEYS;
+        float vr[KPG];                                   // all V loads of this thread in flight together
         if (grp < GROUPS) {
-            float vr[KPG];                                   // all V loads of this thread in flight together
+            if (kb + AD_KEYS <= n1s) {                    // the whole chunk lies in the first segment: one base, fixed strides
+                const float *vb = a.v + (int64_t)(k00 + kb + grp * KPG) * a.ldk + kvh * HD + d;
 #pragma unroll
-            for (int jj = 0; jj < KPG; jj++) {
-                const int j = grp * KPG + jj;
-                vr[jj] = (k0 + j < n1) ? vrow(k0 + j)[kvh * HD + d] : 0.f;
+                for (int jj = 0; jj < KPG; jj++) vr[jj] = vb[(int64_t)jj * a.ldk];
+            } else {
+#pragma unroll
+                for (int jj = 0; jj < KPG; jj++) {
+                    const int j = grp * KPG + jj;
+                    vr[jj] = (kb + j < n1) ? vrow(kb + j)[kvh * HD + d] : 0.f;
+                }
             }
-#pragma unroll
-            for (int jj = 0; jj < KPG; jj++) {
-                const int j = grp * KPG + jj;
-#pragma unroll
-                for (int g = 0; g < AD_MAXG; g++) if (g < G) acc[g] = fmaf(sc[g][j], vr[jj], acc[g]);
-            }
-#pragma unroll
-            for (int g = 0; g < AD_MAXG; g++) if (g < G) red[grp][g][d] = acc[g];
         }
+        {   // scores of the chunk
+            const bool valid = kb + sj < n1;
+#pragma unroll
+            for (int g = 0; g < GM; g++) {
+                if (g < G) {                              // warp-uniform
+                    const float4 *qp = (const float4 *)&qs[g][spart * QP];
+                    float dot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < DP / 4; i++) {
+                        const float4 t = qp[i];
+                        dot = fmaf(kr[4 * i], t.x, dot); dot = fmaf(kr[4 * i + 1], t.y, dot);
+                        dot = fmaf(kr[4 * i + 2], t.z, dot); dot = fmaf(kr[4 * i + 3], t.w, dot);
+                    }
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+                    if (spart == 0) sc[sj][g] = valid ? dot * a.scale : -INFINITY;
+                }
+            }
+        }
+        if (c + 1 < nch) load_k(kb + AD_KEYS);
+        __syncthreads();
+        for (int g = warp; g < G; g += AD_THREADS / 32) {   // chunk softmax against the running maximum, one warp per head
+            float s = sc[lane][g];
+            float m = s;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const float mold = mg[g];
+            m = fmaxf(m, mold);
+            float p = (s == -INFINITY) ? 0.f : expf(s - m);
+            float l = p;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            sc[lane][g] = p;
+            __syncwarp();
+            if (lane == 0) {
+                const float al = (mold == -INFINITY) ? 0.f : expf(mold - m);
+                alpha[g] = al; mg[g] = m; lg[g] = fmaf(lg[g], al, l);
+            }
+        }
+        __syncthreads();
+        if (grp < GROUPS) {
+#pragma unroll
+            for (int g = 0; g < GM; g++) acc[g] *= alpha[g];
+#pragma unroll
+            for (int jj = 0; jj < KPG; jj++) {
+                const int j = grp * KPG + jj;
+                if constexpr (GM % 4 == 0) {
+#pragma unroll
+                    for (int g4 = 0; g4 < GM / 4; g4++) {
+                        const float4 pr = *(const float4 *)&sc[j][4 * g4];     // the same address for the whole warp: a broadcast
+                        acc[4 * g4] = fmaf(pr.x, vr[jj], acc[4 * g4]); acc[4 * g4 + 1] = fmaf(pr.y, vr[jj], acc[4 * g4 + 1]);
+                        acc[4 * g4 + 2] = fmaf(pr.z, vr[jj], acc[4 * g4 + 2]); acc[4 * g4 + 3] = fmaf(pr.w, vr[jj], acc[4 * g4 + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int g = 0; g < GM; g++) acc[g] = fmaf(sc[j][g], vr[jj], acc[g]);
+                }
+            }
+        }
+        __syncthreads();                                  // sc and alpha are rewritten by the next chunk
+    }
+    if (grp < GROUPS) {
+#pragma unroll
+        for (int g = 0; g < GM; g++) red[grp][g][d] = acc[g];
     }
     __syncthreads();
+    if (nsplit == 1) {                                    // the CTA saw every key of the row: no partials, no merge
+        for (int i = tid; i < G * HD; i += AD_THREADS) {
+            int g = i / HD, dd = i % HD;
+            float o = 0.f;
+#pragma unroll
+            for (int r = 0; r < GROUPS; r++) o += red[r][g][dd];
+            const float L = lg[g];
+            const float r = L > 0.f ? o / L : 0.f;
+            const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + dd;
+            if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+            else a.out[at] = r;
+        }
+        return;
+    }
     float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * AD_MAXG * (HD + 2);
     for (int i = tid; i < G * HD; i += AD_THREADS) {
         int g = i / HD, d = i % HD;
@@ -148,7 +217,7 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     // merge: the chunk partials of this (row, kv head), read through L2. Maxima and sums first (one load per
     // thread, all in flight together), then the rescaling weights once per head, then the context columns
     // with independent loads -- a chain of dependent L2 round trips per split would dominate the kernel.
-    __shared__ float wsm[AD_MAXSPLIT][AD_MAXG], lsm[AD_MAXSPLIT][AD_MAXG], Lg[AD_MAXG];
+    __shared__ float wsm[AD_MAXSPLIT][GM], lsm[AD_MAXSPLIT][GM], Lg[GM];
     const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * AD_MAXG * (HD + 2);
     for (int i = tid; i < nsplit * G; i += AD_THREADS) {
         int s = i / G, g = i % G;
@@ -197,7 +266,17 @@ bool attention_decode_supported(const AttnArgs &a) {
 void attention_decode(const AttnArgs &a) {
     static float *part = nullptr; static size_t part_cap = 0;
     static unsigned *count = nullptr; static size_t count_cap = 0;
-    const int max_split = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
+    // Keys of a row are shared out in 32-key chunks. With few (row, kv head) pairs every chunk gets a CTA of its own
+    // (a batch-1 decode step has nothing else to fill the GPU with); with many pairs a CTA walks several chunks,
+    // so that the fixed cost per CTA (query load, partials through L2, the merge) is paid about 16 x SMs times
+    // and not once per chunk.
+    const int max_chunks = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
+    const int64_t pairs = (int64_t)a.rows * a.Hkv;
+    int want_split = (int)std::min<int64_t>(max_chunks, cdiv((int64_t)ctx().sm_count * 16, pairs));
+    if (want_split < 1) want_split = 1;
+    static const int cps_env = getenv("NCM_B200_ATTN_DEC_CPS") ? atoi(getenv("NCM_B200_ATTN_DEC_CPS")) : 0;
+    const int cps = cps_env > 0 ? std::min(cps_env, max_chunks) : (int)cdiv(max_chunks, want_split);
+    const int max_split = (int)cdiv(max_chunks, cps);
     size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
     if (need > part_cap) {
         if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
@@ -214,17 +293,26 @@ void attention_decode(const AttnArgs &a) {
     d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
     d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
     d.step_d = a.step_d; d.len_step = a.k1_len_step;
-    d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split;
+    d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split; d.cps = cps;
     d.scale = 1.0f / sqrtf((float)a.hd);
     d.part = part; d.count = count;
     dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
     ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+    const int gq = (a.H / a.Hkv) * a.max_q;
+#define AD_LAUNCH(HD_)                                                                              \
+    do {                                                                                            \
+        if (gq <= 1) LAUNCH_PDL((k_attention_decode<HD_, 1>), grid, AD_THREADS, 0, d);              \
+        else if (gq <= 4) LAUNCH_PDL((k_attention_decode<HD_, 4>), grid, AD_THREADS, 0, d);         \
+        else if (gq <= 8) LAUNCH_PDL((k_attention_decode<HD_, 8>), grid, AD_THREADS, 0, d);         \
+        else LAUNCH_PDL((k_attention_decode<HD_, 16>), grid, AD_THREADS, 0, d);                     \
+    } while (0)
     switch (a.hd) {
-        case 16: LAUNCH_PDL(k_attention_decode<16>, grid, AD_THREADS, 0, d); break;
-        case 32: LAUNCH_PDL(k_attention_decode<32>, grid, AD_THREADS, 0, d); break;
-        case 64: LAUNCH_PDL(k_attention_decode<64>, grid, AD_THREADS, 0, d); break;
-        default: LAUNCH_PDL(k_attention_decode<128>, grid, AD_THREADS, 0, d); break;
+        case 16: AD_LAUNCH(16); break;
+        case 32: AD_LAUNCH(32); break;
+        case 64: AD_LAUNCH(64); break;
+        default: AD_LAUNCH(128); break;
     }
+#undef AD_LAUNCH
 }
 
 } // namespace ncmb

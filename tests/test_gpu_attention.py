@@ -93,6 +93,10 @@ DECODE_CASES = {
     "gpt2_like_12_heads": ([1, 31, 32, 33, 300, 1000], 12, 12),
     "qwen_like_7_heads_per_kv": ([5, 64, 513, 2048], 14, 2),
     "single_head_group_of_4": ([129, 7], 4, 1),
+    # many rows: a CTA walks several 32-key chunks with a running maximum (640 row/kv-head pairs, up to 10 chunks)
+    "many_rows_several_chunks_per_cta": (list(np.random.default_rng(1).integers(1, 300, 320)) + [320, 289], 8, 2),
+    # enough rows to fill the GPU without splitting keys: one CTA sees all keys of its row and writes the context itself
+    "one_cta_per_row_no_merge": (list(np.random.default_rng(2).integers(1, 100, 1300)), 4, 2),
 }
 
 
