@@ -11,15 +11,19 @@
 //               for up to eight chunks ahead) is transposed on chip, tcgen05.mma accumulates the
 //               128 x 64 output in TMEM; P / V^T are double-buffered so the MMAs of one chunk run
 //               under the softmax of the next
-// Every product is three TF32 MMAs over hi/lo splits (a = a_hi + a_lo), formed on chip from the
-// fp32 tiles TMA brings in, so scores and outputs are fp32-grade like the CUDA-core kernel.
+// Scores are three TF32 MMAs over hi/lo splits (a = a_hi + a_lo), formed on chip from the fp32 tiles TMA
+// brings in. P V runs on fp16 pairs (v = v1 + v2 * 2^-11, as the fp16-pair GEMM does): main += p1 v1 and
+// cross += p1 v2 + p2 v1 in two accumulators, O = main + cross * 2^-11 -- six kind::f16 MMAs per chunk where
+// TF32 needed twelve of half the depth, and that chain of small MMAs is what paces the chunk loop. Both
+// are fp32-grade like the CUDA-core kernel. A P or V^T tile is ONE 128-byte-swizzled tile whose rows hold the
+// 32 hi halves followed by the 32 lo halves; the MMA descriptors start at the half they need.
 // Key rows come from up to two segments (cached prefix, tokens of the current pass); each
 // segment is padded to a multiple of 32 score columns and the padding is masked in the softmax.
 //
 // Shared memory, reused between the two phases:
-//   QA  (64 KB)   Q hi | Q lo                                 then  V^T hi/lo, two buffers (32 KB)
+//   QA  (64 KB)   Q hi | Q lo                                 then  V^T pairs, two buffers (16 KB)
 //   KA  (144 KB)  K hi atoms | K lo atoms, 288 rows each      then  raw V, one 8 KB slot per 32-key chunk (72 KB)
-//                                                                   and P hi/lo, two buffers (64 KB)
+//                                                                   and P pairs, two buffers (32 KB)
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "split.cuh"
@@ -29,7 +33,8 @@ namespace ncmb {
 constexpr int ATC_THREADS = 512;          // softmax team: four threads per query row, eight score columns of a chunk each
 constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the PV MMAs while the team works on the next chunk
 constexpr int ATC_MAXK = 288;            // padded keys per row the kernel keeps resident
-constexpr int ATC_OCOL = 288;            // TMEM column of the output accumulator; scores use columns [0, 288)
+constexpr int ATC_OCOL = 288;            // TMEM columns of the output accumulators (main, then cross terms); scores use [0, 288)
+constexpr int ATC_PBUF = 16384, ATC_VBUF = 8192;   // one P tile (128 rows x 128 B) / one V^T tile (64 rows x 128 B)
 constexpr int ATC_VSLOTS = ATC_MAXK / 32;
 constexpr int ATC_KATOM = ATC_MAXK * 128;                    // one 32-column atom of all key rows: 36 KB
 constexpr int ATC_QA = 65536, ATC_KA = 4 * ATC_KATOM;        // 64 KB + 144 KB
@@ -48,6 +53,10 @@ struct AttnTcDev {
 // byte offset of element (row, col) in a K-major tile of 32 floats per row with 128-byte swizzle
 __device__ __forceinline__ uint32_t sw128_off(int row, int col) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) & 7) << 4) + ((col & 3) << 2));
+}
+// byte offset of byte column cb (0..127) of a row in a 128-byte-swizzled tile
+__device__ __forceinline__ uint32_t sw128_boff(int row, int cb) {
+    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((cb >> 4) ^ (row & 7)) & 7) << 4) + (cb & 15));
 }
 __device__ __forceinline__ float atc_hi(float v) {
     uint32_t u;
@@ -235,19 +244,19 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     if (warp == ATC_THREADS / 32) {
         // ---- MMA warp: O += P V for every chunk as soon as the team has filled a P / V^T buffer ----
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_tf32(128, 64);
-            const uint32_t d = tmem + (uint32_t)ATC_OCOL;
+            const uint32_t idesc = umma_idesc_f16(128, 64);
+            const uint32_t dm = tmem + (uint32_t)ATC_OCOL, dc = dm + 64u;
             for (int c = 0; c < nchunks; c++) {
                 const int b = c & 1;
                 w.wait(bar_rdy0 + 8 * b, (uint32_t)(c >> 1) & 1u, 17);
                 tc_fence_after();
-                uint64_t ph = umma_desc_sw128(smem_u32(R2 + b * 32768)), pl = umma_desc_sw128(smem_u32(R2 + b * 32768 + 16384));
-                uint64_t vh = umma_desc_sw128(smem_u32(R0 + b * 16384)), vl = umma_desc_sw128(smem_u32(R0 + b * 16384 + 8192));
+                const uint64_t p1 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF)), p2 = p1 + 4;     // lo halves start 64 B into the row
+                const uint64_t v1 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF)), v2 = v1 + 4;
 #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    umma_tf32(d, pl + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
-                    umma_tf32(d, ph + (uint64_t)(k * 2), vl + (uint64_t)(k * 2), idesc, 1u);
-                    umma_tf32(d, ph + (uint64_t)(k * 2), vh + (uint64_t)(k * 2), idesc, 1u);
+                for (int k = 0; k < 2; k++) {                                                     // 16 keys per MMA
+                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
+                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
+                    umma_f16(dc, p2 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, 1u);
                 }
                 umma_commit(bar_pv0 + 8 * b);
             }
@@ -298,20 +307,19 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
 
         // shared-memory offsets of the thread's four V elements (source: raw [key][d] atoms, destination: V^T)
         const int kk = tid & 31;
-        uint32_t vsrc[4], vdst[4];
+        uint32_t vsrc[4], vdst[4];                                   // vdst: the hi half; the lo half sits 64 B further along the row
 #pragma unroll
         for (int n = 0; n < 4; n++) {
             const int d = (tid >> 5) + 16 * n;
             vsrc[n] = (uint32_t)((d >> 5) * 4096) + sw128_off(kk, d & 31);
-            vdst[n] = sw128_off(d, kk);
+            vdst[n] = sw128_boff(d, kk * 2);
         }
         float l = 0.f;
 #pragma unroll
         for (int c = 0; c < ATC_VSLOTS; c++) {
             if (c >= nchunks) break;
             const int b = c & 1;
-            unsigned char *Phi = R2 + b * 32768, *Plo = Phi + 16384;
-            unsigned char *Vthi = R0 + b * 16384, *Vtlo = Vthi + 8192;
+            unsigned char *Pb = R2 + b * ATC_PBUF, *Vt = R0 + b * ATC_VBUF;
             if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
             {
                 const uint32_t *v = sv[c];
@@ -320,20 +328,22 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 jlo -= part * 8; jhi -= part * 8;
                 const bool inner = any && jlo <= 0 && jhi >= 8;
                 const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+                uint32_t hw[4], lw[4];                                 // eight probabilities as packed fp16 pairs
 #pragma unroll
-                for (int g = 0; g < 2; g++) {
-                    float p[4], ph[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const int j = g * 4 + e;
-                        float x = atc_ex2((__uint_as_float(v[j]) - mx) * sl2);
-                        if (!inner && !(any && j >= jlo && j < jhi)) x = 0.f;     // interior chunks skip the range tests
-                        l += x; p[e] = x; ph[e] = atc_hi(x);
+                for (int e = 0; e < 4; e++) {
+                    unsigned short h0, l0, h1, l1;
+                    float x0 = atc_ex2((__uint_as_float(v[2 * e]) - mx) * sl2), x1 = atc_ex2((__uint_as_float(v[2 * e + 1]) - mx) * sl2);
+                    if (!inner) {                                      // interior chunks skip the range tests
+                        if (!(any && 2 * e >= jlo && 2 * e < jhi)) x0 = 0.f;
+                        if (!(any && 2 * e + 1 >= jlo && 2 * e + 1 < jhi)) x1 = 0.f;
                     }
-                    const uint32_t o = rowoff + ((uint32_t)(((part * 2 + g) ^ (r & 7)) & 7) << 4);
-                    *(float4 *)(Phi + o) = make_float4(ph[0], ph[1], ph[2], ph[3]);
-                    *(float4 *)(Plo + o) = make_float4(p[0] - ph[0], p[1] - ph[1], p[2] - ph[2], p[3] - ph[3]);
+                    l += x0 + x1;
+                    h16_pair(x0, h0, l0); h16_pair(x1, h1, l1);
+                    hw[e] = (uint32_t)h0 | ((uint32_t)h1 << 16); lw[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
                 }
+                // the thread's eight keys are 16-byte chunk `part` of the hi half and chunk 4 + part of the lo half
+                *(uint4 *)(Pb + rowoff + ((uint32_t)((part ^ (r & 7)) & 7) << 4)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                *(uint4 *)(Pb + rowoff + ((uint32_t)(((4 + part) ^ (r & 7)) & 7) << 4)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
             }
             w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
             {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
@@ -344,8 +354,9 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 for (int n = 0; n < 4; n++) {
                     float x = *(const float *)(Vraw + vsrc[n]);
                     if (kk >= nvalid) x = 0.f;
-                    float hi = atc_hi(x);
-                    *(float *)(Vthi + vdst[n]) = hi; *(float *)(Vtlo + vdst[n]) = x - hi;
+                    unsigned short hi, lo;
+                    h16_pair(x, hi, lo);
+                    *(unsigned short *)(Vt + vdst[n]) = hi; *(unsigned short *)(Vt + (vdst[n] ^ 64u)) = lo;
                 }
             }
             // hand the buffers to the MMA warp: this warp's writes are visible to the async proxy, one arrival per warp
@@ -364,13 +375,18 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
-            uint32_t v[16];
-            if (nchunks > 0) tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
+            uint32_t v[16], vc[16];
+            if (nchunks > 0) {
+                tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
+                tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
+            }
             if (live) {
 #pragma unroll
                 for (int j = 0; j < 16; j += 4) {
-                    float4 o4 = make_float4(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv,
-                                            __uint_as_float(v[j + 2]) * inv, __uint_as_float(v[j + 3]) * inv);
+                    float4 o4 = make_float4(fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv,
+                                            fmaf(__uint_as_float(vc[j + 1]), H16_LO_UNSCALE, __uint_as_float(v[j + 1])) * inv,
+                                            fmaf(__uint_as_float(vc[j + 2]), H16_LO_UNSCALE, __uint_as_float(v[j + 2])) * inv,
+                                            fmaf(__uint_as_float(vc[j + 3]), H16_LO_UNSCALE, __uint_as_float(v[j + 3])) * inv);
                     if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
                     else *(float4 *)(a.out + ofs + j) = o4;

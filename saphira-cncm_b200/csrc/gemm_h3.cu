@@ -31,16 +31,6 @@ constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand 
 constexpr int h3_wtile(int BN) { return BN * H3_BK * 2; }  // one BN-row weight tile
 constexpr int h3_stage(int BN) { return 2 * H3_TILE + 2 * h3_wtile(BN); }   // x1 | x2 | W1 | W2
 
-// instruction descriptor: D fp32, A/B fp16, both K-major, M x N tile
-__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N) {
-    return (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-
 template <int H3_BN>
 __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
                                                        const __grid_constant__ CUtensorMap tmX2,
