@@ -15,15 +15,15 @@
 // brings in. P V runs on fp16 pairs (v = v1 + v2 * 2^-11, as the fp16-pair GEMM does): main += p1 v1 and
 // cross += p1 v2 + p2 v1 in two accumulators, O = main + cross * 2^-11 -- six kind::f16 MMAs per chunk where
 // TF32 needed twelve of half the depth, and that chain of small MMAs is what paces the chunk loop. Both
-// are fp32-grade like the CUDA-core kernel. A P or V^T tile is ONE 128-byte-swizzled tile whose rows hold the
-// 32 hi halves followed by the 32 lo halves; the MMA descriptors start at the half they need.
+// are fp32-grade like the CUDA-core kernel. Two chunks share one hand-over: P and V^T tiles are 64 keys wide
+// (one 128-byte-swizzled row of fp16), hi and lo in tiles of their own.
 // Key rows come from up to two segments (cached prefix, tokens of the current pass); each
 // segment is padded to a multiple of 32 score columns and the padding is masked in the softmax.
 //
 // Shared memory, reused between the two phases:
-//   QA  (64 KB)   Q hi | Q lo                                 then  V^T pairs, two buffers (16 KB)
+//   QA  (64 KB)   Q hi | Q lo                                 then  V^T pairs, two buffers (32 KB)
 //   KA  (144 KB)  K hi atoms | K lo atoms, 288 rows each      then  raw V, one 8 KB slot per 32-key chunk (72 KB)
-//                                                                   and P pairs, two buffers (32 KB)
+//                                                                   and P pairs, two buffers (64 KB)
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "split.cuh"
@@ -34,7 +34,7 @@ constexpr int ATC_THREADS = 512;          // softmax team: four threads per quer
 constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the PV MMAs while the team works on the next chunk
 constexpr int ATC_MAXK = 288;            // padded keys per row the kernel keeps resident
 constexpr int ATC_OCOL = 288;            // TMEM columns of the output accumulators (main, then cross terms); scores use [0, 288)
-constexpr int ATC_PBUF = 16384, ATC_VBUF = 8192;   // one P tile (128 rows x 128 B) / one V^T tile (64 rows x 128 B)
+constexpr int ATC_PBUF = 32768, ATC_VBUF = 16384;  // P hi | lo tiles (128 rows x 128 B each) / V^T hi | lo tiles (64 rows x 128 B each) of a 64-key step
 constexpr int ATC_VSLOTS = ATC_MAXK / 32;
 constexpr int ATC_KATOM = ATC_MAXK * 128;                    // one 32-column atom of all key rows: 36 KB
 constexpr int ATC_QA = 65536, ATC_KA = 4 * ATC_KATOM;        // 64 KB + 144 KB
@@ -246,16 +246,16 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(128, 64);
             const uint32_t dm = tmem + (uint32_t)ATC_OCOL, dc = dm + 64u;
-            for (int c = 0; c < nchunks; c++) {
-                const int b = c & 1;
-                w.wait(bar_rdy0 + 8 * b, (uint32_t)(c >> 1) & 1u, 17);
+            for (int c2 = 0; 2 * c2 < nchunks; c2++) {                 // a step = two 32-key chunks (the last one may have one)
+                const int b = c2 & 1;
+                w.wait(bar_rdy0 + 8 * b, (uint32_t)(c2 >> 1) & 1u, 17);
                 tc_fence_after();
-                const uint64_t p1 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF)), p2 = p1 + 4;     // lo halves start 64 B into the row
-                const uint64_t v1 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF)), v2 = v1 + 4;
-#pragma unroll
-                for (int k = 0; k < 2; k++) {                                                     // 16 keys per MMA
-                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
-                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)(k * 2), idesc, (c | k) ? 1u : 0u);
+                const uint64_t p1 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF)), p2 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF + 16384));
+                const uint64_t v1 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF)), v2 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF + 8192));
+                const int nk = (nchunks - 2 * c2 >= 2) ? 4 : 2;                                   // 16 keys per MMA
+                for (int k = 0; k < nk; k++) {
+                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, (c2 | k) ? 1u : 0u);
+                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)(k * 2), idesc, (c2 | k) ? 1u : 0u);
                     umma_f16(dc, p2 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, 1u);
                 }
                 umma_commit(bar_pv0 + 8 * b);
@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
 
         // shared-memory offsets of the thread's four V elements (source: raw [key][d] atoms, destination: V^T)
         const int kk = tid & 31;
-        uint32_t vsrc[4], vdst[4];                                   // vdst: the hi half; the lo half sits 64 B further along the row
+        uint32_t vsrc[4], vdst[4];                                   // vdst: offset in the hi tile; the lo tile takes the same offset
 #pragma unroll
         for (int n = 0; n < 4; n++) {
             const int d = (tid >> 5) + 16 * n;
@@ -315,48 +315,57 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             vdst[n] = sw128_boff(d, kk * 2);
         }
         float l = 0.f;
+        const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        // A step hands TWO 32-key chunks to the MMA warp: the fence, the barrier arrival and the wait for the
+        // buffer are paid once per 64 keys.
 #pragma unroll
-        for (int c = 0; c < ATC_VSLOTS; c++) {
-            if (c >= nchunks) break;
-            const int b = c & 1;
+        for (int c2 = 0; c2 < (ATC_VSLOTS + 1) / 2; c2++) {
+            if (2 * c2 >= nchunks) break;
+            const int b = c2 & 1;
             unsigned char *Pb = R2 + b * ATC_PBUF, *Vt = R0 + b * ATC_VBUF;
-            if (c >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c >> 1) - 1) & 1u, 15);   // MMAs of chunk c-2 are done with buffer b
-            {
-                const uint32_t *v = sv[c];
-                int jlo, jhi;
-                chunk_range(c, jlo, jhi);
-                jlo -= part * 8; jhi -= part * 8;
-                const bool inner = any && jlo <= 0 && jhi >= 8;
-                const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-                uint32_t hw[4], lw[4];                                 // eight probabilities as packed fp16 pairs
+            if (c2 >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c2 >> 1) - 1) & 1u, 15);   // MMAs of step c2-2 are done with buffer b
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    unsigned short h0, l0, h1, l1;
-                    float x0 = atc_ex2((__uint_as_float(v[2 * e]) - mx) * sl2), x1 = atc_ex2((__uint_as_float(v[2 * e + 1]) - mx) * sl2);
-                    if (!inner) {                                      // interior chunks skip the range tests
-                        if (!(any && 2 * e >= jlo && 2 * e < jhi)) x0 = 0.f;
-                        if (!(any && 2 * e + 1 >= jlo && 2 * e + 1 < jhi)) x1 = 0.f;
+            for (int hf = 0; hf < 2; hf++) {
+                const int c = 2 * c2 + hf;
+                if (c >= ATC_VSLOTS || c >= nchunks) break;
+                {
+                    const uint32_t *v = sv[c];
+                    int jlo, jhi;
+                    chunk_range(c, jlo, jhi);
+                    jlo -= part * 8; jhi -= part * 8;
+                    const bool inner = any && jlo <= 0 && jhi >= 8;
+                    uint32_t hw[4], lw[4];                                 // eight probabilities as packed fp16 pairs
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        unsigned short h0, l0, h1, l1;
+                        float x0 = atc_ex2((__uint_as_float(v[2 * e]) - mx) * sl2), x1 = atc_ex2((__uint_as_float(v[2 * e + 1]) - mx) * sl2);
+                        if (!inner) {                                      // interior chunks skip the range tests
+                            if (!(any && 2 * e >= jlo && 2 * e < jhi)) x0 = 0.f;
+                            if (!(any && 2 * e + 1 >= jlo && 2 * e + 1 < jhi)) x1 = 0.f;
+                        }
+                        l += x0 + x1;
+                        h16_pair(x0, h0, l0); h16_pair(x1, h1, l1);
+                        hw[e] = (uint32_t)h0 | ((uint32_t)h1 << 16); lw[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
                     }
-                    l += x0 + x1;
-                    h16_pair(x0, h0, l0); h16_pair(x1, h1, l1);
-                    hw[e] = (uint32_t)h0 | ((uint32_t)h1 << 16); lw[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+                    // the thread's eight keys are 16-byte chunk 4 hf + part of its row in the hi tile and in the lo tile
+                    const uint32_t o = rowoff + ((uint32_t)(((4 * hf + part) ^ (r & 7)) & 7) << 4);
+                    *(uint4 *)(Pb + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                    *(uint4 *)(Pb + 16384 + o) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
                 }
-                // the thread's eight keys are 16-byte chunk `part` of the hi half and chunk 4 + part of the lo half
-                *(uint4 *)(Pb + rowoff + ((uint32_t)((part ^ (r & 7)) & 7) << 4)) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                *(uint4 *)(Pb + rowoff + ((uint32_t)(((4 + part) ^ (r & 7)) & 7) << 4)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-            }
-            w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
-            {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
-                const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
-                const int c0 = c * 32;
-                const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
+                w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
+                {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
+                    const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
+                    const int c0 = c * 32;
+                    const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
 #pragma unroll
-                for (int n = 0; n < 4; n++) {
-                    float x = *(const float *)(Vraw + vsrc[n]);
-                    if (kk >= nvalid) x = 0.f;
-                    unsigned short hi, lo;
-                    h16_pair(x, hi, lo);
-                    *(unsigned short *)(Vt + vdst[n]) = hi; *(unsigned short *)(Vt + (vdst[n] ^ 64u)) = lo;
+                    for (int n = 0; n < 4; n++) {
+                        float x = *(const float *)(Vraw + vsrc[n]);
+                        if (kk >= nvalid) x = 0.f;
+                        unsigned short hi, lo;
+                        h16_pair(x, hi, lo);
+                        const uint32_t o = vdst[n] ^ (uint32_t)(hf * 64);      // keys 32..63 of the step: 64 B further along the row
+                        *(unsigned short *)(Vt + o) = hi; *(unsigned short *)(Vt + 8192 + o) = lo;
+                    }
                 }
             }
             // hand the buffers to the MMA warp: this warp's writes are visible to the async proxy, one arrival per warp
@@ -365,7 +374,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             if (lane == 0) mbar_arrive(bar_rdy0 + 8 * b);
         }
         // the commits complete in order: the last one covers every earlier MMA
-        if (nchunks > 0) { const int c = nchunks - 1; w.wait(bar_pv0 + 8 * (c & 1), (uint32_t)(c >> 1) & 1u, 16); }
+        if (nchunks > 0) { const int c2 = (nchunks - 1) >> 1; w.wait(bar_pv0 + 8 * (c2 & 1), (uint32_t)(c2 >> 1) & 1u, 16); }
         tc_fence_after();
         xch[tid] = l;
         team_sync();

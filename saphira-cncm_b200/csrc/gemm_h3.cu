@@ -22,8 +22,8 @@
 namespace ncmb {
 
 constexpr int H3_BM = 128, H3_BK = 64;                   // BK halfs = 128 bytes = one swizzle row
-// Tile widths: 128 columns for large problems; 32 columns when there are few rows (batched decode steps,
-// M <= 128), so that N / 32 CTAs stream the weights instead of N / 128.
+// Tile widths: 128 columns for large problems; 64 or 32 columns for small ones (batched decode steps, the first
+// NCP levels), chosen per call so that the busiest CTA moves the fewest bytes.
 constexpr int h3_stages(int BN) { return BN >= 128 ? 3 : 4; }
 constexpr int H3_EPI_WARPS = 8;                         // two per TMEM lane quadrant, 64 columns each
 constexpr int H3_THREADS = 64 + 32 * H3_EPI_WARPS;
@@ -266,11 +266,21 @@ void gemm_h3(const GemmArgs &a) {
         split_h16(a.W, a.K, p1, p2, a.N, a.K);
         w1 = p1; w2 = p2;
     }
-    // small problems (decode steps, the first NCP levels): 128-wide tiles would leave most SMs idle, and the
-    // call is bound by streaming W once -- narrow tiles put four times as many CTAs on it
+    // Tile width. Small problems (decode steps, the first NCP levels) leave most SMs idle with 128-wide tiles and
+    // are paced by what ONE CTA pulls through its shared memory: tiles per CTA x bytes per k-step (the 128-row
+    // activation pair plus the bn-row weight pair). The width with the least of that wins; ties go to the wider.
     static const bool narrow_ok = !getenv("NCM_B200_NO_BN32");
-    const bool narrow = narrow_ok && cdiv(a.N, 128) * cdiv(a.M, H3_BM) * 2 <= ctx().sm_count;
-    const int bn = narrow ? 32 : 128;
+    static const int bn_env = getenv("NCM_B200_H3_BN") ? atoi(getenv("NCM_B200_H3_BN")) : 0;
+    int bn = 128;
+    if (bn_env == 32 || bn_env == 64 || bn_env == 128) bn = bn_env;
+    else if (narrow_ok) {
+        int64_t best = -1;
+        for (int cand : {128, 64, 32}) {
+            const int64_t waves = cdiv(cdiv(a.N, cand) * cdiv(a.M, H3_BM), ctx().sm_count);
+            const int64_t cost = waves * (2 * H3_TILE + 2 * h3_wtile(cand));
+            if (best < 0 || cost < best) { best = cost; bn = cand; }
+        }
+    }
     const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
     const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
     // fp32 results leave through TMA stores when the rows keep 16-byte strides
@@ -283,18 +293,18 @@ void gemm_h3(const GemmArgs &a) {
     int num_kb = (int)cdiv(a.K, H3_BK);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
-    if (narrow) {
-        constexpr size_t smem = 1024 + (size_t)h3_stages(32) * h3_stage(32) + H3_EPI_WARPS * 4096 + (2 * h3_stages(32) + 4) * 8 + 16;
-        static bool set = false;
-        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        LAUNCH(k_gemm_h3<32>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
-    } else {
-        constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
-        static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");
-        static bool set = false;
-        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        LAUNCH(k_gemm_h3<128>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
-    }
+#define H3_LAUNCH(BN_)                                                                                                      \
+    do {                                                                                                                    \
+        constexpr size_t smem = 1024 + (size_t)h3_stages(BN_) * h3_stage(BN_) + H3_EPI_WARPS * 4096 + (2 * h3_stages(BN_) + 4) * 8 + 16; \
+        static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");                               \
+        static bool set = false;                                                                                            \
+        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
+        LAUNCH(k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);        \
+    } while (0)
+    if (bn == 32) H3_LAUNCH(32);
+    else if (bn == 64) H3_LAUNCH(64);
+    else H3_LAUNCH(128);
+#undef H3_LAUNCH
 }
 
 } // namespace ncmb

@@ -14,7 +14,9 @@ pytestmark = pytest.mark.gpu
 # (rows, out features, in features): full tiles, ragged tiles, K tails inside a TMA box,
 # K not a multiple of 8 (fp16 rows would break the 16-byte stride rule: engine 3 hands over to 2),
 # few rows (CUDA-core weight streaming)
-SHAPES = [(128, 128, 64), (256, 256, 512), (1000, 768, 520), (333, 200, 100), (2048, 1024, 2048), (8, 512, 512)]
+SHAPES = [(128, 128, 64), (256, 256, 512), (1000, 768, 520), (333, 200, 100), (2048, 1024, 2048), (8, 512, 512),
+          # the fp16-pair engine picks 64-column tiles for these two (the second with ragged edges), 32-column ones for the third
+          (2048, 512, 512), (1100, 520, 192), (64, 768, 128)]
 
 
 @pytest.fixture(scope="module")
