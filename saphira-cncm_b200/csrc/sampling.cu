@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
     __shared__ int hist[256];
     __shared__ unsigned long long red[SM_THREADS];
     __shared__ unsigned s_prefix, s_mask;
+    __shared__ double s_den;
     __shared__ int s_remaining, s_ncand, s_pick, s_eqbase[SM_THREADS + 1];
 
     const int b = blockIdx.x, tid = threadIdx.x, V = a.V, Lc = a.Lc;
@@ -230,10 +231,20 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
             for (int r = tid; r < keep; r += SM_THREADS)
                 probs[r] = exp((double)okey_inv((unsigned)(cand[r] >> 32)) - mx);
             __syncthreads();
+            // the sums run in rank order on one thread, as the reference's do; the divisions are independent
             if (tid == 0) {
                 double den = 0;
                 for (int r = 0; r < keep; r++) den += probs[r];
-                for (int r = 0; r < keep; r++) probs[r] /= den;
+                s_den = den;
+            }
+            __syncthreads();
+            {
+                const double den = s_den;
+                for (int r = tid; r < keep; r += SM_THREADS) probs[r] /= den;
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double den;
                 double cum = 0;
                 int nkeep = keep;
                 for (int r = 0; r < keep; r++) {
