@@ -337,6 +337,8 @@ __global__ void __launch_bounds__(256) k_qk_post_tok(float *q, int64_t ldq, int 
                                                     int64_t ntok, const float *__restrict__ qw, const float *__restrict__ kw,
                                                     const float *__restrict__ cs, const float *__restrict__ sn,
                                                     const int *__restrict__ pos, const int *__restrict__ step_d, int64_t pos_step) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     if (step_d) pos += (int64_t)(*step_d) * pos_step;
     const int64_t tok = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31, half = hd / 2, HT = H + Hkv;
@@ -385,7 +387,7 @@ void qk_post(float *q, int64_t ldq, int H, float *k, int64_t ldk, int Hkv, int h
     if (ntok <= 0 || (!qnorm_w && !cos_t)) return;
     ProfScope ps(NCMB_K_ELEM, 0, (double)ntok * (H + Hkv) * hd * 8);
     if (hd <= 64 && (hd & 1) == 0) {
-        LAUNCH(k_qk_post_tok, grid1d(ntok * 32, 256), 256, 0, q, ldq, H, k, ldk, Hkv, hd, ntok,
+        LAUNCH_PDL_IF(pdl_small(ntok / 8), k_qk_post_tok, grid1d(ntok * 32, 256), 256, 0, q, ldq, H, k, ldk, Hkv, hd, ntok,
                qnorm_w, knorm_w, cos_t, sin_t, pos_dev, step_d, pos_step);
         return;
     }

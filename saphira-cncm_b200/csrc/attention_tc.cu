@@ -108,6 +108,8 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                                                              const __grid_constant__ CUtensorMap mk1,
                                                              const __grid_constant__ CUtensorMap mk2,
                                                              AttnTcDev a) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *R0 = smem;                                    // QA
@@ -448,7 +450,7 @@ void attention_tc(const AttnArgs &a) {
     }
     dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
     ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
-    LAUNCH(k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, *mq, *mk1, *mk2, d);
+    LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, *mq, *mk1, *mk2, d);
 }
 
 } // namespace ncmb

@@ -38,6 +38,8 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                                                        const __grid_constant__ CUtensorMap tmW2,
                                                        const __grid_constant__ CUtensorMap tmY,
                                                        TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     constexpr int H3_STAGES = h3_stages(H3_BN), H3_STAGE = h3_stage(H3_BN), H3_WTILE = h3_wtile(H3_BN);
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -299,7 +301,7 @@ void gemm_h3(const GemmArgs &a) {
         static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");                               \
         static bool set = false;                                                                                            \
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
-        LAUNCH(k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);        \
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);        \
     } while (0)
     if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);

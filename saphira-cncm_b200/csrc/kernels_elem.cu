@@ -36,6 +36,8 @@ template <bool VEC4>
 __global__ void __launch_bounds__(256) k_layernorm(const float *__restrict__ x, const float *__restrict__ w,
                                                   const float *__restrict__ b, float *__restrict__ y,
                                                   float *__restrict__ ylo, int64_t rows, int C, float eps, int fmt) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -90,8 +92,8 @@ void layernorm_split(const float *x, const float *w, const float *b, float *y, f
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * (y_lo ? 12 : 8));
     bool v4 = (C % 4 == 0) && aligned16(x) && aligned16(y) && (!y_lo || aligned16(y_lo)) && (!w || aligned16(w)) && (!b || aligned16(b));
     unsigned g = grid1d(rows, 8);
-    if (v4) LAUNCH(k_layernorm<true>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
-    else LAUNCH(k_layernorm<false>, g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
+    if (v4) LAUNCH_PDL_IF(pdl_small(g), (k_layernorm<true>), g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
+    else LAUNCH_PDL_IF(pdl_small(g), (k_layernorm<false>), g, 256, 0, x, w, b, y, y_lo, rows, C, eps, fmt);
 }
 void layernorm(const float *x, const float *w, const float *b, float *y, int64_t rows, int C, float eps) {
     layernorm_split(x, w, b, y, nullptr, rows, C, eps, SPLIT_NONE);
@@ -101,6 +103,8 @@ void layernorm(const float *x, const float *w, const float *b, float *y, int64_t
 __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, const float *__restrict__ w,
                                                 float *__restrict__ y, float *__restrict__ ylo, int64_t rows, int C,
                                                 int64_t ldx, int64_t ldy, int fmt) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -121,12 +125,12 @@ __global__ void __launch_bounds__(256) k_rmsnorm(const float *__restrict__ x, co
 void rmsnorm(const float *x, const float *w, float *y, int64_t rows, int C, int64_t ldx, int64_t ldy) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 8);
-    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, (float *)nullptr, rows, C, ldx, ldy, (int)SPLIT_NONE);
+    LAUNCH_PDL_IF(pdl_small(rows / 8), k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, (float *)nullptr, rows, C, ldx, ldy, (int)SPLIT_NONE);
 }
 void rmsnorm_split(const float *x, const float *w, float *y, float *y_lo, int64_t rows, int C, int fmt) {
     if (rows <= 0) return;
     ProfScope ps(NCMB_K_NORM, 0, (double)rows * C * 12);
-    LAUNCH(k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, y_lo, rows, C, (int64_t)C, (int64_t)C, fmt);
+    LAUNCH_PDL_IF(pdl_small(rows / 8), k_rmsnorm, grid1d(rows, 8), 256, 0, x, w, y, y_lo, rows, C, (int64_t)C, (int64_t)C, fmt);
 }
 
 // ---- element-wise ----

@@ -36,6 +36,8 @@ void apply_norm(const float *x, const float *w, const float *b, float *y, int64_
 __global__ void k_kv_store(const float *__restrict__ src, int64_t ldsrc, float *__restrict__ dst, int64_t pitch,
                            int rows_per_seq, int64_t seq_pitch, int64_t ntok, int width4,
                            const int *__restrict__ step_d, int64_t step_stride) {
+    pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    pdl_wait();
     if (step_d) dst += (int64_t)(*step_d) * step_stride;       // decode steps replayed from one graph
     int64_t total = ntok * width4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -121,7 +123,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         int64_t n = ntok * width4;
         int64_t gsz = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
         ProfScope ps(NCMB_K_ELEM, 0, (double)ntok * 2 * kvd * 8);
-        LAUNCH(k_kv_store, (unsigned)(gsz > cap ? cap : gsz), 256, 0, kp, (int64_t)Wq, p.kv_store, p.kv_pitch,
+        LAUNCH_PDL_IF(pdl_small(gsz), k_kv_store, (unsigned)(gsz > cap ? cap : gsz), 256, 0, kp, (int64_t)Wq, p.kv_store, p.kv_pitch,
                p.kv_rows_per_seq, p.kv_seq_pitch, ntok, width4, p.step_d, p.kv_store_step);
     }
     if (p.kv_only) return;
