@@ -256,6 +256,7 @@ struct SampleArgs {
     int out_stride, out_off;
     float *blend_out;          // optional [Bn][Lc][V] copy of the logits actually sampled from
     float *scratch;            // [Bn][V] when V does not fit shared memory, else null
+    int picks_bound = 0;       // upper bound on the tokens a row has picked before and during this call (0 = unknown)
 };
 void sample_rows(const SampleArgs &a);
 size_t sample_scratch_floats(int Bn, int V);

@@ -550,7 +550,7 @@ static void gen_l0(NCPGen *g) {
         s.uniforms = g->uni_d ? g->uni_d + g->uni_off : nullptr;
         s.rng_seed = g->seed; s.rng_row0 = ctx().row_offset; s.rng_level = 0;
         s.out = g->l0tmp_d; s.out_stride = l0len; s.out_off = 0;
-        s.blend_out = g->blend; s.scratch = g->samp_scr;
+        s.blend_out = g->blend; s.scratch = g->samp_scr; s.picks_bound = g->total;
         sample_rows(s);
         if (g->temp > 0) g->uni_off += (size_t)Bm * l0len;
         CUDA_CHECK(cudaMemcpy2DAsync(g->codes_d, (size_t)g->total * 4, g->l0tmp_d, (size_t)l0len * 4, (size_t)l0len * 4, B,
@@ -590,7 +590,7 @@ static void gen_level(NCPGen *g, int li) {
     s.uniforms = g->uni_d ? g->uni_d + g->uni_off : nullptr;
     s.rng_seed = g->seed; s.rng_row0 = ctx().row_offset; s.rng_level = li + 1;
     s.out = g->codes_d; s.out_stride = g->total; s.out_off = g->out_off;
-    s.blend_out = g->blend; s.scratch = g->samp_scr;
+    s.blend_out = g->blend; s.scratch = g->samp_scr; s.picks_bound = g->total;
     sample_rows(s);
     if (g->temp > 0) g->uni_off += (size_t)B * Lcur;
     capture_level(g, Lcur, V);

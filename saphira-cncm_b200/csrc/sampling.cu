@@ -274,6 +274,235 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
     if (tid == 0 && a.hist_len) a.hist_len[b] = hl;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Two-phase sampling. The sequential kernel above spends most of a position on work that does not
+// depend on earlier picks: the blend and the 4096-wide selection. Penalties that only LOWER logits
+// (frequency excess, adjacency with a >= 0; no deficit bonus) touch at most P tokens, the ones
+// picked so far in the row, so the `keep` best penalised logits of a position lie among its
+// keep + P best raw ones: a token of the penalised top-keep is preceded in raw order by at most
+// keep - 1 unpenalised tokens (which precede it in penalised order too) and P penalised ones.
+//   k_sample_topc  one CTA per (row, position), all positions at once: blend, the Kc >= keep + P
+//                  best raw logits (same radix select, ties to the lowest index) -> candidates
+//   k_sample_seq   one CTA per row, positions in order, Kc entries each: the same penalty, temperature,
+//                  ordering (value descending, index ascending), fp64 probabilities and walk as above
+// Picks equal the one-kernel path's bit for bit: every number a pick depends on is computed by the
+// same operations in the same order.
+constexpr int SC_MAXC = 256;
+
+struct SampleCand {
+    SampleArgs a;
+    int Kc;
+    unsigned long long *cand;       // [Bn][Lc][Kc]: ordered key << 32 | ~index of the raw (blended) logit
+};
+
+__global__ void __launch_bounds__(SM_THREADS) k_sample_topc(SampleCand sc) {
+    const SampleArgs &a = sc.a;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    float *vals = (float *)smraw;
+    __shared__ int hist[256];
+    __shared__ unsigned s_prefix, s_mask;
+    __shared__ int s_remaining, s_ncand, s_eqbase[SM_THREADS + 1];
+    const int tid = threadIdx.x, V = a.V, Lc = a.Lc, keep = sc.Kc;
+    const int b = blockIdx.x / Lc, t = blockIdx.x % Lc;
+    const float *lc = a.logits + ((size_t)b * Lc + t) * V;
+    const float *lu = a.uncond_off ? a.logits + (((size_t)b + a.uncond_off) * Lc + t) * V : nullptr;
+    float *bo = a.blend_out ? a.blend_out + ((size_t)b * Lc + t) * V : nullptr;
+    unsigned long long *out = sc.cand + ((size_t)b * Lc + t) * keep;
+    for (int v = tid; v < V; v += SM_THREADS) {
+        float x = lc[v];
+        if (lu) x = (float)((1.0 + a.cfg_w) * (double)x - a.cfg_w * (double)lu[v]);
+        if (bo) bo[v] = x;
+        vals[v] = x;
+    }
+    if (tid == 0) { s_prefix = 0; s_mask = 0; s_remaining = keep; }
+    __syncthreads();
+    for (int pass = 3; pass >= 0; pass--) {
+        hist[tid] = 0;
+        __syncthreads();
+        unsigned prefix = s_prefix, mask = s_mask;
+        for (int v = tid; v < V; v += SM_THREADS) {
+            unsigned k = okey(vals[v]);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> (8 * pass)) & 0xff], 1);
+        }
+        __syncthreads();
+        if (tid < 32) {
+            const int rem = s_remaining, top = 255 - 8 * tid;
+            int h8[8], tot = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) { h8[i] = hist[top - i]; tot += h8[i]; }
+            int incl = tot;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int t2 = __shfl_up_sync(0xffffffffu, incl, o); if (tid >= o) incl += t2; }
+            int cum = incl - tot;
+            const bool here = cum < rem && incl >= rem;
+            const unsigned who = __ballot_sync(0xffffffffu, here);
+            if (who == 0) {
+                if (tid == 31) { s_remaining = rem - (incl - h8[7]); s_prefix = prefix; s_mask = mask | (0xffu << (8 * pass)); }
+            } else if (tid == __ffs(who) - 1) {
+                int bin = top;
+                for (int i = 0; i < 8; i++) {
+                    bin = top - i;
+                    if (bin == 0 || cum + h8[i] >= rem) break;
+                    cum += h8[i];
+                }
+                s_remaining = rem - cum;
+                s_prefix = prefix | ((unsigned)bin << (8 * pass));
+                s_mask = mask | (0xffu << (8 * pass));
+            }
+        }
+        __syncthreads();
+    }
+    const unsigned thr = s_prefix;
+    const int need_eq = s_remaining;
+    if (tid == 0) s_ncand = 0;
+    __syncthreads();
+    for (int v = tid; v < V; v += SM_THREADS) {
+        unsigned k = okey(vals[v]);
+        if (k > thr) {
+            int p = atomicAdd(&s_ncand, 1);
+            out[p] = ((unsigned long long)k << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+        }
+    }
+    const int chunk = (V + SM_THREADS - 1) / SM_THREADS;
+    const int v0 = tid * chunk, v1 = (v0 + chunk < V) ? v0 + chunk : V;
+    int eq = 0;
+    for (int v = v0; v < v1; v++) if (okey(vals[v]) == thr) eq++;
+    {
+        const int lane = tid & 31, wp = tid >> 5;
+        int v = eq;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { int t2 = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += t2; }
+        __syncthreads();                       // hist is reused for the warp totals
+        if (lane == 31) hist[wp] = v;
+        __syncthreads();
+        int base = 0;
+        for (int i = 0; i < wp; i++) base += hist[i];
+        s_eqbase[tid + 1] = base + v;
+        if (tid == 0) s_eqbase[0] = 0;
+    }
+    __syncthreads();
+    {
+        int rank = s_eqbase[tid], gt = s_ncand;
+        for (int v = v0; v < v1 && rank < need_eq; v++)
+            if (okey(vals[v]) == thr) {
+                out[gt + rank] = ((unsigned long long)thr << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+                rank++;
+            }
+    }
+}
+
+__global__ void __launch_bounds__(SC_MAXC) k_sample_seq(SampleCand sc) {
+    const SampleArgs &a = sc.a;
+    __shared__ unsigned long long cand[SC_MAXC];
+    __shared__ double probs[SC_MAXC];
+    __shared__ double s_den;
+    __shared__ int s_pick;
+    const int b = blockIdx.x, tid = threadIdx.x, Lc = a.Lc, Kc = sc.Kc;
+    double *cnt = a.cnt ? a.cnt + (size_t)b * a.cnt_stride : nullptr;
+    int *hst = a.hist ? a.hist + (size_t)b * a.hist_stride : nullptr;
+    int hl = a.hist_len ? a.hist_len[b] : 0;
+    const bool penal = (a.freq > 0.f) || (a.adj_a != 0.f);
+    const int keep = (a.top_k > 0) ? (a.top_k < a.V ? a.top_k : a.V) : a.V;
+    for (int t = 0; t < Lc; t++) {
+        unsigned long long key = 0;
+        if (tid < Kc) {
+            const unsigned long long c = sc.cand[((size_t)b * Lc + t) * Kc + tid];
+            const int v = (int)(0xffffffffu - (unsigned)(c & 0xffffffffu));
+            float x = okey_inv((unsigned)(c >> 32));
+            if (penal) {
+                double lg = x;
+                if (a.freq > 0.f) {
+                    double al = a.allow_dev ? a.allow_dev[v] * Lc : 0.0;
+                    double cc = cnt[v];
+                    double excess = cc - al;
+                    if (excess < 0) excess = 0;
+                    lg -= (double)a.freq * excess;
+                }
+                x = (float)lg;
+                if (a.adj_a != 0.f) {                    // window entries in order: the same id may repeat
+                    int w = a.adj_w > 0 ? a.adj_w : 1;
+                    int start = hl - w;
+                    if (start < 0) start = 0;
+                    for (int h = start; h < hl; h++)
+                        if (hst[h] == v) {
+                            double pen = (double)a.adj_a * pow((double)a.adj_d, (double)(hl - 1 - h));
+                            x -= (float)pen;
+                        }
+                }
+            }
+            x = x / a.temp;
+            key = ((unsigned long long)okey(x) << 32) | (unsigned)(0xffffffffu - (unsigned)v);
+        }
+        cand[tid] = key;
+        __syncthreads();
+        for (int k = 2; k <= Kc; k <<= 1)
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                if (tid < Kc) {
+                    int ixj = tid ^ j;
+                    if (ixj > tid) {
+                        unsigned long long x = cand[tid], y = cand[ixj];
+                        bool desc = ((tid & k) == 0);
+                        if (desc ? (x < y) : (x > y)) { cand[tid] = y; cand[ixj] = x; }
+                    }
+                }
+                __syncthreads();
+            }
+        const double mx = (double)okey_inv((unsigned)(cand[0] >> 32));
+        if (tid < keep) probs[tid] = exp((double)okey_inv((unsigned)(cand[tid] >> 32)) - mx);
+        __syncthreads();
+        if (tid == 0) {
+            double den = 0;
+            for (int r = 0; r < keep; r++) den += probs[r];
+            s_den = den;
+        }
+        __syncthreads();
+        if (tid < keep) probs[tid] /= s_den;
+        __syncthreads();
+        if (tid == 0) {
+            double den;
+            double cum = 0;
+            int nkeep = keep;
+            for (int r = 0; r < keep; r++) {
+                if (cum - probs[r] > (double)a.top_p) { nkeep = r; break; }
+                cum += probs[r];
+            }
+            den = 0;
+            for (int r = 0; r < nkeep; r++) den += probs[r];
+            double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
+                                    : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
+            double u = u01 * den, acc = 0;
+            int pr = nkeep - 1;
+            for (int r = 0; r < nkeep; r++) { acc += probs[r]; if (u <= acc) { pr = r; break; } }
+            int pick = (int)(0xffffffffu - (unsigned)(cand[pr] & 0xffffffffu));
+            s_pick = pick;
+            a.out[(size_t)b * a.out_stride + a.out_off + t] = pick;
+            if (cnt) cnt[pick] += 1.0;
+            if (hst) hst[hl] = pick;
+        }
+        hl++;
+        __syncthreads();                 // cnt / hist of this position are visible to the next one
+    }
+    if (tid == 0 && a.hist_len) a.hist_len[b] = hl;
+}
+
+// Kc for the two-phase path, or 0 when it does not apply
+static int two_phase_width(const SampleArgs &a) {
+    if (!(a.temp > 0.f) || a.top_k <= 0 || a.V > SM_SMEM_V) return 0;
+    const char *e = getenv("NCM_B200_SAMPLE_PHASES");          // 1 = one kernel always, 2 = two phases whenever valid
+    const int mode = e ? atoi(e) : 0;
+    if (mode == 1) return 0;
+    const bool penal = (a.freq > 0.f) || (a.adj_a != 0.f);
+    if (a.adj_a < 0.f || (a.adj_a != 0.f && a.adj_d < 0.f)) return 0;   // a negative adjacency weight (or decay) raises logits
+    if (penal && a.freq > 0.f && a.mu > 0.f && a.allow_dev) return 0;   // so does the deficit bonus
+    if (penal && a.picks_bound <= 0) return 0;
+    const int keep = a.top_k < a.V ? a.top_k : a.V;
+    int need = keep + (penal ? a.picks_bound : 0), Kc = 32;
+    while (Kc < need) Kc <<= 1;
+    if (Kc > SC_MAXC || Kc > a.V) return 0;
+    if (mode != 2 && (a.V < 8 * Kc || a.Lc < 2)) return 0;      // nothing to gain on short rows or a single position
+    return Kc;
+}
+
 size_t sample_scratch_floats(int Bn, int V) { return V > SM_SMEM_V ? (size_t)Bn * V : 0; }
 
 // ---- large candidate sets (top_k = 0 or > 2048 over a big vocabulary, one position per row) ----
@@ -417,6 +646,22 @@ void sample_rows(const SampleArgs &a) {
     if (a.temp > 0.f) {
         int keep = (a.top_k > 0) ? (a.top_k < a.V ? a.top_k : a.V) : a.V;
         if (keep > SM_MAXKEEP) { sample_rows_large(a, keep); return; }
+    }
+    if (const int Kc = two_phase_width(a)) {
+        static unsigned long long *cand = nullptr; static size_t cand_cap = 0;
+        const size_t need = (size_t)a.Bn * a.Lc * Kc;
+        if (need > cand_cap) {
+            if (cand) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(cand); }
+            cand = (unsigned long long *)dev_alloc(need * 8); cand_cap = need;
+        }
+        SampleCand sc;
+        sc.a = a; sc.Kc = Kc; sc.cand = cand;
+        static bool set = false;
+        if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_sample_topc, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * SM_SMEM_V)); set = true; }
+        ProfScope ps(NCMB_K_SAMPLE, 0, (double)a.Bn * a.Lc * a.V * (a.uncond_off ? 8 : 4));
+        LAUNCH(k_sample_topc, (unsigned)(a.Bn * a.Lc), SM_THREADS, sizeof(float) * (size_t)a.V, sc);
+        LAUNCH(k_sample_seq, (unsigned)a.Bn, SC_MAXC, 0, sc);
+        return;
     }
     SampleDev sd;
     sd.a = a;

@@ -15,6 +15,8 @@ SAMPLERS = {
     "cfg_pen": dict(temp=0.8, top_k=5, top_p=0.9, cfg=1.5, freq=0.2, mu=0.1, adj=(0.3, 2, 0.5),
                     seed=11, allow=True),
     "nucleus": dict(temp=1.0, top_k=0, top_p=0.7, seed=13),
+    # penalties that only lower logits (no deficit bonus): the case the two-phase device sampler covers
+    "cfg_pen_down": dict(temp=0.8, top_k=5, top_p=0.9, cfg=1.5, freq=0.2, adj=(0.3, 2, 0.5), seed=17, allow=True),
 }
 
 # tiny NCP variants: name -> spec overrides

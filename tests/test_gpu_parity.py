@@ -77,6 +77,34 @@ def test_ncp_variant_matches_oracle(cuda, tmp, variant):
     assert not bad, f"integer outputs differ from the oracle: {bad}"
 
 
+@pytest.mark.parametrize("variant", ["full", "shared", "plain"])
+def test_two_phase_sampler_picks_what_the_one_kernel_sampler_picks(cuda, tmp, variant):
+    """Candidate selection for all positions at once + a sequential kernel over the candidates (used when penalties
+    can only lower logits) against the oracle and against the one-kernel sampler, forced on at the tiny vocabularies."""
+    import capi
+    import cases
+    import orc
+    import synth
+    spec = cases.ncp_spec(variant)
+    conf, w = synth.write_ncp(spec, tmp)
+    pre, l0, _ = cases.ncp_inputs(spec)
+    om = orc.Model(conf, w)
+    gm = capi.NcpModel(cuda, conf, w, arena_mb=64)
+    try:
+        for sname in ("topk", "cfg", "cfg_pen_down"):
+            kw = cases.sampler_kwargs(sname, spec)
+            if kw.get("cfg", 0) > 0 and spec.pad_id < 0:
+                continue
+            use_l0 = l0 if not spec.query_level0 else None
+            want = om.generate(pre, l0=use_l0, **kw)
+            for mode in ("1", "2"):
+                os.environ["NCM_B200_SAMPLE_PHASES"] = mode
+                got = gm.generate(pre, l0=use_l0, **kw)
+                assert np.array_equal(got, want), (variant, sname, mode)
+    finally:
+        os.environ.pop("NCM_B200_SAMPLE_PHASES", None)
+
+
 def _gen_kwargs(spec):
     g = dict(spec.gen)
     kw = dict(temp=g.get("temperature", 0.0), top_k=g.get("top_k", 0), top_p=g.get("top_p", 1.0),
