@@ -342,7 +342,7 @@ void ncmb_vq_nearest_dev(VQState *vq, int level, const float *x_dev, long long n
  * fp32-only reference consumes them); every projection matrix whose elements all are bf16 values gets an
  * exact 2-byte copy that decode steps stream instead of the fp32 one -- same results, half the bytes. */
 typedef struct NcmbLM NcmbLM;
-NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights);
+NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_qwen, int bf16_weights);   /* weights: .ncm, .nckpt or .safetensors */
 void   ncmb_lm_close(NcmbLM *m);
 int    ncmb_lm_vocab(const NcmbLM *m);
 /* Decode steps of up to four sequences (head dim 64) can run as ONE persistent cooperative kernel with grid
@@ -356,6 +356,12 @@ int    ncmb_lm_generate(NcmbLM *m, const int *prompts, int B, int np, int n_new,
                         int eos, int *out);
 /* logits of one sequence: all positions ([T][V]) or the last one ([V]) to host */
 void   ncmb_lm_logits(NcmbLM *m, const int *ids, int T, int last_only, float *out_host);
+/* A Hugging Face .safetensors file straight into a WeightStore on the device, with the tensor rules of the
+ * reference's offline converters (tools/gpt2import.c:385-417, tools/qwenimport.c:383-420, which write an NCM1
+ * file instead): F16 / BF16 widened to fp32, "*.attn.bias" mask buffers dropped, names and order kept, and with
+ * conv1d_transpose != 0 (GPT-2) the 2-D c_attn / c_proj / c_fc weights transposed from [in][out] to [out][in].
+ * 0 / -1. ncmb_lm_open takes such a path too. Tokenizer assets stay with the reference's tools (host text). */
+int    ncmb_weights_import_safetensors(WeightStore *ws, const char *path, int conv1d_transpose);
 /* Mean next-token negative log-likelihood of B windows (gpt2_nll gpt2.c:160-176, qwen_nll qwen.c:192-208, which
  * take one window and read the [T][V] logits on the host). ids: host int[B][T]; lens: host int[B] ids used per
  * window (NULL = T); nll_out: host double[B], the mean over lens[b] - 1 positions of

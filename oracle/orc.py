@@ -361,3 +361,41 @@ class LM:
         n = lib().orc_lm_generate(self.h, _p(prompt), prompt.size, n_new, temp, top_k, top_p, seed,
                                   eos, _p(out))
         return out[:n]
+
+
+def safetensors_import_rules(path: str, conv1d_transpose: bool) -> "dict[str, np.ndarray]":
+    """What the reference's offline converters make of a .safetensors file (tools/gpt2import.c:385-417,
+    tools/qwenimport.c:383-420): F16 / BF16 widened to float32, buffers named "*.attn.bias" dropped, and for GPT-2
+    the 2-D c_attn / c_proj / c_fc "*.weight" matrices transposed. Test infrastructure."""
+    import json
+    import struct
+    raw = open(path, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])
+    data = raw[8 + hlen:]
+    out = {}
+    for name, e in header.items():
+        if name == "__metadata__" or name.endswith(".attn.bias"):
+            continue
+        a, b = e["data_offsets"]
+        if e["dtype"] == "F32":
+            x = np.frombuffer(data[a:b], np.float32)
+        elif e["dtype"] == "F16":
+            # f16_to_f32 of the converters (gpt2import.c:250-259): normal numbers, infinities and NaNs as IEEE; a
+            # subnormal with mantissa m becomes the float whose BITS are 0x33800000 + (m << 13), which equals
+            # m * 2^-24 only for m = 1 -- kept, because the .ncm files the reference runs on hold these values
+            h = np.frombuffer(data[a:b], np.uint16).astype(np.uint32)
+            sg, ex, m = (h >> 15) & 1, (h >> 10) & 0x1F, h & 0x3FF
+            bits = np.where(ex == 0, np.where(m != 0, 0x33800000 + (m << 13), 0),
+                            np.where(ex == 31, 0x7F800000 | (m << 13), ((ex + 112) << 23) | (m << 13)))
+            x = ((sg << 31) | bits).astype(np.uint32).view(np.float32)
+        elif e["dtype"] == "BF16":
+            x = (np.frombuffer(data[a:b], np.uint16).astype(np.uint32) << 16).view(np.float32)
+        else:
+            raise ValueError(e["dtype"])
+        x = x.reshape(e["shape"])
+        if conv1d_transpose and x.ndim == 2 and name.endswith(".weight") and \
+                any(k in name for k in ("c_attn", "c_proj", "c_fc", "proj")):
+            x = np.ascontiguousarray(x.T)
+        out[name] = np.ascontiguousarray(x, np.float32)
+    return out

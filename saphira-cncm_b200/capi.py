@@ -146,6 +146,7 @@ _SIGS = {
     "ncmb_lm_generate": (_I, [_P, _P, _I, _I, _I, _F, _I, _F, _U64, _I, _P]),
     "ncmb_lm_logits": (None, [_P, _P, _I, _I, _P]),
     "ncmb_lm_nll": (None, [_P, _P, _I, _I, _P, _P]),
+    "ncmb_weights_import_safetensors": (_I, [C.POINTER(WeightStore), C.c_char_p, _I]),
     "gpt2_cmd_ppl": (_I, [_P, C.c_char_p, C.c_char_p, C.c_char_p]),
     "gpt2_cmd_verify": (_I, [_P, C.c_char_p, C.c_char_p, C.c_char_p]),
     "qwen_cmd_ppl": (_I, [_P, C.c_char_p, C.c_char_p, C.c_char_p]),

@@ -22,6 +22,8 @@ int tok_encode(TokState *t, const char *text, int *out, int cap) __attribute__((
 int tok_decode(TokState *t, const int *ids, int n, char *out, int cap, int skip_special) __attribute__((weak));
 }
 
+extern "C" int ncmb_weights_import_safetensors(WeightStore *ws, const char *path, int conv1d_transpose);
+
 struct NcmbLM {
     NCMConfig cfg;
     WeightStore ws{};
@@ -53,7 +55,12 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
     ensure_device();
     NcmbLM *m = new NcmbLM();
     m->cfg = *c; m->is_qwen = is_qwen;
-    if (weights_load(&m->ws, weights)) { delete m; return nullptr; }
+    {   // a Hugging Face checkpoint is read directly (the reference converts it to NCM1 offline first)
+        const size_t wl = strlen(weights);
+        const bool st = wl > 12 && strcmp(weights + wl - 12, ".safetensors") == 0;
+        const int rc = st ? ncmb_weights_import_safetensors(&m->ws, weights, is_qwen ? 0 : 1) : weights_load(&m->ws, weights);
+        if (rc) { delete m; return nullptr; }
+    }
     WeightStore *ws = &m->ws;
     m->NL = c->n_layer; m->H = c->n_head; m->C = c->n_embd; m->hd = m->C / m->H;
     m->nkv = (is_qwen && c->n_kv_heads > 0) ? c->n_kv_heads : c->n_head;

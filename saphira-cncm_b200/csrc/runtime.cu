@@ -358,6 +358,13 @@ struct Cursor {
 };
 } // namespace
 
+// a store whose tensors were placed in `slab` by another loader (the safetensors import): weights_free then treats it
+// like a store of weights_load
+void ncmb_store_adopt_slab(WeightStore *ws, void *slab) {
+    for (int i = 0; i < ws->count; i++) slab_members().insert(ws->items[i].t->data);
+    slab_of_store()[ws->items] = slab;
+}
+
 // 1 = NCK1 checkpoint, 0 = NCM1 weights, -1 = neither / unreadable (reference ckpt_probe src/ckpt.c:67-77)
 int ckpt_probe(const char *path) {
     FILE *f = fopen(path, "rb");

@@ -91,6 +91,58 @@ def write_nck1(path: str, tensors: "dict[str, np.ndarray]", step: int = 7, optim
         f.write(out)
 
 
+def _to_f16_bits(a: np.ndarray) -> np.ndarray:
+    return a.astype(np.float16).view(np.uint16)
+
+
+def _to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    return (_round_bf16_early(a).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def _round_bf16_early(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def write_safetensors(path: str, tensors: "dict[str, np.ndarray]", dtypes: "dict[str, str] | str" = "F32",
+                      metadata: "dict[str, str] | None" = None) -> None:
+    """A Hugging Face .safetensors file: u64 header length, JSON header (name -> dtype, shape, data_offsets),
+    then the tensors' bytes. dtypes: one of F32 / F16 / BF16 for all tensors, or per tensor name."""
+    import json
+    header, blobs, off = {}, [], 0
+    if metadata is not None:
+        header["__metadata__"] = metadata
+    for name, arr in tensors.items():
+        dt = dtypes if isinstance(dtypes, str) else dtypes.get(name, "F32")
+        a = np.ascontiguousarray(arr, np.float32)
+        raw = {"F32": lambda x: x.tobytes(), "F16": lambda x: _to_f16_bits(x).tobytes(),
+               "BF16": lambda x: _to_bf16_bits(x).tobytes()}[dt](a)
+        header[name] = {"dtype": dt, "shape": list(a.shape), "data_offsets": [off, off + len(raw)]}
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def lm_tensors_hf(s: "LMSpec", seed: int) -> "dict[str, np.ndarray]":
+    """The tensors of lm_tensors() as a Hugging Face checkpoint stores them: GPT-2's Conv1D matrices [in][out]
+    and a causal-mask buffer per layer; Qwen2's nn.Linear matrices unchanged."""
+    out = {}
+    for name, a in lm_tensors(s, seed).items():
+        if s.kind == "gpt2" and a.ndim == 2 and name.endswith(".weight") and any(k in name for k in ("c_attn", "c_proj", "c_fc")):
+            a = np.ascontiguousarray(a.T)
+        out[name] = a
+        if s.kind == "gpt2" and name.endswith("attn.c_attn.weight"):
+            out[name[:-len("c_attn.weight")] + "bias"] = np.tril(np.ones((1, 1, 8, 8), np.float32))
+    return out
+
+
 def write_conf(path: str, kv: "dict[str, object]") -> None:
     with open(path, "w") as f:
         for k, v in kv.items():

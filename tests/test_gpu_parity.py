@@ -538,3 +538,46 @@ def _read_ncm(path):
             (nb,) = struct.unpack("<Q", f.read(8))
             out[name] = np.frombuffer(f.read(nb), np.float32).reshape(shape).copy()
     return out
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "qwen"])
+def test_safetensors_import_on_the_device(cuda, tmp, kind):
+    """ncmb_weights_import_safetensors against the converters' rules (orc.safetensors_import_rules, itself pinned
+    against tools/gpt2import.c / tools/qwenimport.c in the CPU suite), and a model opened from the checkpoint."""
+    import ctypes as C
+    import capi
+    import orc
+    import synth
+    from test_oracle_pin import _hf_files
+    spec, paths = _hf_files(tmp, kind)
+    for tag, p in paths.items():
+        want = orc.safetensors_import_rules(p, kind == "gpt2")
+        ws = capi.WeightStore()
+        assert cuda.ncmb_weights_import_safetensors(C.byref(ws), p.encode(), int(kind == "gpt2")) == 0
+        assert ws.count == len(want)
+        for name, w in want.items():
+            got = cuda.tensor_host(ws, name)
+            assert got is not None and helpers.same_bits(got, w), (tag, name)
+        assert cuda.tensor_host(ws, "h.0.attn.bias") is None
+        cuda.weights_free(C.byref(ws))
+    # broken files are refused
+    raw = open(paths["f32"], "rb").read()
+    for tag, data in (("cut", raw[:len(raw) // 2]), ("nojson", raw[:8] + b"[" + raw[9:])):
+        bad = os.path.join(tmp, f"{kind}_{tag}.safetensors")
+        open(bad, "wb").write(data)
+        ws = capi.WeightStore()
+        assert cuda.ncmb_weights_import_safetensors(C.byref(ws), bad.encode(), 1) == -1, tag
+        assert ws.count == 0 and not ws.items
+    # the model runs from the checkpoint as it runs from the converted weights
+    conf, w = synth.write_lm(spec, tmp)
+    cfg = cuda.load_config(conf)
+    pr = np.ascontiguousarray(synth.lm_prompts(spec, 1, 9, 3)[0])
+    outs = []
+    for path in (w, paths["f32"]):
+        m = cuda.ncmb_lm_open(cfg, path.encode(), int(kind == "qwen"), 0)
+        assert m
+        lg = np.zeros((pr.size, spec.vocab), np.float32)
+        cuda.ncmb_lm_logits(m, pr.ctypes.data, pr.size, 0, lg.ctypes.data)
+        outs.append(lg)
+        cuda.ncmb_lm_close(m)
+    assert helpers.same_bits(outs[0], outs[1])

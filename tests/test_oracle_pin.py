@@ -95,3 +95,51 @@ def test_checkpoint_writer_is_read_by_the_reference(tmp_path):
     open(bad, "wb").write(raw)
     with pytest.raises(RuntimeError):
         ref.load_weights(bad)
+
+
+def _hf_files(tmp, kind):
+    import synth
+    spec = synth.spec_gpt2_tiny() if kind == "gpt2" else synth.spec_qwen_tiny()
+    hf = synth.lm_tensors_hf(spec, 4321)
+    names = list(hf)
+    dtypes = {n: ("F32", "F16", "BF16")[i % 3] for i, n in enumerate(names)}
+    paths = {}
+    for tag, dt in (("f32", "F32"), ("mixed", dtypes)):
+        p = os.path.join(tmp, f"{kind}_{tag}.safetensors")
+        synth.write_safetensors(p, hf, dt, metadata={"format": "pt", "note": 'quotes " and \\ and {braces}'})
+        paths[tag] = p
+    return spec, paths
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "qwen"])
+def test_safetensors_rules_match_the_reference_converters(tmp_path, kind):
+    """oracle.safetensors_import_rules (which the GPU import is compared with) against the reference's own offline
+    converters, tools/gpt2import.c and tools/qwenimport.c, built unchanged into oracle/_ref."""
+    import subprocess
+    tool = os.path.join(os.path.dirname(helpers.REF_LIB), f"{kind}import")
+    if not os.path.exists(tool):
+        pytest.skip("reference converters not built")
+    from test_gpu_parity import _read_ncm
+    spec, paths = _hf_files(str(tmp_path), kind)
+    (tmp_path / "vocab.json").write_text("{}")
+    (tmp_path / "tokenizer.json").write_text('{"model": {"vocab": {}, "merges": []}, "added_tokens": []}')
+    (tmp_path / "merges.txt").write_text("#version: 0.2\n")
+    for tag, p in paths.items():
+        out = tmp_path / f"out_{tag}"
+        out.mkdir()
+        second = "vocab.json" if kind == "gpt2" else "tokenizer.json"
+        subprocess.run([tool, p, str(tmp_path / second), str(tmp_path / "merges.txt"), str(out)],
+                       capture_output=True, timeout=120)            # the tokenizer half may reject the empty vocabulary
+        assert (out / "model.ncm").exists(), tag
+        ref = _read_ncm(str(out / "model.ncm"))
+        mine = orc.safetensors_import_rules(p, kind == "gpt2")
+        assert list(ref) == list(mine), tag
+        for n in ref:
+            assert helpers.same_bits(ref[n], mine[n]), (tag, n)
+    # and the f32 file converts back to the tensors the NCM1 writer emits for the same spec
+    import synth
+    direct = synth.lm_tensors(spec, 4321)
+    mine = orc.safetensors_import_rules(paths["f32"], kind == "gpt2")
+    assert set(mine) == set(direct)
+    for n in direct:
+        assert helpers.same_bits(mine[n], np.ascontiguousarray(direct[n], np.float32)), n
