@@ -31,6 +31,9 @@ def build_ref(ref_dir: str = "/root/reference") -> "str | None":
     if not os.path.isdir(os.path.join(ref_dir, "src")):
         return REF_LIB if os.path.exists(REF_LIB) else None
     subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref_dir}"])
+    # the reference's command-line front end linked against the GPU library (needs that library built)
+    if os.path.exists(os.path.join(HERE, "..", "saphira-cncm_b200", "libncm_b200.so")):
+        subprocess.check_call(["make", "-s", "-C", HERE, "cli", f"REF={ref_dir}"])
     return REF_LIB
 
 

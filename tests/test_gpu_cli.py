@@ -1,0 +1,133 @@
+"""The reference's own command-line front end, linked against libncm_b200.so, beside the reference's CPU build.
+
+oracle/Makefile's `cli` target compiles the reference's main.c, tok.c and tok_tables.c unchanged, adds the library's
+link-time stand-ins for the training / viewer entry points (saphira-cncm_b200/cli_stubs.c) and links them against
+the GPU library; `ref` builds the all-CPU binary from the same main.c. Both are run on the same seeded model files
+and their output is compared: the text of `gen`, the `idx:` line and stage checksums of `infer`, the per-board
+records of `eval-sudoku`, the event stream of `sudoku-stream`, the `ids:` line of `gpt2-gen` / `qwen-gen` and the
+`docs=... nll=...` line of `gpt2-ppl`. This is the drop-in boundary exercised the way a user of the reference
+would: same commands, same files, the compute objects swapped."""
+import dataclasses
+import json
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+REF_DIR = os.path.dirname(helpers.REF_LIB)
+CPU, GPU = os.path.join(REF_DIR, "cncm"), os.path.join(REF_DIR, "cncm_b200")
+
+
+def _run(exe, args, cwd):
+    r = subprocess.run([exe] + args, capture_output=True, text=True, timeout=600, cwd=cwd)
+    return r.returncode, r.stdout, r.stderr
+
+
+@pytest.fixture(scope="module")
+def both(tmp_path_factory):
+    if not (os.path.exists(CPU) and os.path.exists(GPU)):
+        pytest.skip("linked command-line binaries not built (make -C oracle ref cli)")
+    return str(tmp_path_factory.mktemp("cli"))
+
+
+def _sudoku_model(tmp):
+    import synth
+    # a 9 x 9 board in the reference's framing: wrap | 9 cells (sep 9 cells) x 8 | wrap = 91 ids, ids 0..11
+    spec = dataclasses.replace(synth.spec_c1(ladder=(1, 3, 9, 91)), name="cli_sudoku", prefix_len=91)
+    conf, w = synth.write_ncp(spec, tmp)
+    rng = np.random.default_rng(3)
+    rows = []
+    for _ in range(5):
+        cells = rng.integers(1, 10, size=(9, 9)) * (rng.random((9, 9)) < 0.5)
+        ids = [11]
+        for r in range(9):
+            ids += [int(v) for v in cells[r]]
+            if r < 8:
+                ids.append(10)
+        ids.append(11)
+        rows.append(ids)
+    return spec, conf, w, rows
+
+
+def _floats_close(a, b, tol):
+    fa, fb = re.findall(r"-?\d+\.\d+", a), re.findall(r"-?\d+\.\d+", b)
+    assert len(fa) == len(fb), (a, b)
+    for x, y in zip(fa, fb):
+        assert abs(float(x) - float(y)) <= tol * max(1.0, abs(float(y))), (a, b)
+
+
+def test_gen_and_infer_print_what_the_cpu_build_prints(both):
+    spec, conf, w, rows = _sudoku_model(both)
+    base = ["--conf", conf, "--weights", w, "--asset-dir", both]
+    ids = ",".join(map(str, rows[0]))
+    for extra in (["--temp", "0"], ["--temp", "0.8", "--top-k", "5", "--top-p", "0.9", "--seed", "3", "--n", "2"]):
+        args = ["gen"] + base + ["--prefix", ids] + extra
+        want, got = _run(CPU, args, both), _run(GPU, args, both)
+        assert want[0] == 0 and got[0] == 0, (want, got)
+        assert got[1] == want[1] and want[1].strip(), (extra, got[1], want[1])
+    args = ["infer"] + base + ["--ids", ",".join(map(str, rows[1]))]
+    want, got = _run(CPU, args, both), _run(GPU, args, both)
+    assert want[0] == 0 and got[0] == 0, (want, got)
+    wl, gl = want[1].strip().splitlines(), got[1].strip().splitlines()
+    assert len(wl) == len(gl) and len(wl) >= 4
+    for a, b in zip(gl, wl):
+        assert a.split()[0] == b.split()[0]
+        if b.startswith("idx:"):
+            assert a == b                                  # quantizer codes: exact
+        else:
+            _floats_close(a, b, 2e-4)                      # checksums printed with six decimals
+
+
+def test_eval_sudoku_and_stream_records(both):
+    spec, conf, w, rows = _sudoku_model(both)
+    base = ["--conf", conf, "--weights", w, "--asset-dir", both]
+    inp, refs = os.path.join(both, "inputs.txt"), os.path.join(both, "refs.txt")
+    with open(inp, "w") as f, open(refs, "w") as g:
+        for r in rows:
+            f.write(" ".join(map(str, r)) + "\n")
+            g.write(" ".join(map(str, r)) + "\n")
+    outs = {}
+    for tag, exe in (("cpu", CPU), ("gpu", GPU)):
+        jl = os.path.join(both, f"eval_{tag}.jsonl")
+        rc, out, err = _run(exe, ["eval-sudoku"] + base + ["--inputs", inp, "--refs", refs, "--jsonl", jl], both)
+        assert rc == 0, err
+        recs = [json.loads(ln) for ln in open(jl)]
+        for r in recs:
+            r.pop("ms")                                    # wall-clock per board
+        outs[tag] = (out, recs)
+    assert outs["gpu"][0] == outs["cpu"][0] and "solved" in outs["cpu"][0]
+    assert outs["gpu"][1] == outs["cpu"][1] and len(outs["cpu"][1]) == len(rows)
+    # the level-by-level event stream (NDJSON) of one board, driven through the stepper API
+    args = ["sudoku-stream"] + base + ["--prefix", ",".join(map(str, rows[2])), "--seed", "1"]
+    want, got = _run(CPU, args, both), _run(GPU, args, both)
+    assert want[0] == got[0] == 0, (want[2], got[2])
+
+    def events(text):
+        evs = []
+        for ln in text.strip().splitlines():
+            e = json.loads(ln)
+            for k in [k for k in e if k.endswith("ms") or k in ("t", "elapsed", "time")]:
+                e.pop(k)
+            evs.append(e)
+        return evs
+    assert events(got[1]) == events(want[1]) and len(events(want[1])) >= 3
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "qwen"])
+def test_decoder_lm_commands(both, kind):
+    import synth
+    spec = synth.spec_gpt2_tiny() if kind == "gpt2" else synth.spec_qwen_tiny()
+    conf, w = synth.write_lm(spec, both)
+    base = ["--conf", conf, "--weights", w, "--asset-dir", both]
+    pr = ",".join(str(int(v)) for v in synth.lm_prompts(spec, 1, 9, 3)[0])
+    for extra in (["--n", "12"], ["--n", "12", "--temp", "0.7", "--top-p", "0.95", "--seed", "9"]):
+        args = [f"{kind}-gen"] + base + ["--ids", pr] + extra
+        want, got = _run(CPU, args, both), _run(GPU, args, both)
+        assert want[0] == 0 and got[0] == 0, (want, got)
+        assert got[1].splitlines()[0] == want[1].splitlines()[0] and want[1].startswith("ids:"), (got[1], want[1])
