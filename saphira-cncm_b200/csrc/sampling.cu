@@ -403,10 +403,12 @@ __global__ void __launch_bounds__(SC_MAXC) k_sample_seq(SampleCand sc) {
     int hl = a.hist_len ? a.hist_len[b] : 0;
     const bool penal = (a.freq > 0.f) || (a.adj_a != 0.f);
     const int keep = (a.top_k > 0) ? (a.top_k < a.V ? a.top_k : a.V) : a.V;
+    unsigned long long c_next = tid < Kc ? sc.cand[(size_t)b * Lc * Kc + tid] : 0;
     for (int t = 0; t < Lc; t++) {
         unsigned long long key = 0;
+        const unsigned long long c = c_next;
+        if (t + 1 < Lc && tid < Kc) c_next = sc.cand[((size_t)b * Lc + t + 1) * Kc + tid];   // in flight under this position's work
         if (tid < Kc) {
-            const unsigned long long c = sc.cand[((size_t)b * Lc + t) * Kc + tid];
             const int v = (int)(0xffffffffu - (unsigned)(c & 0xffffffffu));
             float x = okey_inv((unsigned)(c >> 32));
             if (penal) {
@@ -433,20 +435,24 @@ __global__ void __launch_bounds__(SC_MAXC) k_sample_seq(SampleCand sc) {
             x = x / a.temp;
             key = ((unsigned long long)okey(x) << 32) | (unsigned)(0xffffffffu - (unsigned)v);
         }
-        cand[tid] = key;
-        __syncthreads();
+        // bitonic sort, descending, one entry per thread: exchanges within a warp by shuffle, the few across
+        // warps (partner distance >= 32) through shared memory
         for (int k = 2; k <= Kc; k <<= 1)
             for (int j = k >> 1; j > 0; j >>= 1) {
-                if (tid < Kc) {
-                    int ixj = tid ^ j;
-                    if (ixj > tid) {
-                        unsigned long long x = cand[tid], y = cand[ixj];
-                        bool desc = ((tid & k) == 0);
-                        if (desc ? (x < y) : (x > y)) { cand[tid] = y; cand[ixj] = x; }
-                    }
+                unsigned long long other;
+                if (j >= 32) {
+                    cand[tid] = key;
+                    __syncthreads();
+                    other = cand[tid ^ j];
+                    __syncthreads();
+                } else {
+                    other = __shfl_xor_sync(0xffffffffu, key, j);
                 }
-                __syncthreads();
+                const bool keep_max = (((tid & k) == 0) == ((tid & j) == 0));   // descending run: the lower index keeps the larger
+                key = keep_max ? (key > other ? key : other) : (key < other ? key : other);
             }
+        cand[tid] = key;
+        __syncthreads();
         const double mx = (double)okey_inv((unsigned)(cand[0] >> 32));
         if (tid < keep) probs[tid] = exp((double)okey_inv((unsigned)(cand[tid] >> 32)) - mx);
         __syncthreads();
@@ -459,25 +465,36 @@ __global__ void __launch_bounds__(SC_MAXC) k_sample_seq(SampleCand sc) {
         if (tid < keep) probs[tid] /= s_den;
         __syncthreads();
         if (tid == 0) {
-            double den;
+            // nucleus cut. The running sum of the kept ranks is at once the reference's renormaliser (its second sum
+            // adds the same numbers in the same order) and, rank by rank, the accumulator of its final walk.
             double cum = 0;
             int nkeep = keep;
             for (int r = 0; r < keep; r++) {
                 if (cum - probs[r] > (double)a.top_p) { nkeep = r; break; }
                 cum += probs[r];
+                probs[r] = cum;                          // from here on: inclusive running sums
             }
-            den = 0;
-            for (int r = 0; r < nkeep; r++) den += probs[r];
-            double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
-                                    : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
-            double u = u01 * den, acc = 0;
-            int pr = nkeep - 1;
-            for (int r = 0; r < nkeep; r++) { acc += probs[r]; if (u <= acc) { pr = r; break; } }
-            int pick = (int)(0xffffffffu - (unsigned)(cand[pr] & 0xffffffffu));
-            s_pick = pick;
-            a.out[(size_t)b * a.out_stride + a.out_off + t] = pick;
-            if (cnt) cnt[pick] += 1.0;
-            if (hst) hst[hl] = pick;
+            const double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
+                                          : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
+            s_den = u01 * cum;
+            s_pick = nkeep;                              // handed to the search below
+        }
+        __syncthreads();
+        {   // first rank whose running sum reaches u; the last kept rank if none does
+            const int nkeep = s_pick;
+            const double u = s_den;
+            const bool hit = tid < nkeep && u <= probs[tid];
+            __shared__ int s_first;
+            if (tid == 0) s_first = nkeep - 1;
+            __syncthreads();
+            if (hit) atomicMin(&s_first, tid);
+            __syncthreads();
+            if (tid == 0) {
+                const int pick = (int)(0xffffffffu - (unsigned)(cand[s_first] & 0xffffffffu));
+                a.out[(size_t)b * a.out_stride + a.out_off + t] = pick;
+                if (cnt) cnt[pick] += 1.0;
+                if (hst) hst[hl] = pick;
+            }
         }
         hl++;
         __syncthreads();                 // cnt / hist of this position are visible to the next one
@@ -660,7 +677,7 @@ void sample_rows(const SampleArgs &a) {
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_sample_topc, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * SM_SMEM_V)); set = true; }
         ProfScope ps(NCMB_K_SAMPLE, 0, (double)a.Bn * a.Lc * a.V * (a.uncond_off ? 8 : 4));
         LAUNCH(k_sample_topc, (unsigned)(a.Bn * a.Lc), SM_THREADS, sizeof(float) * (size_t)a.V, sc);
-        LAUNCH(k_sample_seq, (unsigned)a.Bn, SC_MAXC, 0, sc);
+        LAUNCH(k_sample_seq, (unsigned)a.Bn, Kc, 0, sc);           // one thread per candidate
         return;
     }
     SampleDev sd;
