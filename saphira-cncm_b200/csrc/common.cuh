@@ -157,6 +157,15 @@ struct GemmArgs {
     // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
     const float *argmin_colnorm = nullptr;
     unsigned long long *argmin_best = nullptr;
+    // fused QKV projection, head dim 64 (fp16-pair engine with 128-column tiles only): the per-head RMSNorm and
+    // the rotary embedding of the query / key heads (what qk_post() does in a pass of its own) are applied in the
+    // epilogue, where a thread holds the 64 columns of one head of its row. Columns [0, qk_heads * 64) are heads
+    // (the first qk_H of them queries); qk_pos[m] selects the table row. *qk_applied tells the caller whether the
+    // engine did it (otherwise the caller runs qk_post()).
+    int qk_heads = 0, qk_H = 0;
+    const float *qk_qw = nullptr, *qk_kw = nullptr, *qk_cos = nullptr, *qk_sin = nullptr;
+    const int *qk_pos = nullptr;
+    bool *qk_applied = nullptr;
 };
 void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
 void gemm_simt(const GemmArgs &a);

@@ -31,7 +31,8 @@ constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand 
 constexpr int h3_wtile(int BN) { return BN * H3_BK * 2; }  // one BN-row weight tile
 constexpr int h3_stage(int BN) { return 2 * H3_TILE + 2 * h3_wtile(BN); }   // x1 | x2 | W1 | W2
 
-template <int H3_BN>
+// QKP: the epilogue applies the per-head RMSNorm / rotary embedding of a fused QKV projection (128-column tiles)
+template <int H3_BN, bool QKP = false>
 __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
                                                        const __grid_constant__ CUtensorMap tmX2,
                                                        const __grid_constant__ CUtensorMap tmW1,
@@ -155,6 +156,24 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
             tc_fence_after();
             if (!ok) break;
             const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN + ch * (H3_BN / 2));
+            if constexpr (QKP) {
+                // both halves of the thread's head (64 columns) before anything is stored
+                uint32_t r0[32], r1[32];
+                {
+                    uint32_t x[32];
+                    tmem_ld32_issue(trow, r0);
+                    tmem_ld32_issue(trow + (uint32_t)H3_BN, x);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r0[j])));
+                    tmem_ld32_issue(trow + 32u, r1);
+                    tmem_ld32_issue(trow + (uint32_t)(H3_BN + 32), x);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r1[j])));
+                }
+                tc_epilogue_head_qkpost(ep, r0, r1, m, m - lane, n0, stage, &tmY, lane);
+            } else
 #pragma unroll
             for (int c = 0; c < NCH1; c++) {
                 if (!has_cols) break;
@@ -230,13 +249,23 @@ bool gemm_h3_supported(const GemmArgs &a) {
     return true;
 }
 
+// The fused QKV epilogue is opt-in (NCM_B200_QK_EPILOGUE=1, read per call so that a test can switch it): it removes
+// the norm / rotation pass (2.4 -> 0.6 ms of element-wise kernels per 12-layer generate step) but the K = 512
+// projection is already paced by its fp32 epilogue, which grows by as much (25.3 -> 26.6 ms of GEMM), so the step
+// as a whole measured 0.3 ms slower with it.
+static bool qk_epilogue_on() {
+    const char *e = getenv("NCM_B200_QK_EPILOGUE");
+    return e && e[0] == '1';
+}
+
 void gemm_h3(const GemmArgs &a) {
     if (a.M <= 0 || a.N <= 0) return;
-    TcEpi ep;
+    TcEpi ep{};
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
     ep.y = a.y; ep.y_lo = a.y_lo; ep.y_fmt = a.y_fmt; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
     ep.colnorm = nullptr; ep.best = nullptr;
+    ep.qk_heads = a.qk_heads; ep.qk_H = a.qk_H; ep.qk_qw = a.qk_qw; ep.qk_kw = a.qk_kw; ep.qk_cos = a.qk_cos; ep.qk_sin = a.qk_sin; ep.qk_pos = a.qk_pos;
     const int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool pre_split = a.x_lo != nullptr;
     const int64_t nx = pre_split ? 0 : a.M * a.K, nw = (int64_t)a.N * a.K;
@@ -277,11 +306,15 @@ void gemm_h3(const GemmArgs &a) {
     if (bn_env == 32 || bn_env == 64 || bn_env == 128) bn = bn_env;
     else if (narrow_ok) {
         int64_t best = -1;
+        int64_t cost128 = 0;
         for (int cand : {128, 64, 32}) {
             const int64_t waves = cdiv(cdiv(a.N, cand) * cdiv(a.M, H3_BM), ctx().sm_count);
             const int64_t cost = waves * (2 * H3_TILE + 2 * h3_wtile(cand));
+            if (cand == 128) cost128 = cost;
             if (best < 0 || cost < best) { best = cost; bn = cand; }
         }
+        // a fused QKV projection needs 128-column tiles (two heads each) and saves a whole pass over q and k
+        if (qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && a.N % 128 == 0 && cost128 <= 2 * best) bn = 128;
     }
     const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
     const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
@@ -303,7 +336,16 @@ void gemm_h3(const GemmArgs &a) {
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
         LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);        \
     } while (0)
-    if (bn == 32) H3_LAUNCH(32);
+    // fused QKV projection: heads are 64 columns, a 128-column tile holds two, results leave as fp32 tiles
+    const bool qkp = qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && bn == 128 && ep.tma_store && a.N % 128 == 0 && !a.res &&
+                     a.act == ACT_NONE && (a.qk_qw || a.qk_kw || a.qk_cos) && (!a.qk_cos || a.qk_pos);
+    if (a.qk_applied) *a.qk_applied = qkp;
+    if (qkp) {
+        constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
+        static bool set = false;
+        if (!set) { CUDA_CHECK(cudaFuncSetAttribute((k_gemm_h3<128, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
+    } else if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);
     else H3_LAUNCH(128);
 #undef H3_LAUNCH

@@ -334,7 +334,7 @@ static void launch_tc(const GemmArgs &a, const TcEpi &ep, const CUtensorMap *ma,
 
 void gemm_tc(const GemmArgs &a) {
     if (a.M <= 0 || a.N <= 0) return;
-    TcEpi ep;
+    TcEpi ep{};
     ep.bias = a.bias; ep.res = a.res; ep.ldres = a.ldres ? a.ldres : a.N;
     ep.y = a.y; ep.y_lo = a.y_lo; ep.y_fmt = a.y_fmt; ep.ldy = a.ldy ? a.ldy : (a.glu ? a.N / 2 : a.N);
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
@@ -476,7 +476,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     CUtensorMap ma, mal, mb, mbl;
     encode_map_now(&ma, xhi, batch, K, K, TC_BM, false); encode_map_now(&mal, xlo, batch, K, K, TC_BM, true);
     encode_map_now(&mb, whi, M, K, K, 128, false); encode_map_now(&mbl, wlo, M, K, K, 128, true);
-    TcEpi ep;
+    TcEpi ep{};
     ep.bias = b; ep.res = nullptr; ep.ldres = M; ep.y = y; ep.y_lo = nullptr; ep.y_fmt = SPLIT_TF32; ep.tma_store = 0; ep.ldy = M; ep.colnorm = nullptr; ep.best = nullptr; ep.M = batch; ep.N = M; ep.act = ACT_NONE; ep.glu = 0;
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);

@@ -17,6 +17,10 @@ struct TcEpi {
     const float *colnorm; unsigned long long *best;     // nearest-row mode
     int *err;
     int tma_store;                                      // fp32 result tiles leave through shared memory and TMA stores
+    // per-head RMSNorm + rotary embedding of a fused QKV projection (head dim 64), see GemmArgs
+    int qk_heads, qk_H;
+    const float *qk_qw, *qk_kw, *qk_cos, *qk_sin;
+    const int *qk_pos;
 };
 
 
@@ -165,6 +169,84 @@ __device__ __forceinline__ void tc_epilogue_chunk_tma(const TcEpi &ep, const uin
         asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                      ::"l"(tmY), "r"(n0 + c0), "r"((int)m_warp0), "r"((uint32_t)__cvta_generic_to_shared(stage)) : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+
+// One head (64 columns starting at n0) of row m of a fused QKV projection: bias, then for query / key heads the
+// per-head RMSNorm (x * rsqrt(mean x^2 + 1e-6) * w, the products rounded one by one) and the rotation of the pairs
+// (d, d + 32) with the table row of the token's position -- the arithmetic of qk_post(), on values that are still
+// in registers. r0 / r1 hold columns [0, 32) / [32, 64) of the head. Both halves then leave through the warp's
+// staging buffer and two TMA stores.
+__device__ __forceinline__ void tc_epilogue_head_qkpost(const TcEpi &ep, uint32_t *r0, uint32_t *r1, int64_t m, int64_t m_warp0,
+                                                       int n0, unsigned char *stage, const CUtensorMap *tmY, int lane) {
+    const int head = n0 >> 6;
+    if (ep.bias) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const float4 b0 = *(const float4 *)(ep.bias + n0 + j), b1 = *(const float4 *)(ep.bias + n0 + 32 + j);
+            r0[j] = __float_as_uint(__uint_as_float(r0[j]) + b0.x); r0[j + 1] = __float_as_uint(__uint_as_float(r0[j + 1]) + b0.y);
+            r0[j + 2] = __float_as_uint(__uint_as_float(r0[j + 2]) + b0.z); r0[j + 3] = __float_as_uint(__uint_as_float(r0[j + 3]) + b0.w);
+            r1[j] = __float_as_uint(__uint_as_float(r1[j]) + b1.x); r1[j + 1] = __float_as_uint(__uint_as_float(r1[j + 1]) + b1.y);
+            r1[j + 2] = __float_as_uint(__uint_as_float(r1[j + 2]) + b1.z); r1[j + 3] = __float_as_uint(__uint_as_float(r1[j + 3]) + b1.w);
+        }
+    }
+    if (head < ep.qk_heads && m < ep.M) {
+        const float *nw = head < ep.qk_H ? ep.qk_qw : ep.qk_kw;
+        if (nw) {
+            float s[32];                                   // pair sums, added up in the order of a 32-lane butterfly
+#pragma unroll
+            for (int i = 0; i < 32; i++) { const float a = __uint_as_float(r0[i]), b = __uint_as_float(r1[i]); s[i] = a * a + b * b; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int i = 0; i < o; i++) s[i] += s[i + o];
+            const float rinv = 1.0f / sqrtf(s[0] / 64.0f + 1e-6f);
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 w0 = *(const float4 *)(nw + j), w1 = *(const float4 *)(nw + 32 + j);
+                r0[j] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r0[j]), rinv), w0.x));
+                r0[j + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r0[j + 1]), rinv), w0.y));
+                r0[j + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r0[j + 2]), rinv), w0.z));
+                r0[j + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r0[j + 3]), rinv), w0.w));
+                r1[j] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r1[j]), rinv), w1.x));
+                r1[j + 1] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r1[j + 1]), rinv), w1.y));
+                r1[j + 2] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r1[j + 2]), rinv), w1.z));
+                r1[j + 3] = __float_as_uint(__fmul_rn(__fmul_rn(__uint_as_float(r1[j + 3]), rinv), w1.w));
+            }
+        }
+        if (ep.qk_cos) {
+            const float *cs = ep.qk_cos + (int64_t)ep.qk_pos[m] * 64, *sn = ep.qk_sin + (int64_t)ep.qk_pos[m] * 64;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 c0 = *(const float4 *)(cs + j), c1 = *(const float4 *)(cs + 32 + j);
+                const float4 s0 = *(const float4 *)(sn + j), s1 = *(const float4 *)(sn + 32 + j);
+                const float cc0[4] = {c0.x, c0.y, c0.z, c0.w}, cc1[4] = {c1.x, c1.y, c1.z, c1.w};
+                const float ss0[4] = {s0.x, s0.y, s0.z, s0.w}, ss1[4] = {s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float x0 = __uint_as_float(r0[j + e]), x1 = __uint_as_float(r1[j + e]);
+                    r0[j + e] = __float_as_uint(__fadd_rn(__fmul_rn(x0, cc0[e]), __fmul_rn(-x1, ss0[e])));
+                    r1[j + e] = __float_as_uint(__fadd_rn(__fmul_rn(x1, cc1[e]), __fmul_rn(x0, ss1[e])));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        const uint32_t *r = half ? r1 : r0;
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous store has read the buffer
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+            *(float4 *)(stage + lane * 128 + ((((j >> 2) ^ (lane & 7)) & 7) << 4)) =
+                make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                         ::"l"(tmY), "r"(n0 + half * 32), "r"((int)m_warp0), "r"((uint32_t)__cvta_generic_to_shared(stage)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
     }
 }
 

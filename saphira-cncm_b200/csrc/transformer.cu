@@ -115,9 +115,15 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         g.x_fmt = fmt;
         g.x = b.ln; g.x_lo = ln_lo;
     }
+    // head dim 64: the GEMM's epilogue can apply the per-head norm and the rotation itself (it says whether it did)
+    bool qk_done = false;
+    if (hd == 64 && !small && !p.step_d && (w.qnw || w.knw || p.cos_t)) {
+        g.qk_heads = H + nkv; g.qk_H = H; g.qk_qw = w.qnw; g.qk_kw = w.knw; g.qk_cos = p.cos_t; g.qk_sin = p.sin_t; g.qk_pos = p.pos;
+        g.qk_applied = &qk_done;
+    }
     gemm(g);
     float *qp = b.qkv, *kp = b.qkv + C, *vp = b.qkv + C + kvd;
-    qk_post(qp, Wq, H, kp, Wq, nkv, hd, ntok, w.qnw, w.knw, p.cos_t, p.sin_t, p.pos, p.step_d, p.pos_step);
+    if (!qk_done) qk_post(qp, Wq, H, kp, Wq, nkv, hd, ntok, w.qnw, w.knw, p.cos_t, p.sin_t, p.pos, p.step_d, p.pos_step);
     if (p.kv_store && !kv_written) {
         int width4 = 2 * kvd / 4;
         int64_t n = ntok * width4;

@@ -189,6 +189,35 @@ def test_c2_shape_reduced_depth_sampled_codes(cuda, tmp):
     _cmp_float("c2 logits", lg_g, lg_o, ATOL_LOGITS)
 
 
+def test_qkv_projection_with_norm_and_rotation_in_its_epilogue(cuda, tmp):
+    """Opt-in path: the per-head RMSNorm and the rotary embedding applied by the QKV GEMM's epilogue (head dim 64)
+    instead of a pass of their own. Same codes as the oracle, logits within the usual bound."""
+    import capi
+    import orc
+    import synth
+    spec = synth.spec_c2(n_layer=2, name="c2_l2_qkepi")
+    conf, w = synth.write_ncp(spec, tmp)
+    pre = synth.ncp_prefixes(spec, 3, 11)
+    kw = _gen_kwargs(spec)
+    cap = sum(l * v for l, v in zip(spec.levels, spec.vocab))
+    want, lg_o = orc.Model(conf, w).generate(pre, seed=5, cap_floats=cap, **kw)
+    gm = capi.NcpModel(cuda, conf, w, arena_mb=64)
+    gm.generate_ex(pre, cap, seed=5, **kw)           # the first call also prepares the weights' fp16 pairs
+    os.environ["NCM_B200_QK_EPILOGUE"] = "1"
+    try:
+        n0 = cuda.ncmb_launch_count()
+        got, lg_g = gm.generate_ex(pre, cap, seed=5, **kw)
+        fused = cuda.ncmb_launch_count() - n0
+    finally:
+        os.environ.pop("NCM_B200_QK_EPILOGUE", None)
+    n0 = cuda.ncmb_launch_count()
+    got2, _ = gm.generate_ex(pre, cap, seed=5, **kw)
+    plain = cuda.ncmb_launch_count() - n0
+    assert fused < plain                       # the separate norm / rotation launches are gone
+    assert np.array_equal(got, want) and np.array_equal(got2, want)
+    _cmp_float("logits, fused QKV epilogue", lg_g, lg_o, ATOL_LOGITS)
+
+
 def test_stepper_equals_monolithic_and_is_deterministic(cuda, tmp):
     import ctypes as C
     import capi
