@@ -143,9 +143,22 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
             // so its latency runs under the tile's MMAs
             float4 resv[8 * NCH1];
             bool pre[NCH1];
+            // fp32 tiles that leave by TMA store: the warp fetches the residual block together, full row segments per
+            // request (see tc_epilogue_chunk_tma_coop); otherwise every thread fetches its own row
+            const bool coop = ep.tma_store && ep.res && has_cols && ((ep.ldres & 3) == 0) && (((uintptr_t)ep.res & 15) == 0);
 #pragma unroll
             for (int c = 0; c < NCH1; c++) {
-                pre[c] = has_cols && tc_residual_prefetchable(ep, m, n0, c * 32);
+                if (coop && n0 + c * 32 + 32 <= ep.N) {
+                    pre[c] = true;
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {
+                        const int64_t row = (m - lane) + i * 4 + (lane >> 3);
+                        resv[c * 8 + i] = row < ep.M ? *(const float4 *)(ep.res + row * ep.ldres + n0 + c * 32 + (lane & 7) * 4)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                    continue;
+                }
+                pre[c] = !coop && has_cols && tc_residual_prefetchable(ep, m, n0, c * 32);
                 if (pre[c]) {
                     const float4 *rr = (const float4 *)(ep.res + m * ep.ldres + n0 + c * 32);
 #pragma unroll
@@ -185,6 +198,8 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 for (int j = 0; j < 32; j++)
                     r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
                 if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
+                else if (coop && n0 + c * 32 + 32 <= ep.N)
+                    tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, &resv[c * 8], stage, &tmY, lane);
                 else if (ep.tma_store && n0 + c * 32 + 32 <= ep.N)
                     tc_epilogue_chunk_tma(ep, r, m, m - lane, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr, stage, &tmY, lane);
                 else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr);

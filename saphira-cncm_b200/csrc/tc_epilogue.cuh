@@ -172,6 +172,43 @@ __device__ __forceinline__ void tc_epilogue_chunk_tma(const TcEpi &ep, const uin
     }
 }
 
+// fp32 tile out through staging + TMA store, with the residual arriving the coalesced way: the warp fetched the
+// chunk's 32 x 32 residual block together (lane L, step i: row 4 i + L / 8, four columns at 4 (L % 8): full 128-byte
+// row segments per request, where a thread reading its own row touches 32 separate sectors per request) and holds it
+// in `coop`; here the block goes through the swizzled staging buffer, each thread adds its row to its accumulators in
+// place, and the buffer leaves by TMA store.
+__device__ __forceinline__ void tc_epilogue_chunk_tma_coop(const TcEpi &ep, const uint32_t *r, int64_t m_warp0, int n0, int c0,
+                                                           const float4 *coop, unsigned char *stage, const CUtensorMap *tmY, int lane) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");    // the previous store has read the buffer
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int row = i * 4 + (lane >> 3), c4 = lane & 7;
+        *(float4 *)(stage + row * 128 + (((c4 ^ (row & 7)) & 7) << 4)) = coop[i];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        if (ep.bias) {
+            float4 b = *(const float4 *)(ep.bias + n0 + c0 + j);
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+        }
+        if (ep.act != ACT_NONE) { v.x = tc_act(v.x, ep.act); v.y = tc_act(v.y, ep.act); v.z = tc_act(v.z, ep.act); v.w = tc_act(v.w, ep.act); }
+        float4 *slot = (float4 *)(stage + lane * 128 + ((((j >> 2) ^ (lane & 7)) & 7) << 4));
+        const float4 q4 = *slot;
+        v.x += q4.x; v.y += q4.y; v.z += q4.z; v.w += q4.w;
+        *slot = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+                     ::"l"(tmY), "r"(n0 + c0), "r"((int)m_warp0), "r"((uint32_t)__cvta_generic_to_shared(stage)) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+
 // One head (64 columns starting at n0) of row m of a fused QKV projection: bias, then for query / key heads the
 // per-head RMSNorm (x * rsqrt(mean x^2 + 1e-6) * w, the products rounded one by one) and the rotation of the pairs
 // (d, d + 32) with the table row of the token's position -- the arithmetic of qk_post(), on values that are still
