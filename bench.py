@@ -94,10 +94,14 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=self._read, daemon=True)
             self.th.start()
+            t0 = time.time()                      # the tool needs a moment to start: wait for its first line, so that
+            while not self.rows and time.time() - t0 < 3.0:      # the samples that follow fall inside the region
+                time.sleep(0.01)
+            self.rows.clear()
         except OSError:
             self.proc = None
         return self
