@@ -37,6 +37,7 @@ struct NCPState {
     VQVAEState *vqvae = nullptr;
     VQState *vq = nullptr;
     int L = 0, T = 0, P = 0, lvl_first = 0, n_tgt = 0;
+    int one_pass_rows = 0; size_t one_pass_cap = 0;       // largest model batch that ran in one pass, on a workspace of this size
     int C = 0, H = 0, nkv = 0, hd = 0, D = 0, Hh = 0, NL = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     std::vector<float *> gcos, gsin;
@@ -710,18 +711,26 @@ int *ncmb_ncp_generate_ex(NCPState *m, const int *l0, const int *prefix_ids, int
     const bool use_cfg = cfg_scale > 0;
     if (use_cfg && c->prefix_pad_token_id < 0)
         fatal("classifier-free guidance needs model.prefix_pad_token_id >= 0 (the null prefix is built from it)");
+    // A batch no larger than one that already ran in a single pass on the workspace this state still holds fits
+    // again: the free-memory query (about a millisecond on this device) is skipped for it.
+    const bool known_fit = !getenv("NCM_B200_WAVE_MB") && m->one_pass_rows >= (use_cfg ? 2 * B : B) && m->work.cap >= m->one_pass_cap &&
+                           m->one_pass_cap > 0;
     size_t free_b = 0, total_b = 0;
-    CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
+    if (!known_fit) CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
     double budget = 0.6 * ((double)free_b + (double)m->work.cap);      // head room for the engines' own scratch and the caller
     if (const char *e = getenv("NCM_B200_WAVE_MB")) budget = atof(e) * 1048576.0;
     int Bw = B;
-    if (gen_bytes_bound(m, B, use_cfg, logits_host != nullptr) > budget) {
+    if (!known_fit && gen_bytes_bound(m, B, use_cfg, logits_host != nullptr) > budget) {
         int lo = 1, hi = B;                                  // largest wave that fits
         while (lo < hi) { int mid = (lo + hi + 1) / 2; if (gen_bytes_bound(m, mid, use_cfg, logits_host != nullptr) <= budget) lo = mid; else hi = mid - 1; }
         Bw = lo;
     }
     if (const char *e = getenv("NCM_B200_WAVE_ROWS")) { int v = atoi(e); if (v >= 1 && v < Bw) Bw = v; }   // testing: force waves
-    if (Bw >= B) return gen_one(m, l0, prefix_ids, B, temp, top_k, top_p, cfg_scale, freq, mu, adj_a, adj_w, adj_d, allow, seed, logits_host, nullptr);
+    if (Bw >= B) {
+        int *codes = gen_one(m, l0, prefix_ids, B, temp, top_k, top_p, cfg_scale, freq, mu, adj_a, adj_w, adj_d, allow, seed, logits_host, nullptr);
+        if (!logits_host) { m->one_pass_rows = use_cfg ? 2 * B : B; m->one_pass_cap = m->work.cap; }
+        return codes;
+    }
     if (logits_host) fatal("ncp_generate_ex: logits capture needs the batch in one wave (%d rows fit, %d asked)", Bw, B);
 
     const int nlev = c->n_qlevels, P = m->P, l0len = c->levels[0];
