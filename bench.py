@@ -284,12 +284,18 @@ def run_gpu_arm(args):
         g = lib.ncp_gen_begin(model.ncp, None, prefix.data_ptr(), B, kw["temp"], kw["top_k"], kw["top_p"], kw["cfg"],
                               kw["freq"], kw["mu"], 0.0, 0, 1.0, allow_p, seed)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [e0]                                   # one event per stepper step (a level): the step latencies
         e0.record(stream)
         while lib.ncp_gen_step(g, None, None) == 0:
-            pass
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            marks.append(ev)
         lib.ncmb_decode_tokens_dev(model.vqvae, lib.ncmb_gen_codes_dev(g), B, tokens_dev.data_ptr())
         e1.record(stream)
+        level_marks.append(marks)
         return g, e0, e1
+
+    level_marks = []
 
     def step_e2e(seed):
         """host prefix ids in, host token ids out, through the public C API."""
@@ -319,6 +325,11 @@ def run_gpu_arm(args):
         barrier()
         t_wall = time.perf_counter() - t_wall0
     launches = lib.ncmb_launch_count() - n0
+    # latency of a stepper step (the prefix pass + level 0, then one refinement level each) over the timed steps
+    lvl_ms = [[a.elapsed_time(b) for a, b in zip(mk[:-1], mk[1:])] for mk in level_marks[-args.steps:]]
+    flat = sorted(x for row in lvl_ms for x in row)
+    p50_level = flat[len(flat) // 2] if flat else None
+    by_level = [float(np.median([row[i] for row in lvl_ms])) for i in range(len(lvl_ms[0]))] if lvl_ms else []
     # ---- the same steps again with the per-kernel timers on: kernel classes and the roofline's launch times ----
     lib.ncmb_prof_reset()
     lib.ncmb_prof_enable(1)
@@ -381,6 +392,8 @@ def run_gpu_arm(args):
             "data": "synthetic",
             "config": workload_config(args.workload, spec, B, world),
             "codes_per_sec": world * B * sum(spec.levels) * args.steps / dev_s,
+            # step = one call of the level stepper: the prefix pass with level 0, then one refinement level each
+            "p50_step_latency_ms": p50_level, "step_latency_ms_by_level": by_level,
             "e2e": {"value": total_tok / e2e_max, "unit": "tokens/s",
                     "h2d_bytes_per_step": (h1.value - h0.value) // args.steps,
                     "d2h_bytes_per_step": (d1.value - d0.value) // args.steps},
