@@ -142,20 +142,80 @@ __global__ void __launch_bounds__(TC_THREADS) k_gemm_tc(const __grid_constant__ 
             tc_fence_after();
             if (!ok) break;
             float bestd = INFINITY; int bestn = 0x7fffffff;
+            if (ep.best) {
+                // Nearest row. The tile has one k-block (K = 64 for the codebook search), so this loop is the kernel:
+                // the next 32 columns are on their way out of tensor memory while these are compared, the column
+                // norms come as float4, and four independent running minima (columns j mod 4) break the
+                // compare-select chain; they merge at the end by (distance, index), which keeps the first minimum.
+                const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+                float bd[4] = {INFINITY, INFINITY, INFINITY, INFINITY};
+                int bn[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+                uint32_t ra[32], rb[32];
+                tmem_ld32_issue(trow, ra);
+                tmem_ld_wait();
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
-                if (ep.best) {
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    if (c0 + 32 < BN) tmem_ld32_issue(trow + (uint32_t)(c0 + 32), rb);
+                    {
+                        const int nb = n0 + c0;
+                        if (nb + 32 <= ep.N) {
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        int n = n0 + c0 + j;
-                        if (n < ep.N) {
-                            float d = fmaf(-2.0f, __uint_as_float(r[j]), ep.colnorm[n]);
-                            if (d < bestd) { bestd = d; bestn = n; }      // ascending n: strict < keeps the first minimum
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 cn = *(const float4 *)(ep.colnorm + nb + j);
+                                const float cc[4] = {cn.x, cn.y, cn.z, cn.w};
+#pragma unroll
+                                for (int e = 0; e < 4; e++) {
+                                    const float d = fmaf(-2.0f, __uint_as_float(ra[j + e]), cc[e]);
+                                    if (d < bd[e]) { bd[e] = d; bn[e] = nb + j + e; }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int n = nb + j;
+                                if (n < ep.N) {
+                                    const float d = fmaf(-2.0f, __uint_as_float(ra[j]), ep.colnorm[n]);
+                                    if (d < bd[j & 3]) { bd[j & 3] = d; bn[j & 3] = n; }
+                                }
+                            }
                         }
                     }
-                } else {
+                    tmem_ld_wait();
+                    if (c0 + 64 < BN) tmem_ld32_issue(trow + (uint32_t)(c0 + 64), ra);
+                    if (c0 + 32 < BN) {
+                        const int nb = n0 + c0 + 32;
+                        if (nb + 32 <= ep.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 cn = *(const float4 *)(ep.colnorm + nb + j);
+                                const float cc[4] = {cn.x, cn.y, cn.z, cn.w};
+#pragma unroll
+                                for (int e = 0; e < 4; e++) {
+                                    const float d = fmaf(-2.0f, __uint_as_float(rb[j + e]), cc[e]);
+                                    if (d < bd[e]) { bd[e] = d; bn[e] = nb + j + e; }
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                const int n = nb + j;
+                                if (n < ep.N) {
+                                    const float d = fmaf(-2.0f, __uint_as_float(rb[j]), ep.colnorm[n]);
+                                    if (d < bd[j & 3]) { bd[j & 3] = d; bn[j & 3] = n; }
+                                }
+                            }
+                        }
+                    }
+                    tmem_ld_wait();
+                }
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (bd[e] < bestd || (bd[e] == bestd && bn[e] < bestn)) { bestd = bd[e]; bestn = bn[e]; }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c0), r);
                     tc_epilogue_chunk(ep, r, m, n0, c0);
                 }
             }
