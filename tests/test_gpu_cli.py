@@ -131,3 +131,15 @@ def test_decoder_lm_commands(both, kind):
         want, got = _run(CPU, args, both), _run(GPU, args, both)
         assert want[0] == 0 and got[0] == 0, (want, got)
         assert got[1].splitlines()[0] == want[1].splitlines()[0] and want[1].startswith("ids:"), (got[1], want[1])
+    # likelihood of a texts file (the configuration's character tokenizer turns the digits into ids on the host)
+    texts = os.path.join(both, f"{kind}_texts.txt")
+    with open(texts, "w") as f:
+        # documents stay inside the tiny models' 64-token context (the reference reads past its rotary table beyond it)
+        f.write("123456789|987654321\n5555|1234|99\n\n3\n" + "|".join(["918273645"] * 6) + "\n")
+    args = [f"{kind}-ppl"] + base + ["--texts", texts]
+    want, got = _run(CPU, args, both), _run(GPU, args, both)
+    assert want[0] == 0 and got[0] == 0, (want, got)
+    fw = dict(kv.split("=") for kv in want[1].split())
+    fg = dict(kv.split("=") for kv in got[1].split())
+    assert fg["docs"] == fw["docs"] and fg["tokens"] == fw["tokens"] and int(fw["tokens"]) > 50, (got[1], want[1])
+    assert abs(float(fg["nll"]) - float(fw["nll"])) < 1e-4, (got[1], want[1])
