@@ -199,6 +199,7 @@ void attention(const AttnArgs &a) {
     if (a.rows <= 0 || a.max_q <= 0) return;
     if (attention_decode_supported(a)) { attention_decode(a); return; }
     if (ctx().gemm_mode >= 1 && attention_tc_supported(a)) { attention_tc(a); return; }
+    if (ctx().gemm_mode >= 1 && attention_tc_long_supported(a)) { attention_tc_long(a); return; }
     if (a.step_d) fatal("attention: a step-indexed plan reached a kernel that does not read the step counter");
     AttnDev d;
     d.q = a.q; d.ldq = a.ldq; d.k1 = a.k1; d.v1 = a.v1; d.ldk1 = a.ldk1;

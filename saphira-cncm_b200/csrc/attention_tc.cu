@@ -48,6 +48,11 @@ struct AttnTcDev {
     int pack;        // 1: the tile holds the (<= 32) queries of all H/Hkv (<= 4) heads that share one kv head, 32 rows per head
     float scale;
     int *err;
+    // key-block mode (rows with more keys than the kernel keeps resident): this launch sees keys [kb_off, kb_off + kb_len)
+    // of segment 1 only, writes its normalised context to `out` (a per-block scratch) and, per (token, head), the
+    // block's maximum (log2 domain, scaled) and sum to ml, for k_attention_merge to combine the blocks
+    int kb_off, kb_len;
+    float *ml;
 };
 
 // byte offset of element (row, col) in a K-major tile of 32 floats per row with 128-byte swizzle
@@ -130,7 +135,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     if (qt * 128 >= nq) return;
     // one query, one key (the unconditional rows of a classifier-free-guidance batch: a one-token prefix):
     // the softmax weight is exactly 1, the context is the value row
-    if (!a.pack && nq == 1 && !a.k2_start && (a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - a.k1_start[row]) == 1) {
+    if (!a.pack && !a.ml && nq == 1 && !a.k2_start && (a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - a.k1_start[row]) == 1) {
         if (tid < 64) {
             const int kvh1 = (int)blockIdx.y / G;
             const float x = a.v1[(int64_t)a.k1_start[row] * a.ldv1 + kvh1 * 64 + tid];
@@ -145,7 +150,14 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     if (tid == 0) s_abort = *(volatile int *)a.err;
     __syncthreads();
     if (s_abort) return;
-    const int k10 = a.k1_start[row], n1 = a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - k10;
+    int k10 = a.k1_start[row], n1 = a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - k10;
+    int causal_off = a.causal_off;
+    if (a.ml) {                                    // key-block mode: the block's slice of the row's keys
+        k10 += a.kb_off; n1 -= a.kb_off; causal_off -= a.kb_off;
+        n1 = n1 < 0 ? 0 : (n1 > a.kb_len ? a.kb_len : n1);
+    }
+    // causal rows: no query of this tile sees a key past its last query's position
+    if (a.causal && !a.pack) { const int vis = qt * 128 + 128 + causal_off; n1 = n1 < vis ? n1 : (vis > 0 ? vis : 0); }
     const int k20 = a.k2_start ? a.k2_start[row] : 0, n2 = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
     const int n1p = (n1 + 31) & ~31, n2p = (n2 + 31) & ~31, nkp = n1p + n2p;
     const int nchunks = nkp >> 5;
@@ -274,7 +286,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             int lo, hi, base;                                         // key index = base + j
             if (c0 < n1p) {
                 base = c0; lo = 0; hi = n1;
-                if (a.causal) hi = min(hi, qi + a.causal_off + 1);
+                if (a.causal) hi = min(hi, qi + causal_off + 1);
             } else {
                 base = n1 + (c0 - n1p); lo = n1; hi = n1 + n2;
             }
@@ -381,6 +393,10 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         xch[tid] = l;
         team_sync();
         l = (xch[r] + xch[r + 128]) + (xch[r + 256] + xch[r + 384]);
+        if (a.ml && part == 0 && qi < nq) {
+            float *mlp = a.ml + ((int64_t)(q0 + qi) * a.H + (int)blockIdx.y) * 2;
+            mlp[0] = any ? mx * sl2 : -INFINITY; mlp[1] = l;
+        }
         // ---- output row: O / l; the four threads of a row take 16 columns each ----
         {
             const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
@@ -430,16 +446,18 @@ bool attention_tc_supported(const AttnArgs &a) {
     return true;
 }
 
-void attention_tc(const AttnArgs &a) {
+// one launch; ml != null: key-block mode over keys [kb_off, kb_off + kb_len) into the scratch `out`
+static void attention_tc_launch(const AttnArgs &a, float *out, float *out_lo, int64_t ldo, int kb_off, int kb_len, float *ml) {
     AttnTcDev d;
-    d.out = a.out; d.out_lo = a.out_lo; d.ldo = a.ldo; d.out_fmt = a.out_fmt;
+    d.out = out; d.out_lo = out_lo; d.ldo = ldo; d.out_fmt = a.out_fmt;
     d.q_start = a.q_start; d.k1_start = a.k1_start; d.k2_start = a.k2 ? a.k2_start : nullptr; d.k1_len = a.k1_len;
     d.v1 = a.v1; d.ldv1 = a.ldk1;
     d.H = a.H; d.Hkv = a.Hkv; d.causal = a.causal; d.causal_off = a.causal_off; d.window = a.window;
     d.scale = 1.0f / sqrtf(64.0f);
     d.err = tc_err_flag();
+    d.kb_off = kb_off; d.kb_len = kb_len; d.ml = ml;
     const int G = a.H / a.Hkv;
-    d.pack = (a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
+    d.pack = (!ml && a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
     const CUtensorMap *mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);
     const CUtensorMap *mk1 = tc_get_map(a.k1, a.k1_total, 2 * a.Hkv * 64, a.ldk1, 32, false);
     const CUtensorMap *mk2 = a.k2 ? tc_get_map(a.k2, a.k2_total, 2 * a.Hkv * 64, a.ldk2, 32, false) : mk1;
@@ -449,8 +467,77 @@ void attention_tc(const AttnArgs &a) {
         set = true;
     }
     dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
-    ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
     LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, *mq, *mk1, *mk2, d);
+}
+
+void attention_tc(const AttnArgs &a) {
+    ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+    attention_tc_launch(a, a.out, a.out_lo, a.ldo, 0, 0, nullptr);
+}
+
+// ---- rows with more keys than one launch keeps resident: key blocks + merge ----
+constexpr int ATC_KBLOCK = 256;
+
+// out[token][h][d] = sum_b w_b ctx_b / sum_b w_b with w_b = 2^(m_b - M) l_b, the usual log-sum-exp merge of blocks
+// whose contexts arrive normalised by their own sums
+__global__ void k_attention_merge(const float *__restrict__ part, const float *__restrict__ ml, int nblk, int64_t ntok, int H,
+                                  float *__restrict__ out, float *__restrict__ out_lo, int64_t ldo, int fmt) {
+    const int64_t n4 = ntok * H * 16;                                   // float4 elements of the output
+    const int64_t bstride = ntok * H * 64, mstride = ntok * H * 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t th = i >> 4;                                     // token * H + head
+        const int d4 = (int)(i & 15);
+        float M = -INFINITY;
+        for (int b = 0; b < nblk; b++) M = fmaxf(M, ml[b * mstride + th * 2]);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float L = 0.f;
+        for (int b = 0; b < nblk; b++) {
+            const float m = ml[b * mstride + th * 2], l = ml[b * mstride + th * 2 + 1];
+            if (!(l > 0.f)) continue;
+            const float w = exp2f(m - M) * l;
+            const float4 c = *(const float4 *)(part + b * bstride + th * 64 + d4 * 4);
+            acc.x = fmaf(w, c.x, acc.x); acc.y = fmaf(w, c.y, acc.y); acc.z = fmaf(w, c.z, acc.z); acc.w = fmaf(w, c.w, acc.w);
+            L += w;
+        }
+        const float inv = L > 0.f ? 1.0f / L : 0.f;
+        const float4 o = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+        const int64_t tok = th / H; const int h = (int)(th % H);
+        const int64_t at = tok * ldo + h * 64 + d4 * 4;
+        if (out_lo) store_split4(out, out_lo, at, o, fmt);
+        else *(float4 *)(out + at) = o;
+    }
+}
+
+static size_t atc_long_scratch_floats(const AttnArgs &a, int nblk) { return (size_t)nblk * a.q_total * a.H * 66; }
+
+bool attention_tc_long_supported(const AttnArgs &a) {
+    static const bool off = getenv("NCM_B200_ATTN_SIMT") != nullptr || getenv("NCM_B200_NO_ATTN_BLOCKS") != nullptr;
+    if (off || a.hd != 64 || a.Hkv <= 0 || a.H % a.Hkv || a.k2 || a.window > 0 || a.max_q < 64) return false;
+    if (a.max_k1 <= ATC_MAXK || a.max_k1 > 16 * ATC_KBLOCK) return false;
+    if (a.q_total <= 0 || a.k1_total <= 0) return false;
+    if ((a.ldq | a.ldk1 | a.ldo) & 3) return false;
+    if (a.v1 != a.k1 + a.Hkv * 64) return false;
+    auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
+    if (!al(a.q) || !al(a.k1) || !al(a.out) || (a.out_lo && !al(a.out_lo))) return false;
+    return atc_long_scratch_floats(a, (int)cdiv(a.max_k1, ATC_KBLOCK)) * 4 <= ((size_t)2 << 30);      // at most 2 GB of block contexts
+}
+
+void attention_tc_long(const AttnArgs &a) {
+    static float *scr = nullptr; static size_t scr_cap = 0;
+    const int nblk = (int)cdiv(a.max_k1, ATC_KBLOCK);
+    const size_t need = atc_long_scratch_floats(a, nblk);
+    if (need > scr_cap) {
+        if (scr) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(scr); }
+        scr = (float *)dev_alloc(need * 4); scr_cap = need;
+    }
+    float *part = scr, *ml = scr + (size_t)nblk * a.q_total * a.H * 64;
+    ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+    for (int b = 0; b < nblk; b++)
+        attention_tc_launch(a, part + (size_t)b * a.q_total * a.H * 64, nullptr, (int64_t)a.H * 64, b * ATC_KBLOCK, ATC_KBLOCK,
+                            ml + (size_t)b * a.q_total * a.H * 2);
+    const int64_t n4 = a.q_total * a.H * 16, g = cdiv(n4, 256), cap = (int64_t)ctx().sm_count * 32;
+    LAUNCH(k_attention_merge, (unsigned)(g > cap ? cap : g), 256, 0, (const float *)part, (const float *)ml, nblk, (int64_t)a.q_total, a.H,
+           a.out, a.out_lo, (int64_t)a.ldo, a.out_fmt);
 }
 
 } // namespace ncmb
@@ -486,8 +573,9 @@ extern "C" int ncmb_attention_check(const float *q, const float *kv1, const floa
     if (engine == 1) {
         int saved_max_q = a.max_q;
         a.max_q = std::max(a.max_q, 64);               // the size threshold is a dispatch heuristic, not a limit
-        if (!attention_tc_supported(a)) rc = -1;
-        else { a.max_q = saved_max_q; attention_tc(a); rc = gemm_tc_check(); }
+        if (attention_tc_supported(a)) { a.max_q = saved_max_q; attention_tc(a); rc = gemm_tc_check(); }
+        else if (attention_tc_long_supported(a)) { attention_tc_long(a); rc = gemm_tc_check(); }
+        else rc = -1;
     } else if (engine == 2) {
         if (!attention_decode_supported(a)) rc = -1;
         else attention_decode(a);

@@ -238,6 +238,8 @@ bool attention_decode_supported(const AttnArgs &a);   // attention_decode.cu: on
 void attention_decode(const AttnArgs &a);
 bool attention_tc_supported(const AttnArgs &a);  // attention_tc.cu: head dim 64, <= 288 padded keys per row
 void attention_tc(const AttnArgs &a);
+bool attention_tc_long_supported(const AttnArgs &a);   // more keys: 256-key blocks through the same kernel + a merge
+void attention_tc_long(const AttnArgs &a);
 // reference-layout SDPA with an additive [Tq][Tkv] mask (ncm.h API)
 void sdpa_masked(const float *q, const float *k, const float *v, const float *mask, float *out,
                  int B, int Hq, int Hkv, int Tq, int Tkv, int hd);

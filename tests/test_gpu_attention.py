@@ -58,6 +58,9 @@ CASES = {
     "level_pass_packed_g2": ([16, 5], [40, 100], [16, 5], 4, 2, 0, 0),
     "packed_one_segment_all_288_keys": ([8, 32], [288, 129], None, 4, 1, 0, 0),
     "windowed": ([150], [150], None, 2, 2, 0, 16),
+    # rows with more keys than one launch keeps resident: 256-key blocks through the same kernel, then a merge
+    "long_causal_prefill_blocks": ([512, 300, 700, 64], [512, 300, 700, 64], None, 4, 2, 1, 0),
+    "long_bidirectional_blocks": ([130, 64], [1000, 289], None, 2, 1, 0, 0),
 }
 
 
@@ -143,10 +146,11 @@ def test_split_key_attention_with_a_few_queries_and_two_key_segments(cuda):
 
 
 def test_shapes_outside_the_tensor_core_kernel_are_reported_not_rerouted(cuda):
-    # the kernel keeps at most 288 padded keys of a row resident
+    # a launch keeps at most 288 padded keys of a row resident, longer rows go through key blocks -- but not with a
+    # window mask, which the block form does not take
     qs = np.array([0, 64], np.int32)
     ks = np.array([0, 480], np.int32)
     q = cuda.alloc(64 * 64)
     kv = cuda.alloc(480 * 128)
     out = cuda.alloc(64 * 64)
-    assert cuda.ncmb_attention_check(q, kv, None, out, qs.ctypes.data, ks.ctypes.data, None, 1, 1, 1, 0, 0, 1) == -1
+    assert cuda.ncmb_attention_check(q, kv, None, out, qs.ctypes.data, ks.ctypes.data, None, 1, 1, 1, 0, 16, 1) == -1
