@@ -403,6 +403,28 @@ PPL_SPECS = {
 }
 
 
+@pytest.mark.parametrize("B", [2, 11])
+def test_nucleus_sampling_over_a_vocabulary_too_large_for_the_block_sampler(cuda, tmp, B):
+    """top_k = 0 over 2500 entries (the Qwen2 setting, temp 0.7 / top-p 0.95, at a size the oracle finishes quickly):
+    every row's ids equal the oracle's full-sort walk."""
+    import orc
+    import synth
+    spec = synth.LMSpec("qwen_v2500", "qwen", 1, 64, 2, 1, 128, 2500, 64, rope_theta=1e6, rand_affine=1)
+    conf, w = synth.write_lm(spec, tmp)
+    cfg = cuda.load_config(conf)
+    m = cuda.ncmb_lm_open(cfg, w.encode(), 1, 0)
+    om = orc.LM(conf, w, True)
+    P = np.ascontiguousarray(synth.lm_prompts(spec, B, 7, 21))
+    n_new = 10
+    for (t, tp, sd) in ((0.7, 0.95, 9), (1.3, 0.5, 4)):
+        out = np.zeros((B, n_new), np.int32)
+        cuda.ncmb_lm_generate(m, P.ctypes.data, B, P.shape[1], n_new, t, 0, tp, sd, -1, out.ctypes.data)
+        for b in range(B):
+            want = om.generate(P[b], n_new, temp=t, top_k=0, top_p=tp, seed=sd)
+            assert (out[b] == want).all(), (B, t, tp, b, out[b], want)
+    cuda.ncmb_lm_close(m)
+
+
 @pytest.mark.parametrize("kind", sorted(PPL_SPECS))
 def test_decoder_lm_likelihood_and_fixture_commands(cuda, tmp, kind, capfd):
     """ncmb_lm_nll, *_cmd_ppl and *_cmd_verify against the oracle's window likelihood (reference gpt2_nll / qwen_nll)."""
