@@ -537,6 +537,16 @@ __global__ void k_sort_prep(const float *__restrict__ logits, float temp, int64_
     }
 }
 
+// all rows in ONE device-wide sort: key = row << 32 | (0xffffffff - ordered value bits), ascending, so rows stay in
+// order and every row comes out largest value first (the sort is stable: equal values keep ascending indices)
+__global__ void k_sort_prep64(const float *__restrict__ logits, float temp, int64_t n, int V, unsigned long long *__restrict__ keys,
+                              int *__restrict__ idx) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        keys[i] = ((unsigned long long)(i / V) << 32) | (unsigned long long)(0xffffffffu - okey(logits[i] / temp));
+        idx[i] = (int)(i % V);
+    }
+}
+
 __device__ __forceinline__ double block_excl_scan(double v, double *sm, double *total) {
     // exclusive scan of one value per thread over SL_THREADS threads
     int tid = threadIdx.x;
@@ -554,20 +564,27 @@ __device__ __forceinline__ double block_excl_scan(double v, double *sm, double *
     return incl - v;
 }
 
-__global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const float *__restrict__ keys, const int *__restrict__ idx, int V, int keep,
+// K64: keys are the composite 64-bit keys of k_sort_prep64 (the value is recovered from the low word)
+template <bool K64>
+__global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restrict__ keys, const int *__restrict__ idx, int V, int keep,
                                                            float top_p, const double *__restrict__ uniforms,
                                                            unsigned long long seed, long long row0, int level,
                                                            int *__restrict__ out, int out_stride, int out_off) {
     __shared__ double sm[SL_THREADS];
     __shared__ int s_min;
     const int b = blockIdx.x, tid = threadIdx.x;
-    const float *kr = keys + (size_t)b * V;
+    const float *kf = (const float *)keys + (size_t)b * V;
+    const unsigned long long *k8 = (const unsigned long long *)keys + (size_t)b * V;
+    auto val = [&](int r) -> double {
+        if (K64) return (double)okey_inv(0xffffffffu - (unsigned)(k8[r] & 0xffffffffull));
+        return (double)kf[r];
+    };
     const int *ir = idx + (size_t)b * V;
-    const double mx = (double)kr[0];
+    const double mx = val(0);
     const int chunk = (keep + SL_THREADS - 1) / SL_THREADS;
     const int r0 = tid * chunk, r1 = min(r0 + chunk, keep);
     double local = 0;
-    for (int r = r0; r < r1; r++) local += exp((double)kr[r] - mx);
+    for (int r = r0; r < r1; r++) local += exp(val(r) - mx);
     double den;
     const double base = block_excl_scan(local, sm, &den);
     // nucleus cut: first rank with (cum_before - p) / den > top_p
@@ -576,7 +593,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const float *__restr
     {
         double cum = base;
         for (int r = r0; r < r1; r++) {
-            double p = exp((double)kr[r] - mx);
+            double p = exp(val(r) - mx);
             if ((cum - p) / den > (double)top_p) { atomicMin(&s_min, r); break; }
             cum += p;
         }
@@ -586,7 +603,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const float *__restr
     __syncthreads();
     // mass of the kept prefix
     double lk = 0;
-    for (int r = r0; r < r1 && r < nkeep; r++) lk += exp((double)kr[r] - mx);
+    for (int r = r0; r < r1 && r < nkeep; r++) lk += exp(val(r) - mx);
     double den2;
     const double base2 = block_excl_scan(lk, sm, &den2);
     const double u01 = uniforms ? uniforms[b] : counter_uniform(seed, row0 + b, level, 0);
@@ -596,7 +613,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const float *__restr
     {
         double acc = base2;
         for (int r = r0; r < r1 && r < nkeep; r++) {
-            acc += exp((double)kr[r] - mx);
+            acc += exp(val(r) - mx);
             if (u <= acc) { atomicMin(&s_min, r); break; }
         }
     }
@@ -610,52 +627,46 @@ static void sample_rows_large(const SampleArgs &a, int keep) {
               "without CFG or penalties only; set top_k <= %d", SM_MAXKEEP, a.top_k, a.V, SM_MAXKEEP);
     static Workspace ws;
     const int64_t n = (int64_t)a.Bn * a.V;
-    // Few rows: one device-wide radix sort per row (the segmented sort gives each row a single CTA, which
-    // takes ~1 ms for a 150 K vocabulary); many rows: one segmented sort over all of them.
-    const bool per_row = a.Bn <= 8;
+    // One row: a device-wide 32-bit radix sort. More rows: ONE device-wide sort of all rows on composite keys
+    // (row index above the value bits); a segmented sort gives each row a single CTA, about a millisecond for a
+    // 150 K vocabulary whatever the number of rows.
+    const bool per_row = a.Bn == 1;
+    int row_bits = 1;
+    while ((1 << row_bits) < a.Bn) row_bits++;
     size_t temp_bytes = 0;
     if (per_row)
         cub::DeviceRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
                                                   (const int *)nullptr, (int *)nullptr, a.V, 0, 32, stream());
     else
-        cub::DeviceSegmentedRadixSort::SortPairsDescending(nullptr, temp_bytes, (const float *)nullptr, (float *)nullptr,
-                                                           (const int *)nullptr, (int *)nullptr, n, a.Bn, (const int *)nullptr,
-                                                           (const int *)nullptr, 0, 32, stream());
-    size_t need = (size_t)n * 16 + (size_t)(a.Bn + 1) * 4 + temp_bytes + 4096;
+        cub::DeviceRadixSort::SortPairs(nullptr, temp_bytes, (const unsigned long long *)nullptr, (unsigned long long *)nullptr,
+                                        (const int *)nullptr, (int *)nullptr, n, 0, 32 + row_bits, stream());
+    size_t need = (size_t)n * 24 + temp_bytes + 4096;
     if (need > ws.cap) ws.reserve(need);
     ws.reset();
-    float *k_in = ws.get<float>(n), *k_out = ws.get<float>(n);
-    int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
-    int *offs = ws.get<int>(a.Bn + 1);
-    void *temp = ws.alloc(temp_bytes);
-    // segment offsets b * V: uploaded only when the shape or the buffer changes, so a decode step that
-    // repeats the call (possibly inside a stream capture) issues no host copy
-    static std::vector<int> hoffs;
-    static int last_Bn = -1, last_V = -1; static const int *last_offs = nullptr;
-    if (!per_row && (last_Bn != a.Bn || last_V != a.V || last_offs != offs)) {
-        hoffs.resize(a.Bn + 1);
-        for (int b = 0; b <= a.Bn; b++) hoffs[b] = b * a.V;
-        upload(offs, hoffs.data(), hoffs.size() * 4);
-        CUDA_CHECK(cudaStreamSynchronize(stream()));
-        last_Bn = a.Bn; last_V = a.V; last_offs = offs;
-    }
     ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
     int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
-    LAUNCH(k_sort_prep, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
     cudaError_t e = cudaSuccess;
     if (per_row) {
-        for (int b = 0; b < a.Bn && e == cudaSuccess; b++)
-            e = cub::DeviceRadixSort::SortPairsDescending(temp, temp_bytes, k_in + (size_t)b * a.V, k_out + (size_t)b * a.V,
-                                                          i_in + (size_t)b * a.V, i_out + (size_t)b * a.V, a.V, 0, 32, stream());
-        ctx().launches += 7 * a.Bn;
+        float *k_in = ws.get<float>(n), *k_out = ws.get<float>(n);
+        int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
+        void *temp = ws.alloc(temp_bytes);
+        LAUNCH(k_sort_prep, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
+        e = cub::DeviceRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, a.V, 0, 32, stream());
+        ctx().launches += 7;
+        if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
+        LAUNCH(k_pick_sorted<false>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
+               a.rng_row0, a.rng_level, a.out, a.out_stride, a.out_off);
     } else {
-        e = cub::DeviceSegmentedRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, n, a.Bn,
-                                                               offs, offs + 1, 0, 32, stream());
-        ctx().launches += 4;
+        unsigned long long *k_in = ws.get<unsigned long long>(n), *k_out = ws.get<unsigned long long>(n);
+        int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
+        void *temp = ws.alloc(temp_bytes);
+        LAUNCH(k_sort_prep64, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
+        e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, k_in, k_out, i_in, i_out, n, 0, 32 + row_bits, stream());
+        ctx().launches += 2 * ((32 + row_bits + 7) / 8) + 1;
+        if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
+        LAUNCH(k_pick_sorted<true>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
+               a.rng_row0, a.rng_level, a.out, a.out_stride, a.out_off);
     }
-    if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
-    LAUNCH(k_pick_sorted, (unsigned)a.Bn, SL_THREADS, 0, k_out, i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed, a.rng_row0,
-           a.rng_level, a.out, a.out_stride, a.out_off);
 }
 
 void sample_rows(const SampleArgs &a) {
