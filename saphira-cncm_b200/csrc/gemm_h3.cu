@@ -17,6 +17,7 @@
 #include "tc_common.cuh"
 #include "tc_epilogue.cuh"
 
+#include <algorithm>
 #include <unordered_map>
 
 namespace ncmb {
@@ -38,7 +39,10 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                                                        const __grid_constant__ CUtensorMap tmW1,
                                                        const __grid_constant__ CUtensorMap tmW2,
                                                        const __grid_constant__ CUtensorMap tmY,
-                                                       TcEpi ep, int num_kb, int tiles_n, int num_tiles) {
+                                                       TcEpi ep, int num_kb, int tiles_n, int num_tiles, int ksplit, int kb_per,
+                                                       int m_pad) {
+    // ksplit > 1: a work item is (output tile, slice of K); the item's raw sums go to slice s of a partial buffer whose
+    // slices are m_pad rows apart (the tensor map of the stores covers all slices), and a second kernel adds the slices
     pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
     pdl_wait();
     constexpr int H3_STAGES = h3_stages(H3_BN), H3_STAGE = h3_stage(H3_BN), H3_WTILE = h3_wtile(H3_BN);
@@ -74,9 +78,11 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         if (lane == 0) {
             int kbg = 0, armed = 0;                       // k-block counter over all of this CTA's tiles
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int w = blockIdx.x; w < num_tiles * ksplit && ok; w += gridDim.x) {
+                const int t = w / ksplit, ks = w - t * ksplit;
                 const int n0 = (t % tiles_n) * H3_BN, m0 = (t / tiles_n) * H3_BM;
-                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                const int kb1 = min(num_kb, (ks + 1) * kb_per);
+                for (int kb = ks * kb_per; kb < kb1; kb++, kbg++) {
                     int s = kbg % H3_STAGES; uint32_t ph = (uint32_t)(kbg / H3_STAGES) & 1u;
                     ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 21);
                     if (!ok) break;
@@ -99,13 +105,14 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
             constexpr uint32_t idesc = umma_idesc_f16(H3_BM, H3_BN);
             int kbg = 0, it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+            for (int w = blockIdx.x; w < num_tiles * ksplit && ok; w += gridDim.x, it++) {
                 const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
                 ok = mbar_wait(aempty0 + 8 * acc, (use & 1u) ^ 1u, ep.err, 25);    // epilogue has drained this accumulator pair
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t tmain = tmem_base + (uint32_t)(acc * 2 * H3_BN), tcross = tmain + (uint32_t)H3_BN;
-                for (int kb = 0; kb < num_kb; kb++, kbg++) {
+                const int nkb = min(num_kb, (w % ksplit + 1) * kb_per) - (w % ksplit) * kb_per;
+                for (int kb = 0; kb < nkb; kb++, kbg++) {
                     int s = kbg % H3_STAGES; uint32_t ph = (uint32_t)(kbg / H3_STAGES) & 1u;
                     ok = mbar_wait(full0 + 8 * s, ph, ep.err, 22);
                     if (!ok) break;
@@ -135,7 +142,9 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         bool ok = true;
         const bool glu_fast = tc_glu_silu_h16(ep);
         unsigned char *stage = stage0 + (warp - 2) * 4096;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, it++) {
+        for (int w = blockIdx.x; w < num_tiles * ksplit && ok; w += gridDim.x, it++) {
+            const int t = w / ksplit;
+            const int64_t slice_row0 = (int64_t)(w - t * ksplit) * m_pad;          // row offset of this K slice's partial sums
             const int acc = it & 1; const uint32_t use = (uint32_t)(it >> 1);
             const int n0 = (t % tiles_n) * H3_BN + ch * (H3_BN / 2);
             const int64_t m = (int64_t)(t / tiles_n) * H3_BM + q * 32 + lane;
@@ -201,7 +210,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 else if (coop && n0 + c * 32 + 32 <= ep.N)
                     tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, &resv[c * 8], stage, &tmY, lane);
                 else if (ep.tma_store && n0 + c * 32 + 32 <= ep.N)
-                    tc_epilogue_chunk_tma(ep, r, m, m - lane, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr, stage, &tmY, lane);
+                    tc_epilogue_chunk_tma(ep, r, m, m - lane + slice_row0, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr, stage, &tmY, lane);
                 else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr);
             }
             tc_fence_before();
@@ -262,6 +271,26 @@ bool gemm_h3_supported(const GemmArgs &a) {
     if (a.glu && ((a.N & 1) || (ldy & 1))) return false;
     if (a.y_lo && a.y_fmt == SPLIT_H16 && (ldy & 7)) return false;
     return true;
+}
+
+// y = act(sum_s part[s] + bias) + res, the slices added in order (N a multiple of 4, rows 16-byte aligned)
+__global__ void k_splitk_reduce(const float *__restrict__ part, int ksplit, int64_t m_pad, int64_t M, int N, const float *__restrict__ bias,
+                                int act, const float *__restrict__ res, int64_t ldres, float *__restrict__ y, int64_t ldy) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n4 = N / 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / n4; const int c = (int)(i % n4) * 4;
+        float4 v = *(const float4 *)(part + m * N + c);
+        for (int s = 1; s < ksplit; s++) {
+            const float4 p = *(const float4 *)(part + ((int64_t)s * m_pad + m) * N + c);
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        if (bias) { const float4 b = *(const float4 *)(bias + c); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+        if (act != ACT_NONE) { v.x = tc_act(v.x, act); v.y = tc_act(v.y, act); v.z = tc_act(v.z, act); v.w = tc_act(v.w, act); }
+        if (res) { const float4 r = *(const float4 *)(res + m * ldres + c); v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w; }
+        *(float4 *)(y + m * ldy + c) = v;
+    }
 }
 
 // The fused QKV epilogue is opt-in (NCM_B200_QK_EPILOGUE=1, read per call so that a test can switch it): it removes
@@ -335,12 +364,41 @@ void gemm_h3(const GemmArgs &a) {
     const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
     // fp32 results leave through TMA stores when the rows keep 16-byte strides
     ep.tma_store = (!a.glu && !a.y_lo && (ep.ldy & 3) == 0 && !getenv("NCM_B200_NO_TMA_STORE")) ? 1 : 0;
-    const CUtensorMap *my = ep.tma_store ? tc_get_map(a.y, a.M, a.N, ep.ldy, 32, false) : mx1;
     int tiles_n = (int)cdiv(a.N, bn);
     int64_t tiles = (int64_t)tiles_n * cdiv(a.M, H3_BM);
     if (tiles > 0x7fffffff) fatal("gemm_h3: too many tiles");
-    int grid = (int)(tiles < ctx().sm_count ? tiles : ctx().sm_count);     // persistent: one CTA per SM
     int num_kb = (int)cdiv(a.K, H3_BK);
+    // Few tiles and a long K (batched decode steps): a CTA's serial chain of MMAs, about 53 ns each whatever their
+    // width, is what the call takes. K is cut into slices that run as work items of their own; their raw sums go
+    // to a partial buffer and k_splitk_reduce adds the slices in order and applies bias / activation / residual.
+    static const bool splitk_ok = !getenv("NCM_B200_NO_SPLITK");
+    int ksplit = 1, kb_per = num_kb, m_pad = 0;
+    float *part = nullptr;
+    auto al16 = [](const void *q) { return ((uintptr_t)q & 15) == 0; };
+    if (splitk_ok && ep.tma_store && !a.qk_applied && tiles * 2 <= ctx().sm_count && num_kb >= 24 && a.N % 32 == 0 &&
+        al16(a.bias) && al16(a.res) && (ep.ldres & 3) == 0) {
+        int want = (int)std::min<int64_t>(ctx().sm_count / tiles, num_kb / 8);
+        if (want > 16) want = 16;
+        if (want >= 2) {
+            kb_per = (int)cdiv(num_kb, want);
+            ksplit = (int)cdiv(num_kb, kb_per);                    // every slice has at least one k-block
+            m_pad = (int)(cdiv(a.M, H3_BM) * H3_BM);
+            static float *pbuf = nullptr; static size_t pcap = 0;
+            const size_t need = (size_t)ksplit * m_pad * a.N;
+            if (need > pcap) {
+                if (pbuf) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(pbuf); }
+                pbuf = (float *)dev_alloc(need * 4); pcap = need;
+            }
+            part = pbuf;
+        }
+    }
+    TcEpi epf = ep;                                                // the call's own epilogue, for the reduce kernel
+    if (ksplit > 1) { ep.bias = nullptr; ep.res = nullptr; ep.act = ACT_NONE; ep.y = part; ep.ldy = a.N; }
+    const CUtensorMap *my = !ep.tma_store ? mx1
+                          : ksplit > 1 ? tc_get_map(part, (int64_t)ksplit * m_pad, a.N, a.N, 32, false)
+                                       : tc_get_map(a.y, a.M, a.N, ep.ldy, 32, false);
+    const int64_t items = tiles * ksplit;
+    int grid = (int)(items < ctx().sm_count ? items : ctx().sm_count);     // persistent: one CTA per SM
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
 #define H3_LAUNCH(BN_)                                                                                                      \
@@ -349,7 +407,7 @@ void gemm_h3(const GemmArgs &a) {
         static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");                               \
         static bool set = false;                                                                                            \
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);        \
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);        \
     } while (0)
     // fused QKV projection: heads are 64 columns, a 128-column tile holds two, results leave as fp32 tiles
     const bool qkp = qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && bn == 128 && ep.tma_store && a.N % 128 == 0 && !a.res &&
@@ -359,11 +417,16 @@ void gemm_h3(const GemmArgs &a) {
         constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
         static bool set = false;
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute((k_gemm_h3<128, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles);
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);
     } else if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);
     else H3_LAUNCH(128);
 #undef H3_LAUNCH
+    if (ksplit > 1) {
+        const int64_t n4 = a.M * (int64_t)(a.N / 4), g = cdiv(n4, 256), cap = (int64_t)ctx().sm_count * 8;
+        LAUNCH_PDL(k_splitk_reduce, (unsigned)(g > cap ? cap : g), 256, 0, (const float *)part, ksplit, (int64_t)m_pad, a.M, a.N, epf.bias, epf.act,
+                   epf.res, epf.ldres, epf.y, epf.ldy);
+    }
 }
 
 } // namespace ncmb

@@ -16,7 +16,9 @@ pytestmark = pytest.mark.gpu
 # few rows (CUDA-core weight streaming)
 SHAPES = [(128, 128, 64), (256, 256, 512), (1000, 768, 520), (333, 200, 100), (2048, 1024, 2048), (8, 512, 512),
           # the fp16-pair engine picks 64-column tiles for these two (the second with ragged edges), 32-column ones for the third
-          (2048, 512, 512), (1100, 520, 192), (64, 768, 128)]
+          (2048, 512, 512), (1100, 520, 192), (64, 768, 128),
+          # few rows, long K: K runs as slices on CTAs of their own, a second kernel adds them
+          (20, 896, 4864), (64, 768, 3072), (130, 512, 2048)]
 
 
 @pytest.fixture(scope="module")
