@@ -372,12 +372,14 @@ void gemm_h3(const GemmArgs &a) {
     // width, is what the call takes. K is cut into slices that run as work items of their own; their raw sums go
     // to a partial buffer and k_splitk_reduce adds the slices in order and applies bias / activation / residual.
     static const bool splitk_ok = !getenv("NCM_B200_NO_SPLITK");
+    static const int sk_min = getenv("NCM_B200_SPLITK_MINKB") ? atoi(getenv("NCM_B200_SPLITK_MINKB")) : 12;
+    static const int sk_per = getenv("NCM_B200_SPLITK_PER") ? atoi(getenv("NCM_B200_SPLITK_PER")) : 4;
     int ksplit = 1, kb_per = num_kb, m_pad = 0;
     float *part = nullptr;
     auto al16 = [](const void *q) { return ((uintptr_t)q & 15) == 0; };
-    if (splitk_ok && ep.tma_store && !a.qk_applied && tiles * 2 <= ctx().sm_count && num_kb >= 24 && a.N % 32 == 0 &&
+    if (splitk_ok && ep.tma_store && !a.qk_applied && tiles * 2 <= ctx().sm_count && num_kb >= sk_min && a.N % 32 == 0 &&
         al16(a.bias) && al16(a.res) && (ep.ldres & 3) == 0) {
-        int want = (int)std::min<int64_t>(ctx().sm_count / tiles, num_kb / 8);
+        int want = (int)std::min<int64_t>(ctx().sm_count / tiles, num_kb / sk_per);
         if (want > 16) want = 16;
         if (want >= 2) {
             kb_per = (int)cdiv(num_kb, want);
