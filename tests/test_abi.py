@@ -133,3 +133,34 @@ def test_host_side_helpers_match_oracle(lib):
         want, ost = orc.sample_topkp(row, t, tk, tp, ost)
         assert got == want and st.value == ost
         assert lib.argmax_row(row.ctypes.data, row.size) == int(row.argmax())
+
+
+def test_reference_front_end_links_against_the_library():
+    """The reference's main.c + tok.c + tok_tables.c, compiled unchanged, link against libncm_b200.so with nothing but
+    the library's stand-ins for the training / viewer entry points (oracle/Makefile `cli`): every inference symbol
+    the reference's command-line front end uses is exported. (What the linked binary prints is compared with the
+    CPU build in tests/test_gpu_cli.py.)"""
+    ref_dir = os.path.dirname(helpers.REF_LIB)
+    exe, main_o = os.path.join(ref_dir, "cncm_b200"), os.path.join(ref_dir, "main_cli.o")
+    if not os.path.exists(main_o):
+        pytest.skip("reference sources were not available when the checkers were built")
+    assert os.path.exists(exe)
+    need = {ln.split()[-1] for ln in subprocess.check_output(["nm", "-u", main_o], text=True).splitlines() if ln.strip()}
+    have = set()
+    for f in (helpers.CUDA_LIB, os.path.join(ref_dir, "tok.o"), os.path.join(ref_dir, "tok_tables.o"), os.path.join(ref_dir, "cli_stubs.o")):
+        flag = ["-D", "--defined-only"] if f.endswith(".so") else ["--defined-only"]
+        have |= {ln.split()[-1] for ln in subprocess.check_output(["nm"] + flag + [f], text=True).splitlines() if ln.strip()}
+    missing = sorted(s for s in need - have if not s.startswith("_") and "@" not in s and s not in _LIBC)
+    assert not missing, missing
+    # the stand-ins cover training / viewers only: none of them shadows an inference entry point of the library
+    stubs = {ln.split()[-1] for ln in subprocess.check_output(["nm", "--defined-only", os.path.join(ref_dir, "cli_stubs.o")], text=True).splitlines()
+             if " T " in ln}
+    lib_syms = {ln.split()[-1] for ln in subprocess.check_output(["nm", "-D", "--defined-only", helpers.CUDA_LIB], text=True).splitlines() if ln.strip()}
+    assert not (stubs & lib_syms), sorted(stubs & lib_syms)
+
+
+_LIBC = {"calloc", "clock_gettime", "exit", "fclose", "fflush", "fgets", "fopen", "fputc", "free", "fseek", "ftell", "fwrite", "getenv",
+         "malloc", "memcpy", "memset", "omp_set_num_threads", "snprintf", "stderr", "stdin", "stdout", "strchr", "strcmp", "strlen",
+         "strncmp", "strtod", "strtol", "strtoll", "strtoull", "printf", "fprintf", "puts", "putchar", "atoi", "atof", "strstr", "qsort",
+         "realloc", "fread", "sprintf", "sscanf", "memcmp", "strncpy", "strcpy", "strdup", "exp", "log", "pow", "sqrt", "fputs", "getline",
+         "strrchr", "memmove", "abort", "rand", "srand", "time", "floor", "ceil", "fabs", "usleep", "nanosleep", "isatty", "fileno", "read"}
