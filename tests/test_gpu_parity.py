@@ -403,6 +403,32 @@ PPL_SPECS = {
 }
 
 
+@pytest.mark.parametrize("kind", ["gpt2", "qwen"])
+def test_batched_decode_steps_through_k_sliced_projections(cuda, tmp, kind):
+    """20 rows per decode step at width 768: too many rows for the GEMV path, few tiles and a long K for the
+    tensor-core GEMM, so the attention-output and MLP-down projections run K in slices with a reduce kernel behind
+    them. Ids equal independent oracle runs."""
+    import orc
+    import synth
+    if kind == "gpt2":
+        spec = synth.LMSpec("gpt2_w768", "gpt2", 1, 768, 12, 12, 3072, 300, 32, rand_affine=1)
+    else:
+        spec = synth.LMSpec("qwen_w768", "qwen", 1, 768, 12, 2, 2048, 300, 32, rope_theta=1e6, rand_affine=1)
+    conf, w = synth.write_lm(spec, tmp)
+    cfg = cuda.load_config(conf)
+    m = cuda.ncmb_lm_open(cfg, w.encode(), int(kind == "qwen"), 0)
+    om = orc.LM(conf, w, kind == "qwen")
+    B, n_new = 20, 5
+    P = np.ascontiguousarray(synth.lm_prompts(spec, B, 6, 17))
+    out = np.zeros((B, n_new), np.int32)
+    cuda.ncmb_lm_generate(m, P.ctypes.data, B, P.shape[1], n_new, 0.0, 0, 1.0, 0, -1, out.ctypes.data)
+    for b in range(B):
+        want = om.generate(P[b], n_new, temp=0.0)
+        assert (out[b] == want).all(), (kind, b, out[b], want)
+    assert cuda.ncmb_gemm_tc_check() == 0
+    cuda.ncmb_lm_close(m)
+
+
 @pytest.mark.parametrize("B", [2, 11])
 def test_nucleus_sampling_over_a_vocabulary_too_large_for_the_block_sampler(cuda, tmp, B):
     """top_k = 0 over 2500 entries (the Qwen2 setting, temp 0.7 / top-p 0.95, at a size the oracle finishes quickly):
