@@ -268,11 +268,12 @@ void attention_decode(const AttnArgs &a) {
     static unsigned *count = nullptr; static size_t count_cap = 0;
     // Keys of a row are shared out in 32-key chunks. With few (row, kv head) pairs every chunk gets a CTA of its own
     // (a batch-1 decode step has nothing else to fill the GPU with); with many pairs a CTA walks several chunks,
-    // so that the fixed cost per CTA (query load, partials through L2, the merge) is paid about 16 x SMs times
+    // so that the fixed cost per CTA (query load, partials through L2, the merge) is paid about 8 x SMs times
     // and not once per chunk.
     const int max_chunks = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
     const int64_t pairs = (int64_t)a.rows * a.Hkv;
-    int want_split = (int)std::min<int64_t>(max_chunks, cdiv((int64_t)ctx().sm_count * 16, pairs));
+    static const int per_sm = getenv("NCM_B200_ATTN_DEC_PER_SM") ? atoi(getenv("NCM_B200_ATTN_DEC_PER_SM")) : 8;
+    int want_split = (int)std::min<int64_t>(max_chunks, cdiv((int64_t)ctx().sm_count * per_sm, pairs));
     if (want_split < 1) want_split = 1;
     static const int cps_env = getenv("NCM_B200_ATTN_DEC_CPS") ? atoi(getenv("NCM_B200_ATTN_DEC_CPS")) : 0;
     const int cps = cps_env > 0 ? std::min(cps_env, max_chunks) : (int)cdiv(max_chunks, want_split);
