@@ -15,7 +15,6 @@
 #include "common.cuh"
 
 #include <cub/device/device_radix_sort.cuh>
-#include <cub/device/device_segmented_radix_sort.cuh>
 #include <vector>
 
 namespace ncmb {
