@@ -522,7 +522,7 @@ static int two_phase_width(const SampleArgs &a) {
 size_t sample_scratch_floats(int Bn, int V) { return V > SM_SMEM_V ? (size_t)Bn * V : 0; }
 
 // ---- large candidate sets (top_k = 0 or > 2048 over a big vocabulary, one position per row) ----
-// The row is sorted once (value descending, index ascending on ties: a stable segmented
+// The rows are sorted once (value descending, index ascending on ties: a stable device-wide
 // radix sort) and one CTA per row then walks it with block-wide fp64 prefix sums: the
 // nucleus cut "cum_before - p > top_p" and the draw "u <= cum" are monotone in the sorted
 // rank, so each is the minimum rank that satisfies a predicate. Sums are formed in a
