@@ -565,7 +565,7 @@ __device__ __forceinline__ double block_excl_scan(double v, double *sm, double *
 
 // K64: keys are the composite 64-bit keys of k_sort_prep64 (the value is recovered from the low word)
 template <bool K64>
-__global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restrict__ keys, const int *__restrict__ idx, int V, int keep,
+__global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restrict__ keys, const int *__restrict__ idx, double *__restrict__ pcache, int V, int keep,
                                                            float top_p, const double *__restrict__ uniforms,
                                                            unsigned long long seed, long long row0, int level,
                                                            int *__restrict__ out, int out_stride, int out_off) {
@@ -583,7 +583,10 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restri
     const int chunk = (keep + SL_THREADS - 1) / SL_THREADS;
     const int r0 = tid * chunk, r1 = min(r0 + chunk, keep);
     double local = 0;
-    for (int r = r0; r < r1; r++) local += exp(val(r) - mx);
+    // the exponentials are taken once and kept: the passes below read them back. A thread's i-th entry sits at
+    // [i][thread], so that a warp's accesses fall into one line although every thread walks its own run of ranks
+    double *pc = pcache + (size_t)b * ((size_t)chunk * SL_THREADS) + tid;
+    for (int r = r0; r < r1; r++) { const double p = exp(val(r) - mx); pc[(size_t)(r - r0) * SL_THREADS] = p; local += p; }
     double den;
     const double base = block_excl_scan(local, sm, &den);
     // nucleus cut: first rank with (cum_before - p) / den > top_p
@@ -592,7 +595,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restri
     {
         double cum = base;
         for (int r = r0; r < r1; r++) {
-            double p = exp(val(r) - mx);
+            double p = pc[(size_t)(r - r0) * SL_THREADS];
             if ((cum - p) / den > (double)top_p) { atomicMin(&s_min, r); break; }
             cum += p;
         }
@@ -602,7 +605,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restri
     __syncthreads();
     // mass of the kept prefix
     double lk = 0;
-    for (int r = r0; r < r1 && r < nkeep; r++) lk += exp(val(r) - mx);
+    for (int r = r0; r < r1 && r < nkeep; r++) lk += pc[(size_t)(r - r0) * SL_THREADS];
     double den2;
     const double base2 = block_excl_scan(lk, sm, &den2);
     const double u01 = uniforms ? uniforms[b] : counter_uniform(seed, row0 + b, level, 0);
@@ -612,7 +615,7 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restri
     {
         double acc = base2;
         for (int r = r0; r < r1 && r < nkeep; r++) {
-            acc += exp(val(r) - mx);
+            acc += pc[(size_t)(r - r0) * SL_THREADS];
             if (u <= acc) { atomicMin(&s_min, r); break; }
         }
     }
@@ -639,7 +642,8 @@ static void sample_rows_large(const SampleArgs &a, int keep) {
     else
         cub::DeviceRadixSort::SortPairs(nullptr, temp_bytes, (const unsigned long long *)nullptr, (unsigned long long *)nullptr,
                                         (const int *)nullptr, (int *)nullptr, n, 0, 32 + row_bits, stream());
-    size_t need = (size_t)n * 24 + temp_bytes + 4096;
+    const size_t pc_per_row = (size_t)cdiv(keep, SL_THREADS) * SL_THREADS;
+    size_t need = (size_t)n * 24 + (size_t)a.Bn * pc_per_row * 8 + temp_bytes + 8192;
     if (need > ws.cap) ws.reserve(need);
     ws.reset();
     ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
@@ -649,21 +653,23 @@ static void sample_rows_large(const SampleArgs &a, int keep) {
         float *k_in = ws.get<float>(n), *k_out = ws.get<float>(n);
         int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
         void *temp = ws.alloc(temp_bytes);
+        double *pcache = ws.get<double>((size_t)a.Bn * pc_per_row);
         LAUNCH(k_sort_prep, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
         e = cub::DeviceRadixSort::SortPairsDescending(temp, temp_bytes, k_in, k_out, i_in, i_out, a.V, 0, 32, stream());
         ctx().launches += 7;
         if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
-        LAUNCH(k_pick_sorted<false>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
+        LAUNCH(k_pick_sorted<false>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, pcache, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
                a.rng_row0, a.rng_level, a.out, a.out_stride, a.out_off);
     } else {
         unsigned long long *k_in = ws.get<unsigned long long>(n), *k_out = ws.get<unsigned long long>(n);
         int *i_in = ws.get<int>(n), *i_out = ws.get<int>(n);
         void *temp = ws.alloc(temp_bytes);
+        double *pcache = ws.get<double>((size_t)a.Bn * pc_per_row);
         LAUNCH(k_sort_prep64, (unsigned)(g > cap ? cap : g), 256, 0, a.logits, a.temp, n, a.V, k_in, i_in);
         e = cub::DeviceRadixSort::SortPairs(temp, temp_bytes, k_in, k_out, i_in, i_out, n, 0, 32 + row_bits, stream());
         ctx().launches += 2 * ((32 + row_bits + 7) / 8) + 1;
         if (e != cudaSuccess) fatal("radix sort failed: %s", cudaGetErrorString(e));
-        LAUNCH(k_pick_sorted<true>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
+        LAUNCH(k_pick_sorted<true>, (unsigned)a.Bn, SL_THREADS, 0, (const void *)k_out, (const int *)i_out, pcache, a.V, keep, a.top_p, a.uniforms, a.rng_seed,
                a.rng_row0, a.rng_level, a.out, a.out_stride, a.out_off);
     }
 }
