@@ -373,7 +373,7 @@ void gemm_h3(const GemmArgs &a) {
     // to a partial buffer and k_splitk_reduce adds the slices in order and applies bias / activation / residual.
     static const bool splitk_ok = !getenv("NCM_B200_NO_SPLITK");
     static const int sk_min = getenv("NCM_B200_SPLITK_MINKB") ? atoi(getenv("NCM_B200_SPLITK_MINKB")) : 12;
-    static const int sk_per = getenv("NCM_B200_SPLITK_PER") ? atoi(getenv("NCM_B200_SPLITK_PER")) : 4;
+    static const int sk_per = getenv("NCM_B200_SPLITK_PER") ? atoi(getenv("NCM_B200_SPLITK_PER")) : 2;
     int ksplit = 1, kb_per = num_kb, m_pad = 0;
     float *part = nullptr;
     auto al16 = [](const void *q) { return ((uintptr_t)q & 15) == 0; };
