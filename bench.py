@@ -133,13 +133,16 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- CPU arm
 
-def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int):
+def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int, keep: "dict | None" = None):
     """Times the reference's CPU build (oracle/_ref) -- or, where that build is not
     present, the CPU oracle port -- on `rows` sequences of the workload per step.
-    Returns (kind, cores, [seconds per step])."""
+    Returns (kind, cores, [seconds per step]); `keep` receives the prefixes, seed, codes and
+    token ids of the last step so that the caller can check its own results against them."""
     cores = os.cpu_count() or 1
     kw = gen_kwargs(spec)
     pre = synth.ncp_prefixes(spec, rows, seed)
+    if keep is not None:
+        keep.update(prefix=pre, seed=seed)
     ref_lib = os.path.join(ROOT, "oracle", "_ref", "libcncm_ref.so")
     times = []
     if os.path.exists(ref_lib):
@@ -157,10 +160,12 @@ def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int)
             lg = ref.arena_alloc(rows * L * Vp)
             ref.vq_idx_to_zhats(m.vq, codes.ctypes.data, rows, (C.c_void_p * nl)(*zh))
             ref.vqvae_decode(m.vqvae, zh[-1], lg, rows)
-            ref.to_host(lg, (rows, L, Vp)).argmax(axis=-1)
+            toks = ref.to_host(lg, (rows, L, Vp)).argmax(axis=-1)
             dt = time.perf_counter() - t0
             if it >= warmup:
                 times.append(dt)
+            if keep is not None:
+                keep.update(codes=codes, tokens=toks.astype(np.int32))
         return "reference", cores, times
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import orc
@@ -168,10 +173,12 @@ def cpu_sample_run(spec, conf, w, rows: int, steps: int, warmup: int, seed: int)
     for it in range(warmup + steps):
         t0 = time.perf_counter()
         codes = m.generate(pre, seed=seed, **kw)
-        m.decode_tokens(codes)
+        toks = m.decode_tokens(codes)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
+        if keep is not None:
+            keep.update(codes=codes, tokens=toks)
     return "port", min(cores, rows * (2 if kw["cfg"] > 0 else 1)), times
 
 
@@ -221,7 +228,13 @@ def shard_plan(rank: int, world: int, per_gpu: int) -> dict:
     draws its own prefixes (seed 1000 + r) and keys the counter-based sampler by global row."""
     assert 0 <= rank < world
     return {"rows": per_gpu, "row_offset": rank * per_gpu, "prefix_seed": 1000 + rank,
-            "global_rows": world * per_gpu}
+            "global_rows": world * per_gpu, "rng_mode": 1}
+
+
+def token_checksum(tokens) -> int:
+    """CRC-32 of a rank's decoded token ids (int32, row-major): printed per rank so that runs can be compared"""
+    import zlib
+    return zlib.crc32(np.ascontiguousarray(tokens, dtype=np.int32).tobytes())
 
 
 def max_over_ranks(values, device="cpu"):
@@ -272,6 +285,10 @@ def run_gpu_arm(args):
     tokens_dev = torch.empty((B, spec.L), dtype=torch.int32, device="cuda")
     allow = kw.get("allow")
     allow_p = allow.ctypes.data if allow is not None else None
+    # timed runs draw from the counter-based stream keyed by the global sequence index: a sequence's codes do not
+    # depend on which rank, batch or wave it runs in (the reference's batch-ordered stream is used for the parity
+    # check against the CPU run further down)
+    lib.ncmb_set_rng_mode(plan["rng_mode"])
     lib.ncmb_set_row_offset(plan["row_offset"])
 
     def barrier():
@@ -366,6 +383,12 @@ def run_gpu_arm(args):
     lib.ncmb_copy_bytes(C.byref(h1), C.byref(d1))
 
     dev_s, e2e_max, _ = max_over_ranks([dev_ms / 1000.0, e2e_s, t_wall], device="cuda")
+    # checksum of the token ids of the last end-to-end step, one per rank
+    sums = torch.zeros(world, dtype=torch.int64, device="cuda")
+    sums[rank] = token_checksum(tokens_host.numpy())
+    if world > 1:
+        dist.all_reduce(sums)
+    checksums = [int(v) for v in sums.tolist()]
     if rank == 0:
         peaks = {}
         pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -412,11 +435,28 @@ def run_gpu_arm(args):
             "kernel_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
             "profiled_ms_per_step": prof_ms / args.steps,
         }
+        line["rng"] = "counter-based, keyed by (seed, global sequence index, level, position)"
+        line["token_checksums"] = checksums
         if world == 1 and not args.no_cpu_baseline:
-            kind, cores, times = cpu_sample_run(spec, conf, w, args.cpu_rows, 1, 0, 7)
+            got = {}
+            kind, cores, times = cpu_sample_run(spec, conf, w, args.cpu_rows, 1, 0, 7, keep=got)
             line["cpu_baseline"] = {
                 "value": args.cpu_rows * tok / times[0], "unit": "tokens/s", "cores": cores, "kind": kind,
                 "sample": f"{args.cpu_rows} of the {B} sequences, one pass (reference cost is linear in sequences)"}
+            # result check: the same prefixes and seed through the library, on the reference's own sampling stream
+            lib.ncmb_set_rng_mode(0)
+            lib.ncmb_set_row_offset(0)
+            codes = model.generate(got["prefix"], seed=got["seed"], **kw)
+            toks = model.decode_tokens(codes, spec.L)
+            lib.ncmb_set_rng_mode(plan["rng_mode"])
+            line["parity_check"] = {
+                "rows": int(codes.shape[0]), "against": kind,
+                "codes_equal": bool(np.array_equal(codes, got["codes"])),
+                "tokens_equal": bool(np.array_equal(toks, got["tokens"])),
+                "codes_differing": int((codes != got["codes"]).sum()), "codes_total": int(codes.size),
+                "tensor_core_timeouts": int(lib.ncmb_gemm_tc_check())}
+        if world == 1 and args.workload == "c2" and not args.no_workloads:
+            line["workloads"] = other_workloads(lib, args)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -425,8 +465,9 @@ def run_gpu_arm(args):
 
 def describe_gemm_shape(spec, flops):
     """Names the transformer GEMM whose 2*M*N*K equals `flops` and, for the gated up-projection, scales the
-    DRAM traffic measured under ncu (profiles/k_gemm_h3__c2s_b128.md: 293.3 MB read+write at M=32896,
-    N=4096, K=512, i.e. 8916 bytes per token row; traffic is proportional to M at fixed N, K)."""
+    DRAM traffic of one captured launch of that kernel (dram bytes read + written: 293.3 MB at M=32896, N=4096,
+    K=512, i.e. 8916 bytes per token row; input and output bytes are per row and the 8 MB weight pair is read
+    once, so traffic is proportional to M at fixed N, K)."""
     C_ = spec.n_embd
     Hh = spec.mlp_hidden if spec.mlp_hidden else 4 * C_
     kvd = (spec.n_kv_heads or spec.n_head) * (C_ // spec.n_head)
@@ -456,8 +497,100 @@ def lm_workload(name):
     raise SystemExit(f"unknown workload {name}")
 
 
-def run_lm_arm(args):
-    """GPT-2 / Qwen2 shaped decoding with a KV cache: tokens/s and achieved HBM GB/s per decode step."""
+def _peaks():
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    return json.load(open(pk)) if os.path.exists(pk) else {}
+
+
+# Dense TF32 throughput of one B200 of this pool: torch.matmul on 8192^3 fp32 operands with TF32 allowed, best of
+# 10, measured once with a scratch script in the way the bf16 figure of MEASURED_PEAKS.json is measured (that file
+# has no TF32 entry). Used as the denominator of the quantizer sweep, whose distance GEMM runs on the TF32 pipe.
+TF32_PEAK_TFLOPS_MEASURED = None
+
+
+def tf32_peak():
+    p = _peaks()
+    if "tf32_tflops" in p:
+        return p["tf32_tflops"], "MEASURED_PEAKS.json tf32_tflops"
+    if TF32_PEAK_TFLOPS_MEASURED:
+        return TF32_PEAK_TFLOPS_MEASURED, "torch.matmul TF32 8192^3 on this pool (builder-measured)"
+    return p.get("bf16_tflops", 1590.0) / 2.0, "half of the measured bf16 burst peak (no TF32 measurement)"
+
+
+def lm_bytes_per_step(spec, B, mean_ctx):
+    """Algorithmic bytes of one decode step: every parameter once plus the K/V cache of B sequences at the mean
+    context, at the storage width the configuration states (fp32 for the GPT-2 shape; 2-byte weights and 2-byte
+    K/V for the bf16 Qwen2 shape)."""
+    C_, hd = spec.n_embd, spec.n_embd // spec.n_head
+    kvd = spec.n_kv_heads * hd
+    per_layer = C_ * (C_ + 2 * kvd) + C_ * C_ + (3 if spec.kind == "qwen" else 2) * C_ * spec.n_inner
+    params = spec.n_layer * per_layer + spec.vocab * C_
+    width = 2.0 if spec.bf16_round else 4.0
+    return width * params + B * spec.n_layer * 2 * kvd * width * mean_ctx
+
+
+def measure_lm(lib, stream, name, batches, steps, warmup, local):
+    """GPT-2 / Qwen2 shaped decoding with a KV cache, one line per batch size: tokens/s (prefill included) and
+    achieved HBM GB/s per decode step. The model is opened once for all batch sizes."""
+    import torch
+    spec, w = lm_workload(name)
+    tmp = tempfile.TemporaryDirectory()
+    conf, wt = synth.write_lm(spec, tmp.name)
+    cfg = lib.load_config(conf)
+    m = lib.ncmb_lm_open(cfg, wt.encode(), int(spec.kind == "qwen"), int(spec.bf16_round))
+    os.remove(wt)                                              # up to 2 GB; the model holds its own copy
+    peak = _peaks().get("hbm_gbs", 6650.0)
+    lines = []
+    for B in batches:
+        prompts = np.ascontiguousarray(synth.lm_prompts(spec, B, w["prompt"], 5))
+        out = np.zeros((B, w["n_new"]), np.int32)
+
+        def step(seed):
+            lib.ncmb_lm_generate(m, prompts.ctypes.data, B, w["prompt"], w["n_new"], w["temp"], w["top_k"], w["top_p"],
+                                 seed, -1, out.ctypes.data)
+
+        for i in range(warmup):
+            step(1 + i)
+        n0 = lib.ncmb_launch_count()
+        torch.cuda.synchronize()
+        with ClockSampler(local) as clk:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record(stream)
+            for i in range(steps):
+                step(100 + i)
+            e1.record(stream)
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+        dev_s = e0.elapsed_time(e1) / 1000.0
+        launches = lib.ncmb_launch_count() - n0
+        bytes_step = lm_bytes_per_step(spec, B, w["prompt"] + w["n_new"] / 2.0)
+        steps_total = steps * w["n_new"]
+        ach = bytes_step * steps_total / dev_s / 1e9
+        lines.append({
+            "metric": "generated tokens/sec", "value": B * steps_total / dev_s, "unit": "tokens/s", "n_gpus": 1,
+            "steps": steps, "warmup": warmup, "ms_per_step": 1000.0 * dev_s / steps,
+            "token_latency_ms": 1000.0 * dev_s / steps_total, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 (2-byte weight copies streamed by the decode steps)" if spec.bf16_round else "f32",
+            "data": "synthetic",
+            "config": {"workload": f"{name}: {spec.kind} {spec.n_layer}x{spec.n_embd}, vocab {spec.vocab}, prompt {w['prompt']}, "
+                                   f"+{w['n_new']} tokens, batch {B}, temp {w['temp']}, top-p {w['top_p']}; KV-cached decode incl. prefill"},
+            "e2e": {"value": B * steps_total / wall, "unit": "tokens/s", "h2d_bytes_per_step": int(prompts.nbytes),
+                    "d2h_bytes_per_step": int(out.nbytes)},
+            "gpu_launches": launches, "clocks": clk.summary(),
+            "roofline": {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)", "achieved": ach,
+                         "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_bytes_per_step": bytes_step,
+                         "note": "token latency here is the mean over the run (prefill included); bytes per step count "
+                                 + ("2 B per parameter and 2 B per cached K/V element" if spec.bf16_round else "4 B per parameter and per cached K/V element")},
+        })
+    assert lib.ncmb_gemm_tc_check() == 0
+    lib.ncmb_lm_close(m)
+    tmp.cleanup()
+    return lines
+
+
+def _lm_setup(args):
     import torch
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -466,97 +599,140 @@ def run_lm_arm(args):
         lib.ncmb_set_gemm_mode(args.gemm)
     stream = torch.cuda.current_stream()
     lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
-    spec, w = lm_workload(args.workload)
-    B = args.batch or w["batch"]
-    tmp = tempfile.TemporaryDirectory()
-    conf, wt = synth.write_lm(spec, tmp.name)
-    cfg = lib.load_config(conf)
-    m = lib.ncmb_lm_open(cfg, wt.encode(), int(spec.kind == "qwen"), int(spec.bf16_round))
-    prompts = np.ascontiguousarray(synth.lm_prompts(spec, B, w["prompt"], 5))
-    out = np.zeros((B, w["n_new"]), np.int32)
-
-    def step(seed):
-        lib.ncmb_lm_generate(m, prompts.ctypes.data, B, w["prompt"], w["n_new"], w["temp"], w["top_k"], w["top_p"],
-                             seed, -1, out.ctypes.data)
-
-    for i in range(args.warmup):
-        step(1 + i)
-    n0 = lib.ncmb_launch_count()
-    torch.cuda.synchronize()
-    with ClockSampler(local) as clk:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        e0.record(stream)
-        for i in range(args.steps):
-            step(100 + i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        wall = time.perf_counter() - t0
-    dev_s = e0.elapsed_time(e1) / 1000.0
-    launches = lib.ncmb_launch_count() - n0
-    C_, hd = spec.n_embd, spec.n_embd // spec.n_head
-    kvd = spec.n_kv_heads * hd
-    per_layer = C_ * (C_ + 2 * kvd) + C_ * C_ + (3 if spec.kind == "qwen" else 2) * C_ * spec.n_inner
-    params = spec.n_layer * per_layer + spec.vocab * C_
-    mean_ctx = w["prompt"] + w["n_new"] / 2.0
-    bytes_step = 4.0 * params + B * spec.n_layer * 2 * kvd * 4.0 * mean_ctx
-    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-    peak = peaks.get("hbm_gbs", 6650.0)
-    steps_total = args.steps * w["n_new"]
-    ach = bytes_step * steps_total / dev_s / 1e9
-    line = {
-        "metric": "generated tokens/sec", "value": B * steps_total / dev_s, "unit": "tokens/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * dev_s / args.steps,
-        "p50_token_latency_ms": 1000.0 * dev_s / steps_total, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: {spec.kind} {spec.n_layer}x{spec.n_embd}, vocab {spec.vocab}, prompt {w['prompt']}, "
-                               f"+{w['n_new']} tokens, batch {B}, temp {w['temp']}, top-p {w['top_p']}; KV-cached decode incl. prefill"},
-        "e2e": {"value": B * steps_total / wall, "unit": "tokens/s", "h2d_bytes_per_step": int(prompts.nbytes),
-                "d2h_bytes_per_step": int(out.nbytes)},
-        "gpu_launches": launches, "clocks": clk.summary(),
-        "roofline": {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)", "achieved": ach,
-                     "peak": peak, "unit": "GB/s", "frac": ach / peak, "traffic": None,
-                     "algorithmic_bytes_per_step": bytes_step},
-    }
-    print(json.dumps(line), flush=True)
-    lib.ncmb_lm_close(m)
-    tmp.cleanup()
+    return lib, stream, local
 
 
-def run_quantizer_arm(args):
+def run_lm_arm(args):
+    lib, stream, local = _lm_setup(args)
+    _, w = lm_workload(args.workload)
+    for line in measure_lm(lib, stream, args.workload, [args.batch or w["batch"]], args.steps, args.warmup, local):
+        print(json.dumps(line), flush=True)
+
+
+def measure_quantizer(lib, stream, n, steps, warmup):
     """Flat nearest-code search: N(0,1) 64-d vectors against a 16384 x 64 codebook (config-5 sweep)."""
     import torch
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-    lib = capi.NcmLib(os.path.join(ROOT, "saphira-cncm_b200", "libncm_b200.so"))
-    stream = torch.cuda.current_stream()
-    lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
     spec = synth.spec_c2(n_layer=1, vocab=16384, name="c5q")
     tmp = tempfile.TemporaryDirectory()
     conf, wt = synth.write_ncp(spec, tmp.name)
     model = capi.NcpModel(lib, conf, wt, arena_mb=64)
-    n = args.batch or (1 << 20)
     x = torch.randn((n, 64), device="cuda", dtype=torch.float32, generator=torch.Generator(device="cuda").manual_seed(3))
     idx = torch.empty((n,), device="cuda", dtype=torch.int32)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         lib.ncmb_vq_nearest_dev(model.vq, 3, x.data_ptr(), n, idx.data_ptr())
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         lib.ncmb_vq_nearest_dev(model.vq, 3, x.data_ptr(), n, idx.data_ptr())
     e1.record(stream)
     torch.cuda.synchronize()
-    dev_s = e0.elapsed_time(e1) / 1000.0 / args.steps
+    dev_s = e0.elapsed_time(e1) / 1000.0 / steps
     flops = 2.0 * n * 16384 * 64
-    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-    peak = peaks.get("bf16_tflops", 1590.0)
-    print(json.dumps({"metric": "quantized vectors/sec", "value": n / dev_s, "unit": "vectors/s", "n_gpus": 1,
-                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * dev_s, "higher_is_better": True,
-                      "dtype": "f32", "data": "synthetic",
-                      "config": {"workload": f"c5q: {n} fp32 N(0,1) 64-d vectors vs 16384 x 64 codebook, nearest code"},
-                      "roofline": {"bound": "tensor", "achieved": flops / dev_s / 1e12, "peak": peak, "unit": "TFLOP/s",
-                                   "frac": flops / dev_s / 1e12 / peak, "traffic": None}}), flush=True)
+    peak, src = tf32_peak()
+    line = {"metric": "quantized vectors/sec", "value": n / dev_s, "unit": "vectors/s", "n_gpus": 1,
+            "steps": steps, "warmup": warmup, "ms_per_step": 1000 * dev_s, "higher_is_better": True,
+            "dtype": "3xtf32 (fp32-grade distances)", "data": "synthetic",
+            "config": {"workload": f"c5q: {n} fp32 N(0,1) 64-d vectors vs 16384 x 64 codebook, nearest code"},
+            "roofline": {"bound": "tensor", "achieved": flops / dev_s / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": flops / dev_s / 1e12 / peak, "traffic": None, "peak_source": src, "mma_passes": 3}}
+    lib.ncp_free(model.ncp)
+    lib.vqvae_free(model.vqvae)
+    lib.weights_free(C.byref(model.ws))
     tmp.cleanup()
+    return line
+
+
+def run_quantizer_arm(args):
+    lib, stream, _ = _lm_setup(args)
+    print(json.dumps(measure_quantizer(lib, stream, args.batch or (1 << 20), args.steps, args.warmup)), flush=True)
+
+
+def measure_ncp_brief(lib, stream, name, B, steps, warmup, local):
+    """A short device-timed run of another NCP configuration (ids resident, stepper + device decode): throughput,
+    level latencies and the algorithmic tensor-core fraction of the whole step."""
+    import torch
+    spec, B0 = workload(name)
+    B = B or B0
+    kw = gen_kwargs(spec)
+    tmp = tempfile.TemporaryDirectory()
+    conf, w = synth.write_ncp(spec, tmp.name)
+    model = capi.NcpModel(lib, conf, w, arena_mb=64)
+    os.remove(w)
+    prefix = torch.from_numpy(synth.ncp_prefixes(spec, B, 1000)).pin_memory()
+    tokens_dev = torch.empty((B, spec.L), dtype=torch.int32, device="cuda")
+    allow = kw.get("allow")
+    allow_p = allow.ctypes.data if allow is not None else None
+    lat, total_ms = [], 0.0
+
+    def step(seed, timed):
+        nonlocal total_ms
+        g = lib.ncp_gen_begin(model.ncp, None, prefix.data_ptr(), B, kw["temp"], kw["top_k"], kw["top_p"], kw["cfg"],
+                              kw["freq"], kw["mu"], 0.0, 0, 1.0, allow_p, seed)
+        marks = [torch.cuda.Event(enable_timing=True)]
+        marks[0].record(stream)
+        while lib.ncp_gen_step(g, None, None) == 0:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            marks.append(ev)
+        lib.ncmb_decode_tokens_dev(model.vqvae, lib.ncmb_gen_codes_dev(g), B, tokens_dev.data_ptr())
+        end = torch.cuda.Event(enable_timing=True)
+        end.record(stream)
+        end.synchronize()
+        lib.ncp_gen_abort(g)
+        if timed:
+            total_ms += marks[0].elapsed_time(end)
+            lat.extend(a.elapsed_time(b) for a, b in zip(marks[:-1], marks[1:]))
+
+    for i in range(warmup):
+        step(100 + i, False)
+    n0 = lib.ncmb_launch_count()
+    with ClockSampler(local) as clk:
+        for i in range(steps):
+            step(200 + i, True)
+    launches = lib.ncmb_launch_count() - n0
+    tok = NOMINAL_TOKENS[name]
+    flop = algorithmic_flops_per_row(spec) * B * (2 if kw["cfg"] > 0 else 1)
+    peak = _peaks().get("bf16_tflops_sustained", 1400.0)
+    ach = flop * steps / (total_ms * 1e-3) / 1e12
+    line = {"metric": "generated tokens/sec", "value": B * tok * steps / (total_ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": steps, "warmup": warmup, "ms_per_step": total_ms / steps,
+            "p50_step_latency_ms": sorted(lat)[len(lat) // 2], "higher_is_better": True, "scaling": "weak",
+            "dtype": "f16 pairs x3 (fp32-grade operands, fp32 accumulate)", "data": "synthetic",
+            "config": workload_config(name, spec, B, 1), "gpu_launches": launches, "clocks": clk.summary(),
+            "roofline": {"bound": "tensor", "kernel": "whole step (all kernels)", "achieved": ach, "peak": peak,
+                         "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_tflop_per_step": flop / 1e12,
+                         "note": "algorithmic flops of the step (prefix once per model row) over the device time of "
+                                 "the whole step, not of one kernel"}}
+    assert lib.ncmb_gemm_tc_check() == 0
+    lib.ncp_free(model.ncp)
+    lib.vqvae_free(model.vqvae)
+    lib.weights_free(C.byref(model.ws))
+    tmp.cleanup()
+    return line
+
+
+def other_workloads(lib, args):
+    """Short runs of the other stated configurations on the same GPU, appended to the default 1-GPU line: the small
+    NCP (c1), the GPT-2 shape at batch 1 / 64 (c3), the Qwen2 shape at batch 1 / 32 / 256 (c4), the box-scale NCP on
+    1 024 sequences (c5) and the 2^20-vector quantizer sweep (c5q). Config 2 stays the headline."""
+    import torch
+    stream = torch.cuda.current_stream()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    lib.ncmb_set_rng_mode(1)
+    lib.ncmb_set_row_offset(0)
+    out = {}
+    t0 = time.perf_counter()
+    out["c1"] = measure_ncp_brief(lib, stream, "c1", 64, 5, 3, local)
+    for ln, B in zip(measure_lm(lib, stream, "c3", [1, 64], 2, 1, local), (1, 64)):
+        out[f"c3_b{B}"] = ln
+    for ln, B in zip(measure_lm(lib, stream, "c4", [1, 32, 256], 1, 1, local), (1, 32, 256)):
+        out[f"c4_b{B}"] = ln
+    out["c5_1024seq"] = measure_ncp_brief(lib, stream, "c5", 1024, 1, 1, local)
+    out["c5q"] = measure_quantizer(lib, stream, 1 << 20, 5, 3)
+    out["seconds"] = time.perf_counter() - t0
+    return out
 
 
 def main():
@@ -570,6 +746,8 @@ def main():
     ap.add_argument("--gemm", type=int, default=None, help="GEMM engine override (0 fp32, 1 tf32, 2 3xtf32, 3 fp16 pairs)")
     ap.add_argument("--cpu-rows", type=int, default=1, help="sequences in the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the short runs of the other configurations that the default 1-GPU run appends")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours" and args.workload == "c2":
         args.warmup = 3

@@ -266,6 +266,9 @@ int   ncmb_get_gemm_mode(void);
 /* The tensor-core kernels bound every barrier wait; when one runs out they record a
  * code and drain. Returns and clears that code (0 = never happened); synchronises. */
 int   ncmb_gemm_tc_check(void);
+/* Entries the TMA descriptor caches keep before they start over (default 4096; diagnostic: tests
+ * set 1 so that every lookup evicts the one before it). No counterpart in the reference. */
+void  ncmb_set_map_cache_limit(int entries);
 /* Diagnostic: the transformer blocks' token-major attention (head dim 64) on caller-supplied DEVICE
  * buffers, with engine 0 (CUDA-core kernel), 1 (tcgen05 kernel) or 2 (split-key decode kernel, one query
  * per row, one key segment), so they can be compared on the same
@@ -298,6 +301,8 @@ int   ncmb_prof_top_shape(int klass, long long *launches, double *ms, double *fl
 void  ncmb_prof_dump_shapes(void);
 int   ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes);
 long long ncmb_launch_count(void);            /* kernels launched since load */
+/* free and total bytes of the current device's memory (cudaMemGetInfo) */
+void  ncmb_mem_info(unsigned long long *free_bytes, unsigned long long *total_bytes);
 /* bytes this library has copied host->device and device->host since load */
 void  ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h);
 
@@ -306,12 +311,18 @@ void  ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h);
  * fixed at start-up, host callbacks and stream-capture regions (where cudaMalloc is not
  * legal), or steady-state serving code that must not stall or fail on an allocation. Scratch
  * for the split operands (2*batch*K + 2*M*K floats) comes from a 32 MiB array built into the
- * library; larger problems, or shapes outside batch >= 64, M >= 32, K >= 32, K % 4 == 0 with
- * 16-byte aligned pointers, return -1 with a message (0 = launched). The first call on a
+ * library; larger problems, or shapes outside batch > 16, M >= 32, K >= 32, K % 4 == 0 with
+ * 16-byte aligned pointers, return -1 with a message (0 = kernels queued). The first call on a
  * device resolves the array's address: make it before any stream capture. Calls share the
- * array, so calls that overlap on one GPU race; keep them ordered on one stream. */
+ * array, so calls that overlap on one GPU race; keep them ordered on one stream. A call made
+ * with a device current other than the one the library first ran on is refused (-1).
+ * The kernels bound every barrier wait; whether one ran out is known only after
+ * ncmb_linear_fwd_noalloc_check(): it synchronises the stream, then returns and clears this
+ * entry point's own status word (0 = all calls completed, -1 = never set up on this device).
+ * It allocates nothing either. */
 int ncmb_linear_fwd_noalloc(const float *x, const float *W, const float *b, float *y,
                             int64_t batch, int M, int K);
+int ncmb_linear_fwd_noalloc_check(void);
 
 /* NCP generate, extended: same as ncp_generate, and when logits_host is not NULL
  * it receives the logits each sampled position was drawn from (after the CFG

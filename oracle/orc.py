@@ -26,9 +26,20 @@ def build(force: bool = False) -> str:
     return LIB
 
 
-def build_ref(ref_dir: str = "/root/reference") -> "str | None":
+def reference_dir() -> "str | None":
+    """Where the reference's source tree lies: $NCM_REFERENCE_DIR, else a directory named `reference` beside this
+    repository. None when neither holds a src/ folder (the prebuilt oracle/_ref is used as it is then)."""
+    cands = [os.environ.get("NCM_REFERENCE_DIR"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "src")):
+            return c
+    return None
+
+
+def build_ref(ref_dir: "str | None" = None) -> "str | None":
     """Compile the reference CPU build into oracle/_ref/ when its sources exist."""
-    if not os.path.isdir(os.path.join(ref_dir, "src")):
+    ref_dir = ref_dir or reference_dir()
+    if not ref_dir or not os.path.isdir(os.path.join(ref_dir, "src")):
         return REF_LIB if os.path.exists(REF_LIB) else None
     subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref_dir}"])
     # the reference's command-line front end linked against the GPU library (needs that library built)

@@ -132,7 +132,10 @@ _SIGS = {
     "ncmb_prof_read": (_I, [_I, C.POINTER(C.c_longlong), C.POINTER(C.c_double), C.POINTER(C.c_double),
                             C.POINTER(C.c_double)]),
     "ncmb_linear_fwd_noalloc": (_I, [_P, _P, _P, _P, _I64, _I, _I]),
+    "ncmb_linear_fwd_noalloc_check": (_I, []),
+    "ncmb_set_map_cache_limit": (None, [_I]),
     "ncmb_launch_count": (C.c_longlong, []),
+    "ncmb_mem_info": (None, [C.POINTER(_U64), C.POINTER(_U64)]),
     "ncmb_copy_bytes": (None, [C.POINTER(_U64), C.POINTER(_U64)]),
     "ncmb_ncp_generate_ex": (_P, [_P, _P, _P, _I, _F, _I, _F, _F, _F, _F, _F, _I, _F, _P, _U64, _P]),
     "ncmb_decode_tokens": (None, [_P, _P, _I, _P]),

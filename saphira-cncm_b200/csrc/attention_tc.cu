@@ -458,16 +458,16 @@ static void attention_tc_launch(const AttnArgs &a, float *out, float *out_lo, in
     d.kb_off = kb_off; d.kb_len = kb_len; d.ml = ml;
     const int G = a.H / a.Hkv;
     d.pack = (!ml && a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
-    const CUtensorMap *mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);
-    const CUtensorMap *mk1 = tc_get_map(a.k1, a.k1_total, 2 * a.Hkv * 64, a.ldk1, 32, false);
-    const CUtensorMap *mk2 = a.k2 ? tc_get_map(a.k2, a.k2_total, 2 * a.Hkv * 64, a.ldk2, 32, false) : mk1;
+    const CUtensorMap mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);
+    const CUtensorMap mk1 = tc_get_map(a.k1, a.k1_total, 2 * a.Hkv * 64, a.ldk1, 32, false);
+    const CUtensorMap mk2 = a.k2 ? tc_get_map(a.k2, a.k2_total, 2 * a.Hkv * 64, a.ldk2, 32, false) : mk1;
     static bool set = false;
     if (!set) {
         CUDA_CHECK(cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
         set = true;
     }
     dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
-    LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, *mq, *mk1, *mk2, d);
+    LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, mq, mk1, mk2, d);
 }
 
 void attention_tc(const AttnArgs &a) {

@@ -26,6 +26,7 @@ struct Ctx {
     int rng_mode = 0;
     long long row_offset = 0;
     int sm_count = 148;
+    int device = -1;                  // the device ensure_device() found current; the library's caches belong to it
     int w_static = 0;                 // > 0: GEMM weights are model weights that do not change (split copies may be cached)
     unsigned long long h2d_bytes = 0, d2h_bytes = 0;   // bytes moved across PCIe by this library
     bool inited = false;
@@ -263,6 +264,9 @@ struct SampleArgs {
     int *hist; int *hist_len; int hist_stride;   // [Bn][hist_stride], [Bn]
     const double *uniforms;    // [Bn][Lc] pre-drawn uniforms in [0,1) (temp > 0); null = counter-based
     unsigned long long rng_seed = 0; long long rng_row0 = 0; int rng_level = 0;   // counter-based stream key
+    int rng_wrap = 0;          // > 0: rows b >= rng_wrap are the unconditional twins of rows b - rng_wrap (level 0 under CFG);
+                               // they draw on their sequence's key with a level of their own, so a sequence's draws do
+                               // not depend on how many sequences share the call
     int *out;                  // [Bn][out_stride] picks written at out_off + t
     int out_stride, out_off;
     float *blend_out;          // optional [Bn][Lc][V] copy of the logits actually sampled from

@@ -360,8 +360,8 @@ void gemm_h3(const GemmArgs &a) {
         // a fused QKV projection needs 128-column tiles (two heads each) and saves a whole pass over q and k
         if (qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && a.N % 128 == 0 && cost128 <= 2 * best) bn = 128;
     }
-    const CUtensorMap *mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), *mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
-    const CUtensorMap *mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), *mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
+    const CUtensorMap mx1 = tc_get_map_h16(x1, a.M, a.K, ldh, H3_BM), mx2 = tc_get_map_h16(x2, a.M, a.K, ldh, H3_BM);
+    const CUtensorMap mw1 = tc_get_map_h16(w1, a.N, a.K, a.K, bn), mw2 = tc_get_map_h16(w2, a.N, a.K, a.K, bn);
     // fp32 results leave through TMA stores when the rows keep 16-byte strides
     ep.tma_store = (!a.glu && !a.y_lo && (ep.ldy & 3) == 0 && !getenv("NCM_B200_NO_TMA_STORE")) ? 1 : 0;
     int tiles_n = (int)cdiv(a.N, bn);
@@ -396,7 +396,7 @@ void gemm_h3(const GemmArgs &a) {
     }
     TcEpi epf = ep;                                                // the call's own epilogue, for the reduce kernel
     if (ksplit > 1) { ep.bias = nullptr; ep.res = nullptr; ep.act = ACT_NONE; ep.y = part; ep.ldy = a.N; }
-    const CUtensorMap *my = !ep.tma_store ? mx1
+    const CUtensorMap my = !ep.tma_store ? mx1
                           : ksplit > 1 ? tc_get_map(part, (int64_t)ksplit * m_pad, a.N, a.N, 32, false)
                                        : tc_get_map(a.y, a.M, a.N, ep.ldy, 32, false);
     const int64_t items = tiles * ksplit;
@@ -409,7 +409,7 @@ void gemm_h3(const GemmArgs &a) {
         static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");                               \
         static bool set = false;                                                                                            \
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);        \
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);        \
     } while (0)
     // fused QKV projection: heads are 64 columns, a 128-column tile holds two, results leave as fp32 tiles
     const bool qkp = qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && bn == 128 && ep.tma_store && a.N % 128 == 0 && !a.res &&
@@ -419,7 +419,7 @@ void gemm_h3(const GemmArgs &a) {
         constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
         static bool set = false;
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute((k_gemm_h3<128, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, *mx1, *mx2, *mw1, *mw2, *my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);
     } else if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);
     else H3_LAUNCH(128);

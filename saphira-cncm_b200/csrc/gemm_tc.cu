@@ -9,8 +9,8 @@
 //            tcgen05.mma.kind::tf32 over each stage, tcgen05.commit frees the stage;
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (lane = output row), fuse bias /
 //            activation / gated product / residual, store fp32 rows.
-// Two CTAs fit one SM (shared memory and tensor-memory columns), so one tile's
-// epilogue overlaps the other's main loop. Every mbarrier wait is bounded: on a
+// One persistent CTA per SM with two tensor-memory accumulators, so one tile's
+// epilogue overlaps the next tile's main loop. Every mbarrier wait is bounded: on a
 // timeout the kernel records an error code and drains instead of spinning.
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -267,6 +267,11 @@ struct MapKeyHash {
     }
 };
 
+// Entries the tensor-map caches hold before they start over (ncmb_set_map_cache_limit; tests set it to 1 so that
+// every lookup of one launch evicts the previous one).
+static size_t g_map_cache_limit = 4096;
+static size_t tc_map_cache_limit() { return g_map_cache_limit; }
+
 static int tma_dtype_mode() {          // 1 (default): TMA rounds fp32 to tf32 while loading; 0: raw fp32 bits
     static int m = -1;
     if (m < 0) { const char *e = getenv("NCM_B200_TMA_TF32"); m = e ? atoi(e) : 1; }
@@ -275,13 +280,15 @@ static int tma_dtype_mode() {          // 1 (default): TMA rounds fp32 to tf32 w
 
 // 2-D map over a row-major [rows][K] fp32 matrix with row stride ld: box = 32 floats x box_rows.
 // round_tf32: let the TMA unit round each element to TF32 on the way into shared memory.
-const CUtensorMap *tc_get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
+// Returned by value: the cache may evict entries on a later lookup, so callers that fetch several maps for one
+// launch never hold pointers into it.
+CUtensorMap tc_get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     int dt = (round_tf32 && tma_dtype_mode()) ? 1 : 0;
     MapKey key{p, rows, ld, K, box_rows, dt};
     auto it = cache.find(key);
-    if (it != cache.end()) return &it->second;
-    if (cache.size() > 4096) cache.clear();
+    if (it != cache.end()) return it->second;
+    if (cache.size() > tc_map_cache_limit()) cache.clear();
     CUtensorMap tm;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
@@ -291,16 +298,17 @@ const CUtensorMap *tc_get_map(const float *p, int64_t rows, int K, int64_t ld, i
                              (void *)p, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) fatal("cuTensorMapEncodeTiled failed (%d) for [%lld][%d] ld %lld", (int)r, (long long)rows, K, (long long)ld);
-    return &cache.emplace(key, tm).first->second;
+    cache.emplace(key, tm);
+    return tm;
 }
 
 // 2-D map over a row-major [rows][K] fp16 matrix with row stride ld (elements): box = 64 halfs x box_rows
-const CUtensorMap *tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld, int box_rows) {
+CUtensorMap tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld, int box_rows) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
     MapKey key{p, rows, ld, K, box_rows, 2};
     auto it = cache.find(key);
-    if (it != cache.end()) return &it->second;
-    if (cache.size() > 4096) cache.clear();
+    if (it != cache.end()) return it->second;
+    if (cache.size() > tc_map_cache_limit()) cache.clear();
     CUtensorMap tm;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -310,8 +318,13 @@ const CUtensorMap *tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) fatal("cuTensorMapEncodeTiled (fp16) failed (%d) for [%lld][%d] ld %lld", (int)r, (long long)rows, K, (long long)ld);
-    return &cache.emplace(key, tm).first->second;
+    cache.emplace(key, tm);
+    return tm;
 }
+
+} // namespace ncmb
+extern "C" void ncmb_set_map_cache_limit(int entries) { ncmb::g_map_cache_limit = entries < 1 ? 1 : (size_t)entries; }
+namespace ncmb {
 
 int *tc_err_flag() {
     static int *d = nullptr;
@@ -402,11 +415,11 @@ void gemm_tc(const GemmArgs &a) {
     int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool x3 = ctx().gemm_mode >= 2;
     if (!x3) {
-        const CUtensorMap *ma = tc_get_map(a.x, a.M, a.K, ldx, TC_BM, true);
-        const CUtensorMap *mb = tc_get_map(a.W, a.N, a.K, a.K, 128, true);
+        const CUtensorMap ma = tc_get_map(a.x, a.M, a.K, ldx, TC_BM, true);
+        const CUtensorMap mb = tc_get_map(a.W, a.N, a.K, a.K, 128, true);
         ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                      4.0 * ((double)a.M * a.K + (double)a.N * a.K + (double)a.M * a.N));
-        launch_tc<128, 6, false>(a, ep, ma, mb, ma, mb);
+        launch_tc<128, 6, false>(a, ep, &ma, &mb, &ma, &mb);
         return;
     }
     // three-pass mode: split both operands; static weights are split once and cached
@@ -439,17 +452,17 @@ void gemm_tc(const GemmArgs &a) {
         split_tf32(a.W, a.K, whi, wlo, a.N, a.K);
     }
     if (!pre_split) split_tf32(a.x, ldx, (float *)xhi, (float *)xlo, a.M, a.K);
-    const CUtensorMap *ma = tc_get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), *mal = tc_get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
+    const CUtensorMap ma = tc_get_map(xhi, a.M, a.K, ldsplit, TC_BM, false), mal = tc_get_map(xlo, a.M, a.K, ldsplit, TC_BM, true);
     // 256-wide N tiles read a third less of the operands per MMA flop (from L2 and from shared memory);
     // they are used once the launch still fills every SM a few times over
     static const bool wide_ok = !getenv("NCM_B200_NO_BN256");
     const bool wide = wide_ok && a.N >= 256 && cdiv(a.N, 256) * cdiv(a.M, TC_BM) >= 2 * (int64_t)ctx().sm_count;
     const int bn = wide ? 256 : 128;
-    const CUtensorMap *mb = tc_get_map(whi, a.N, a.K, a.K, bn, false), *mbl = tc_get_map(wlo, a.N, a.K, a.K, bn, true);
+    const CUtensorMap mb = tc_get_map(whi, a.N, a.K, a.K, bn, false), mbl = tc_get_map(wlo, a.N, a.K, a.K, bn, true);
     ProfScope ps(NCMB_K_GEMM, 2.0 * (double)a.M * a.N * a.K,
                  4.0 * (2.0 * (double)a.M * a.K + 2.0 * (double)a.N * a.K + (double)a.M * a.N));
-    if (wide) launch_tc<256, 2, true>(a, ep, ma, mb, mal, mbl);
-    else launch_tc<128, 3, true>(a, ep, ma, mb, mal, mbl);
+    if (wide) launch_tc<256, 2, true>(a, ep, &ma, &mb, &mal, &mbl);
+    else launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
 }
 
 
@@ -461,6 +474,8 @@ void gemm_tc(const GemmArgs &a) {
 constexpr size_t NOALLOC_SCRATCH_FLOATS = (size_t)8 << 20;           // 32 MiB, resident on every GPU that loads the library
 static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_SCRATCH_FLOATS];
 static __device__ int g_noalloc_err;
+static float *g_noalloc_scratch_of[64] = {nullptr};      // device addresses of the two symbols, per device ordinal
+static int *g_noalloc_err_of[64] = {nullptr};
 
 static void encode_map_now(CUtensorMap *tm, const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32) {
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -486,8 +501,12 @@ static void encode_map_now(CUtensorMap *tm, const float *p, int64_t rows, int K,
 //
 // Scratch: the split operands (2*batch*K + 2*M*K floats) live in a 32 MiB array
 // compiled into the library. Sizes beyond it (or shapes the tensor-core kernel does
-// not take: batch < 64, M < 32, K < 32, K % 4 != 0, pointers not 16-byte aligned)
-// are refused with -1 and a message; nothing is launched then. Returns 0 on success.
+// not take: batch <= 16, M < 32, K < 32, K % 4 != 0, pointers not 16-byte aligned)
+// are refused with -1 and a message; nothing is launched then. Returns 0 once the
+// kernels are queued; whether a bounded wait inside them ran out is only known after
+// ncmb_linear_fwd_noalloc_check(), which synchronises and reads the kernel's status word.
+// The library keeps its per-process state (SM count, kernel attributes) for the device
+// that was current at its first call; a call with another device current is refused.
 // The first call on each device looks up the array's device address and clears its
 // error word; make that first call outside any stream capture. Every call reuses
 // the same array and overwrites all of the part it reads, so earlier contents never
@@ -497,11 +516,15 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
                                        int64_t batch, int M, int K) {
     using namespace ncmb;
     ensure_device();
-    static float *scratch_of[64] = {nullptr};
-    static int *err_of[64] = {nullptr};
+    float **scratch_of = g_noalloc_scratch_of;
+    int **err_of = g_noalloc_err_of;
     int dev = 0;
     CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) { fprintf(stderr, "ncmb_linear_fwd_noalloc: device index %d out of range\n", dev); return -1; }
+    if (dev != ctx().device) {
+        fprintf(stderr, "ncmb_linear_fwd_noalloc: device %d is current but the library was set up on device %d\n", dev, ctx().device);
+        return -1;
+    }
     if (!scratch_of[dev]) {
         // set-up, once per device, with that device current: the symbol name is only a
         // host-side handle; kernels must be given the address it resolves to on the device
@@ -520,7 +543,7 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     a.x = x; a.ldx = K; a.W = W; a.bias = b; a.y = y; a.ldy = M; a.M = batch; a.N = M; a.K = K;
     if (!gemm_tc_supported(a)) {
         fprintf(stderr, "ncmb_linear_fwd_noalloc: shape [%lld x %d] * [%d x %d] not taken by the tensor-core kernel "
-                        "(need batch >= 64, M >= 32, K >= 32, K %% 4 == 0, 16-byte aligned pointers)\n",
+                        "(need batch > 16, M >= 32, K >= 32, K %% 4 == 0, 16-byte aligned pointers)\n",
                 (long long)batch, K, M, K);
         return -1;
     }
@@ -541,4 +564,20 @@ extern "C" int ncmb_linear_fwd_noalloc(const float *x, const float *W, const flo
     ep.err = err_of[dev];
     launch_tc<128, 3, true>(a, ep, &ma, &mb, &mal, &mbl);
     return 0;
+}
+
+// Status of the allocation-free entry point on the current device: waits for the stream, then returns and clears the
+// word its kernels write when a bounded barrier wait runs out (0 = every call so far completed; -1 = the entry point
+// has not been set up on this device). Allocates nothing: a 4-byte copy through the address looked up at set-up.
+extern "C" int ncmb_linear_fwd_noalloc_check(void) {
+    using namespace ncmb;
+    ensure_device();
+    int dev = 0;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !g_noalloc_err_of[dev]) return -1;
+    int v = 0;
+    CUDA_CHECK(cudaMemcpyAsync(&v, g_noalloc_err_of[dev], sizeof(int), cudaMemcpyDeviceToHost, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    if (v) CUDA_CHECK(cudaMemsetAsync(g_noalloc_err_of[dev], 0, sizeof(int), stream()));
+    return v;
 }

@@ -549,7 +549,7 @@ static void gen_l0(NCPGen *g) {
         s.allow_dev = g->allow_d; s.cnt = penal ? g->cnt0_d : nullptr; s.cnt_stride = g->Vmax;
         s.hist = penal ? g->hist_d : nullptr; s.hist_len = penal ? g->hist_len_d + Bm : nullptr; s.hist_stride = g->total + 64;
         s.uniforms = g->uni_d ? g->uni_d + g->uni_off : nullptr;
-        s.rng_seed = g->seed; s.rng_row0 = ctx().row_offset; s.rng_level = 0;
+        s.rng_seed = g->seed; s.rng_row0 = ctx().row_offset; s.rng_level = 0; s.rng_wrap = Bm > B ? B : 0;
         s.out = g->l0tmp_d; s.out_stride = l0len; s.out_off = 0;
         s.blend_out = g->blend; s.scratch = g->samp_scr; s.picks_bound = g->total;
         sample_rows(s);

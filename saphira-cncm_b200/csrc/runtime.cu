@@ -47,6 +47,7 @@ void ensure_device() {
     if (p.major < 10)
         fatal("device %s is sm_%d%d; this build targets sm_100a only", p.name, p.major, p.minor);
     c.sm_count = p.multiProcessorCount;
+    c.device = dev;
     const char *gm = getenv("NCM_B200_GEMM");
     if (gm) c.gemm_mode = atoi(gm);
     const char *rm = getenv("NCM_B200_RNG");
@@ -574,6 +575,13 @@ int ncmb_gemm_tc_check(void) { ensure_device(); return gemm_tc_check(); }
 void ncmb_set_rng_mode(int mode) { ensure_device(); ctx().rng_mode = mode; }
 void ncmb_set_row_offset(long long off) { ctx().row_offset = off; }
 long long ncmb_launch_count(void) { return ctx().launches; }
+void ncmb_mem_info(unsigned long long *free_bytes, unsigned long long *total_bytes) {
+    ensure_device();
+    size_t f = 0, t = 0;
+    CUDA_CHECK(cudaMemGetInfo(&f, &t));
+    if (free_bytes) *free_bytes = f;
+    if (total_bytes) *total_bytes = t;
+}
 void ncmb_copy_bytes(unsigned long long *h2d, unsigned long long *d2h) {
     if (h2d) *h2d = ctx().h2d_bytes;
     if (d2h) *d2h = ctx().d2h_bytes;

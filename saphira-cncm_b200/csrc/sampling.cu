@@ -49,6 +49,12 @@ __device__ __forceinline__ double counter_uniform(unsigned long long seed, long 
     return (double)(z >> 11) * (1.0 / 9007199254740992.0);
 }
 
+// the draw of model row b at position t: keyed by the sequence's global index, never by the row's place in the call
+__device__ __forceinline__ double counter_uniform_row(const SampleArgs &a, int b, int t) {
+    const bool twin = a.rng_wrap > 0 && b >= a.rng_wrap;
+    return counter_uniform(a.rng_seed, a.rng_row0 + (twin ? b - a.rng_wrap : b), a.rng_level + (twin ? 64 : 0), t);
+}
+
 __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
     const SampleArgs &a = sd.a;
     extern __shared__ __align__(16) unsigned char smraw[];
@@ -253,7 +259,7 @@ __global__ void __launch_bounds__(SM_THREADS) k_sample(SampleDev sd) {
                 den = 0;
                 for (int r = 0; r < nkeep; r++) den += probs[r];
                 double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
-                                        : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
+                                        : counter_uniform_row(a, b, t);
                 double u = u01 * den, acc = 0;
                 int pr = nkeep - 1;
                 for (int r = 0; r < nkeep; r++) { acc += probs[r]; if (u <= acc) { pr = r; break; } }
@@ -474,7 +480,7 @@ __global__ void __launch_bounds__(SC_MAXC) k_sample_seq(SampleCand sc) {
                 probs[r] = cum;                          // from here on: inclusive running sums
             }
             const double u01 = a.uniforms ? a.uniforms[(size_t)b * Lc + t]
-                                          : counter_uniform(a.rng_seed, a.rng_row0 + b, a.rng_level, t);
+                                          : counter_uniform_row(a, b, t);
             s_den = u01 * cum;
             s_pick = nkeep;                              // handed to the search below
         }

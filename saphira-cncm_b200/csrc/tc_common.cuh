@@ -112,8 +112,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 
 // host side (gemm_tc.cu): cached 2-D tensor maps over row-major fp32 matrices (box = 32 floats x box_rows,
 // 128-byte swizzle), and the device error word the bounded waits report into
-const CUtensorMap *tc_get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32);
-const CUtensorMap *tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld, int box_rows);
+CUtensorMap tc_get_map(const float *p, int64_t rows, int K, int64_t ld, int box_rows, bool round_tf32);
+CUtensorMap tc_get_map_h16(const void *p, int64_t rows, int K, int64_t ld, int box_rows);
 int *tc_err_flag();
 
 } // namespace ncmb

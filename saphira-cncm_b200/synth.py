@@ -506,9 +506,11 @@ class LMSpec:
 
 
 def _round_bf16(a: np.ndarray) -> np.ndarray:
-    u = a.astype(np.float32).view(np.uint32).astype(np.uint64)
-    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    return u.astype(np.uint32).view(np.float32)
+    """round-to-nearest-even to bf16, kept as float32 (finite weights: the 32-bit add cannot wrap)"""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).copy()
+    u += np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))
+    u &= np.uint32(0xFFFF0000)
+    return u.view(np.float32)
 
 
 def lm_tensors(s: LMSpec, seed: int) -> "dict[str, np.ndarray]":

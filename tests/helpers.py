@@ -264,3 +264,27 @@ def same_bits(a, b):
     if a.shape != b.shape or a.dtype != b.dtype:
         return False
     return a.tobytes() == b.tobytes()
+
+
+def top2_gap(row):
+    top = np.partition(np.asarray(row, np.float64), -2)[-2:]
+    return abs(top[1] - top[0]) / max(abs(top[1]), 1e-30)
+
+
+def decoded_tokens_equal_or_near_tie(gm, om, codes, spec, tag):
+    """token ids from the library's decoder against the oracle's on the same codes; a differing position is
+    accepted only when the oracle's decoder logits there have a top-2 gap within 1e-5 relative"""
+    tok_g = gm.decode_tokens(codes, spec.L)
+    tok_o = om.decode_tokens(codes)
+    diff = np.argwhere(tok_g != tok_o)
+    ties = 0
+    if len(diff):
+        zh = om.idx_to_zhats(codes, len(spec.levels))
+        lg = om.decode(zh[-1])
+        for b, t in diff:
+            gap = top2_gap(lg[b, t])
+            assert gap <= 1e-5, f"{tag}: token ({b},{t}) differs, oracle top-2 gap {gap:.2e}"
+            assert tok_g[b, t] in np.argsort(lg[b, t])[-2:]
+            ties += 1
+    print(f"{tag}: {tok_g.size} decoded tokens, {ties} near-ties")
+    return tok_g

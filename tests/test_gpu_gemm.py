@@ -50,3 +50,27 @@ def test_linear_fwd_on_every_engine(cuda, shape):
         y = cuda.to_host(yd, (M, N))
         err = np.abs(y - want) / row_scale
         assert err.max() <= rel, f"engine {mode}: {err.max():.3e} of the row scale"
+
+
+def test_descriptor_cache_eviction_between_the_lookups_of_one_launch(cuda):
+    """The TMA descriptor caches start over when full. With the limit at one entry every lookup of a launch evicts
+    the one before it (a GEMM fetches four or five descriptors, attention three); results must not change."""
+    M, N, K = 300, 256, 192
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    xd, Wd = cuda.to_backend(x), cuda.to_backend(W)
+    yd = cuda.alloc(M * N)
+    try:
+        for mode in (2, 3):
+            cuda.ncmb_set_gemm_mode(mode)
+            cuda.ncmb_set_map_cache_limit(4096)
+            cuda.linear_fwd(xd, Wd, None, yd, M, N, K)
+            want = cuda.to_host(yd, (M, N))
+            cuda.ncmb_set_map_cache_limit(1)
+            for _ in range(3):
+                cuda.linear_fwd(xd, Wd, None, yd, M, N, K)
+                assert np.array_equal(cuda.to_host(yd, (M, N)), want), mode
+            assert cuda.ncmb_gemm_tc_check() == 0
+    finally:
+        cuda.ncmb_set_map_cache_limit(4096)

@@ -54,6 +54,12 @@ def test_shard_plans_and_max_reduction_with_two_gloo_ranks(tmp_path):
     assert [p["row_offset"] for p in plans] == [0, 256]
     assert all(p["rows"] == 256 and p["global_rows"] == 512 for p in plans)
     assert len({p["prefix_seed"] for p in plans}) == 2
+    # every rank draws from the counter-based stream keyed by the global row, so sharding does not change a row's codes
+    assert all(p["rng_mode"] == 1 for p in plans)
+    import numpy as np
+    import bench
+    a = np.arange(12, dtype=np.int32).reshape(3, 4)
+    assert bench.token_checksum(a) == bench.token_checksum(a.copy()) != bench.token_checksum(a[::-1])
     assert out["max"] == [2.0, 10.0]
 
 
