@@ -130,6 +130,13 @@ void weights_free(WeightStore *ws);
 Tensor *weights_get(WeightStore *ws, const char *name);   /* NULL if missing */
 int  config_load(NCMConfig *c, const char *path);         /* 0 / -1 */
 void *backend_to_host(const float *d, size_t nbytes);     /* malloc'ed host copy */
+/* src/ncm.h:262-264 (tensor.c:375-397): rows of token ids in an "NCMT" file (magic, u64 row count, u64 row
+ * length, int32 ids) -- what the data-preparation commands vq-encode / vq-recon read before they call
+ * vqvae_encode_z and vq_z_to_idx. Host memory; max_rows > 0 keeps the first max_rows rows. NULL with a message
+ * on a missing file, a wrong magic or a short file. */
+typedef struct { int *rows; int n_rows, row_len; } TrainData;
+TrainData *train_data_load(const char *path, int max_rows);
+void train_data_free(TrainData *d);
 
 /* ---------------------------------------------------------------- layer kernels
  * src/ncm.h:146-199 (kernels.c). fp32 in, fp32 out, out-parameter last. */

@@ -44,7 +44,7 @@ def build_ref(ref_dir: "str | None" = None) -> "str | None":
     subprocess.check_call(["make", "-s", "-C", HERE, "ref", f"REF={ref_dir}"])
     # the reference's command-line front end linked against the GPU library (needs that library built)
     if os.path.exists(os.path.join(HERE, "..", "saphira-cncm_b200", "libncm_b200.so")):
-        subprocess.check_call(["make", "-s", "-C", HERE, "cli", f"REF={ref_dir}"])
+        subprocess.check_call(["make", "-s", "-C", HERE, "cli", "ktest", f"REF={ref_dir}"])
     return REF_LIB
 
 
@@ -243,6 +243,61 @@ def l2sq(a, b):
     d = np.empty((a.shape[0], b.shape[0]), np.float32)
     lib().orc_l2sq(_p(a), _p(b), _p(d), a.shape[0], b.shape[0], a.shape[1])
     return d
+
+
+# Data-movement and element-wise kernels of the public kernel API: index arithmetic restated in numpy
+# (fp32 throughout, one rounding per element like the reference's scalar loops).
+
+def embedding(W, idx):
+    """y[i, :] = W[idx[i], :]  (reference src/kernels.c:67-74)"""
+    return _f(W)[_i(idx)].copy()
+
+
+def rope_gqa(q, k, cs, sn):
+    """q [B,H,T,hd], k [B,K,T,hd] rotated with the same [T,hd] tables, row r of either using table row r % T
+    (reference src/kernels.c:299-309 on rope_one_exact, :270-283)."""
+    T, hd = _f(cs).shape
+    return rope(q, cs, sn, T), rope(k, cs, sn, T)
+
+
+def heads_transpose(x, T, H, hd):
+    """[T][H*hd] -> [H][T][hd]  (reference src/kernels.c:322-332)"""
+    return np.ascontiguousarray(_f(x).reshape(T, H, hd).transpose(1, 0, 2))
+
+
+def heads_transpose_b(x, B, T, H, hd):
+    """[B][T][H*hd] -> [B][H][T][hd]  (reference src/kernels.c:345-357)"""
+    return np.ascontiguousarray(_f(x).reshape(B, T, H, hd).transpose(0, 2, 1, 3))
+
+
+def add(a, b):
+    """reference src/kernels.c:843-849"""
+    return _f(a) + _f(b)
+
+
+def mul(a, b):
+    """reference src/kernels.c:859-866"""
+    return _f(a) * _f(b)
+
+
+def scale(x, s):
+    """y = x * s with s a float32 (reference src/kernels.c:868-874)"""
+    return _f(x) * np.float32(s)
+
+
+def qkv_split(x, B, T, C_, H, hd, K, rep):
+    """[B,T,C+2*K*hd] -> q, k, v [B,H,T,hd]; query head h reads kv head h // rep (reference src/kernels.c:913-926)"""
+    x = _f(x).reshape(B, T, C_ + 2 * K * hd)
+    q = x[:, :, :H * hd].reshape(B, T, H, hd).transpose(0, 2, 1, 3)
+    kk = x[:, :, C_:C_ + K * hd].reshape(B, T, K, hd).transpose(0, 2, 1, 3)
+    vv = x[:, :, C_ + K * hd:].reshape(B, T, K, hd).transpose(0, 2, 1, 3)
+    sel = np.arange(H) // rep
+    return np.ascontiguousarray(q), np.ascontiguousarray(kk[:, sel]), np.ascontiguousarray(vv[:, sel])
+
+
+def head_merge(ctx, B, T, C_, H, hd):
+    """[B,H,T,hd] -> [B,T,C]  (reference src/kernels.c:928-936)"""
+    return np.ascontiguousarray(_f(ctx).reshape(B, H, T, hd).transpose(0, 2, 1, 3).reshape(B, T, C_))
 
 
 def sample_topkp(logits, temp, top_k, top_p, rng_state: int):

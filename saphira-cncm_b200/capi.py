@@ -58,6 +58,8 @@ _SIGS = {
     "ckpt_load_weights_only": (_I, [C.c_char_p, C.POINTER(WeightStore), C.c_char_p, _SZ]),
     "weights_get": (_P, [C.POINTER(WeightStore), C.c_char_p]),
     "config_load": (_I, [_P, C.c_char_p]),
+    "train_data_load": (_P, [C.c_char_p, _I]),
+    "train_data_free": (None, [_P]),
     # layer kernels (src/ncm.h:146-199)
     "linear_fwd": (None, [_P, _P, _P, _P, _I64, _I, _I]),
     "embedding_fwd": (None, [_P, _P, _P, _I64, _I]),

@@ -1,6 +1,6 @@
 /* Link-time stand-ins for the entry points the reference's command-line front end (src/main.c) references but
  * that are not part of the inference library: trainers, gradient checks, checkpoint inspection, weight saving,
- * dead-code revival, the training-row reader and the live viewers (src/ncm.h:233, 263-265, 324, 351-381,
+ * dead-code revival and the live viewers (src/ncm.h:233, 265, 324, 351-381,
  * 402-414, 463). With them, the reference's main.c + tok.c + tok_tables.c link against libncm_b200.so and its
  * gen / infer / eval-* / sudoku-stream / gpt2-* / qwen-* commands run on the GPU; a command that needs one of
  * these says so and fails. Parameters are left unspecified on purpose (C11): nothing here reads them.
@@ -28,8 +28,6 @@ int qwen_cmd_taped() { return absent("qwen-taped"); }
 int ckpt_info() { return absent("ckpt-info"); }
 int weights_save() { absent("weights_save"); return -1; }
 int vq_revive_dead() { absent("vq-revive"); return -1; }
-void *train_data_load() { absent("the .nctrain reader (vq-encode / vq-recon / vq-revive)"); return NULL; }
-void train_data_free() {}
 
 /* live viewers: report "could not open", which the commands treat as "run without a viewer" */
 int viewer_open() { return -1; }

@@ -366,6 +366,44 @@ void ncmb_store_adopt_slab(WeightStore *ws, void *slab) {
     slab_of_store()[ws->items] = slab;
 }
 
+// Rows of token ids from an "NCMT" file (reference train_data_load src/tensor.c:375-397): a 20-byte header (magic,
+// u64 rows, u64 row length) and rows * row_len little-endian int32. Host-only; the file's size is checked against the
+// header before anything is allocated.
+TrainData *train_data_load(const char *path, int max_rows) {
+    FILE *f = fopen(path, "rb");
+    if (!f) { fprintf(stderr, "cannot open %s\n", path); return nullptr; }
+    struct __attribute__((packed)) { char magic[4]; uint64_t rows, row_len; } hd;
+    if (fread(&hd, 1, sizeof(hd), f) != sizeof(hd) || memcmp(hd.magic, "NCMT", 4) != 0) {
+        fprintf(stderr, "%s: bad magic\n", path);
+        fclose(f);
+        return nullptr;
+    }
+    uint64_t rows = hd.rows;
+    if (max_rows > 0 && rows > (uint64_t)max_rows) rows = (uint64_t)max_rows;
+    fseek(f, 0, SEEK_END);
+    const uint64_t have = (uint64_t)ftell(f) - sizeof(hd);
+    if (hd.row_len == 0 || hd.row_len > 0x7fffffffu || rows > 0x7fffffffu || rows * hd.row_len * sizeof(int) > have) {
+        fprintf(stderr, "%s: short read\n", path);
+        fclose(f);
+        return nullptr;
+    }
+    TrainData *d = (TrainData *)calloc(1, sizeof(TrainData));
+    const size_t n = (size_t)(rows * hd.row_len);
+    int *ids = (int *)malloc((n ? n : 1) * sizeof(int));
+    if (!d || !ids) fatal("oom reading %s", path);
+    fseek(f, (long)sizeof(hd), SEEK_SET);
+    const size_t got = fread(ids, sizeof(int), n, f);
+    fclose(f);
+    if (got != n) { fprintf(stderr, "%s: short read\n", path); free(ids); free(d); return nullptr; }
+    d->rows = ids; d->n_rows = (int)rows; d->row_len = (int)hd.row_len;
+    return d;
+}
+void train_data_free(TrainData *d) {
+    if (!d) return;
+    free(d->rows);
+    free(d);
+}
+
 // 1 = NCK1 checkpoint, 0 = NCM1 weights, -1 = neither / unreadable (reference ckpt_probe src/ckpt.c:67-77)
 int ckpt_probe(const char *path) {
     FILE *f = fopen(path, "rb");

@@ -83,4 +83,19 @@ def kernel_inputs():
     d["li_x"] = f(2, 4, 9)
     d["l2_a"], d["l2_b"] = f(16, 32), f(8, 32)
     d["smp"] = f(6, 50)
+    # data-movement / element-wise kernels (drawn after everything above, so the earlier inputs keep their values)
+    d["emb_W"] = f(37, 24)
+    d["emb_idx"] = r.integers(0, 37, size=19).astype(np.int32)
+    d["rg_q"], d["rg_k"] = f(2, 6, 5, 16), f(2, 2, 5, 16)          # 6 query heads on 2 kv heads
+    d["rg_cos"], d["rg_sin"] = f(5, 16), f(5, 16)
+    d["ht_x"] = f(7, 3 * 8)                                        # [T][H*hd]
+    d["htb_x"] = f(2, 7, 3 * 8)                                    # [B][T][H*hd]
+    d["ew_a"], d["ew_b"] = f(1000), f(1000)
+    d["qs_x"] = f(2, 5, 32 + 2 * 2 * 8)                            # [B][T][C + 2*K*hd], shapes in QS below
+    d["hm_x"] = f(2, 3, 5, 8)
     return d
+
+
+# qkv_split_fwd / head_merge_fwd shapes: B, T, C, H, hd, kv heads, query heads per kv head
+QS = dict(B=2, T=5, C=32, H=4, hd=8, K=2, rep=2)
+HM = dict(B=2, T=5, C=24, H=3, hd=8)

@@ -76,6 +76,33 @@ def capi_kernels(ref, out):
     ref.interpolate_linear_fwd(B(d["li_x"][:, :, :1].copy()), y, 2, 4, 1, 8); out["k_lin_interp1"] = H(y, (2, 4, 8))
     dd = ref.alloc(16 * 8)
     ref.rowwise_l2sq(B(d["l2_a"]), B(d["l2_b"]), dd, 16, 8, 32); out["k_l2sq"] = H(dd, (16, 8))
+    # data movement and element-wise kernels (src/ncm.h:149, 161-165, 184-190)
+    W, idx = d["emb_W"], d["emb_idx"]
+    y = ref.alloc(idx.size * W.shape[1])
+    ref.embedding_fwd(B(W), B(idx), y, idx.size, W.shape[1]); out["k_embedding"] = H(y, (idx.size, W.shape[1]))
+    q, k = B(d["rg_q"]), B(d["rg_k"])
+    ref.rope_apply_gqa(q, k, B(d["rg_cos"]), B(d["rg_sin"]), 2, 6, 2, 5, 16)
+    out["k_rope_gqa_q"], out["k_rope_gqa_k"] = H(q, d["rg_q"].shape), H(k, d["rg_k"].shape)
+    y = ref.alloc(d["htb_x"].size)
+    ref.heads_transpose_fwd(B(d["ht_x"]), y, 7, 3, 8); out["k_heads_t"] = H(y, (3, 7, 8))
+    ref.heads_transpose_fwd_b(B(d["htb_x"]), y, 2, 7, 3, 8); out["k_heads_tb"] = H(y, (2, 3, 7, 8))
+    a, b = d["ew_a"], d["ew_b"]
+    y = ref.alloc(a.size)
+    ref.add_fwd(B(a), B(b), y, a.size); out["k_add"] = H(y, a.shape)
+    ref.mul_fwd(B(a), B(b), y, a.size); out["k_mul"] = H(y, a.shape)
+    ref.scale_fwd(B(a), 0.37, y, a.size); out["k_scale"] = H(y, a.shape)
+    acc = B(a)
+    ref.add_inplace_fwd(acc, B(b), a.size); out["k_add_inplace"] = H(acc, a.shape)
+    s = cases.QS
+    n = s["B"] * s["H"] * s["T"] * s["hd"]
+    qq, kk, vv = ref.alloc(n), ref.alloc(n), ref.alloc(n)
+    ref.qkv_split_fwd(B(d["qs_x"]), qq, kk, vv, s["B"], s["T"], s["C"], s["H"], s["hd"], s["K"], s["rep"])
+    shp = (s["B"], s["H"], s["T"], s["hd"])
+    out["k_qkv_q"], out["k_qkv_k"], out["k_qkv_v"] = H(qq, shp), H(kk, shp), H(vv, shp)
+    s = cases.HM
+    y = ref.alloc(s["B"] * s["T"] * s["C"])
+    ref.head_merge_fwd(B(d["hm_x"]), y, s["B"], s["T"], s["C"], s["H"], s["hd"])
+    out["k_head_merge"] = H(y, (s["B"], s["T"], s["C"]))
     # sampling: one shared stream across six rows and three settings
     picks = []
     st = C.c_ulonglong(0x1234ABCD)
@@ -187,6 +214,17 @@ def orc_kernels(out):
     out["k_lin_interp"] = orc.interp_linear(d["li_x"], 32)
     out["k_lin_interp1"] = orc.interp_linear(d["li_x"][:, :, :1].copy(), 8)
     out["k_l2sq"] = orc.l2sq(d["l2_a"], d["l2_b"])
+    out["k_embedding"] = orc.embedding(d["emb_W"], d["emb_idx"])
+    out["k_rope_gqa_q"], out["k_rope_gqa_k"] = orc.rope_gqa(d["rg_q"], d["rg_k"], d["rg_cos"], d["rg_sin"])
+    out["k_heads_t"] = orc.heads_transpose(d["ht_x"], 7, 3, 8)
+    out["k_heads_tb"] = orc.heads_transpose_b(d["htb_x"], 2, 7, 3, 8)
+    out["k_add"], out["k_mul"] = orc.add(d["ew_a"], d["ew_b"]), orc.mul(d["ew_a"], d["ew_b"])
+    out["k_scale"] = orc.scale(d["ew_a"], 0.37)
+    out["k_add_inplace"] = orc.add(d["ew_a"], d["ew_b"])
+    s = cases.QS
+    out["k_qkv_q"], out["k_qkv_k"], out["k_qkv_v"] = orc.qkv_split(d["qs_x"], s["B"], s["T"], s["C"], s["H"], s["hd"], s["K"], s["rep"])
+    s = cases.HM
+    out["k_head_merge"] = orc.head_merge(d["hm_x"], s["B"], s["T"], s["C"], s["H"], s["hd"])
     picks, st = [], 0x1234ABCD
     for (t, tk, tp) in ((0.0, 0, 1.0), (0.8, 5, 0.9), (1.0, 0, 0.6), (0.7, 50, 1.0)):
         for r in range(d["smp"].shape[0]):

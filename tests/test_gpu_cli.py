@@ -143,3 +143,88 @@ def test_decoder_lm_commands(both, kind):
     fg = dict(kv.split("=") for kv in got[1].split())
     assert fg["docs"] == fw["docs"] and fg["tokens"] == fw["tokens"] and int(fw["tokens"]) > 50, (got[1], want[1])
     assert abs(float(fg["nll"]) - float(fw["nll"])) < 1e-4, (got[1], want[1])
+
+
+def _write_nctrain(path, rows):
+    import struct
+    rows = np.ascontiguousarray(rows, np.int32)
+    with open(path, "wb") as f:
+        f.write(b"NCMT" + struct.pack("<QQ", rows.shape[0], rows.shape[1]))
+        f.write(rows.tobytes())
+
+
+def _grid_model(tmp, n, name):
+    """an n x n board in the reference's framing: wrap | n cells (sep n cells) x (n-1) | wrap, ids 0..11"""
+    import synth
+    T = n * n + (n - 1) + 2
+    spec = dataclasses.replace(synth.spec_c1(ladder=(1, 3, T)), name=name, prefix_len=T)
+    conf, w = synth.write_ncp(spec, tmp)
+    rng = np.random.default_rng(5)
+    rows = []
+    for _ in range(5):
+        cells = rng.integers(1, 10, size=(n, n)) * (rng.random((n, n)) < 0.6)
+        ids = [11]
+        for r in range(n):
+            ids += [int(v) for v in cells[r]]
+            if r < n - 1:
+                ids.append(10)
+        ids.append(11)
+        rows.append(ids)
+    return spec, conf, w, rows
+
+
+def test_eval_magic_records(both):
+    spec, conf, w, rows = _grid_model(both, 3, "cli_magic")
+    base = ["--conf", conf, "--weights", w, "--asset-dir", both]
+    inp, refs = os.path.join(both, "magic_inputs.txt"), os.path.join(both, "magic_refs.txt")
+    with open(inp, "w") as f, open(refs, "w") as g:
+        for r in rows:
+            f.write(" ".join(map(str, r)) + "\n")
+            g.write("".join(str(v) if v else "." for v in r if v < 10)[:9].ljust(9, ".") + "\n")
+    outs = {}
+    for tag, exe in (("cpu", CPU), ("gpu", GPU)):
+        jl = os.path.join(both, f"magic_{tag}.jsonl")
+        rc, out, err = _run(exe, ["eval-magic"] + base + ["--inputs", inp, "--refs", refs, "--size", "3", "--jsonl", jl], both)
+        assert rc == 0, err
+        recs = [json.loads(ln) for ln in open(jl)]
+        for r in recs:
+            r.pop("ms")
+        outs[tag] = (out, recs)
+    assert outs["gpu"][0] == outs["cpu"][0] and "solved" in outs["cpu"][0]
+    assert outs["gpu"][1] == outs["cpu"][1] and len(outs["cpu"][1]) == len(rows)
+
+
+def test_vq_encode_and_vq_recon_on_training_rows(both):
+    """The two data-preparation commands: rows of ids from NCMT files through the encoder and the quantizer
+    (vq-encode writes [prefix | codes] rows) and back through the decoder (vq-recon writes one board per line)."""
+    # vq-recon wants a context of n*n + n - 1 ids: 11 for a 3 x 3 grid
+    import synth
+    spec = dataclasses.replace(synth.spec_c1(ladder=(1, 3, 11)), name="cli_vq", prefix_len=7)
+    conf, w = synth.write_ncp(spec, both)
+    rng = np.random.default_rng(9)
+    nrows = 37                                             # more than one batch of 32
+    sol = rng.integers(0, 12, size=(nrows, 11))
+    pre = rng.integers(0, 12, size=(nrows, 7))
+    ps, pp = os.path.join(both, "sol.nctrain"), os.path.join(both, "pre.nctrain")
+    _write_nctrain(ps, sol)
+    _write_nctrain(pp, pre)
+    base = ["--conf", conf, "--weights", w]
+    res = {}
+    for tag, exe in (("cpu", CPU), ("gpu", GPU)):
+        oe, orc_ = os.path.join(both, f"enc_{tag}.nctrain"), os.path.join(both, f"recon_{tag}.txt")
+        rc, out, err = _run(exe, ["vq-encode"] + base + ["--prefix", pp, "--sol", ps, "--out", oe], both)
+        assert rc == 0, err
+        rc2, out2, err2 = _run(exe, ["vq-recon"] + base + ["--sol", ps, "--out", orc_, "--max-rows", "35"], both)
+        assert rc2 == 0, err2
+        res[tag] = (open(oe, "rb").read(), out.splitlines()[-1], open(orc_).read(), out2.splitlines()[-1])
+    assert res["gpu"][0] == res["cpu"][0]                  # [prefix | codes] rows: bytes equal
+    assert len(res["cpu"][0]) == 20 + nrows * (7 + 15) * 4
+    assert res["gpu"][1] == res["cpu"][1] and res["cpu"][1].startswith("[vq-encode] 37 rows")
+    assert res["gpu"][2] == res["cpu"][2] and len(res["cpu"][2].splitlines()) == 35
+    assert res["gpu"][3] == res["cpu"][3] and "id_match" in res["cpu"][3]
+    # a cut file and a wrong magic are refused by the reader, with the reference's messages
+    bad = os.path.join(both, "cut.nctrain")
+    open(bad, "wb").write(open(ps, "rb").read()[:200])
+    for exe in (CPU, GPU):
+        rc, out, err = _run(exe, ["vq-recon"] + base + ["--sol", bad, "--out", os.path.join(both, "x.txt")], both)
+        assert rc == 1 and "short read" in err
