@@ -735,6 +735,75 @@ def other_workloads(lib, args):
     return out
 
 
+def run_box_arm(args):
+    """Config 5 at its stated size: 65 536 independent sequences (strong scaling: the total is fixed and split over
+    the ranks), each rank calling ncp_generate + ncmb_decode_tokens through the host API. A rank's share does not fit
+    the GPU in one pass; the library runs it as waves of rows. Timed with the wall clock around the calls (each wave
+    ends in a device-to-host copy, so wall time is device time plus the host's part), max over ranks."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = capi.NcmLib(os.path.join(ROOT, "saphira-cncm_b200", "libncm_b200.so"))
+    stream = torch.cuda.current_stream()
+    lib.ncmb_set_stream(C.c_void_p(stream.cuda_stream))
+    spec, _ = workload("c5")
+    total = args.batch or 65536
+    B = total // world
+    kw = gen_kwargs(spec)
+    tmp = tempfile.TemporaryDirectory()
+    conf, w = synth.write_ncp(spec, tmp.name)
+    model = capi.NcpModel(lib, conf, w, arena_mb=64)
+    os.remove(w)
+    prefix = synth.ncp_prefixes(spec, B, 1000 + rank)
+    lib.ncmb_set_rng_mode(1)
+    lib.ncmb_set_row_offset(rank * B)
+    allow = kw.get("allow")
+    warm = synth.ncp_prefixes(spec, 64, 5)
+    model.decode_tokens(model.generate(warm, seed=1, **kw), spec.L)          # kernels loaded, weights converted
+    tokens = np.zeros((B, spec.L), np.int32)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    n0 = lib.ncmb_launch_count()
+    with ClockSampler(local) as clk:
+        t0 = time.perf_counter()
+        codes = model.generate(prefix, seed=7, **kw)
+        for r0 in range(0, B, 4096):
+            tokens[r0:r0 + 4096] = model.decode_tokens(codes[r0:r0 + 4096], spec.L)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    launches = lib.ncmb_launch_count() - n0
+    (dt_max,) = max_over_ranks([dt], device="cuda")
+    sums = torch.zeros(world, dtype=torch.int64, device="cuda")
+    sums[rank] = token_checksum(tokens)
+    if world > 1:
+        dist.all_reduce(sums)
+    if rank == 0:
+        flop = algorithmic_flops_per_row(spec) * total * 2
+        peak = _peaks().get("bf16_tflops_sustained", 1400.0) * world
+        ach = flop / dt_max / 1e12
+        print(json.dumps({
+            "metric": "generated tokens/sec", "value": total * NOMINAL_TOKENS["c5"] / dt_max, "unit": "tokens/s",
+            "n_gpus": world, "steps": 1, "warmup": 0, "ms_per_step": 1000.0 * dt_max, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 pairs x3 (fp32-grade operands, fp32 accumulate)",
+            "data": "synthetic", "config": workload_config("c5", spec, B, world),
+            "e2e": {"value": total * NOMINAL_TOKENS["c5"] / dt_max, "unit": "tokens/s",
+                    "h2d_bytes_per_step": int(prefix.nbytes), "d2h_bytes_per_step": int(codes.nbytes + tokens.nbytes)},
+            "gpu_launches": launches, "clocks": clk.summary(), "token_checksums": [int(v) for v in sums.tolist()],
+            "tensor_core_timeouts": int(lib.ncmb_gemm_tc_check()),
+            "roofline": {"bound": "tensor", "kernel": "whole job (all kernels, all waves)", "achieved": ach, "peak": peak,
+                         "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
+                         "algorithmic_tflop": flop / 1e12}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    tmp.cleanup()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -755,6 +824,8 @@ def main():
         run_lm_arm(args)
     elif args.workload == "c5q":
         run_quantizer_arm(args)
+    elif args.workload == "c5box":
+        run_box_arm(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:
