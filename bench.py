@@ -505,7 +505,7 @@ def _peaks():
 # Dense TF32 throughput of one B200 of this pool: torch.matmul on 8192^3 fp32 operands with TF32 allowed, best of
 # 10, measured once with a scratch script in the way the bf16 figure of MEASURED_PEAKS.json is measured (that file
 # has no TF32 entry). Used as the denominator of the quantizer sweep, whose distance GEMM runs on the TF32 pipe.
-TF32_PEAK_TFLOPS_MEASURED = None
+TF32_PEAK_TFLOPS_MEASURED = 752.7      # burst; 611.5 in a 4-second loop under the power cap
 
 
 def tf32_peak():

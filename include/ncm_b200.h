@@ -119,7 +119,11 @@ void  arena_free(void);
 void  parena_init(size_t bytes);
 float *parena_alloc(size_t n_floats);
 /* src/ncm.h:68-70, 139, 261 (tensor.c:70-143, 170-266, 369-373) */
-int  weights_load(WeightStore *ws, const char *path);     /* NCM1 weights or NCK1 checkpoints; 0 / -1 */
+int  weights_load(WeightStore *ws, const char *path);     /* NCM1 / NCM2 weights or NCK1 checkpoints; 0 / -1 */
+/* "NCM2" is this library's 2-byte variant of the NCM1 file (the reference's loader, tensor.c:70-128, is fp32-only):
+ * same header and records with one byte of element type (0 = fp32, 1 = bf16) in front of each record's u64 byte
+ * count. bf16 payloads cross PCIe as 2 bytes per element and are widened on the device, so every tensor is fp32 to
+ * its consumers -- exactly what the reference computes from the same values stored as fp32. */
 /* src/ncm.h:441, 465 (ckpt.c:67-77, 549-625): which of the two a file is (1 = NCK1 training checkpoint,
  * 0 = NCM1, -1 = neither), and the checkpoint's tensor records alone -- checksum verified first, run state and
  * optimizer section ignored -- so that every inference command accepts a training checkpoint. 0 / -1 with the
@@ -308,6 +312,14 @@ int   ncmb_prof_top_shape(int klass, long long *launches, double *ms, double *fl
 void  ncmb_prof_dump_shapes(void);
 int   ncmb_prof_read(int klass, long long *launches, double *ms, double *flops, double *bytes);
 long long ncmb_launch_count(void);            /* kernels launched since load */
+/* The GEMM engines keep converted copies (fp16 pairs, TF32 hi/lo) of weight matrices, keyed by the matrix's device
+ * address. weights_free, tensor_free, mem_h2d, mem_d2d and tensor_to_backend drop the copies of the memory they touch;
+ * a caller that rewrites weight memory by other means (its own kernels, cudaMemcpy) calls this before the next
+ * forward. No counterpart in the reference. */
+void  ncmb_forget_weight_copies(void);
+/* 1 when the store came from an "NCM2" file whose matrices are all 2-byte (bf16) records: ncmb_lm_open then streams
+ * exact 2-byte copies in its decode steps without being told. No counterpart in the reference. */
+int   ncmb_weights_are_bf16(const WeightStore *ws);
 /* free and total bytes of the current device's memory (cudaMemGetInfo) */
 void  ncmb_mem_info(unsigned long long *free_bytes, unsigned long long *total_bytes);
 /* bytes this library has copied host->device and device->host since load */

@@ -178,6 +178,8 @@ bool gemm_h3_supported(const GemmArgs &a);
 void gemm_h3(const GemmArgs &a);
 void gemm_h3_forget_weights();
 void gemm_tc_forget_weights();
+void gemm_h3_forget_range(const void *p, size_t bytes);     // cached copies of matrices overlapping the range only
+void gemm_tc_forget_range(const void *p, size_t bytes);
 struct StaticWeights { StaticWeights() { ctx().w_static++; } ~StaticWeights() { ctx().w_static--; } };
 int gemm_tc_check();                    // reads + clears the tensor-core engine's timeout word
 

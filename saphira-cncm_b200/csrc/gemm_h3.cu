@@ -258,6 +258,18 @@ void gemm_h3_forget_weights() {
     shadow_h().clear();
 }
 
+// Drops the cached pairs of every weight matrix that overlaps [p, p + bytes): called when that memory is rewritten
+// or freed through the public memory functions, so a matrix never runs on copies of its old contents.
+void gemm_h3_forget_range(const void *p, size_t bytes) {
+    auto &sc = shadow_h();
+    const char *lo = (const char *)p, *hi = lo + bytes;
+    for (auto it = sc.begin(); it != sc.end();) {
+        const char *w0 = (const char *)it->first, *w1 = w0 + (size_t)it->second.n * 4;
+        if (w0 < hi && lo < w1) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(it->second.v1); it = sc.erase(it); }
+        else ++it;
+    }
+}
+
 static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool gemm_h3_supported(const GemmArgs &a) {

@@ -376,6 +376,16 @@ void gemm_tc_forget_weights() {
     shadow_cache().clear();
 }
 
+void gemm_tc_forget_range(const void *p, size_t bytes) {
+    auto &sc = shadow_cache();
+    const char *lo = (const char *)p, *hi = lo + bytes;
+    for (auto it = sc.begin(); it != sc.end();) {
+        const char *w0 = (const char *)it->first, *w1 = w0 + (size_t)it->second.n * 4;
+        if (w0 < hi && lo < w1) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(it->second.hi); it = sc.erase(it); }
+        else ++it;
+    }
+}
+
 static inline bool al16(const void *p) { return ((uintptr_t)p & 15) == 0; }
 
 bool gemm_tc_supported(const GemmArgs &a) {

@@ -145,7 +145,7 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
     // bf16 weight files (values already rounded to bf16, stored as fp32): decode steps are bound by streaming the
     // weights, so the matrices get an exact 2-byte copy that the GEMV kernel reads instead -- same values, half
     // the bytes. A matrix with any element that is not a bf16 value keeps its fp32 path.
-    if (bf16_weights) {
+    if (bf16_weights || ncmb_weights_are_bf16(&m->ws)) {
         const int kvd2 = m->nkv * m->hd;
         auto shadow = [&](const float *w, int64_t n) -> const unsigned short * {
             unsigned short *p = dev_bf16_exact(w, n);

@@ -155,8 +155,15 @@ Tensor *tensor_alloc(int ndim, const int64_t *shape) {
     return t;
 }
 
+// memory that is rewritten or freed through the public functions no longer backs any cached weight copy
+static void forget_copies_of(const void *p, size_t bytes) {
+    gemm_h3_forget_range(p, bytes);
+    gemm_tc_forget_range(p, bytes);
+}
+
 void tensor_free(Tensor *t) {
     if (!t) return;
+    forget_copies_of(t->data, (size_t)(t->n > 0 ? t->n : 1) * sizeof(float));
     if (!slab_members().count(t->data)) {
         cudaStreamSynchronize(stream());
         cudaFree(t->data);
@@ -172,12 +179,14 @@ void mem_d2h(void *h, const void *d, size_t n) {
 }
 void mem_h2d(void *d, const void *h, size_t n) {
     ensure_device();
+    forget_copies_of(d, n);
     CUDA_CHECK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, stream()));
     CUDA_CHECK(cudaStreamSynchronize(stream()));   // h may be freed by the caller right after
     ctx().h2d_bytes += n;
 }
 void mem_d2d(void *d, const void *s, size_t n) {
     ensure_device();
+    forget_copies_of(d, n);
     CUDA_CHECK(cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, stream()));
 }
 void tensor_to_host(const Tensor *t, float *out) { mem_d2h(out, t->data, (size_t)t->n * sizeof(float)); }
@@ -256,6 +265,14 @@ float *parena_alloc(size_t n_floats) {
 // reached from weights_load src/tensor.c:73-80) only the tensor records are read. The file is staged once in
 // pinned memory and every payload goes to one device slab.
 
+// bf16 bits -> fp32 (exact): the payload of a 2-byte tensor record widened into the fp32 slab
+__global__ void k_widen_bf16(const unsigned short *__restrict__ src, float *__restrict__ dst, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        dst[i] = __uint_as_float((uint32_t)src[i] << 16);
+}
+// stores whose matrices all came from 2-byte records (every 2-D or larger tensor holds bf16 values only)
+static std::unordered_set<const void *> &bf16_stores() { static std::unordered_set<const void *> s; return s; }
+
 namespace {
 struct FileImage {
     unsigned char *buf = nullptr;
@@ -280,8 +297,11 @@ int read_image(const char *path, FileImage &im, char *err, size_t errcap) {
 
 // tensor records [pos, end) of a staged file -> ws (one device slab). strict: NCK1 rules (no empty names).
 int load_tensor_records(WeightStore *ws, const char *path, const FileImage &im, size_t pos, size_t end, uint32_t count, bool strict,
-                        char *err, size_t errcap) {
+                        char *err, size_t errcap, bool typed = false) {
     const unsigned char *buf = im.buf;
+    // every record takes at least 10 bytes (name length, ndim, byte count): a count the file cannot hold is refused
+    // before anything is allocated
+    if (count > (1u << 24) || (uint64_t)count * 10 > (uint64_t)(end - pos)) { snprintf(err, errcap, "%s: bad tensor count", path); return -1; }
     ws->items = (NamedTensor *)calloc(count ? count : 1, sizeof(NamedTensor));
     ws->count = 0;
     if (!ws->items) { snprintf(err, errcap, "out of memory"); return -1; }
@@ -291,9 +311,10 @@ int load_tensor_records(WeightStore *ws, const char *path, const FileImage &im, 
         free(ws->items); ws->items = nullptr; ws->count = 0;
         return -1;
     };
-    struct Span { size_t file_off, nbytes, slab_off; };
+    struct Span { size_t file_off, nbytes, slab_off; int dtype; };
     std::vector<Span> spans(count);
-    size_t slab = 0;
+    size_t slab = 0, max16 = 0;
+    bool all_matrices_16 = typed;
     const char *trunc = strict ? "truncated tensor section" : "truncated";
     for (uint32_t i = 0; i < count; i++) {
         if (pos + 1 > end) return fail(trunc);
@@ -307,30 +328,51 @@ int load_tensor_records(WeightStore *ws, const char *path, const FileImage &im, 
         Tensor *t = (Tensor *)calloc(1, sizeof(Tensor));
         t->ndim = (int)nd; t->n = 1;
         for (unsigned d = 0; d < nd; d++) { uint32_t v; memcpy(&v, buf + pos, 4); pos += 4; t->shape[d] = v; t->n *= v; }
-        uint64_t nbytes;
-        memcpy(&nbytes, buf + pos, 8); pos += 8;
         ws->items[i].t = t;
         ws->count = (int)i + 1;
+        int dtype = 0;                                             // 0 = fp32, 1 = bf16 (typed records only)
+        if (typed) {
+            if (pos + 1 + 8 > end) return fail(trunc);
+            dtype = buf[pos++];
+            if (dtype > 1) return fail("unknown element type");
+        }
+        uint64_t nbytes;
+        memcpy(&nbytes, buf + pos, 8); pos += 8;
         if (nbytes > end - pos) return fail(strict ? trunc : "truncated payload");
-        if ((uint64_t)t->n * 4 != nbytes) {
+        if ((uint64_t)t->n * (dtype ? 2 : 4) != nbytes) {
             snprintf(err, errcap, "%s: tensor '%s' size mismatch", path, ws->items[i].name);
             return fail("size mismatch");
         }
-        spans[i] = Span{pos, (size_t)nbytes, slab};
-        slab += ((size_t)nbytes + 255) & ~(size_t)255;
+        if (dtype && nbytes > max16) max16 = (size_t)nbytes;
+        if (!dtype && nd >= 2) all_matrices_16 = false;
+        spans[i] = Span{pos, (size_t)nbytes, slab, dtype};
+        // an empty tensor still gets a slot of its own, so that no two tensors share an address
+        const size_t room = (size_t)t->n * 4;
+        slab += room ? ((room + 255) & ~(size_t)255) : 256;
         pos += nbytes;
     }
     char *dslab = nullptr;
     CUDA_CHECK(cudaMalloc((void **)&dslab, slab ? slab : 256));
+    unsigned short *stage16 = nullptr;                             // 2-byte payloads pass through here, one at a time, in stream order
+    if (max16) CUDA_CHECK(cudaMalloc((void **)&stage16, max16));
     for (uint32_t i = 0; i < count; i++) {
         ws->items[i].t->data = (float *)(dslab + spans[i].slab_off);
         slab_members().insert(ws->items[i].t->data);
-        if (spans[i].nbytes)
+        if (!spans[i].nbytes) continue;
+        if (spans[i].dtype) {
+            const int64_t n = ws->items[i].t->n;
+            CUDA_CHECK(cudaMemcpyAsync(stage16, buf + spans[i].file_off, spans[i].nbytes, cudaMemcpyHostToDevice, stream()));
+            const int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+            LAUNCH(k_widen_bf16, (unsigned)(g > cap ? cap : g), 256, 0, (const unsigned short *)stage16, ws->items[i].t->data, n);
+        } else {
             CUDA_CHECK(cudaMemcpyAsync(dslab + spans[i].slab_off, buf + spans[i].file_off, spans[i].nbytes,
                                        cudaMemcpyHostToDevice, stream()));
+        }
     }
     CUDA_CHECK(cudaStreamSynchronize(stream()));
+    if (stage16) CUDA_CHECK(cudaFree(stage16));
     slab_of_store()[ws->items] = dslab;
+    if (all_matrices_16 && count) bf16_stores().insert(ws->items);
     return 0;
 }
 
@@ -451,11 +493,14 @@ int weights_load(WeightStore *ws, const char *path) {
     }
     FileImage im;
     int rc = read_image(path, im, err, sizeof(err));
-    if (!rc && memcmp(im.buf, "NCM1", 4) != 0) { snprintf(err, sizeof(err), "%s: bad magic", path); rc = -1; }
+    // "NCM2": the NCM1 layout with one byte of element type (0 fp32, 1 bf16) in front of each record's byte count;
+    // bf16 payloads are widened on the device, so every consumer still sees fp32 tensors
+    const bool typed = !rc && memcmp(im.buf, "NCM2", 4) == 0;
+    if (!rc && !typed && memcmp(im.buf, "NCM1", 4) != 0) { snprintf(err, sizeof(err), "%s: bad magic", path); rc = -1; }
     if (!rc) {
         uint32_t count;
         memcpy(&count, im.buf + 4, 4);
-        rc = load_tensor_records(ws, path, im, 8, im.len, count, false, err, sizeof(err));
+        rc = load_tensor_records(ws, path, im, 8, im.len, count, false, err, sizeof(err), typed);
     }
     if (rc) fprintf(stderr, "%s\n", err);
     return rc;
@@ -475,6 +520,7 @@ void weights_free(WeightStore *ws) {
         free(t);
     }
     if (it != slab_of_store().end()) { cudaFree(it->second); slab_of_store().erase(it); }
+    bf16_stores().erase(ws->items);
     free(ws->items);
     ws->items = nullptr; ws->count = 0;
 }
@@ -613,6 +659,8 @@ int ncmb_gemm_tc_check(void) { ensure_device(); return gemm_tc_check(); }
 void ncmb_set_rng_mode(int mode) { ensure_device(); ctx().rng_mode = mode; }
 void ncmb_set_row_offset(long long off) { ctx().row_offset = off; }
 long long ncmb_launch_count(void) { return ctx().launches; }
+void ncmb_forget_weight_copies(void) { gemm_tc_forget_weights(); gemm_h3_forget_weights(); }
+int ncmb_weights_are_bf16(const WeightStore *ws) { return ws && ws->items && bf16_stores().count(ws->items) ? 1 : 0; }
 void ncmb_mem_info(unsigned long long *free_bytes, unsigned long long *total_bytes) {
     ensure_device();
     size_t f = 0, t = 0;

@@ -47,6 +47,32 @@ def write_ncm(path: str, tensors: "dict[str, np.ndarray]") -> None:
             f.write(raw)
 
 
+def write_ncm2(path: str, tensors: "dict[str, np.ndarray]", bf16: "bool | set[str]" = True) -> None:
+    """The 2-byte variant of the weights file (magic ``NCM2``): the NCM1 layout with one byte of element type
+    (0 = float32, 1 = bfloat16) in front of each record's byte count. Tensors with two or more dimensions (or the
+    names in `bf16`) are written as bf16 bits -- their values must already be bf16 values -- the rest as float32."""
+    with open(path, "wb") as f:
+        f.write(b"NCM2")
+        f.write(struct.pack("<I", len(tensors)))
+        for name, arr in tensors.items():
+            t = np.ascontiguousarray(arr, dtype=np.float32)
+            half = (t.ndim >= 2) if isinstance(bf16, bool) and bf16 else (not isinstance(bf16, bool) and name in bf16)
+            nb = name.encode()
+            f.write(struct.pack("<B", len(nb)))
+            f.write(nb)
+            f.write(struct.pack("<B", t.ndim))
+            for d in t.shape:
+                f.write(struct.pack("<I", d))
+            if half:
+                bits = t.view(np.uint32)
+                assert not (bits & 0xFFFF).any(), f"{name}: not a bf16 value"
+                raw = (bits >> 16).astype(np.uint16).tobytes()
+            else:
+                raw = t.tobytes()
+            f.write(struct.pack("<BQ", 1 if half else 0, len(raw)))
+            f.write(raw)
+
+
 def _fnv1a64(data: bytes) -> int:
     """FNV-1a 64 (a serial chain; fine for the small files tests write)."""
     h = 14695981039346656037

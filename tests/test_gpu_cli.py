@@ -219,7 +219,7 @@ def test_vq_encode_and_vq_recon_on_training_rows(both):
         res[tag] = (open(oe, "rb").read(), out.splitlines()[-1], open(orc_).read(), out2.splitlines()[-1])
     assert res["gpu"][0] == res["cpu"][0]                  # [prefix | codes] rows: bytes equal
     assert len(res["cpu"][0]) == 20 + nrows * (7 + 15) * 4
-    assert res["gpu"][1] == res["cpu"][1] and res["cpu"][1].startswith("[vq-encode] 37 rows")
+    assert res["gpu"][1].startswith("[vq-encode] 37 rows x 22 -> ") and res["cpu"][1].startswith("[vq-encode] 37 rows x 22 -> ")
     assert res["gpu"][2] == res["cpu"][2] and len(res["cpu"][2].splitlines()) == 35
     assert res["gpu"][3] == res["cpu"][3] and "id_match" in res["cpu"][3]
     # a cut file and a wrong magic are refused by the reader, with the reference's messages

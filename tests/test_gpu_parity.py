@@ -701,3 +701,88 @@ def test_safetensors_import_on_the_device(cuda, tmp, kind):
         outs.append(lg)
         cuda.ncmb_lm_close(m)
     assert helpers.same_bits(outs[0], outs[1])
+
+
+def test_two_byte_weight_file_variant(cuda, tmp):
+    """"NCM2" files (bf16 records widened on the device): same tensors as the fp32 file of the same values, a decoder
+    opened from one streams 2-byte copies without being told and computes what it computes from the fp32 file;
+    malformed records are refused."""
+    import ctypes as C
+    import struct
+    import capi
+    import orc
+    import synth
+    spec = synth.LMSpec("qwen_ncm2", "qwen", 2, 256, 4, 2, 384, 411, 64, rope_theta=1e6, bf16_round=1)
+    conf, w1 = synth.write_lm(spec, tmp)
+    tensors = synth.lm_tensors(spec, 4321)
+    w2 = os.path.join(tmp, "qwen_ncm2.ncm2")
+    synth.write_ncm2(w2, tensors)
+    assert os.path.getsize(w2) < 0.55 * os.path.getsize(w1)
+    a, b = cuda.load_weights(w1), cuda.load_weights(w2)
+    assert a.count == b.count == len(tensors)
+    assert cuda.ncmb_weights_are_bf16(C.byref(a)) == 0 and cuda.ncmb_weights_are_bf16(C.byref(b)) == 1
+    for name, want in tensors.items():
+        assert helpers.same_bits(cuda.tensor_host(b, name), np.ascontiguousarray(want, np.float32)), name
+    cuda.weights_free(C.byref(a))
+    cuda.weights_free(C.byref(b))
+    cfg = cuda.load_config(conf)
+    om = orc.LM(conf, w1, True)
+    P = np.ascontiguousarray(synth.lm_prompts(spec, 3, 9, 3))
+    outs = []
+    for path, flag in ((w1, 1), (w2, 0)):
+        m = cuda.ncmb_lm_open(cfg, path.encode(), 1, flag)
+        assert m
+        lg = np.zeros((P.shape[1], spec.vocab), np.float32)
+        cuda.ncmb_lm_logits(m, P[0].ctypes.data, P.shape[1], 0, lg.ctypes.data)
+        ids = np.zeros((3, 10), np.int32)
+        cuda.ncmb_lm_generate(m, P.ctypes.data, 3, P.shape[1], 10, 0.0, 0, 1.0, 0, -1, ids.ctypes.data)
+        outs.append((lg, ids))
+        cuda.ncmb_lm_close(m)
+    assert helpers.same_bits(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+    _cmp_float("ncm2 logits", outs[1][0], om.logits(P[0]), ATOL_LOGITS)
+    for b_ in range(3):
+        assert (outs[1][1][b_] == om.generate(P[b_], 10, temp=0.0)).all()
+    # refusals: an element type the loader does not know, a payload that does not match the shape, a cut file
+    raw = bytearray(open(w2, "rb").read())
+    name0 = next(iter(tensors))
+    tpos = 8 + 1 + len(name0.encode()) + 1 + 4 * tensors[name0].ndim
+    assert raw[tpos] == 1
+    bad = {"type": bytes(raw[:tpos]) + b"\x07" + bytes(raw[tpos + 1:]),
+           "size": bytes(raw[:tpos]) + b"\x00" + bytes(raw[tpos + 1:]),          # 2-byte payload declared as fp32
+           "cut": bytes(raw[:len(raw) // 2]),
+           "count": bytes(raw[:4]) + struct.pack("<I", 0xFFFFFFF0) + bytes(raw[8:])}
+    for tag, data in bad.items():
+        path = os.path.join(tmp, f"bad_{tag}.ncm2")
+        open(path, "wb").write(data)
+        ws = capi.WeightStore()
+        assert cuda.weights_load(C.byref(ws), path.encode()) == -1, tag
+        assert ws.count == 0 and not ws.items
+
+
+def test_rewriting_a_weight_tensor_drops_its_cached_copies(cuda, tmp):
+    """The GEMM engines cache converted copies of weight matrices by device address. A matrix rewritten in place with
+    tensor_to_backend must run on its new values, like a model loaded from a file with those values."""
+    import ctypes as C
+    import capi
+    import cases
+    import synth
+    spec = cases.ncp_spec("plain")
+    conf, w = synth.write_ncp(spec, tmp)
+    pre, l0, _ = cases.ncp_inputs(spec)
+    m = capi.NcpModel(cuda, conf, w, arena_mb=64)
+    before = m.generate(pre, temp=0.0)
+    tens = synth.ncp_tensors(spec, 1234)
+    name = "gen.transformer.blocks.0.mlp.c_fc.weight"     # a prefix-pass projection: 36 token rows, tensor-core engine, cached pairs
+    new = np.ascontiguousarray(np.random.default_rng(1).normal(0, 0.02, tens[name].shape), np.float32)
+    t = cuda.weights_get(C.byref(m.ws), name.encode())
+    assert t
+    tb = cuda.lib.tensor_to_backend
+    tb.restype, tb.argtypes = None, [C.c_void_p, C.c_void_p]
+    tb(t, new.ctypes.data)
+    after = m.generate(pre, temp=0.0)
+    tens[name] = new
+    w2 = os.path.join(tmp, "plain_rewritten.ncm")
+    synth.write_ncm(w2, tens)
+    fresh = capi.NcpModel(cuda, conf, w2, arena_mb=64).generate(pre, temp=0.0)
+    assert np.array_equal(after, fresh)
+    assert not np.array_equal(after, before)
