@@ -343,6 +343,13 @@ int ncmb_linear_fwd_noalloc(const float *x, const float *W, const float *b, floa
                             int64_t batch, int M, int K);
 int ncmb_linear_fwd_noalloc_check(void);
 
+/* Diagnostic: the device sampler on caller-supplied DEVICE rows (one position per row, no CFG, no penalties):
+ * sample_topkp's rule (src/kernels.c:794-825) with row b's uniform taken from uniforms[b] (device doubles in
+ * [0, 1)); picks is a device int[B]. Lets tests feed crafted rows (ties, constant rows) to the selection-based and
+ * the sort-based nucleus paths. Synchronises. No counterpart in the reference. */
+void ncmb_sample_rows_dev(const float *logits, int B, int V, float temp, int top_k, float top_p,
+                          const double *uniforms, int *picks);
+
 /* NCP generate, extended: same as ncp_generate, and when logits_host is not NULL
  * it receives the logits each sampled position was drawn from (after the CFG
  * blend, before penalties), per sampled row, level-major. */

@@ -137,6 +137,7 @@ _SIGS = {
     "ncmb_linear_fwd_noalloc_check": (_I, []),
     "ncmb_set_map_cache_limit": (None, [_I]),
     "ncmb_launch_count": (C.c_longlong, []),
+    "ncmb_sample_rows_dev": (None, [_P, _I, _I, _F, _I, _F, _P, _P]),
     "ncmb_forget_weight_copies": (None, []),
     "ncmb_weights_are_bf16": (_I, [C.POINTER(WeightStore)]),
     "ncmb_mem_info": (None, [C.POINTER(_U64), C.POINTER(_U64)]),

@@ -629,10 +629,368 @@ __global__ void __launch_bounds__(SL_THREADS) k_pick_sorted(const void *__restri
     if (tid == 0) out[(size_t)b * out_stride + out_off] = ir[s_min < 0 ? 0 : s_min];
 }
 
+// ---- the same draw without sorting the row (top_k = 0: the nucleus is cut from the whole vocabulary) ----
+// With seeded or near-uniform logits the nucleus holds most of a 150 K vocabulary, so the sort above is the
+// sampler. Both the cut ("cum_before - p > top_p") and the draw ("u <= cum") are the first rank at which a
+// monotone predicate over cumulative probability turns true, so each can be found the way a radix select finds
+// a rank: three passes over the row's ordered 32-bit keys (11 + 11 + 10 bits), each building per-bin probability
+// mass, element counts and the smallest / largest key of a bin, descending into the bin where the predicate
+// flips. Probabilities are accumulated as 64-bit fixed point (2^-44 steps, exact and order-independent integer
+// sums, so runs are reproducible whatever order the atomics land in); the absolute error of a cumulative sum is
+// below 1e-11 of the row's mass, which moves a draw only when it falls that close to a boundary. Ties of equal
+// logits are ranked by ascending index, like the stable sort.
+constexpr int NS_THREADS = 1024;
+constexpr int NS_BINS = 2048;
+constexpr double NS_FIX = 17592186044416.0;                       // 2^44
+
+struct NsHist {
+    unsigned long long sum[NS_BINS];
+    unsigned cnt[NS_BINS];
+    unsigned kmin_inv[NS_BINS];       // ~(smallest key of the bin): zero-initialised storage, atomicMax
+    unsigned kmax[NS_BINS];
+};
+// Per-row state handed from one kernel of the sequence to the next. A field is written by the first CTA of a row
+// in one kernel and read only by LATER kernels (the CTAs of a kernel each repeat its decision for themselves), hence
+// one slot per stage for the fields that change from stage to stage.
+struct NsRow {
+    unsigned maxkey;
+    int n_done[2];                     // nucleus cut resolved by the first / second level (den2 valid)
+    unsigned n_prefix[2];              // key bits fixed by the nucleus descent after its first / second level
+    unsigned long long n_above[2];     // mass strictly above the nucleus descent's range after those levels
+    unsigned long long total, den2;    // mass of the row / of the kept prefix
+    unsigned p_prefix[2];
+    unsigned long long p_above[2];
+    double U;                          // the draw, in fixed-point units of mass
+};
+
+__device__ __forceinline__ unsigned long long ns_q_of_key(unsigned key, double mx) {
+    return __double2ull_rn(exp((double)okey_inv(key) - mx) * NS_FIX);
+}
+
+// exclusive block scan of one u64 per thread (NS_THREADS threads); every thread gets its prefix
+__device__ __forceinline__ unsigned long long ns_block_excl_scan(unsigned long long v, unsigned long long *wsum) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned long long x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        unsigned long long y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+    }
+    __syncthreads();                                               // wsum may still be read from an earlier call
+    if (lane == 31) wsum[warp] = x;
+    __syncthreads();
+    unsigned long long base = 0;
+    for (int w = 0; w < warp; w++) base += wsum[w];
+    return base + x - v;
+}
+
+// One level of a descent over a histogram of `nbins` bins, highest bin first. NUCLEUS: the first bin whose LAST
+// element satisfies cum_before - p > T (then *first_hit tells whether already its first element does, in which
+// case the cut lies exactly in front of the bin). Otherwise: the first bin with cum_incl >= T. Results through
+// shared memory: *sel = bin (-1: no bin satisfies), *sel_above = mass above that bin.
+template <bool NUCLEUS>
+__device__ void ns_decide(const NsHist *h, int nbins, unsigned long long above, double T, double mx, unsigned key_hi, int shift,
+                          unsigned long long *wsum, int *sel, unsigned long long *sel_above, int *first_hit) {
+    const int tid = threadIdx.x;
+    unsigned long long s[2]; int bin[2];
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const int d = 2 * tid + e;
+        bin[e] = nbins - 1 - d;
+        s[e] = (d < nbins) ? h->sum[bin[e]] : 0ull;
+    }
+    if (tid == 0) { *sel = 0x7fffffff; *first_hit = 0; }
+    const unsigned long long ex = ns_block_excl_scan(s[0] + s[1], wsum);    // contains a __syncthreads after the init above
+    unsigned long long ab = above + ex;
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const int d = 2 * tid + e;
+        if (d < nbins && h->cnt[bin[e]] > 0) {
+            bool hit;
+            if (NUCLEUS) {
+                const unsigned kmin = ~h->kmin_inv[bin[e]];
+                const long long g = (long long)(ab + s[e]) - 2ll * (long long)ns_q_of_key(kmin, mx);
+                hit = (double)g > T;
+            } else {
+                hit = (double)(ab + s[e]) >= T;
+            }
+            if (hit) atomicMin(sel, d);
+        }
+        ab += s[e];
+    }
+    __syncthreads();
+    const int dsel = *sel;
+    __syncthreads();
+    if (dsel == 0x7fffffff) { if (tid == 0) *sel = -1; __syncthreads(); return; }
+    if (dsel >> 1 == tid) {
+        const int e = dsel & 1;
+        const unsigned long long a0 = above + ex + (e ? s[0] : 0ull);
+        *sel = bin[e];
+        *sel_above = a0;
+        if (NUCLEUS) {
+            const long long g0 = (long long)a0 - (long long)ns_q_of_key(h->kmax[bin[e]], mx);
+            *first_hit = (double)g0 > T ? 1 : 0;
+        }
+    }
+    __syncthreads();
+}
+
+__global__ void __launch_bounds__(NS_THREADS) k_ns_max(const float *__restrict__ logits, float temp, int V, NsRow *rows) {
+    const int b = blockIdx.y;
+    const float *lg = logits + (size_t)b * V;
+    unsigned m = 0;
+    for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) m = max(m, okey(lg[i] / temp));
+    for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(&rows[b].maxkey, m);
+}
+
+// accumulates the elements of this CTA's slice whose key, shifted right by `fshift`, equals `want` (fshift = 32:
+// every element) into the histogram of the next `bits` key bits below that; shared histogram, then one atomic
+// per touched bin into the row's global one
+__device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned long long *__restrict__ q, int V, int fshift, unsigned want,
+                             int shift, int nbins, NsHist *sh, NsHist *gh) {
+    for (int i = threadIdx.x; i < nbins; i += NS_THREADS) { sh->sum[i] = 0; sh->cnt[i] = 0; sh->kmin_inv[i] = 0; sh->kmax[i] = 0; }
+    __syncthreads();
+    for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) {
+        const unsigned k = keys[i];
+        if (fshift < 32 && (k >> fshift) != want) continue;
+        const int bin = (int)((k >> shift) & (unsigned)(nbins - 1));
+        atomicAdd(&sh->sum[bin], q[i]);
+        atomicAdd(&sh->cnt[bin], 1u);
+        atomicMax(&sh->kmin_inv[bin], ~k);
+        atomicMax(&sh->kmax[bin], k);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nbins; i += NS_THREADS)
+        if (sh->cnt[i]) {
+            atomicAdd(&gh->sum[i], sh->sum[i]);
+            atomicAdd(&gh->cnt[i], sh->cnt[i]);
+            atomicMax(&gh->kmin_inv[i], sh->kmin_inv[i]);
+            atomicMax(&gh->kmax[i], sh->kmax[i]);
+        }
+}
+
+// keys, fixed-point probabilities and the histogram of the top 11 key bits
+__global__ void __launch_bounds__(NS_THREADS) k_ns_prob(const float *__restrict__ logits, float temp, int V, NsRow *rows, unsigned *keys,
+                                                        unsigned long long *q, NsHist *hist) {
+    __shared__ NsHist sh;
+    const int b = blockIdx.y;
+    const float *lg = logits + (size_t)b * V;
+    unsigned *kr = keys + (size_t)b * V;
+    unsigned long long *qr = q + (size_t)b * V;
+    const double mx = (double)okey_inv(rows[b].maxkey);
+    for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) {
+        const unsigned k = okey(lg[i] / temp);
+        kr[i] = k;
+        qr[i] = ns_q_of_key(k, mx);
+    }
+    __syncthreads();                                               // this CTA re-reads only what it wrote itself
+    ns_histogram(kr, qr, V, 32, 0u, 21, NS_BINS, &sh, hist + (size_t)b * 5);
+}
+
+// STAGE 2, 3: nucleus descent (decide on the previous histogram, build the next); 4: end of the nucleus descent,
+// the draw, first level of the pick descent; 5: second level of the pick descent
+template <int STAGE>
+__global__ void __launch_bounds__(NS_THREADS) k_ns_refine(int V, float top_p, const double *__restrict__ uniforms, unsigned long long seed,
+                                                          long long row0, int level, NsRow *rows, const unsigned *keys,
+                                                          const unsigned long long *q, NsHist *hist) {
+    __shared__ NsHist sh;
+    __shared__ unsigned long long wsum[32];
+    __shared__ int s_sel, s_first;
+    __shared__ unsigned long long s_above;
+    const int b = blockIdx.y, tid = threadIdx.x;
+    NsRow *row = rows + b;
+    NsHist *H = hist + (size_t)b * 5;                              // 0: top bits | 1, 2: nucleus levels | 3, 4: pick levels
+    const unsigned *kr = keys + (size_t)b * V;
+    const unsigned long long *qr = q + (size_t)b * V;
+    const double mx = (double)okey_inv(row->maxkey);
+    const bool lead = blockIdx.x == 0 && tid == 0;
+    const unsigned long long total = (STAGE == 2) ? 0ull : row->total;
+    if (STAGE == 2) {
+        // total mass = sum over the top-level bins (every CTA computes it; the leader records it)
+        unsigned long long t = H[0].sum[2 * tid] + H[0].sum[2 * tid + 1];
+        const unsigned long long ex = ns_block_excl_scan(t, wsum);
+        __shared__ unsigned long long s_total;
+        if (tid == NS_THREADS - 1) s_total = ex + t;
+        __syncthreads();
+        const unsigned long long tot = s_total;
+        if (lead) row->total = tot;
+        if (!(top_p < 1.0f)) { if (lead) { row->n_done[0] = 1; row->den2 = tot; } return; }
+        const double T = (double)top_p * (double)tot;
+        ns_decide<true>(&H[0], NS_BINS, 0ull, T, mx, 0u, 21, wsum, &s_sel, &s_above, &s_first);
+        if (s_sel < 0) { if (lead) { row->n_done[0] = 1; row->den2 = tot; } return; }       // the cut is never reached
+        if (s_first) { if (lead) { row->n_done[0] = 1; row->den2 = s_above; } return; }
+        if (lead) { row->n_prefix[0] = (unsigned)s_sel; row->n_above[0] = s_above; }
+        ns_histogram(kr, qr, V, 21, (unsigned)s_sel, 10, NS_BINS, &sh, &H[1]);
+        return;
+    }
+    if (STAGE == 3) {
+        if (row->n_done[0]) return;
+        const double T = (double)top_p * (double)total;
+        ns_decide<true>(&H[1], NS_BINS, row->n_above[0], T, mx, 0u, 10, wsum, &s_sel, &s_above, &s_first);
+        // the parent bin's last element satisfies the predicate, so a bin is always found
+        const unsigned pre = (row->n_prefix[0] << 11) | (unsigned)(s_sel < 0 ? 0 : s_sel);
+        if (s_first || s_sel < 0) { __syncthreads(); if (lead) { row->n_done[1] = 1; row->den2 = s_sel < 0 ? total : s_above; } return; }
+        __syncthreads();
+        if (lead) { row->n_prefix[1] = pre; row->n_above[1] = s_above; }
+        ns_histogram(kr, qr, V, 10, pre, 0, 1024, &sh, &H[2]);
+        return;
+    }
+    if (STAGE == 4) {
+        unsigned long long den2 = row->den2;
+        if (!row->n_done[0] && !row->n_done[1]) {
+            const double T = (double)top_p * (double)total;
+            ns_decide<true>(&H[2], 1024, row->n_above[1], T, mx, 0u, 0, wsum, &s_sel, &s_above, &s_first);
+            // the bin is one exact key held by cnt tied elements of mass qk each: the j-th of them (ascending index)
+            // has cum_before - p = above + (j - 1) qk; the cut is the first j for which that exceeds T
+            den2 = total;
+            if (s_sel >= 0) {
+                const unsigned long long qk = ns_q_of_key((row->n_prefix[1] << 10) | (unsigned)s_sel, mx);
+                const long long cnt = (long long)H[2].cnt[s_sel];
+                long long j = 0;
+                if (qk > 0) {
+                    j = (long long)floor((T - (double)s_above) / (double)qk) + 1;
+                    if (j < 0) j = 0;
+                    if (j > cnt) j = cnt;
+                    while (j > 0 && (double)((long long)s_above + (j - 2) * (long long)qk) > T) j--;       // smallest j with the predicate true
+                    while (j < cnt && !((double)((long long)s_above + (j - 1) * (long long)qk) > T)) j++;
+                }
+                den2 = s_above + (unsigned long long)j * qk;
+            }
+            __syncthreads();
+        }
+        const double u01 = uniforms ? uniforms[b] : counter_uniform(seed, row0 + b, level, 0);
+        const double U = u01 * (double)den2;
+        if (lead) { row->den2 = den2; row->U = U; }
+        ns_decide<false>(&H[0], NS_BINS, 0ull, U, mx, 0u, 21, wsum, &s_sel, &s_above, &s_first);
+        int sel = s_sel;
+        unsigned long long ab = s_above;
+        if (sel < 0) {                                              // rounding put the draw past the last mass: take the lowest occupied bin
+            sel = 0; ab = 0;
+            __syncthreads();
+            if (tid == 0) { int bsel = -1; unsigned long long acc = 0, accb = 0; for (int i = NS_BINS - 1; i >= 0; i--) if (H[0].cnt[i]) { bsel = i; accb = acc; acc += H[0].sum[i]; } s_sel = bsel; s_above = accb; }
+            __syncthreads();
+            sel = s_sel; ab = s_above;
+        }
+        __syncthreads();
+        if (lead) { row->p_prefix[0] = (unsigned)sel; row->p_above[0] = ab; }
+        ns_histogram(kr, qr, V, 21, (unsigned)sel, 10, NS_BINS, &sh, &H[3]);
+        return;
+    }
+    if (STAGE == 5) {
+        ns_decide<false>(&H[3], NS_BINS, row->p_above[0], row->U, mx, 0u, 10, wsum, &s_sel, &s_above, &s_first);
+        int sel = s_sel;
+        unsigned long long ab = s_above;
+        if (sel < 0) {
+            __syncthreads();
+            if (tid == 0) { int bsel = 0; unsigned long long acc = row->p_above[0], accb = acc; for (int i = NS_BINS - 1; i >= 0; i--) if (H[3].cnt[i]) { bsel = i; accb = acc; acc += H[3].sum[i]; } s_sel = bsel; s_above = accb; }
+            __syncthreads();
+            sel = s_sel; ab = s_above;
+        }
+        const unsigned pre = (row->p_prefix[0] << 11) | (unsigned)sel;
+        __syncthreads();
+        if (lead) { row->p_prefix[1] = pre; row->p_above[1] = ab; }
+        ns_histogram(kr, qr, V, 10, pre, 0, 1024, &sh, &H[4]);
+        return;
+    }
+}
+
+// last level of the pick descent, then the index: the pick_tie-th (ascending index) element holding the chosen key
+__global__ void __launch_bounds__(NS_THREADS) k_ns_pick(int V, NsRow *rows, const unsigned *keys, NsHist *hist, int *__restrict__ out, int out_stride,
+                                                        int out_off) {
+    __shared__ unsigned long long wsum[32];
+    __shared__ int s_sel, s_first, s_n, s_list[2048];
+    __shared__ unsigned long long s_above;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    NsRow *row = rows + b;
+    NsHist *H = hist + (size_t)b * 5;
+    const unsigned *kr = keys + (size_t)b * V;
+    const double mx = (double)okey_inv(row->maxkey);
+    ns_decide<false>(&H[4], 1024, row->p_above[1], row->U, mx, 0u, 0, wsum, &s_sel, &s_above, &s_first);
+    if (s_sel < 0) {
+        __syncthreads();
+        if (tid == 0) { int bsel = 0; unsigned long long acc = row->p_above[1], accb = acc; for (int i = 1023; i >= 0; i--) if (H[4].cnt[i]) { bsel = i; accb = acc; acc += H[4].sum[i]; } s_sel = bsel; s_above = accb; }
+        __syncthreads();
+    }
+    const unsigned key = (row->p_prefix[1] << 10) | (unsigned)s_sel;
+    const long long cnt = (long long)H[4].cnt[s_sel];
+    const unsigned long long qk = ns_q_of_key(key, mx);
+    // the j-th tied element has cum_incl = above + (j + 1) qk: the first j for which that reaches U
+    long long j = 0;
+    if (qk > 0 && cnt > 1) {
+        j = (long long)ceil((row->U - (double)s_above) / (double)qk) - 1;
+        if (j < 0) j = 0;
+        if (j > cnt - 1) j = cnt - 1;
+        while (j > 0 && (double)(s_above + (unsigned long long)j * qk) >= row->U) j--;
+        while (j < cnt - 1 && !((double)(s_above + (unsigned long long)(j + 1) * qk) >= row->U)) j++;
+    }
+    if (tid == 0) s_n = 0;
+    __syncthreads();
+    // indices holding the key (a handful at most for real logits; a constant row makes it the whole vocabulary)
+    if (cnt <= 2048) {
+        for (int i = tid; i < V; i += NS_THREADS)
+            if (kr[i] == key) { int at = atomicAdd(&s_n, 1); if (at < 2048) s_list[at] = i; }
+        __syncthreads();
+        const int n = s_n < 2048 ? s_n : 2048;
+        for (int e = tid; e < n; e += NS_THREADS) {
+            int r = 0;
+            for (int f = 0; f < n; f++) r += s_list[f] < s_list[e];
+            if (r == (int)j) out[(size_t)b * out_stride + out_off] = s_list[e];
+        }
+    } else {
+        // many ties: the j-th match in index order, by counting matches per thread slice and scanning
+        const int per = (V + NS_THREADS - 1) / NS_THREADS, i0 = tid * per, i1 = min(V, i0 + per);
+        unsigned long long c = 0;
+        for (int i = i0; i < i1; i++) c += kr[i] == key;
+        const unsigned long long ex = ns_block_excl_scan(c, wsum);
+        if ((unsigned long long)j >= ex && (unsigned long long)j < ex + c) {
+            long long need = j - (long long)ex;
+            for (int i = i0; i < i1; i++)
+                if (kr[i] == key && need-- == 0) { out[(size_t)b * out_stride + out_off] = i; break; }
+        }
+    }
+}
+
+static bool sample_rows_select(const SampleArgs &a) {
+    // NCM_B200_SORT_SAMPLER=1 keeps the sort-based path (read per call: tests compare the two on the same rows);
+    // NCM_B200_SELECT_MIN_V lowers the vocabulary size from which the selection path is taken (default 4096)
+    const char *e = getenv("NCM_B200_SORT_SAMPLER"), *mv = getenv("NCM_B200_SELECT_MIN_V");
+    if ((e && atoi(e)) || a.V < (mv ? atoi(mv) : 4096)) return false;
+    static Workspace ws;
+    const size_t n = (size_t)a.Bn * a.V;
+    const size_t head = ((size_t)a.Bn * sizeof(NsRow) + (size_t)a.Bn * 5 * sizeof(NsHist) + 255) & ~(size_t)255;
+    const size_t need = head + n * 12 + 4096;
+    if (need > ws.cap) ws.reserve(need + need / 8);
+    ws.reset();
+    char *base = (char *)ws.alloc(head);
+    NsRow *rows = (NsRow *)base;
+    NsHist *hist = (NsHist *)(base + (((size_t)a.Bn * sizeof(NsRow) + 15) & ~(size_t)15));
+    unsigned long long *q = ws.get<unsigned long long>(n);
+    unsigned *keys = ws.get<unsigned>(n);
+    ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
+    CUDA_CHECK(cudaMemsetAsync(base, 0, head, stream()));
+    // CTAs per row: enough to occupy the GPU when there are few rows
+    int G = (2 * ctx().sm_count + a.Bn - 1) / a.Bn;
+    const int gmax = (a.V + 4 * NS_THREADS - 1) / (4 * NS_THREADS);
+    if (G > gmax) G = gmax;
+    if (G > 32) G = 32;
+    if (G < 1) G = 1;
+    const dim3 grid((unsigned)G, (unsigned)a.Bn);
+    LAUNCH(k_ns_max, grid, NS_THREADS, 0, a.logits, a.temp, a.V, rows);
+    LAUNCH(k_ns_prob, grid, NS_THREADS, 0, a.logits, a.temp, a.V, rows, keys, q, hist);
+    LAUNCH(k_ns_refine<2>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
+    LAUNCH(k_ns_refine<3>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
+    LAUNCH(k_ns_refine<4>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
+    LAUNCH(k_ns_refine<5>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
+    LAUNCH(k_ns_pick, (unsigned)a.Bn, NS_THREADS, 0, a.V, rows, (const unsigned *)keys, hist, a.out, a.out_stride, a.out_off);
+    return true;
+}
+
 static void sample_rows_large(const SampleArgs &a, int keep) {
     if (a.Lc != 1 || a.uncond_off || a.freq > 0.f || a.adj_a != 0.f)
         fatal("sampling: more than %d candidates (top_k=%d, V=%d) is supported for single-position rows "
               "without CFG or penalties only; set top_k <= %d", SM_MAXKEEP, a.top_k, a.V, SM_MAXKEEP);
+    if (keep == a.V && sample_rows_select(a)) return;
     static Workspace ws;
     const int64_t n = (int64_t)a.Bn * a.V;
     // One row: a device-wide 32-bit radix sort. More rows: ONE device-wide sort of all rows on composite keys
@@ -717,6 +1075,24 @@ void sample_rows(const SampleArgs &a) {
 }
 
 } // namespace ncmb
+
+// Diagnostic: the device sampler on caller-supplied DEVICE rows, one position per row, no CFG and no penalties --
+// sample_topkp's rule (src/kernels.c:794-825) with the uniform of row b taken from uniforms[b] (device doubles in
+// [0, 1)). picks: device int[B].
+extern "C" void ncmb_sample_rows_dev(const float *logits, int B, int V, float temp, int top_k, float top_p,
+                                     const double *uniforms, int *picks) {
+    using namespace ncmb;
+    ensure_device();
+    SampleArgs s{};
+    s.logits = logits; s.Bn = B; s.Lc = 1; s.V = V; s.temp = temp; s.top_k = top_k; s.top_p = top_p;
+    s.uniforms = uniforms; s.out = picks; s.out_stride = 1; s.out_off = 0; s.picks_bound = 1;
+    float *scr = nullptr;
+    const size_t need = sample_scratch_floats(B, V);
+    if (need) { scr = (float *)dev_alloc(need * 4); s.scratch = scr; }
+    sample_rows(s);
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    if (scr) dev_free(scr);
+}
 
 // Host-side sampling helper of the reference kernel API (src/ncm.h:197): logits is a
 // host row; same algorithm and the same single uniform draw per call.

@@ -494,6 +494,79 @@ def test_nucleus_sampling_over_a_vocabulary_too_large_for_the_block_sampler(cuda
     cuda.ncmb_lm_close(m)
 
 
+def test_nucleus_draw_by_selection_equals_the_sorted_walk(cuda, tmp):
+    """The sort-free nucleus sampler (three-level descent over ordered keys with fixed-point probability mass) against
+    the sort-based one and the oracle: a 5 000-entry vocabulary, 40 rows, several temperature / top-p settings, plus rows
+    made of a few distinct logit values only, so that cuts and draws fall inside groups of tied entries."""
+    import orc
+    import synth
+    spec = synth.LMSpec("qwen_v5000", "qwen", 1, 64, 2, 1, 128, 5000, 64, rope_theta=1e6, rand_affine=1)
+    conf, w = synth.write_lm(spec, tmp)
+    cfg = cuda.load_config(conf)
+    m = cuda.ncmb_lm_open(cfg, w.encode(), 1, 0)
+    om = orc.LM(conf, w, True)
+    B, n_new = 40, 6
+    P = np.ascontiguousarray(synth.lm_prompts(spec, B, 7, 33))
+    try:
+        for (t, tp, sd) in ((0.7, 0.95, 9), (1.3, 0.5, 4), (1.0, 1.0, 2), (0.2, 0.999, 7)):
+            outs = {}
+            for mode in ("1", "0"):
+                os.environ["NCM_B200_SORT_SAMPLER"] = mode
+                out = np.zeros((B, n_new), np.int32)
+                cuda.ncmb_lm_generate(m, P.ctypes.data, B, P.shape[1], n_new, t, 0, tp, sd, -1, out.ctypes.data)
+                outs[mode] = out
+            assert np.array_equal(outs["0"], outs["1"]), (t, tp, np.argwhere(outs["0"] != outs["1"])[:5])
+            for b in (0, 17, 39):
+                want = om.generate(P[b], n_new, temp=t, top_k=0, top_p=tp, seed=sd)
+                assert (outs["0"][b] == want).all(), (t, tp, b, outs["0"][b], want)
+    finally:
+        os.environ.pop("NCM_B200_SORT_SAMPLER", None)
+    cuda.ncmb_lm_close(m)
+
+
+def test_selection_sampler_on_rows_of_tied_logits(cuda):
+    """Direct rows through sample_topkp's device twin: logits drawn from eight distinct values, so every key is held
+    by hundreds of tied entries and both the nucleus cut and the draw land inside tie groups (ties rank by index)."""
+    import ctypes as C
+    import orc
+    if not cuda.has("ncmb_sample_rows_dev"):
+        pytest.skip("device row sampler not exported")
+    rng = np.random.default_rng(12)
+    V, B = 6000, 24
+    vals = np.array([-3.0, -1.5, -0.25, 0.0, 0.5, 1.0, 2.0, 2.5], np.float32)
+    lg = vals[rng.integers(0, 8, size=(B, V))]
+    lg[3] = 1.25                                            # one constant row: a single key for the whole vocabulary
+    u = rng.random(B)
+    d_lg, d_u, d_out = cuda.to_backend(lg), cuda.to_backend(u.astype(np.float64)), cuda.alloc(B)
+    for (t, tp) in ((0.8, 0.9), (1.0, 0.35), (2.0, 1.0)):
+        got = {}
+        for mode in ("1", "0"):
+            os.environ["NCM_B200_SORT_SAMPLER"] = mode
+            cuda.ncmb_sample_rows_dev(d_lg, B, V, t, 0, tp, d_u, d_out)
+            got[mode] = cuda.to_host(d_out, (B,), np.int32)
+        os.environ.pop("NCM_B200_SORT_SAMPLER", None)
+        assert np.array_equal(got["0"], got["1"]), (t, tp, got)
+        for b in range(B):
+            # the oracle's walk with the same uniform: a stable descending order (ties by ascending index)
+            w_ = (lg[b] / np.float32(t)).astype(np.float32)
+            order = np.argsort(-w_.astype(np.float64), kind="stable")
+            p = np.exp(w_[order].astype(np.float64) - float(w_[order[0]]))
+            p /= p.sum()
+            cum, nkeep = 0.0, V
+            for r in range(V):
+                if cum - p[r] > tp:
+                    nkeep = r
+                    break
+                cum += p[r]
+            den = p[:nkeep].sum()
+            acc, pick = 0.0, order[nkeep - 1]
+            x = u[b] * den
+            c = np.cumsum(p[:nkeep])
+            j = int(np.searchsorted(c, x, side="left"))
+            pick = order[min(j, nkeep - 1)]
+            assert got["0"][b] == pick, (t, tp, b, got["0"][b], pick)
+
+
 @pytest.mark.parametrize("kind", sorted(PPL_SPECS))
 def test_decoder_lm_likelihood_and_fixture_commands(cuda, tmp, kind, capfd):
     """ncmb_lm_nll, *_cmd_ppl and *_cmd_verify against the oracle's window likelihood (reference gpt2_nll / qwen_nll)."""
