@@ -154,6 +154,15 @@ struct GemmArgs {
     float *y2 = nullptr; int y2_col0 = 0; int64_t ldy2 = 0; const int *y2_step_d = nullptr; int64_t y2_step = 0;
     //  * W16: an exact bf16 copy of W ([N][K]); the GEMV kernel streams it instead of W (other engines ignore it)
     const unsigned short *W16 = nullptr;
+    // up to four rows on the warp-per-row-pair GEMV only (gemv_warp_takes()):
+    //  * gv_pair_half > 0: W holds gate rows [0, half) then up rows [half, 2*half) (N = 2*half); the result is
+    //    y[m][j] = act(x.W_j + b_j) * (x.W_{half+j} + b_{half+j}), `half` columns wide
+    //  * gv_rope_cos set: columns [0, gv_rope_cols) are heads of width gv_hd whose halves (d, d + gv_hd/2) are
+    //    rotated with table row gv_rope_pos[(*gv_rope_step_d) * gv_rope_pos_step + m] before anything is stored
+    int gv_pair_half = 0;
+    const float *gv_rope_cos = nullptr, *gv_rope_sin = nullptr;
+    const int *gv_rope_pos = nullptr, *gv_rope_step_d = nullptr; int64_t gv_rope_pos_step = 0;
+    int gv_rope_cols = 0, gv_hd = 0;
     // nearest-row search instead of a stored product (tensor-core engine only): for every x row, the
     // W row n minimising colnorm[n] - 2 x.W_n, kept as min over packed (ordered distance << 32 | n).
     const float *argmin_colnorm = nullptr;
@@ -171,6 +180,7 @@ struct GemmArgs {
 void gemm(const GemmArgs &a);            // dispatches on ctx().gemm_mode and shape
 void gemm_simt(const GemmArgs &a);
 bool gemv_fusable(const GemmArgs &a);    // true when the call will run on the GEMV kernel (M <= 16, 16-byte rows)
+bool gemv_warp_takes(const GemmArgs &a); // ... on the warp-per-row-pair GEMV, which also takes the gv_* epilogues (M <= 4)
 bool gemm_tc_supported(const GemmArgs &a);
 void gemm_tc(const GemmArgs &a);
 // gemm mode 3: fp16 split pairs, three kind::f16 MMAs per k-step into two accumulators (gemm_h3.cu)

@@ -366,9 +366,280 @@ __global__ void __launch_bounds__(256) k_gemv(GemmDev a) {
     }
 }
 
+// ---- decode-step GEMV, up to four rows: one WARP per pair of weight rows ----
+// A decode step of one to four sequences is a chain of matrix-vector products whose only real cost is streaming
+// the weights once. Here a warp owns two weight rows at a time: lane l takes eight consecutive elements of every
+// 256-element chunk of K (one 16-byte load of bf16 weights, two of fp32), all loads of up to four chunks of both
+// rows are issued before any is used, partial sums are reduced by shuffles alone, and lane 0 finishes the pair --
+// so there is no block-wide reduction and no shared-memory traffic per output. The input rows are staged (and
+// normalised, when a norm is fused) in shared memory once per CTA; CTAs are persistent over the row pairs. Which
+// two rows form a pair is free, and three epilogues use that:
+//   plain   rows (2g, 2g + 1)
+//   gated   rows (g, half + g) of a [gate ; up] matrix: out[g] = act(gate) * up -- no separate gating pass
+//   rotary  rows (h*hd + d, h*hd + d + hd/2) of the query / key heads of a fused QKV projection: the pair is
+//           rotated before it is stored, and K|V columns go straight to the cache -- no rotation pass, no copy
+// Launched with programmatic stream serialization: the first loads of the first pair are issued before the wait
+// for the predecessor (weights are not written by any kernel of a decode step).
+struct GemvW {
+    const float *x; int64_t ldx;
+    const float *W; const unsigned short *W16;
+    const float *bias; const float *res; int64_t ldres;
+    float *y; int64_t ldy;
+    int M, N, K, act;
+    int ln_kind; const float *ln_w, *ln_b; float ln_eps;
+    float *y2; int y2_col0; int64_t ldy2; const int *y2_step_d; int64_t y2_step;
+    int pair_half;
+    const float *rope_cos, *rope_sin; const int *rope_pos, *rope_step_d; int64_t rope_pos_step; int rope_cols, hd;
+    int ngroups;
+};
+
+constexpr int GW_U = 4;                      // chunks of 256 elements whose loads are in flight together
+
+template <bool W16>
+struct GwTile { uint4 a[GW_U], b[GW_U]; };   // fp32 weights: a = elements 0..3, b = elements 4..7 of the lane's eight; bf16: a only
+
+template <bool W16>
+__device__ __forceinline__ void gw_load(const GemvW &p, int64_t row, int c0, int lane, GwTile<W16> &t) {
+#pragma unroll
+    for (int u = 0; u < GW_U; u++) {
+        const int k = (c0 + u) * 256 + lane * 8;
+        if (k < p.K) {
+            if (W16) t.a[u] = __ldg((const uint4 *)(p.W16 + row * p.K + k));
+            else {
+                t.a[u] = __ldg((const uint4 *)(p.W + row * p.K + k));
+                t.b[u] = __ldg((const uint4 *)(p.W + row * p.K + k + 4));
+            }
+        }
+    }
+}
+
+template <bool W16>
+__device__ __forceinline__ void gw_w8(const GwTile<W16> &t, int u, float *w) {
+    if (W16) {
+        w[0] = __uint_as_float(t.a[u].x << 16); w[1] = __uint_as_float(t.a[u].x & 0xffff0000u);
+        w[2] = __uint_as_float(t.a[u].y << 16); w[3] = __uint_as_float(t.a[u].y & 0xffff0000u);
+        w[4] = __uint_as_float(t.a[u].z << 16); w[5] = __uint_as_float(t.a[u].z & 0xffff0000u);
+        w[6] = __uint_as_float(t.a[u].w << 16); w[7] = __uint_as_float(t.a[u].w & 0xffff0000u);
+    } else {
+        w[0] = __uint_as_float(t.a[u].x); w[1] = __uint_as_float(t.a[u].y); w[2] = __uint_as_float(t.a[u].z); w[3] = __uint_as_float(t.a[u].w);
+        w[4] = __uint_as_float(t.b[u].x); w[5] = __uint_as_float(t.b[u].y); w[6] = __uint_as_float(t.b[u].z); w[7] = __uint_as_float(t.b[u].w);
+    }
+}
+
+// the two weight rows of pair g
+__device__ __forceinline__ void gw_rows(const GemvW &p, int g, int &r0, int &r1) {
+    if (p.pair_half) { r0 = g; r1 = g + p.pair_half; return; }
+    const int half = p.hd >> 1, gr = p.rope_cols >> 1;
+    if (p.rope_cos && g < gr) { r0 = (g / half) * p.hd + g % half; r1 = r0 + half; return; }
+    r0 = p.rope_cols + 2 * (g - (p.rope_cos ? gr : 0));
+    if (!p.rope_cos) r0 = 2 * g;
+    r1 = r0 + 1;
+}
+
+template <int MT, bool W16>
+__global__ void __launch_bounds__(512) k_gemv_warp(GemvW p) {
+    extern __shared__ __align__(16) float gw_xs[];          // [MT][K] input rows (normalised), then 64 floats of reduction scratch
+    float *red = gw_xs + (size_t)MT * p.K;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarp = blockDim.x >> 5;
+    pdl_launch_dependents();
+    const int nch = (p.K + 255) >> 8;
+    int g = blockIdx.x * nwarp + warp;
+    const int gstride = gridDim.x * nwarp;
+    GwTile<W16> t0, t1;
+    int r0 = 0, r1 = 0;
+    if (g < p.ngroups) {
+        gw_rows(p, g, r0, r1);
+        gw_load<W16>(p, r0, 0, lane, t0);
+        gw_load<W16>(p, min(r1, p.N - 1), 0, lane, t1);
+    }
+    pdl_wait();
+    // ---- stage (and normalise) the input rows ----
+    for (int i = tid * 4; i < MT * p.K; i += blockDim.x * 4) {
+        const int m = i / p.K, k = i - m * p.K;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < p.M) v = *(const float4 *)(p.x + (int64_t)m * p.ldx + k);
+        *(float4 *)(gw_xs + i) = v;
+    }
+    __syncthreads();
+    if (p.ln_kind) {
+        // statistics per row in two passes (mean, then squared deviations), as the stand-alone norm kernels take them
+        for (int m = 0; m < MT; m++) {
+            float mean = 0.f;
+            for (int pass = (p.ln_kind == 2 ? 1 : 0); pass < 2; pass++) {
+                float part = 0.f;
+                for (int k = tid * 4; k < p.K; k += blockDim.x * 4) {
+                    const float4 v = *(const float4 *)(gw_xs + (size_t)m * p.K + k);
+                    if (pass == 0) part += (v.x + v.y) + (v.z + v.w);
+                    else {
+                        const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+                        part += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                if (lane == 0) red[warp] = part;
+                __syncthreads();
+                float tot = 0.f;
+                for (int w = 0; w < nwarp; w++) tot += red[w];
+                tot /= (float)p.K;
+                __syncthreads();
+                if (pass == 0) mean = tot;
+                else {
+                    const float rs = 1.0f / sqrtf(tot + p.ln_eps);
+                    const float mu = p.ln_kind == 1 ? mean : 0.f;
+                    for (int k = tid * 4; k < p.K; k += blockDim.x * 4) {
+                        float4 v = *(float4 *)(gw_xs + (size_t)m * p.K + k);
+                        float4 lw = make_float4(1.f, 1.f, 1.f, 1.f), lb = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p.ln_w) lw = __ldg((const float4 *)(p.ln_w + k));
+                        if (p.ln_b) lb = __ldg((const float4 *)(p.ln_b + k));
+                        v.x = __fadd_rn(__fmul_rn(__fmul_rn(v.x - mu, rs), lw.x), lb.x);
+                        v.y = __fadd_rn(__fmul_rn(__fmul_rn(v.y - mu, rs), lw.y), lb.y);
+                        v.z = __fadd_rn(__fmul_rn(__fmul_rn(v.z - mu, rs), lw.z), lb.z);
+                        v.w = __fadd_rn(__fmul_rn(__fmul_rn(v.w - mu, rs), lw.w), lb.w);
+                        *(float4 *)(gw_xs + (size_t)m * p.K + k) = v;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // ---- row pairs ----
+    for (; g < p.ngroups; g += gstride) {
+        float acc0[MT], acc1[MT];
+#pragma unroll
+        for (int m = 0; m < MT; m++) { acc0[m] = 0.f; acc1[m] = 0.f; }
+        const int64_t rr1 = min(r1, p.N - 1);
+        for (int c0 = 0; c0 < nch; c0 += GW_U) {
+            if (c0 > 0) { gw_load<W16>(p, r0, c0, lane, t0); gw_load<W16>(p, rr1, c0, lane, t1); }
+#pragma unroll
+            for (int u = 0; u < GW_U; u++) {
+                const int k = (c0 + u) * 256 + lane * 8;
+                if (k < p.K) {
+                    float w0[8], w1[8];
+                    gw_w8<W16>(t0, u, w0);
+                    gw_w8<W16>(t1, u, w1);
+#pragma unroll
+                    for (int m = 0; m < MT; m++) {
+                        const float4 xa = *(const float4 *)(gw_xs + (size_t)m * p.K + k), xb = *(const float4 *)(gw_xs + (size_t)m * p.K + k + 4);
+                        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++) { acc0[m] = fmaf(xv[j], w0[j], acc0[m]); acc1[m] = fmaf(xv[j], w1[j], acc1[m]); }
+                    }
+                }
+            }
+        }
+        // the next pair's first loads go out before this pair's reduction and epilogue
+        const int gn = g + gstride;
+        int n0 = r0, n1 = r1;
+        const int c_r0 = r0, c_r1 = r1;
+        if (gn < p.ngroups) {
+            gw_rows(p, gn, n0, n1);
+            gw_load<W16>(p, n0, 0, lane, t0);
+            gw_load<W16>(p, min(n1, p.N - 1), 0, lane, t1);
+        }
+        r0 = n0; r1 = n1;
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], o);
+                acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], o);
+            }
+        }
+        if (lane == 0) {
+            const bool has1 = c_r1 < p.N;
+            const float b0 = p.bias ? p.bias[c_r0] : 0.f, b1 = (p.bias && has1) ? p.bias[c_r1] : 0.f;
+            const int gr = p.rope_cols >> 1;
+            const bool rot = p.rope_cos && !p.pair_half && (g < gr);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                if (m >= p.M) break;
+                float v0 = acc0[m] + b0, v1 = acc1[m] + b1;
+                if (p.pair_half) {
+                    p.y[(int64_t)m * p.ldy + g] = act_fn(v0, p.act) * v1;
+                    continue;
+                }
+                if (rot) {
+                    const int half = p.hd >> 1, d = c_r0 % p.hd;
+                    const int64_t pos = (int64_t)p.rope_pos[(p.rope_step_d ? (int64_t)(*p.rope_step_d) * p.rope_pos_step : 0) + m] * p.hd;
+                    const float c0v = p.rope_cos[pos + d], c1v = p.rope_cos[pos + d + half], s0v = p.rope_sin[pos + d], s1v = p.rope_sin[pos + d + half];
+                    const float y0 = __fadd_rn(__fmul_rn(v0, c0v), __fmul_rn(-v1, s0v));
+                    const float y1 = __fadd_rn(__fmul_rn(v1, c1v), __fmul_rn(v0, s1v));
+                    v0 = y0; v1 = y1;
+                }
+                v0 = act_fn(v0, p.act); v1 = act_fn(v1, p.act);
+                if (p.res) { v0 += p.res[(int64_t)m * p.ldres + c_r0]; if (has1) v1 += p.res[(int64_t)m * p.ldres + c_r1]; }
+                p.y[(int64_t)m * p.ldy + c_r0] = v0;
+                if (has1) p.y[(int64_t)m * p.ldy + c_r1] = v1;
+                if (p.y2) {
+                    const int64_t base = (int64_t)m * p.ldy2 + (p.y2_step_d ? (int64_t)(*p.y2_step_d) * p.y2_step : 0);
+                    if (c_r0 >= p.y2_col0) p.y2[base + (c_r0 - p.y2_col0)] = v0;
+                    if (has1 && c_r1 >= p.y2_col0) p.y2[base + (c_r1 - p.y2_col0)] = v1;
+                }
+            }
+        }
+    }
+}
+
+bool gemv_warp_takes(const GemmArgs &g) {
+    static const bool off = getenv("NCM_B200_OLD_GEMV") != nullptr;
+    if (off || !gemv_fusable(g)) return false;
+    if (g.M > 4 || (g.K % 8) != 0 || g.K < 64) return false;
+    if (g.res && g.res == g.y && g.gv_pair_half) return false;
+    if (g.W16 && (((uintptr_t)g.W16 & 15) != 0)) return false;
+    const size_t smem = (size_t)(g.M <= 1 ? 1 : g.M <= 2 ? 2 : 4) * g.K * 4 + 256;
+    return smem <= 200 * 1024;
+}
+
+template <int MT, bool W16>
+static void launch_gemv_warp(const GemvW &p, int threads, int grid, size_t smem) {
+    static size_t set = 0;
+    if (smem > set) {
+        CUDA_CHECK(cudaFuncSetAttribute((k_gemv_warp<MT, W16>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(200 * 1024)));
+        set = 200 * 1024;
+    }
+    LAUNCH_PDL((k_gemv_warp<MT, W16>), grid, threads, smem, p);
+}
+
+static void gemv_warp(const GemmArgs &g) {
+    GemvW p;
+    p.x = g.x; p.ldx = g.ldx ? g.ldx : g.K; p.W = g.W; p.W16 = g.W16; p.bias = g.bias;
+    p.res = g.res; p.ldres = g.ldres ? g.ldres : g.N;
+    p.y = g.y; p.ldy = g.ldy ? g.ldy : (g.gv_pair_half ? g.gv_pair_half : g.N);
+    p.M = (int)g.M; p.N = g.N; p.K = g.K; p.act = g.act;
+    p.ln_kind = g.ln_kind; p.ln_w = g.ln_w; p.ln_b = g.ln_b; p.ln_eps = g.ln_eps;
+    p.y2 = g.y2; p.y2_col0 = g.y2_col0; p.ldy2 = g.ldy2; p.y2_step_d = g.y2_step_d; p.y2_step = g.y2_step;
+    p.pair_half = g.gv_pair_half;
+    p.rope_cos = g.gv_rope_cos; p.rope_sin = g.gv_rope_sin; p.rope_pos = g.gv_rope_pos; p.rope_step_d = g.gv_rope_step_d;
+    p.rope_pos_step = g.gv_rope_pos_step; p.rope_cols = g.gv_rope_cos ? g.gv_rope_cols : 0; p.hd = g.gv_hd > 0 ? g.gv_hd : 2;
+    if (p.pair_half && g.N != 2 * p.pair_half) fatal("gemv: gated pairs need N = 2 * half");
+    if (p.rope_cos && ((p.rope_cols % p.hd) || (p.hd & 1) || ((g.N - p.rope_cols) & 1))) fatal("gemv: rotary heads do not tile the columns");
+    p.ngroups = p.pair_half ? p.pair_half : (g.N + 1) / 2;
+    const int mt = g.M <= 1 ? 1 : g.M <= 2 ? 2 : 4;
+    const size_t smem = (size_t)mt * g.K * 4 + 256;
+    // warps per CTA: as many as still leave every SM a CTA; CTAs: one or two per SM, persistent over the pairs
+    const int sms = ctx().sm_count;
+    int threads = 512;
+    while (threads > 128 && (p.ngroups + (threads / 32) - 1) / (threads / 32) < sms) threads >>= 1;
+    const int per_sm = smem > 100 * 1024 ? 1 : 2;
+    int grid = (p.ngroups + (threads / 32) - 1) / (threads / 32);
+    if (grid > sms * per_sm) grid = sms * per_sm;
+    if (grid < 1) grid = 1;
+    const bool w16 = g.W16 != nullptr;
+    if (mt == 1) { if (w16) launch_gemv_warp<1, true>(p, threads, grid, smem); else launch_gemv_warp<1, false>(p, threads, grid, smem); }
+    else if (mt == 2) { if (w16) launch_gemv_warp<2, true>(p, threads, grid, smem); else launch_gemv_warp<2, false>(p, threads, grid, smem); }
+    else { if (w16) launch_gemv_warp<4, true>(p, threads, grid, smem); else launch_gemv_warp<4, false>(p, threads, grid, smem); }
+}
+
 void gemm_simt(const GemmArgs &g) {
     if (g.M <= 0 || g.N <= 0) return;
     if (g.glu) fatal("gemm_simt: fused gated epilogue is a tensor-core engine feature");
+    if (gemv_warp_takes(g)) {
+        ProfScope ps(NCMB_K_GEMM, 2.0 * (double)g.M * g.N * g.K, (g.W16 ? 2.0 : 4.0) * (double)g.N * g.K);
+        gemv_warp(g);
+        return;
+    }
+    if (g.gv_pair_half || g.gv_rope_cos) fatal("gemm_simt: gated-pair / rotary epilogue on a call the warp GEMV does not take");
     GemmDev d;
     d.x = g.x; d.ldx = g.ldx ? g.ldx : g.K;
     d.W = g.W; d.bias = g.bias;

@@ -102,10 +102,17 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     g.ln_kind = w.norm == NORM_RMS ? 2 : 1; g.ln_w = w.ln1w; g.ln_b = w.ln1b; g.ln_eps = w.norm == NORM_RMS ? 1e-6f : w.eps;
     static const bool fuse_small = !getenv("NCM_B200_NO_GEMV_FUSE");
     const bool small = fuse_small && !split && gemv_fusable(g);
-    bool kv_written = false;
+    bool kv_written = false, qk_done = false;
     g.W16 = w.qkvw16;
     if (small) {
-        if (p.kv_store && !w.qnw && !p.cos_t && p.kv_rows_per_seq == 1) {
+        // up to four rows: the warp-per-row-pair GEMV also rotates the query / key heads in its epilogue, so the
+        // rotation pass and the cache copy of a decode step disappear (per-head norms keep their own pass)
+        if (p.cos_t && !w.qnw && !w.knw && (hd & 1) == 0 && gemv_warp_takes(g)) {
+            g.gv_rope_cos = p.cos_t; g.gv_rope_sin = p.sin_t; g.gv_rope_pos = p.pos; g.gv_rope_step_d = p.step_d;
+            g.gv_rope_pos_step = p.pos_step; g.gv_rope_cols = C + kvd; g.gv_hd = hd;
+            qk_done = true;
+        }
+        if (p.kv_store && !w.qnw && !w.knw && (!p.cos_t || qk_done) && p.kv_rows_per_seq == 1) {
             g.y2 = p.kv_store; g.y2_col0 = C; g.ldy2 = p.kv_seq_pitch; g.y2_step_d = p.step_d; g.y2_step = p.kv_store_step;
             kv_written = true;
         }
@@ -116,7 +123,6 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         g.x = b.ln; g.x_lo = ln_lo;
     }
     // head dim 64: the GEMM's epilogue can apply the per-head norm and the rotation itself (it says whether it did)
-    bool qk_done = false;
     if (hd == 64 && !small && !p.step_d && (w.qnw || w.knw || p.cos_t)) {
         g.qk_heads = H + nkv; g.qk_H = H; g.qk_qw = w.qnw; g.qk_kw = w.knw; g.qk_cos = p.cos_t; g.qk_sin = p.sin_t; g.qk_pos = p.pos;
         g.qk_applied = &qk_done;
@@ -164,7 +170,12 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         g.x_fmt = fmt; g.y_fmt = fmt;
         g.x = b.ln; g.x_lo = ln_lo;
     }
-    if (w.gated) {
+    if (w.gated && small && w.fcw && gemv_warp_takes(g)) {
+        // up to four rows: gate and up rows are paired inside the GEMV, the gated product leaves from its epilogue
+        g.W = w.fcw; g.W16 = w.fcw16; g.bias = w.fcb; g.N = 2 * w.Hh; g.gv_pair_half = w.Hh; g.act = w.act; g.y = b.h; g.ldy = w.Hh;
+        gemm(g);
+        h_lo = nullptr;
+    } else if (w.gated) {
         GemmArgs t = g;
         t.W = w.fcw_il; t.bias = w.fcb_il; t.N = 2 * w.Hh; t.glu = 1; t.act = w.act; t.y = b.h; t.ldy = w.Hh;
         static const bool fuse_glu = !getenv("NCM_B200_NO_GLU_FUSE");
