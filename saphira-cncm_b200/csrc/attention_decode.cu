@@ -253,6 +253,169 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     if (tid == 0) a.count[row * a.Hkv + kvh] = 0;          // ready for the next launch
 }
 
+// ---- head dim 64: one WARP per 32-key chunk ----
+// The kernel above gives every 32-key chunk a CTA, three block-wide barriers per chunk, and merges all chunk
+// partials of a row through global memory; at one sequence that chain of barriers and L2 round trips is the kernel
+// (16 us per layer for 800 cached keys of the 14-query-head / 2-kv-head shape). Here a CTA of four or eight warps
+// covers 128 or 256 consecutive keys and a warp works alone on its 32: the lane holding key j forms that key's
+// scores with all G query heads of the kv group (q broadcast from shared memory), the softmax statistics of the
+// chunk are warp shuffles, and for O += P V the lanes switch to owning two output dimensions each while the
+// probabilities travel by shuffle -- K and V rows are requested before anything is computed and no barrier is
+// needed until the warps' partials (maximum, sum, context) meet in shared memory. One partial per CTA goes to
+// global memory, and only when the row needs more than one CTA.
+constexpr int ADW_MAXW = 8;
+
+template <int GM>
+__global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev a) {
+    constexpr int HD = 64;
+    __shared__ __align__(16) float qs[GM][HD];
+    __shared__ float pm[ADW_MAXW][GM], pl[ADW_MAXW][GM];
+    __shared__ __align__(8) float po[ADW_MAXW][GM][HD];
+    __shared__ float Mg[GM], Lg[GM], wg[ADW_MAXW][GM];
+    __shared__ int s_last;
+    const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
+    const int Gh = a.H / a.Hkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int *lens = a.k_len ? a.k_len + (a.step_d ? (int64_t)(*a.step_d) * a.len_step : 0) : nullptr;
+    const int k00 = a.k_start[row], n1s = lens ? lens[row] : a.k_start[row + 1] - k00;
+    const int k20 = a.k2_start ? a.k2_start[row] : 0, n2s = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
+    const int n1 = n1s + n2s;
+    const int per_cta = nw * 32;
+    const int nsplit = (n1 + per_cta - 1) / per_cta;
+    if (sp >= nsplit) return;
+    const int kw = sp * per_cta + warp * 32;              // first key of this warp's chunk
+    const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
+    const int G = Gh * nq;                                // virtual heads: vh = g * nq + qi
+    auto krow = [&](int j) -> const float * {
+        return j < n1s ? a.k + (int64_t)(k00 + j) * a.ldk : a.k2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
+    auto vrow = [&](int j) -> const float * {
+        return j < n1s ? a.v + (int64_t)(k00 + j) * a.ldk : a.v2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        const int vh = i / HD, d = i % HD;
+        qs[vh][d] = a.q[(int64_t)(q0 + vh % nq) * a.ldq + (kvh * Gh + vh / nq) * HD + d];
+    }
+    // every load of the chunk is requested now: the lane's key row, and for the context step the two dimensions
+    // (2 lane, 2 lane + 1) of all 32 value rows
+    const bool valid = kw + lane < n1;
+    float4 kr[HD / 4];
+    {
+        const float4 *kp = (const float4 *)(krow(valid ? kw + lane : 0) + kvh * HD);
+#pragma unroll
+        for (int i = 0; i < HD / 4; i++) kr[i] = valid ? kp[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float2 vv[32];
+#pragma unroll
+    for (int jj = 0; jj < 32; jj++)
+        vv[jj] = (kw + jj < n1) ? *(const float2 *)(vrow(kw + jj) + kvh * HD + 2 * lane) : make_float2(0.f, 0.f);
+    __syncthreads();
+    float s[GM];
+#pragma unroll
+    for (int g = 0; g < GM; g++) {
+        s[g] = 0.f;
+        if (g < G) {                                          // block-uniform
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < HD / 4; i++) {
+                const float4 t = *(const float4 *)&qs[g][4 * i];   // one address for the whole warp: a broadcast
+                dot = fmaf(kr[i].x, t.x, dot); dot = fmaf(kr[i].y, t.y, dot); dot = fmaf(kr[i].z, t.z, dot); dot = fmaf(kr[i].w, t.w, dot);
+            }
+            const float sc = valid ? dot * a.scale : -INFINITY;
+            float m = sc;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            const float p = (sc == -INFINITY) ? 0.f : expf(sc - m);
+            float l = p;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            s[g] = p;
+            if (lane == 0) { pm[warp][g] = m; pl[warp][g] = l; }
+        }
+    }
+    float2 acc[GM];
+#pragma unroll
+    for (int g = 0; g < GM; g++) acc[g] = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int jj = 0; jj < 32; jj++) {
+#pragma unroll
+        for (int g = 0; g < GM; g++) {
+            const float pj = __shfl_sync(0xffffffffu, s[g], jj);
+            acc[g].x = fmaf(pj, vv[jj].x, acc[g].x); acc[g].y = fmaf(pj, vv[jj].y, acc[g].y);
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < GM; g++)
+        if (g < G) *(float2 *)&po[warp][g][2 * lane] = acc[g];
+    __syncthreads();
+    // ---- the warps' partials meet: maximum and weights per head, then the context columns ----
+    if (tid < G) {
+        float M = -INFINITY, L = 0.f;
+        for (int w = 0; w < nw; w++) M = fmaxf(M, pm[w][tid]);
+        for (int w = 0; w < nw; w++) {
+            const float e = (pm[w][tid] == -INFINITY) ? 0.f : expf(pm[w][tid] - M);
+            wg[w][tid] = e; L = fmaf(pl[w][tid], e, L);
+        }
+        Mg[tid] = M; Lg[tid] = L;
+    }
+    __syncthreads();
+    float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * AD_MAXG * (HD + 2);
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        float O = 0.f;
+        for (int w = 0; w < nw; w++) O = fmaf(po[w][g][d], wg[w][g], O);
+        if (nsplit == 1) {
+            const float L = Lg[g];
+            const float r = L > 0.f ? O / L : 0.f;
+            const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
+            if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+            else a.out[at] = r;
+        } else {
+            mine[g * (HD + 2) + 2 + d] = O;
+            if (d == 0) { mine[g * (HD + 2)] = Mg[g]; mine[g * (HD + 2) + 1] = Lg[g]; }
+        }
+    }
+    if (nsplit == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned old = atomicAdd(a.count + row * a.Hkv + kvh, 1u);
+        s_last = (old == (unsigned)(nsplit - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // the last CTA of the (row, kv head) merges the CTAs' partials (a handful: 128 or 256 keys each)
+    __shared__ float wsm[AD_MAXSPLIT][GM], lsm[AD_MAXSPLIT][GM];
+    const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * AD_MAXG * (HD + 2);
+    for (int i = tid; i < nsplit * G; i += blockDim.x) {
+        const int sidx = i / G, g = i % G;
+        const float *ps = base + ((int64_t)sidx * AD_MAXG + g) * (HD + 2);
+        wsm[sidx][g] = __ldcg(ps); lsm[sidx][g] = __ldcg(ps + 1);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY, L = 0.f;
+        for (int x = 0; x < nsplit; x++) M = fmaxf(M, wsm[x][tid]);
+        for (int x = 0; x < nsplit; x++) { const float w = expf(wsm[x][tid] - M); wsm[x][tid] = w; L = fmaf(lsm[x][tid], w, L); }
+        Lg[tid] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        float O = 0.f;
+        for (int x = 0; x < nsplit; x++) O = fmaf(__ldcg(base + ((int64_t)x * AD_MAXG + g) * (HD + 2) + 2 + d), wsm[x][g], O);
+        const float L = Lg[g];
+        const float r = L > 0.f ? O / L : 0.f;
+        const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
+        if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+        else a.out[at] = r;
+    }
+    if (tid == 0) a.count[row * a.Hkv + kvh] = 0;
+}
+
 bool attention_decode_supported(const AttnArgs &a) {
     if (a.max_q < 1 || a.max_q > 4 || a.causal || a.window > 0) return false;      // a few queries per row, no mask
     if (a.hd != 16 && a.hd != 32 && a.hd != 64 && a.hd != 128) return false;
@@ -272,6 +435,41 @@ void attention_decode(const AttnArgs &a) {
     // and not once per chunk.
     const int max_chunks = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
     const int64_t pairs = (int64_t)a.rows * a.Hkv;
+    static const bool warp_kernel = !getenv("NCM_B200_OLD_ATTN_DEC");
+    if (warp_kernel && a.hd == 64 && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0)) {
+        // warp-per-chunk kernel: four warps per CTA while that still gives the GPU fewer CTAs than SMs, else eight
+        const int nw = (pairs * cdiv(max_chunks, 4) <= (int64_t)ctx().sm_count) ? 4 : ADW_MAXW;
+        const int max_split = (int)cdiv(max_chunks, nw);
+        if (max_split <= AD_MAXSPLIT) {
+            size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
+            if (need > part_cap) {
+                if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
+                part = (float *)dev_alloc(need * 4); part_cap = need;
+            }
+            size_t nc = (size_t)a.rows * a.Hkv;
+            if (nc > count_cap) {
+                if (count) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(count); }
+                count = (unsigned *)dev_alloc(nc * 4); count_cap = nc;
+                CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
+            }
+            AttnDecDev d;
+            d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1;
+            d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
+            d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
+            d.step_d = a.step_d; d.len_step = a.k1_len_step;
+            d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split; d.cps = nw;
+            d.scale = 1.0f / sqrtf((float)a.hd);
+            d.part = part; d.count = count;
+            dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
+            ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+            const int gq = (a.H / a.Hkv) * a.max_q;
+            if (gq <= 1) LAUNCH_PDL((k_attention_dec_warp<1>), grid, nw * 32, 0, d);
+            else if (gq <= 4) LAUNCH_PDL((k_attention_dec_warp<4>), grid, nw * 32, 0, d);
+            else if (gq <= 8) LAUNCH_PDL((k_attention_dec_warp<8>), grid, nw * 32, 0, d);
+            else LAUNCH_PDL((k_attention_dec_warp<16>), grid, nw * 32, 0, d);
+            return;
+        }
+    }
     static const int per_sm = getenv("NCM_B200_ATTN_DEC_PER_SM") ? atoi(getenv("NCM_B200_ATTN_DEC_PER_SM")) : 8;
     int want_split = (int)std::min<int64_t>(max_chunks, cdiv((int64_t)ctx().sm_count * per_sm, pairs));
     if (want_split < 1) want_split = 1;

@@ -462,43 +462,40 @@ __global__ void __launch_bounds__(512) k_gemv_warp(GemvW p) {
     }
     __syncthreads();
     if (p.ln_kind) {
-        // statistics per row in two passes (mean, then squared deviations), as the stand-alone norm kernels take them
+        // Row statistics in two passes (mean, then squared deviations), as the stand-alone norm kernels take them.
+        // Every warp forms them for itself from the staged row -- a few dozen elements per lane and two shuffle
+        // reductions, the same value in every warp -- so no block-wide reduction is needed; the threads then
+        // normalise the row in place, each its own part.
         for (int m = 0; m < MT; m++) {
+            const float *xr = gw_xs + (size_t)m * p.K;
             float mean = 0.f;
-            for (int pass = (p.ln_kind == 2 ? 1 : 0); pass < 2; pass++) {
+            if (p.ln_kind == 1) {
                 float part = 0.f;
-                for (int k = tid * 4; k < p.K; k += blockDim.x * 4) {
-                    const float4 v = *(const float4 *)(gw_xs + (size_t)m * p.K + k);
-                    if (pass == 0) part += (v.x + v.y) + (v.z + v.w);
-                    else {
-                        const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
-                        part += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-                    }
-                }
+                for (int k = lane * 4; k < p.K; k += 128) { const float4 v = *(const float4 *)(xr + k); part += (v.x + v.y) + (v.z + v.w); }
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-                if (lane == 0) red[warp] = part;
-                __syncthreads();
-                float tot = 0.f;
-                for (int w = 0; w < nwarp; w++) tot += red[w];
-                tot /= (float)p.K;
-                __syncthreads();
-                if (pass == 0) mean = tot;
-                else {
-                    const float rs = 1.0f / sqrtf(tot + p.ln_eps);
-                    const float mu = p.ln_kind == 1 ? mean : 0.f;
-                    for (int k = tid * 4; k < p.K; k += blockDim.x * 4) {
-                        float4 v = *(float4 *)(gw_xs + (size_t)m * p.K + k);
-                        float4 lw = make_float4(1.f, 1.f, 1.f, 1.f), lb = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (p.ln_w) lw = __ldg((const float4 *)(p.ln_w + k));
-                        if (p.ln_b) lb = __ldg((const float4 *)(p.ln_b + k));
-                        v.x = __fadd_rn(__fmul_rn(__fmul_rn(v.x - mu, rs), lw.x), lb.x);
-                        v.y = __fadd_rn(__fmul_rn(__fmul_rn(v.y - mu, rs), lw.y), lb.y);
-                        v.z = __fadd_rn(__fmul_rn(__fmul_rn(v.z - mu, rs), lw.z), lb.z);
-                        v.w = __fadd_rn(__fmul_rn(__fmul_rn(v.w - mu, rs), lw.w), lb.w);
-                        *(float4 *)(gw_xs + (size_t)m * p.K + k) = v;
-                    }
-                }
+                mean = part / (float)p.K;
+            }
+            float part = 0.f;
+            for (int k = lane * 4; k < p.K; k += 128) {
+                const float4 v = *(const float4 *)(xr + k);
+                const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
+                part += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            const float rs = 1.0f / sqrtf(part / (float)p.K + p.ln_eps);
+            __syncthreads();                                  // every warp has read the raw row
+            for (int k = tid * 4; k < p.K; k += blockDim.x * 4) {
+                float4 v = *(float4 *)(gw_xs + (size_t)m * p.K + k);
+                float4 lw = make_float4(1.f, 1.f, 1.f, 1.f), lb = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (p.ln_w) lw = __ldg((const float4 *)(p.ln_w + k));
+                if (p.ln_b) lb = __ldg((const float4 *)(p.ln_b + k));
+                v.x = __fadd_rn(__fmul_rn(__fmul_rn(v.x - mean, rs), lw.x), lb.x);
+                v.y = __fadd_rn(__fmul_rn(__fmul_rn(v.y - mean, rs), lw.y), lb.y);
+                v.z = __fadd_rn(__fmul_rn(__fmul_rn(v.z - mean, rs), lw.z), lb.z);
+                v.w = __fadd_rn(__fmul_rn(__fmul_rn(v.w - mean, rs), lw.w), lb.w);
+                *(float4 *)(gw_xs + (size_t)m * p.K + k) = v;
             }
         }
         __syncthreads();
