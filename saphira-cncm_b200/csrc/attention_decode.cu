@@ -436,9 +436,17 @@ void attention_decode(const AttnArgs &a) {
     const int max_chunks = (int)cdiv(a.max_k1 + a.max_k2, AD_KEYS);
     const int64_t pairs = (int64_t)a.rows * a.Hkv;
     static const bool warp_kernel = !getenv("NCM_B200_OLD_ATTN_DEC");
-    if (warp_kernel && a.hd == 64 && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0)) {
-        // warp-per-chunk kernel: four warps per CTA while that still gives the GPU fewer CTAs than SMs, else eight
-        const int nw = (pairs * cdiv(max_chunks, 4) <= (int64_t)ctx().sm_count) ? 4 : ADW_MAXW;
+    const bool warp_always = getenv("NCM_B200_ATTN_DEC_WARP") != nullptr;       // read per call: tests run both kernels on the same inputs
+    // The warp-per-chunk kernel where it measured faster: one or two (query, head) pairs per kv head (a warp then
+    // has little arithmetic per key: GPT-2 at one sequence, 0.43 -> 0.40 ms per token) and few enough CTAs that
+    // all are resident at once. With seven heads per kv head a warp's serial arithmetic outweighs the barriers it
+    // saves (Qwen2 shape at one sequence: 1.10 -> 1.16 ms), and with hundreds of (row, kv head) pairs its 160
+    // registers per thread leave one CTA per SM (GPT-2 at 64 sequences: 1.44 -> 1.94 ms per step).
+    const int gq_w = (a.H / a.Hkv) * a.max_q;
+    const bool warp_pays = warp_always || (gq_w <= 2 && pairs * cdiv(max_chunks, 4) <= 2 * (int64_t)ctx().sm_count);
+    if (warp_kernel && warp_pays && a.hd == 64 && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0)) {
+        // four warps per CTA while that still gives the GPU fewer CTAs than SMs, else eight
+        const int nw = (pairs * cdiv(max_chunks, 4) <= 2 * (int64_t)ctx().sm_count) ? 4 : ADW_MAXW;
         const int max_split = (int)cdiv(max_chunks, nw);
         if (max_split <= AD_MAXSPLIT) {
             size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);

@@ -399,10 +399,10 @@ template <bool W16>
 struct GwTile { uint4 a[GW_U], b[GW_U]; };   // fp32 weights: a = elements 0..3, b = elements 4..7 of the lane's eight; bf16: a only
 
 template <bool W16>
-__device__ __forceinline__ void gw_load(const GemvW &p, int64_t row, int c0, int lane, GwTile<W16> &t) {
+__device__ __forceinline__ void gw_load(const GemvW &p, int64_t row, int c0, int lane, GwTile<W16> &t, int cstep = 1) {
 #pragma unroll
     for (int u = 0; u < GW_U; u++) {
-        const int k = (c0 + u) * 256 + lane * 8;
+        const int k = (c0 + u * cstep) * 256 + lane * 8;
         if (k < p.K) {
             if (W16) t.a[u] = __ldg((const uint4 *)(p.W16 + row * p.K + k));
             else {
@@ -434,6 +434,100 @@ __device__ __forceinline__ void gw_rows(const GemvW &p, int g, int &r0, int &r1)
     r0 = p.rope_cols + 2 * (g - (p.rope_cos ? gr : 0));
     if (!p.rope_cos) r0 = 2 * g;
     r1 = r0 + 1;
+}
+
+// lane 0 of the warp that holds the finished sums of pair g (rows c_r0, c_r1): bias, the pair's epilogue, stores
+template <int MT>
+__device__ __forceinline__ void gw_epilogue(const GemvW &p, int g, int c_r0, int c_r1, const float *acc0, const float *acc1) {
+    const bool has1 = c_r1 < p.N;
+    const float b0 = p.bias ? p.bias[c_r0] : 0.f, b1 = (p.bias && has1) ? p.bias[c_r1] : 0.f;
+    const int gr = p.rope_cols >> 1;
+    const bool rot = p.rope_cos && !p.pair_half && (g < gr);
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+        if (m >= p.M) break;
+        float v0 = acc0[m] + b0, v1 = acc1[m] + b1;
+        if (p.pair_half) {
+            p.y[(int64_t)m * p.ldy + g] = act_fn(v0, p.act) * v1;
+            continue;
+        }
+        if (rot) {
+            const int half = p.hd >> 1, d = c_r0 % p.hd;
+            const int64_t pos = (int64_t)p.rope_pos[(p.rope_step_d ? (int64_t)(*p.rope_step_d) * p.rope_pos_step : 0) + m] * p.hd;
+            const float c0v = p.rope_cos[pos + d], c1v = p.rope_cos[pos + d + half], s0v = p.rope_sin[pos + d], s1v = p.rope_sin[pos + d + half];
+            const float y0 = __fadd_rn(__fmul_rn(v0, c0v), __fmul_rn(-v1, s0v));
+            const float y1 = __fadd_rn(__fmul_rn(v1, c1v), __fmul_rn(v0, s1v));
+            v0 = y0; v1 = y1;
+        }
+        v0 = act_fn(v0, p.act); v1 = act_fn(v1, p.act);
+        if (p.res) { v0 += p.res[(int64_t)m * p.ldres + c_r0]; if (has1) v1 += p.res[(int64_t)m * p.ldres + c_r1]; }
+        p.y[(int64_t)m * p.ldy + c_r0] = v0;
+        if (has1) p.y[(int64_t)m * p.ldy + c_r1] = v1;
+        if (p.y2) {
+            const int64_t base = (int64_t)m * p.ldy2 + (p.y2_step_d ? (int64_t)(*p.y2_step_d) * p.y2_step : 0);
+            if (c_r0 >= p.y2_col0) p.y2[base + (c_r0 - p.y2_col0)] = v0;
+            if (has1 && c_r1 >= p.y2_col0) p.y2[base + (c_r1 - p.y2_col0)] = v1;
+        }
+    }
+}
+
+// Few row pairs and a long K (the attention-output and MLP-down projections of a decode step): a warp walking the
+// whole of K would issue its loads in several dependent rounds while most SMs idle. Here the eight warps of a CTA
+// share ONE row pair, warp w taking chunks w, w + 8, w + 16, ... of K (at most four, all in flight at once), each
+// lane reads its slice of the input rows straight from global memory, and the eight partial sums meet in shared
+// memory. No fused norm on this path (the projections that use it take an un-normalised input).
+template <int MT, bool W16>
+__global__ void __launch_bounds__(256) k_gemv_ksplit(GemvW p) {
+    __shared__ float part[8][MT][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = blockIdx.x;
+    pdl_launch_dependents();
+    int r0, r1;
+    gw_rows(p, g, r0, r1);
+    GwTile<W16> t0, t1;
+    gw_load<W16>(p, r0, warp, lane, t0, 8);
+    gw_load<W16>(p, min(r1, p.N - 1), warp, lane, t1, 8);
+    pdl_wait();
+    float acc0[MT], acc1[MT];
+#pragma unroll
+    for (int m = 0; m < MT; m++) { acc0[m] = 0.f; acc1[m] = 0.f; }
+#pragma unroll
+    for (int u = 0; u < GW_U; u++) {
+        const int k = (warp + 8 * u) * 256 + lane * 8;
+        if (k < p.K) {
+            float w0[8], w1[8];
+            gw_w8<W16>(t0, u, w0);
+            gw_w8<W16>(t1, u, w1);
+#pragma unroll
+            for (int m = 0; m < MT; m++) {
+                if (m < p.M) {
+                    const float4 xa = *(const float4 *)(p.x + (int64_t)m * p.ldx + k), xb = *(const float4 *)(p.x + (int64_t)m * p.ldx + k + 4);
+                    const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                    for (int j = 0; j < 8; j++) { acc0[m] = fmaf(xv[j], w0[j], acc0[m]); acc1[m] = fmaf(xv[j], w1[j], acc1[m]); }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MT; m++) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            acc0[m] += __shfl_xor_sync(0xffffffffu, acc0[m], o);
+            acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], o);
+        }
+        if (lane == 0) { part[warp][m][0] = acc0[m]; part[warp][m][1] = acc1[m]; }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int m = 0; m < MT; m++) {
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) { a0 += part[w][m][0]; a1 += part[w][m][1]; }
+            acc0[m] = a0; acc1[m] = a1;
+        }
+        gw_epilogue<MT>(p, g, r0, r1, acc0, acc1);
+    }
 }
 
 template <int MT, bool W16>
@@ -543,38 +637,7 @@ __global__ void __launch_bounds__(512) k_gemv_warp(GemvW p) {
                 acc1[m] += __shfl_xor_sync(0xffffffffu, acc1[m], o);
             }
         }
-        if (lane == 0) {
-            const bool has1 = c_r1 < p.N;
-            const float b0 = p.bias ? p.bias[c_r0] : 0.f, b1 = (p.bias && has1) ? p.bias[c_r1] : 0.f;
-            const int gr = p.rope_cols >> 1;
-            const bool rot = p.rope_cos && !p.pair_half && (g < gr);
-#pragma unroll
-            for (int m = 0; m < MT; m++) {
-                if (m >= p.M) break;
-                float v0 = acc0[m] + b0, v1 = acc1[m] + b1;
-                if (p.pair_half) {
-                    p.y[(int64_t)m * p.ldy + g] = act_fn(v0, p.act) * v1;
-                    continue;
-                }
-                if (rot) {
-                    const int half = p.hd >> 1, d = c_r0 % p.hd;
-                    const int64_t pos = (int64_t)p.rope_pos[(p.rope_step_d ? (int64_t)(*p.rope_step_d) * p.rope_pos_step : 0) + m] * p.hd;
-                    const float c0v = p.rope_cos[pos + d], c1v = p.rope_cos[pos + d + half], s0v = p.rope_sin[pos + d], s1v = p.rope_sin[pos + d + half];
-                    const float y0 = __fadd_rn(__fmul_rn(v0, c0v), __fmul_rn(-v1, s0v));
-                    const float y1 = __fadd_rn(__fmul_rn(v1, c1v), __fmul_rn(v0, s1v));
-                    v0 = y0; v1 = y1;
-                }
-                v0 = act_fn(v0, p.act); v1 = act_fn(v1, p.act);
-                if (p.res) { v0 += p.res[(int64_t)m * p.ldres + c_r0]; if (has1) v1 += p.res[(int64_t)m * p.ldres + c_r1]; }
-                p.y[(int64_t)m * p.ldy + c_r0] = v0;
-                if (has1) p.y[(int64_t)m * p.ldy + c_r1] = v1;
-                if (p.y2) {
-                    const int64_t base = (int64_t)m * p.ldy2 + (p.y2_step_d ? (int64_t)(*p.y2_step_d) * p.y2_step : 0);
-                    if (c_r0 >= p.y2_col0) p.y2[base + (c_r0 - p.y2_col0)] = v0;
-                    if (has1 && c_r1 >= p.y2_col0) p.y2[base + (c_r1 - p.y2_col0)] = v1;
-                }
-            }
-        }
+        if (lane == 0) gw_epilogue<MT>(p, g, c_r0, c_r1, acc0, acc1);
     }
 }
 
@@ -616,13 +679,25 @@ static void gemv_warp(const GemmArgs &g) {
     const size_t smem = (size_t)mt * g.K * 4 + 256;
     // warps per CTA: as many as still leave every SM a CTA; CTAs: one or two per SM, persistent over the pairs
     const int sms = ctx().sm_count;
+    static const int thr_env = getenv("NCM_B200_GW_THREADS") ? atoi(getenv("NCM_B200_GW_THREADS")) : 0;     // A/B knobs
+    static const int psm_env = getenv("NCM_B200_GW_PER_SM") ? atoi(getenv("NCM_B200_GW_PER_SM")) : 0;
     int threads = 512;
     while (threads > 128 && (p.ngroups + (threads / 32) - 1) / (threads / 32) < sms) threads >>= 1;
-    const int per_sm = smem > 100 * 1024 ? 1 : 2;
+    if (thr_env >= 32 && thr_env <= 512) threads = thr_env;
+    const int per_sm = psm_env > 0 ? psm_env : (smem > 100 * 1024 ? 1 : 2);
     int grid = (p.ngroups + (threads / 32) - 1) / (threads / 32);
     if (grid > sms * per_sm) grid = sms * per_sm;
     if (grid < 1) grid = 1;
     const bool w16 = g.W16 != nullptr;
+    // few pairs, long K, no fused norm: the eight warps of a CTA share one pair (see k_gemv_ksplit)
+    static const bool ksplit_ok = !getenv("NCM_B200_NO_GEMV_KSPLIT");
+    const int nch = (g.K + 255) / 256;
+    if (ksplit_ok && !g.ln_kind && nch > GW_U && nch <= 8 * GW_U && p.ngroups <= sms * 8) {
+        if (mt == 1) { if (w16) LAUNCH_PDL((k_gemv_ksplit<1, true>), p.ngroups, 256, 0, p); else LAUNCH_PDL((k_gemv_ksplit<1, false>), p.ngroups, 256, 0, p); }
+        else if (mt == 2) { if (w16) LAUNCH_PDL((k_gemv_ksplit<2, true>), p.ngroups, 256, 0, p); else LAUNCH_PDL((k_gemv_ksplit<2, false>), p.ngroups, 256, 0, p); }
+        else { if (w16) LAUNCH_PDL((k_gemv_ksplit<4, true>), p.ngroups, 256, 0, p); else LAUNCH_PDL((k_gemv_ksplit<4, false>), p.ngroups, 256, 0, p); }
+        return;
+    }
     if (mt == 1) { if (w16) launch_gemv_warp<1, true>(p, threads, grid, smem); else launch_gemv_warp<1, false>(p, threads, grid, smem); }
     else if (mt == 2) { if (w16) launch_gemv_warp<2, true>(p, threads, grid, smem); else launch_gemv_warp<2, false>(p, threads, grid, smem); }
     else { if (w16) launch_gemv_warp<4, true>(p, threads, grid, smem); else launch_gemv_warp<4, false>(p, threads, grid, smem); }

@@ -103,8 +103,18 @@ DECODE_CASES = {
 }
 
 
+@pytest.fixture(params=["chosen", "warp_per_chunk"])
+def decode_kernel(request):
+    """the split-key path as dispatched, and with the warp-per-chunk kernel forced for every shape it takes"""
+    import os
+    if request.param == "warp_per_chunk":
+        os.environ["NCM_B200_ATTN_DEC_WARP"] = "1"
+    yield request.param
+    os.environ.pop("NCM_B200_ATTN_DEC_WARP", None)
+
+
 @pytest.mark.parametrize("name", sorted(DECODE_CASES))
-def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name):
+def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name, decode_kernel):
     lens, H, Hkv = DECODE_CASES[name]
     rng = np.random.default_rng(sum(map(ord, name)))
     rows = len(lens)
@@ -128,7 +138,7 @@ def test_split_key_decode_attention_matches_cuda_core_and_float64(cuda, name):
     assert np.array_equal(cuda.to_host(od, q.shape), got[2])
 
 
-def test_split_key_attention_with_a_few_queries_and_two_key_segments(cuda):
+def test_split_key_attention_with_a_few_queries_and_two_key_segments(cuda, decode_kernel):
     # the first NCP levels: 1 or 4 new tokens per row attend to the cached prefix and to themselves
     rng = np.random.default_rng(77)
     qlens, k1lens, H, Hkv = [1, 4, 3, 4], [250, 3, 77, 1], 8, 2
