@@ -53,6 +53,9 @@ struct AttnTcDev {
     // block's maximum (log2 domain, scaled) and sum to ml, for k_attention_merge to combine the blocks
     int kb_off, kb_len;
     float *ml;
+    // 1: the value tiles stay in their natural [key][dim] order and the P V MMAs read them as an MN-major B operand
+    // (no transpose: a thread converts one float4 to four hi and four lo halves); 0: transposed on chip into [dim][key]
+    int v_mn;
 };
 
 // byte offset of element (row, col) in a K-major tile of 32 floats per row with 128-byte swizzle
@@ -267,10 +270,14 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 const uint64_t p1 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF)), p2 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF + 16384));
                 const uint64_t v1 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF)), v2 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF + 8192));
                 const int nk = (nchunks - 2 * c2 >= 2) ? 4 : 2;                                   // 16 keys per MMA
+                // 16 keys further along: 32 bytes in a [row][key] tile (P, transposed V), two 8-key groups of 1024 bytes
+                // in a [key][dim] tile read as an MN-major operand
+                const uint64_t vstep = a.v_mn ? 128u : 2u;
+                const uint32_t idv = a.v_mn ? (idesc | (1u << 16)) : idesc;
                 for (int k = 0; k < nk; k++) {
-                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, (c2 | k) ? 1u : 0u);
-                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)(k * 2), idesc, (c2 | k) ? 1u : 0u);
-                    umma_f16(dc, p2 + (uint64_t)(k * 2), v1 + (uint64_t)(k * 2), idesc, 1u);
+                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)k * vstep, idv, (c2 | k) ? 1u : 0u);
+                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)k * vstep, idv, (c2 | k) ? 1u : 0u);
+                    umma_f16(dc, p2 + (uint64_t)(k * 2), v1 + (uint64_t)k * vstep, idv, 1u);
                 }
                 umma_commit(bar_pv0 + 8 * b);
             }
@@ -367,7 +374,19 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                     *(uint4 *)(Pb + 16384 + o) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
                 }
                 w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
-                {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
+                if (a.v_mn) {   // split only: Vraw[key][d] (two 32-column atoms) -> pair tiles [key][d], one float4 per thread
+                    const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
+                    const int c0 = c * 32;
+                    const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
+                    const int vk = tid >> 4, d4 = tid & 15;                   // key of the chunk, which four dims
+                    float4 x = *(const float4 *)(Vraw + (d4 >> 3) * 4096 + sw128_off(vk, (d4 & 7) * 4));
+                    if (vk >= nvalid) x = make_float4(0.f, 0.f, 0.f, 0.f);
+                    unsigned short h0, l0, h1, l1, h2, l2, h3, l3;
+                    h16_pair(x.x, h0, l0); h16_pair(x.y, h1, l1); h16_pair(x.z, h2, l2); h16_pair(x.w, h3, l3);
+                    const uint32_t o = sw128_boff(hf * 32 + vk, d4 * 8);
+                    *(uint2 *)(Vt + o) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
+                    *(uint2 *)(Vt + 8192 + o) = make_uint2((uint32_t)l0 | ((uint32_t)l1 << 16), (uint32_t)l2 | ((uint32_t)l3 << 16));
+                } else {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
                     const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
                     const int c0 = c * 32;
                     const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
@@ -456,6 +475,8 @@ static void attention_tc_launch(const AttnArgs &a, float *out, float *out_lo, in
     d.scale = 1.0f / sqrtf(64.0f);
     d.err = tc_err_flag();
     d.kb_off = kb_off; d.kb_len = kb_len; d.ml = ml;
+    static const int v_mn = getenv("NCM_B200_ATTN_VT") ? 0 : 1;       // A/B: NCM_B200_ATTN_VT=1 keeps the on-chip transpose
+    d.v_mn = v_mn;
     const int G = a.H / a.Hkv;
     d.pack = (!ml && a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
     const CUtensorMap mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);

@@ -40,7 +40,9 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                                                        const __grid_constant__ CUtensorMap tmW2,
                                                        const __grid_constant__ CUtensorMap tmY,
                                                        TcEpi ep, int num_kb, int tiles_n, int num_tiles, int ksplit, int kb_per,
-                                                       int m_pad) {
+                                                       int m_pad, int skip_w2) {
+    // skip_w2: every element of the W2 half is zero (a matrix whose scaled elements are all fp16 values, which is the
+    // case for bf16 weights): the x1 W2 product is not issued -- two MMAs per k-step instead of three, same result
     // ksplit > 1: a work item is (output tile, slice of K); the item's raw sums go to slice s of a partial buffer whose
     // slices are m_pad rows apart (the tensor map of the stores covers all slices), and a second kernel adds the slices
     pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
@@ -125,7 +127,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                         const uint64_t o = (uint64_t)(k * 2);
                         umma_f16(tmain, x1 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
                         umma_f16(tcross, x2 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
-                        umma_f16(tcross, x1 + o, w2 + o, idesc, 1u);
+                        if (!skip_w2) umma_f16(tcross, x1 + o, w2 + o, idesc, 1u);
                     }
                     umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
                 }
@@ -187,12 +189,12 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                     tmem_ld32_issue(trow + (uint32_t)H3_BN, x);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r0[j])));
+                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r0[j]) * ep.acc_scale));
                     tmem_ld32_issue(trow + 32u, r1);
                     tmem_ld32_issue(trow + (uint32_t)(H3_BN + 32), x);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r1[j])));
+                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r1[j]) * ep.acc_scale));
                 }
                 tc_epilogue_head_qkpost(ep, r0, r1, m, m - lane, n0, stage, &tmY, lane);
             } else
@@ -205,7 +207,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; j++)
-                    r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), H16_LO_UNSCALE, __uint_as_float(r[j])));
+                    r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r[j]) * ep.acc_scale));
                 if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
                 else if (coop && n0 + c * 32 + 32 <= ep.N)
                     tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, &resv[c * 8], stage, &tmY, lane);
@@ -248,7 +250,63 @@ static void split_h16(const float *x, int64_t ldx, void *v1, void *v2, int64_t r
            (unsigned short *)v2, rows, K / 4);
 }
 
-struct ShadowH { unsigned short *v1, *v2; int64_t n; };
+// ---- weight matrices: scaled pair + "second half all zero" test ----
+__global__ void k_absmax(const float *__restrict__ w, int64_t n, unsigned *__restrict__ out) {
+    unsigned m = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        m = max(m, __float_as_uint(fabsf(w[i])));                 // non-negative floats order like their bits
+    for (int o = 16; o; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) atomicMax(out, m);
+}
+__global__ void k_split_h16_scaled(const float *__restrict__ w, float scale, unsigned short *__restrict__ v1, unsigned short *__restrict__ v2,
+                                   int64_t n, unsigned *__restrict__ lo_seen) {
+    unsigned any = 0;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        unsigned short hi, lo;
+        h16_pair(w[i] * scale, hi, lo);
+        v1[i] = hi; v2[i] = lo;
+        any |= (unsigned)(lo & 0x7fffu);
+    }
+    if (__any_sync(0xffffffffu, any != 0) && (threadIdx.x & 31) == 0) atomicOr(lo_seen, 1u);
+}
+// one-time conversion of a static weight matrix (a host synchronisation: the scale depends on the largest element)
+static void split_h16_weights(const float *W, unsigned short *v1, unsigned short *v2, int64_t n, float *scale_out, bool *w2_zero) {
+    static const bool no_scale = getenv("NCM_B200_H3_NO_WSCALE") != nullptr;
+    unsigned *d = (unsigned *)dev_alloc(8);
+    CUDA_CHECK(cudaMemsetAsync(d, 0, 8, stream()));
+    const int64_t g = cdiv(n, 256), cap = (int64_t)ctx().sm_count * 16;
+    const unsigned grid = (unsigned)(g > cap ? cap : (g < 1 ? 1 : g));
+    float scale = 1.0f;
+    if (!no_scale) {
+        LAUNCH(k_absmax, grid, 256, 0, W, n, d);
+        unsigned bits = 0;
+        CUDA_CHECK(cudaMemcpyAsync(&bits, d, 4, cudaMemcpyDeviceToHost, stream()));
+        CUDA_CHECK(cudaStreamSynchronize(stream()));
+        float mx;
+        memcpy(&mx, &bits, 4);
+        if (mx > 0.f && std::isfinite(mx)) {
+            int e = 0;
+            frexpf(mx, &e);                                        // mx = f * 2^e, f in [0.5, 1)
+            int sh = 14 - e;                                       // mx * 2^sh in [8192, 16384)
+            if (sh > 24) sh = 24;
+            if (sh < -24) sh = -24;
+            scale = ldexpf(1.0f, sh);
+        }
+    }
+    ProfScope ps(NCMB_K_ELEM, 0, (double)n * 8);
+    LAUNCH(k_split_h16_scaled, grid, 256, 0, W, scale, v1, v2, n, d + 1);
+    unsigned seen = 1;
+    CUDA_CHECK(cudaMemcpyAsync(&seen, d + 1, 4, cudaMemcpyDeviceToHost, stream()));
+    CUDA_CHECK(cudaStreamSynchronize(stream()));
+    dev_free(d);
+    static const bool no_skip = getenv("NCM_B200_H3_NO_SKIP_W2") != nullptr;
+    *scale_out = scale;
+    *w2_zero = !seen && !no_skip;
+}
+
+// cached pair of a weight matrix: formed from W * scale (a power of two that brings the largest element to
+// [8192, 16384): small weights stay clear of the fp16 subnormals); w2_zero: no element needed its second half
+struct ShadowH { unsigned short *v1, *v2; int64_t n; float scale; bool w2_zero; };
 static std::unordered_map<const float *, ShadowH> &shadow_h() { static std::unordered_map<const float *, ShadowH> c; return c; }
 static Workspace &split_ws_h() { static Workspace w; return w; }
 
@@ -322,6 +380,8 @@ void gemm_h3(const GemmArgs &a) {
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
     ep.colnorm = nullptr; ep.best = nullptr;
     ep.qk_heads = a.qk_heads; ep.qk_H = a.qk_H; ep.qk_qw = a.qk_qw; ep.qk_kw = a.qk_kw; ep.qk_cos = a.qk_cos; ep.qk_sin = a.qk_sin; ep.qk_pos = a.qk_pos;
+    ep.acc_scale = 1.0f; ep.lo_scale = H16_LO_UNSCALE;
+    int skip_w2 = 0;
     const int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool pre_split = a.x_lo != nullptr;
     const int64_t nx = pre_split ? 0 : a.M * a.K, nw = (int64_t)a.N * a.K;
@@ -344,10 +404,13 @@ void gemm_h3(const GemmArgs &a) {
         if (it == sc.end() || it->second.n != nw) {
             if (it != sc.end()) dev_free(it->second.v1);
             unsigned short *buf = (unsigned short *)dev_alloc((size_t)2 * nw * 2);
-            split_h16(a.W, a.K, buf, buf + nw, a.N, a.K);
-            it = sc.insert_or_assign(a.W, ShadowH{buf, buf + nw, nw}).first;
+            float scale = 1.0f; bool w2_zero = false;
+            split_h16_weights(a.W, buf, buf + nw, nw, &scale, &w2_zero);
+            it = sc.insert_or_assign(a.W, ShadowH{buf, buf + nw, nw, scale, w2_zero}).first;
         }
         w1 = it->second.v1; w2 = it->second.v2;
+        ep.acc_scale = 1.0f / it->second.scale; ep.lo_scale = H16_LO_UNSCALE / it->second.scale;
+        skip_w2 = it->second.w2_zero ? 1 : 0;
     } else {
         unsigned short *p1 = ws.get<unsigned short>(nw), *p2 = ws.get<unsigned short>(nw);
         split_h16(a.W, a.K, p1, p2, a.N, a.K);
@@ -421,7 +484,7 @@ void gemm_h3(const GemmArgs &a) {
         static_assert(smem <= 227 * 1024, "stage ring + store staging exceed shared memory");                               \
         static bool set = false;                                                                                            \
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute(k_gemm_h3<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; } \
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);        \
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), k_gemm_h3<BN_>, grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad, skip_w2);        \
     } while (0)
     // fused QKV projection: heads are 64 columns, a 128-column tile holds two, results leave as fp32 tiles
     const bool qkp = qk_epilogue_on() && a.qk_heads > 0 && a.qk_applied && bn == 128 && ep.tma_store && a.N % 128 == 0 && !a.res &&
@@ -431,7 +494,7 @@ void gemm_h3(const GemmArgs &a) {
         constexpr size_t smem = 1024 + (size_t)h3_stages(128) * h3_stage(128) + H3_EPI_WARPS * 4096 + (2 * h3_stages(128) + 4) * 8 + 16;
         static bool set = false;
         if (!set) { CUDA_CHECK(cudaFuncSetAttribute((k_gemm_h3<128, true>), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad);
+        LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad, skip_w2);
     } else if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);
     else H3_LAUNCH(128);
