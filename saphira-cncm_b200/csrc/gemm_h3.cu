@@ -32,6 +32,11 @@ constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand 
 constexpr int h3_wtile(int BN) { return BN * H3_BK * 2; }  // one BN-row weight tile
 constexpr int h3_stage(int BN) { return 2 * H3_TILE + 2 * h3_wtile(BN); }   // x1 | x2 | W1 | W2
 
+// main + cross * 2^-11, times the inverse of the weight pair's prescale when there is one
+__device__ __forceinline__ float h3_combine(const TcEpi &ep, float mainv, float crossv, bool scaled) {
+    return scaled ? fmaf(crossv, ep.lo_scale, mainv * ep.acc_scale) : fmaf(crossv, H16_LO_UNSCALE, mainv);
+}
+
 // QKP: the epilogue applies the per-head RMSNorm / rotary embedding of a fused QKV projection (128-column tiles)
 template <int H3_BN, bool QKP = false>
 __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant__ CUtensorMap tmX1,
@@ -89,11 +94,11 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                     ok = mbar_wait(empty0 + 8 * s, ph ^ 1u, ep.err, 21);
                     if (!ok) break;
                     const uint32_t dst = smem_u32(smem + s * H3_STAGE), bar = full0 + 8 * s;
-                    mbar_expect_tx(bar, H3_STAGE);
+                    mbar_expect_tx(bar, skip_w2 ? H3_STAGE - H3_WTILE : H3_STAGE);       // an all-zero second half is neither fetched nor multiplied
                     tma_load_2d(dst, &tmX1, kb * H3_BK, m0, bar);
                     tma_load_2d(dst + H3_TILE, &tmX2, kb * H3_BK, m0, bar);
                     tma_load_2d(dst + 2 * H3_TILE, &tmW1, kb * H3_BK, n0, bar);
-                    tma_load_2d(dst + 2 * H3_TILE + H3_WTILE, &tmW2, kb * H3_BK, n0, bar);
+                    if (!skip_w2) tma_load_2d(dst + 2 * H3_TILE + H3_WTILE, &tmW2, kb * H3_BK, n0, bar);
                     armed = kbg + 1;
                 }
             }
@@ -143,6 +148,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         int it = 0;
         bool ok = true;
         const bool glu_fast = tc_glu_silu_h16(ep);
+        const bool scaled = ep.acc_scale != 1.0f;                 // uniform: the unscaled combine stays one FMA per element
         unsigned char *stage = stage0 + (warp - 2) * 4096;
         for (int w = blockIdx.x; w < num_tiles * ksplit && ok; w += gridDim.x, it++) {
             const int t = w / ksplit;
@@ -189,12 +195,12 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                     tmem_ld32_issue(trow + (uint32_t)H3_BN, x);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r0[j]) * ep.acc_scale));
+                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r0[j]), __uint_as_float(x[j]), scaled));
                     tmem_ld32_issue(trow + 32u, r1);
                     tmem_ld32_issue(trow + (uint32_t)(H3_BN + 32), x);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r1[j]) * ep.acc_scale));
+                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r1[j]), __uint_as_float(x[j]), scaled));
                 }
                 tc_epilogue_head_qkpost(ep, r0, r1, m, m - lane, n0, stage, &tmY, lane);
             } else
@@ -207,7 +213,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 32; j++)
-                    r[j] = __float_as_uint(fmaf(__uint_as_float(x[j]), ep.lo_scale, __uint_as_float(r[j]) * ep.acc_scale));
+                    r[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r[j]), __uint_as_float(x[j]), scaled));
                 if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
                 else if (coop && n0 + c * 32 + 32 <= ep.N)
                     tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, &resv[c * 8], stage, &tmY, lane);
@@ -298,10 +304,17 @@ static void split_h16_weights(const float *W, unsigned short *v1, unsigned short
     unsigned seen = 1;
     CUDA_CHECK(cudaMemcpyAsync(&seen, d + 1, 4, cudaMemcpyDeviceToHost, stream()));
     CUDA_CHECK(cudaStreamSynchronize(stream()));
-    dev_free(d);
     static const bool no_skip = getenv("NCM_B200_H3_NO_SKIP_W2") != nullptr;
     *scale_out = scale;
     *w2_zero = !seen && !no_skip;
+    if (!*w2_zero && scale != 1.0f) {
+        // The prescale pays when it makes the second half vanish (bf16 weights). For a matrix that needs its second
+        // half anyway the pair is formed unscaled, as activations are: the epilogue then keeps its one-FMA combine.
+        LAUNCH(k_split_h16_scaled, grid, 256, 0, W, 1.0f, v1, v2, n, d + 1);
+        CUDA_CHECK(cudaStreamSynchronize(stream()));
+        *scale_out = 1.0f;
+    }
+    dev_free(d);
 }
 
 // cached pair of a weight matrix: formed from W * scale (a power of two that brings the largest element to

@@ -751,30 +751,17 @@ __device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned l
                              int shift, int nbins, NsHist *sh, NsHist *gh) {
     for (int i = threadIdx.x; i < nbins; i += NS_THREADS) { sh->sum[i] = 0; sh->cnt[i] = 0; sh->kmin_inv[i] = 0; sh->kmax[i] = 0; }
     __syncthreads();
-    // Logits of a row cluster in a few bins (the top key bits are sign, exponent and two mantissa bits), so the
-    // lanes of a warp that fall into the same bin are combined first -- match, then hardware warp reductions on
-    // the two 22-bit halves of the mass (each partial sum stays below 2^28), the keys and the count -- and only
-    // one lane per distinct bin touches shared memory.
-    const int nloop = (V + gridDim.x * NS_THREADS - 1) / (gridDim.x * NS_THREADS);
-    for (int it = 0; it < nloop; it++) {
-        const int i = (it * gridDim.x + blockIdx.x) * NS_THREADS + threadIdx.x;
-        unsigned k = 0;
-        bool on = i < V;
-        if (on) { k = keys[i]; on = !(fshift < 32 && (k >> fshift) != want); }
-        const unsigned active = __ballot_sync(0xffffffffu, on);
-        if (!on) continue;
+    // (Combining the lanes of a warp that fall into the same bin first -- match + warp reductions, one lane per
+    // distinct bin touching shared memory -- measured slower than these plain shared-memory atomics: 2.6 against
+    // 1.5 ms per step at 256 rows of 151 936 entries.)
+    for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) {
+        const unsigned k = keys[i];
+        if (fshift < 32 && (k >> fshift) != want) continue;
         const int bin = (int)((k >> shift) & (unsigned)(nbins - 1));
-        const unsigned long long qv = q[i];
-        const unsigned peers = __match_any_sync(active, bin);
-        const unsigned lo = __reduce_add_sync(peers, (unsigned)(qv & 0x3fffffull));
-        const unsigned hi = __reduce_add_sync(peers, (unsigned)(qv >> 22));
-        const unsigned kmx = __reduce_max_sync(peers, k), kmn = __reduce_min_sync(peers, k);
-        if ((threadIdx.x & 31) == __ffs(peers) - 1) {
-            atomicAdd(&sh->sum[bin], ((unsigned long long)hi << 22) + lo);
-            atomicAdd(&sh->cnt[bin], (unsigned)__popc(peers));
-            atomicMax(&sh->kmin_inv[bin], ~kmn);
-            atomicMax(&sh->kmax[bin], kmx);
-        }
+        atomicAdd(&sh->sum[bin], q[i]);
+        atomicAdd(&sh->cnt[bin], 1u);
+        atomicMax(&sh->kmin_inv[bin], ~k);
+        atomicMax(&sh->kmax[bin], k);
     }
     __syncthreads();
     for (int i = threadIdx.x; i < nbins; i += NS_THREADS)
@@ -795,13 +782,29 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_prob(const float *__restrict_
     unsigned *kr = keys + (size_t)b * V;
     unsigned long long *qr = q + (size_t)b * V;
     const double mx = (double)okey_inv(rows[b].maxkey);
+    NsHist *gh = hist + (size_t)b * 5;
+    for (int i = threadIdx.x; i < NS_BINS; i += NS_THREADS) { sh.sum[i] = 0; sh.cnt[i] = 0; sh.kmin_inv[i] = 0; sh.kmax[i] = 0; }
+    __syncthreads();
+    // keys and masses are stored for the later passes and enter the top-level histogram in the same sweep
     for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) {
         const unsigned k = okey(lg[i] / temp);
+        const unsigned long long qv = ns_q_of_key(k, mx);
         kr[i] = k;
-        qr[i] = ns_q_of_key(k, mx);
+        qr[i] = qv;
+        const int bin = (int)(k >> 21);
+        atomicAdd(&sh.sum[bin], qv);
+        atomicAdd(&sh.cnt[bin], 1u);
+        atomicMax(&sh.kmin_inv[bin], ~k);
+        atomicMax(&sh.kmax[bin], k);
     }
-    __syncthreads();                                               // this CTA re-reads only what it wrote itself
-    ns_histogram(kr, qr, V, 32, 0u, 21, NS_BINS, &sh, hist + (size_t)b * 5);
+    __syncthreads();
+    for (int i = threadIdx.x; i < NS_BINS; i += NS_THREADS)
+        if (sh.cnt[i]) {
+            atomicAdd(&gh->sum[i], sh.sum[i]);
+            atomicAdd(&gh->cnt[i], sh.cnt[i]);
+            atomicMax(&gh->kmin_inv[i], sh.kmin_inv[i]);
+            atomicMax(&gh->kmax[i], sh.kmax[i]);
+        }
 }
 
 // STAGE 2, 3: nucleus descent (decide on the previous histogram, build the next); 4: end of the nucleus descent,
