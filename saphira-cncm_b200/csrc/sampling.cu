@@ -647,7 +647,33 @@ struct NsHist {
     unsigned long long sum[NS_BINS];
     unsigned cnt[NS_BINS];
     unsigned kmin_inv[NS_BINS];       // ~(smallest key of the bin): zero-initialised storage, atomicMax
-    unsigned kmax[NS_BINS];
+};
+// A CTA's shared-memory copy. The 45-bit masses are added as three 15-bit limbs with native 32-bit atomics (a 64-bit
+// shared-memory add is a compare-and-swap loop, and the rows' keys cluster in a few bins: it was 0.6 of the 0.7 ms
+// the first sweep took at 256 rows). A limb sum stays below 2^32 for up to 2^17 elements per CTA.
+constexpr int NS_MAX_PER_CTA = 1 << 17;
+struct NsShHist {
+    unsigned s0[NS_BINS], s1[NS_BINS], s2[NS_BINS];
+    unsigned cnt[NS_BINS];
+    unsigned kmin_inv[NS_BINS];
+    __device__ __forceinline__ void clear(int nbins) {
+        for (int i = threadIdx.x; i < nbins; i += NS_THREADS) { s0[i] = 0; s1[i] = 0; s2[i] = 0; cnt[i] = 0; kmin_inv[i] = 0; }
+    }
+    __device__ __forceinline__ void add(int bin, unsigned k, unsigned long long qv) {
+        atomicAdd(&s0[bin], (unsigned)(qv & 0x7fffull));
+        atomicAdd(&s1[bin], (unsigned)((qv >> 15) & 0x7fffull));
+        atomicAdd(&s2[bin], (unsigned)(qv >> 30));
+        atomicAdd(&cnt[bin], 1u);
+        atomicMax(&kmin_inv[bin], ~k);
+    }
+    __device__ __forceinline__ void flush(int nbins, NsHist *gh) {
+        for (int i = threadIdx.x; i < nbins; i += NS_THREADS)
+            if (cnt[i]) {
+                atomicAdd(&gh->sum[i], (unsigned long long)s0[i] + ((unsigned long long)s1[i] << 15) + ((unsigned long long)s2[i] << 30));
+                atomicAdd(&gh->cnt[i], cnt[i]);
+                atomicMax(&gh->kmin_inv[i], kmin_inv[i]);
+            }
+    }
 };
 // Per-row state handed from one kernel of the sequence to the next. A field is written by the first CTA of a row
 // in one kernel and read only by LATER kernels (the CTAs of a kernel each repeat its decision for themselves), hence
@@ -685,9 +711,9 @@ __device__ __forceinline__ unsigned long long ns_block_excl_scan(unsigned long l
 }
 
 // One level of a descent over a histogram of `nbins` bins, highest bin first. NUCLEUS: the first bin whose LAST
-// element satisfies cum_before - p > T (then *first_hit tells whether already its first element does, in which
-// case the cut lies exactly in front of the bin). Otherwise: the first bin with cum_incl >= T. Results through
-// shared memory: *sel = bin (-1: no bin satisfies), *sel_above = mass above that bin.
+// element satisfies cum_before - p > T (the cut then lies inside that bin or exactly in front of it; the descent
+// into the bin settles which). Otherwise: the first bin with cum_incl >= T. Results through shared memory:
+// *sel = bin (-1: no bin satisfies), *sel_above = mass above that bin; *first_hit is always 0.
 template <bool NUCLEUS>
 __device__ void ns_decide(const NsHist *h, int nbins, unsigned long long above, double T, double mx, unsigned key_hi, int shift,
                           unsigned long long *wsum, int *sel, unsigned long long *sel_above, int *first_hit) {
@@ -727,10 +753,6 @@ __device__ void ns_decide(const NsHist *h, int nbins, unsigned long long above, 
         const unsigned long long a0 = above + ex + (e ? s[0] : 0ull);
         *sel = bin[e];
         *sel_above = a0;
-        if (NUCLEUS) {
-            const long long g0 = (long long)a0 - (long long)ns_q_of_key(h->kmax[bin[e]], mx);
-            *first_hit = (double)g0 > T ? 1 : 0;
-        }
     }
     __syncthreads();
 }
@@ -748,8 +770,8 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_max(const float *__restrict__
 // every element) into the histogram of the next `bits` key bits below that; shared histogram, then one atomic
 // per touched bin into the row's global one
 __device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned long long *__restrict__ q, int V, int fshift, unsigned want,
-                             int shift, int nbins, NsHist *sh, NsHist *gh) {
-    for (int i = threadIdx.x; i < nbins; i += NS_THREADS) { sh->sum[i] = 0; sh->cnt[i] = 0; sh->kmin_inv[i] = 0; sh->kmax[i] = 0; }
+                             int shift, int nbins, NsShHist *sh, NsHist *gh) {
+    sh->clear(nbins);
     __syncthreads();
     // (Combining the lanes of a warp that fall into the same bin first -- match + warp reductions, one lane per
     // distinct bin touching shared memory -- measured slower than these plain shared-memory atomics: 2.6 against
@@ -758,32 +780,23 @@ __device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned l
         const unsigned k = keys[i];
         if (fshift < 32 && (k >> fshift) != want) continue;
         const int bin = (int)((k >> shift) & (unsigned)(nbins - 1));
-        atomicAdd(&sh->sum[bin], q[i]);
-        atomicAdd(&sh->cnt[bin], 1u);
-        atomicMax(&sh->kmin_inv[bin], ~k);
-        atomicMax(&sh->kmax[bin], k);
+        sh->add(bin, k, q[i]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < nbins; i += NS_THREADS)
-        if (sh->cnt[i]) {
-            atomicAdd(&gh->sum[i], sh->sum[i]);
-            atomicAdd(&gh->cnt[i], sh->cnt[i]);
-            atomicMax(&gh->kmin_inv[i], sh->kmin_inv[i]);
-            atomicMax(&gh->kmax[i], sh->kmax[i]);
-        }
+    sh->flush(nbins, gh);
 }
 
 // keys, fixed-point probabilities and the histogram of the top 11 key bits
 __global__ void __launch_bounds__(NS_THREADS) k_ns_prob(const float *__restrict__ logits, float temp, int V, NsRow *rows, unsigned *keys,
                                                         unsigned long long *q, NsHist *hist) {
-    __shared__ NsHist sh;
+    __shared__ NsShHist sh;
     const int b = blockIdx.y;
     const float *lg = logits + (size_t)b * V;
     unsigned *kr = keys + (size_t)b * V;
     unsigned long long *qr = q + (size_t)b * V;
     const double mx = (double)okey_inv(rows[b].maxkey);
     NsHist *gh = hist + (size_t)b * 5;
-    for (int i = threadIdx.x; i < NS_BINS; i += NS_THREADS) { sh.sum[i] = 0; sh.cnt[i] = 0; sh.kmin_inv[i] = 0; sh.kmax[i] = 0; }
+    sh.clear(NS_BINS);
     __syncthreads();
     // keys and masses are stored for the later passes and enter the top-level histogram in the same sweep
     for (int i = blockIdx.x * NS_THREADS + threadIdx.x; i < V; i += gridDim.x * NS_THREADS) {
@@ -791,20 +804,10 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_prob(const float *__restrict_
         const unsigned long long qv = ns_q_of_key(k, mx);
         kr[i] = k;
         qr[i] = qv;
-        const int bin = (int)(k >> 21);
-        atomicAdd(&sh.sum[bin], qv);
-        atomicAdd(&sh.cnt[bin], 1u);
-        atomicMax(&sh.kmin_inv[bin], ~k);
-        atomicMax(&sh.kmax[bin], k);
+        sh.add((int)(k >> 21), k, qv);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < NS_BINS; i += NS_THREADS)
-        if (sh.cnt[i]) {
-            atomicAdd(&gh->sum[i], sh.sum[i]);
-            atomicAdd(&gh->cnt[i], sh.cnt[i]);
-            atomicMax(&gh->kmin_inv[i], sh.kmin_inv[i]);
-            atomicMax(&gh->kmax[i], sh.kmax[i]);
-        }
+    sh.flush(NS_BINS, gh);
 }
 
 // STAGE 2, 3: nucleus descent (decide on the previous histogram, build the next); 4: end of the nucleus descent,
@@ -813,7 +816,7 @@ template <int STAGE>
 __global__ void __launch_bounds__(NS_THREADS) k_ns_refine(int V, float top_p, const double *__restrict__ uniforms, unsigned long long seed,
                                                           long long row0, int level, NsRow *rows, const unsigned *keys,
                                                           const unsigned long long *q, NsHist *hist) {
-    __shared__ NsHist sh;
+    __shared__ NsShHist sh;
     __shared__ unsigned long long wsum[32];
     __shared__ int s_sel, s_first;
     __shared__ unsigned long long s_above;
@@ -993,6 +996,8 @@ static bool sample_rows_select(const SampleArgs &a) {
     const int gmax = (a.V + 4 * NS_THREADS - 1) / (4 * NS_THREADS);
     if (G > gmax) G = gmax;
     if (G > 32) G = 32;
+    const int gmin = (a.V + NS_MAX_PER_CTA - 1) / NS_MAX_PER_CTA;          // the limb sums of a CTA's histogram must not wrap
+    if (G < gmin) G = gmin;
     if (G < 1) G = 1;
     const dim3 grid((unsigned)G, (unsigned)a.Bn);
     LAUNCH(k_ns_max, grid, NS_THREADS, 0, a.logits, a.temp, a.V, rows);
