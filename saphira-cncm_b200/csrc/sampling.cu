@@ -687,7 +687,9 @@ struct NsRow {
     unsigned p_prefix[2];
     unsigned long long p_above[2];
     double U;                          // the draw, in fixed-point units of mass
+    unsigned n_cand;                   // entries the last histogram pass put on the row's candidate list
 };
+constexpr int NS_CAND = 2048;          // (key, index) pairs per row kept for the final index search
 
 __device__ __forceinline__ unsigned long long ns_q_of_key(unsigned key, double mx) {
     return __double2ull_rn(exp((double)okey_inv(key) - mx) * NS_FIX);
@@ -770,7 +772,7 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_max(const float *__restrict__
 // every element) into the histogram of the next `bits` key bits below that; shared histogram, then one atomic
 // per touched bin into the row's global one
 __device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned long long *__restrict__ q, int V, int fshift, unsigned want,
-                             int shift, int nbins, NsShHist *sh, NsHist *gh) {
+                             int shift, int nbins, NsShHist *sh, NsHist *gh, unsigned *n_cand = nullptr, unsigned long long *cand = nullptr) {
     sh->clear(nbins);
     __syncthreads();
     // (Combining the lanes of a warp that fall into the same bin first -- match + warp reductions, one lane per
@@ -781,6 +783,10 @@ __device__ void ns_histogram(const unsigned *__restrict__ keys, const unsigned l
         if (fshift < 32 && (k >> fshift) != want) continue;
         const int bin = (int)((k >> shift) & (unsigned)(nbins - 1));
         sh->add(bin, k, q[i]);
+        if (n_cand) {      // last level of the pick descent: the handful of entries left are kept with their indices
+            const unsigned at = atomicAdd(n_cand, 1u);
+            if (at < (unsigned)NS_CAND) cand[at] = ((unsigned long long)k << 32) | (unsigned)i;
+        }
     }
     __syncthreads();
     sh->flush(nbins, gh);
@@ -815,7 +821,7 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_prob(const float *__restrict_
 template <int STAGE>
 __global__ void __launch_bounds__(NS_THREADS) k_ns_refine(int V, float top_p, const double *__restrict__ uniforms, unsigned long long seed,
                                                           long long row0, int level, NsRow *rows, const unsigned *keys,
-                                                          const unsigned long long *q, NsHist *hist) {
+                                                          const unsigned long long *q, NsHist *hist, unsigned long long *cand) {
     __shared__ NsShHist sh;
     __shared__ unsigned long long wsum[32];
     __shared__ int s_sel, s_first;
@@ -912,14 +918,14 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_refine(int V, float top_p, co
         const unsigned pre = (row->p_prefix[0] << 11) | (unsigned)sel;
         __syncthreads();
         if (lead) { row->p_prefix[1] = pre; row->p_above[1] = ab; }
-        ns_histogram(kr, qr, V, 10, pre, 0, 1024, &sh, &H[4]);
+        ns_histogram(kr, qr, V, 10, pre, 0, 1024, &sh, &H[4], &row->n_cand, cand + (size_t)b * NS_CAND);
         return;
     }
 }
 
 // last level of the pick descent, then the index: the pick_tie-th (ascending index) element holding the chosen key
-__global__ void __launch_bounds__(NS_THREADS) k_ns_pick(int V, NsRow *rows, const unsigned *keys, NsHist *hist, int *__restrict__ out, int out_stride,
-                                                        int out_off) {
+__global__ void __launch_bounds__(NS_THREADS) k_ns_pick(int V, NsRow *rows, const unsigned *keys, NsHist *hist, const unsigned long long *cand,
+                                                        int *__restrict__ out, int out_stride, int out_off) {
     __shared__ unsigned long long wsum[32];
     __shared__ int s_sel, s_first, s_n, s_list[2048];
     __shared__ unsigned long long s_above;
@@ -950,8 +956,18 @@ __global__ void __launch_bounds__(NS_THREADS) k_ns_pick(int V, NsRow *rows, cons
     __syncthreads();
     // indices holding the key (a handful at most for real logits; a constant row makes it the whole vocabulary)
     if (cnt <= 2048) {
-        for (int i = tid; i < V; i += NS_THREADS)
-            if (kr[i] == key) { int at = atomicAdd(&s_n, 1); if (at < 2048) s_list[at] = i; }
+        const unsigned nc = row->n_cand;
+        if (nc <= (unsigned)NS_CAND) {
+            // the entries sharing the key's upper 22 bits were listed by the last histogram pass: no sweep over the row
+            const unsigned long long *cl = cand + (size_t)b * NS_CAND;
+            for (unsigned i = tid; i < nc; i += NS_THREADS) {
+                const unsigned long long e = cl[i];
+                if ((unsigned)(e >> 32) == key) { int at = atomicAdd(&s_n, 1); if (at < 2048) s_list[at] = (int)(unsigned)(e & 0xffffffffull); }
+            }
+        } else {
+            for (int i = tid; i < V; i += NS_THREADS)
+                if (kr[i] == key) { int at = atomicAdd(&s_n, 1); if (at < 2048) s_list[at] = i; }
+        }
         __syncthreads();
         const int n = s_n < 2048 ? s_n : 2048;
         for (int e = tid; e < n; e += NS_THREADS) {
@@ -981,7 +997,7 @@ static bool sample_rows_select(const SampleArgs &a) {
     static Workspace ws;
     const size_t n = (size_t)a.Bn * a.V;
     const size_t head = ((size_t)a.Bn * sizeof(NsRow) + (size_t)a.Bn * 5 * sizeof(NsHist) + 255) & ~(size_t)255;
-    const size_t need = head + n * 12 + 4096;
+    const size_t need = head + n * 12 + (size_t)a.Bn * NS_CAND * 8 + 8192;
     if (need > ws.cap) ws.reserve(need + need / 8);
     ws.reset();
     char *base = (char *)ws.alloc(head);
@@ -989,6 +1005,7 @@ static bool sample_rows_select(const SampleArgs &a) {
     NsHist *hist = (NsHist *)(base + (((size_t)a.Bn * sizeof(NsRow) + 15) & ~(size_t)15));
     unsigned long long *q = ws.get<unsigned long long>(n);
     unsigned *keys = ws.get<unsigned>(n);
+    unsigned long long *cand = ws.get<unsigned long long>((size_t)a.Bn * NS_CAND);
     ProfScope ps(NCMB_K_SAMPLE, 0, (double)n * 40);
     CUDA_CHECK(cudaMemsetAsync(base, 0, head, stream()));
     // CTAs per row: enough to occupy the GPU when there are few rows
@@ -1002,11 +1019,11 @@ static bool sample_rows_select(const SampleArgs &a) {
     const dim3 grid((unsigned)G, (unsigned)a.Bn);
     LAUNCH(k_ns_max, grid, NS_THREADS, 0, a.logits, a.temp, a.V, rows);
     LAUNCH(k_ns_prob, grid, NS_THREADS, 0, a.logits, a.temp, a.V, rows, keys, q, hist);
-    LAUNCH(k_ns_refine<2>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
-    LAUNCH(k_ns_refine<3>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
-    LAUNCH(k_ns_refine<4>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
-    LAUNCH(k_ns_refine<5>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist);
-    LAUNCH(k_ns_pick, (unsigned)a.Bn, NS_THREADS, 0, a.V, rows, (const unsigned *)keys, hist, a.out, a.out_stride, a.out_off);
+    LAUNCH(k_ns_refine<2>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist, cand);
+    LAUNCH(k_ns_refine<3>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist, cand);
+    LAUNCH(k_ns_refine<4>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist, cand);
+    LAUNCH(k_ns_refine<5>, grid, NS_THREADS, 0, a.V, a.top_p, a.uniforms, a.rng_seed, a.rng_row0, a.rng_level, rows, (const unsigned *)keys, (const unsigned long long *)q, hist, cand);
+    LAUNCH(k_ns_pick, (unsigned)a.Bn, NS_THREADS, 0, a.V, rows, (const unsigned *)keys, hist, (const unsigned long long *)cand, a.out, a.out_stride, a.out_off);
     return true;
 }
 
