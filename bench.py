@@ -529,11 +529,13 @@ def lm_bytes_per_step(spec, B, mean_ctx):
     return width * params + B * spec.n_layer * 2 * kvd * width * mean_ctx
 
 
-def measure_lm(lib, stream, name, batches, steps, warmup, local):
+def measure_lm(lib, stream, name, batches, steps, warmup, local, n_new=0):
     """GPT-2 / Qwen2 shaped decoding with a KV cache, one line per batch size: tokens/s (prefill included) and
     achieved HBM GB/s per decode step. The model is opened once for all batch sizes."""
     import torch
     spec, w = lm_workload(name)
+    if n_new > 0:
+        w = dict(w, n_new=n_new)                               # shorter generations: profiler captures of a few decode steps
     tmp = tempfile.TemporaryDirectory()
     conf, wt = synth.write_lm(spec, tmp.name)
     cfg = lib.load_config(conf)
@@ -605,7 +607,7 @@ def _lm_setup(args):
 def run_lm_arm(args):
     lib, stream, local = _lm_setup(args)
     _, w = lm_workload(args.workload)
-    for line in measure_lm(lib, stream, args.workload, [args.batch or w["batch"]], args.steps, args.warmup, local):
+    for line in measure_lm(lib, stream, args.workload, [args.batch or w["batch"]], args.steps, args.warmup, local, args.n_new):
         print(json.dumps(line), flush=True)
 
 
@@ -815,6 +817,7 @@ def main():
     ap.add_argument("--gemm", type=int, default=None, help="GEMM engine override (0 fp32, 1 tf32, 2 3xtf32, 3 fp16 pairs)")
     ap.add_argument("--cpu-rows", type=int, default=1, help="sequences in the CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-new", type=int, default=0, help="decoder-LM workloads: tokens to generate (default: the configuration's)")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the short runs of the other configurations that the default 1-GPU run appends")
     args = ap.parse_args()
