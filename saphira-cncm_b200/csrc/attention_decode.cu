@@ -32,6 +32,7 @@ struct AttnDecDev {
     const int *q_start, *k_start, *k_len;
     const int *step_d; int64_t len_step;
     int H, Hkv, max_split, cps;
+    int hs;                            // warp-per-chunk kernel: warps that share a chunk's (query, head) pairs
     float scale;
     float *part; unsigned *count;
 };
@@ -253,41 +254,45 @@ __global__ void __launch_bounds__(AD_THREADS) k_attention_decode(AttnDecDev a) {
     if (tid == 0) a.count[row * a.Hkv + kvh] = 0;          // ready for the next launch
 }
 
-// ---- head dim 64: one WARP per 32-key chunk ----
+// ---- head dim 64: one WARP per (32-key chunk, group of heads) ----
 // The kernel above gives every 32-key chunk a CTA, three block-wide barriers per chunk, and merges all chunk
 // partials of a row through global memory; at one sequence that chain of barriers and L2 round trips is the kernel
-// (16 us per layer for 800 cached keys of the 14-query-head / 2-kv-head shape). Here a CTA of four or eight warps
-// covers 128 or 256 consecutive keys and a warp works alone on its 32: the lane holding key j forms that key's
-// scores with all G query heads of the kv group (q broadcast from shared memory), the softmax statistics of the
-// chunk are warp shuffles, and for O += P V the lanes switch to owning two output dimensions each while the
-// probabilities travel by shuffle -- K and V rows are requested before anything is computed and no barrier is
-// needed until the warps' partials (maximum, sum, context) meet in shared memory. One partial per CTA goes to
-// global memory, and only when the row needs more than one CTA.
-constexpr int ADW_MAXW = 8;
+// (16 us per layer for 800 cached keys of the 14-query-head / 2-kv-head shape). Here a warp works alone on 32 keys
+// and up to GMW of the kv group's (query, head) pairs: the lane holding key j forms that key's scores (q broadcast
+// from shared memory), the softmax statistics of the chunk are warp shuffles, and for O += P V the lanes switch to
+// owning two output dimensions each while the probabilities travel by shuffle -- K and V rows are requested
+// before anything is computed and no barrier is needed until the warps' partials (maximum, sum, context) meet in
+// shared memory. A kv group with more pairs than one warp takes is shared out over `hs` warps per chunk (they read
+// the same K and V rows, out of L1), so a warp's arithmetic stays short. A CTA covers `blockDim / 32 / hs` chunks;
+// one partial per CTA goes to global memory, and only when the row needs more than one CTA.
+constexpr int ADW_MAXC = 8;            // chunks per CTA at most
 
-template <int GM>
-__global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev a) {
-    constexpr int HD = 64;
-    __shared__ __align__(16) float qs[GM][HD];
-    __shared__ float pm[ADW_MAXW][GM], pl[ADW_MAXW][GM];
-    __shared__ __align__(8) float po[ADW_MAXW][GM][HD];
-    __shared__ float Mg[GM], Lg[GM], wg[ADW_MAXW][GM];
+template <int GMW>
+__global__ void __launch_bounds__(256) k_attention_dec_warp(AttnDecDev a) {
+    constexpr int HD = 64, GA = AD_MAXG;
+    __shared__ __align__(16) float qs[GA][HD];
+    __shared__ float pm[ADW_MAXC][GA], pl[ADW_MAXC][GA], wg[ADW_MAXC][GA];
+    __shared__ __align__(8) float po[ADW_MAXC][GA][HD];
+    __shared__ float Mg[GA], Lg[GA];
     __shared__ int s_last;
     const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
     const int Gh = a.H / a.Hkv;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hs = a.hs, cpc = (blockDim.x >> 5) / hs;        // warps per chunk, chunks per CTA
+    const int cw = warp / hs, hg = warp - cw * hs;
     pdl_launch_dependents();
     pdl_wait();
     const int *lens = a.k_len ? a.k_len + (a.step_d ? (int64_t)(*a.step_d) * a.len_step : 0) : nullptr;
     const int k00 = a.k_start[row], n1s = lens ? lens[row] : a.k_start[row + 1] - k00;
     const int k20 = a.k2_start ? a.k2_start[row] : 0, n2s = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
     const int n1 = n1s + n2s;
-    const int per_cta = nw * 32;
+    const int per_cta = cpc * 32;
     const int nsplit = (n1 + per_cta - 1) / per_cta;
     if (sp >= nsplit) return;
-    const int kw = sp * per_cta + warp * 32;              // first key of this warp's chunk
+    const int kw = sp * per_cta + cw * 32;                    // first key of this warp's chunk
     const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
-    const int G = Gh * nq;                                // virtual heads: vh = g * nq + qi
+    const int G = Gh * nq;                                    // virtual heads: vh = g * nq + qi
+    const int g0 = hg * GMW;                                  // this warp's heads: [g0, g0 + GMW) below G
     auto krow = [&](int j) -> const float * {
         return j < n1s ? a.k + (int64_t)(k00 + j) * a.ldk : a.k2 + (int64_t)(k20 + j - n1s) * a.ldk2;
     };
@@ -312,11 +317,12 @@ __global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev
     for (int jj = 0; jj < 32; jj++)
         vv[jj] = (kw + jj < n1) ? *(const float2 *)(vrow(kw + jj) + kvh * HD + 2 * lane) : make_float2(0.f, 0.f);
     __syncthreads();
-    float s[GM];
+    float s[GMW];
 #pragma unroll
-    for (int g = 0; g < GM; g++) {
-        s[g] = 0.f;
-        if (g < G) {                                          // block-uniform
+    for (int gi = 0; gi < GMW; gi++) {
+        s[gi] = 0.f;
+        const int g = g0 + gi;
+        if (g < G) {                                          // warp-uniform
             float dot = 0.f;
 #pragma unroll
             for (int i = 0; i < HD / 4; i++) {
@@ -331,30 +337,30 @@ __global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev
             float l = p;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-            s[g] = p;
-            if (lane == 0) { pm[warp][g] = m; pl[warp][g] = l; }
+            s[gi] = p;
+            if (lane == 0) { pm[cw][g] = m; pl[cw][g] = l; }
         }
     }
-    float2 acc[GM];
+    float2 acc[GMW];
 #pragma unroll
-    for (int g = 0; g < GM; g++) acc[g] = make_float2(0.f, 0.f);
+    for (int gi = 0; gi < GMW; gi++) acc[gi] = make_float2(0.f, 0.f);
 #pragma unroll
     for (int jj = 0; jj < 32; jj++) {
 #pragma unroll
-        for (int g = 0; g < GM; g++) {
-            const float pj = __shfl_sync(0xffffffffu, s[g], jj);
-            acc[g].x = fmaf(pj, vv[jj].x, acc[g].x); acc[g].y = fmaf(pj, vv[jj].y, acc[g].y);
+        for (int gi = 0; gi < GMW; gi++) {
+            const float pj = __shfl_sync(0xffffffffu, s[gi], jj);
+            acc[gi].x = fmaf(pj, vv[jj].x, acc[gi].x); acc[gi].y = fmaf(pj, vv[jj].y, acc[gi].y);
         }
     }
 #pragma unroll
-    for (int g = 0; g < GM; g++)
-        if (g < G) *(float2 *)&po[warp][g][2 * lane] = acc[g];
+    for (int gi = 0; gi < GMW; gi++)
+        if (g0 + gi < G) *(float2 *)&po[cw][g0 + gi][2 * lane] = acc[gi];
     __syncthreads();
-    // ---- the warps' partials meet: maximum and weights per head, then the context columns ----
+    // ---- the chunks' partials meet: maximum and weights per head, then the context columns ----
     if (tid < G) {
         float M = -INFINITY, L = 0.f;
-        for (int w = 0; w < nw; w++) M = fmaxf(M, pm[w][tid]);
-        for (int w = 0; w < nw; w++) {
+        for (int w = 0; w < cpc; w++) M = fmaxf(M, pm[w][tid]);
+        for (int w = 0; w < cpc; w++) {
             const float e = (pm[w][tid] == -INFINITY) ? 0.f : expf(pm[w][tid] - M);
             wg[w][tid] = e; L = fmaf(pl[w][tid], e, L);
         }
@@ -365,7 +371,7 @@ __global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev
     for (int i = tid; i < G * HD; i += blockDim.x) {
         const int g = i / HD, d = i % HD;
         float O = 0.f;
-        for (int w = 0; w < nw; w++) O = fmaf(po[w][g][d], wg[w][g], O);
+        for (int w = 0; w < cpc; w++) O = fmaf(po[w][g][d], wg[w][g], O);
         if (nsplit == 1) {
             const float L = Lg[g];
             const float r = L > 0.f ? O / L : 0.f;
@@ -387,26 +393,27 @@ __global__ void __launch_bounds__(ADW_MAXW * 32) k_attention_dec_warp(AttnDecDev
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // the last CTA of the (row, kv head) merges the CTAs' partials (a handful: 128 or 256 keys each)
-    __shared__ float wsm[AD_MAXSPLIT][GM], lsm[AD_MAXSPLIT][GM];
+    // the last CTA of the (row, kv head) merges the CTAs' partials (a handful: 64 to 256 keys each); the weights of a
+    // partial are recomputed where they are used (an exponential per load) rather than staged
     const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * AD_MAXG * (HD + 2);
-    for (int i = tid; i < nsplit * G; i += blockDim.x) {
-        const int sidx = i / G, g = i % G;
-        const float *ps = base + ((int64_t)sidx * AD_MAXG + g) * (HD + 2);
-        wsm[sidx][g] = __ldcg(ps); lsm[sidx][g] = __ldcg(ps + 1);
-    }
-    __syncthreads();
     if (tid < G) {
         float M = -INFINITY, L = 0.f;
-        for (int x = 0; x < nsplit; x++) M = fmaxf(M, wsm[x][tid]);
-        for (int x = 0; x < nsplit; x++) { const float w = expf(wsm[x][tid] - M); wsm[x][tid] = w; L = fmaf(lsm[x][tid], w, L); }
-        Lg[tid] = L;
+        for (int x = 0; x < nsplit; x++) M = fmaxf(M, __ldcg(base + ((int64_t)x * AD_MAXG + tid) * (HD + 2)));
+        for (int x = 0; x < nsplit; x++) {
+            const float *ps = base + ((int64_t)x * AD_MAXG + tid) * (HD + 2);
+            L = fmaf(__ldcg(ps + 1), expf(__ldcg(ps) - M), L);
+        }
+        Mg[tid] = M; Lg[tid] = L;
     }
     __syncthreads();
     for (int i = tid; i < G * HD; i += blockDim.x) {
         const int g = i / HD, d = i % HD;
+        const float M = Mg[g];
         float O = 0.f;
-        for (int x = 0; x < nsplit; x++) O = fmaf(__ldcg(base + ((int64_t)x * AD_MAXG + g) * (HD + 2) + 2 + d), wsm[x][g], O);
+        for (int x = 0; x < nsplit; x++) {
+            const float *ps = base + ((int64_t)x * AD_MAXG + g) * (HD + 2);
+            O = fmaf(__ldcg(ps + 2 + d), expf(__ldcg(ps) - M), O);
+        }
         const float L = Lg[g];
         const float r = L > 0.f ? O / L : 0.f;
         const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
@@ -437,46 +444,46 @@ void attention_decode(const AttnArgs &a) {
     const int64_t pairs = (int64_t)a.rows * a.Hkv;
     static const bool warp_kernel = !getenv("NCM_B200_OLD_ATTN_DEC");
     const bool warp_always = getenv("NCM_B200_ATTN_DEC_WARP") != nullptr;       // read per call: tests run both kernels on the same inputs
-    // The warp-per-chunk kernel where it measured faster: one or two (query, head) pairs per kv head (a warp then
-    // has little arithmetic per key: GPT-2 at one sequence, 0.43 -> 0.40 ms per token) and few enough CTAs that
-    // all are resident at once. With seven heads per kv head a warp's serial arithmetic outweighs the barriers it
-    // saves (Qwen2 shape at one sequence: 1.10 -> 1.16 ms), and with hundreds of (row, kv head) pairs its 160
-    // registers per thread leave one CTA per SM (GPT-2 at 64 sequences: 1.44 -> 1.94 ms per step).
+    // The warp-per-chunk kernel for few (row, kv head) pairs, where the older kernel is a chain of barriers and a long
+    // merge: a warp takes up to two (query, head) pairs (more make its serial arithmetic the kernel: seven per warp
+    // measured 1.10 -> 1.16 ms per token on the Qwen2 shape), two or four chunks per CTA, and all CTAs must be resident at
+    // once. With hundreds of pairs the older kernel's higher occupancy wins (GPT-2 at 64 sequences: 1.44 against
+    // 1.94 ms per step).
     const int gq_w = (a.H / a.Hkv) * a.max_q;
-    const bool warp_pays = warp_always || (gq_w <= 2 && pairs * cdiv(max_chunks, 4) <= 2 * (int64_t)ctx().sm_count);
-    if (warp_kernel && warp_pays && a.hd == 64 && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0)) {
-        // four warps per CTA while that still gives the GPU fewer CTAs than SMs, else eight
-        const int nw = (pairs * cdiv(max_chunks, 4) <= 2 * (int64_t)ctx().sm_count) ? 4 : ADW_MAXW;
-        const int max_split = (int)cdiv(max_chunks, nw);
-        if (max_split <= AD_MAXSPLIT) {
-            size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
-            if (need > part_cap) {
-                if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
-                part = (float *)dev_alloc(need * 4); part_cap = need;
-            }
-            size_t nc = (size_t)a.rows * a.Hkv;
-            if (nc > count_cap) {
-                if (count) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(count); }
-                count = (unsigned *)dev_alloc(nc * 4); count_cap = nc;
-                CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
-            }
-            AttnDecDev d;
-            d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1;
-            d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
-            d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
-            d.step_d = a.step_d; d.len_step = a.k1_len_step;
-            d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split; d.cps = nw;
-            d.scale = 1.0f / sqrtf((float)a.hd);
-            d.part = part; d.count = count;
-            dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
-            ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
-            const int gq = (a.H / a.Hkv) * a.max_q;
-            if (gq <= 1) LAUNCH_PDL((k_attention_dec_warp<1>), grid, nw * 32, 0, d);
-            else if (gq <= 4) LAUNCH_PDL((k_attention_dec_warp<4>), grid, nw * 32, 0, d);
-            else if (gq <= 8) LAUNCH_PDL((k_attention_dec_warp<8>), grid, nw * 32, 0, d);
-            else LAUNCH_PDL((k_attention_dec_warp<16>), grid, nw * 32, 0, d);
-            return;
+    const int gmw = gq_w <= 1 ? 1 : (gq_w <= 8 ? 2 : 4);
+    const int hs = (int)cdiv(gq_w, gmw);                                         // 1, 2, 3 or 4 warps per chunk
+    const int cpc = hs <= 2 ? 4 : 2;                                             // chunks per CTA (128 or 64 keys): at most eight warps
+    const int max_split_w = (int)cdiv(max_chunks, cpc);
+    const bool warp_pays = warp_always || pairs * max_split_w <= 2 * (int64_t)ctx().sm_count;
+    if (warp_kernel && warp_pays && a.hd == 64 && hs * cpc <= 8 && max_split_w <= AD_MAXSPLIT &&
+        ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0)) {
+        const int max_split = max_split_w;
+        size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
+        if (need > part_cap) {
+            if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
+            part = (float *)dev_alloc(need * 4); part_cap = need;
         }
+        size_t nc = (size_t)a.rows * a.Hkv;
+        if (nc > count_cap) {
+            if (count) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(count); }
+            count = (unsigned *)dev_alloc(nc * 4); count_cap = nc;
+            CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
+        }
+        AttnDecDev d;
+        d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1;
+        d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
+        d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
+        d.step_d = a.step_d; d.len_step = a.k1_len_step;
+        d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split; d.cps = cpc; d.hs = hs;
+        d.scale = 1.0f / sqrtf((float)a.hd);
+        d.part = part; d.count = count;
+        dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
+        ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+        const int threads = hs * cpc * 32;
+        if (gmw == 1) LAUNCH_PDL((k_attention_dec_warp<1>), grid, threads, 0, d);
+        else if (gmw == 2) LAUNCH_PDL((k_attention_dec_warp<2>), grid, threads, 0, d);
+        else LAUNCH_PDL((k_attention_dec_warp<4>), grid, threads, 0, d);
+        return;
     }
     static const int per_sm = getenv("NCM_B200_ATTN_DEC_PER_SM") ? atoi(getenv("NCM_B200_ATTN_DEC_PER_SM")) : 8;
     int want_split = (int)std::min<int64_t>(max_chunks, cdiv((int64_t)ctx().sm_count * per_sm, pairs));
