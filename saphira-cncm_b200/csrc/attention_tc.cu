@@ -1,29 +1,29 @@
 // Tensor-core attention for head dim 64 on sm_100a (tcgen05 + TMEM + TMA).
 //
-// One CTA (512 threads) per (sequence row, head, 128-query tile):
-//   S = Q K^T   tcgen05.mma.kind::tf32 into tensor memory; the query tile and ALL keys of the row (up to 288
-//               padded keys: a 256-token prefix plus a 32-token level) are fetched together by TMA and stay
-//               resident, so the score phase is one load, one split pass and one batch of MMAs
-//   softmax     four threads per query row (each takes a quarter of the columns) read the scores with
-//               tcgen05.ld; all keys of a row are resident, so the row maximum is known before
-//               any exponential is taken and no rescaling is needed
-//   O += P V    per 32-key chunk: P is written to shared memory by the softmax threads, V (fetched
-//               for up to eight chunks ahead) is transposed on chip, tcgen05.mma accumulates the
-//               128 x 64 output in TMEM; P / V^T are double-buffered so the MMAs of one chunk run
-//               under the softmax of the next
-// Scores are three TF32 MMAs over hi/lo splits (a = a_hi + a_lo), formed on chip from the fp32 tiles TMA
-// brings in. P V runs on fp16 pairs (v = v1 + v2 * 2^-11, as the fp16-pair GEMM does): main += p1 v1 and
-// cross += p1 v2 + p2 v1 in two accumulators, O = main + cross * 2^-11 -- six kind::f16 MMAs per chunk where
-// TF32 needed twelve of half the depth, and that chain of small MMAs is what paces the chunk loop. Both
-// are fp32-grade like the CUDA-core kernel. Two chunks share one hand-over: P and V^T tiles are 64 keys wide
-// (one 128-byte-swizzled row of fp16), hi and lo in tiles of their own.
-// Key rows come from up to two segments (cached prefix, tokens of the current pass); each
-// segment is padded to a multiple of 32 score columns and the padding is masked in the softmax.
+// One CTA (16 softmax warps + one MMA warp) per (sequence row, group of heads that share a kv head, 128-query tile).
+// The keys and values of the row (up to 288 padded keys: a 256-token prefix plus a 32-token level) are fetched ONCE
+// by TMA, turned into fp16 pairs in place and stay resident; the CTA then walks its heads ("items") one after the
+// other, so the fetch and the conversion are shared by the heads of the group and the phases of neighbouring items
+// overlap: the score MMAs of item i+1 run under the output phase of item i, the query tile of item i+1 arrives and
+// is converted under the softmax of item i.
+//   S = Q K^T   three kind::f16 MMAs per 16 dims over pairs x = x1 + x2 (x1 = rn_f16(x), x2 = rn_f16(x - x1), NOT
+//               scaled: one accumulator takes q2 k1 + q1 k2 + q1 k1; where x2 falls into the fp16 subnormals,
+//               |x| < 1/8, it is exact to 3e-8 absolute, below the dropped q2 k2 term for every |k| that matters)
+//   softmax     four threads per query row (each takes a quarter of every 32-key chunk) read the scores with
+//               tcgen05.ld once and keep them in registers; all keys of a row are resident, so the row maximum is
+//               known before any exponential is taken and nothing is rescaled
+//   O += P V    per 32-key chunk: the team writes P as fp16 pairs (p = p1 + p2 * 2^-11, as the fp16-pair GEMM does)
+//               into the half of a 64-key tile, the MMA warp accumulates main += p1 v1 and cross += p1 v2 + p2 v1;
+//               the value pairs are read in their natural [key][dim] order as an MN-major operand
+// Both products are fp32-grade like the CUDA-core kernel. Key rows come from up to two segments (cached prefix,
+// tokens of the current pass); each segment is padded to a multiple of 32 score columns, the padding is masked
+// in the softmax and its value rows are zeroed.
 //
-// Shared memory, reused between the two phases:
-//   QA  (64 KB)   Q hi | Q lo                                 then  V^T pairs, two buffers (32 KB)
-//   KA  (144 KB)  K hi atoms | K lo atoms, 288 rows each      then  raw V, one 8 KB slot per 32-key chunk (72 KB)
-//                                                                   and P pairs, two buffers (64 KB)
+// Shared memory (208 KB of tiles):
+//   QB[2] (32 KB each)  raw query tile (two 32-column atoms) -> Q hi | Q lo -> after the item's score MMAs the P
+//                       hi | lo tile of the same item (two 32-key halves, handed over one at a time)
+//   KP    (72 KB)       raw keys -> K hi rows | K lo rows            VP (72 KB) the same for the values
+// Tensor memory: scores [0, 288), output main [288, 352), cross [352, 416).
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "split.cuh"
@@ -31,14 +31,13 @@
 namespace ncmb {
 
 constexpr int ATC_THREADS = 512;          // softmax team: four threads per query row, eight score columns of a chunk each
-constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the PV MMAs while the team works on the next chunk
+constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the MMAs
 constexpr int ATC_MAXK = 288;            // padded keys per row the kernel keeps resident
 constexpr int ATC_OCOL = 288;            // TMEM columns of the output accumulators (main, then cross terms); scores use [0, 288)
-constexpr int ATC_PBUF = 32768, ATC_VBUF = 16384;  // P hi | lo tiles (128 rows x 128 B each) / V^T hi | lo tiles (64 rows x 128 B each) of a 64-key step
 constexpr int ATC_VSLOTS = ATC_MAXK / 32;
-constexpr int ATC_KATOM = ATC_MAXK * 128;                    // one 32-column atom of all key rows: 36 KB
-constexpr int ATC_QA = 65536, ATC_KA = 4 * ATC_KATOM;        // 64 KB + 144 KB
-constexpr int ATC_SMEM = 1024 + ATC_QA + ATC_KA + ATC_THREADS * 4 + 32 * 8 + 64;
+constexpr int ATC_QB = 32768;                                // a 128 x 64 tile as pairs: hi 16 KB | lo 16 KB
+constexpr int ATC_KP = ATC_MAXK * 128;                       // all key rows, one half of the pair (or one raw atom): 36 KB
+constexpr int ATC_SMEM = 1024 + 2 * ATC_QB + 4 * ATC_KP + 2 * ATC_THREADS * 4 + 32 * 8 + 64;
 
 struct AttnTcDev {
     float *out; float *out_lo; int64_t ldo; int out_fmt;
@@ -46,6 +45,7 @@ struct AttnTcDev {
     int H, Hkv, causal, causal_off, window;
     const float *v1; int64_t ldv1;   // segment-1 values as plain pointers (single-key shortcut)
     int pack;        // 1: the tile holds the (<= 32) queries of all H/Hkv (<= 4) heads that share one kv head, 32 rows per head
+    int hpc;         // heads a CTA walks (pack == 0): a divisor of H/Hkv; blockIdx.y * hpc is its first head
     float scale;
     int *err;
     // key-block mode (rows with more keys than the kernel keeps resident): this launch sees keys [kb_off, kb_off + kb_len)
@@ -53,37 +53,18 @@ struct AttnTcDev {
     // block's maximum (log2 domain, scaled) and sum to ml, for k_attention_merge to combine the blocks
     int kb_off, kb_len;
     float *ml;
-    // 1: the value tiles stay in their natural [key][dim] order and the P V MMAs read them as an MN-major B operand
-    // (no transpose: a thread converts one float4 to four hi and four lo halves); 0: transposed on chip into [dim][key]
-    int v_mn;
 };
 
-// byte offset of element (row, col) in a K-major tile of 32 floats per row with 128-byte swizzle
-__device__ __forceinline__ uint32_t sw128_off(int row, int col) {
-    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) & 7) << 4) + ((col & 3) << 2));
-}
-// byte offset of byte column cb (0..127) of a row in a 128-byte-swizzled tile
-__device__ __forceinline__ uint32_t sw128_boff(int row, int cb) {
-    return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((((cb >> 4) ^ (row & 7)) & 7) << 4) + (cb & 15));
-}
-__device__ __forceinline__ float atc_hi(float v) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
-    return __uint_as_float(u);
-}
 // 2^x through the special-function unit (about 2 ulp): the probabilities are split into 22-bit pairs right after
 __device__ __forceinline__ float atc_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+__device__ __forceinline__ float atc_max3(float a, float b, float c) {
+    float m;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(m) : "f"(a), "f"(b), "f"(c));
+    return m;
 }
 // without the wait: issue all loads of a row, then tmem_ld_wait() once
 __device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t *r) {
@@ -91,19 +72,57 @@ __device__ __forceinline__ void tmem_ld8_issue(uint32_t taddr, uint32_t *r) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
 }
-// in place: tile -> hi, and lo into the twin buffer; n4 float4 elements, layout-agnostic
-__device__ __forceinline__ void split_tile(unsigned char *hi, unsigned char *lo, int n4, int tid) {
-    for (int i = tid; i < n4; i += ATC_THREADS) {
-        float4 x = ((float4 *)hi)[i];
-        float4 h = make_float4(atc_hi(x.x), atc_hi(x.y), atc_hi(x.z), atc_hi(x.w));
-        ((float4 *)hi)[i] = h;
-        ((float4 *)lo)[i] = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+}
+
+// A tile as TMA delivers it -- rows of 64 floats as two 32-float atoms (128-byte swizzle), the atoms `atom` bytes
+// apart -- becomes fp16 pairs IN PLACE: hi rows (64 halves = 128 bytes, same swizzle) where atom 0 was, lo rows where
+// atom 1 was. A unit is eight dims of one row: two float4 in, one 16-byte store per half out. All units are read
+// into registers (atc_units_read) before anyone writes (atc_units_write); the caller puts a team barrier in between.
+template <int NU>
+__device__ __forceinline__ void atc_units_read(const unsigned char *base, uint32_t atom, int nrows, int tid, float4 (&x)[NU][2]) {
+#pragma unroll
+    for (int i = 0; i < NU; i++) {
+        const int u = tid + i * ATC_THREADS, row = u >> 3, d8 = u & 7;
+        if (row < nrows) {
+            const unsigned char *rp = base + (size_t)(d8 >> 2) * atom + (row >> 3) * 1024 + (row & 7) * 128;
+            const int c0 = (d8 & 3) * 2;
+            x[i][0] = *(const float4 *)(rp + (((c0) ^ (row & 7)) << 4));
+            x[i][1] = *(const float4 *)(rp + (((c0 + 1) ^ (row & 7)) << 4));
+        }
+    }
+}
+// lo_scale: 1 for the score operands, 2^11 for the values; rows whose index in its segment is past the segment's
+// length (n1 of the first n1p rows, then n2) are written as zeros
+template <int NU>
+__device__ __forceinline__ void atc_units_write(unsigned char *base, uint32_t atom, int nrows, int tid, const float4 (&x)[NU][2],
+                                                float lo_scale, int n1p, int n1, int n2) {
+#pragma unroll
+    for (int i = 0; i < NU; i++) {
+        const int u = tid + i * ATC_THREADS, row = u >> 3, d8 = u & 7;
+        if (row < nrows) {
+            const bool valid = row < n1p ? row < n1 : (row - n1p) < n2;
+            const float v[8] = {x[i][0].x, x[i][0].y, x[i][0].z, x[i][0].w, x[i][1].x, x[i][1].y, x[i][1].z, x[i][1].w};
+            uint32_t hw[4], lw[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                h16_pair2(valid ? v[2 * e] : 0.f, valid ? v[2 * e + 1] : 0.f, hw[e], lw[e], lo_scale);
+            }
+            const uint32_t o = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + (((d8) ^ (row & 7)) << 4));
+            *(uint4 *)(base + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+            *(uint4 *)(base + atom + o) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+        }
     }
 }
 
 // A barrier wait that ran out marks the thread: its later waits return at once, so a CTA leaves within a
 // few wait limits. Control flow never depends on the outcome (all threads keep meeting at the same
-// __syncthreads); the host sees the code and discards the results.
+// barriers); the host sees the code and discards the results.
 struct BoundedWaiter {
     int *err; bool dead;
     __device__ __forceinline__ void wait(uint32_t bar, uint32_t parity, int code) {
@@ -112,6 +131,8 @@ struct BoundedWaiter {
     }
 };
 
+// NCH: 32-key chunks a thread keeps the scores of in registers (8 for rows of up to 256 padded keys, else 9)
+template <int NCH>
 __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constant__ CUtensorMap mq,
                                                              const __grid_constant__ CUtensorMap mk1,
                                                              const __grid_constant__ CUtensorMap mk2,
@@ -120,29 +141,31 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     pdl_wait();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char *R0 = smem;                                    // QA
-    unsigned char *KA = smem + ATC_QA;                           // K hi atom 0 | hi atom 1 | lo atom 0 | lo atom 1
-    unsigned char *R1 = KA;                                      // phase 2: raw V slots
-    unsigned char *R2 = KA + ATC_VSLOTS * 8192;                  // phase 2: P buffers
-    float *xch = (float *)(smem + ATC_QA + ATC_KA);                       // one float per thread: row max / row sum exchange
-    uint64_t *bars = (uint64_t *)(xch + ATC_THREADS);
+    unsigned char *QB = smem;                                    // two query / P tiles
+    unsigned char *KP = smem + 2 * ATC_QB;                       // K hi | K lo
+    unsigned char *VP = KP + 2 * ATC_KP;                         // V hi | V lo
+    float *xmax = (float *)(VP + 2 * ATC_KP);                    // one float per thread: row maximum exchange
+    float *xsum = xmax + ATC_THREADS;                            // ... and row sum exchange
+    uint64_t *bars = (uint64_t *)(xsum + ATC_THREADS);
     uint32_t *tmem_slot = (uint32_t *)(bars + 32);
-    // barriers: 0 Q | 1 K full | 3 S MMAs done | 5,6 PV MMAs of a buffer done | 8..16 V slots | 20,21 P / V^T buffer ready
-    const uint32_t bar_q = smem_u32(bars), bar_k0 = smem_u32(bars + 1), bar_s0 = smem_u32(bars + 3);
-    const uint32_t bar_pv0 = smem_u32(bars + 5), bar_v0 = smem_u32(bars + 8), bar_rdy0 = smem_u32(bars + 20);
+    // barriers: 0,1 query tile landed | 2 keys landed | 3 values landed | 4 Q (and K) pairs ready for the score MMAs |
+    //           5 score MMAs done | 6,7 P half ready | 8,9 PV MMAs of a P half done
+    const uint32_t bar_q = smem_u32(bars), bar_k = smem_u32(bars + 2), bar_v = smem_u32(bars + 3), bar_qrdy = smem_u32(bars + 4);
+    const uint32_t bar_s = smem_u32(bars + 5), bar_rdy0 = smem_u32(bars + 6), bar_pv0 = smem_u32(bars + 8);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = blockIdx.z, qt = blockIdx.x;
     const int G = a.H / a.Hkv;
-    const int kvh = a.pack ? (int)blockIdx.y : (int)blockIdx.y / G;
+    const int h0 = a.pack ? (int)blockIdx.y * G : (int)blockIdx.y * a.hpc;     // first head of this CTA
+    const int kvh = h0 / G;
+    const int gn = a.pack ? 1 : a.hpc;                                         // items: one head each (pack: all heads in one)
     const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
     if (qt * 128 >= nq) return;
     // one query, one key (the unconditional rows of a classifier-free-guidance batch: a one-token prefix):
     // the softmax weight is exactly 1, the context is the value row
     if (!a.pack && !a.ml && nq == 1 && !a.k2_start && (a.k1_len ? a.k1_len[row] : a.k1_start[row + 1] - a.k1_start[row]) == 1) {
-        if (tid < 64) {
-            const int kvh1 = (int)blockIdx.y / G;
-            const float x = a.v1[(int64_t)a.k1_start[row] * a.ldv1 + kvh1 * 64 + tid];
-            const int64_t at = (int64_t)q0 * a.ldo + (int)blockIdx.y * 64 + tid;
+        if (tid < 64 * gn) {
+            const float x = a.v1[(int64_t)a.k1_start[row] * a.ldv1 + kvh * 64 + (tid & 63)];
+            const int64_t at = (int64_t)q0 * a.ldo + (h0 + (tid >> 6)) * 64 + (tid & 63);
             if (a.out_lo) store_split1(a.out, a.out_lo, at, x, a.out_fmt);
             else a.out[at] = x;
         }
@@ -165,12 +188,31 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     const int n1p = (n1 + 31) & ~31, n2p = (n2 + 31) & ~31, nkp = n1p + n2p;
     const int nchunks = nkp >> 5;
     const int vofs = a.Hkv * 64;
+    if (nkp == 0) {                                // no key in sight: zero context, empty block statistics
+        if (tid < ATC_THREADS) {
+            const int r = tid & 127, part = tid >> 7, qi = a.pack ? (r & 31) : qt * 128 + r;
+            for (int it = 0; it < gn; it++) {
+                const int h = a.pack ? h0 + (r >> 5) : h0 + it;
+                if (qi >= nq || h >= (kvh + 1) * G) continue;
+                if (a.ml && part == 0) { float *mlp = a.ml + ((int64_t)(q0 + qi) * a.H + h) * 2; mlp[0] = -INFINITY; mlp[1] = 0.f; }
+                const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
+                const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < 16; j += 4) {
+                    if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, z, a.out_fmt);
+                    else *(float4 *)(a.out + ofs + j) = z;
+                }
+            }
+        }
+        return;
+    }
     BoundedWaiter w{a.err, false};
 
     if (tid == 0) {
-        for (int i = 0; i < 7; i++) mbar_init(bar_q + 8 * i, 1);
-        for (int i = 0; i < ATC_VSLOTS; i++) mbar_init(bar_v0 + 8 * i, 1);
-        mbar_init(bar_rdy0, ATC_THREADS / 32); mbar_init(bar_rdy0 + 8, ATC_THREADS / 32);   // one arrival per team warp
+        mbar_init(bar_q, 1); mbar_init(bar_q + 8, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
+        mbar_init(bar_qrdy, ATC_THREADS / 32);                                   // one arrival per team warp
+        mbar_init(bar_s, 1);
+        mbar_init(bar_rdy0, ATC_THREADS / 32); mbar_init(bar_rdy0 + 8, ATC_THREADS / 32);
+        mbar_init(bar_pv0, 1); mbar_init(bar_pv0 + 8, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -183,110 +225,123 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    // all (padded) key rows of the row -> KA as raw fp32, 32-row boxes, two 32-column atoms
-    auto load_keys = [&]() {
-        mbar_expect_tx(bar_k0, (uint32_t)nkp * 256);
-        for (int g = 0; g < nkp / 32; g++) {
-            int j0 = g * 32;
-            const CUtensorMap *mk = j0 < n1p ? &mk1 : &mk2;
-            int tok = j0 < n1p ? k10 + j0 : k20 + (j0 - n1p);
-            tma_load_2d(smem_u32(KA + g * 4096), mk, kvh * 64, tok, bar_k0);
-            tma_load_2d(smem_u32(KA + ATC_KATOM + g * 4096), mk, kvh * 64 + 32, tok, bar_k0);
-        }
-    };
-    auto load_vchunk = [&](int c) {
-        const int c0 = c * 32, slot = c % ATC_VSLOTS;
-        const CUtensorMap *mk = c0 < n1p ? &mk1 : &mk2;
-        int tok = c0 < n1p ? k10 + c0 : k20 + (c0 - n1p);
-        const uint32_t bar = bar_v0 + 8 * slot;
-        mbar_expect_tx(bar, 8192);
-        tma_load_2d(smem_u32(R1 + slot * 8192), mk, vofs + kvh * 64, tok, bar);
-        tma_load_2d(smem_u32(R1 + slot * 8192 + 4096), mk, vofs + kvh * 64 + 32, tok, bar);
-    };
-
-    // ================= phase 1: S = Q K^T =================
-    if (tid == 0) {
+    // the query tile of item `it` -> QB[it & 1] as raw fp32 (two atoms)
+    auto load_q = [&](int it) {
+        const uint32_t bar = bar_q + 8 * (it & 1);
+        const uint32_t dst = smem_u32(QB + (it & 1) * ATC_QB);
         if (a.pack) {                                             // mq has 32-row boxes here: one per head of the group
-            mbar_expect_tx(bar_q, (uint32_t)G * 8192);
+            mbar_expect_tx(bar, (uint32_t)G * 8192);
             for (int g = 0; g < G; g++) {
-                tma_load_2d(smem_u32(R0 + g * 4096), &mq, (kvh * G + g) * 64, q0, bar_q);
-                tma_load_2d(smem_u32(R0 + 16384 + g * 4096), &mq, (kvh * G + g) * 64 + 32, q0, bar_q);
+                tma_load_2d(dst + g * 4096, &mq, (h0 + g) * 64, q0, bar);
+                tma_load_2d(dst + 16384 + g * 4096, &mq, (h0 + g) * 64 + 32, q0, bar);
             }
         } else {
-            mbar_expect_tx(bar_q, 32768);
-            tma_load_2d(smem_u32(R0), &mq, (int)blockIdx.y * 64, q0 + qt * 128, bar_q);
-            tma_load_2d(smem_u32(R0 + 16384), &mq, (int)blockIdx.y * 64 + 32, q0 + qt * 128, bar_q);
+            mbar_expect_tx(bar, 32768);
+            tma_load_2d(dst, &mq, (h0 + it) * 64, q0 + qt * 128, bar);
+            tma_load_2d(dst + 16384, &mq, (h0 + it) * 64 + 32, q0 + qt * 128, bar);
         }
-        if (nkp > 0) load_keys();
+    };
+    // 32 (padded) key or value rows of the row -> dst as raw fp32: group g of 32 rows, two 32-column atoms
+    auto load_row_group = [&](unsigned char *dst, int col0, uint32_t bar, int g) {
+        const int j0 = g * 32;
+        const CUtensorMap *mk = j0 < n1p ? &mk1 : &mk2;
+        const int tok = j0 < n1p ? k10 + j0 : k20 + (j0 - n1p);
+        tma_load_2d(smem_u32(dst + g * 4096), mk, col0, tok, bar);
+        tma_load_2d(smem_u32(dst + ATC_KP + g * 4096), mk, col0 + 32, tok, bar);
+    };
+    auto team_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(ATC_THREADS) : "memory"); };
+
+    // the first warp issues every load of the prologue, a lane per 32-row group of the keys (lanes 0..8) and of the
+    // values (lanes 16..24): thirty-odd copies leave in the time of two
+    if (warp == 0) {
+        if (lane == 0) {
+            load_q(0);
+            mbar_expect_tx(bar_k, (uint32_t)nkp * 256);
+            mbar_expect_tx(bar_v, (uint32_t)nkp * 256);
+        }
+        __syncwarp();
+        if (lane < 16) { if (lane < nchunks) load_row_group(KP, kvh * 64, bar_k, lane); }
+        else if (lane - 16 < nchunks) load_row_group(VP, vofs + kvh * 64, bar_v, lane - 16);
+        if (lane == 0 && gn > 1) load_q(1);
     }
-    w.wait(bar_q, 0, 11);
-    if (tid < ATC_THREADS) split_tile(R0, R0 + 32768, 2048, tid);
-    if (nkp > 0) {
-        w.wait(bar_k0, 0, 12);
-        if (tid < ATC_THREADS)
-            for (int at = 0; at < 2; at++) split_tile(KA + at * ATC_KATOM, KA + (2 + at) * ATC_KATOM, nkp * 8, tid);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    __syncthreads();
-    if (nkp > 0) {
-        if (tid == 0) {
-            tc_fence_after();
-            for (int r0 = 0; r0 < nkp; r0 += 256) {                   // N <= 256 per MMA: 256 + 32 for a full row
-                const int nrows = (nkp - r0) < 256 ? (nkp - r0) : 256;
-                const uint32_t idesc = umma_idesc_tf32(128, nrows);
-                const uint32_t d = tmem + (uint32_t)r0;
-                for (int at = 0; at < 2; at++) {
-                    uint64_t qh = umma_desc_sw128(smem_u32(R0 + at * 16384)), ql = umma_desc_sw128(smem_u32(R0 + 32768 + at * 16384));
-                    uint64_t kh = umma_desc_sw128(smem_u32(KA + at * ATC_KATOM + r0 * 128));
-                    uint64_t kl = umma_desc_sw128(smem_u32(KA + (2 + at) * ATC_KATOM + r0 * 128));
+
+    // where in an item the next item's query tile is converted and its score MMAs are issued: after the fourth
+    // chunk when there are more (the scores then finish under the rest of the chunk loop), else after the last
+    const bool conv_mid = nchunks > 4;
+    if (warp == ATC_THREADS / 32) {
+        // ================= MMA warp =================
+        if (lane == 0) {
+            const uint32_t idpv = umma_idesc_f16(128, 64) | (1u << 16);       // B (values) MN-major
+            const uint32_t dm = tmem + (uint32_t)ATC_OCOL, dc = dm + 64u;
+            const uint64_t kh = umma_desc_sw128(smem_u32(KP)), kl = umma_desc_sw128(smem_u32(KP + ATC_KP));
+            const uint64_t vh = umma_desc_sw128(smem_u32(VP)), vl = umma_desc_sw128(smem_u32(VP + ATC_KP));
+            auto scores = [&](int it) {
+                w.wait(bar_qrdy, (uint32_t)it & 1u, 12);
+                tc_fence_after();
+                const uint64_t qh = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB)), ql = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB + 16384));
+                for (int r0 = 0; r0 < nkp; r0 += 256) {                   // N <= 256 per MMA: 256 + 32 for a full row
+                    const int nrows = (nkp - r0) < 256 ? (nkp - r0) : 256;
+                    const uint32_t idesc = umma_idesc_f16(128, nrows);
+                    const uint32_t d = tmem + (uint32_t)r0;
+                    const uint64_t ro = (uint64_t)(r0 * 8);               // r0 rows of 128 bytes, in 16-byte units
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        umma_tf32(d, ql + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, (at | k) ? 1u : 0u);
-                        umma_tf32(d, qh + (uint64_t)(k * 2), kl + (uint64_t)(k * 2), idesc, 1u);
-                        umma_tf32(d, qh + (uint64_t)(k * 2), kh + (uint64_t)(k * 2), idesc, 1u);
+                    for (int k = 0; k < 4; k++) {                         // 16 dims per MMA: 32 bytes along the swizzled row
+                        umma_f16(d, ql + (uint64_t)(k * 2), kh + ro + (uint64_t)(k * 2), idesc, k ? 1u : 0u);
+                        umma_f16(d, qh + (uint64_t)(k * 2), kl + ro + (uint64_t)(k * 2), idesc, 1u);
+                        umma_f16(d, qh + (uint64_t)(k * 2), kh + ro + (uint64_t)(k * 2), idesc, 1u);
                     }
                 }
-            }
-            umma_commit(bar_s0);
-        }
-        w.wait(bar_s0, 0, 13);
-    }
-    tc_fence_after();
-    __syncthreads();                                              // every thread is past phase 1: regions may be reused
-
-    // ================= phase 2: softmax and O = P V =================
-    if (tid == 0)
-        for (int c = 0; c < nchunks; c++) load_vchunk(c);      // one slot per chunk: every V load is in flight now
-    auto team_sync = [&]() { asm volatile("bar.sync 1, %0;" ::"n"(ATC_THREADS) : "memory"); };
-    if (warp == ATC_THREADS / 32) {
-        // ---- MMA warp: O += P V for every chunk as soon as the team has filled a P / V^T buffer ----
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_f16(128, 64);
-            const uint32_t dm = tmem + (uint32_t)ATC_OCOL, dc = dm + 64u;
-            for (int c2 = 0; 2 * c2 < nchunks; c2++) {                 // a step = two 32-key chunks (the last one may have one)
-                const int b = c2 & 1;
-                w.wait(bar_rdy0 + 8 * b, (uint32_t)(c2 >> 1) & 1u, 17);
-                tc_fence_after();
-                const uint64_t p1 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF)), p2 = umma_desc_sw128(smem_u32(R2 + b * ATC_PBUF + 16384));
-                const uint64_t v1 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF)), v2 = umma_desc_sw128(smem_u32(R0 + b * ATC_VBUF + 8192));
-                const int nk = (nchunks - 2 * c2 >= 2) ? 4 : 2;                                   // 16 keys per MMA
-                // 16 keys further along: 32 bytes in a [row][key] tile (P, transposed V), two 8-key groups of 1024 bytes
-                // in a [key][dim] tile read as an MN-major operand
-                const uint64_t vstep = a.v_mn ? 128u : 2u;
-                const uint32_t idv = a.v_mn ? (idesc | (1u << 16)) : idesc;
-                for (int k = 0; k < nk; k++) {
-                    umma_f16(dm, p1 + (uint64_t)(k * 2), v1 + (uint64_t)k * vstep, idv, (c2 | k) ? 1u : 0u);
-                    umma_f16(dc, p1 + (uint64_t)(k * 2), v2 + (uint64_t)k * vstep, idv, (c2 | k) ? 1u : 0u);
-                    umma_f16(dc, p2 + (uint64_t)(k * 2), v1 + (uint64_t)k * vstep, idv, 1u);
+                umma_commit(bar_s);
+            };
+            uint32_t use[2] = {0u, 0u};                                   // hand-overs seen so far per P half
+            scores(0);
+            for (int it = 0; it < gn; it++) {
+                const uint64_t p1 = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB)), p2 = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB + 16384));
+                for (int c = 0; c < nchunks; c++) {
+                    const int hf = c & 1;
+                    w.wait(bar_rdy0 + 8 * hf, use[hf] & 1u, 17);
+                    use[hf]++;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {                         // 16 keys per MMA: 32 bytes of a P row, two 8-key groups of V rows
+                        const uint64_t po = (uint64_t)((2 * hf + k) * 2), vo = (uint64_t)(c * 256 + k * 128);
+                        umma_f16(dm, p1 + po, vh + vo, idpv, (c | k) ? 1u : 0u);
+                        umma_f16(dc, p1 + po, vl + vo, idpv, (c | k) ? 1u : 0u);
+                        umma_f16(dc, p2 + po, vh + vo, idpv, 1u);
+                    }
+                    umma_commit(bar_pv0 + 8 * hf);
+                    // the next item's scores: its query pairs are ready once the team is past chunk 3
+                    if (c == 3 && conv_mid && it + 1 < gn) scores(it + 1);
                 }
-                umma_commit(bar_pv0 + 8 * b);
+                if (!conv_mid && it + 1 < gn) scores(it + 1);
             }
         }
     } else {
+        // ================= softmax team =================
         const int r = tid & 127, part = tid >> 7;                     // query row of the tile, which quarter of each chunk's columns
         const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
-        const int h = a.pack ? kvh * G + (r >> 5) : (int)blockIdx.y;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        // ---- prologue: Q of item 0 and the keys -> pairs, then the values ----
+        {
+            float4 xq[2][2];
+            w.wait(bar_q, 0, 11);
+            atc_units_read<2>(QB, 16384, 128, tid, xq);
+            team_sync();
+            atc_units_write<2>(QB, 16384, 128, tid, xq, 1.0f, 128, 128, 0);
+            float4 xk[5][2];
+            w.wait(bar_k, 0, 12);
+            atc_units_read<5>(KP, ATC_KP, nkp, tid, xk);
+            team_sync();
+            atc_units_write<5>(KP, ATC_KP, nkp, tid, xk, 1.0f, nkp, nkp, 0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_qrdy);
+            w.wait(bar_v, 0, 14);
+            atc_units_read<5>(VP, ATC_KP, nkp, tid, xk);
+            team_sync();
+            atc_units_write<5>(VP, ATC_KP, nkp, tid, xk, H16_LO_SCALE, n1p, n1, n2);
+            // made visible to the MMA warp by the fence before the first P hand-over
+        }
         // visible columns of chunk c for this thread's query, as [jlo, jhi) relative to the chunk start
         auto chunk_range = [&](int c, int &jlo, int &jhi) {
             const int c0 = c * 32;
@@ -300,142 +355,121 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             if (a.window > 0) { lo = max(lo, qi - a.window); hi = min(hi, qi + a.window + 1); }
             jlo = lo - base; jhi = hi - base;
         };
-        // The thread's scores -- eight columns of every chunk -- are read from tensor memory ONCE, all loads in
-        // flight together, and stay in registers for the maximum and for the exponentials: a tcgen05.ld round
-        // trip costs about a microsecond, and one per chunk was most of the chunk loop.
-        uint32_t sv[ATC_VSLOTS][8];
-#pragma unroll
-        for (int c = 0; c < ATC_VSLOTS; c++) tmem_ld8_issue(lane_addr + (uint32_t)(c * 32 + part * 8), sv[c]);
-        tmem_ld_wait();
-        float mx = -INFINITY;
-#pragma unroll
-        for (int c = 0; c < ATC_VSLOTS; c++) {
-            if (c < nchunks) {
-                int jlo, jhi;
-                chunk_range(c, jlo, jhi);
-                jlo -= part * 8; jhi -= part * 8;
-#pragma unroll
-                for (int j = 0; j < 8; j++)
-                    if (j >= jlo && j < jhi) mx = fmaxf(mx, __uint_as_float(sv[c][j]));
-            }
-        }
-        xch[tid] = mx;
-        team_sync();
-        mx = fmaxf(fmaxf(xch[r], xch[r + 128]), fmaxf(xch[r + 256], xch[r + 384]));
-        team_sync();                                                  // xch is reused for the row sums
-        const bool any = mx != -INFINITY;
         const float sl2 = a.scale * 1.4426950408889634f;
-
-        // shared-memory offsets of the thread's four V elements (source: raw [key][d] atoms, destination: V^T)
-        const int kk = tid & 31;
-        uint32_t vsrc[4], vdst[4];                                   // vdst: offset in the hi tile; the lo tile takes the same offset
-#pragma unroll
-        for (int n = 0; n < 4; n++) {
-            const int d = (tid >> 5) + 16 * n;
-            vsrc[n] = (uint32_t)((d >> 5) * 4096) + sw128_off(kk, d & 31);
-            vdst[n] = sw128_boff(d, kk * 2);
-        }
-        float l = 0.f;
         const uint32_t rowoff = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        // A step hands TWO 32-key chunks to the MMA warp: the fence, the barrier arrival and the wait for the
-        // buffer are paid once per 64 keys.
+        uint32_t use0 = 0u, use1 = 0u;                                // hand-overs made so far per P half
+        for (int it = 0; it < gn; it++) {
+            unsigned char *Pb = QB + (it & 1) * ATC_QB;               // this item's query pairs, dead once its scores are in
+            const int h = a.pack ? h0 + (r >> 5) : h0 + it;
+            w.wait(bar_s, (uint32_t)it & 1u, 13);
+            tc_fence_after();
+            // The thread's scores -- eight columns of every chunk -- are read from tensor memory ONCE, all loads in
+            // flight together, and stay in registers for the maximum and for the exponentials.
+            uint32_t sv[NCH][8];
 #pragma unroll
-        for (int c2 = 0; c2 < (ATC_VSLOTS + 1) / 2; c2++) {
-            if (2 * c2 >= nchunks) break;
-            const int b = c2 & 1;
-            unsigned char *Pb = R2 + b * ATC_PBUF, *Vt = R0 + b * ATC_VBUF;
-            if (c2 >= 2) w.wait(bar_pv0 + 8 * b, (uint32_t)((c2 >> 1) - 1) & 1u, 15);   // MMAs of step c2-2 are done with buffer b
+            for (int c = 0; c < NCH; c++) tmem_ld8_issue(lane_addr + (uint32_t)(c * 32 + part * 8), sv[c]);
+            tmem_ld_wait();
+            float mx = -INFINITY;
 #pragma unroll
-            for (int hf = 0; hf < 2; hf++) {
-                const int c = 2 * c2 + hf;
-                if (c >= ATC_VSLOTS || c >= nchunks) break;
-                {
-                    const uint32_t *v = sv[c];
+            for (int c = 0; c < NCH; c++) {
+                if (c < nchunks) {
+                    // columns this query does not see (padding, causal / window limits) become -inf once, here: the
+                    // maximum and the exponentials below then run without range tests (2^-inf = 0)
                     int jlo, jhi;
                     chunk_range(c, jlo, jhi);
                     jlo -= part * 8; jhi -= part * 8;
-                    const bool inner = any && jlo <= 0 && jhi >= 8;
+                    uint32_t *v = sv[c];
+                    if (jlo > 0 || jhi < 8) {
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (j < jlo || j >= jhi) v[j] = 0xff800000u;
+                    }
+                    const float m0 = atc_max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+                    const float m1 = atc_max3(__uint_as_float(v[3]), __uint_as_float(v[4]), __uint_as_float(v[5]));
+                    mx = atc_max3(mx, m0, atc_max3(m1, __uint_as_float(v[6]), __uint_as_float(v[7])));
+                }
+            }
+            xmax[tid] = mx;
+            team_sync();
+            mx = fmaxf(fmaxf(xmax[r], xmax[r + 128]), fmaxf(xmax[r + 256], xmax[r + 384]));
+            const bool any = mx != -INFINITY;
+            // 2^(s sl2 - mx sl2): one multiply-add per score; a row that sees no key keeps its -inf scores as they are
+            const float nmx = any ? -mx * sl2 : 0.f;
+            const bool conv = it + 1 < gn;
+            // the next item's query tile (it landed long ago) -> pairs in place, then its score MMAs may go
+            auto convert_next_q = [&]() {
+                float4 xq[2][2];
+                unsigned char *Qn = QB + ((it + 1) & 1) * ATC_QB;
+                w.wait(bar_q + 8 * ((it + 1) & 1), (uint32_t)((it + 1) >> 1) & 1u, 11);
+                atc_units_read<2>(Qn, 16384, 128, tid, xq);
+                team_sync();
+                atc_units_write<2>(Qn, 16384, 128, tid, xq, 1.0f, 128, 128, 0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_qrdy);
+            };
+            float l = 0.f;
+#pragma unroll
+            for (int c = 0; c < NCH; c++) {
+                if (c >= nchunks) break;
+                const int hf = c & 1;
+                // the MMAs of the previous hand-over of this half are done with it
+                { const uint32_t n = hf ? use1 : use0; if (n >= 1u) w.wait(bar_pv0 + 8 * hf, (n - 1u) & 1u, 15); }
+                {
+                    const uint32_t *v = sv[c];
                     uint32_t hw[4], lw[4];                                 // eight probabilities as packed fp16 pairs
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        unsigned short h0, l0, h1, l1;
-                        float x0 = atc_ex2((__uint_as_float(v[2 * e]) - mx) * sl2), x1 = atc_ex2((__uint_as_float(v[2 * e + 1]) - mx) * sl2);
-                        if (!inner) {                                      // interior chunks skip the range tests
-                            if (!(any && 2 * e >= jlo && 2 * e < jhi)) x0 = 0.f;
-                            if (!(any && 2 * e + 1 >= jlo && 2 * e + 1 < jhi)) x1 = 0.f;
-                        }
+                        const float x0 = atc_ex2(fmaf(__uint_as_float(v[2 * e]), sl2, nmx)), x1 = atc_ex2(fmaf(__uint_as_float(v[2 * e + 1]), sl2, nmx));
                         l += x0 + x1;
-                        h16_pair(x0, h0, l0); h16_pair(x1, h1, l1);
-                        hw[e] = (uint32_t)h0 | ((uint32_t)h1 << 16); lw[e] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+                        h16_pair2(x0, x1, hw[e], lw[e]);
                     }
                     // the thread's eight keys are 16-byte chunk 4 hf + part of its row in the hi tile and in the lo tile
                     const uint32_t o = rowoff + ((uint32_t)(((4 * hf + part) ^ (r & 7)) & 7) << 4);
                     *(uint4 *)(Pb + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
                     *(uint4 *)(Pb + 16384 + o) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
                 }
-                w.wait(bar_v0 + 8 * (c % ATC_VSLOTS), (uint32_t)(c / ATC_VSLOTS) & 1u, 14);
-                if (a.v_mn) {   // split only: Vraw[key][d] (two 32-column atoms) -> pair tiles [key][d], one float4 per thread
-                    const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
-                    const int c0 = c * 32;
-                    const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
-                    const int vk = tid >> 4, d4 = tid & 15;                   // key of the chunk, which four dims
-                    float4 x = *(const float4 *)(Vraw + (d4 >> 3) * 4096 + sw128_off(vk, (d4 & 7) * 4));
-                    if (vk >= nvalid) x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    unsigned short h0, l0, h1, l1, h2, l2, h3, l3;
-                    h16_pair(x.x, h0, l0); h16_pair(x.y, h1, l1); h16_pair(x.z, h2, l2); h16_pair(x.w, h3, l3);
-                    const uint32_t o = sw128_boff(hf * 32 + vk, d4 * 8);
-                    *(uint2 *)(Vt + o) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
-                    *(uint2 *)(Vt + 8192 + o) = make_uint2((uint32_t)l0 | ((uint32_t)l1 << 16), (uint32_t)l2 | ((uint32_t)l3 << 16));
-                } else {   // transpose + split: Vraw[key][d] (two 32-column atoms) -> Vt[d][key]; keys past the segment end read as 0
-                    const unsigned char *Vraw = R1 + (c % ATC_VSLOTS) * 8192;
-                    const int c0 = c * 32;
-                    const int nvalid = c0 < n1p ? (n1 - c0) : (n2 - (c0 - n1p));
+                // hand the half to the MMA warp: this warp's writes (and its reads of the previous item's output) are
+                // ordered before the MMAs, one arrival per warp
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_rdy0 + 8 * hf);
+                if (hf) use1++; else use0++;
+                if (c == 3 && conv_mid && conv) convert_next_q();
+            }
+            if (!conv_mid && conv) convert_next_q();
+            // the commits complete in order: the last one covers every earlier MMA of the item
+            { const int hf = (nchunks - 1) & 1; const uint32_t n = hf ? use1 : use0; w.wait(bar_pv0 + 8 * hf, (n - 1u) & 1u, 16); }
+            tc_fence_after();
+            xsum[tid] = l;
+            team_sync();
+            l = (xsum[r] + xsum[r + 128]) + (xsum[r + 256] + xsum[r + 384]);
+            // every thread is past the item's last MMA: its tile takes the query tile of the item after the next
+            if (tid == 0 && it + 2 < gn) load_q(it + 2);
+            if (a.ml && part == 0 && qi < nq) {
+                float *mlp = a.ml + ((int64_t)(q0 + qi) * a.H + h) * 2;
+                mlp[0] = any ? mx * sl2 : -INFINITY; mlp[1] = l;
+            }
+            // ---- output row: O / l; the four threads of a row take 16 columns each ----
+            {
+                const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
+                const float inv = l > 0.f ? 1.0f / l : 0.f;
+                const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
+                uint32_t v[16], vc[16];
+                tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
+                tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
+                tmem_ld_wait();
+                if (live) {
 #pragma unroll
-                    for (int n = 0; n < 4; n++) {
-                        float x = *(const float *)(Vraw + vsrc[n]);
-                        if (kk >= nvalid) x = 0.f;
-                        unsigned short hi, lo;
-                        h16_pair(x, hi, lo);
-                        const uint32_t o = vdst[n] ^ (uint32_t)(hf * 64);      // keys 32..63 of the step: 64 B further along the row
-                        *(unsigned short *)(Vt + o) = hi; *(unsigned short *)(Vt + 8192 + o) = lo;
+                    for (int j = 0; j < 16; j += 4) {
+                        const float4 o4 = make_float4(fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv,
+                                                      fmaf(__uint_as_float(vc[j + 1]), H16_LO_UNSCALE, __uint_as_float(v[j + 1])) * inv,
+                                                      fmaf(__uint_as_float(vc[j + 2]), H16_LO_UNSCALE, __uint_as_float(v[j + 2])) * inv,
+                                                      fmaf(__uint_as_float(vc[j + 3]), H16_LO_UNSCALE, __uint_as_float(v[j + 3])) * inv);
+                        if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
+                        else *(float4 *)(a.out + ofs + j) = o4;
                     }
-                }
-            }
-            // hand the buffers to the MMA warp: this warp's writes are visible to the async proxy, one arrival per warp
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_rdy0 + 8 * b);
-        }
-        // the commits complete in order: the last one covers every earlier MMA
-        if (nchunks > 0) { const int c2 = (nchunks - 1) >> 1; w.wait(bar_pv0 + 8 * (c2 & 1), (uint32_t)(c2 >> 1) & 1u, 16); }
-        tc_fence_after();
-        xch[tid] = l;
-        team_sync();
-        l = (xch[r] + xch[r + 128]) + (xch[r + 256] + xch[r + 384]);
-        if (a.ml && part == 0 && qi < nq) {
-            float *mlp = a.ml + ((int64_t)(q0 + qi) * a.H + (int)blockIdx.y) * 2;
-            mlp[0] = any ? mx * sl2 : -INFINITY; mlp[1] = l;
-        }
-        // ---- output row: O / l; the four threads of a row take 16 columns each ----
-        {
-            const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
-            const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
-            uint32_t v[16], vc[16];
-            if (nchunks > 0) {
-                tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
-                tmem_ld16(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
-            }
-            if (live) {
-#pragma unroll
-                for (int j = 0; j < 16; j += 4) {
-                    float4 o4 = make_float4(fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv,
-                                            fmaf(__uint_as_float(vc[j + 1]), H16_LO_UNSCALE, __uint_as_float(v[j + 1])) * inv,
-                                            fmaf(__uint_as_float(vc[j + 2]), H16_LO_UNSCALE, __uint_as_float(v[j + 2])) * inv,
-                                            fmaf(__uint_as_float(vc[j + 3]), H16_LO_UNSCALE, __uint_as_float(v[j + 3])) * inv);
-                    if (nchunks == 0) o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
-                    else *(float4 *)(a.out + ofs + j) = o4;
                 }
             }
         }
@@ -475,20 +509,36 @@ static void attention_tc_launch(const AttnArgs &a, float *out, float *out_lo, in
     d.scale = 1.0f / sqrtf(64.0f);
     d.err = tc_err_flag();
     d.kb_off = kb_off; d.kb_len = kb_len; d.ml = ml;
-    static const int v_mn = getenv("NCM_B200_ATTN_VT") ? 0 : 1;       // A/B: NCM_B200_ATTN_VT=1 keeps the on-chip transpose
-    d.v_mn = v_mn;
     const int G = a.H / a.Hkv;
     d.pack = (!ml && a.max_q <= 32 && G >= 2 && G <= 4) ? 1 : 0;
+    // heads per CTA: all heads of a kv group share one fetch and conversion of its keys and values, as long as
+    // that leaves at least two CTAs per SM; fewer heads per CTA (a divisor of the group) otherwise
+    const char *hpc_s = getenv("NCM_B200_ATTN_HPC");                  // read per call: the tests force each grouping
+    const int hpc_env = hpc_s ? atoi(hpc_s) : 0;
+    d.hpc = 1;
+    if (!d.pack) {
+        const int64_t per_head = (int64_t)cdiv(a.max_q, 128) * a.rows * a.H;
+        for (int c = G; c >= 1; c--)
+            if (G % c == 0 && (c == 1 || per_head / c >= 2 * (int64_t)ctx().sm_count)) { d.hpc = c; break; }
+        if (hpc_env > 0 && G % hpc_env == 0) d.hpc = hpc_env;
+    }
     const CUtensorMap mq = tc_get_map(a.q, a.q_total, a.H * 64, a.ldq, d.pack ? 32 : 128, false);
     const CUtensorMap mk1 = tc_get_map(a.k1, a.k1_total, 2 * a.Hkv * 64, a.ldk1, 32, false);
     const CUtensorMap mk2 = a.k2 ? tc_get_map(a.k2, a.k2_total, 2 * a.Hkv * 64, a.ldk2, 32, false) : mk1;
     static bool set = false;
     if (!set) {
-        CUDA_CHECK(cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+        CUDA_CHECK(cudaFuncSetAttribute(k_attention_tc<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+        CUDA_CHECK(cudaFuncSetAttribute(k_attention_tc<9>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
         set = true;
     }
-    dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H), (unsigned)a.rows);
-    LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc, grid, ATC_BLOCK, ATC_SMEM, mq, mk1, mk2, d);
+    dim3 grid((unsigned)cdiv(a.max_q, 128), (unsigned)(d.pack ? a.Hkv : a.H / d.hpc), (unsigned)a.rows);
+    const int max_n1 = ml ? std::min(kb_len, a.max_k1) : a.max_k1;
+    const int max_keys = ((max_n1 + 31) & ~31) + (a.k2 ? ((a.max_k2 + 31) & ~31) : 0);
+    if (max_keys <= 256) {
+        LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc<8>, grid, ATC_BLOCK, ATC_SMEM, mq, mk1, mk2, d);
+    } else {
+        LAUNCH_PDL_IF(pdl_small((int64_t)grid.x * grid.y * grid.z), k_attention_tc<9>, grid, ATC_BLOCK, ATC_SMEM, mq, mk1, mk2, d);
+    }
 }
 
 void attention_tc(const AttnArgs &a) {

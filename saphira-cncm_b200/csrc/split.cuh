@@ -25,6 +25,13 @@ __device__ __forceinline__ void h16_pair(float v, unsigned short &hi, unsigned s
     hi = f16_sat(v);
     lo = f16_sat((v - __half2float(__ushort_as_half(hi))) * H16_LO_SCALE);
 }
+// two values at once, packed (a in the low half-word): the same roundings as h16_pair, with one conversion
+// instruction per packed result instead of one per value
+__device__ __forceinline__ void h16_pair2(float a, float b, uint32_t &hi, uint32_t &lo, float lo_scale = H16_LO_SCALE) {
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(hi) : "f"(b), "f"(a));
+    const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&hi));
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(lo) : "f"((b - f.y) * lo_scale), "f"((a - f.x) * lo_scale));
+}
 // element index i into both arrays
 __device__ __forceinline__ void store_split1(float *y, float *y_lo, int64_t i, float v, int fmt) {
     if (fmt == SPLIT_H16) {
@@ -39,10 +46,10 @@ __device__ __forceinline__ void store_split1(float *y, float *y_lo, int64_t i, f
 // four consecutive elements, i a multiple of 4 and both rows 16-byte aligned
 __device__ __forceinline__ void store_split4(float *y, float *y_lo, int64_t i, float4 v, int fmt) {
     if (fmt == SPLIT_H16) {
-        unsigned short h0, h1, h2, h3, l0, l1, l2, l3;
-        h16_pair(v.x, h0, l0); h16_pair(v.y, h1, l1); h16_pair(v.z, h2, l2); h16_pair(v.w, h3, l3);
-        *(uint2 *)((unsigned short *)y + i) = make_uint2((uint32_t)h0 | ((uint32_t)h1 << 16), (uint32_t)h2 | ((uint32_t)h3 << 16));
-        *(uint2 *)((unsigned short *)y_lo + i) = make_uint2((uint32_t)l0 | ((uint32_t)l1 << 16), (uint32_t)l2 | ((uint32_t)l3 << 16));
+        uint32_t h0, h1, l0, l1;
+        h16_pair2(v.x, v.y, h0, l0); h16_pair2(v.z, v.w, h1, l1);
+        *(uint2 *)((unsigned short *)y + i) = make_uint2(h0, h1);
+        *(uint2 *)((unsigned short *)y_lo + i) = make_uint2(l0, l1);
     } else {
         float4 h = make_float4(split_tf32_hi(v.x), split_tf32_hi(v.y), split_tf32_hi(v.z), split_tf32_hi(v.w));
         *(float4 *)(y + i) = h;

@@ -133,10 +133,7 @@ __device__ __forceinline__ void tc_epilogue_glu_silu_h16(const TcEpi &ep, const 
         }
         const float o0 = __fmul_rn(__fdividef(g0, 1.0f + __expf(-g0)), u0);
         const float o1 = __fmul_rn(__fdividef(g1, 1.0f + __expf(-g1)), u1);
-        unsigned short h0, l0, h1, l1;
-        h16_pair(o0, h0, l0); h16_pair(o1, h1, l1);
-        p1[j] = (uint32_t)h0 | ((uint32_t)h1 << 16);
-        p2[j] = (uint32_t)l0 | ((uint32_t)l1 << 16);
+        h16_pair2(o0, o1, p1[j], p2[j]);
     }
     const int64_t e0 = m * ep.ldy + ((n0 + c0) >> 1);   // first output element; a multiple of 8 halfs (16 bytes)
     uint4 *d1 = (uint4 *)((unsigned short *)ep.y + e0), *d2 = (uint4 *)((unsigned short *)ep.y_lo + e0);

@@ -53,6 +53,8 @@ CASES = {
     "ragged_prefix_rows": ([256, 70, 131, 1], [256, 70, 131, 1], None, 8, 8, 0, 0),
     "grouped_heads_prefix": ([200, 33], [200, 33], None, 8, 2, 0, 0),
     "causal_prefill": ([200, 64, 288], [200, 64, 288], None, 4, 2, 1, 0),
+    "grouped_heads_c2_prefix_shape": ([256, 1, 256, 1, 190], [256, 1, 256, 1, 190], None, 8, 2, 0, 0),
+    "grouped_heads_16q_4kv": ([256, 100], [256, 100], None, 16, 4, 0, 0),
     "cache_plus_own_tokens": ([32, 17, 24], [250, 3, 77], [32, 17, 24], 4, 4, 0, 0),
     "level_pass_packed_g4": ([32, 17, 1, 4], [250, 3, 77, 256], [32, 17, 1, 4], 8, 2, 0, 0),
     "level_pass_packed_g2": ([16, 5], [40, 100], [16, 5], 4, 2, 0, 0),
@@ -64,9 +66,18 @@ CASES = {
 }
 
 
+@pytest.mark.parametrize("grouping", ["chosen", "kv_group_per_cta"])
 @pytest.mark.parametrize("name", sorted(CASES))
-def test_tensor_core_attention_matches_cuda_core_and_float64(cuda, name):
+def test_tensor_core_attention_matches_cuda_core_and_float64(cuda, name, grouping, monkeypatch):
     qlens, k1lens, k2lens, H, Hkv, causal, window = CASES[name]
+    if grouping == "kv_group_per_cta":
+        # one CTA walks all heads that share a kv head (what large batches get): keys and values are fetched and
+        # converted once, the heads' phases overlap
+        if H == Hkv:
+            pytest.skip("one head per kv head: nothing to group")
+        monkeypatch.setenv("NCM_B200_ATTN_HPC", str(H // Hkv))
+    else:
+        monkeypatch.delenv("NCM_B200_ATTN_HPC", raising=False)
     rng = np.random.default_rng(sum(map(ord, name)))
     off = lambda lens: np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     qs, k1s = off(qlens), off(k1lens)
@@ -85,7 +96,7 @@ def test_tensor_core_attention_matches_cuda_core_and_float64(cuda, name):
                                        len(qlens), H, Hkv, causal, window, engine)
         assert rc == 0, (name, engine, rc)
         got[engine] = cuda.to_host(od, q.shape)
-    # fp32 CUDA-core kernel: ~1e-6; three-pass TF32 drops only the lo*lo term: a few 1e-6
+    # fp32 CUDA-core kernel: ~1e-6; the fp16-pair products drop only the lo*lo term: a few 1e-6
     assert np.abs(got[0] - want).max() < 4e-6
     assert np.abs(got[1] - want).max() < 8e-6
     assert not np.isnan(got[1]).any()
