@@ -1,11 +1,12 @@
 // Tensor-core attention for head dim 64 on sm_100a (tcgen05 + TMEM + TMA).
 //
-// One CTA (16 softmax warps + one MMA warp) per (sequence row, group of heads that share a kv head, 128-query tile).
-// The keys and values of the row (up to 288 padded keys: a 256-token prefix plus a 32-token level) are fetched ONCE
-// by TMA, turned into fp16 pairs in place and stay resident; the CTA then walks its heads ("items") one after the
-// other, so the fetch and the conversion are shared by the heads of the group and the phases of neighbouring items
-// overlap: the score MMAs of item i+1 run under the output phase of item i, the query tile of item i+1 arrives and
-// is converted under the softmax of item i.
+// One CTA (16 softmax warps, one MMA warp, three converter warps) per (sequence row, group of heads that share a kv
+// head, 128-query tile). The keys and values of the row (up to 288 padded keys: a 256-token prefix plus a 32-token
+// level) are fetched ONCE by TMA, turned into fp16 pairs in place and stay resident; the CTA then walks its heads
+// ("items") one after the other, so the fetch and the conversion are shared by the heads of the group and the phases
+// of neighbouring items overlap: the query tile of item i+1 arrives and is converted by the converter warps while
+// the team works on item i, and its score MMAs are issued in four batches between the P V MMAs of item i.
+// The team raises its register allowance (setmaxnreg) with what the other four warps give up.
 //   S = Q K^T   three kind::f16 MMAs per 16 dims over pairs x = x1 + x2 (x1 = rn_f16(x), x2 = rn_f16(x - x1), NOT
 //               scaled: one accumulator takes q2 k1 + q1 k2 + q1 k1; where x2 falls into the fp16 subnormals,
 //               |x| < 1/8, it is exact to 3e-8 absolute, below the dropped q2 k2 term for every |k| that matters)
@@ -31,10 +32,10 @@
 namespace ncmb {
 
 constexpr int ATC_THREADS = 512;          // softmax team: four threads per query row, eight score columns of a chunk each
-constexpr int ATC_BLOCK = ATC_THREADS + 32;  // + one warp whose first lane issues the MMAs
+constexpr int ATC_CONV = 96;              // converter threads: the query tiles' fp32 -> pair conversion, off the team's path
+constexpr int ATC_BLOCK = ATC_THREADS + 32 + ATC_CONV;  // team + one warp whose first lane issues the MMAs + converters: five warpgroups
 constexpr int ATC_MAXK = 288;            // padded keys per row the kernel keeps resident
 constexpr int ATC_OCOL = 288;            // TMEM columns of the output accumulators (main, then cross terms); scores use [0, 288)
-constexpr int ATC_VSLOTS = ATC_MAXK / 32;
 constexpr int ATC_QB = 32768;                                // a 128 x 64 tile as pairs: hi 16 KB | lo 16 KB
 constexpr int ATC_KP = ATC_MAXK * 128;                       // all key rows, one half of the pair (or one raw atom): 36 KB
 constexpr int ATC_SMEM = 1024 + 2 * ATC_QB + 4 * ATC_KP + 2 * ATC_THREADS * 4 + 32 * 8 + 64;
@@ -82,13 +83,15 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t *r) {
 
 // A tile as TMA delivers it -- rows of 64 floats as two 32-float atoms (128-byte swizzle), the atoms `atom` bytes
 // apart -- becomes fp16 pairs IN PLACE: hi rows (64 halves = 128 bytes, same swizzle) where atom 0 was, lo rows where
-// atom 1 was. A unit is eight dims of one row: two float4 in, one 16-byte store per half out. All units are read
-// into registers (atc_units_read) before anyone writes (atc_units_write); the caller puts a team barrier in between.
-template <int NU>
+// atom 1 was. A unit is eight dims of one row: two float4 in, one 16-byte store per half out. The eight units of a
+// row sit in eight neighbouring lanes of one warp and touch that row's two 128-byte lines only, so reading a batch
+// of units into registers (atc_units_read), __syncwarp(), then writing them (atc_units_write) is all the ordering
+// the in-place conversion needs.
+template <int NU, int NT = ATC_THREADS>
 __device__ __forceinline__ void atc_units_read(const unsigned char *base, uint32_t atom, int nrows, int tid, float4 (&x)[NU][2]) {
 #pragma unroll
     for (int i = 0; i < NU; i++) {
-        const int u = tid + i * ATC_THREADS, row = u >> 3, d8 = u & 7;
+        const int u = tid + i * NT, row = u >> 3, d8 = u & 7;
         if (row < nrows) {
             const unsigned char *rp = base + (size_t)(d8 >> 2) * atom + (row >> 3) * 1024 + (row & 7) * 128;
             const int c0 = (d8 & 3) * 2;
@@ -99,12 +102,12 @@ __device__ __forceinline__ void atc_units_read(const unsigned char *base, uint32
 }
 // lo_scale: 1 for the score operands, 2^11 for the values; rows whose index in its segment is past the segment's
 // length (n1 of the first n1p rows, then n2) are written as zeros
-template <int NU>
+template <int NU, int NT = ATC_THREADS>
 __device__ __forceinline__ void atc_units_write(unsigned char *base, uint32_t atom, int nrows, int tid, const float4 (&x)[NU][2],
                                                 float lo_scale, int n1p, int n1, int n2) {
 #pragma unroll
     for (int i = 0; i < NU; i++) {
-        const int u = tid + i * ATC_THREADS, row = u >> 3, d8 = u & 7;
+        const int u = tid + i * NT, row = u >> 3, d8 = u & 7;
         if (row < nrows) {
             const bool valid = row < n1p ? row < n1 : (row - n1p) < n2;
             const float v[8] = {x[i][0].x, x[i][0].y, x[i][0].z, x[i][0].w, x[i][1].x, x[i][1].y, x[i][1].z, x[i][1].w};
@@ -148,10 +151,11 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
     float *xsum = xmax + ATC_THREADS;                            // ... and row sum exchange
     uint64_t *bars = (uint64_t *)(xsum + ATC_THREADS);
     uint32_t *tmem_slot = (uint32_t *)(bars + 32);
-    // barriers: 0,1 query tile landed | 2 keys landed | 3 values landed | 4 Q (and K) pairs ready for the score MMAs |
-    //           5 score MMAs done | 6,7 P half ready | 8,9 PV MMAs of a P half done
+    // barriers: 0,1 query tile landed | 2 keys landed | 3 values landed | 4,5 query pairs of a tile ready | 6 score MMAs
+    //           done | 7,8 P half ready | 9,10 PV MMAs of a P half done | 11 key pairs ready | 12 scores are in registers
     const uint32_t bar_q = smem_u32(bars), bar_k = smem_u32(bars + 2), bar_v = smem_u32(bars + 3), bar_qrdy = smem_u32(bars + 4);
-    const uint32_t bar_s = smem_u32(bars + 5), bar_rdy0 = smem_u32(bars + 6), bar_pv0 = smem_u32(bars + 8);
+    const uint32_t bar_s = smem_u32(bars + 6), bar_rdy0 = smem_u32(bars + 7), bar_pv0 = smem_u32(bars + 9);
+    const uint32_t bar_krdy = smem_u32(bars + 11), bar_sfree = smem_u32(bars + 12);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = blockIdx.z, qt = blockIdx.x;
     const int G = a.H / a.Hkv;
@@ -209,7 +213,8 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
 
     if (tid == 0) {
         mbar_init(bar_q, 1); mbar_init(bar_q + 8, 1); mbar_init(bar_k, 1); mbar_init(bar_v, 1);
-        mbar_init(bar_qrdy, ATC_THREADS / 32);                                   // one arrival per team warp
+        mbar_init(bar_qrdy, ATC_CONV / 32); mbar_init(bar_qrdy + 8, ATC_CONV / 32);   // one arrival per converter warp
+        mbar_init(bar_krdy, ATC_THREADS / 32); mbar_init(bar_sfree, ATC_THREADS / 32);   // one arrival per team warp
         mbar_init(bar_s, 1);
         mbar_init(bar_rdy0, ATC_THREADS / 32); mbar_init(bar_rdy0 + 8, ATC_THREADS / 32);
         mbar_init(bar_pv0, 1); mbar_init(bar_pv0 + 8, 1);
@@ -265,37 +270,56 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         if (lane == 0 && gn > 1) load_q(1);
     }
 
-    // where in an item the next item's query tile is converted and its score MMAs are issued: after the fourth
-    // chunk when there are more (the scores then finish under the rest of the chunk loop), else after the last
-    const bool conv_mid = nchunks > 4;
-    if (warp == ATC_THREADS / 32) {
+    if (warp > ATC_THREADS / 32) {
+        // ================= converter warps: every item's query tile, fp32 -> pairs in place =================
+        const int ct = tid - ATC_THREADS - 32;
+        for (int it = 0; it < gn; it++) {
+            unsigned char *Qn = QB + (it & 1) * ATC_QB;
+            w.wait(bar_q + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, 11);
+            for (int i = 0; i < 12; i += 2) {                             // 1024 units over 96 threads, two at a time
+                float4 xq[2][2];
+                atc_units_read<2, ATC_CONV>(Qn, 16384, 128, ct + i * ATC_CONV, xq);
+                __syncwarp();
+                atc_units_write<2, ATC_CONV>(Qn, 16384, 128, ct + i * ATC_CONV, xq, 1.0f, 128, 128, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_qrdy + 8 * (it & 1));
+        }
+    } else if (warp == ATC_THREADS / 32) {
         // ================= MMA warp =================
         if (lane == 0) {
             const uint32_t idpv = umma_idesc_f16(128, 64) | (1u << 16);       // B (values) MN-major
             const uint32_t dm = tmem + (uint32_t)ATC_OCOL, dc = dm + 64u;
             const uint64_t kh = umma_desc_sw128(smem_u32(KP)), kl = umma_desc_sw128(smem_u32(KP + ATC_KP));
             const uint64_t vh = umma_desc_sw128(smem_u32(VP)), vl = umma_desc_sw128(smem_u32(VP + ATC_KP));
-            auto scores = [&](int it) {
-                w.wait(bar_qrdy, (uint32_t)it & 1u, 12);
-                tc_fence_after();
-                const uint64_t qh = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB)), ql = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB + 16384));
+            // the scores of item `it`, 16 dims (32 bytes along the swizzled rows) at a time: the first batch waits for
+            // the item's query pairs and for the score columns to be free (the team holds the previous item's scores
+            // in registers; for item 0, for the key pairs instead), the last one commits
+            auto score_batch = [&](int it, int k) {
+                if (k == 0) {
+                    w.wait(bar_qrdy + 8 * (it & 1), (uint32_t)(it >> 1) & 1u, 12);
+                    if (it > 0) w.wait(bar_sfree, (uint32_t)(it - 1) & 1u, 18);
+                    else w.wait(bar_krdy, 0, 18);
+                    tc_fence_after();
+                }
+                const uint64_t qh = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB)) + (uint64_t)(k * 2);
+                const uint64_t ql = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB + 16384)) + (uint64_t)(k * 2);
                 for (int r0 = 0; r0 < nkp; r0 += 256) {                   // N <= 256 per MMA: 256 + 32 for a full row
                     const int nrows = (nkp - r0) < 256 ? (nkp - r0) : 256;
                     const uint32_t idesc = umma_idesc_f16(128, nrows);
                     const uint32_t d = tmem + (uint32_t)r0;
-                    const uint64_t ro = (uint64_t)(r0 * 8);               // r0 rows of 128 bytes, in 16-byte units
-#pragma unroll
-                    for (int k = 0; k < 4; k++) {                         // 16 dims per MMA: 32 bytes along the swizzled row
-                        umma_f16(d, ql + (uint64_t)(k * 2), kh + ro + (uint64_t)(k * 2), idesc, k ? 1u : 0u);
-                        umma_f16(d, qh + (uint64_t)(k * 2), kl + ro + (uint64_t)(k * 2), idesc, 1u);
-                        umma_f16(d, qh + (uint64_t)(k * 2), kh + ro + (uint64_t)(k * 2), idesc, 1u);
-                    }
+                    const uint64_t ro = (uint64_t)(r0 * 8 + k * 2);       // r0 rows of 128 bytes, in 16-byte units
+                    umma_f16(d, ql, kh + ro, idesc, k ? 1u : 0u);
+                    umma_f16(d, qh, kl + ro, idesc, 1u);
+                    umma_f16(d, qh, kh + ro, idesc, 1u);
                 }
-                umma_commit(bar_s);
+                if (k == 3) umma_commit(bar_s);
             };
             uint32_t use[2] = {0u, 0u};                                   // hand-overs seen so far per P half
-            scores(0);
+            for (int k = 0; k < 4; k++) score_batch(0, k);
             for (int it = 0; it < gn; it++) {
+                int sb = it + 1 < gn ? 0 : 4;                             // score batches of the next item still to issue
                 const uint64_t p1 = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB)), p2 = umma_desc_sw128(smem_u32(QB + (it & 1) * ATC_QB + 16384));
                 for (int c = 0; c < nchunks; c++) {
                     const int hf = c & 1;
@@ -310,10 +334,11 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                         umma_f16(dc, p2 + po, vh + vo, idpv, 1u);
                     }
                     umma_commit(bar_pv0 + 8 * hf);
-                    // the next item's scores: its query pairs are ready once the team is past chunk 3
-                    if (c == 3 && conv_mid && it + 1 < gn) scores(it + 1);
+                    // a quarter of the next item's scores behind each of chunks 1..4: short enough not to hold up the
+                    // P V chain, early enough to be done when the team comes back for them
+                    if (c >= 1 && sb < 4 && nchunks >= 5) score_batch(it + 1, sb++);
                 }
-                if (!conv_mid && it + 1 < gn) scores(it + 1);
+                while (sb < 4) score_batch(it + 1, sb++);
             }
         }
     } else {
@@ -321,24 +346,19 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
         const int r = tid & 127, part = tid >> 7;                     // query row of the tile, which quarter of each chunk's columns
         const int qi = a.pack ? (r & 31) : qt * 128 + r;             // query index inside the sequence row
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        // ---- prologue: Q of item 0 and the keys -> pairs, then the values ----
+        // ---- prologue: the keys -> pairs, then the values ----
         {
-            float4 xq[2][2];
-            w.wait(bar_q, 0, 11);
-            atc_units_read<2>(QB, 16384, 128, tid, xq);
-            team_sync();
-            atc_units_write<2>(QB, 16384, 128, tid, xq, 1.0f, 128, 128, 0);
             float4 xk[5][2];
             w.wait(bar_k, 0, 12);
             atc_units_read<5>(KP, ATC_KP, nkp, tid, xk);
-            team_sync();
+            __syncwarp();
             atc_units_write<5>(KP, ATC_KP, nkp, tid, xk, 1.0f, nkp, nkp, 0);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_qrdy);
+            if (lane == 0) mbar_arrive(bar_krdy);
             w.wait(bar_v, 0, 14);
             atc_units_read<5>(VP, ATC_KP, nkp, tid, xk);
-            team_sync();
+            __syncwarp();
             atc_units_write<5>(VP, ATC_KP, nkp, tid, xk, H16_LO_SCALE, n1p, n1, n2);
             // made visible to the MMA warp by the fence before the first P hand-over
         }
@@ -369,6 +389,9 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
 #pragma unroll
             for (int c = 0; c < NCH; c++) tmem_ld8_issue(lane_addr + (uint32_t)(c * 32 + part * 8), sv[c]);
             tmem_ld_wait();
+            tc_fence_before();                                            // the score columns may take the next item's scores
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_sfree);
             float mx = -INFINITY;
 #pragma unroll
             for (int c = 0; c < NCH; c++) {
@@ -395,19 +418,6 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             const bool any = mx != -INFINITY;
             // 2^(s sl2 - mx sl2): one multiply-add per score; a row that sees no key keeps its -inf scores as they are
             const float nmx = any ? -mx * sl2 : 0.f;
-            const bool conv = it + 1 < gn;
-            // the next item's query tile (it landed long ago) -> pairs in place, then its score MMAs may go
-            auto convert_next_q = [&]() {
-                float4 xq[2][2];
-                unsigned char *Qn = QB + ((it + 1) & 1) * ATC_QB;
-                w.wait(bar_q + 8 * ((it + 1) & 1), (uint32_t)((it + 1) >> 1) & 1u, 11);
-                atc_units_read<2>(Qn, 16384, 128, tid, xq);
-                team_sync();
-                atc_units_write<2>(Qn, 16384, 128, tid, xq, 1.0f, 128, 128, 0);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_qrdy);
-            };
             float l = 0.f;
 #pragma unroll
             for (int c = 0; c < NCH; c++) {
@@ -436,39 +446,81 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_rdy0 + 8 * hf);
                 if (hf) use1++; else use0++;
-                if (c == 3 && conv_mid && conv) convert_next_q();
             }
-            if (!conv_mid && conv) convert_next_q();
             // the commits complete in order: the last one covers every earlier MMA of the item
             { const int hf = (nchunks - 1) & 1; const uint32_t n = hf ? use1 : use0; w.wait(bar_pv0 + 8 * hf, (n - 1u) & 1u, 16); }
             tc_fence_after();
             xsum[tid] = l;
             team_sync();
             l = (xsum[r] + xsum[r + 128]) + (xsum[r + 256] + xsum[r + 384]);
-            // every thread is past the item's last MMA: its tile takes the query tile of the item after the next
-            if (tid == 0 && it + 2 < gn) load_q(it + 2);
             if (a.ml && part == 0 && qi < nq) {
                 float *mlp = a.ml + ((int64_t)(q0 + qi) * a.H + h) * 2;
                 mlp[0] = any ? mx * sl2 : -INFINITY; mlp[1] = l;
             }
-            // ---- output row: O / l; the four threads of a row take 16 columns each ----
+            // ---- output rows: O / l; the four threads of a row take 16 columns each ----
             {
-                const bool live = qi < nq && h < (kvh + 1) * G && !w.dead;
                 const float inv = l > 0.f ? 1.0f / l : 0.f;
-                const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
-                uint32_t v[16], vc[16];
-                tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
-                tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
-                tmem_ld_wait();
-                if (live) {
+                float o[16];
+                {
+                    uint32_t v[16], vc[16];
+                    tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + part * 16), v);
+                    tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
+                    tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4) {
-                        const float4 o4 = make_float4(fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv,
-                                                      fmaf(__uint_as_float(vc[j + 1]), H16_LO_UNSCALE, __uint_as_float(v[j + 1])) * inv,
-                                                      fmaf(__uint_as_float(vc[j + 2]), H16_LO_UNSCALE, __uint_as_float(v[j + 2])) * inv,
-                                                      fmaf(__uint_as_float(vc[j + 3]), H16_LO_UNSCALE, __uint_as_float(v[j + 3])) * inv);
-                        if (a.out_lo) store_split4(a.out, a.out_lo, ofs + j, o4, a.out_fmt);
-                        else *(float4 *)(a.out + ofs + j) = o4;
+                    for (int j = 0; j < 16; j++) o[j] = fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv;
+                }
+                const bool h16 = a.out_lo && a.out_fmt == SPLIT_H16;
+                if (a.out_lo && !h16) {
+                    // TF32 hi / lo outputs (two fp32 arrays) go straight to global memory, a thread per 64-byte piece
+                    if (tid == 0 && it + 2 < gn) load_q(it + 2);
+                    if (qi < nq && h < (kvh + 1) * G && !w.dead) {
+                        const int64_t ofs = (int64_t)(q0 + qi) * a.ldo + h * 64 + part * 16;
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) store_split4(a.out, a.out_lo, ofs + j, make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]), a.out_fmt);
+                    }
+                } else {
+                    // fp16 pairs or plain fp32: the tile is staged in the item's P tile (every MMA that read it is done)
+                    // and leaves as whole 128-byte lines; a thread writing its own row's piece would put 32 lines
+                    // into every store instruction
+                    unsigned char *St = Pb;
+                    if (h16) {
+#pragma unroll
+                        for (int q = 0; q < 2; q++) {
+                            uint32_t hw[4], lw[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) h16_pair2(o[q * 8 + 2 * e], o[q * 8 + 2 * e + 1], hw[e], lw[e]);
+                            const uint32_t so = rowoff + ((uint32_t)(((2 * part + q) ^ (r & 7)) & 7) << 4);
+                            *(uint4 *)(St + so) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                            *(uint4 *)(St + 16384 + so) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; q++)                           // 256-byte rows, 16-byte pieces swizzled by the row
+                            *(float4 *)(St + r * 256 + ((uint32_t)(((4 * part + q) ^ (r & 15)) & 15) << 4)) = make_float4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+                    }
+                    team_sync();
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int idx = tid + k * ATC_THREADS;                // 2048 16-byte pieces
+                        const int rr = h16 ? (idx >> 3) & 127 : idx >> 4;
+                        const int qi2 = a.pack ? (rr & 31) : qt * 128 + rr, h2 = a.pack ? h0 + (rr >> 5) : h;
+                        if (qi2 < nq && h2 < (kvh + 1) * G) {
+                            const int64_t e0 = (int64_t)(q0 + qi2) * a.ldo + h2 * 64;
+                            if (h16) {
+                                const int tile = idx >> 10, j = idx & 7;
+                                const uint4 x = *(const uint4 *)(St + tile * 16384 + (rr >> 3) * 1024 + (rr & 7) * 128 + (((j ^ (rr & 7)) & 7) << 4));
+                                *(uint4 *)((unsigned short *)(tile ? a.out_lo : a.out) + e0 + j * 8) = x;
+                            } else {
+                                const int j = idx & 15;
+                                *(float4 *)(a.out + e0 + j * 4) = *(const float4 *)(St + rr * 256 + (((j ^ (rr & 15)) & 15) << 4));
+                            }
+                        }
+                    }
+                    team_sync();                                              // the staged tile has left
+                    // the tile now takes the query tile of the item after the next
+                    if (tid == 0 && it + 2 < gn) {
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        load_q(it + 2);
                     }
                 }
             }
@@ -492,7 +544,7 @@ bool attention_tc_supported(const AttnArgs &a) {
     int n1p = (a.max_k1 + 31) & ~31, n2p = (a.max_k2 + 31) & ~31;
     if (n1p + n2p > ATC_MAXK || n1p + n2p == 0) return false;
     if (a.q_total <= 0 || a.k1_total <= 0 || (a.k2 && a.k2_total <= 0)) return false;
-    if ((a.ldq | a.ldk1 | a.ldk2 | a.ldo) & 3) return false;
+    if (((a.ldq | a.ldk1 | a.ldk2) & 3) || (a.ldo & 7)) return false;
     if (a.v1 != a.k1 + a.Hkv * 64 || (a.k2 && a.v2 != a.k2 + a.Hkv * 64)) return false;
     auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     if (!al(a.q) || !al(a.k1) || (a.k2 && !al(a.k2)) || !al(a.out) || (a.out_lo && !al(a.out_lo))) return false;
@@ -586,7 +638,7 @@ bool attention_tc_long_supported(const AttnArgs &a) {
     if (off || a.hd != 64 || a.Hkv <= 0 || a.H % a.Hkv || a.k2 || a.window > 0 || a.max_q < 64) return false;
     if (a.max_k1 <= ATC_MAXK || a.max_k1 > 16 * ATC_KBLOCK) return false;
     if (a.q_total <= 0 || a.k1_total <= 0) return false;
-    if ((a.ldq | a.ldk1 | a.ldo) & 3) return false;
+    if (((a.ldq | a.ldk1) & 3) || (a.ldo & 7)) return false;
     if (a.v1 != a.k1 + a.Hkv * 64) return false;
     auto al = [](const void *p) { return ((uintptr_t)p & 15) == 0; };
     if (!al(a.q) || !al(a.k1) || !al(a.out) || (a.out_lo && !al(a.out_lo))) return false;
