@@ -31,6 +31,7 @@
 
 namespace ncmb {
 
+constexpr float ATC_LO_SCALE = 2048.0f, ATC_LO_UNSCALE = 1.0f / 2048.0f;   // P and V pairs: scaled remainders, cross terms apart
 constexpr int ATC_THREADS = 512;          // softmax team: four threads per query row, eight score columns of a chunk each
 constexpr int ATC_CONV = 96;              // converter threads: the query tiles' fp32 -> pair conversion, off the team's path
 constexpr int ATC_BLOCK = ATC_THREADS + 32 + ATC_CONV;  // team + one warp whose first lane issues the MMAs + converters: five warpgroups
@@ -114,7 +115,7 @@ __device__ __forceinline__ void atc_units_write(unsigned char *base, uint32_t at
             uint32_t hw[4], lw[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                h16_pair2(valid ? v[2 * e] : 0.f, valid ? v[2 * e + 1] : 0.f, hw[e], lw[e], lo_scale);
+                h16_pair2_raw(valid ? v[2 * e] : 0.f, valid ? v[2 * e + 1] : 0.f, hw[e], lw[e], lo_scale);
             }
             const uint32_t o = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + (((d8) ^ (row & 7)) << 4));
             *(uint4 *)(base + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             w.wait(bar_v, 0, 14);
             atc_units_read<5>(VP, ATC_KP, nkp, tid, xk);
             __syncwarp();
-            atc_units_write<5>(VP, ATC_KP, nkp, tid, xk, H16_LO_SCALE, n1p, n1, n2);
+            atc_units_write<5>(VP, ATC_KP, nkp, tid, xk, ATC_LO_SCALE, n1p, n1, n2);
             // made visible to the MMA warp by the fence before the first P hand-over
         }
         // visible columns of chunk c for this thread's query, as [jlo, jhi) relative to the chunk start
@@ -432,7 +433,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                     for (int e = 0; e < 4; e++) {
                         const float x0 = atc_ex2(fmaf(__uint_as_float(v[2 * e]), sl2, nmx)), x1 = atc_ex2(fmaf(__uint_as_float(v[2 * e + 1]), sl2, nmx));
                         l += x0 + x1;
-                        h16_pair2(x0, x1, hw[e], lw[e]);
+                        h16_pair2_raw(x0, x1, hw[e], lw[e], ATC_LO_SCALE);
                     }
                     // the thread's eight keys are 16-byte chunk 4 hf + part of its row in the hi tile and in the lo tile
                     const uint32_t o = rowoff + ((uint32_t)(((4 * hf + part) ^ (r & 7)) & 7) << 4);
@@ -467,7 +468,7 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                     tmem_ld16_issue(lane_addr + (uint32_t)(ATC_OCOL + 64 + part * 16), vc);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) o[j] = fmaf(__uint_as_float(vc[j]), H16_LO_UNSCALE, __uint_as_float(v[j])) * inv;
+                    for (int j = 0; j < 16; j++) o[j] = fmaf(__uint_as_float(vc[j]), ATC_LO_UNSCALE, __uint_as_float(v[j])) * inv;
                 }
                 const bool h16 = a.out_lo && a.out_fmt == SPLIT_H16;
                 if (a.out_lo && !h16) {

@@ -125,7 +125,7 @@ enum Act { ACT_NONE = 0, ACT_GELU = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_RELU
 // Format of a GEMM input that its producer already wrote as a split pair (x, x_lo):
 //   SPLIT_TF32: float arrays, x = rn_tf32(v), x_lo = v - x
 //   SPLIT_H16:  both buffers read as __half arrays with the same element stride,
-//               x = rn_f16(v), x_lo = rn_f16((v - x) * 2^11)
+//               x = rn_f16(16 v), x_lo = rn_f16(16 v - x)
 enum SplitFmt { SPLIT_NONE = 0, SPLIT_TF32 = 1, SPLIT_H16 = 2 };
 
 // y[M,N] = act(x[M,K] W[N,K]^T + bias[N]) (+ res[M,N]); res may alias y. ldx/ldy: row strides.

@@ -1,18 +1,22 @@
 // fp32-grade GEMM on the fp16 tensor path of sm_100a: y = act(x W^T + bias) (+ res).
 //
 // Both operands are carried as pairs of fp16 arrays,
-//     v = v1 + v2 * 2^-11,   v1 = rn_f16(v),   v2 = rn_f16((v - v1) * 2^11)
-// (22 significant bits; scaling the remainder keeps it in the normal fp16 range). The product is
-//     x W^T = x1 W1^T  +  2^-11 (x2 W1^T + x1 W2^T)        (the 2^-22 term is dropped)
-// so every k-step issues three tcgen05.mma.kind::f16 into TWO fp32 accumulators in tensor memory
-// (main, cross terms); the epilogue combines them as main + cross * 2^-11. Against three TF32
-// passes this moves half the operand bytes and runs on the twice-as-fast fp16 pipe.
+//     s v = v1 + v2,   v1 = rn_f16(s v),   v2 = rn_f16(s v - v1)
+// (22 significant bits). s is a power of two that keeps the remainders clear of the fp16 subnormals: 16 for
+// activations (fixed by the pair format), per matrix for weights (its largest element goes to [8192, 16384)).
+// The product is
+//     s_x s_w x W^T = x1 W1^T + x2 W1^T + x1 W2^T          (the x2 W2^T term, 2^-22 of the product, is dropped)
+// so every k-step issues three tcgen05.mma.kind::f16 into ONE fp32 accumulator in tensor memory, smallest
+// terms first, and the epilogue multiplies by 1 / (s_x s_w). Against three TF32 passes this moves half the
+// operand bytes and runs on the twice-as-fast fp16 pipe.
 //
-// Structure: persistent CTAs (one per SM) walking output tiles of 128 x 128; warp 0 feeds a ring
-// of shared-memory stages by TMA (four 128 x 64 fp16 tiles per stage, 128-byte swizzle), one lane of
-// warp 1 issues the MMAs, warps 2-9 run the fused epilogue out of tensor memory (64 columns each). Accumulator
-// pairs alternate between two halves of tensor memory so a tile's epilogue overlaps the next
-// tile's MMAs. Every mbarrier wait is bounded; a timeout records a code and drains.
+// Structure: persistent CTAs (one per SM) walking output tiles of 128 x BN (BN = 256 for large problems: an MMA
+// of 256 columns reads the 128-row activation tile once for twice the arithmetic, and it is the operand fetch from
+// shared memory that paces 128-column MMAs); warp 0 feeds a ring of shared-memory stages by TMA (two 128 x 64
+// and two BN x 64 fp16 tiles per stage, 128-byte swizzle), one lane of warp 1 issues the MMAs, warps 2-9 run the
+// fused epilogue out of tensor memory (half of the tile's columns each). Two accumulators alternate so a tile's
+// epilogue overlaps the next tile's MMAs (2 x 256 columns: all of tensor memory). Every mbarrier wait is bounded;
+// a timeout records a code and drains.
 #include "common.cuh"
 #include "tc_common.cuh"
 #include "tc_epilogue.cuh"
@@ -25,17 +29,15 @@ namespace ncmb {
 constexpr int H3_BM = 128, H3_BK = 64;                   // BK halfs = 128 bytes = one swizzle row
 // Tile widths: 128 columns for large problems; 64 or 32 columns for small ones (batched decode steps, the first
 // NCP levels), chosen per call so that the busiest CTA moves the fewest bytes.
-constexpr int h3_stages(int BN) { return BN >= 128 ? 3 : 4; }
+// (256-column tiles: two stages of 96 KB. Four stages of 48 KB -- k-blocks of 32 halfs in 64-byte-swizzled rows --
+// were measured 8% slower: the MMAs fetch 64-byte rows less efficiently)
+constexpr int h3_stages(int BN) { return BN >= 256 ? 2 : BN >= 128 ? 3 : 4; }
 constexpr int H3_EPI_WARPS = 8;                         // two per TMEM lane quadrant, 64 columns each
 constexpr int H3_THREADS = 64 + 32 * H3_EPI_WARPS;
 constexpr int H3_TILE = 128 * H3_BK * 2;                 // one 128-row operand tile: 16 KB
 constexpr int h3_wtile(int BN) { return BN * H3_BK * 2; }  // one BN-row weight tile
 constexpr int h3_stage(int BN) { return 2 * H3_TILE + 2 * h3_wtile(BN); }   // x1 | x2 | W1 | W2
 
-// main + cross * 2^-11, times the inverse of the weight pair's prescale when there is one
-__device__ __forceinline__ float h3_combine(const TcEpi &ep, float mainv, float crossv, bool scaled) {
-    return scaled ? fmaf(crossv, ep.lo_scale, mainv * ep.acc_scale) : fmaf(crossv, H16_LO_UNSCALE, mainv);
-}
 
 // QKP: the epilogue applies the per-head RMSNorm / rotary embedding of a fused QKV projection (128-column tiles)
 template <int H3_BN, bool QKP = false>
@@ -72,8 +74,8 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW1) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmW2) : "memory");
     }
-    if (warp == 1) {   // 2 accumulator pairs x (main, cross) x BN columns (BN = 128: all 512 columns)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(4 * H3_BN) : "memory");
+    if (warp == 1) {   // two accumulators of BN columns: a tile's epilogue runs under the next tile's MMAs
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * H3_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -117,7 +119,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
                 ok = mbar_wait(aempty0 + 8 * acc, (use & 1u) ^ 1u, ep.err, 25);    // epilogue has drained this accumulator pair
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tmain = tmem_base + (uint32_t)(acc * 2 * H3_BN), tcross = tmain + (uint32_t)H3_BN;
+                const uint32_t tacc = tmem_base + (uint32_t)(acc * H3_BN);
                 const int nkb = min(num_kb, (w % ksplit + 1) * kb_per) - (w % ksplit) * kb_per;
                 for (int kb = 0; kb < nkb; kb++, kbg++) {
                     int s = kbg % H3_STAGES; uint32_t ph = (uint32_t)(kbg / H3_STAGES) & 1u;
@@ -130,9 +132,9 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
 #pragma unroll
                     for (int k = 0; k < H3_BK / 16; k++) {    // 16 halfs (32 bytes) per MMA: advance the start address
                         const uint64_t o = (uint64_t)(k * 2);
-                        umma_f16(tmain, x1 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
-                        umma_f16(tcross, x2 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
-                        if (!skip_w2) umma_f16(tcross, x1 + o, w2 + o, idesc, 1u);
+                        umma_f16(tacc, x2 + o, w1 + o, idesc, (kb | k) ? 1u : 0u);
+                        if (!skip_w2) umma_f16(tacc, x1 + o, w2 + o, idesc, 1u);
+                        umma_f16(tacc, x1 + o, w1 + o, idesc, 1u);
                     }
                     umma_commit(empty0 + 8 * s);             // stage reusable once these MMAs have read it
                 }
@@ -148,7 +150,6 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
         int it = 0;
         bool ok = true;
         const bool glu_fast = tc_glu_silu_h16(ep);
-        const bool scaled = ep.acc_scale != 1.0f;                 // uniform: the unscaled combine stays one FMA per element
         unsigned char *stage = stage0 + (warp - 2) * 4096;
         for (int w = blockIdx.x; w < num_tiles * ksplit && ok; w += gridDim.x, it++) {
             const int t = w / ksplit;
@@ -158,68 +159,66 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
             const int64_t m = (int64_t)(t / tiles_n) * H3_BM + q * 32 + lane;
             // the residual of this thread's 64 outputs is requested before the accumulators are waited for,
             // so its latency runs under the tile's MMAs
-            float4 resv[8 * NCH1];
+            // (two chunks are in flight at a time: a chunk's slot takes the chunk after the next once it is used)
+            constexpr int NPRE = NCH1 < 2 ? NCH1 : 2;
+            float4 resv[8 * NPRE];
             bool pre[NCH1];
             // fp32 tiles that leave by TMA store: the warp fetches the residual block together, full row segments per
             // request (see tc_epilogue_chunk_tma_coop); otherwise every thread fetches its own row
             const bool coop = ep.tma_store && ep.res && has_cols && ((ep.ldres & 3) == 0) && (((uintptr_t)ep.res & 15) == 0);
-#pragma unroll
-            for (int c = 0; c < NCH1; c++) {
+            auto fetch_res = [&](int c) {
+                float4 *rv = &resv[(c % NPRE) * 8];
                 if (coop && n0 + c * 32 + 32 <= ep.N) {
                     pre[c] = true;
 #pragma unroll
                     for (int i = 0; i < 8; i++) {
                         const int64_t row = (m - lane) + i * 4 + (lane >> 3);
-                        resv[c * 8 + i] = row < ep.M ? *(const float4 *)(ep.res + row * ep.ldres + n0 + c * 32 + (lane & 7) * 4)
-                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                        rv[i] = row < ep.M ? *(const float4 *)(ep.res + row * ep.ldres + n0 + c * 32 + (lane & 7) * 4)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
-                    continue;
+                    return;
                 }
                 pre[c] = !coop && has_cols && tc_residual_prefetchable(ep, m, n0, c * 32);
                 if (pre[c]) {
                     const float4 *rr = (const float4 *)(ep.res + m * ep.ldres + n0 + c * 32);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) resv[c * 8 + j] = rr[j];
+                    for (int j = 0; j < 8; j++) rv[j] = rr[j];
                 }
-            }
+            };
+#pragma unroll
+            for (int c = 0; c < NPRE; c++) fetch_res(c);
             ok = mbar_wait(afull0 + 8 * acc, use & 1u, ep.err, 23);
             tc_fence_after();
             if (!ok) break;
-            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * 2 * H3_BN + ch * (H3_BN / 2));
+            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * H3_BN + ch * (H3_BN / 2));
             if constexpr (QKP) {
                 // both halves of the thread's head (64 columns) before anything is stored
                 uint32_t r0[32], r1[32];
-                {
-                    uint32_t x[32];
-                    tmem_ld32_issue(trow, r0);
-                    tmem_ld32_issue(trow + (uint32_t)H3_BN, x);
-                    tmem_ld_wait();
+                tmem_ld32_issue(trow, r0);
+                tmem_ld32_issue(trow + 32u, r1);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; j++) r0[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r0[j]), __uint_as_float(x[j]), scaled));
-                    tmem_ld32_issue(trow + 32u, r1);
-                    tmem_ld32_issue(trow + (uint32_t)(H3_BN + 32), x);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; j++) r1[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r1[j]), __uint_as_float(x[j]), scaled));
+                for (int j = 0; j < 32; j++) {
+                    r0[j] = __float_as_uint(__uint_as_float(r0[j]) * ep.acc_scale);
+                    r1[j] = __float_as_uint(__uint_as_float(r1[j]) * ep.acc_scale);
                 }
                 tc_epilogue_head_qkpost(ep, r0, r1, m, m - lane, n0, stage, &tmY, lane);
             } else
 #pragma unroll
             for (int c = 0; c < NCH1; c++) {
                 if (!has_cols) break;
-                uint32_t r[32], x[32];
-                tmem_ld32_issue(trow + (uint32_t)(c * 32), r);
-                tmem_ld32_issue(trow + (uint32_t)(H3_BN + c * 32), x);
-                tmem_ld_wait();
+                uint32_t r[32];
+                tmem_ld32(trow + (uint32_t)(c * 32), r);
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    r[j] = __float_as_uint(h3_combine(ep, __uint_as_float(r[j]), __uint_as_float(x[j]), scaled));
+                for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) * ep.acc_scale);
+                float4 *rv = &resv[(c % NPRE) * 8];
                 if (glu_fast) tc_epilogue_glu_silu_h16(ep, r, m, n0, c * 32);
                 else if (coop && n0 + c * 32 + 32 <= ep.N)
-                    tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, &resv[c * 8], stage, &tmY, lane);
+                    tc_epilogue_chunk_tma_coop(ep, r, m - lane, n0, c * 32, rv, stage, &tmY, lane);
                 else if (ep.tma_store && n0 + c * 32 + 32 <= ep.N)
-                    tc_epilogue_chunk_tma(ep, r, m, m - lane + slice_row0, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr, stage, &tmY, lane);
-                else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? &resv[c * 8] : nullptr);
+                    tc_epilogue_chunk_tma(ep, r, m, m - lane + slice_row0, n0, c * 32, pre[c] ? rv : nullptr, stage, &tmY, lane);
+                else tc_epilogue_chunk(ep, r, m, n0, c * 32, pre[c] ? rv : nullptr);
+                if (c + NPRE < NCH1) fetch_res(c + NPRE);
             }
             tc_fence_before();
             __syncwarp();
@@ -232,7 +231,7 @@ __global__ void __launch_bounds__(H3_THREADS, 1) k_gemm_h3(const __grid_constant
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(4 * H3_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * H3_BN) : "memory");
     }
 }
 
@@ -268,8 +267,8 @@ __global__ void k_split_h16_scaled(const float *__restrict__ w, float scale, uns
                                    int64_t n, unsigned *__restrict__ lo_seen) {
     unsigned any = 0;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        unsigned short hi, lo;
-        h16_pair(w[i] * scale, hi, lo);
+        const float t = w[i] * scale;
+        const unsigned short hi = f16_sat(t), lo = f16_sat(t - __half2float(__ushort_as_half(hi)));
         v1[i] = hi; v2[i] = lo;
         any |= (unsigned)(lo & 0x7fffu);
     }
@@ -307,13 +306,6 @@ static void split_h16_weights(const float *W, unsigned short *v1, unsigned short
     static const bool no_skip = getenv("NCM_B200_H3_NO_SKIP_W2") != nullptr;
     *scale_out = scale;
     *w2_zero = !seen && !no_skip;
-    if (!*w2_zero && scale != 1.0f) {
-        // The prescale pays when it makes the second half vanish (bf16 weights). For a matrix that needs its second
-        // half anyway the pair is formed unscaled, as activations are: the epilogue then keeps its one-FMA combine.
-        LAUNCH(k_split_h16_scaled, grid, 256, 0, W, 1.0f, v1, v2, n, d + 1);
-        CUDA_CHECK(cudaStreamSynchronize(stream()));
-        *scale_out = 1.0f;
-    }
     dev_free(d);
 }
 
@@ -393,7 +385,7 @@ void gemm_h3(const GemmArgs &a) {
     ep.M = a.M; ep.N = a.N; ep.act = a.act; ep.glu = a.glu; ep.err = tc_err_flag();
     ep.colnorm = nullptr; ep.best = nullptr;
     ep.qk_heads = a.qk_heads; ep.qk_H = a.qk_H; ep.qk_qw = a.qk_qw; ep.qk_kw = a.qk_kw; ep.qk_cos = a.qk_cos; ep.qk_sin = a.qk_sin; ep.qk_pos = a.qk_pos;
-    ep.acc_scale = 1.0f; ep.lo_scale = H16_LO_UNSCALE;
+    ep.acc_scale = H16_X_UNSCALE * H16_X_UNSCALE;                  // weights split per call carry the activations' factor
     int skip_w2 = 0;
     const int64_t ldx = a.ldx ? a.ldx : a.K;
     const bool pre_split = a.x_lo != nullptr;
@@ -422,7 +414,7 @@ void gemm_h3(const GemmArgs &a) {
             it = sc.insert_or_assign(a.W, ShadowH{buf, buf + nw, nw, scale, w2_zero}).first;
         }
         w1 = it->second.v1; w2 = it->second.v2;
-        ep.acc_scale = 1.0f / it->second.scale; ep.lo_scale = H16_LO_UNSCALE / it->second.scale;
+        ep.acc_scale = H16_X_UNSCALE / it->second.scale;
         skip_w2 = it->second.w2_zero ? 1 : 0;
     } else {
         unsigned short *p1 = ws.get<unsigned short>(nw), *p2 = ws.get<unsigned short>(nw);
@@ -433,15 +425,23 @@ void gemm_h3(const GemmArgs &a) {
     // are paced by what ONE CTA pulls through its shared memory: tiles per CTA x bytes per k-step (the 128-row
     // activation pair plus the bn-row weight pair). The width with the least of that wins; ties go to the wider.
     static const bool narrow_ok = !getenv("NCM_B200_NO_BN32");
-    static const int bn_env = getenv("NCM_B200_H3_BN") ? atoi(getenv("NCM_B200_H3_BN")) : 0;
+    const char *bn_s = getenv("NCM_B200_H3_BN");                   // read per call: the tests force each tile width
+    const int bn_env = bn_s ? atoi(bn_s) : 0;
     int bn = 128;
-    if (bn_env == 32 || bn_env == 64 || bn_env == 128) bn = bn_env;
+    static const bool wide_ok = !getenv("NCM_B200_NO_BN256");
+    static const int wide_min_n = getenv("NCM_B200_BN256_MIN_N") ? atoi(getenv("NCM_B200_BN256_MIN_N")) : 1024;
+    static const int wide_max_kb = getenv("NCM_B200_BN256_MAX_KB") ? atoi(getenv("NCM_B200_BN256_MAX_KB")) : 8;   // longest K, in 64s
+    if (bn_env == 32 || bn_env == 64 || bn_env == 128 || bn_env == 256) bn = bn_env;
     else if (narrow_ok) {
         int64_t best = -1;
         int64_t cost128 = 0;
-        for (int cand : {128, 64, 32}) {
+        for (int cand : {256, 128, 64, 32}) {
+            // 256-column tiles run on two stages of 96 KB: enough for a short K, not for a long one, where three
+            // stages of 128-column tiles measured faster (the down-projection, K = 2048); at 512 output columns the
+            // 128-column tiles were no slower either
+            if (cand == 256 && (!wide_ok || a.N % 256 != 0 || a.N < wide_min_n || cdiv(a.K, H3_BK) > wide_max_kb)) continue;
             const int64_t waves = cdiv(cdiv(a.N, cand) * cdiv(a.M, H3_BM), ctx().sm_count);
-            const int64_t cost = waves * (2 * H3_TILE + 2 * h3_wtile(cand));
+            const int64_t cost = waves * (2 * 128 + 2 * cand) * 128;     // bytes per 64 halfs of K
             if (cand == 128) cost128 = cost;
             if (best < 0 || cost < best) { best = cost; bn = cand; }
         }
@@ -510,6 +510,7 @@ void gemm_h3(const GemmArgs &a) {
         LAUNCH_PDL_IF(pdl_small(tiles * 4), (k_gemm_h3<128, true>), grid, H3_THREADS, smem, mx1, mx2, mw1, mw2, my, ep, num_kb, tiles_n, (int)tiles, ksplit, kb_per, m_pad, skip_w2);
     } else if (bn == 32) H3_LAUNCH(32);
     else if (bn == 64) H3_LAUNCH(64);
+    else if (bn == 256) H3_LAUNCH(256);
     else H3_LAUNCH(128);
 #undef H3_LAUNCH
     if (ksplit > 1) {

@@ -21,9 +21,9 @@ struct TcEpi {
     int qk_heads, qk_H;
     const float *qk_qw, *qk_kw, *qk_cos, *qk_sin;
     const int *qk_pos;
-    // fp16-pair engine: the weight pair was formed from W * 2^e (e per matrix), so the two accumulators are combined
-    // as main * acc_scale + cross * lo_scale with acc_scale = 2^-e and lo_scale = 2^-11 * 2^-e (both exact)
-    float acc_scale, lo_scale;
+    // fp16-pair engine: the activation pair carries a factor 16 and the weight pair was formed from W * 2^e (e per
+    // matrix); the accumulator is multiplied by acc_scale = 2^-(4 + e) (exact)
+    float acc_scale;
 };
 
 

@@ -25,6 +25,11 @@ pytestmark = pytest.mark.gpu
 
 ATOL_LOGITS = 1e-3
 NEAR_TIE = 1e-5
+# sampled ids: the nucleus walk goes down the sorted probabilities until the running sum passes the draw, so which
+# of two neighbours of that order it stops at moves with the logits' last bits; over 151 936 near-uniform
+# probabilities neighbours are ~1e-5 apart in logit. A differing id is accepted only if the oracle's logits of the
+# two ids are closer than this (a tenth of the logits tolerance), and is counted.
+NEAR_TIE_SAMPLED = 1e-4
 
 
 @pytest.fixture(scope="module")
@@ -184,6 +189,24 @@ def _greedy_ids_or_near_tie(om, prompt, got, tag):
     return ties
 
 
+def _sampled_ids_or_near_tie(om, prompt, got, temp, top_k, top_p, seed, tag):
+    """got: ids the library sampled after `prompt` with the reference's generator (one draw per id). Walks the oracle
+    step by step on the library's own ids and the same draws; a step where they part is accepted only between two
+    ids whose oracle logits are within NEAR_TIE_SAMPLED."""
+    import orc
+    ids = list(map(int, prompt))
+    state, ties = seed, 0
+    for i, g in enumerate(got):
+        lg = om.logits(np.array(ids, np.int32), last_only=True)
+        w, state = orc.sample_topkp(lg.copy(), temp, top_k, top_p, state)
+        if g != w:
+            gap = abs(float(lg[g]) - float(lg[w]))
+            assert gap <= NEAR_TIE_SAMPLED, f"{tag}: id {i} is {g}, oracle {w}, their logits {gap:.2e} apart"
+            ties += 1
+        ids.append(int(g))
+    return ties
+
+
 def test_gpt2_124m_shape_logits_and_greedy_ids(cuda, tmp):
     import orc
     import synth
@@ -239,9 +262,9 @@ def test_qwen2_05b_shape_bf16_weights_logits_greedy_and_sampled_ids(cuda, tmp):
     n_s = 2
     outs = np.zeros((1, n_s), np.int32)
     cuda.ncmb_lm_generate(m, pr.ctypes.data, 1, P, n_s, 0.7, 0, 0.95, 9, -1, outs.ctypes.data)
-    want = om.generate(pr, n_s, temp=0.7, top_k=0, top_p=0.95, seed=9)
     assert cuda.ncmb_gemm_tc_check() == 0
-    assert (outs[0] == want).all(), (outs[0], want)
+    ties = _sampled_ids_or_near_tie(om, pr, outs[0], 0.7, 0, 0.95, 9, "qwen sampled")
+    print(f"qwen2 0.5B shape: {n_s} sampled ids, {ties} near-ties")
     cuda.ncmb_lm_close(m)
     try:
         os.remove(w)                                       # 2 GB of weights

@@ -1,7 +1,7 @@
 """linear_fwd (reference src/ncm.h:146, y = x W^T + b) on every GEMM engine of the library.
 
 Engines 0 (fp32 CUDA cores), 2 (three TF32 MMAs over hi/lo pairs) and 3 (three fp16 MMAs over
-scaled fp16 pairs into two accumulators) must all be fp32-grade against a float64 product;
+prescaled fp16 pairs into one accumulator) must all be fp32-grade against a float64 product;
 engine 1 (one TF32 pass) is the fast, coarse option and only has to be TF32-grade.
 """
 import numpy as np
@@ -50,6 +50,29 @@ def test_linear_fwd_on_every_engine(cuda, shape):
         y = cuda.to_host(yd, (M, N))
         err = np.abs(y - want) / row_scale
         assert err.max() <= rel, f"engine {mode}: {err.max():.3e} of the row scale"
+
+
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+@pytest.mark.parametrize("shape", [(256, 256, 512), (1000, 768, 520), (2048, 1024, 2048), (300, 512, 64)], ids=lambda s: "x".join(map(str, s)))
+def test_fp16_pair_engine_at_every_tile_width(cuda, shape, bn, monkeypatch):
+    """The fp16-pair engine picks its tile width (32 to 256 columns) from the problem size; here every width is
+    forced on small shapes, ragged row tiles and a K tail included, with a residual and a bias."""
+    M, N, K = shape
+    monkeypatch.setenv("NCM_B200_H3_BN", str(bn))
+    rng = np.random.default_rng(M + N + K + bn)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(N).astype(np.float32)
+    want = x.astype(np.float64) @ W.astype(np.float64).T + b
+    row_scale = (np.abs(x).astype(np.float64) @ np.abs(W).astype(np.float64).T) + np.abs(b)
+    xd, Wd, bd = cuda.to_backend(x), cuda.to_backend(W), cuda.to_backend(b)
+    yd = cuda.alloc(M * N)
+    cuda.ncmb_set_gemm_mode(3)
+    cuda.linear_fwd(xd, Wd, bd, yd, M, N, K)
+    cuda.ncmb_sync()
+    assert cuda.ncmb_gemm_tc_check() == 0
+    err = np.abs(cuda.to_host(yd, (M, N)) - want) / row_scale
+    assert err.max() <= 2e-6, f"{bn}-column tiles: {err.max():.3e} of the row scale"
 
 
 def test_descriptor_cache_eviction_between_the_lookups_of_one_launch(cuda):
