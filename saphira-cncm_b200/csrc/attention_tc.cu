@@ -424,8 +424,6 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
             for (int c = 0; c < NCH; c++) {
                 if (c >= nchunks) break;
                 const int hf = c & 1;
-                // the MMAs of the previous hand-over of this half are done with it
-                { const uint32_t n = hf ? use1 : use0; if (n >= 1u) w.wait(bar_pv0 + 8 * hf, (n - 1u) & 1u, 15); }
                 {
                     const uint32_t *v = sv[c];
                     uint32_t hw[4], lw[4];                                 // eight probabilities as packed fp16 pairs
@@ -435,6 +433,9 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                         l += x0 + x1;
                         h16_pair2_raw(x0, x1, hw[e], lw[e], ATC_LO_SCALE);
                     }
+                    // the probabilities are ready in registers; only the stores need the half free: the MMAs of its
+                    // previous hand-over are done with it
+                    { const uint32_t n = hf ? use1 : use0; if (n >= 1u) w.wait(bar_pv0 + 8 * hf, (n - 1u) & 1u, 15); }
                     // the thread's eight keys are 16-byte chunk 4 hf + part of its row in the hi tile and in the lo tile
                     const uint32_t o = rowoff + ((uint32_t)(((4 * hf + part) ^ (r & 7)) & 7) << 4);
                     *(uint4 *)(Pb + o) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
