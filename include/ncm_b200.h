@@ -270,8 +270,9 @@ void *ncmb_get_stream(void);
 void  ncmb_sync(void);
 /* GEMM engine: 0 = fp32 CUDA cores, 1 = tcgen05 TF32 single pass,
  * 2 = tcgen05 3xTF32 (fp32-grade), 3 = tcgen05 fp16 pairs: every operand is carried as
- * v1 + v2 * 2^-11 in fp16 and the product takes three fp16 MMAs into two fp32
- * accumulators (fp32-grade, twice the MMA rate of 2). Default from NCM_B200_GEMM, else 3. */
+ * v1 + v2 in fp16 behind a power-of-two factor and the product takes three fp16 MMAs into
+ * one fp32 accumulator (fp32-grade, twice the MMA rate of 2; activations beyond +-4094
+ * saturate). Default from NCM_B200_GEMM, else 3. */
 void  ncmb_set_gemm_mode(int mode);
 int   ncmb_get_gemm_mode(void);
 /* The tensor-core kernels bound every barrier wait; when one runs out they record a

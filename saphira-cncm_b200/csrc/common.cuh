@@ -183,7 +183,7 @@ bool gemv_fusable(const GemmArgs &a);    // true when the call will run on the G
 bool gemv_warp_takes(const GemmArgs &a); // ... on the warp-per-row-pair GEMV, which also takes the gv_* epilogues (M <= 4)
 bool gemm_tc_supported(const GemmArgs &a);
 void gemm_tc(const GemmArgs &a);
-// gemm mode 3: fp16 split pairs, three kind::f16 MMAs per k-step into two accumulators (gemm_h3.cu)
+// gemm mode 3: fp16 split pairs, three kind::f16 MMAs per k-step into one accumulator (gemm_h3.cu)
 bool gemm_h3_supported(const GemmArgs &a);
 void gemm_h3(const GemmArgs &a);
 void gemm_h3_forget_weights();
