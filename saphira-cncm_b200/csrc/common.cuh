@@ -146,6 +146,10 @@ struct GemmArgs {
     const float *x_lo = nullptr;
     float *y_lo = nullptr;
     int x_fmt = SPLIT_TF32, y_fmt = SPLIT_TF32;   // formats of (x, x_lo) and (y, y_lo) when the lo pointer is set
+    // few-row (decode) calls only: bytes the NEXT weight-streaming kernel of the step will read; the GEMV asks L2 for
+    // them while it runs (a 2 - 20 MB matrix is about one memory latency's worth of bandwidth, so a chain of such
+    // kernels is paced by latency unless each one's weights are on their way before it starts)
+    const void *pf_next = nullptr; size_t pf_next_bytes = 0;
     // few-row (decode) calls only, honoured by the GEMV kernel (see gemv_fusable()):
     //  * the input rows are normalised on the fly: x <- norm(x) * ln_w (+ ln_b), ln_kind 1 LayerNorm, 2 RMSNorm
     //  * output columns >= y2_col0 are also written to y2[m*ldy2 + (*y2_step_d)*y2_step + (n - y2_col0)]
@@ -301,6 +305,9 @@ struct BlockWeights {
     const float *pw = nullptr, *pb = nullptr;          // [C][Hh]
     // exact bf16 copies of the four matrices (decode steps stream these), or null
     const unsigned short *qkvw16 = nullptr, *ow16 = nullptr, *fcw16 = nullptr, *pw16 = nullptr;
+    // decode steps: the matrix the step's next weight-streaming kernel will read after this block's last one (the
+    // next block's QKV matrix, or the start of the vocabulary projection), for that kernel's L2 prefetch
+    const void *next_w = nullptr; size_t next_w_bytes = 0;
     int Hh = 0, gated = 0, act = ACT_GELU;
 };
 struct BlockBufs { float *ln, *qkv, *ctx, *mlp, *h; };   // [n][C], [n][C+2kvd], [n][C], [n][Hh or 2Hh], [n][Hh]

@@ -391,7 +391,21 @@ struct GemvW {
     int pair_half;
     const float *rope_cos, *rope_sin; const int *rope_pos, *rope_step_d; int64_t rope_pos_step; int rope_cols, hd;
     int ngroups;
+    const char *pf; unsigned long long pf_bytes;      // the next kernel's weights, for L2 (null: none)
 };
+
+// Each CTA asks L2 for its slice of the NEXT kernel's weight matrix (bulk prefetch, 16-byte granules, up to 32 KB per
+// instruction): a hint with no completion to wait for.
+__device__ __forceinline__ void gw_prefetch_next(const GemvW &p) {
+    if (!p.pf || threadIdx.x != 0) return;
+    const unsigned long long share = ((p.pf_bytes + gridDim.x - 1) / gridDim.x + 15ull) & ~15ull;
+    unsigned long long off = (unsigned long long)blockIdx.x * share;
+    const unsigned long long end = off + share < p.pf_bytes ? off + share : (p.pf_bytes & ~15ull);
+    for (; off < end; off += 32768ull) {
+        const unsigned n = (unsigned)(end - off < 32768ull ? end - off : 32768ull);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.pf + off), "r"(n) : "memory");
+    }
+}
 
 constexpr int GW_U = 4;                      // chunks of 256 elements whose loads are in flight together
 
@@ -486,6 +500,7 @@ __global__ void __launch_bounds__(256) k_gemv_ksplit(GemvW p) {
     GwTile<W16> t0, t1;
     gw_load<W16>(p, r0, warp, lane, t0, 8);
     gw_load<W16>(p, min(r1, p.N - 1), warp, lane, t1, 8);
+    gw_prefetch_next(p);
     pdl_wait();
     float acc0[MT], acc1[MT];
 #pragma unroll
@@ -546,6 +561,7 @@ __global__ void __launch_bounds__(512) k_gemv_warp(GemvW p) {
         gw_load<W16>(p, r0, 0, lane, t0);
         gw_load<W16>(p, min(r1, p.N - 1), 0, lane, t1);
     }
+    gw_prefetch_next(p);
     pdl_wait();
     // ---- stage (and normalise) the input rows ----
     for (int i = tid * 4; i < MT * p.K; i += blockDim.x * 4) {
@@ -675,6 +691,9 @@ static void gemv_warp(const GemmArgs &g) {
     if (p.pair_half && g.N != 2 * p.pair_half) fatal("gemv: gated pairs need N = 2 * half");
     if (p.rope_cos && ((p.rope_cols % p.hd) || (p.hd & 1) || ((g.N - p.rope_cols) & 1))) fatal("gemv: rotary heads do not tile the columns");
     p.ngroups = p.pair_half ? p.pair_half : (g.N + 1) / 2;
+    static const bool pf_ok = !getenv("NCM_B200_NO_GEMV_PREFETCH");
+    p.pf = (pf_ok && g.pf_next && ((uintptr_t)g.pf_next & 15) == 0) ? (const char *)g.pf_next : nullptr;
+    p.pf_bytes = g.pf_next_bytes;
     const int mt = g.M <= 1 ? 1 : g.M <= 2 ? 2 : 4;
     const size_t smem = (size_t)mt * g.K * 4 + 256;
     // warps per CTA: as many as still leave every SM a CTA; CTAs: one or two per SM, persistent over the pairs

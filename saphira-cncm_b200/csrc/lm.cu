@@ -160,6 +160,21 @@ extern "C" NcmbLM *ncmb_lm_open(const NCMConfig *c, const char *weights, int is_
         }
         m->wte16 = shadow(m->wte, (int64_t)m->V * m->C);
     }
+    // what a decode step's weight-streaming kernels read after each block's last one: the next block's QKV matrix,
+    // after the last block the first 32 MB of the vocabulary projection (the whole of it would evict what L2 holds)
+    for (size_t li = 0; li < m->blocks.size(); li++) {
+        BlockWeights &bw = m->blocks[li];
+        if (li + 1 < m->blocks.size()) {
+            const BlockWeights &nx = m->blocks[li + 1];
+            const int64_t n = (int64_t)(m->C + 2 * m->nkv * m->hd) * m->C;
+            bw.next_w = nx.qkvw16 ? (const void *)nx.qkvw16 : (const void *)nx.qkvw;
+            bw.next_w_bytes = (size_t)n * (nx.qkvw16 ? 2 : 4);
+        } else {
+            const size_t bytes = (size_t)m->V * m->C * (m->wte16 ? 2 : 4);
+            bw.next_w = m->wte16 ? (const void *)m->wte16 : (const void *)m->wte;
+            bw.next_w_bytes = bytes < ((size_t)32 << 20) ? bytes : ((size_t)32 << 20);
+        }
+    }
     CUDA_CHECK(cudaStreamSynchronize(stream()));
     return m;
 }

@@ -104,7 +104,13 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     const bool small = fuse_small && !split && gemv_fusable(g);
     bool kv_written = false, qk_done = false;
     g.W16 = w.qkvw16;
+    // decode steps: every weight-streaming kernel asks L2 for the matrix the next one reads (2- or 4-byte form)
+    auto next_is = [&](GemmArgs &q, const float *W, const unsigned short *W16, int64_t n) {
+        q.pf_next = small ? (W16 ? (const void *)W16 : (const void *)W) : nullptr;
+        q.pf_next_bytes = (size_t)n * (W16 ? 2 : 4);
+    };
     if (small) {
+        next_is(g, w.ow, w.ow16, (int64_t)C * C);
         // up to four rows: the warp-per-row-pair GEMV also rotates the query / key heads in its epilogue, so the
         // rotation pass and the cache copy of a decode step disappear (per-head norms keep their own pass)
         if (p.cos_t && !w.qnw && !w.knw && (hd & 1) == 0 && gemv_warp_takes(g)) {
@@ -159,6 +165,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     g = GemmArgs();
     g.x_fmt = fmt;
     g.x = b.ctx; g.x_lo = ctx_lo; g.ldx = C; g.W = w.ow; g.W16 = w.ow16; g.bias = w.ob; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = C;
+    next_is(g, w.fcw, w.fcw16, (int64_t)(w.gated ? 2 : 1) * w.Hh * C);
     gemm(g);
     g = GemmArgs();
     g.ldx = C; g.M = ntok; g.K = C;
@@ -170,6 +177,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
         g.x_fmt = fmt; g.y_fmt = fmt;
         g.x = b.ln; g.x_lo = ln_lo;
     }
+    next_is(g, w.pw, w.pw16, (int64_t)C * w.Hh);                       // the up-projection is followed by the down-projection
     if (w.gated && small && w.fcw && gemv_warp_takes(g)) {
         // up to four rows: gate and up rows are paired inside the GEMV, the gated product leaves from its epilogue
         g.W = w.fcw; g.W16 = w.fcw16; g.bias = w.fcb; g.N = 2 * w.Hh; g.gv_pair_half = w.Hh; g.act = w.act; g.y = b.h; g.ldy = w.Hh;
@@ -197,6 +205,7 @@ void run_block(float *x, int64_t ntok, int C, int H, int nkv, const BlockWeights
     g = GemmArgs();
     g.x_fmt = fmt;
     g.x = b.h; g.x_lo = h_lo; g.ldx = w.Hh; g.W = w.pw; g.W16 = w.pw16; g.bias = w.pb; g.res = x; g.ldres = C; g.y = x; g.ldy = C; g.M = ntok; g.N = C; g.K = w.Hh;
+    if (small) { g.pf_next = w.next_w; g.pf_next_bytes = w.next_w_bytes; }
     gemm(g);
 }
 
