@@ -142,6 +142,11 @@ __global__ void __launch_bounds__(ATC_BLOCK) k_attention_tc(const __grid_constan
                                                              const __grid_constant__ CUtensorMap mk2,
                                                              AttnTcDev a) {
     pdl_launch_dependents();          // programmatic dependent launch: see launch_pdl()
+    if (threadIdx.x == 0) {           // the descriptors are on their way while the predecessor finishes
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mq) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mk1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&mk2) : "memory");
+    }
     pdl_wait();
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
