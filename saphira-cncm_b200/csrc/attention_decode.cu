@@ -423,6 +423,240 @@ __global__ void __launch_bounds__(256) k_attention_dec_warp(AttnDecDev a) {
     if (tid == 0) a.count[row * a.Hkv + kvh] = 0;
 }
 
+// ---- head dim 64, many (query, head) pairs per kv group: one WARP per run of 32-key chunks, products on mma.sync ----
+// With 7 to 16 (query, head) pairs per kv group (grouped-query decode steps of many sequences, the 4-token NCP
+// level) the kernels above spend their time re-reading q and the probabilities from shared memory, one load per four
+// multiply-adds. Here the pairs are the 16 rows of an m16n8k8 tensor-core tile: S[16 x 32] = Q[16 x 64] K^T and
+// O[16 x 64] += P[16 x 32] V per 32-key chunk, each product as three TF32 MMAs over hi/lo splits (fp32-grade, as
+// the three-pass GEMM engine). Every K and V element of a chunk is loaded from global memory exactly once, straight
+// into the lane that needs it as a B fragment; Q stays in registers as A fragments for the whole kernel; the
+// probabilities cross from the accumulator layout to the A-fragment layout through 2 KB of shared memory per warp.
+// A warp walks `cps` consecutive chunks with a running maximum and sum per row; the four warps of a CTA take
+// consecutive runs of the same (row, kv head) and their partials meet in shared memory; one partial per CTA goes to
+// global memory, and only when the row needs more than one CTA (last CTA merges, as above). The tcgen05 path needs
+// 64 rows at least: for 16 it would idle three quarters of the tile.
+constexpr int ADM_WARPS = 4;
+#ifndef ADM_MINB
+#define ADM_MINB 3
+#endif
+__device__ __forceinline__ void adm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void adm_split(float v, uint32_t &hi, uint32_t &lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+    const float r = v - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+__device__ __forceinline__ float adm_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(AttnDecDev a) {
+    constexpr int HD = 64, GA = AD_MAXG;
+    __shared__ __align__(8) float ps[ADM_WARPS][GA][36];      // a warp's probabilities of a chunk, [row][key] (padded rows)
+    __shared__ float pm[ADM_WARPS][GA], pl[ADM_WARPS][GA], wg[ADM_WARPS][GA];
+    __shared__ __align__(8) float po[ADM_WARPS][GA][HD];
+    __shared__ float Mg[GA], Lg[GA];
+    __shared__ int s_last;
+    const int row = blockIdx.z, kvh = blockIdx.y, sp = blockIdx.x;
+    const int Gh = a.H / a.Hkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;                // fragment coordinates of the lane
+    pdl_launch_dependents();
+    pdl_wait();
+    const int *lens = a.k_len ? a.k_len + (a.step_d ? (int64_t)(*a.step_d) * a.len_step : 0) : nullptr;
+    const int k00 = a.k_start[row], n1s = lens ? lens[row] : a.k_start[row + 1] - k00;
+    const int k20 = a.k2_start ? a.k2_start[row] : 0, n2s = a.k2_start ? a.k2_start[row + 1] - k20 : 0;
+    const int n1 = n1s + n2s;
+    const int per_warp = a.cps * 32, per_cta = ADM_WARPS * per_warp;
+    const int nsplit = (n1 + per_cta - 1) / per_cta;
+    if (sp >= nsplit) return;
+    const int kbeg = sp * per_cta + warp * per_warp;          // first key of this warp's run
+    const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
+    const int G = Gh * nq;                                    // virtual heads (tile rows): vh = g * nq + qi
+    auto krow = [&](int j) -> const float * {
+        return j < n1s ? a.k + (int64_t)(k00 + j) * a.ldk : a.k2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
+    auto vrow = [&](int j) -> const float * {
+        return j < n1s ? a.v + (int64_t)(k00 + j) * a.ldk : a.v2 + (int64_t)(k20 + j - n1s) * a.ldk2;
+    };
+    // Q as A fragments (row-major 16 x 8 per k-step: a0 (gid, tig), a1 (gid + 8, tig), a2 (gid, tig + 4), a3 (gid + 8, tig + 4))
+    uint32_t qh[8][4], ql[8][4];
+    {
+        const int r0 = gid, r1 = gid + 8;
+        const float *p0 = r0 < G ? a.q + (int64_t)(q0 + r0 % nq) * a.ldq + (kvh * Gh + r0 / nq) * HD : nullptr;
+        const float *p1 = r1 < G ? a.q + (int64_t)(q0 + r1 % nq) * a.ldq + (kvh * Gh + r1 / nq) * HD : nullptr;
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            adm_split(p0 ? p0[8 * s + tig] : 0.f, qh[s][0], ql[s][0]);
+            adm_split(p1 ? p1[8 * s + tig] : 0.f, qh[s][1], ql[s][1]);
+            adm_split(p0 ? p0[8 * s + tig + 4] : 0.f, qh[s][2], ql[s][2]);
+            adm_split(p1 ? p1[8 * s + tig + 4] : 0.f, qh[s][3], ql[s][3]);
+        }
+    }
+    const float sl2 = a.scale * 1.4426950408889634f;          // scores in the log2 domain
+    float oacc[8][4];                                         // O[16 x 64]: n-tile j = dims 8 j .. 8 j + 7, rows gid / gid + 8
+#pragma unroll
+    for (int j = 0; j < 8; j++) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f; // running maximum (log2 domain) and sum of rows gid, gid + 8
+    for (int c = 0; c < a.cps; c++) {
+        const int kc = kbeg + c * 32;
+        if (kc >= n1) break;                                  // warp-uniform
+        // ---- S = Q K^T: B fragment of n-tile j (keys kc + 8 j ..), k-step s: b0 = K[key gid][dim 8 s + tig], b1 = dim + 4 ----
+        float sacc[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
+        const float *kp[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const int key = kc + 8 * j + gid; kp[j] = key < n1 ? krow(key) + kvh * HD : nullptr; }
+#pragma unroll
+        for (int s = 0; s < 8; s++) {
+            float kb0[4], kb1[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { kb0[j] = kp[j] ? kp[j][8 * s + tig] : 0.f; kb1[j] = kp[j] ? kp[j][8 * s + tig + 4] : 0.f; }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t bh0, bl0, bh1, bl1;
+                adm_split(kb0[j], bh0, bl0); adm_split(kb1[j], bh1, bl1);
+                adm_mma(sacc[j], ql[s], bh0, bh1);
+                adm_mma(sacc[j], qh[s], bl0, bl1);
+                adm_mma(sacc[j], qh[s], bh0, bh1);
+            }
+        }
+        // ---- softmax of the chunk, rows gid (c0, c1) and gid + 8 (c2, c3); columns 8 j + 2 tig, + 1 ----
+        float cm0 = -INFINITY, cm1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const bool ok = kc + 8 * j + 2 * tig + e < n1;
+                sacc[j][e] = ok ? sacc[j][e] * sl2 : -INFINITY;
+                sacc[j][2 + e] = ok ? sacc[j][2 + e] * sl2 : -INFINITY;
+                cm0 = fmaxf(cm0, sacc[j][e]); cm1 = fmaxf(cm1, sacc[j][2 + e]);
+            }
+        }
+        cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 1)); cm0 = fmaxf(cm0, __shfl_xor_sync(0xffffffffu, cm0, 2));
+        cm1 = fmaxf(cm1, __shfl_xor_sync(0xffffffffu, cm1, 1)); cm1 = fmaxf(cm1, __shfl_xor_sync(0xffffffffu, cm1, 2));
+        const float nm0 = fmaxf(m0, cm0), nm1 = fmaxf(m1, cm1);   // finite: the chunk has at least one key
+        const float al0 = m0 == -INFINITY ? 0.f : adm_ex2(m0 - nm0), al1 = m1 == -INFINITY ? 0.f : adm_ex2(m1 - nm1);
+        m0 = nm0; m1 = nm1;
+        float cs0 = 0.f, cs1 = 0.f;
+        __syncwarp();                                         // the previous chunk's reads of ps are done
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float p00 = adm_ex2(sacc[j][0] - nm0), p01 = adm_ex2(sacc[j][1] - nm0);
+            const float p10 = adm_ex2(sacc[j][2] - nm1), p11 = adm_ex2(sacc[j][3] - nm1);
+            cs0 += p00 + p01; cs1 += p10 + p11;
+            *(float2 *)&ps[warp][gid][8 * j + 2 * tig] = make_float2(p00, p01);
+            *(float2 *)&ps[warp][gid + 8][8 * j + 2 * tig] = make_float2(p10, p11);
+        }
+        cs0 += __shfl_xor_sync(0xffffffffu, cs0, 1); cs0 += __shfl_xor_sync(0xffffffffu, cs0, 2);
+        cs1 += __shfl_xor_sync(0xffffffffu, cs1, 1); cs1 += __shfl_xor_sync(0xffffffffu, cs1, 2);
+        l0 = fmaf(l0, al0, cs0); l1 = fmaf(l1, al1, cs1);
+#pragma unroll
+        for (int j = 0; j < 8; j++) { oacc[j][0] *= al0; oacc[j][1] *= al0; oacc[j][2] *= al1; oacc[j][3] *= al1; }
+        __syncwarp();
+        // ---- O += P V: A fragment of k-step s (keys kc + 8 s ..) from ps; B of n-tile j: b0 = V[key tig][dim 8 j + gid], b1 = key + 4 ----
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            uint32_t ph[4], pl_[4];
+            adm_split(ps[warp][gid][8 * s + tig], ph[0], pl_[0]);
+            adm_split(ps[warp][gid + 8][8 * s + tig], ph[1], pl_[1]);
+            adm_split(ps[warp][gid][8 * s + tig + 4], ph[2], pl_[2]);
+            adm_split(ps[warp][gid + 8][8 * s + tig + 4], ph[3], pl_[3]);
+            const int ka = kc + 8 * s + tig, kb = ka + 4;
+            const float *va = ka < n1 ? vrow(ka) + kvh * HD : nullptr, *vb = kb < n1 ? vrow(kb) + kvh * HD : nullptr;
+            float vb0[8], vb1[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) { vb0[j] = va ? va[8 * j + gid] : 0.f; vb1[j] = vb ? vb[8 * j + gid] : 0.f; }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                uint32_t bh0, bl0, bh1, bl1;
+                adm_split(vb0[j], bh0, bl0); adm_split(vb1[j], bh1, bl1);
+                adm_mma(oacc[j], pl_, bh0, bh1);
+                adm_mma(oacc[j], ph, bl0, bl1);
+                adm_mma(oacc[j], ph, bh0, bh1);
+            }
+        }
+    }
+    // ---- the warps' partials meet in shared memory ----
+    if (tig == 0) { pm[warp][gid] = m0; pm[warp][gid + 8] = m1; pl[warp][gid] = l0; pl[warp][gid + 8] = l1; }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        *(float2 *)&po[warp][gid][8 * j + 2 * tig] = make_float2(oacc[j][0], oacc[j][1]);
+        *(float2 *)&po[warp][gid + 8][8 * j + 2 * tig] = make_float2(oacc[j][2], oacc[j][3]);
+    }
+    __syncthreads();
+    if (tid < G) {
+        float M = -INFINITY, L = 0.f;
+        for (int w = 0; w < ADM_WARPS; w++) M = fmaxf(M, pm[w][tid]);
+        for (int w = 0; w < ADM_WARPS; w++) {
+            const float e = (pm[w][tid] == -INFINITY) ? 0.f : adm_ex2(pm[w][tid] - M);
+            wg[w][tid] = e; L = fmaf(pl[w][tid], e, L);
+        }
+        Mg[tid] = M; Lg[tid] = L;
+    }
+    __syncthreads();
+    float *mine = a.part + ((int64_t)(row * a.Hkv + kvh) * a.max_split + sp) * AD_MAXG * (HD + 2);
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        float O = 0.f;
+        for (int w = 0; w < ADM_WARPS; w++) O = fmaf(po[w][g][d], wg[w][g], O);
+        if (nsplit == 1) {
+            const float L = Lg[g];
+            const float r = L > 0.f ? O / L : 0.f;
+            const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
+            if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+            else a.out[at] = r;
+        } else {
+            mine[g * (HD + 2) + 2 + d] = O;
+            if (d == 0) { mine[g * (HD + 2)] = Mg[g]; mine[g * (HD + 2) + 1] = Lg[g]; }
+        }
+    }
+    if (nsplit == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        unsigned old = atomicAdd(a.count + row * a.Hkv + kvh, 1u);
+        s_last = (old == (unsigned)(nsplit - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // the last CTA of the (row, kv head) merges the CTAs' partials (maxima in the log2 domain here)
+    const float *base = a.part + (int64_t)(row * a.Hkv + kvh) * a.max_split * AD_MAXG * (HD + 2);
+    if (tid < G) {
+        float M = -INFINITY, L = 0.f;
+        for (int x = 0; x < nsplit; x++) M = fmaxf(M, __ldcg(base + ((int64_t)x * AD_MAXG + tid) * (HD + 2)));
+        for (int x = 0; x < nsplit; x++) {
+            const float *pp = base + ((int64_t)x * AD_MAXG + tid) * (HD + 2);
+            const float mx = __ldcg(pp);
+            L = fmaf(__ldcg(pp + 1), mx == -INFINITY ? 0.f : adm_ex2(mx - M), L);
+        }
+        Mg[tid] = M; Lg[tid] = L;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * HD; i += blockDim.x) {
+        const int g = i / HD, d = i % HD;
+        const float M = Mg[g];
+        float O = 0.f;
+        for (int x = 0; x < nsplit; x++) {
+            const float *pp = base + ((int64_t)x * AD_MAXG + g) * (HD + 2);
+            const float mx = __ldcg(pp);
+            O = fmaf(__ldcg(pp + 2 + d), mx == -INFINITY ? 0.f : adm_ex2(mx - M), O);
+        }
+        const float L = Lg[g];
+        const float r = L > 0.f ? O / L : 0.f;
+        const int64_t at = (int64_t)(q0 + g % nq) * a.ldo + (kvh * Gh + g / nq) * HD + d;
+        if (a.out_lo) store_split1(a.out, a.out_lo, at, r, a.out_fmt);
+        else a.out[at] = r;
+    }
+    if (tid == 0) a.count[row * a.Hkv + kvh] = 0;
+}
+
 bool attention_decode_supported(const AttnArgs &a) {
     if (a.max_q < 1 || a.max_q > 4 || a.causal || a.window > 0) return false;      // a few queries per row, no mask
     if (a.hd != 16 && a.hd != 32 && a.hd != 64 && a.hd != 128) return false;
@@ -450,6 +684,47 @@ void attention_decode(const AttnArgs &a) {
     // once. With hundreds of pairs the older kernel's higher occupancy wins (GPT-2 at 64 sequences: 1.44 against
     // 1.94 ms per step).
     const int gq_w = (a.H / a.Hkv) * a.max_q;
+    // many (query, head) pairs per kv group and enough (row, kv head) pairs to fill the GPU with warps: the
+    // tensor-core kernel (read per call: the tests run every kernel on the same inputs)
+    const char *mma_s = getenv("NCM_B200_ATTN_DEC_MMA");
+    const int mma_env = mma_s ? atoi(mma_s) : -1;
+    const bool mma_takes = a.hd == 64 && gq_w <= AD_MAXG && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0);
+    // (measured: 99 -> 67 us for the 4-token level of config 2, 16 pairs per group and 9 chunks; slower than the kernels
+    // above on the Qwen2 decode shape, 7 pairs and 16 - 32 chunks: a warp's chunks are a serial chain of loads)
+    const bool mma_pays = gq_w >= 12 && max_chunks <= 16 && pairs * 4 >= (int64_t)ctx().sm_count;
+    if (mma_takes && (mma_env == 1 || (mma_env != 0 && mma_pays))) {
+        // chunks per warp: as few CTAs per (row, kv head) as still give every SM about eight warps
+        const int64_t want_ctas = std::max<int64_t>(1, cdiv((int64_t)ctx().sm_count * 2, pairs));
+        int cpw = (int)cdiv(max_chunks, ADM_WARPS * want_ctas);
+        if (cpw < 1) cpw = 1;
+        if (cpw > 16) cpw = 16;
+        const int max_split = (int)cdiv(max_chunks, ADM_WARPS * cpw);
+        if (max_split <= AD_MAXSPLIT) {
+            size_t need = (size_t)a.rows * a.Hkv * max_split * AD_MAXG * (a.hd + 2);
+            if (need > part_cap) {
+                if (part) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(part); }
+                part = (float *)dev_alloc(need * 4); part_cap = need;
+            }
+            size_t nc = (size_t)a.rows * a.Hkv;
+            if (nc > count_cap) {
+                if (count) { CUDA_CHECK(cudaStreamSynchronize(stream())); dev_free(count); }
+                count = (unsigned *)dev_alloc(nc * 4); count_cap = nc;
+                CUDA_CHECK(cudaMemsetAsync(count, 0, nc * 4, stream()));
+            }
+            AttnDecDev d;
+            d.q = a.q; d.ldq = a.ldq; d.k = a.k1; d.v = a.v1; d.ldk = a.ldk1;
+            d.k2 = a.k2; d.v2 = a.v2; d.ldk2 = a.ldk2; d.k2_start = a.k2 ? a.k2_start : nullptr; d.out = a.out; d.out_lo = a.out_lo; d.out_fmt = a.out_fmt; d.ldo = a.ldo;
+            d.q_start = a.q_start; d.k_start = a.k1_start; d.k_len = a.k1_len;
+            d.step_d = a.step_d; d.len_step = a.k1_len_step;
+            d.H = a.H; d.Hkv = a.Hkv; d.max_split = max_split; d.cps = cpw; d.hs = 1;
+            d.scale = 1.0f / sqrtf((float)a.hd);
+            d.part = part; d.count = count;
+            dim3 grid((unsigned)max_split, (unsigned)a.Hkv, (unsigned)a.rows);
+            ProfScope ps(NCMB_K_ATTN, 4.0 * (double)a.total_q * a.avg_keys * a.H * a.hd, 0);
+            LAUNCH_PDL(k_attention_dec_mma, grid, ADM_WARPS * 32, 0, d);
+            return;
+        }
+    }
     const int gmw = gq_w <= 1 ? 1 : (gq_w <= 8 ? 2 : 4);
     const int hs = (int)cdiv(gq_w, gmw);                                         // 1, 2, 3 or 4 warps per chunk
     const int cpc = hs <= 2 ? 4 : 2;                                             // chunks per CTA (128 or 64 keys): at most eight warps
