@@ -429,7 +429,10 @@ __global__ void __launch_bounds__(256) k_attention_dec_warp(AttnDecDev a) {
 // multiply-adds. Here the pairs are the 16 rows of an m16n8k8 tensor-core tile: S[16 x 32] = Q[16 x 64] K^T and
 // O[16 x 64] += P[16 x 32] V per 32-key chunk, each product as three TF32 MMAs over hi/lo splits (fp32-grade, as
 // the three-pass GEMM engine). Every K and V element of a chunk is loaded from global memory exactly once, straight
-// into the lane that needs it as a B fragment; Q stays in registers as A fragments for the whole kernel; the
+// into the lane that needs it as a B fragment, sixteen bytes at a time: which head dimension sits at which k position
+// of a score MMA, and which at which column of an output tile, is free as long as both operands agree, so the
+// positions are chosen to make a lane's elements contiguous (k-step 2 m + h holds dims 16 m + 4 tig + 2 h and + 1 at
+// positions tig and tig + 4; column gid of output tile j is dim 8 gid + j). Q stays in registers as A fragments; the
 // probabilities cross from the accumulator layout to the A-fragment layout through 2 KB of shared memory per warp.
 // A warp walks `cps` consecutive chunks with a running maximum and sum per row; the four warps of a CTA take
 // consecutive runs of the same (row, kv head) and their partials meet in shared memory; one partial per CTA goes to
@@ -483,18 +486,21 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
     auto vrow = [&](int j) -> const float * {
         return j < n1s ? a.v + (int64_t)(k00 + j) * a.ldk : a.v2 + (int64_t)(k20 + j - n1s) * a.ldk2;
     };
-    // Q as A fragments (row-major 16 x 8 per k-step: a0 (gid, tig), a1 (gid + 8, tig), a2 (gid, tig + 4), a3 (gid + 8, tig + 4))
+    // Q as A fragments (16 x 8 per k-step: a0 (row gid, k tig), a1 (gid + 8, tig), a2 (gid, tig + 4), a3 (gid + 8, tig + 4)),
+    // k positions mapped to head dims as described above
     uint32_t qh[8][4], ql[8][4];
     {
         const int r0 = gid, r1 = gid + 8;
         const float *p0 = r0 < G ? a.q + (int64_t)(q0 + r0 % nq) * a.ldq + (kvh * Gh + r0 / nq) * HD : nullptr;
         const float *p1 = r1 < G ? a.q + (int64_t)(q0 + r1 % nq) * a.ldq + (kvh * Gh + r1 / nq) * HD : nullptr;
+        const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int s = 0; s < 8; s++) {
-            adm_split(p0 ? p0[8 * s + tig] : 0.f, qh[s][0], ql[s][0]);
-            adm_split(p1 ? p1[8 * s + tig] : 0.f, qh[s][1], ql[s][1]);
-            adm_split(p0 ? p0[8 * s + tig + 4] : 0.f, qh[s][2], ql[s][2]);
-            adm_split(p1 ? p1[8 * s + tig + 4] : 0.f, qh[s][3], ql[s][3]);
+        for (int m = 0; m < 4; m++) {
+            const float4 f0 = p0 ? *(const float4 *)(p0 + 16 * m + 4 * tig) : z4, f1 = p1 ? *(const float4 *)(p1 + 16 * m + 4 * tig) : z4;
+            adm_split(f0.x, qh[2 * m][0], ql[2 * m][0]); adm_split(f1.x, qh[2 * m][1], ql[2 * m][1]);
+            adm_split(f0.y, qh[2 * m][2], ql[2 * m][2]); adm_split(f1.y, qh[2 * m][3], ql[2 * m][3]);
+            adm_split(f0.z, qh[2 * m + 1][0], ql[2 * m + 1][0]); adm_split(f1.z, qh[2 * m + 1][1], ql[2 * m + 1][1]);
+            adm_split(f0.w, qh[2 * m + 1][2], ql[2 * m + 1][2]); adm_split(f1.w, qh[2 * m + 1][3], ql[2 * m + 1][3]);
         }
     }
     const float sl2 = a.scale * 1.4426950408889634f;          // scores in the log2 domain
@@ -505,25 +511,31 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
     for (int c = 0; c < a.cps; c++) {
         const int kc = kbeg + c * 32;
         if (kc >= n1) break;                                  // warp-uniform
-        // ---- S = Q K^T: B fragment of n-tile j (keys kc + 8 j ..), k-step s: b0 = K[key gid][dim 8 s + tig], b1 = dim + 4 ----
+        // ---- S = Q K^T: n-tile j = keys kc + 8 j + gid; the lane's sixteen dims of its key as four 16-byte loads ----
         float sacc[4][4];
+        float4 kf[4][4];
+        const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < 4; j++) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
-        const float *kp[4];
+        for (int j = 0; j < 4; j++) {
+            sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
+            const int key = kc + 8 * j + gid;
+            const float *kp = key < n1 ? krow(key) + kvh * HD + 4 * tig : nullptr;
 #pragma unroll
-        for (int j = 0; j < 4; j++) { const int key = kc + 8 * j + gid; kp[j] = key < n1 ? krow(key) + kvh * HD : nullptr; }
+            for (int m = 0; m < 4; m++) kf[j][m] = kp ? *(const float4 *)(kp + 16 * m) : z4;
+        }
 #pragma unroll
-        for (int s = 0; s < 8; s++) {
-            float kb0[4], kb1[4];
+        for (int j = 0; j < 4; j++) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) { kb0[j] = kp[j] ? kp[j][8 * s + tig] : 0.f; kb1[j] = kp[j] ? kp[j][8 * s + tig + 4] : 0.f; }
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int m = 0; m < 4; m++) {
                 uint32_t bh0, bl0, bh1, bl1;
-                adm_split(kb0[j], bh0, bl0); adm_split(kb1[j], bh1, bl1);
-                adm_mma(sacc[j], ql[s], bh0, bh1);
-                adm_mma(sacc[j], qh[s], bl0, bl1);
-                adm_mma(sacc[j], qh[s], bh0, bh1);
+                adm_split(kf[j][m].x, bh0, bl0); adm_split(kf[j][m].y, bh1, bl1);        // k-step 2 m
+                adm_mma(sacc[j], ql[2 * m], bh0, bh1);
+                adm_mma(sacc[j], qh[2 * m], bl0, bl1);
+                adm_mma(sacc[j], qh[2 * m], bh0, bh1);
+                adm_split(kf[j][m].z, bh0, bl0); adm_split(kf[j][m].w, bh1, bl1);        // k-step 2 m + 1
+                adm_mma(sacc[j], ql[2 * m + 1], bh0, bh1);
+                adm_mma(sacc[j], qh[2 * m + 1], bl0, bl1);
+                adm_mma(sacc[j], qh[2 * m + 1], bh0, bh1);
             }
         }
         // ---- softmax of the chunk, rows gid (c0, c1) and gid + 8 (c2, c3); columns 8 j + 2 tig, + 1 ----
@@ -559,7 +571,8 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
 #pragma unroll
         for (int j = 0; j < 8; j++) { oacc[j][0] *= al0; oacc[j][1] *= al0; oacc[j][2] *= al1; oacc[j][3] *= al1; }
         __syncwarp();
-        // ---- O += P V: A fragment of k-step s (keys kc + 8 s ..) from ps; B of n-tile j: b0 = V[key tig][dim 8 j + gid], b1 = key + 4 ----
+        // ---- O += P V: A fragment of k-step s (keys kc + 8 s + tig, + 4) from ps; column gid of output tile j is dim
+        // 8 gid + j, so the lane's eight dims of a value row are two 16-byte loads ----
 #pragma unroll
         for (int s = 0; s < 4; s++) {
             uint32_t ph[4], pl_[4];
@@ -568,10 +581,11 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
             adm_split(ps[warp][gid][8 * s + tig + 4], ph[2], pl_[2]);
             adm_split(ps[warp][gid + 8][8 * s + tig + 4], ph[3], pl_[3]);
             const int ka = kc + 8 * s + tig, kb = ka + 4;
-            const float *va = ka < n1 ? vrow(ka) + kvh * HD : nullptr, *vb = kb < n1 ? vrow(kb) + kvh * HD : nullptr;
-            float vb0[8], vb1[8];
-#pragma unroll
-            for (int j = 0; j < 8; j++) { vb0[j] = va ? va[8 * j + gid] : 0.f; vb1[j] = vb ? vb[8 * j + gid] : 0.f; }
+            const float *va = ka < n1 ? vrow(ka) + kvh * HD + 8 * gid : nullptr, *vb = kb < n1 ? vrow(kb) + kvh * HD + 8 * gid : nullptr;
+            const float4 a0 = va ? *(const float4 *)va : z4, a1 = va ? *(const float4 *)(va + 4) : z4;
+            const float4 b0 = vb ? *(const float4 *)vb : z4, b1 = vb ? *(const float4 *)(vb + 4) : z4;
+            const float vb0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float vb1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 uint32_t bh0, bl0, bh1, bl1;
@@ -585,9 +599,9 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
     // ---- the warps' partials meet in shared memory ----
     if (tig == 0) { pm[warp][gid] = m0; pm[warp][gid + 8] = m1; pl[warp][gid] = l0; pl[warp][gid + 8] = l1; }
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        *(float2 *)&po[warp][gid][8 * j + 2 * tig] = make_float2(oacc[j][0], oacc[j][1]);
-        *(float2 *)&po[warp][gid + 8][8 * j + 2 * tig] = make_float2(oacc[j][2], oacc[j][3]);
+    for (int j = 0; j < 8; j++) {                             // columns 2 tig, 2 tig + 1 of tile j are dims 16 tig + j, + 8
+        po[warp][gid][16 * tig + j] = oacc[j][0]; po[warp][gid][16 * tig + 8 + j] = oacc[j][1];
+        po[warp][gid + 8][16 * tig + j] = oacc[j][2]; po[warp][gid + 8][16 * tig + 8 + j] = oacc[j][3];
     }
     __syncthreads();
     if (tid < G) {
@@ -688,10 +702,15 @@ void attention_decode(const AttnArgs &a) {
     // tensor-core kernel (read per call: the tests run every kernel on the same inputs)
     const char *mma_s = getenv("NCM_B200_ATTN_DEC_MMA");
     const int mma_env = mma_s ? atoi(mma_s) : -1;
-    const bool mma_takes = a.hd == 64 && gq_w <= AD_MAXG && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0);
-    // (measured: 99 -> 67 us for the 4-token level of config 2, 16 pairs per group and 9 chunks; slower than the kernels
-    // above on the Qwen2 decode shape, 7 pairs and 16 - 32 chunks: a warp's chunks are a serial chain of loads)
-    const bool mma_pays = gq_w >= 12 && max_chunks <= 16 && pairs * 4 >= (int64_t)ctx().sm_count;
+    auto al16 = [](const void *q) { return ((uintptr_t)q & 15) == 0; };
+    const bool mma_takes = a.hd == 64 && gq_w <= AD_MAXG && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0) && ((a.ldq & 3) == 0) &&
+                           al16(a.q) && al16(a.k1) && al16(a.v1) && (!a.k2 || (al16(a.k2) && al16(a.v2)));
+    // (measured: the 4-token level of config 2 -- 16 pairs per group, 9 chunks -- 2.99 -> 2.50 ms over its 12 layers; on
+    // the Qwen2 batched-decode shape -- 7 pairs, 16 - 32 chunks -- 5 - 12% slower than the kernels above: a warp's
+    // chunks are a serial chain of load, MMAs, load, MMAs with nothing in flight under the arithmetic)
+    static const int mma_min_g = getenv("NCM_B200_ATTN_DEC_MMA_MIN_G") ? atoi(getenv("NCM_B200_ATTN_DEC_MMA_MIN_G")) : 12;
+    static const int mma_max_ch = getenv("NCM_B200_ATTN_DEC_MMA_MAX_CHUNKS") ? atoi(getenv("NCM_B200_ATTN_DEC_MMA_MAX_CHUNKS")) : 16;
+    const bool mma_pays = gq_w >= mma_min_g && max_chunks <= mma_max_ch && pairs * 4 >= (int64_t)ctx().sm_count;
     if (mma_takes && (mma_env == 1 || (mma_env != 0 && mma_pays))) {
         // chunks per warp: as few CTAs per (row, kv head) as still give every SM about eight warps
         const int64_t want_ctas = std::max<int64_t>(1, cdiv((int64_t)ctx().sm_count * 2, pairs));
