@@ -432,15 +432,18 @@ __global__ void __launch_bounds__(256) k_attention_dec_warp(AttnDecDev a) {
 // into the lane that needs it as a B fragment, sixteen bytes at a time: which head dimension sits at which k position
 // of a score MMA, and which at which column of an output tile, is free as long as both operands agree, so the
 // positions are chosen to make a lane's elements contiguous (k-step 2 m + h holds dims 16 m + 4 tig + 2 h and + 1 at
-// positions tig and tig + 4; column gid of output tile j is dim 8 gid + j). Q stays in registers as A fragments; the
+// positions tig and tig + 4; column gid of output tile j is dim 8 gid + j). The hi / lo halves of Q sit in shared
+// memory (a lane's A fragments of two k-steps are four 16-byte reads); the
 // probabilities cross from the accumulator layout to the A-fragment layout through 2 KB of shared memory per warp.
+// Loads run a phase ahead of the arithmetic (the next chunk's keys are requested when the score MMAs are done with
+// their registers, the chunk's values before its score MMAs).
 // A warp walks `cps` consecutive chunks with a running maximum and sum per row; the four warps of a CTA take
 // consecutive runs of the same (row, kv head) and their partials meet in shared memory; one partial per CTA goes to
 // global memory, and only when the row needs more than one CTA (last CTA merges, as above). The tcgen05 path needs
 // 64 rows at least: for 16 it would idle three quarters of the tile.
 constexpr int ADM_WARPS = 4;
 #ifndef ADM_MINB
-#define ADM_MINB 3
+#define ADM_MINB 2
 #endif
 __device__ __forceinline__ void adm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -460,6 +463,7 @@ __device__ __forceinline__ float adm_ex2(float x) {
 __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(AttnDecDev a) {
     constexpr int HD = 64, GA = AD_MAXG;
     __shared__ __align__(8) float ps[ADM_WARPS][GA][36];      // a warp's probabilities of a chunk, [row][key] (padded rows)
+    __shared__ __align__(16) uint32_t qsh[GA][68], qsl[GA][68];   // TF32 hi / lo halves of the query tile (padded rows)
     __shared__ float pm[ADM_WARPS][GA], pl[ADM_WARPS][GA], wg[ADM_WARPS][GA];
     __shared__ __align__(8) float po[ADM_WARPS][GA][HD];
     __shared__ float Mg[GA], Lg[GA];
@@ -487,57 +491,77 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
         return j < n1s ? a.v + (int64_t)(k00 + j) * a.ldk : a.v2 + (int64_t)(k20 + j - n1s) * a.ldk2;
     };
     // Q as A fragments (16 x 8 per k-step: a0 (row gid, k tig), a1 (gid + 8, tig), a2 (gid, tig + 4), a3 (gid + 8, tig + 4)),
-    // k positions mapped to head dims as described above
-    uint32_t qh[8][4], ql[8][4];
+    // k positions mapped to head dims as described above. The hi / lo halves of the 16 x 64 tile are formed once per CTA
+    // and kept in shared memory; a lane fetches its fragments of two k-steps with four 16-byte reads.
     {
-        const int r0 = gid, r1 = gid + 8;
-        const float *p0 = r0 < G ? a.q + (int64_t)(q0 + r0 % nq) * a.ldq + (kvh * Gh + r0 / nq) * HD : nullptr;
-        const float *p1 = r1 < G ? a.q + (int64_t)(q0 + r1 % nq) * a.ldq + (kvh * Gh + r1 / nq) * HD : nullptr;
+        const int r = tid >> 3, d0 = (tid & 7) * 8;                  // 128 threads: row, eight dims
+        const float *p = r < G ? a.q + (int64_t)(q0 + r % nq) * a.ldq + (kvh * Gh + r / nq) * HD + d0 : nullptr;
         const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int m = 0; m < 4; m++) {
-            const float4 f0 = p0 ? *(const float4 *)(p0 + 16 * m + 4 * tig) : z4, f1 = p1 ? *(const float4 *)(p1 + 16 * m + 4 * tig) : z4;
-            adm_split(f0.x, qh[2 * m][0], ql[2 * m][0]); adm_split(f1.x, qh[2 * m][1], ql[2 * m][1]);
-            adm_split(f0.y, qh[2 * m][2], ql[2 * m][2]); adm_split(f1.y, qh[2 * m][3], ql[2 * m][3]);
-            adm_split(f0.z, qh[2 * m + 1][0], ql[2 * m + 1][0]); adm_split(f1.z, qh[2 * m + 1][1], ql[2 * m + 1][1]);
-            adm_split(f0.w, qh[2 * m + 1][2], ql[2 * m + 1][2]); adm_split(f1.w, qh[2 * m + 1][3], ql[2 * m + 1][3]);
-        }
+        const float4 f0 = p ? *(const float4 *)p : z4, f1 = p ? *(const float4 *)(p + 4) : z4;
+        uint4 h0, l0, h1, l1;
+        adm_split(f0.x, h0.x, l0.x); adm_split(f0.y, h0.y, l0.y); adm_split(f0.z, h0.z, l0.z); adm_split(f0.w, h0.w, l0.w);
+        adm_split(f1.x, h1.x, l1.x); adm_split(f1.y, h1.y, l1.y); adm_split(f1.z, h1.z, l1.z); adm_split(f1.w, h1.w, l1.w);
+        *(uint4 *)&qsh[r][d0] = h0; *(uint4 *)&qsh[r][d0 + 4] = h1;
+        *(uint4 *)&qsl[r][d0] = l0; *(uint4 *)&qsl[r][d0 + 4] = l1;
     }
+    __syncthreads();
     const float sl2 = a.scale * 1.4426950408889634f;          // scores in the log2 domain
-    float oacc[8][4];                                         // O[16 x 64]: n-tile j = dims 8 j .. 8 j + 7, rows gid / gid + 8
+    float oacc[8][4];                                         // O[16 x 64]: tile j column n is dim 8 n + j, rows gid / gid + 8
 #pragma unroll
     for (int j = 0; j < 8; j++) { oacc[j][0] = oacc[j][1] = oacc[j][2] = oacc[j][3] = 0.f; }
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f; // running maximum (log2 domain) and sum of rows gid, gid + 8
-    for (int c = 0; c < a.cps; c++) {
-        const int kc = kbeg + c * 32;
-        if (kc >= n1) break;                                  // warp-uniform
-        // ---- S = Q K^T: n-tile j = keys kc + 8 j + gid; the lane's sixteen dims of its key as four 16-byte loads ----
-        float sacc[4][4];
-        float4 kf[4][4];
-        const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    // Loads run a phase ahead of the arithmetic: the keys of chunk c + 1 are requested when the score MMAs of chunk c
+    // are done with their registers (they arrive under the softmax and the P V MMAs), the values of chunk c before its
+    // score MMAs.
+    float4 kf[4][4];                                          // n-tile j = keys kc + 8 j + gid; the lane's sixteen dims, 16 m + 4 tig ..
+    auto load_k = [&](int kc) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f;
             const int key = kc + 8 * j + gid;
             const float *kp = key < n1 ? krow(key) + kvh * HD + 4 * tig : nullptr;
 #pragma unroll
             for (int m = 0; m < 4; m++) kf[j][m] = kp ? *(const float4 *)(kp + 16 * m) : z4;
         }
+    };
+    if (kbeg < n1) load_k(kbeg);
+    for (int c = 0; c < a.cps; c++) {
+        const int kc = kbeg + c * 32;
+        if (kc >= n1) break;                                  // warp-uniform
+        // the chunk's values: k-step s takes keys kc + 8 s + tig (b0) and + 4 (b1); column gid of output tile j is dim
+        // 8 gid + j, so the lane's eight dims of a value row are two 16-byte loads
+        float4 vf[4][4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+        for (int s = 0; s < 4; s++) {
+            const int ka = kc + 8 * s + tig, kb = ka + 4;
+            const float *va = ka < n1 ? vrow(ka) + kvh * HD + 8 * gid : nullptr, *vb = kb < n1 ? vrow(kb) + kvh * HD + 8 * gid : nullptr;
+            vf[s][0] = va ? *(const float4 *)va : z4; vf[s][1] = va ? *(const float4 *)(va + 4) : z4;
+            vf[s][2] = vb ? *(const float4 *)vb : z4; vf[s][3] = vb ? *(const float4 *)(vb + 4) : z4;
+        }
+        // ---- S = Q K^T ----
+        float sacc[4][4];
 #pragma unroll
-            for (int m = 0; m < 4; m++) {
+        for (int j = 0; j < 4; j++) { sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0.f; }
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            const uint4 h0 = *(const uint4 *)&qsh[gid][16 * m + 4 * tig], h1 = *(const uint4 *)&qsh[gid + 8][16 * m + 4 * tig];
+            const uint4 q0l = *(const uint4 *)&qsl[gid][16 * m + 4 * tig], q1l = *(const uint4 *)&qsl[gid + 8][16 * m + 4 * tig];
+            const uint32_t ah0[4] = {h0.x, h1.x, h0.y, h1.y}, al0[4] = {q0l.x, q1l.x, q0l.y, q1l.y};      // k-step 2 m
+            const uint32_t ah1[4] = {h0.z, h1.z, h0.w, h1.w}, al1[4] = {q0l.z, q1l.z, q0l.w, q1l.w};      // k-step 2 m + 1
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
                 uint32_t bh0, bl0, bh1, bl1;
-                adm_split(kf[j][m].x, bh0, bl0); adm_split(kf[j][m].y, bh1, bl1);        // k-step 2 m
-                adm_mma(sacc[j], ql[2 * m], bh0, bh1);
-                adm_mma(sacc[j], qh[2 * m], bl0, bl1);
-                adm_mma(sacc[j], qh[2 * m], bh0, bh1);
-                adm_split(kf[j][m].z, bh0, bl0); adm_split(kf[j][m].w, bh1, bl1);        // k-step 2 m + 1
-                adm_mma(sacc[j], ql[2 * m + 1], bh0, bh1);
-                adm_mma(sacc[j], qh[2 * m + 1], bl0, bl1);
-                adm_mma(sacc[j], qh[2 * m + 1], bh0, bh1);
+                adm_split(kf[j][m].x, bh0, bl0); adm_split(kf[j][m].y, bh1, bl1);
+                adm_mma(sacc[j], al0, bh0, bh1);
+                adm_mma(sacc[j], ah0, bl0, bl1);
+                adm_mma(sacc[j], ah0, bh0, bh1);
+                adm_split(kf[j][m].z, bh0, bl0); adm_split(kf[j][m].w, bh1, bl1);
+                adm_mma(sacc[j], al1, bh0, bh1);
+                adm_mma(sacc[j], ah1, bl0, bl1);
+                adm_mma(sacc[j], ah1, bh0, bh1);
             }
         }
+        if (c + 1 < a.cps && kc + 32 < n1) load_k(kc + 32);    // the next chunk's keys, under the rest of this chunk
         // ---- softmax of the chunk, rows gid (c0, c1) and gid + 8 (c2, c3); columns 8 j + 2 tig, + 1 ----
         float cm0 = -INFINITY, cm1 = -INFINITY;
 #pragma unroll
@@ -571,8 +595,7 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
 #pragma unroll
         for (int j = 0; j < 8; j++) { oacc[j][0] *= al0; oacc[j][1] *= al0; oacc[j][2] *= al1; oacc[j][3] *= al1; }
         __syncwarp();
-        // ---- O += P V: A fragment of k-step s (keys kc + 8 s + tig, + 4) from ps; column gid of output tile j is dim
-        // 8 gid + j, so the lane's eight dims of a value row are two 16-byte loads ----
+        // ---- O += P V: A fragment of k-step s (keys kc + 8 s + tig, + 4) from ps ----
 #pragma unroll
         for (int s = 0; s < 4; s++) {
             uint32_t ph[4], pl_[4];
@@ -580,12 +603,8 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
             adm_split(ps[warp][gid + 8][8 * s + tig], ph[1], pl_[1]);
             adm_split(ps[warp][gid][8 * s + tig + 4], ph[2], pl_[2]);
             adm_split(ps[warp][gid + 8][8 * s + tig + 4], ph[3], pl_[3]);
-            const int ka = kc + 8 * s + tig, kb = ka + 4;
-            const float *va = ka < n1 ? vrow(ka) + kvh * HD + 8 * gid : nullptr, *vb = kb < n1 ? vrow(kb) + kvh * HD + 8 * gid : nullptr;
-            const float4 a0 = va ? *(const float4 *)va : z4, a1 = va ? *(const float4 *)(va + 4) : z4;
-            const float4 b0 = vb ? *(const float4 *)vb : z4, b1 = vb ? *(const float4 *)(vb + 4) : z4;
-            const float vb0[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float vb1[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const float vb0[8] = {vf[s][0].x, vf[s][0].y, vf[s][0].z, vf[s][0].w, vf[s][1].x, vf[s][1].y, vf[s][1].z, vf[s][1].w};
+            const float vb1[8] = {vf[s][2].x, vf[s][2].y, vf[s][2].z, vf[s][2].w, vf[s][3].x, vf[s][3].y, vf[s][3].z, vf[s][3].w};
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 uint32_t bh0, bl0, bh1, bl1;
@@ -705,12 +724,13 @@ void attention_decode(const AttnArgs &a) {
     auto al16 = [](const void *q) { return ((uintptr_t)q & 15) == 0; };
     const bool mma_takes = a.hd == 64 && gq_w <= AD_MAXG && ((a.ldk1 & 3) == 0) && (!a.k2 || (a.ldk2 & 3) == 0) && ((a.ldq & 3) == 0) &&
                            al16(a.q) && al16(a.k1) && al16(a.v1) && (!a.k2 || (al16(a.k2) && al16(a.v2)));
-    // (measured: the 4-token level of config 2 -- 16 pairs per group, 9 chunks -- 2.99 -> 2.50 ms over its 12 layers; on
-    // the Qwen2 batched-decode shape -- 7 pairs, 16 - 32 chunks -- 5 - 12% slower than the kernels above: a warp's
-    // chunks are a serial chain of load, MMAs, load, MMAs with nothing in flight under the arithmetic)
+    // (measured: the 4-token level of config 2 -- 16 pairs per group, 9 chunks -- 2.99 -> 2.44 ms over its 12 layers; the
+    // Qwen2 batched-decode shape -- 7 pairs, 16 - 32 chunks -- at 256 sequences 42 936 -> 44 923 tokens/s, at 32
+    // sequences 12 821 -> 12 661: with few (row, kv head) pairs the CTA-per-chunk kernels spread a row over more SMs)
     static const int mma_min_g = getenv("NCM_B200_ATTN_DEC_MMA_MIN_G") ? atoi(getenv("NCM_B200_ATTN_DEC_MMA_MIN_G")) : 12;
     static const int mma_max_ch = getenv("NCM_B200_ATTN_DEC_MMA_MAX_CHUNKS") ? atoi(getenv("NCM_B200_ATTN_DEC_MMA_MAX_CHUNKS")) : 16;
-    const bool mma_pays = gq_w >= mma_min_g && max_chunks <= mma_max_ch && pairs * 4 >= (int64_t)ctx().sm_count;
+    const bool mma_pays = (gq_w >= mma_min_g && max_chunks <= mma_max_ch && pairs * 4 >= (int64_t)ctx().sm_count) ||
+                          (gq_w >= 6 && pairs >= 2 * (int64_t)ctx().sm_count);
     if (mma_takes && (mma_env == 1 || (mma_env != 0 && mma_pays))) {
         // chunks per warp: as few CTAs per (row, kv head) as still give every SM about eight warps
         const int64_t want_ctas = std::max<int64_t>(1, cdiv((int64_t)ctx().sm_count * 2, pairs));
