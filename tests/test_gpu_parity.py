@@ -446,13 +446,19 @@ PPL_SPECS = {
 }
 
 
+@pytest.mark.parametrize("decode_attention", ["chosen", "tensor_core_rows"])
 @pytest.mark.parametrize("kind", ["gpt2", "qwen"])
-def test_batched_decode_steps_through_k_sliced_projections(cuda, tmp, kind):
+def test_batched_decode_steps_through_k_sliced_projections(cuda, tmp, kind, decode_attention, monkeypatch):
     """20 rows per decode step at width 768: too many rows for the GEMV path, few tiles and a long K for the
     tensor-core GEMM, so the attention-output and MLP-down projections run K in slices with a reduce kernel behind
-    them. Ids equal independent oracle runs."""
+    them. Ids equal independent oracle runs. Run a second time with the decode attention that makes the (query, head)
+    pairs of a kv group the rows of an mma.sync tile (what large batches of the grouped-query model get)."""
     import orc
     import synth
+    if decode_attention == "tensor_core_rows":
+        monkeypatch.setenv("NCM_B200_ATTN_DEC_MMA", "1")
+    else:
+        monkeypatch.delenv("NCM_B200_ATTN_DEC_MMA", raising=False)
     if kind == "gpt2":
         spec = synth.LMSpec("gpt2_w768", "gpt2", 1, 768, 12, 12, 3072, 300, 32, rand_affine=1)
     else:
