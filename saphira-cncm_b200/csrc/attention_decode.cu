@@ -437,8 +437,8 @@ __global__ void __launch_bounds__(256) k_attention_dec_warp(AttnDecDev a) {
 // probabilities cross from the accumulator layout to the A-fragment layout through 2 KB of shared memory per warp.
 // Loads run a phase ahead of the arithmetic (the next chunk's keys are requested when the score MMAs are done with
 // their registers, the chunk's values before its score MMAs).
-// A warp walks `cps` consecutive chunks with a running maximum and sum per row; the four warps of a CTA take
-// consecutive runs of the same (row, kv head) and their partials meet in shared memory; one partial per CTA goes to
+// A warp walks `cps` chunks with a running maximum and sum per row; the four warps of a CTA take every fourth chunk
+// of the CTA's stretch of the (row, kv head)'s keys and their partials meet in shared memory; one partial per CTA goes to
 // global memory, and only when the row needs more than one CTA (last CTA merges, as above). The tcgen05 path needs
 // 64 rows at least: for 16 it would idle three quarters of the tile.
 constexpr int ADM_WARPS = 4;
@@ -481,7 +481,10 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
     const int per_warp = a.cps * 32, per_cta = ADM_WARPS * per_warp;
     const int nsplit = (n1 + per_cta - 1) / per_cta;
     if (sp >= nsplit) return;
-    const int kbeg = sp * per_cta + warp * per_warp;          // first key of this warp's run
+    // the CTA's chunks are dealt to its warps in turn (warp w takes chunks w, w + 4, ...): rows shorter than the
+    // longest the launch was sized for -- early steps of a graph-replayed decode loop -- still occupy all four warps
+    const int kbeg = sp * per_cta + warp * 32;                // first key of this warp's first chunk
+    constexpr int KSTEP = ADM_WARPS * 32;                     // keys from one of its chunks to the next
     const int q0 = a.q_start[row], nq = a.q_start[row + 1] - q0;
     const int G = Gh * nq;                                    // virtual heads (tile rows): vh = g * nq + qi
     auto krow = [&](int j) -> const float * {
@@ -526,7 +529,7 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
     };
     if (kbeg < n1) load_k(kbeg);
     for (int c = 0; c < a.cps; c++) {
-        const int kc = kbeg + c * 32;
+        const int kc = kbeg + c * KSTEP;
         if (kc >= n1) break;                                  // warp-uniform
         // the chunk's values: k-step s takes keys kc + 8 s + tig (b0) and + 4 (b1); column gid of output tile j is dim
         // 8 gid + j, so the lane's eight dims of a value row are two 16-byte loads
@@ -561,7 +564,7 @@ __global__ void __launch_bounds__(ADM_WARPS * 32, ADM_MINB) k_attention_dec_mma(
                 adm_mma(sacc[j], ah1, bh0, bh1);
             }
         }
-        if (c + 1 < a.cps && kc + 32 < n1) load_k(kc + 32);    // the next chunk's keys, under the rest of this chunk
+        if (c + 1 < a.cps && kc + KSTEP < n1) load_k(kc + KSTEP);   // the next chunk's keys, under the rest of this chunk
         // ---- softmax of the chunk, rows gid (c0, c1) and gid + 8 (c2, c3); columns 8 j + 2 tig, + 1 ----
         float cm0 = -INFINITY, cm1 = -INFINITY;
 #pragma unroll
